@@ -1,0 +1,481 @@
+/*
+ * quamba_b200 -- C ABI of the B200 (sm_100a) quantized Mamba mixer kernels.
+ *
+ * Every entry point takes a pointer to a plain-old-data argument struct and the CUDA
+ * stream to enqueue on (a cudaStream_t passed as void*), returns a qb_status, never
+ * synchronises the host, never allocates device memory, and borrows every buffer.
+ * Device pointers are raw addresses on the current device; strides are in ELEMENTS.
+ * Scales that the reference passes as CUDA tensors stay device pointers (const float*);
+ * scales that the reference passes as Python floats are floats by value.
+ *
+ * The struct definitions below are also parsed by the Python loader (one field per
+ * line, "type name;"), so keep that shape when editing.
+ *
+ * "Replaces" comments cite the reference interface (path inside the reference project).
+ */
+#ifndef QUAMBA_B200_H_
+#define QUAMBA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  QB_OK = 0,
+  QB_ERR_INVALID_ARG = -1, /* shape / stride / alignment / null pointer rejected on the host */
+  QB_ERR_UNSUPPORTED = -2, /* a configuration the reference also rejects, or not built yet  */
+  QB_ERR_CUDA = -3,        /* a CUDA runtime call or launch failed                          */
+  QB_ERR_TIMEOUT = -4,     /* a bounded device-side wait expired (read from a status word)  */
+  QB_ERR_TOO_LARGE = -5    /* a size beyond a stated maximum                                */
+} qb_status;
+
+/* Human-readable text of the last non-OK status returned on the calling thread. */
+const char* qb_last_error(void);
+/* Library ABI version (bumped when a struct changes). */
+int qb_abi_version(void);
+/* sizeof() of an argument struct by name, for binding self-checks; -1 if unknown. */
+int64_t qb_sizeof(const char* struct_name);
+/* Synchronises `stream`, then returns and clears the device status word: QB_OK, or QB_ERR_TIMEOUT
+ * if a kernel gave up on a bounded wait (its outputs are then undefined).  The only entry point
+ * that blocks the host. */
+int qb_read_device_status(void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * int8 causal conv1d, Quamba1 (one scale set for all channels).
+ * Replaces quant_causal_conv1d_cuda.fwd / .update
+ *   (csrc/causal_conv1d/quant_causal_conv1d.cpp:77-164, :168-226).
+ * y = silu( scale_w*scale_x * sum_w w[c,w] x[c, l-(W-1-w)] + scale_b*bias[c] ),
+ * q_y = clamp(roundf(y / scale_out)).  x (B, D, L) with either L or D contiguous
+ * (x_sl == 1 or x_sd == 1); out has the same strides as x.  width 2..4.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const int8_t* x;
+  int8_t* out;
+  const int8_t* weight;
+  const int8_t* bias;
+  int64_t x_sb;
+  int64_t x_sd;
+  int64_t x_sl;
+  int64_t out_sb;
+  int64_t out_sd;
+  int64_t out_sl;
+  int32_t batch;
+  int32_t dim;
+  int32_t seqlen;
+  int32_t width;
+  float scale_x;
+  float scale_w;
+  float scale_out;
+  float scale_b;
+  int32_t silu;
+} qb_conv1d_fwd_args;
+int qb_causal_conv1d_fwd(const qb_conv1d_fwd_args* a, void* stream);
+
+/* Decode step: conv_state (B, D, W) int8 (any strides) is shifted left by one and x appended,
+ * in place; out (B, D) int8. */
+typedef struct {
+  const int8_t* x;
+  int8_t* conv_state;
+  int8_t* out;
+  const int8_t* weight;
+  const int8_t* bias;
+  int64_t x_sb;
+  int64_t x_sd;
+  int64_t state_sb;
+  int64_t state_sd;
+  int64_t state_sw;
+  int64_t out_sb;
+  int64_t out_sd;
+  int32_t batch;
+  int32_t dim;
+  int32_t width;
+  float scale_x;
+  float scale_w;
+  float scale_out;
+  float scale_b;
+  int32_t silu;
+} qb_conv1d_update_args;
+int qb_causal_conv1d_update(const qb_conv1d_update_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * int8 causal conv1d, Quamba2: one pass over the concatenated [x | B | C] channels with
+ * per-segment input / weight / bias scales, per-(ssd group, head group, dim group) output
+ * scales for x and per-ssd-group output scales for B and C; writes three tensors.
+ * Replaces quamba2_conv1d_cuda.fwd / .update
+ *   (csrc/causal_conv1d/quamba2_conv1d.cpp:122-260, :263-380).
+ * xBC (B, dim, L) channel-last: element (b, c, l) at b*xBC_sb + l*xBC_sl + c.
+ * Outputs x (B, L, x_dim), Bm / Cm (B, L, d_state*n_groups), all contiguous.
+ * head_group_range / dim_group_range null  =>  x_scales, B_scales, C_scales have 1 element.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const int8_t* xBC;
+  int8_t* x;
+  int8_t* Bm;
+  int8_t* Cm;
+  const int8_t* weight;
+  const int8_t* bias;
+  const int32_t* head_group_range;
+  const int32_t* dim_group_range;
+  const float* x_scales;
+  const float* B_scales;
+  const float* C_scales;
+  int64_t xBC_sb;
+  int64_t xBC_sl;
+  int32_t batch;
+  int32_t dim;
+  int32_t seqlen;
+  int32_t width;
+  int32_t x_dim;
+  int32_t x_headdim;
+  int32_t d_state;
+  int32_t n_groups;
+  int32_t nhead_groups;
+  int32_t ndim_groups;
+  float scale_x;
+  float scale_B;
+  float scale_C;
+  float scale_wx;
+  float scale_wB;
+  float scale_wC;
+  float scale_bx;
+  float scale_bB;
+  float scale_bC;
+  int32_t silu;
+} qb_quamba2_conv1d_fwd_args;
+int qb_quamba2_conv1d_fwd(const qb_quamba2_conv1d_fwd_args* a, void* stream);
+
+/* Decode step: xBC (B, dim); conv_state element (b, c, w) at b*state_sb + c*state_sd + w*state_sw,
+ * updated in place; outputs x (B, x_dim), Bm / Cm (B, d_state*n_groups) contiguous. */
+typedef struct {
+  const int8_t* xBC;
+  int8_t* conv_state;
+  int8_t* x;
+  int8_t* Bm;
+  int8_t* Cm;
+  const int8_t* weight;
+  const int8_t* bias;
+  const int32_t* head_group_range;
+  const int32_t* dim_group_range;
+  const float* x_scales;
+  const float* B_scales;
+  const float* C_scales;
+  int64_t xBC_sb;
+  int64_t state_sb;
+  int64_t state_sd;
+  int64_t state_sw;
+  int32_t batch;
+  int32_t dim;
+  int32_t width;
+  int32_t x_dim;
+  int32_t x_headdim;
+  int32_t d_state;
+  int32_t n_groups;
+  int32_t nhead_groups;
+  int32_t ndim_groups;
+  float scale_x;
+  float scale_B;
+  float scale_C;
+  float scale_wx;
+  float scale_wB;
+  float scale_wC;
+  float scale_bx;
+  float scale_bB;
+  float scale_bC;
+  int32_t silu;
+} qb_quamba2_conv1d_update_args;
+int qb_quamba2_conv1d_update(const qb_quamba2_conv1d_update_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused Hadamard rotation + int8 quantisation: out = sat_int8(roundf((H_dim x) * scale)).
+ * Replaces quant_hadamard.fast_hadamard_transform{,_12N,_20N,_28N,_40N}
+ *   (csrc/hadamard/quant_hadamard.cpp:72-294).
+ * x (rows, dim) row-contiguous, in_dtype 0 = fp16, 1 = bf16, 2 = fp32.  special = 1 (dim a power
+ * of two) or 12 / 20 / 28 / 40 (dim = special * 2^k).  Unlike the reference (which casts an
+ * out-of-range float to int8, undefined), the result saturates to [-128, 127].
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const void* x;
+  int8_t* out;
+  int64_t x_row_stride;
+  int64_t out_row_stride;
+  int64_t rows;
+  int32_t dim;
+  int32_t special;
+  int32_t in_dtype;
+  float scale;
+} qb_hadamard_quant_args;
+int qb_hadamard_quant(const qb_hadamard_quant_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Mamba1 int8 selective scan forward.
+ * Replaces quant_sscan_cuda.fwd (csrc/selective_scan/quant_sscan.cpp:122-265).
+ * u, delta, z: (B, D, L) int8, L contiguous.  Bm, Cm: (B, G, N, L) int8, L contiguous.
+ * A_log (D, N) int8, D / delta_bias (D) int8 (nullable).  out: (B, L, D) fp16 contiguous (the
+ * transposed layout the reference returns).  x_states: (B, D, nchunks, N) int8, nchunks =
+ * ceil(L / 2048): the state after each 2048-step chunk, quantised with roundf + clamp.
+ * All *_scale are device pointers to one float.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const int8_t* u;
+  const int8_t* delta;
+  const int8_t* z;
+  const int8_t* Bm;
+  const int8_t* Cm;
+  const int8_t* A_log;
+  const int8_t* D;
+  const int8_t* delta_bias;
+  const float* u_scale;
+  const float* delta_scale;
+  const float* z_scale;
+  const float* B_scale;
+  const float* C_scale;
+  const float* A_scale;
+  const float* D_scale;
+  const float* delta_bias_scale;
+  const float* ssm_state_scale;
+  void* out;
+  int8_t* x_states;
+  int64_t u_sb;
+  int64_t u_sd;
+  int64_t delta_sb;
+  int64_t delta_sd;
+  int64_t z_sb;
+  int64_t z_sd;
+  int64_t B_sb;
+  int64_t B_sg;
+  int64_t B_sn;
+  int64_t C_sb;
+  int64_t C_sg;
+  int64_t C_sn;
+  int32_t batch;
+  int32_t dim;
+  int32_t seqlen;
+  int32_t dstate;
+  int32_t n_groups;
+  int32_t delta_softplus;
+} qb_sscan_fwd_args;
+int qb_sscan_fwd(const qb_sscan_fwd_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Single-step state update (decode), int8 state updated in place.
+ * Replaces quant_sscan_update_triton / quamba2_sscan_update_triton
+ *   (quamba/triton/selective_state_update.py:129-227, :365-478).
+ * state (B, H, P, N) int8 contiguous in N (Mamba1: H = 1, P = d_inner).  x (B, H, P) int8;
+ * dt int8 with strides (dt_sb, dt_sh, dt_sp) (dt_sp = 0 when tied across P); A_log int8 with
+ * strides (A_sh, A_sp, A_sn) (0 strides when tied); Bm / Cm (B, G, N) int8; D int8 strides
+ * (D_sh, D_sp), nullable; z like x, nullable.  dt_bias: int8 + dt_bias_scale (Mamba1), or fp16
+ * added unscaled when dt_bias_is_half != 0 (Mamba2); strides (bias_sh, bias_sp).
+ * Scale layouts: per-tensor (grouped == 0: x_scales / state_scale / B_scale / C_scale point to
+ * one float) or grouped (x_scales [G,HG,DG], state_scale [G,HG,DG,N], B_scale / C_scale [G],
+ * ranges as in the conv).  State requantised with rint (half to even) + clamp; out (B, H, P)
+ * fp16 uses the un-requantised fp32 state.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  int8_t* state;
+  const int8_t* x;
+  const int8_t* dt;
+  const int8_t* A_log;
+  const int8_t* Bm;
+  const int8_t* Cm;
+  const int8_t* D;
+  const int8_t* z;
+  const void* dt_bias;
+  const float* x_scales;
+  const float* dt_scale;
+  const float* A_scale;
+  const float* state_scale;
+  const float* B_scale;
+  const float* C_scale;
+  const float* D_scale;
+  const float* z_scale;
+  const float* dt_bias_scale;
+  const int32_t* head_group_range;
+  const int32_t* dim_group_range;
+  void* out;
+  int64_t state_sb;
+  int64_t state_sh;
+  int64_t state_sp;
+  int64_t x_sb;
+  int64_t x_sh;
+  int64_t dt_sb;
+  int64_t dt_sh;
+  int64_t dt_sp;
+  int64_t A_sh;
+  int64_t A_sp;
+  int64_t A_sn;
+  int64_t B_sb;
+  int64_t B_sg;
+  int64_t C_sb;
+  int64_t C_sg;
+  int64_t D_sh;
+  int64_t D_sp;
+  int64_t z_sb;
+  int64_t z_sh;
+  int64_t bias_sh;
+  int64_t bias_sp;
+  int64_t out_sb;
+  int64_t out_sh;
+  int32_t batch;
+  int32_t nheads;
+  int32_t headdim;
+  int32_t dstate;
+  int32_t ngroups;
+  int32_t grouped;
+  int32_t nhead_groups;
+  int32_t ndim_groups;
+  int32_t dt_bias_is_half;
+  int32_t dt_softplus;
+} qb_sscan_update_args;
+int qb_sscan_update(const qb_sscan_update_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Mamba2 int8 SSD chunk scan with inter-chunk state passing.
+ * Replaces _quant_mamba_chunk_scan_combined_fwd / _quamba2_mamba_chunk_scan_combined_fwd
+ *   (quamba/triton/quant_ssd_combined.py:11-81, :84-166) and the six Triton kernels below them.
+ * x (B, L, H, P) int8, P contiguous, strides (x_sb, x_sl, x_sh); dt (B, L, H) int8 with strides
+ * (dt_sb, dt_sl), H contiguous; Bm / Cm (B, L, G, N) int8, N contiguous, strides (sb, sl, sg);
+ * A_log (H) int8; D (H) or (H, P) int8, nullable; dt_bias (H) fp16, nullable; z like x, nullable.
+ * out (B, L, H, P) fp16 contiguous; final_states (B, H, P, N) int8 contiguous (rint + clamp).
+ * Scales: grouped == 0 => x_scales / ssm_state_scale / B_scale / C_scale point to one float;
+ * grouped != 0 => [G,HG,DG], [G,HG,DG,N], [G], [G] with the cumulative range tables.
+ * workspace: device scratch of at least qb_ssd_workspace_bytes() bytes, 256-byte aligned;
+ * contents are undefined on entry and on exit.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const int8_t* x;
+  const int8_t* dt;
+  const int8_t* Bm;
+  const int8_t* Cm;
+  const int8_t* A_log;
+  const int8_t* D;
+  const int8_t* z;
+  const void* dt_bias;
+  const float* x_scales;
+  const float* dt_scale;
+  const float* A_scale;
+  const float* B_scale;
+  const float* C_scale;
+  const float* D_scale;
+  const float* z_scale;
+  const float* ssm_state_scale;
+  const int32_t* head_group_range;
+  const int32_t* dim_group_range;
+  void* out;
+  int8_t* final_states;
+  void* workspace;
+  int64_t workspace_bytes;
+  int64_t x_sb;
+  int64_t x_sl;
+  int64_t x_sh;
+  int64_t dt_sb;
+  int64_t dt_sl;
+  int64_t B_sb;
+  int64_t B_sl;
+  int64_t B_sg;
+  int64_t C_sb;
+  int64_t C_sl;
+  int64_t C_sg;
+  int64_t z_sb;
+  int64_t z_sl;
+  int64_t z_sh;
+  int32_t batch;
+  int32_t seqlen;
+  int32_t nheads;
+  int32_t headdim;
+  int32_t ngroups;
+  int32_t dstate;
+  int32_t chunk_size;
+  int32_t grouped;
+  int32_t nhead_groups;
+  int32_t ndim_groups;
+  int32_t D_has_hdim;
+  int32_t dt_softplus;
+  float dt_min;
+  float dt_max;
+} qb_ssd_args;
+int64_t qb_ssd_workspace_bytes(int32_t batch, int32_t seqlen, int32_t nheads, int32_t headdim,
+                               int32_t ngroups, int32_t dstate, int32_t chunk_size);
+int qb_ssd_chunk_scan_fwd(const qb_ssd_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * W4A8 linears (Marlin-QQQ packed int4 weights, int8 activations).
+ * Replaces quant_linear_cuda.w4a8o16_gemm / w4a8o8_gemm
+ *   (csrc/linear/marlin_qqq_gemm_kernel.cuh:1187-1314, marlin_qqq_gemm_kernel_o8.cuh:1199-).
+ *
+ * qb_w4a8_unpack converts the module's buffers (weight int32 (K/16, N*16/8) in the Marlin-QQQ
+ * tile order, s_group fp16 (K/128, N) and s_channel fp32 (1, N) in their permuted orders) into
+ * the layout the B200 kernels stream: w8 int8 (N, K) K-contiguous holding exactly the int8
+ * values the reference multiplies with (per-group: (q-8)*s_group rounded half-to-even by one
+ * fp16 fma; per-channel: 16*q), and s_channel_nat fp32 (N) in natural column order.  It is a
+ * one-time (or per-call, it is cheap) preparation; s_group == null selects per-channel.
+ *
+ * qb_w4a8_gemm: acc = a (M,K) int8 @ w8^T, out = acc * s_channel[n] * s_tok -> fp16 (cvt.rn) or
+ * int8 (cvt.rni, saturating); s_tok has 1 element or M elements (s_tok_per_row).  out is (M, N)
+ * row-major, or (N, M) when output_transpose != 0.  out_row_stride in elements.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const int32_t* packed;
+  const void* s_group;
+  const float* s_channel;
+  int8_t* w8;
+  float* s_channel_nat;
+  int32_t size_k;
+  int32_t size_n;
+  int32_t group_size;
+} qb_w4a8_unpack_args;
+int qb_w4a8_unpack(const qb_w4a8_unpack_args* a, void* stream);
+
+typedef struct {
+  const int8_t* a;
+  const int8_t* w8;
+  const float* s_channel_nat;
+  const float* s_tok;
+  void* out;
+  int64_t a_row_stride;
+  int64_t out_row_stride;
+  int32_t m;
+  int32_t n;
+  int32_t k;
+  int32_t s_tok_per_row;
+  int32_t out_int8;
+  int32_t output_transpose;
+} qb_w4a8_gemm_args;
+int qb_w4a8_gemm(const qb_w4a8_gemm_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * W8A8 linears.
+ * Replaces quant_linear_cuda.cutlass_scaled_mm_dq / cutlass_scaled_mv_dq / w8a8o8_gemv
+ *   (csrc/linear/quant_linear_fwd_kernel.cuh:356-401, quant_linear_fwd_gemv_kernel.cuh:96-134).
+ * D (M, N) = cvt( a_scale (.) ( b_scale (.) float(A (M,K) @ B (K,N)) ) ) with A row-major
+ * (a_row_stride) and B column-major (element (k, n) at n*b_col_stride + k); a_scale has 1 or M
+ * elements, b_scale 1 or N.  out_dtype 0 = int8 (round half to even, saturating), 1 = fp16,
+ * 2 = bf16.  The "mv" forms of the reference are this call with M = 1 and the scalars in
+ * alpha (by value, use_alpha != 0) or roundf rounding (round_half_away != 0, w8a8o8_gemv).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const int8_t* a;
+  const int8_t* b;
+  const float* a_scale;
+  const float* b_scale;
+  void* out;
+  int64_t a_row_stride;
+  int64_t b_col_stride;
+  int64_t out_row_stride;
+  int32_t m;
+  int32_t n;
+  int32_t k;
+  int32_t a_scale_per_row;
+  int32_t b_scale_per_col;
+  int32_t out_dtype;
+  int32_t use_alpha;
+  int32_t round_half_away;
+  float alpha;
+} qb_w8a8_gemm_args;
+int qb_w8a8_gemm(const qb_w8a8_gemm_args* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUAMBA_B200_H_ */

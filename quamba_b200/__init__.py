@@ -1,0 +1,17 @@
+"""quamba_b200: the quantized Mamba mixer hot path of Quamba on B200 (sm_100a).
+
+Hand-written CUDA behind a C ABI (include/quamba_b200.h, libquamba_b200.so), wrapped with the
+reference's own extension-level and module-level interfaces:
+
+    from quamba_b200 import ops                 # quant_sscan_cuda, quamba2_conv1d_cuda, ...
+    from quamba_b200 import QSScan, Quamba2ChunkScan, QCausalConv1D, Quamb2Conv1D, QHadamard, \
+        W4A8B16O16Linear, W4A8B8O8Linear, W4A8B8O8LinearParallel, W8A8B8O8Linear, \
+        W8A8B8O8LinearParallel, W8A8B16O16Linear
+
+Importing the package does not touch the GPU; the shared library is loaded on first use and
+its absence is an error (there is no CPU or PyTorch fallback).
+"""
+from . import _lib  # noqa: F401
+from . import ops  # noqa: F401
+
+__version__ = "0.1.0"

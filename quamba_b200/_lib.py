@@ -1,0 +1,102 @@
+"""ctypes binding of libquamba_b200.so.
+
+The argument structs are generated from ``include/quamba_b200.h`` at import time (the
+header keeps one ``type name;`` field per line for exactly this purpose), so the C ABI
+has a single source of truth.  There is no CPU fallback: if the shared library is
+missing, importing this module raises.
+"""
+import ctypes
+import re
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+HEADER = _PKG.parent / "include" / "quamba_b200.h"
+LIB_PATH = _PKG / "libquamba_b200.so"
+
+_CTYPES = {
+    "int64_t": ctypes.c_int64,
+    "int32_t": ctypes.c_int32,
+    "int": ctypes.c_int32,
+    "float": ctypes.c_float,
+}
+
+QB_OK = 0
+QB_ERR_INVALID_ARG = -1
+QB_ERR_UNSUPPORTED = -2
+QB_ERR_CUDA = -3
+QB_ERR_TIMEOUT = -4
+QB_ERR_TOO_LARGE = -5
+
+
+def parse_header(text: str):
+    """Return ({struct_name: [(field, ctype), ...]}, [function names])."""
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    structs = {}
+    for body, name in re.findall(r"typedef\s+struct\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
+        fields = []
+        for line in body.strip().splitlines():
+            line = line.strip()
+            if not line:
+                continue
+            m = re.match(r"^(.*?)(\w+)\s*;$", line)
+            ctype_txt, fname = m.group(1).strip(), m.group(2)
+            if "*" in ctype_txt:
+                ct = ctypes.c_void_p
+            else:
+                ct = _CTYPES[ctype_txt.replace("const", "").strip()]
+            fields.append((fname, ct))
+        structs[name] = fields
+    funcs = re.findall(r"^\s*(?:const\s+char\s*\*|int64_t|int)\s+(qb_\w+)\s*\(", text, flags=re.M)
+    return structs, funcs
+
+
+_STRUCT_FIELDS, FUNCTIONS = parse_header(HEADER.read_text())
+STRUCTS = {name: type(name, (ctypes.Structure,), {"_fields_": fields}) for name, fields in _STRUCT_FIELDS.items()}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m quamba_b200.build` (nvcc, sm_100a). "
+                "quamba_b200 has no CPU or PyTorch fallback.")
+        _lib = ctypes.CDLL(str(LIB_PATH))
+        _lib.qb_last_error.restype = ctypes.c_char_p
+        _lib.qb_sizeof.restype = ctypes.c_int64
+        _lib.qb_sizeof.argtypes = [ctypes.c_char_p]
+        _lib.qb_ssd_workspace_bytes.restype = ctypes.c_int64
+        _lib.qb_ssd_workspace_bytes.argtypes = [ctypes.c_int32] * 7
+        _lib.qb_read_device_status.argtypes = [ctypes.c_void_p]
+        for name, st in STRUCTS.items():
+            got = _lib.qb_sizeof(name.encode())
+            if got != ctypes.sizeof(st):
+                raise RuntimeError(f"ABI mismatch for {name}: library {got} bytes, binding {ctypes.sizeof(st)}")
+    return _lib
+
+
+def make(struct_name: str, **kw):
+    st = STRUCTS[struct_name]()
+    names = {f for f, _ in st._fields_}
+    for k, v in kw.items():
+        if k not in names:
+            raise KeyError(f"{struct_name} has no field {k}")
+        setattr(st, k, v)
+    return st
+
+
+def check(status: int):
+    if status != QB_OK:
+        msg = lib().qb_last_error().decode(errors="replace")
+        raise RuntimeError(f"quamba_b200 error {status}: {msg}")
+
+
+def call(fn: str, args, stream: int):
+    f = getattr(lib(), fn)
+    check(f(ctypes.byref(args), ctypes.c_void_p(stream)))
+
+
+def read_device_status(stream: int):
+    check(lib().qb_read_device_status(ctypes.c_void_p(stream)))

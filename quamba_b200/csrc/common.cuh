@@ -1,0 +1,99 @@
+// Shared host/device helpers for the quamba_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/quamba_b200.h"
+
+namespace qb {
+
+// ---- host-side error reporting --------------------------------------------------------------
+void set_error(const char* fmt, ...);
+
+#define QB_REQUIRE(cond, code, ...)        \
+  do {                                     \
+    if (!(cond)) {                         \
+      ::qb::set_error(__VA_ARGS__);        \
+      return (code);                       \
+    }                                      \
+  } while (0)
+
+#define QB_CUDA_OK(expr)                                                         \
+  do {                                                                           \
+    cudaError_t e__ = (expr);                                                    \
+    if (e__ != cudaSuccess) {                                                    \
+      ::qb::set_error("%s failed: %s", #expr, cudaGetErrorString(e__));          \
+      return QB_ERR_CUDA;                                                        \
+    }                                                                            \
+  } while (0)
+
+#define QB_LAUNCH_OK(name)                                                       \
+  do {                                                                           \
+    cudaError_t e__ = cudaGetLastError();                                        \
+    if (e__ != cudaSuccess) {                                                    \
+      ::qb::set_error("launch of %s failed: %s", name, cudaGetErrorString(e__)); \
+      return QB_ERR_CUDA;                                                        \
+    }                                                                            \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+int sm_count();  // multiprocessor count of the current device (cached per device)
+
+// ---- device helpers ------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// x * sigmoid(x) with one MUFU op: sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5.
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float silu_fast(float v) {
+  const float h = 0.5f * v;
+  return fmaf(h, tanh_approx(h), h);
+}
+// v / (1 + exp(-v)) evaluated the long way (exp2 + divide): used where the result stays fp16.
+__device__ __forceinline__ float silu_exact(float v) { return v / (1.0f + __expf(-v)); }
+
+// 2^x on the MUFU pipe (flushes denormal results to zero).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// x <= 20 ? log1p(exp(x)) : x
+__device__ __forceinline__ float softplus_f(float x) { return x <= 20.0f ? log1pf(__expf(x)) : x; }
+
+// C roundf (halves away from zero) followed by a clamp to int8, as one int.
+__device__ __forceinline__ int round_away_s8(float v) {
+  int r = __float2int_rz(v + copysignf(0.5f, v));
+  return max(-128, min(127, r));
+}
+// rint (halves to even) + clamp.
+__device__ __forceinline__ int rint_s8(float v) {
+  int r = __float2int_rn(v);
+  return max(-128, min(127, r));
+}
+// pack four already-clamped ints into one little-endian word of int8
+__device__ __forceinline__ uint32_t pack4_s8(int a, int b, int c, int d) {
+  return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)d << 24);
+}
+
+// Grouped ("group_heads") lookup: number of cumulative range ends <= idx, clamped to n-1.
+__device__ __forceinline__ int group_lookup(const int32_t* range, int n, int idx) {
+  int g = 0;
+  for (int i = 0; i < n; ++i) g += (idx >= range[i]) ? 1 : 0;
+  return min(g, n - 1);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace qb

@@ -1,0 +1,416 @@
+// int8 causal depthwise conv1d (+bias, SiLU, int8 requantisation) for sm_100a.
+//
+// Both layouts are pure streaming passes (1 byte in, 1 byte out per element), so the kernels
+// are organised around 16-byte coalesced loads/stores and keep the arithmetic per element to
+// one byte-permute (window slide), one dp4a (the <=4 taps), one fma, one tanh.approx (SiLU)
+// and the rounding.
+//
+//   channel-last  (Quamba2 xBC, and Quamba1 when the channel stride is 1): a thread owns 16
+//                 adjacent channels and walks TL consecutive time steps, keeping each channel's
+//                 last four samples packed in one register.
+//   sequence-last (Quamba1 (B, D, L) with L contiguous): a thread owns 16 adjacent time steps
+//                 of one (batch, channel) row; windows are funnel shifts of adjacent words.
+#include "common.cuh"
+
+namespace qb {
+namespace {
+
+constexpr int kVec = 16;  // channels (or time steps) per thread = one 16-byte access
+
+struct ClSegments {
+  // Three output segments [0, end0), [end0, end1), [end1, dim) of the channel axis.
+  int8_t* dst[3];
+  int64_t dst_sb[3];
+  int64_t dst_sl[3];
+  int end0, end1;
+  float scale_in[3];    // scale_w * scale_x per segment
+  float scale_bias[3];  // bias scale per segment
+  const float* out_scales[3];  // out_scales[0] == nullptr => out_scale_value (scale by value)
+  float out_scale_value;
+  // grouped x scales (segment 0 only)
+  const int32_t* head_group_range;
+  const int32_t* dim_group_range;
+  int nhead_groups, ndim_groups, headdim, x_group_size, d_state;
+  int grouped;
+};
+
+// weight bytes (C, W) -> one word whose byte i multiplies window byte i (= x[l-3+i])
+__device__ __forceinline__ int pack_taps(const int8_t* w, int width) {
+  uint32_t r = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int tap = i - (4 - width);
+    const uint32_t v = tap >= 0 ? (uint32_t)(uint8_t)w[tap] : 0u;
+    r |= v << (8 * i);
+  }
+  return (int)r;
+}
+
+__global__ void __launch_bounds__(128)
+conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t in_sl,
+                           const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
+                           ClSegments seg, int batch, int dim, int seqlen, int width, int tl,
+                           int nseg, int silu) {
+  const int cv = dim / kVec;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)batch * nseg * cv;
+  if (idx >= total) return;
+  const int vec = (int)(idx % cv);
+  const int sg = (int)((idx / cv) % nseg);
+  const int b = (int)(idx / ((int64_t)cv * nseg));
+  const int c0 = vec * kVec;
+  const int s = c0 < seg.end0 ? 0 : (c0 < seg.end1 ? 1 : 2);
+  const int cbase = s == 0 ? 0 : (s == 1 ? seg.end0 : seg.end1);
+
+  int wpk[kVec];
+  float hb[kVec], inv_out[kVec];
+  const float hs_in = 0.5f * seg.scale_in[s];
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) {
+    const int c = c0 + j;
+    wpk[j] = pack_taps(weight + (int64_t)c * width, width);
+    hb[j] = bias != nullptr ? 0.5f * seg.scale_bias[s] * (float)bias[c] : 0.0f;
+    float so;
+    if (seg.out_scales[0] == nullptr) {
+      so = seg.out_scale_value;
+    } else if (!seg.grouped) {
+      so = seg.out_scales[s][0];
+    } else if (s == 0) {
+      const int g = c / seg.x_group_size;
+      const int head = (c % seg.x_group_size) / seg.headdim;
+      const int d = c % seg.headdim;
+      const int hg = group_lookup(seg.head_group_range + g * seg.nhead_groups, seg.nhead_groups, head);
+      const int dg = group_lookup(seg.dim_group_range + (g * seg.nhead_groups + hg) * seg.ndim_groups,
+                                  seg.ndim_groups, d);
+      so = seg.out_scales[0][(g * seg.nhead_groups + hg) * seg.ndim_groups + dg];
+    } else {
+      so = seg.out_scales[s][(c - cbase) / seg.d_state];
+    }
+    inv_out[j] = 1.0f / so;
+  }
+
+  const int l0 = sg * tl;
+  const int l1 = min(seqlen, l0 + tl);
+  const int8_t* src = in + (int64_t)b * in_sb + c0;
+  int8_t* dst = seg.dst[s] + (int64_t)b * seg.dst_sb[s] + (c0 - cbase);
+  const int64_t dsl = seg.dst_sl[s];
+
+  // windows: byte i of win[j] = x[l-3+i] of channel j
+  uint32_t win[kVec];
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) win[j] = 0;
+#pragma unroll
+  for (int h = 3; h >= 1; --h) {
+    const int l = l0 - h;
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (l >= 0) r = *reinterpret_cast<const uint4*>(src + (int64_t)l * in_sl);
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) win[j] = __byte_perm(win[j], rw[j >> 2], 0x0321 | ((4 + (j & 3)) << 12));
+  }
+
+  constexpr int kUnroll = 4;
+  for (int l = l0; l < l1; l += kUnroll) {
+    uint4 rows[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      rows[u] = make_uint4(0, 0, 0, 0);
+      if (l + u < l1) rows[u] = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)(l + u) * in_sl));
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (l + u < l1) {
+        const uint32_t rw[4] = {rows[u].x, rows[u].y, rows[u].z, rows[u].w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int w4 = 0; w4 < 4; ++w4) {
+          int q[4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int j = w4 * 4 + jj;
+            win[j] = __byte_perm(win[j], rw[w4], 0x0321 | ((4 + jj) << 12));
+            const int acc = __dp4a((int)win[j], wpk[j], 0);
+            const float h = fmaf((float)acc, hs_in, hb[j]);  // half of the pre-activation
+            const float y = silu ? fmaf(h, tanh_approx(h), h) : 2.0f * h;
+            q[jj] = round_away_s8(y * inv_out[j]);
+          }
+          ow[w4] = pack4_s8(q[0], q[1], q[2], q[3]);
+        }
+        *reinterpret_cast<uint4*>(dst + (int64_t)(l + u) * dsl) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
+    }
+  }
+}
+
+// Sequence-last layout.  One thread = 16 consecutive time steps of one (b, d) row.
+__global__ void __launch_bounds__(128)
+conv1d_seq_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t in_sd,
+                       int8_t* __restrict__ out, int64_t out_sb, int64_t out_sd,
+                       const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
+                       int batch, int dim, int seqlen, int width, float scale_in, float scale_bias,
+                       float scale_out, int silu, int vec_ok) {
+  const int nv = (seqlen + kVec - 1) / kVec;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)batch * dim * nv;
+  if (idx >= total) return;
+  const int v = (int)(idx % nv);
+  const int d = (int)((idx / nv) % dim);
+  const int b = (int)(idx / ((int64_t)nv * dim));
+  const int8_t* src = in + (int64_t)b * in_sb + (int64_t)d * in_sd;
+  int8_t* dst = out + (int64_t)b * out_sb + (int64_t)d * out_sd;
+  const int l0 = v * kVec;
+  const int wpk = pack_taps(weight + (int64_t)d * width, width);
+  const float hs_in = 0.5f * scale_in;
+  const float hb = bias != nullptr ? 0.5f * scale_bias * (float)bias[d] : 0.0f;
+  const float inv_out = 1.0f / scale_out;
+
+  uint32_t w[5];  // w[0] = x[l0-4 .. l0-1], w[1..4] = x[l0 .. l0+15]
+  const bool full = vec_ok && (l0 + kVec <= seqlen);
+  if (full) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(src + l0));
+    w[1] = r.x; w[2] = r.y; w[3] = r.z; w[4] = r.w;
+    w[0] = l0 > 0 ? __ldg(reinterpret_cast<const uint32_t*>(src + l0 - 4)) : 0u;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      uint32_t t = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int l = l0 - 4 + i * 4 + k;
+        const uint32_t byte = (l >= 0 && l < seqlen) ? (uint32_t)(uint8_t)src[l] : 0u;
+        t |= byte << (8 * k);
+      }
+      w[i] = t;
+    }
+  }
+  uint32_t ow[4];
+#pragma unroll
+  for (int wi = 0; wi < 4; ++wi) {
+    int q[4];
+#pragma unroll
+    for (int off = 0; off < 4; ++off) {
+      const uint32_t window = off == 3 ? w[wi + 1] : __funnelshift_r(w[wi], w[wi + 1], 8 * (off + 1));
+      const int acc = __dp4a((int)window, wpk, 0);
+      const float h = fmaf((float)acc, hs_in, hb);
+      const float y = silu ? fmaf(h, tanh_approx(h), h) : 2.0f * h;
+      q[off] = round_away_s8(y * inv_out);
+    }
+    ow[wi] = pack4_s8(q[0], q[1], q[2], q[3]);
+  }
+  if (full) {
+    *reinterpret_cast<uint4*>(dst + l0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      if (l0 + i < seqlen) dst[l0 + i] = (int8_t)((ow[i >> 2] >> (8 * (i & 3))) & 0xff);
+    }
+  }
+}
+
+// Decode step, both flavours: one thread per (batch, channel).
+struct UpdSegments {
+  int8_t* dst[3];
+  int64_t dst_sb[3];
+  int64_t dst_sd[3];
+  int end0, end1;
+  float scale_in[3];
+  float scale_bias[3];
+  const float* out_scales[3];
+  float out_scale_value;  // used when out_scales[0] == nullptr (Quamba1: scale by value)
+  const int32_t* head_group_range;
+  const int32_t* dim_group_range;
+  int nhead_groups, ndim_groups, headdim, x_group_size, d_state;
+  int grouped;
+};
+
+__global__ void __launch_bounds__(128)
+conv1d_update_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd,
+                     int8_t* __restrict__ state, int64_t st_sb, int64_t st_sd, int64_t st_sw,
+                     const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
+                     UpdSegments seg, int batch, int dim, int width, int silu) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)batch * dim) return;
+  const int c = (int)(idx % dim);
+  const int b = (int)(idx / dim);
+  int8_t* st = state + (int64_t)b * st_sb + (int64_t)c * st_sd;
+  float acc = 0.0f;
+  // shift left by one, append x, accumulate the dot product in the same pass
+  for (int i = 0; i < width; ++i) {
+    const int8_t v = (i < width - 1) ? st[(int64_t)(i + 1) * st_sw] : x[(int64_t)b * x_sb + (int64_t)c * x_sd];
+    st[(int64_t)i * st_sw] = v;
+    acc += (float)weight[(int64_t)c * width + i] * (float)v;
+  }
+  const int s = c < seg.end0 ? 0 : (c < seg.end1 ? 1 : 2);
+  const int cbase = s == 0 ? 0 : (s == 1 ? seg.end0 : seg.end1);
+  float so;
+  if (seg.out_scales[0] == nullptr) {
+    so = seg.out_scale_value;
+  } else if (!seg.grouped) {
+    so = seg.out_scales[s][0];
+  } else if (s == 0) {
+    const int g = c / seg.x_group_size;
+    const int head = (c % seg.x_group_size) / seg.headdim;
+    const int d = c % seg.headdim;
+    const int hg = group_lookup(seg.head_group_range + g * seg.nhead_groups, seg.nhead_groups, head);
+    const int dg = group_lookup(seg.dim_group_range + (g * seg.nhead_groups + hg) * seg.ndim_groups,
+                                seg.ndim_groups, d);
+    so = seg.out_scales[0][(g * seg.nhead_groups + hg) * seg.ndim_groups + dg];
+  } else {
+    so = seg.out_scales[s][(c - cbase) / seg.d_state];
+  }
+  float v = seg.scale_in[s] * acc + (bias != nullptr ? seg.scale_bias[s] * (float)bias[c] : 0.0f);
+  if (silu) v = silu_fast(v);
+  seg.dst[s][(int64_t)b * seg.dst_sb[s] + (int64_t)(c - cbase) * seg.dst_sd[s]] = (int8_t)round_away_s8(v / so);
+}
+
+int pick_tl(int64_t rows_of_vectors, int seqlen) {
+  // Largest time tile that still leaves ~8 CTAs of 128 threads per SM; the 3-row halo re-read
+  // costs 3/TL extra L2 traffic, so prefer long tiles when the problem is large enough.
+  const int64_t want = (int64_t)sm_count() * 8 * 128;
+  for (int tl = 64; tl >= 8; tl >>= 1) {
+    if (rows_of_vectors * ceil_div(seqlen, tl) >= want) return tl;
+  }
+  return 8;
+}
+
+}  // namespace
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qb_quamba2_conv1d_fwd(const qb_quamba2_conv1d_fwd_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr, QB_ERR_INVALID_ARG, "quamba2_conv1d_fwd: null args");
+  QB_REQUIRE(a->xBC && a->x && a->Bm && a->Cm && a->weight && a->x_scales && a->B_scales && a->C_scales,
+             QB_ERR_INVALID_ARG, "quamba2_conv1d_fwd: null tensor pointer");
+  QB_REQUIRE(a->batch > 0 && a->dim > 0 && a->seqlen > 0, QB_ERR_INVALID_ARG, "quamba2_conv1d_fwd: empty shape");
+  QB_REQUIRE(a->width >= 2 && a->width <= 4, QB_ERR_INVALID_ARG,
+             "causal_conv1d only supports width between 2 and 4");
+  const int gn = a->d_state * a->n_groups;
+  QB_REQUIRE(a->x_dim + 2 * gn == a->dim, QB_ERR_INVALID_ARG, "x_dim + 2*d_state*n_groups must be equal to total dim");
+  QB_REQUIRE(a->x_headdim > 0 && a->x_dim % a->x_headdim == 0, QB_ERR_INVALID_ARG, "x_dim must be divided by x_headdim");
+  QB_REQUIRE(a->x_dim % kVec == 0 && gn % kVec == 0, QB_ERR_INVALID_ARG,
+             "x_dim and d_state*n_groups must be multiples of 16");
+  QB_REQUIRE(a->xBC_sl % kVec == 0 && a->xBC_sb % kVec == 0 && aligned(a->xBC, 16) && aligned(a->x, 16) &&
+                 aligned(a->Bm, 16) && aligned(a->Cm, 16),
+             QB_ERR_INVALID_ARG, "channel-last conv needs 16-byte aligned rows (strides multiple of 16)");
+  const bool grouped = a->head_group_range != nullptr && a->dim_group_range != nullptr;
+  QB_REQUIRE(grouped || (a->head_group_range == nullptr && a->dim_group_range == nullptr), QB_ERR_INVALID_ARG,
+             "x_head_group_range and x_dim_group_range must be both null or both set");
+  QB_REQUIRE(!grouped || (a->nhead_groups > 0 && a->ndim_groups > 0 && a->x_dim % a->n_groups == 0),
+             QB_ERR_INVALID_ARG, "grouped scales need nhead_groups, ndim_groups > 0");
+  ClSegments seg{};
+  seg.dst[0] = a->x; seg.dst[1] = a->Bm; seg.dst[2] = a->Cm;
+  seg.dst_sb[0] = (int64_t)a->seqlen * a->x_dim; seg.dst_sl[0] = a->x_dim;
+  seg.dst_sb[1] = seg.dst_sb[2] = (int64_t)a->seqlen * gn; seg.dst_sl[1] = seg.dst_sl[2] = gn;
+  seg.end0 = a->x_dim; seg.end1 = a->x_dim + gn;
+  seg.scale_in[0] = a->scale_wx * a->scale_x; seg.scale_in[1] = a->scale_wB * a->scale_B; seg.scale_in[2] = a->scale_wC * a->scale_C;
+  seg.scale_bias[0] = a->scale_bx; seg.scale_bias[1] = a->scale_bB; seg.scale_bias[2] = a->scale_bC;
+  seg.out_scales[0] = a->x_scales; seg.out_scales[1] = a->B_scales; seg.out_scales[2] = a->C_scales;
+  seg.head_group_range = a->head_group_range; seg.dim_group_range = a->dim_group_range;
+  seg.nhead_groups = a->nhead_groups; seg.ndim_groups = a->ndim_groups; seg.headdim = a->x_headdim;
+  seg.x_group_size = a->x_dim / a->n_groups; seg.d_state = a->d_state; seg.grouped = grouped ? 1 : 0;
+  const int cv = a->dim / kVec;
+  const int tl = pick_tl((int64_t)a->batch * cv, a->seqlen);
+  const int nseg = (int)ceil_div(a->seqlen, tl);
+  const int64_t total = (int64_t)a->batch * nseg * cv;
+  conv1d_channel_last_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
+      a->xBC, a->xBC_sb, a->xBC_sl, a->weight, a->bias, seg, a->batch, a->dim, a->seqlen, a->width, tl, nseg, a->silu);
+  QB_LAUNCH_OK("conv1d_channel_last_kernel");
+  return QB_OK;
+}
+
+extern "C" int qb_causal_conv1d_fwd(const qb_conv1d_fwd_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr && a->x && a->out && a->weight, QB_ERR_INVALID_ARG, "causal_conv1d_fwd: null pointer");
+  QB_REQUIRE(a->batch > 0 && a->dim > 0 && a->seqlen > 0, QB_ERR_INVALID_ARG, "causal_conv1d_fwd: empty shape");
+  QB_REQUIRE(a->width >= 2 && a->width <= 4, QB_ERR_INVALID_ARG,
+             "causal_conv1d only supports width between 2 and 4");
+  QB_REQUIRE(a->x_sl == 1 || a->x_sd == 1, QB_ERR_INVALID_ARG, "x must be contiguous in seqlen or in channels");
+  const bool channel_last = a->x_sd == 1 && a->x_sl > 1;
+  if (channel_last) {
+    QB_REQUIRE(a->out_sd == 1, QB_ERR_INVALID_ARG, "out must have the layout of x");
+    QB_REQUIRE(a->dim % kVec == 0 && a->x_sl % kVec == 0 && a->x_sb % kVec == 0 && a->out_sl % kVec == 0 &&
+                   a->out_sb % kVec == 0 && aligned(a->x, 16) && aligned(a->out, 16),
+               QB_ERR_INVALID_ARG,
+               "causal_conv1d with channel last layout requires dim and strides to be multiples of 16");
+    ClSegments seg{};
+    for (int i = 0; i < 3; ++i) {
+      seg.dst[i] = a->out; seg.dst_sb[i] = a->out_sb; seg.dst_sl[i] = a->out_sl;
+      seg.scale_in[i] = a->scale_w * a->scale_x; seg.scale_bias[i] = a->scale_b;
+      seg.out_scales[i] = nullptr;
+    }
+    seg.out_scale_value = a->scale_out;
+    seg.end0 = seg.end1 = a->dim;
+    const int cv = a->dim / kVec;
+    const int tl = pick_tl((int64_t)a->batch * cv, a->seqlen);
+    const int nseg = (int)ceil_div(a->seqlen, tl);
+    const int64_t total = (int64_t)a->batch * nseg * cv;
+    conv1d_channel_last_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
+        a->x, a->x_sb, a->x_sl, a->weight, a->bias, seg, a->batch, a->dim, a->seqlen, a->width, tl, nseg, a->silu);
+    QB_LAUNCH_OK("conv1d_channel_last_kernel");
+    return QB_OK;
+  }
+  QB_REQUIRE(a->out_sl == 1, QB_ERR_INVALID_ARG, "out must have the layout of x");
+  const int vec_ok = (a->seqlen % kVec == 0) && (a->x_sd % kVec == 0) && (a->x_sb % kVec == 0) && (a->out_sd % kVec == 0) &&
+                     (a->out_sb % kVec == 0) && aligned(a->x, 16) && aligned(a->out, 16);
+  const int64_t total = (int64_t)a->batch * a->dim * ceil_div(a->seqlen, kVec);
+  conv1d_seq_last_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
+      a->x, a->x_sb, a->x_sd, a->out, a->out_sb, a->out_sd, a->weight, a->bias, a->batch, a->dim, a->seqlen, a->width,
+      a->scale_w * a->scale_x, a->scale_b, a->scale_out, a->silu, vec_ok);
+  QB_LAUNCH_OK("conv1d_seq_last_kernel");
+  return QB_OK;
+}
+
+extern "C" int qb_causal_conv1d_update(const qb_conv1d_update_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr && a->x && a->conv_state && a->out && a->weight, QB_ERR_INVALID_ARG,
+             "causal_conv1d_update: null pointer");
+  QB_REQUIRE(a->batch > 0 && a->dim > 0, QB_ERR_INVALID_ARG, "causal_conv1d_update: empty shape");
+  QB_REQUIRE(a->width >= 2 && a->width <= 4, QB_ERR_INVALID_ARG,
+             "causal_conv1d only supports width between 2 and 4");
+  UpdSegments seg{};
+  for (int i = 0; i < 3; ++i) {
+    seg.dst[i] = a->out; seg.dst_sb[i] = a->out_sb; seg.dst_sd[i] = a->out_sd;
+    seg.scale_in[i] = a->scale_w * a->scale_x; seg.scale_bias[i] = a->scale_b;
+    seg.out_scales[i] = nullptr;
+  }
+  seg.out_scale_value = a->scale_out;
+  seg.end0 = seg.end1 = a->dim;
+  const int64_t total = (int64_t)a->batch * a->dim;
+  conv1d_update_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
+      a->x, a->x_sb, a->x_sd, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight, a->bias, seg,
+      a->batch, a->dim, a->width, a->silu);
+  QB_LAUNCH_OK("conv1d_update_kernel");
+  return QB_OK;
+}
+
+extern "C" int qb_quamba2_conv1d_update(const qb_quamba2_conv1d_update_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr, QB_ERR_INVALID_ARG, "quamba2_conv1d_update: null args");
+  QB_REQUIRE(a->xBC && a->conv_state && a->x && a->Bm && a->Cm && a->weight && a->x_scales && a->B_scales && a->C_scales,
+             QB_ERR_INVALID_ARG, "quamba2_conv1d_update: null tensor pointer");
+  QB_REQUIRE(a->batch > 0 && a->dim > 0, QB_ERR_INVALID_ARG, "quamba2_conv1d_update: empty shape");
+  QB_REQUIRE(a->width == 4, QB_ERR_INVALID_ARG, "causal_conv1d only supports width = 4");
+  const int gn = a->d_state * a->n_groups;
+  QB_REQUIRE(a->x_dim + 2 * gn == a->dim, QB_ERR_INVALID_ARG, "x_dim + 2*d_state*n_groups must be equal to total dim");
+  QB_REQUIRE(a->x_headdim > 0 && a->x_dim % a->x_headdim == 0, QB_ERR_INVALID_ARG, "x_dim must be divided by x_headdim");
+  const bool grouped = a->head_group_range != nullptr && a->dim_group_range != nullptr;
+  QB_REQUIRE(grouped || (a->head_group_range == nullptr && a->dim_group_range == nullptr), QB_ERR_INVALID_ARG,
+             "x_head_group_range and x_dim_group_range must be both null or both set");
+  QB_REQUIRE(!grouped || (a->nhead_groups > 0 && a->ndim_groups > 0 && a->x_dim % a->n_groups == 0),
+             QB_ERR_INVALID_ARG, "grouped scales need nhead_groups, ndim_groups > 0");
+  UpdSegments seg{};
+  seg.dst[0] = a->x; seg.dst[1] = a->Bm; seg.dst[2] = a->Cm;
+  seg.dst_sb[0] = a->x_dim; seg.dst_sb[1] = seg.dst_sb[2] = gn;
+  seg.dst_sd[0] = seg.dst_sd[1] = seg.dst_sd[2] = 1;
+  seg.end0 = a->x_dim; seg.end1 = a->x_dim + gn;
+  seg.scale_in[0] = a->scale_wx * a->scale_x; seg.scale_in[1] = a->scale_wB * a->scale_B; seg.scale_in[2] = a->scale_wC * a->scale_C;
+  seg.scale_bias[0] = a->scale_bx; seg.scale_bias[1] = a->scale_bB; seg.scale_bias[2] = a->scale_bC;
+  seg.out_scales[0] = a->x_scales; seg.out_scales[1] = a->B_scales; seg.out_scales[2] = a->C_scales;
+  seg.head_group_range = a->head_group_range; seg.dim_group_range = a->dim_group_range;
+  seg.nhead_groups = a->nhead_groups; seg.ndim_groups = a->ndim_groups; seg.headdim = a->x_headdim;
+  seg.x_group_size = a->x_dim / a->n_groups; seg.d_state = a->d_state; seg.grouped = grouped ? 1 : 0;
+  const int64_t total = (int64_t)a->batch * a->dim;
+  conv1d_update_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
+      a->xBC, a->xBC_sb, 1, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight, a->bias, seg,
+      a->batch, a->dim, a->width, a->silu);
+  QB_LAUNCH_OK("conv1d_update_kernel");
+  return QB_OK;
+}

@@ -1,0 +1,220 @@
+// int8 x int8 -> int32 GEMM on the Blackwell tensor cores (tcgen05.mma kind::i8, TMEM accumulator),
+// operands streamed by TMA into 128-byte-swizzled shared memory.
+//
+//   C[m, n] = sum_k A[m, k] * W[n, k]      A (M, K) and W (N, K) both K-contiguous int8.
+//
+// One CTA produces one 128 x 128 output tile.  Warp 0 issues the TMA loads (one elected lane),
+// warp 1 owns the TMEM allocation and issues the MMAs (one elected lane), warps 2..5 run the
+// epilogue: tcgen05.ld of the int32 accumulator, scaling, conversion and stores.  Shared memory
+// holds kStages x (A tile 16 KB + W tile 16 KB); two CTAs fit on an SM so that one CTA's epilogue
+// overlaps the other's main loop.  Out-of-range rows / columns / K tails are zero-filled by TMA
+// and masked in the epilogue, so M, N and K need no padding (K and the row pitches only have to be
+// multiples of 16 bytes, the TMA rule).  Every wait is bounded; on expiry the kernel records
+// QB_ERR_TIMEOUT in the device status word, frees its TMEM and returns.
+#include "tc_common.cuh"
+#include "linear_epilogue.cuh"
+
+namespace qb {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 128;  // BK bytes of K per stage = one swizzle atom row
+constexpr int kStages = 3;
+constexpr int kThreads = 192;
+constexpr int kTileBytes = BM * BK;  // 16 KB (A) and BN * BK = 16 KB (W)
+constexpr int kSmemBytes = kStages * 2 * kTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 128;
+
+using namespace tc;
+
+__global__ void __launch_bounds__(kThreads)
+gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                       int M, int N, int K, Epilogue ep, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sW = smem + kStages * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kStages * kTileBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* accum_bar = bars + 2 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t ph = (kb / kStages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, status, QB_ERR_TIMEOUT)) break;
+        mbar_arrive_expect_tx(&full_bar[s], 2 * kTileBytes);
+        tma_load_2d(sA + s * kTileBytes, &tmap_a, &full_bar[s], kb * BK, m0);
+        tma_load_2d(sW + s * kTileBytes, &tmap_w, &full_bar[s], kb * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t ph = (kb / kStages) & 1;
+        ok = mbar_wait(&full_bar[s], ph, status, QB_ERR_TIMEOUT);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(sA + s * kTileBytes);
+        const uint32_t w_addr = smem_u32(sW + s * kTileBytes);
+#pragma unroll
+        for (int k = 0; k < BK / 32; ++k) {
+          const uint64_t da = make_smem_desc(a_addr + k * 32, 16, 1024, kSwizzle128B);
+          const uint64_t dw = make_smem_desc(w_addr + k * 32, 16, 1024, kSwizzle128B);
+          umma_i8(tmem_base, da, dw, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+      }
+      umma_commit(accum_bar);  // accumulator complete (arrives even after an aborted loop)
+    }
+  } else {
+    // Epilogue warps 2..5: warp w may touch TMEM lanes [32 * (w % 4), 32 * (w % 4) + 32).
+    const int q = warp & 3;
+    const bool ok = mbar_wait(accum_bar, 0, status, QB_ERR_TIMEOUT);
+    tc_fence_after_sync();
+    if (ok) {
+      const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
+        tmem_ld_wait();
+        const int nb = n0 + c;
+        if (nb >= N) continue;  // whole warp agrees
+        if (ep.transpose) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (m < M && nb + j < N) ep.store((int)r[j], m, nb + j);
+        } else if (m < M) {
+          const bool full = nb + 32 <= N;
+          if (ep.out_kind == kOutF16 && full && (ep.out_stride % 8 == 0) &&
+              ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) && (nb % 8 == 0)) {
+            __half* dst = static_cast<__half*>(ep.out) + (int64_t)m * ep.out_stride + nb;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              __align__(16) __half2 h[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                h[t] = __floats2half2_rn(ep.scaled((int)r[j + 2 * t], m, nb + j + 2 * t),
+                                         ep.scaled((int)r[j + 2 * t + 1], m, nb + j + 2 * t + 1));
+              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(h);
+            }
+          } else if ((ep.out_kind == kOutS8Rne || ep.out_kind == kOutS8Away) && full && (ep.out_stride % 16 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) && (nb % 16 == 0)) {
+            int8_t* dst = static_cast<int8_t*>(ep.out) + (int64_t)m * ep.out_stride + nb;
+#pragma unroll
+            for (int j = 0; j < 32; j += 16) {
+              uint32_t w[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const int b = j + 4 * t;
+                w[t] = pack4_s8(ep.to_s8(ep.scaled((int)r[b], m, nb + b)), ep.to_s8(ep.scaled((int)r[b + 1], m, nb + b + 1)),
+                                ep.to_s8(ep.scaled((int)r[b + 2], m, nb + b + 2)),
+                                ep.to_s8(ep.scaled((int)r[b + 3], m, nb + b + 3)));
+              }
+              *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < N) ep.store((int)r[j], m, nb + j);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn != nullptr) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+}  // namespace
+
+int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                      uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn enc = get_encoder();
+  QB_REQUIRE(enc != nullptr, QB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t gdim[2] = {cols, rows};
+  const cuuint64_t gstride[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  QB_REQUIRE(r == CUDA_SUCCESS, QB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return QB_OK;
+}
+
+int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K,
+                            const Epilogue& ep, cudaStream_t st) {
+  // TMA rules: 16-byte aligned bases and pitches; the inner extent must cover whole 16-byte units.
+  if (K % 16 != 0 || lda % 16 != 0 || ldw % 16 != 0 || !aligned(A, 16) || !aligned(W, 16)) return QB_ERR_UNSUPPORTED;
+  if (M < 32) return QB_ERR_UNSUPPORTED;  // tiny M is weight-streaming work for the portable kernel
+  CUtensorMap ta, tw;
+  int rc = encode_tmap_2d_u8(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
+  if (rc != QB_OK) return rc;
+  rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, BK);
+  if (rc != QB_OK) return rc;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  QB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 64 || !attr_set[dev]) {
+    QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    if (dev < 64) attr_set[dev] = true;
+  }
+  dim3 grid((unsigned)ceil_div(M, BM), (unsigned)ceil_div(N, BN));
+  int* status = device_status_ptr();
+  QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "device status word unavailable");
+  gemm_s8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
+  QB_LAUNCH_OK("gemm_s8_tcgen05_kernel");
+  return QB_OK;
+}
+
+}  // namespace qb
+

@@ -1,0 +1,315 @@
+// Mamba1 int8 selective scan (prefill) and the single-step state update (decode) for sm_100a.
+//
+// Forward: one thread owns one (batch, channel) row and carries its N states in registers while
+// it walks the sequence; a CTA of 64 rows stages 64-step tiles of u / delta / z (int8, coalesced
+// 16-byte loads along L) and of B / C (shared by every row of the group, converted to fp32 once
+// per tile) in shared memory.  The output is written directly in the (B, L, D) layout the
+// out-projection consumes, so the reference's separate transpose pass does not exist here.
+//
+// Update: eight lanes share one (batch, head, channel) row of the int8 state (16 bytes each),
+// the y reduction is a 3-step shuffle.
+#include "common.cuh"
+
+namespace qb {
+namespace {
+
+constexpr int kRows = 64;    // (b, d) rows per CTA == threads per CTA
+constexpr int kTile = 64;    // time steps per shared-memory tile
+constexpr int kRowPad = 68;  // bytes per staged int8 row: 17 words, conflict-free column reads
+constexpr int kChunk = 2048; // the reference stores the state after every 2048 steps
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int N>
+__global__ void __launch_bounds__(kRows)
+sscan_fwd_kernel(qb_sscan_fwd_args a, int has_z, int vec_ok) {
+  __shared__ __align__(16) int8_t s_u[kRows * kRowPad];
+  __shared__ __align__(16) int8_t s_dt[kRows * kRowPad];
+  __shared__ __align__(16) int8_t s_z[kRows * kRowPad];
+  __shared__ __align__(16) float s_B[kTile * N];
+  __shared__ __align__(16) float s_C[kTile * N];
+
+  const int tid = threadIdx.x;
+  const int tiles_d = (a.dim + kRows - 1) / kRows;
+  const int b = blockIdx.x / tiles_d;
+  const int d0 = (blockIdx.x % tiles_d) * kRows;
+  const int d = d0 + tid;
+  const bool row_ok = d < a.dim;
+  const int dd = row_ok ? d : a.dim - 1;
+  const int group = d0 / (a.dim / a.n_groups);
+  const int nchunks = (a.seqlen + kChunk - 1) / kChunk;
+
+  const float s_u_ = *a.u_scale, s_d_ = *a.delta_scale, s_B_ = *a.B_scale, s_C_ = *a.C_scale;
+  const float s_A_ = *a.A_scale, s_st = *a.ssm_state_scale;
+  const float s_z_ = has_z ? *a.z_scale : 0.0f;
+  const float Dv = a.D != nullptr ? (*a.D_scale) * (float)a.D[dd] : 0.0f;
+  const float bias = a.delta_bias != nullptr ? (*a.delta_bias_scale) * (float)a.delta_bias[dd] : 0.0f;
+  float A2[N], h[N];
+#pragma unroll
+  for (int n = 0; n < N; ++n) {
+    A2[n] = -__expf(s_A_ * (float)a.A_log[(int64_t)dd * N + n]) * kLog2e;
+    h[n] = 0.0f;
+  }
+  const int8_t* u_b = a.u + (int64_t)b * a.u_sb;
+  const int8_t* dt_b = a.delta + (int64_t)b * a.delta_sb;
+  const int8_t* z_b = has_z ? a.z + (int64_t)b * a.z_sb : nullptr;
+  const int8_t* B_b = a.Bm + (int64_t)b * a.B_sb + (int64_t)group * a.B_sg;
+  const int8_t* C_b = a.Cm + (int64_t)b * a.C_sb + (int64_t)group * a.C_sg;
+  __half* out = static_cast<__half*>(a.out) + (int64_t)b * a.seqlen * a.dim + d;
+  int8_t* xs = a.x_states + ((int64_t)b * a.dim + dd) * nchunks * N;
+
+  // stage one 16-byte piece (or its in-range bytes) of a row into a padded shared row
+  auto stage = [&](const int8_t* base, int64_t row_stride, int8_t* dst, int l0) {
+    // kRows rows x 4 pieces; 64 threads -> 4 iterations
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int item = it * kRows + tid;
+      const int r = item >> 2, piece = item & 3;
+      const int rr = min(d0 + r, a.dim - 1);
+      const int l = l0 + piece * 16;
+      const int8_t* src = base + (int64_t)rr * row_stride + l;
+      uint32_t w[4] = {0, 0, 0, 0};
+      if (vec_ok && l + 16 <= a.seqlen) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+      } else {
+        for (int k = 0; k < 16; ++k)
+          if (l + k < a.seqlen) w[k >> 2] |= (uint32_t)(uint8_t)src[k] << (8 * (k & 3));
+      }
+      uint32_t* o = reinterpret_cast<uint32_t*>(dst + r * kRowPad + piece * 16);
+      o[0] = w[0]; o[1] = w[1]; o[2] = w[2]; o[3] = w[3];
+    }
+  };
+  auto stage_bc = [&](const int8_t* base, int64_t sn, float scale, float* dst, int l0) {
+    // N rows x 4 pieces of 16 steps
+    for (int item = tid; item < N * 4; item += kRows) {
+      const int n = item >> 2, piece = item & 3;
+      const int l = l0 + piece * 16;
+      const int8_t* src = base + (int64_t)n * sn + l;
+      __align__(16) int8_t v[16];
+      if (vec_ok && l + 16 <= a.seqlen) {
+        *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(src));
+      } else {
+        for (int k = 0; k < 16; ++k) v[k] = (l + k < a.seqlen) ? src[k] : (int8_t)0;
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) dst[(piece * 16 + k) * N + n] = scale * (float)v[k];
+    }
+  };
+
+  for (int l0 = 0; l0 < a.seqlen; l0 += kTile) {
+    __syncthreads();
+    stage(u_b, a.u_sd, s_u, l0);
+    stage(dt_b, a.delta_sd, s_dt, l0);
+    if (has_z) stage(z_b, a.z_sd, s_z, l0);
+    stage_bc(B_b, a.B_sn, s_B_, s_B, l0);
+    stage_bc(C_b, a.C_sn, s_C_, s_C, l0);
+    __syncthreads();
+    const int steps = min(kTile, a.seqlen - l0);
+    const uint32_t* ru = reinterpret_cast<const uint32_t*>(s_u + tid * kRowPad);
+    const uint32_t* rd = reinterpret_cast<const uint32_t*>(s_dt + tid * kRowPad);
+    const uint32_t* rz = reinterpret_cast<const uint32_t*>(s_z + tid * kRowPad);
+    for (int t4 = 0; t4 < steps; t4 += 4) {
+      const uint32_t wu = ru[t4 >> 2], wd = rd[t4 >> 2];
+      const uint32_t wz = has_z ? rz[t4 >> 2] : 0u;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int t = t4 + k;
+        if (t < steps) {
+          const float u = s_u_ * (float)(int8_t)((wu >> (8 * k)) & 0xff);
+          float delta = fmaf(s_d_, (float)(int8_t)((wd >> (8 * k)) & 0xff), bias);
+          if (a.delta_softplus) delta = softplus_f(delta);
+          const float du = delta * u;
+          float y = Dv * u;
+          const float4* Bt = reinterpret_cast<const float4*>(s_B + t * N);
+          const float4* Ct = reinterpret_cast<const float4*>(s_C + t * N);
+#pragma unroll
+          for (int n4 = 0; n4 < N / 4; ++n4) {
+            const float4 bv = Bt[n4], cv = Ct[n4];
+            const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+            const float cc[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int n = n4 * 4 + j;
+              h[n] = fmaf(fast_exp2(delta * A2[n]), h[n], bb[j] * du);
+              y = fmaf(h[n], cc[j], y);
+            }
+          }
+          if (has_z) {
+            const float z = s_z_ * (float)(int8_t)((wz >> (8 * k)) & 0xff);
+            y = y * silu_exact(z);
+          }
+          const int l = l0 + t;
+          if (row_ok) out[(int64_t)l * a.dim] = __float2half_rn(y);
+          if (((l + 1) % kChunk == 0 || l == a.seqlen - 1) && row_ok) {
+            int8_t* dst = xs + (int64_t)(l / kChunk) * N;
+#pragma unroll
+            for (int n = 0; n < N; ++n) dst[n] = (int8_t)round_away_s8(h[n] / s_st);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---- decode step -----------------------------------------------------------------------------
+// 8 lanes per (b, h, p) row; lane j owns states n = 16*j + 128*i .. (16-byte pieces).
+__global__ void __launch_bounds__(128)
+sscan_update_kernel(qb_sscan_update_args a) {
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid >> 3;
+  const int sub = (int)(gid & 7);
+  const int64_t rows = (int64_t)a.batch * a.nheads * a.headdim;
+  const bool active = row < rows;
+  const int64_t rr = active ? row : rows - 1;
+  const int p = (int)(rr % a.headdim);
+  const int hd = (int)((rr / a.headdim) % a.nheads);
+  const int b = (int)(rr / ((int64_t)a.headdim * a.nheads));
+  const int hpg = a.nheads / a.ngroups;
+  const int g = hd / hpg;
+
+  int hg = 0, dg = 0;
+  float xs, Bs, Cs;
+  if (a.grouped) {
+    hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, hd % hpg);
+    dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
+    xs = a.x_scales[(g * a.nhead_groups + hg) * a.ndim_groups + dg];
+    Bs = a.B_scale[g];
+    Cs = a.C_scale[g];
+  } else {
+    xs = a.x_scales[0];
+    Bs = a.B_scale[0];
+    Cs = a.C_scale[0];
+  }
+  const float* st_scale = a.grouped
+      ? a.state_scale + ((int64_t)(g * a.nhead_groups + hg) * a.ndim_groups + dg) * a.dstate
+      : nullptr;
+  const float st_scale0 = a.grouped ? 0.0f : a.state_scale[0];
+
+  const float x = xs * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
+  float dt = (*a.dt_scale) * (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp];
+  if (a.dt_bias != nullptr) {
+    const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
+    if (a.dt_bias_is_half) dt += __half2float(static_cast<const __half*>(a.dt_bias)[bi]);
+    else dt += (*a.dt_bias_scale) * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
+  }
+  if (a.dt_softplus) dt = softplus_f(dt);
+  const float sA = *a.A_scale;
+  const float dtx = dt * x;
+  const int8_t* Aq = a.A_log + (int64_t)hd * a.A_sh + (int64_t)p * a.A_sp;
+  const int8_t* Bq = a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg;
+  const int8_t* Cq = a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg;
+  int8_t* st = a.state + (int64_t)b * a.state_sb + (int64_t)hd * a.state_sh + (int64_t)p * a.state_sp;
+  const bool vec = (a.dstate % 16 == 0) && ((reinterpret_cast<uintptr_t>(st) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(Bq) & 15) == 0) && ((reinterpret_cast<uintptr_t>(Cq) & 15) == 0);
+  float y = 0.0f;
+  for (int n0 = sub * 16; n0 < a.dstate; n0 += 128) {
+    __align__(16) int8_t sv[16], bv[16], cv[16];
+    if (vec) {
+      *reinterpret_cast<uint4*>(sv) = *reinterpret_cast<const uint4*>(st + n0);
+      *reinterpret_cast<uint4*>(bv) = __ldg(reinterpret_cast<const uint4*>(Bq + n0));
+      *reinterpret_cast<uint4*>(cv) = __ldg(reinterpret_cast<const uint4*>(Cq + n0));
+    } else {
+      for (int k = 0; k < 16; ++k) {
+        const bool ok = n0 + k < a.dstate;
+        sv[k] = ok ? st[n0 + k] : (int8_t)0;
+        bv[k] = ok ? Bq[n0 + k] : (int8_t)0;
+        cv[k] = ok ? Cq[n0 + k] : (int8_t)0;
+      }
+    }
+    __align__(16) int8_t qo[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int n = n0 + k;
+      const bool ok = n < a.dstate;
+      const int nn = ok ? n : 0;
+      const float ss = a.grouped ? st_scale[nn] : st_scale0;
+      const float A = -__expf(sA * (float)Aq[(int64_t)nn * a.A_sn]);
+      const float s = fmaf(ss * (float)sv[k], __expf(A * dt), (Bs * (float)bv[k]) * dtx);
+      qo[k] = (int8_t)rint_s8(s / ss);
+      if (ok) y = fmaf(s, Cs * (float)cv[k], y);
+    }
+    if (active) {
+      if (vec) {
+        *reinterpret_cast<uint4*>(st + n0) = *reinterpret_cast<const uint4*>(qo);
+      } else {
+        for (int k = 0; k < 16; ++k)
+          if (n0 + k < a.dstate) st[n0 + k] = qo[k];
+      }
+    }
+  }
+  y += __shfl_xor_sync(0xffffffffu, y, 1);
+  y += __shfl_xor_sync(0xffffffffu, y, 2);
+  y += __shfl_xor_sync(0xffffffffu, y, 4);
+  if (active && sub == 0) {
+    if (a.D != nullptr) y = fmaf(x, (*a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp], y);
+    if (a.z != nullptr) {
+      const float z = (*a.z_scale) * (float)a.z[(int64_t)b * a.z_sb + (int64_t)hd * a.z_sh + p];
+      y *= silu_exact(z);
+    }
+    static_cast<__half*>(a.out)[(int64_t)b * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
+  }
+}
+
+}  // namespace
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qb_sscan_fwd(const qb_sscan_fwd_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr, QB_ERR_INVALID_ARG, "sscan_fwd: null args");
+  QB_REQUIRE(a->u && a->delta && a->Bm && a->Cm && a->A_log && a->out && a->x_states, QB_ERR_INVALID_ARG,
+             "sscan_fwd: null tensor pointer");
+  QB_REQUIRE(a->u_scale && a->delta_scale && a->B_scale && a->C_scale && a->A_scale && a->ssm_state_scale,
+             QB_ERR_INVALID_ARG, "sscan_fwd: null scale pointer");
+  QB_REQUIRE(a->D == nullptr || a->D_scale != nullptr, QB_ERR_INVALID_ARG, "sscan_fwd: D without D_scale");
+  QB_REQUIRE(a->z == nullptr || a->z_scale != nullptr, QB_ERR_INVALID_ARG, "sscan_fwd: z without z_scale");
+  QB_REQUIRE(a->delta_bias == nullptr || a->delta_bias_scale != nullptr, QB_ERR_INVALID_ARG,
+             "sscan_fwd: delta_bias without its scale");
+  QB_REQUIRE(a->batch > 0 && a->dim > 0 && a->seqlen > 0 && a->n_groups > 0, QB_ERR_INVALID_ARG, "sscan_fwd: empty shape");
+  QB_REQUIRE(a->dstate <= 256, QB_ERR_INVALID_ARG, "quant_sscan only supports state dimension <= 256");
+  QB_REQUIRE(a->dim % a->n_groups == 0, QB_ERR_INVALID_ARG, "sscan_fwd: dim not divisible by n_groups");
+  QB_REQUIRE(a->n_groups == 1 || (a->dim / a->n_groups) % kRows == 0, QB_ERR_UNSUPPORTED,
+             "sscan_fwd: channels per group must be a multiple of %d", kRows);
+  const int vec_ok = aligned(a->u, 16) && aligned(a->delta, 16) && (a->z == nullptr || aligned(a->z, 16)) &&
+                     aligned(a->Bm, 16) && aligned(a->Cm, 16) && a->u_sd % 16 == 0 && a->u_sb % 16 == 0 &&
+                     a->delta_sd % 16 == 0 && a->delta_sb % 16 == 0 && a->z_sd % 16 == 0 && a->z_sb % 16 == 0 &&
+                     a->B_sn % 16 == 0 && a->B_sg % 16 == 0 && a->B_sb % 16 == 0 && a->C_sn % 16 == 0 &&
+                     a->C_sg % 16 == 0 && a->C_sb % 16 == 0;
+  const int tiles_d = (int)ceil_div(a->dim, kRows);
+  const unsigned grid = (unsigned)(a->batch * tiles_d);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int has_z = a->z != nullptr;
+  switch (a->dstate) {
+    case 8: sscan_fwd_kernel<8><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 16: sscan_fwd_kernel<16><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 32: sscan_fwd_kernel<32><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 64: sscan_fwd_kernel<64><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    default:
+      set_error("sscan_fwd: dstate %d not built (8, 16, 32, 64 are)", a->dstate);
+      return QB_ERR_UNSUPPORTED;
+  }
+  QB_LAUNCH_OK("sscan_fwd_kernel");
+  return QB_OK;
+}
+
+extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr, QB_ERR_INVALID_ARG, "sscan_update: null args");
+  QB_REQUIRE(a->state && a->x && a->dt && a->A_log && a->Bm && a->Cm && a->out, QB_ERR_INVALID_ARG,
+             "sscan_update: null tensor pointer");
+  QB_REQUIRE(a->x_scales && a->dt_scale && a->A_scale && a->state_scale && a->B_scale && a->C_scale,
+             QB_ERR_INVALID_ARG, "sscan_update: null scale pointer");
+  QB_REQUIRE(a->D == nullptr || a->D_scale != nullptr, QB_ERR_INVALID_ARG, "sscan_update: D without D_scale");
+  QB_REQUIRE(a->z == nullptr || a->z_scale != nullptr, QB_ERR_INVALID_ARG, "sscan_update: z without z_scale");
+  QB_REQUIRE(a->dt_bias == nullptr || a->dt_bias_is_half || a->dt_bias_scale != nullptr, QB_ERR_INVALID_ARG,
+             "sscan_update: int8 dt_bias without its scale");
+  QB_REQUIRE(a->batch > 0 && a->nheads > 0 && a->headdim > 0 && a->dstate > 0 && a->ngroups > 0,
+             QB_ERR_INVALID_ARG, "sscan_update: empty shape");
+  QB_REQUIRE(a->nheads % a->ngroups == 0, QB_ERR_INVALID_ARG, "nheads must be divisible by ngroups");
+  QB_REQUIRE(!a->grouped || (a->head_group_range && a->dim_group_range && a->nhead_groups > 0 && a->ndim_groups > 0),
+             QB_ERR_INVALID_ARG, "sscan_update: grouped scales need the range tables");
+  const int64_t threads = (int64_t)a->batch * a->nheads * a->headdim * 8;
+  sscan_update_kernel<<<(unsigned)ceil_div(threads, 128), 128, 0, (cudaStream_t)stream>>>(*a);
+  QB_LAUNCH_OK("sscan_update_kernel");
+  return QB_OK;
+}

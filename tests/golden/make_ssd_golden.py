@@ -200,5 +200,5 @@ def run_case(tag, Bsz, L, H, P, G, N, Q, grouped, seed):
 
 if __name__ == "__main__":
     _install_stubs()
-    run_case("pertensor", Bsz=2, L=96, H=4, P=32, G=1, N=32, Q=64, grouped=False, seed=0)
-    run_case("grouped", Bsz=1, L=128, H=8, P=32, G=2, N=32, Q=64, grouped=True, seed=1)
+    run_case("pertensor", Bsz=2, L=96, H=4, P=64, G=1, N=64, Q=64, grouped=False, seed=0)
+    run_case("grouped", Bsz=1, L=128, H=8, P=64, G=2, N=64, Q=64, grouped=True, seed=1)
