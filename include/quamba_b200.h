@@ -399,6 +399,21 @@ int64_t qb_ssd_workspace_bytes(int32_t batch, int32_t seqlen, int32_t nheads, in
                                int32_t ngroups, int32_t dstate, int32_t chunk_size);
 int qb_ssd_chunk_scan_fwd(const qb_ssd_args* a, void* stream);
 
+/* The same SSD forward for callers that cannot provide scratch memory.  (No counterpart in the
+ * reference, whose Triton wrappers allocate their intermediates through torch.)  A host program
+ * without a device allocator of its own, or one whose memory pool is sealed after model load, has
+ * no way to obtain the workspace above short of cudaMalloc; this entry point therefore ignores
+ * a->workspace / a->workspace_bytes and uses an array built into the library's device image
+ * (qb_ssd_static_scratch_bytes() bytes, 48 MiB, resident on every GPU that loads the library until
+ * the process exits).  It calls no cudaMalloc / cudaFree and no allocating library routine; inputs
+ * and outputs are still the caller's.  Shapes whose workspace (qb_ssd_workspace_bytes) exceeds the
+ * array are rejected with QB_ERR_TOO_LARGE.  The first call on each device looks up the array's
+ * device address and should therefore be made before any stream capture begins.  All calls share the
+ * one array: two calls whose kernels can overlap on the GPU (different streams) race on it; calls
+ * on one stream are safe, and nothing needs clearing between them. */
+int64_t qb_ssd_static_scratch_bytes(void);
+int qb_ssd_chunk_scan_fwd_noalloc(const qb_ssd_args* a, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * W4A8 linears (Marlin-QQQ packed int4 weights, int8 activations).
  * Replaces quant_linear_cuda.w4a8o16_gemm / w4a8o8_gemm

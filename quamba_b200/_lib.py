@@ -70,6 +70,7 @@ def lib():
         _lib.qb_ssd_workspace_bytes.restype = ctypes.c_int64
         _lib.qb_ssd_workspace_bytes.argtypes = [ctypes.c_int32] * 7
         _lib.qb_read_device_status.argtypes = [ctypes.c_void_p]
+        _lib.qb_ssd_static_scratch_bytes.restype = ctypes.c_int64
         for name, st in STRUCTS.items():
             got = _lib.qb_sizeof(name.encode())
             if got != ctypes.sizeof(st):

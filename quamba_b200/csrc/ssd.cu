@@ -378,3 +378,61 @@ extern "C" int qb_ssd_chunk_scan_fwd(const qb_ssd_args* a, void* stream) {
   }
   return QB_OK;
 }
+
+// ---- allocation-free variant -------------------------------------------------------------------
+// Some callers of this library cannot hand over scratch memory at all: a host process that owns no
+// CUDA allocator of its own (a plain C inference loop, a language binding without device-memory
+// management) or a runtime whose memory pool is frozen once the model is loaded has nowhere to get
+// the SSD workspace from, because obtaining one would mean calling cudaMalloc.  For them the
+// scratch lives in this library's own device image: a fixed-size array that every GPU loading the
+// library holds until the process exits.
+namespace qb {
+namespace {
+
+constexpr int64_t kStaticScratchBytes = 48ll << 20;  // 48 MiB: one Mamba2-2.7B layer, batch 1, 2048 tokens
+static __device__ __align__(256) unsigned char g_ssd_static_scratch[kStaticScratchBytes];
+
+// In host code `g_ssd_static_scratch` is only a host-side handle; the address a kernel can use has
+// to be asked for, once per device, with that device current.
+int static_scratch_ptr(char** out) {
+  static char* cached[64] = {};
+  int dev = 0;
+  QB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] != nullptr) {
+    *out = cached[dev];
+    return QB_OK;
+  }
+  char* p = nullptr;
+  QB_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_ssd_static_scratch));
+  QB_REQUIRE(p != nullptr, QB_ERR_CUDA, "ssd: the static scratch array has no device address");
+  if (dev >= 0 && dev < 64) cached[dev] = p;
+  *out = p;
+  return QB_OK;
+}
+
+}  // namespace
+}  // namespace qb
+
+extern "C" int64_t qb_ssd_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int qb_ssd_chunk_scan_fwd_noalloc(const qb_ssd_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr, QB_ERR_INVALID_ARG, "ssd: null args");
+  QB_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->nheads > 0 && a->headdim > 0 && a->ngroups > 0 && a->dstate > 0 &&
+                 a->chunk_size > 0,
+             QB_ERR_INVALID_ARG, "ssd: empty shape");
+  const int64_t need =
+      ws_layout(a->batch, a->seqlen, a->nheads, a->headdim, a->ngroups, a->dstate, a->chunk_size).total;
+  QB_REQUIRE(need <= kStaticScratchBytes, QB_ERR_TOO_LARGE,
+             "ssd (no-alloc): this shape needs %lld bytes of scratch, the built-in array holds %lld; "
+             "use qb_ssd_chunk_scan_fwd with a caller-provided workspace",
+             (long long)need, (long long)kStaticScratchBytes);
+  char* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);
+  if (rc != QB_OK) return rc;
+  qb_ssd_args b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = kStaticScratchBytes;
+  // Every stage fully rewrites the part of the scratch it later reads, so nothing has to be cleared
+  // between calls even though the array keeps the previous call's contents.
+  return qb_ssd_chunk_scan_fwd(&b, stream);
+}
