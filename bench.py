@@ -8,7 +8,7 @@ int8 causal conv1d over xBC (+SiLU, requant, x/B/C split) followed by the int8 S
 inter-chunk state passing, at the op configuration B4 L2048 H80 P64 G1 N128 Q256 W4 (the conv + SSD
 shapes of one Mamba2-2.7B layer at batch 4).  Prints ONE JSON line (see the keys below).
 
-  value     tokens/s with inputs resident in HBM (device-timed, CUDA events, max over ranks)
+  value     tokens/s with inputs resident in HBM (device-timed, CUDA events around CUDA-graph replays of the step, max over ranks)
   e2e       the same through the public ops API with pinned HOST buffers: H2D of the int8 inputs and
             D2H of y + final states inside the timed region
   roofline  SSD forward (the dominant part): algorithmic bytes / its CUDA-event time vs measured HBM peak
@@ -204,11 +204,35 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    stream = torch.cuda.current_stream()
+    # Everything below runs on one side stream (CUDA-graph capture needs a non-default stream).
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     for i in range(warmup):
         step(sets[i % NSETS])
     barrier()
     _lib.read_device_status(stream.cuda_stream)
+
+    # ---- CUDA graphs: the step, and its two parts, captured once per input set so that the timed region
+    # contains only device work (the Python/ctypes marshalling of each call is tens of microseconds) ----
+    graphs, conv_graphs, ssd_graphs, keep = [], [], [], []
+    for d in sets:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            keep.append(step(d))
+        graphs.append(g)
+        gc = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gc, stream=stream):
+            xbc = conv_call(d, d["xBC"])
+        conv_graphs.append(gc)
+        gs = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gs, stream=stream):
+            keep.append(ssd_call(d, xbc[0], xbc[1], xbc[2], d["q_dt"]))
+        ssd_graphs.append(gs)
+        keep.append(xbc)
+    for i in range(warmup):
+        graphs[i % NSETS].replay()
+    barrier()
 
     # ---- timed region: whole step, device timed ----
     sampler = ClockSampler(local_rank)
@@ -218,27 +242,25 @@ def main():
     barrier()
     e0.record(stream)
     for i in range(steps):
-        step(sets[i % NSETS])
+        graphs[i % NSETS].replay()
     e1.record(stream)
     barrier()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- per-part timings for the roofline (same stream, CUDA events around each part) ----
-    conv_ms = ssd_ms = 0.0
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    for i in range(steps):
-        d = sets[i % NSETS]
-        ev[0].record(stream)
-        x, Bm, Cm = conv_call(d, d["xBC"])
-        ev[1].record(stream)
-        ssd_call(d, x, Bm, Cm, d["q_dt"])
-        ev[2].record(stream)
-        ev[2].synchronize()
-        conv_ms += ev[0].elapsed_time(ev[1])
-        ssd_ms += ev[1].elapsed_time(ev[2])
-    conv_ms /= steps
-    ssd_ms /= steps
+    # ---- per-part timings for the roofline (same stream, CUDA events around K replays of each part) ----
+    def time_graphs(gl):
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(3):
+            gl[i % NSETS].replay()
+        a.record(stream)
+        for i in range(steps):
+            gl[i % NSETS].replay()
+        b_.record(stream)
+        b_.synchronize()
+        return a.elapsed_time(b_) / steps
+    conv_ms = time_graphs(conv_graphs)
+    ssd_ms = time_graphs(ssd_graphs)
 
     # ---- end to end: pinned host inputs -> device -> hot path -> host outputs ----
     host_y = torch.empty((B, L, H, P), dtype=torch.float16).pin_memory()
@@ -295,8 +317,8 @@ def main():
                    "sharding": "independent batches per GPU, no collective on this path"},
         "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": int(sets[0]["host_xBC"].numel() + sets[0]["host_dt"].numel()),
                 "d2h_bytes_per_step": int(host_y.numel() * 2 + host_f.numel())},
-        "gpu_launches": 6 * steps,
-        "roofline": {"kernel": "ssd_chunk_scan_fwd (5 launches)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
+        "gpu_launches": 4 * steps,
+        "roofline": {"kernel": "ssd_tc_kernel (+ ssd_widen_bc_kernel, ssd_dt_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
                      "frac": ssd_gbs / hbm_peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
                      "algorithmic_bytes": ssd_bytes, "ms": ssd_ms,
                      "conv1d": {"achieved": conv_gbs, "frac": conv_gbs / hbm_peak, "algorithmic_bytes": conv_bytes, "ms": conv_ms}},

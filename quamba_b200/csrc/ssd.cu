@@ -15,6 +15,8 @@
 // is what the reference's tensor-core dots do.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace qb {
 namespace {
 
@@ -316,6 +318,23 @@ ssd_chunk_scan_kernel(qb_ssd_args a, Ws ws, int nc) {
 }
 
 }  // namespace
+
+// Tensor-core path (ssd_tc.cu): headdim 64, d_state 128, no z gate.
+bool ssd_tc_eligible(const qb_ssd_args* a);
+int64_t ssd_tc_workspace_bytes(int B, int L, int H, int G);
+int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st);
+
+namespace {
+bool force_portable() {  // QB_SSD_PORTABLE=1 selects the five-stage path (used to cross-check the two on a device)
+  const char* e = getenv("QB_SSD_PORTABLE");
+  return e != nullptr && e[0] == '1';
+}
+int64_t total_workspace(int B, int L, int H, int P, int G, int N, int Q) {
+  const int64_t a = ws_layout(B, L, H, P, G, N, Q).total;
+  const int64_t b = ssd_tc_workspace_bytes(B, L, H, G);
+  return a > b ? a : b;
+}
+}  // namespace
 }  // namespace qb
 
 using namespace qb;
@@ -324,7 +343,7 @@ extern "C" int64_t qb_ssd_workspace_bytes(int32_t batch, int32_t seqlen, int32_t
                                           int32_t ngroups, int32_t dstate, int32_t chunk_size) {
   if (batch <= 0 || seqlen <= 0 || nheads <= 0 || headdim <= 0 || ngroups <= 0 || dstate <= 0 || chunk_size <= 0)
     return -1;
-  return ws_layout(batch, seqlen, nheads, headdim, ngroups, dstate, chunk_size).total;
+  return total_workspace(batch, seqlen, nheads, headdim, ngroups, dstate, chunk_size);
 }
 
 extern "C" int qb_ssd_chunk_scan_fwd(const qb_ssd_args* a, void* stream) {
@@ -342,8 +361,10 @@ extern "C" int qb_ssd_chunk_scan_fwd(const qb_ssd_args* a, void* stream) {
   QB_REQUIRE(!a->grouped || (a->head_group_range && a->dim_group_range && a->nhead_groups > 0 && a->ndim_groups > 0),
              QB_ERR_INVALID_ARG, "ssd: grouped scales need the range tables");
   const WsLayout wl = ws_layout(a->batch, a->seqlen, a->nheads, a->headdim, a->ngroups, a->dstate, a->chunk_size);
-  QB_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= wl.total && aligned(a->workspace, 256),
-             QB_ERR_INVALID_ARG, "ssd: workspace must be 256-byte aligned and hold %lld bytes", (long long)wl.total);
+  const int64_t need = total_workspace(a->batch, a->seqlen, a->nheads, a->headdim, a->ngroups, a->dstate, a->chunk_size);
+  QB_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= need && aligned(a->workspace, 256),
+             QB_ERR_INVALID_ARG, "ssd: workspace must be 256-byte aligned and hold %lld bytes", (long long)need);
+  if (!force_portable() && ssd_tc_eligible(a)) return ssd_tc_launch(a, (cudaStream_t)stream);
   char* base = static_cast<char*>(a->workspace);
   Ws ws;
   ws.dt = reinterpret_cast<float*>(base + wl.off_dt);
@@ -421,7 +442,7 @@ extern "C" int qb_ssd_chunk_scan_fwd_noalloc(const qb_ssd_args* a, void* stream)
                  a->chunk_size > 0,
              QB_ERR_INVALID_ARG, "ssd: empty shape");
   const int64_t need =
-      ws_layout(a->batch, a->seqlen, a->nheads, a->headdim, a->ngroups, a->dstate, a->chunk_size).total;
+      total_workspace(a->batch, a->seqlen, a->nheads, a->headdim, a->ngroups, a->dstate, a->chunk_size);
   QB_REQUIRE(need <= kStaticScratchBytes, QB_ERR_TOO_LARGE,
              "ssd (no-alloc): this shape needs %lld bytes of scratch, the built-in array holds %lld; "
              "use qb_ssd_chunk_scan_fwd with a caller-provided workspace",

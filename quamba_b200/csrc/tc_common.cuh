@@ -46,14 +46,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: false (and a status code) if the phase does not complete within the budget.
+// A waiting thread backs off between polls so that it does not compete for issue slots and for the
+// shared-memory pipeline with the warps that are doing the work it waits for.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i)
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      __nanosleep(32);
+    }
     if (clock64() - t0 > kWaitBudgetCycles) {
       atomicCAS(status, 0, code);
       return false;
@@ -152,5 +167,8 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_format, uint32_t a_
 // (box_rows x box_cols) box and 128-byte swizzle.  Returns QB_OK or an error.
 int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
                       uint32_t box_rows, uint32_t box_cols);
+// Host: 4-D fp16 tensor map, dims / box innermost first, strides (bytes) for dims 1..3, 128-byte swizzle.
+int encode_tmap_f16_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                       const uint32_t box[4]);
 
 }  // namespace qb

@@ -252,6 +252,38 @@ def test_ssd_against_oracle(Bsz, L, H, P, G, N, Q, grouped, with_z, dh):
     assert_lsb(fs, fq_ref, max_frac=0.02)
 
 
+@pytest.mark.parametrize("Bsz,L,H,G,grouped,dh", [(1, 50, 2, 1, False, False), (2, 333, 4, 2, True, True), (1, 128, 3, 1, False, False),
+                                                  (1, 1000, 8, 8, True, False), (3, 129, 2, 2, False, True)])
+def test_ssd_tensor_core_path_against_oracle(Bsz, L, H, G, grouped, dh):
+    """headdim 64 / d_state 128 / no z: the tcgen05 kernel (128-token blocks, state kept on chip)."""
+    P, N, Q = 64, 128, 256
+    c = make_ssd_case(Bsz, L, H, P, G, N, Q, grouped=grouped, seed=L, d_has_hdim=dh)
+    y_ref, fq_ref = ossd.chunk_scan_faithful(c["q_x"], c["x_scales"], c["hgr"], c["dgr"], c["q_dt"], c["s_dt"], c["q_A_log"], c["s_A"],
+                                             c["q_B"], c["s_B"], c["q_C"], c["s_C"], c["state_scale"], Q, c["q_D"], c["s_D"], None, None,
+                                             c["dt_bias"], True)
+    y_id, h_id = ossd.chunk_scan_ideal(c["q_x"], c["x_scales"], c["hgr"], c["dgr"], c["q_dt"], c["s_dt"], c["q_A_log"], c["s_A"], c["q_B"],
+                                       c["s_B"], c["q_C"], c["s_C"], c["q_D"], c["s_D"], None, None, c["dt_bias"], True, dtype=torch.float32)
+    y, fs = _run_ssd(c, grouped)
+    torch.cuda.synchronize()
+    from quamba_b200 import _lib
+    _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+    assert_fp16(y, y_id)
+    assert_fp16(y, y_ref)
+    assert_lsb(fs, fq_ref, max_frac=0.03)
+
+
+def test_ssd_tensor_core_path_equals_portable_path_on_device(monkeypatch):
+    """Same inputs through both CUDA paths at a layer-sized shape (batch 1 of the benchmark configuration)."""
+    c = make_ssd_case(1, 2048, 80, 64, 1, 128, 256, seed=7)
+    y_tc, f_tc = _run_ssd(c, False)
+    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
+    y_pt, f_pt = _run_ssd(c, False)
+    monkeypatch.delenv("QB_SSD_PORTABLE")
+    torch.cuda.synchronize()
+    assert_fp16(y_tc, y_pt.cpu())
+    assert_lsb(f_tc, f_pt.cpu(), max_frac=0.03)
+
+
 # ---- linears ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("tag", ["g128", "g128_pad", "perchannel"])
 @pytest.mark.parametrize("M", [1, 5, 89, 256])
