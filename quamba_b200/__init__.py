@@ -13,5 +13,9 @@ its absence is an error (there is no CPU or PyTorch fallback).
 """
 from . import _lib  # noqa: F401
 from . import ops  # noqa: F401
+from .modules import (QCausalConv1D, QHadamard, QSScan, Quamb2Conv1D, Quamba2ChunkScan,  # noqa: F401
+                      W4A8B8O8Linear, W4A8B8O8LinearParallel, W4A8B16O16Linear, W8A8B8O8Linear,
+                      W8A8B8O8LinearParallel, W8A8B16O16Linear)
+from .packing import w4a8_quantize  # noqa: F401
 
 __version__ = "0.1.0"
