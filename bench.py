@@ -145,7 +145,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=CFG["B"],
+                    help="sequences per GPU; anything but the default is a reduced case for profiler captures, "
+                         "not the benchmark workload")
     args = ap.parse_args()
+    global WORKLOAD
+    if args.batch != CFG["B"]:
+        WORKLOAD = WORKLOAD.replace("batch 4", f"batch {args.batch} (REDUCED from 4: profiling case)")
+        CFG["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -210,7 +210,7 @@ def test_qcausalconv_forward_and_update():
 @gpu
 @pytest.mark.parametrize("grouped", [False, True])
 def test_quamb2conv_forward_and_update(grouped):
-    H, P, G, N, L, Bsz = 8, 64, 2, 64, 45, 2
+    H, P, G, N, L, Bsz = 8, 64, 2 if grouped else 1, 64, 45, 2      # per-tensor scales need a single SSD group
     c = make_conv2_case(Bsz, L, H, P, G, N, grouped=grouped, seed=11)
     d = c["xBC"].shape[1]
     q = M.Quamb2Conv1D(c["x_dim"], P, N, G, c["hgr"].shape[1] if grouped else 0, c["dgr"].shape[2] if grouped else 0,
