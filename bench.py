@@ -163,6 +163,7 @@ def main():
     import torch
     import torch.distributed as dist
     from quamba_b200 import ops, _lib
+    from quamba_b200.sharding import max_over_ranks
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
     torch.cuda.set_device(local_rank)
@@ -295,10 +296,7 @@ def main():
     ms_e2e = e2.elapsed_time(e3)
     _lib.read_device_status(stream.cuda_stream)
 
-    t = torch.tensor([ms_total, ms_e2e, conv_ms, ssd_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e, conv_ms, ssd_ms = t.tolist()
+    ms_total, ms_e2e, conv_ms, ssd_ms = max_over_ranks([ms_total, ms_e2e, conv_ms, ssd_ms], device=dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
