@@ -2,6 +2,7 @@
 """Benchmark of the quantized Mamba2 mixer hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --op NAME|all      # per-kernel lines (bench_ops.py), one GPU
 
 One "step" = one pass of the hot path over one batch of synthetic input:
 int8 causal conv1d over xBC (+SiLU, requant, x/B/C split) followed by the int8 SSD chunk scan with
@@ -148,7 +149,15 @@ def main():
     ap.add_argument("--batch", type=int, default=CFG["B"],
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures, "
                          "not the benchmark workload")
+    ap.add_argument("--op", default=None,
+                    help="measure one kernel of the path instead of the mixer step (see bench_ops.OPS; 'all' runs each); "
+                         "prints one JSON line per op")
     args = ap.parse_args()
+    if args.op is not None:
+        import bench_ops
+        for line in bench_ops.run(args.op, args.steps, args.warmup):
+            print(json.dumps(line), flush=True)
+        return
     global WORKLOAD
     if args.batch != CFG["B"]:
         WORKLOAD = WORKLOAD.replace("batch 4", f"batch {args.batch} (REDUCED from 4: profiling case)")

@@ -1,0 +1,261 @@
+"""Per-kernel measurements behind ``bench.py --op NAME``: one JSON line per op with its own roofline.
+
+Each op runs at the per-layer shape of the model configuration it belongs to (Mamba2-2.7B: d_model 2560, 80 heads x 64,
+d_state 128; Mamba1-2.8B: d_inner 5120, d_state 16), through the public ops API, inputs resident in HBM.  Timing: the
+call is captured into one CUDA graph per input set, the sets are replayed round-robin (enough sets that consecutive
+replays cannot hit L2: their summed footprint exceeds twice the 126 MB L2), CUDA events on the replay stream.
+"""
+import json
+import math
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+L2_BYTES = 126 * 2 ** 20
+
+
+def _peaks():
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        p = json.loads(pk.read_text())
+        return float(p.get("hbm_gbs", 6650.0)), float(p.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _i8(shape, dev, gen, std=40.0):
+    return (torch.randn(shape, device=dev, generator=gen) * std).round_().clamp_(-127, 127).to(torch.int8)
+
+
+class _ScaleCache:
+    """One-element fp32 device tensors by value, created before graph capture and reused inside it."""
+
+    def __init__(self, dev):
+        self.dev, self.t = dev, {}
+
+    def __call__(self, v):
+        if v not in self.t:
+            self.t[v] = torch.tensor([v], device=self.dev)
+        return self.t[v]
+
+
+def _sets_for(footprint_bytes, cap=48):
+    return max(2, min(cap, math.ceil(2.2 * L2_BYTES / max(footprint_bytes, 1))))
+
+
+def time_graphs(make_call, nsets, steps, warmup, stream):
+    """make_call(i) -> zero-argument callable running the op on input set i."""
+    calls = [make_call(i) for i in range(nsets)]
+    with torch.cuda.stream(stream):
+        for c in calls:
+            c()
+        stream.synchronize()
+        graphs, keep = [], []
+        for c in calls:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                keep.append(c())
+            graphs.append(g)
+        for i in range(max(warmup, 3)):
+            graphs[i % nsets].replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for i in range(steps):
+            graphs[i % nsets].replay()
+        e1.record(stream)
+        e1.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def op_conv(dev, gen, ops):
+    B, L, H, P, G, N, W = 4, 2048, 80, 64, 1, 128, 4
+    C = H * P + 2 * G * N
+    by = 2 * B * C * L + C * (W + 1)
+    n = _sets_for(by)
+    w, b = _i8((C, W), dev, gen), _i8((C,), dev, gen)
+    sx, sB, sC = (torch.tensor([v], device=dev) for v in (0.02, 0.015, 0.017))
+    xs = [_i8((B, L, C), dev, gen).transpose(1, 2) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops.quamba2_conv1d_cuda.fwd(xs[i], 0.03, 0.03, 0.03, H * P, P, N, G, None, None, sx, sB,
+                                                   sC, w, 0.004, 0.004, 0.004, b, 0.0005, 0.0005, 0.0005, None, None,
+                                                   None, True)
+    return dict(workload=f"Quamba2 conv1d fwd B{B} L{L} C{C} W{W} channel-last", bytes=by, flops=0, nsets=n, make=mk,
+                kernel="conv1d_channel_last_kernel", launches=1)
+
+
+def op_conv_update(dev, gen, ops):
+    B, H, P, G, N, W = 64, 80, 64, 1, 128, 4
+    C = H * P + 2 * G * N
+    by = B * C * (2 + 2 * W) + C * (W + 1)
+    n = _sets_for(by)
+    w, b = _i8((C, W), dev, gen), _i8((C,), dev, gen)
+    sx, sB, sC = (torch.tensor([v], device=dev) for v in (0.02, 0.015, 0.017))
+    xs = [_i8((B, C), dev, gen) for _ in range(n)]
+    st = [_i8((B, C, W), dev, gen) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops.quamba2_conv1d_cuda.update(xs[i], st[i], 0.03, 0.03, 0.03, H * P, P, N, G, None, None, sx,
+                                                      sB, sC, w, 0.004, 0.004, 0.004, b, 0.0005, 0.0005, 0.0005,
+                                                      None, None, None, True)
+    return dict(workload=f"Quamba2 conv1d decode step B{B} C{C} W{W}", bytes=by, flops=0, nsets=n, make=mk,
+                kernel="conv1d_update_kernel", launches=1)
+
+
+def op_hadamard(dev, gen, ops):
+    M, D = 8192, 5120
+    by = 3 * M * D
+    n = _sets_for(by)
+    xs = [torch.randn((M, D), device=dev, generator=gen, dtype=torch.float16) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops.quant_hadamard.fast_hadamard_transform_40N(xs[i], 1.0 / math.sqrt(D) / 0.03)
+    return dict(workload=f"Hadamard(40 x 128) + int8 quantise, {M} rows x {D} fp16", bytes=by, flops=0, nsets=n, make=mk,
+                kernel="hadamard_quant_kernel", launches=1)
+
+
+def op_sscan(dev, gen, ops):
+    B, D, L, N = 16, 5120, 1024, 16
+    by = B * D * L * 5 + 2 * B * N * L + B * D * N + D * (N + 2)
+    n = _sets_for(by, cap=3)
+    A = _i8((D, N), dev, gen)
+    Dv, bias = _i8((D,), dev, gen), _i8((D,), dev, gen)
+    s = _ScaleCache(dev)
+    sets = [dict(u=_i8((B, D, L), dev, gen), dt=_i8((B, D, L), dev, gen), z=_i8((B, D, L), dev, gen),
+                 Bm=_i8((B, 1, N, L), dev, gen), Cm=_i8((B, 1, N, L), dev, gen)) for _ in range(n)]
+
+    def mk(i):
+        d = sets[i]
+        return lambda: ops.quant_sscan_cuda.fwd(d["u"], s(0.03), d["dt"], s(0.03), A, s(0.02), d["Bm"], s(0.03), d["Cm"], s(0.03),
+                                                s(0.05), Dv, s(0.01), d["z"], s(0.03), bias, s(0.03), True)
+    return dict(workload=f"Mamba1 int8 selective scan fwd B{B} D{D} L{L} N{N} (Mamba1-2.8B layer, batch 16 x 1024)", bytes=by,
+                flops=0, nsets=n, make=mk, kernel="sscan_fwd_kernel", launches=1)
+
+
+def op_ssd(dev, gen, ops):
+    B, L, H, P, G, N, Q = 4, 2048, 80, 64, 1, 128, 256
+    by = B * L * (H * P + H + 2 * G * N) + 2 * B * L * H * P + B * H * P * N
+    n = _sets_for(by)
+    s = _ScaleCache(dev)
+    A, Dv = _i8((H,), dev, gen), _i8((H,), dev, gen)
+    bias = (torch.rand(H, device=dev, generator=gen) * 2 - 4).half()
+    sets = [dict(x=_i8((B, L, H, P), dev, gen), dt=_i8((B, L, H), dev, gen), Bm=_i8((B, L, G, N), dev, gen),
+                 Cm=_i8((B, L, G, N), dev, gen)) for _ in range(n)]
+
+    def mk(i):
+        d = sets[i]
+        return lambda: ops._quant_mamba_chunk_scan_combined_fwd(d["x"], s(0.03), d["dt"], s(0.03), A, s(0.02), d["Bm"], s(0.03),
+                                                                d["Cm"], s(0.03), s(0.01), Q, Dv, s(0.01), None, None, bias, None,
+                                                                None, None, True)
+    fl = 2 * B * H * L * 128 * (N + P + 2 * P)          # per 128-token block: C.B^T, Lm.X, C.S, Xw^T.B
+    return dict(workload=f"Mamba2 int8 SSD chunk scan B{B} L{L} H{H} P{P} G{G} N{N} Q{Q}", bytes=by, flops=fl, nsets=n, make=mk,
+                kernel="ssd_tc_kernel (+ ssd_widen_bc_kernel, ssd_dt_kernel)", launches=3)
+
+
+def op_ssd_update(dev, gen, ops):
+    B, H, P, G, N = 64, 80, 64, 1, 128
+    by = 2 * B * H * P * N + B * (H * P * 3 + H + 2 * G * N)
+    n = _sets_for(by)
+    s = _ScaleCache(dev)
+    A = _i8((H,), dev, gen)[:, None, None].expand(-1, P, N)
+    Dv = _i8((H,), dev, gen)[:, None].expand(-1, P)
+    bias = (torch.rand(H, device=dev, generator=gen) * 2 - 4).half()[:, None].expand(-1, P)
+    sets = [dict(st=_i8((B, H, P, N), dev, gen), x=_i8((B, H, P), dev, gen), dt=_i8((B, H), dev, gen)[:, :, None].expand(-1, -1, P),
+                 Bm=_i8((B, G, N), dev, gen), Cm=_i8((B, G, N), dev, gen)) for _ in range(n)]
+
+    def mk(i):
+        d = sets[i]
+        return lambda: ops.quant_sscan_update_triton(d["st"], d["x"], s(0.03), d["dt"], s(0.03), A, s(0.02), s(0.01), d["Bm"],
+                                                     s(0.03), d["Cm"], s(0.03), Dv, s(0.01), None, None, bias, None, True)
+    return dict(workload=f"Mamba2 int8 state update (decode) B{B} H{H} P{P} N{N}", bytes=by, flops=0, nsets=n, make=mk,
+                kernel="sscan_update_kernel", launches=1)
+
+
+def _w4a8(dev, gen, ops, M, K, N, out_int8, tag):
+    from quamba_b200.packing import w4a8_quantize
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(K, N, generator=g) * 0.02).half()
+    _, packed, sg, sc = w4a8_quantize(w, 4, 128)
+    packed, sg, sc = packed.to(dev), sg.to(dev), sc.to(dev)
+    by = M * K + K * N // 2 + M * N * (1 if out_int8 else 2)
+    n = _sets_for(by)
+    xs = [_i8((M, K), dev, gen) for _ in range(n)]
+    st = torch.tensor(0.03, device=dev)
+    ws = torch.zeros(N // 64 * 16, dtype=torch.int32, device=dev)
+    fn = ops.quant_linear_cuda.w4a8o8_gemm if out_int8 else ops.quant_linear_cuda.w4a8o16_gemm
+
+    def mk(i):
+        return lambda: fn(xs[i], packed, st, sc, sg, ws, M, N, K, False)
+    return dict(workload=f"W4A8 GEMM {tag}: M{M} K{K} N{N}, int4 group-128 weights, {'int8' if out_int8 else 'fp16'} out",
+                bytes=by, flops=2 * M * N * K, nsets=n, make=mk, kernel="gemm_s8_tcgen05_kernel", launches=1,
+                note="weights unpacked to int8 once at first use (cached); the timed GEMM streams int8 weights")
+
+
+def op_w4a8_in(dev, gen, ops):
+    return _w4a8(dev, gen, ops, 8192, 2560, 10624, True, "Mamba2-2.7B in_proj, 4 x 2048 tokens")
+
+
+def op_w4a8_out(dev, gen, ops):
+    return _w4a8(dev, gen, ops, 8192, 5120, 2560, False, "Mamba2-2.7B out_proj, 4 x 2048 tokens")
+
+
+def op_w4a8_decode(dev, gen, ops):
+    return _w4a8(dev, gen, ops, 1, 2560, 10624, True, "Mamba2-2.7B in_proj, one token")
+
+
+def op_w8a8(dev, gen, ops):
+    M, K, N = 16384, 2560, 10240
+    by = M * K + K * N + M * N
+    n = _sets_for(by)
+    w = _i8((N, K), dev, gen).t()
+    xs = [_i8((M, K), dev, gen) for _ in range(n)]
+    a, b = torch.tensor([[0.5]], device=dev), torch.tensor([[0.001]], device=dev)
+    ys = [torch.empty((M, N), dtype=torch.int8, device=dev) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops.quant_linear_cuda.cutlass_scaled_mm_dq(ys[i], xs[i], w, a, b)
+    return dict(workload=f"W8A8 GEMM Mamba1-2.8B in_proj, 16 x 1024 tokens: M{M} K{K} N{N}, int8 out", bytes=by,
+                flops=2 * M * N * K, nsets=n, make=mk, kernel="gemm_s8_tcgen05_kernel", launches=1)
+
+
+OPS = {"conv": op_conv, "conv_update": op_conv_update, "hadamard": op_hadamard, "sscan": op_sscan, "ssd": op_ssd,
+       "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out, "w4a8_decode": op_w4a8_decode,
+       "w8a8": op_w8a8}
+
+
+def run(name, steps, warmup):
+    """Returns the list of JSON-able result lines for ``name`` ('all' runs every op)."""
+    from quamba_b200 import _lib, ops
+    assert torch.cuda.is_available(), "needs a CUDA device; there is no CPU fallback"
+    dev = torch.device("cuda", 0)
+    hbm, bf16, src = _peaks()
+    int8_peak = 2.0 * bf16                                  # dense int8 tensor peak = 2 x the measured bf16 GEMM peak
+    stream = torch.cuda.Stream(device=dev)
+    out = []
+    for nm in (list(OPS) if name == "all" else [name]):
+        gen = torch.Generator(device=dev).manual_seed(0)
+        spec = OPS[nm](dev, gen, ops)
+        ms = time_graphs(spec["make"], spec["nsets"], steps, warmup, stream)
+        _lib.read_device_status(stream.cuda_stream)
+        gbs = spec["bytes"] / (ms * 1e-3) / 1e9
+        tfl = spec["flops"] / (ms * 1e-3) / 1e12
+        t_hbm, t_tc = spec["bytes"] / (hbm * 1e9), spec["flops"] / (int8_peak * 1e12)
+        tensor_bound = nm.startswith("w") and t_tc > t_hbm
+        roof = ({"bound": "tensor", "achieved": tfl, "peak": int8_peak, "unit": "TFLOP/s", "frac": tfl / int8_peak}
+                if tensor_bound else {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm})
+        roof.update(kernel=spec["kernel"], traffic=None, peak_source=src, algorithmic_bytes=spec["bytes"], flops=spec["flops"],
+                    ms=ms)
+        if tensor_bound:
+            roof["peak_note"] = "2 x measured bf16 cuBLAS peak (dense int8 rate is twice bf16)"
+        line = {"op": nm, "metric": "kernel_time_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3),
+                "higher_is_better": False, "data": "synthetic", "config": {"workload": spec["workload"],
+                                                                            "l2": f"{spec['nsets']} rotating input sets"},
+                "gpu_launches": spec["launches"] * steps, "roofline": roof}
+        if "note" in spec:
+            line["config"]["note"] = spec["note"]
+        out.append(line)
+        del spec
+        torch.cuda.empty_cache()
+    return out

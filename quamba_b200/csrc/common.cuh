@@ -87,6 +87,14 @@ __device__ __forceinline__ uint32_t pack4_s8(int a, int b, int c, int d) {
   return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)d << 24);
 }
 
+// pack four ints into one little-endian word of int8, each saturated to [-128, 127]
+__device__ __forceinline__ uint32_t pack4_sat_s8(int a, int b, int c, int d) {
+  uint32_t hi, r;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+  return r;
+}
+
 // Grouped ("group_heads") lookup: number of cumulative range ends <= idx, clamped to n-1.
 __device__ __forceinline__ int group_lookup(const int32_t* range, int n, int idx) {
   int g = 0;

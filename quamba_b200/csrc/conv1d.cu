@@ -46,27 +46,35 @@ __device__ __forceinline__ int pack_taps(const int8_t* w, int width) {
   return (int)r;
 }
 
-__global__ void __launch_bounds__(128)
+constexpr int kCh = 4;       // channels per thread in the channel-last kernel = one 32-bit word
+constexpr int kClBlock = 256;
+
+// Channel-last layout.  A thread owns 4 adjacent channels (a warp reads / writes one 128-byte line per time step) and
+// walks `tl` consecutive steps; byte i of win[j] = x[l-3+i] of channel j.  Per output the arithmetic is
+//   prmt (slide window), dp4a into the bit pattern of 1.5*2^23 (so the sum is already a float: no I2F),
+//   one subtraction, h = a/2 and hv = a/(2*s_out) as two FMAs, tanh, v = hv*tanh(h) + hv, round, convert;
+// four results are packed with two saturating cvt.pack instructions.
+template <bool kSilu>
+__global__ void __launch_bounds__(kClBlock)
 conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t in_sl,
                            const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
-                           ClSegments seg, int batch, int dim, int seqlen, int width, int tl,
-                           int nseg, int silu) {
-  const int cv = dim / kVec;
+                           ClSegments seg, int batch, int dim, int seqlen, int width, int tl, int nseg) {
+  const int cv = dim / kCh;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = (int64_t)batch * nseg * cv;
   if (idx >= total) return;
   const int vec = (int)(idx % cv);
   const int sg = (int)((idx / cv) % nseg);
   const int b = (int)(idx / ((int64_t)cv * nseg));
-  const int c0 = vec * kVec;
+  const int c0 = vec * kCh;
   const int s = c0 < seg.end0 ? 0 : (c0 < seg.end1 ? 1 : 2);
   const int cbase = s == 0 ? 0 : (s == 1 ? seg.end0 : seg.end1);
 
-  int wpk[kVec];
-  float hb[kVec], inv_out[kVec];
-  const float hs_in = 0.5f * seg.scale_in[s];
+  int wpk[kCh];
+  float hb[kCh], hsi[kCh], hbi[kCh];
+  const float hs = 0.5f * seg.scale_in[s];
 #pragma unroll
-  for (int j = 0; j < kVec; ++j) {
+  for (int j = 0; j < kCh; ++j) {
     const int c = c0 + j;
     wpk[j] = pack_taps(weight + (int64_t)c * width, width);
     hb[j] = bias != nullptr ? 0.5f * seg.scale_bias[s] * (float)bias[c] : 0.0f;
@@ -86,7 +94,9 @@ conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t
     } else {
       so = seg.out_scales[s][(c - cbase) / seg.d_state];
     }
-    inv_out[j] = 1.0f / so;
+    const float inv = 1.0f / so;
+    hsi[j] = hs * inv;
+    hbi[j] = hb[j] * inv;
   }
 
   const int l0 = sg * tl;
@@ -95,50 +105,47 @@ conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t
   int8_t* dst = seg.dst[s] + (int64_t)b * seg.dst_sb[s] + (c0 - cbase);
   const int64_t dsl = seg.dst_sl[s];
 
-  // windows: byte i of win[j] = x[l-3+i] of channel j
-  uint32_t win[kVec];
+  uint32_t win[kCh];
 #pragma unroll
-  for (int j = 0; j < kVec; ++j) win[j] = 0;
+  for (int j = 0; j < kCh; ++j) win[j] = 0;
 #pragma unroll
   for (int h = 3; h >= 1; --h) {
     const int l = l0 - h;
-    uint4 r = make_uint4(0, 0, 0, 0);
-    if (l >= 0) r = *reinterpret_cast<const uint4*>(src + (int64_t)l * in_sl);
-    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+    const uint32_t r = l >= 0 ? __ldg(reinterpret_cast<const uint32_t*>(src + (int64_t)l * in_sl)) : 0u;
 #pragma unroll
-    for (int j = 0; j < kVec; ++j) win[j] = __byte_perm(win[j], rw[j >> 2], 0x0321 | ((4 + (j & 3)) << 12));
+    for (int j = 0; j < kCh; ++j) win[j] = __byte_perm(win[j], r, 0x0321 | ((4 + j) << 12));
   }
 
-  constexpr int kUnroll = 4;
+  constexpr int kUnroll = 8;
+  constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: int bits 0x4B400000 + n read back as the float kMagic + n
+  const int8_t* p = src + (int64_t)l0 * in_sl;
+  int8_t* o = dst + (int64_t)l0 * dsl;
   for (int l = l0; l < l1; l += kUnroll) {
-    uint4 rows[kUnroll];
+    uint32_t rows[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      rows[u] = (l + u < l1) ? __ldg(reinterpret_cast<const uint32_t*>(p + (int64_t)u * in_sl)) : 0u;
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      rows[u] = make_uint4(0, 0, 0, 0);
-      if (l + u < l1) rows[u] = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)(l + u) * in_sl));
-    }
+      int q[kCh];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      if (l + u < l1) {
-        const uint32_t rw[4] = {rows[u].x, rows[u].y, rows[u].z, rows[u].w};
-        uint32_t ow[4];
-#pragma unroll
-        for (int w4 = 0; w4 < 4; ++w4) {
-          int q[4];
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const int j = w4 * 4 + jj;
-            win[j] = __byte_perm(win[j], rw[w4], 0x0321 | ((4 + jj) << 12));
-            const int acc = __dp4a((int)win[j], wpk[j], 0);
-            const float h = fmaf((float)acc, hs_in, hb[j]);  // half of the pre-activation
-            const float y = silu ? fmaf(h, tanh_approx(h), h) : 2.0f * h;
-            q[jj] = round_away_s8(y * inv_out[j]);
-          }
-          ow[w4] = pack4_s8(q[0], q[1], q[2], q[3]);
+      for (int j = 0; j < kCh; ++j) {
+        win[j] = __byte_perm(win[j], rows[u], 0x0321 | ((4 + j) << 12));
+        const float f = __int_as_float(__dp4a((int)win[j], wpk[j], 0x4B400000)) - kMagic;
+        const float hv = fmaf(f, hsi[j], hbi[j]);
+        float v;
+        if (kSilu) {
+          const float h = fmaf(f, hs, hb[j]);
+          v = fmaf(hv, tanh_approx(h), hv);
+        } else {
+          v = hv + hv;
         }
-        *reinterpret_cast<uint4*>(dst + (int64_t)(l + u) * dsl) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        q[j] = __float2int_rz(v + copysignf(0.5f, v));
       }
+      if (l + u < l1) *reinterpret_cast<uint32_t*>(o + (int64_t)u * dsl) = pack4_sat_s8(q[0], q[1], q[2], q[3]);
     }
+    p += (int64_t)kUnroll * in_sl;
+    o += (int64_t)kUnroll * dsl;
   }
 }
 
@@ -264,13 +271,31 @@ conv1d_update_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd,
 }
 
 int pick_tl(int64_t rows_of_vectors, int seqlen) {
-  // Largest time tile that still leaves ~8 CTAs of 128 threads per SM; the 3-row halo re-read
-  // costs 3/TL extra L2 traffic, so prefer long tiles when the problem is large enough.
-  const int64_t want = (int64_t)sm_count() * 8 * 128;
-  for (int tl = 64; tl >= 8; tl >>= 1) {
+  // Largest time tile that still gives every SM ~32 resident warps; the 3-row halo re-read costs 3/TL extra L2
+  // traffic, so prefer long tiles when the problem is large enough.
+  const int64_t want = (int64_t)sm_count() * 32 * 32;
+  for (int tl = 128; tl >= 8; tl >>= 1) {
     if (rows_of_vectors * ceil_div(seqlen, tl) >= want) return tl;
   }
   return 8;
+}
+
+int launch_channel_last(const int8_t* in, int64_t in_sb, int64_t in_sl, const int8_t* weight, const int8_t* bias,
+                        const ClSegments& seg, int batch, int dim, int seqlen, int width, int silu, cudaStream_t stream) {
+  const int cv = dim / kCh;
+  const int tl = pick_tl((int64_t)batch * cv, seqlen);
+  const int nseg = (int)ceil_div(seqlen, tl);
+  const int64_t total = (int64_t)batch * nseg * cv;
+  const unsigned grid = (unsigned)ceil_div(total, kClBlock);
+  if (silu) {
+    conv1d_channel_last_kernel<true><<<grid, kClBlock, 0, stream>>>(in, in_sb, in_sl, weight, bias, seg, batch, dim, seqlen,
+                                                                    width, tl, nseg);
+  } else {
+    conv1d_channel_last_kernel<false><<<grid, kClBlock, 0, stream>>>(in, in_sb, in_sl, weight, bias, seg, batch, dim, seqlen,
+                                                                     width, tl, nseg);
+  }
+  QB_LAUNCH_OK("conv1d_channel_last_kernel");
+  return QB_OK;
 }
 
 }  // namespace
@@ -309,14 +334,8 @@ extern "C" int qb_quamba2_conv1d_fwd(const qb_quamba2_conv1d_fwd_args* a, void* 
   seg.head_group_range = a->head_group_range; seg.dim_group_range = a->dim_group_range;
   seg.nhead_groups = a->nhead_groups; seg.ndim_groups = a->ndim_groups; seg.headdim = a->x_headdim;
   seg.x_group_size = a->x_dim / a->n_groups; seg.d_state = a->d_state; seg.grouped = grouped ? 1 : 0;
-  const int cv = a->dim / kVec;
-  const int tl = pick_tl((int64_t)a->batch * cv, a->seqlen);
-  const int nseg = (int)ceil_div(a->seqlen, tl);
-  const int64_t total = (int64_t)a->batch * nseg * cv;
-  conv1d_channel_last_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
-      a->xBC, a->xBC_sb, a->xBC_sl, a->weight, a->bias, seg, a->batch, a->dim, a->seqlen, a->width, tl, nseg, a->silu);
-  QB_LAUNCH_OK("conv1d_channel_last_kernel");
-  return QB_OK;
+  return launch_channel_last(a->xBC, a->xBC_sb, a->xBC_sl, a->weight, a->bias, seg, a->batch, a->dim, a->seqlen, a->width,
+                             a->silu, (cudaStream_t)stream);
 }
 
 extern "C" int qb_causal_conv1d_fwd(const qb_conv1d_fwd_args* a, void* stream) {
@@ -340,14 +359,8 @@ extern "C" int qb_causal_conv1d_fwd(const qb_conv1d_fwd_args* a, void* stream) {
     }
     seg.out_scale_value = a->scale_out;
     seg.end0 = seg.end1 = a->dim;
-    const int cv = a->dim / kVec;
-    const int tl = pick_tl((int64_t)a->batch * cv, a->seqlen);
-    const int nseg = (int)ceil_div(a->seqlen, tl);
-    const int64_t total = (int64_t)a->batch * nseg * cv;
-    conv1d_channel_last_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
-        a->x, a->x_sb, a->x_sl, a->weight, a->bias, seg, a->batch, a->dim, a->seqlen, a->width, tl, nseg, a->silu);
-    QB_LAUNCH_OK("conv1d_channel_last_kernel");
-    return QB_OK;
+    return launch_channel_last(a->x, a->x_sb, a->x_sl, a->weight, a->bias, seg, a->batch, a->dim, a->seqlen, a->width,
+                               a->silu, (cudaStream_t)stream);
   }
   QB_REQUIRE(a->out_sl == 1, QB_ERR_INVALID_ARG, "out must have the layout of x");
   const int vec_ok = (a->seqlen % kVec == 0) && (a->x_sd % kVec == 0) && (a->x_sb % kVec == 0) && (a->out_sd % kVec == 0) &&

@@ -150,6 +150,74 @@ gemm_s8_dp4a_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __r
     }
 }
 
+// ---- skinny-M kernel (decode: M = batch of single tokens) --------------------------------------------------------
+// HBM-bound on the weights: each warp streams kNW rows of W (K-contiguous int8) with 16-byte loads, every lane taking
+// chunks 512 bytes apart, and multiplies them against up to MB rows of A (re-read through L1/L2, they are small).
+// dp4a accumulation, shuffle reduction, the shared epilogue.
+constexpr int kGemvWarps = 8;
+constexpr int kNW = 2;
+
+template <int MB>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restrict__ W, int64_t ldw, int M, int N, int K,
+               Epilogue ep) {
+  const int lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW;
+  if (n0 >= N) return;
+  const int chunks = K / 16;
+  for (int m0 = 0; m0 < M; m0 += MB) {
+    int acc[MB][kNW];
+#pragma unroll
+    for (int i = 0; i < MB; ++i)
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) acc[i][j] = 0;
+#pragma unroll 2
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 w[kNW];
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) {
+        const int n = min(n0 + j, N - 1);
+        w[j] = __ldg(reinterpret_cast<const uint4*>(W + (int64_t)n * ldw) + c);
+      }
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const int m = min(m0 + i, M - 1);
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + c);
+#pragma unroll
+        for (int j = 0; j < kNW; ++j) {
+          int t = acc[i][j];
+          t = __dp4a((int)a.x, (int)w[j].x, t);
+          t = __dp4a((int)a.y, (int)w[j].y, t);
+          t = __dp4a((int)a.z, (int)w[j].z, t);
+          t = __dp4a((int)a.w, (int)w[j].w, t);
+          acc[i][j] = t;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MB; ++i)
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) {
+        int t = acc[i][j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0 && m0 + i < M && n0 + j < N) ep.store(t, m0 + i, n0 + j);
+      }
+  }
+}
+
+int launch_gemv(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K, const Epilogue& ep,
+                cudaStream_t st) {
+  if (K % 16 != 0 || lda % 16 != 0 || ldw % 16 != 0 || !aligned(A, 16) || !aligned(W, 16)) return QB_ERR_UNSUPPORTED;
+  const unsigned grid = (unsigned)ceil_div(N, kGemvWarps * kNW);
+  if (M == 1) gemv_s8_kernel<1><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
+  else if (M == 2) gemv_s8_kernel<2><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
+  else if (M <= 4) gemv_s8_kernel<4><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
+  else gemv_s8_kernel<8><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
+  QB_LAUNCH_OK("gemv_s8_kernel");
+  return QB_OK;
+}
+
 int launch_portable(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K,
                     const Epilogue& ep, cudaStream_t st) {
   dim3 grid((unsigned)ceil_div(N, GT), (unsigned)ceil_div(M, GT));
@@ -166,6 +234,10 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
 
 int run_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K, const Epilogue& ep,
              cudaStream_t st) {
+  if (M < 32) {  // decode-sized problems stream the weights once; the 128-row MMA tile would be mostly padding
+    const int rc = launch_gemv(A, lda, W, ldw, M, N, K, ep, st);
+    if (rc != QB_ERR_UNSUPPORTED) return rc;
+  }
   const int rc = launch_tensor_core_gemm(A, lda, W, ldw, M, N, K, ep, st);
   if (rc != QB_ERR_UNSUPPORTED) return rc;
   return launch_portable(A, lda, W, ldw, M, N, K, ep, st);

@@ -251,6 +251,117 @@ sscan_update_kernel(qb_sscan_update_args a) {
   }
 }
 
+
+// Streaming form of the decode step for the common layouts (dstate a multiple of 16, 16-byte aligned state rows, all
+// rows of a CTA in one (batch, SSD group)).  LANES lanes share one (b, h, p) row, each owning 16-byte pieces of the
+// int8 state.  B and C are converted and scaled once per CTA into shared memory, exp(A_scale * q) comes from a
+// 256-entry table (A_log is int8), the int8 state is widened with a byte permute into the mantissa of 2^15 (no
+// integer-to-float conversion instruction), and the new state is rounded and packed four at a time.
+template <int LANES>
+__global__ void __launch_bounds__(256)
+sscan_update_stream_kernel(qb_sscan_update_args a, int iters) {
+  constexpr int ROWS = 256 / LANES;
+  constexpr float kLog2e = 1.4426950408889634f;
+  __shared__ __align__(16) float sB[256];
+  __shared__ __align__(16) float sC[256];
+  __shared__ float sLut[256];  // -exp(A_scale * q) * log2(e), q = index - 128
+  const int tid = threadIdx.x;
+  const int64_t rows = (int64_t)a.batch * a.nheads * a.headdim;
+  const int64_t rows_per_b = (int64_t)a.nheads * a.headdim;
+  const int64_t row0 = (int64_t)blockIdx.x * ROWS;
+  const int hpg = a.nheads / a.ngroups;
+  const int b = (int)(row0 / rows_per_b);
+  const int g = (int)(((row0 % rows_per_b) / a.headdim) / hpg);
+  {
+    const float Bs = a.grouped ? a.B_scale[g] : a.B_scale[0];
+    const float Cs = a.grouped ? a.C_scale[g] : a.C_scale[0];
+    const int8_t* Bq = a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg;
+    const int8_t* Cq = a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg;
+    if (tid < a.dstate) {
+      sB[tid] = Bs * (float)Bq[tid];
+      sC[tid] = Cs * (float)Cq[tid];
+    }
+    sLut[tid] = -__expf((*a.A_scale) * (float)(tid - 128)) * kLog2e;
+  }
+  __syncthreads();
+  const int64_t row = row0 + tid / LANES;
+  const int sub = tid % LANES;
+  if (row >= rows) return;
+  const int p = (int)(row % a.headdim);
+  const int hd = (int)((row / a.headdim) % a.nheads);
+
+  float xs, ss0 = 0.0f;
+  const float* ssn = nullptr;
+  if (a.grouped) {
+    const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, hd % hpg);
+    const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
+    xs = a.x_scales[(g * a.nhead_groups + hg) * a.ndim_groups + dg];
+    ssn = a.state_scale + ((int64_t)(g * a.nhead_groups + hg) * a.ndim_groups + dg) * a.dstate;
+  } else {
+    xs = a.x_scales[0];
+    ss0 = a.state_scale[0];
+  }
+  const float x = xs * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
+  float dt = (*a.dt_scale) * (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp];
+  if (a.dt_bias != nullptr) {
+    const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
+    if (a.dt_bias_is_half) dt += __half2float(static_cast<const __half*>(a.dt_bias)[bi]);
+    else dt += (*a.dt_bias_scale) * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
+  }
+  if (a.dt_softplus) dt = softplus_f(dt);
+  const float dtx = dt * x;
+  const int8_t* Aq = a.A_log + (int64_t)hd * a.A_sh + (int64_t)p * a.A_sp;
+  const bool tied = a.A_sn == 0;
+  const float dA_tied = tied ? fast_exp2(sLut[(int)Aq[0] + 128] * dt) : 0.0f;
+  const float inv0 = a.grouped ? 0.0f : 1.0f / ss0;
+  int8_t* st = a.state + (int64_t)b * a.state_sb + (int64_t)hd * a.state_sh + (int64_t)p * a.state_sp;
+
+  float y = 0.0f;
+  for (int it = 0; it < iters; ++it) {
+    const int n0 = (it * LANES + sub) * 16;
+    const uint4 raw = *reinterpret_cast<const uint4*>(st + n0);
+    const uint32_t w[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+    uint32_t ow[4];
+#pragma unroll
+    for (int k4 = 0; k4 < 4; ++k4) {
+      const float4 bf = *reinterpret_cast<const float4*>(sB + n0 + 4 * k4);
+      const float4 cf = *reinterpret_cast<const float4*>(sC + n0 + 4 * k4);
+      const float bb[4] = {bf.x, bf.y, bf.z, bf.w};
+      const float cc[4] = {cf.x, cf.y, cf.z, cf.w};
+      float ssv[4] = {ss0, ss0, ss0, ss0}, inv[4] = {inv0, inv0, inv0, inv0};
+      if (a.grouped) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(ssn + n0 + 4 * k4));
+        ssv[0] = t.x; ssv[1] = t.y; ssv[2] = t.z; ssv[3] = t.w;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) inv[k] = __frcp_rn(ssv[k]);
+      }
+      int q[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        // bytes [0, v + 128, 0, 0x47] read as a float = 32768 + (v + 128)
+        const float sv = __uint_as_float(__byte_perm(w[k4], 0x47000000u, 0x7404 | (k << 4))) - 32896.0f;
+        float dA = dA_tied;
+        if (!tied) dA = fast_exp2(sLut[(int)Aq[(int64_t)(n0 + 4 * k4 + k) * a.A_sn] + 128] * dt);
+        const float snew = fmaf(bb[k], dtx, (ssv[k] * sv) * dA);
+        q[k] = __float2int_rn(snew * inv[k]);
+        y = fmaf(snew, cc[k], y);
+      }
+      ow[k4] = pack4_sat_s8(q[0], q[1], q[2], q[3]);
+    }
+    *reinterpret_cast<uint4*>(st + n0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+#pragma unroll
+  for (int m = 1; m < LANES; m <<= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
+  if (sub == 0) {
+    if (a.D != nullptr) y = fmaf(x, (*a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp], y);
+    if (a.z != nullptr) {
+      const float z = (*a.z_scale) * (float)a.z[(int64_t)b * a.z_sb + (int64_t)hd * a.z_sh + p];
+      y *= silu_exact(z);
+    }
+    static_cast<__half*>(a.out)[(int64_t)b * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
+  }
+}
+
 }  // namespace
 }  // namespace qb
 
@@ -308,6 +419,29 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
   QB_REQUIRE(a->nheads % a->ngroups == 0, QB_ERR_INVALID_ARG, "nheads must be divisible by ngroups");
   QB_REQUIRE(!a->grouped || (a->head_group_range && a->dim_group_range && a->nhead_groups > 0 && a->ndim_groups > 0),
              QB_ERR_INVALID_ARG, "sscan_update: grouped scales need the range tables");
+  // streaming kernel: 16-byte pieces of aligned state rows, every CTA inside one (batch, SSD group)
+  if (a->dstate % 16 == 0 && a->dstate <= 256 && aligned(a->state, 16) && a->state_sp % 16 == 0 && a->state_sh % 16 == 0 &&
+      a->state_sb % 16 == 0 && (!a->grouped || aligned(a->state_scale, 16))) {
+    const int pieces = a->dstate / 16;
+    int lanes = 1;
+    while (lanes < 8 && pieces % (2 * lanes) == 0) lanes *= 2;
+    const int rows_per_cta = 256 / lanes;
+    const int64_t rows_per_group = (int64_t)(a->nheads / a->ngroups) * a->headdim;
+    if (rows_per_group % rows_per_cta == 0) {
+      const int64_t rows = (int64_t)a->batch * a->nheads * a->headdim;
+      const unsigned grid = (unsigned)(rows / rows_per_cta);
+      const int iters = pieces / lanes;
+      cudaStream_t st = (cudaStream_t)stream;
+      switch (lanes) {
+        case 1: sscan_update_stream_kernel<1><<<grid, 256, 0, st>>>(*a, iters); break;
+        case 2: sscan_update_stream_kernel<2><<<grid, 256, 0, st>>>(*a, iters); break;
+        case 4: sscan_update_stream_kernel<4><<<grid, 256, 0, st>>>(*a, iters); break;
+        default: sscan_update_stream_kernel<8><<<grid, 256, 0, st>>>(*a, iters); break;
+      }
+      QB_LAUNCH_OK("sscan_update_stream_kernel");
+      return QB_OK;
+    }
+  }
   const int64_t threads = (int64_t)a->batch * a->nheads * a->headdim * 8;
   sscan_update_kernel<<<(unsigned)ceil_div(threads, 128), 128, 0, (cudaStream_t)stream>>>(*a);
   QB_LAUNCH_OK("sscan_update_kernel");

@@ -274,7 +274,7 @@ def test_qsscan_forward_and_update():
         args = (c["q_u"][:, :, tk], c["q_delta"][:, :, tk], c["q_B"][:, 0, :, tk], c["q_C"][:, 0, :, tk])
         out, st2 = q.update(st_dev, *(d(a.contiguous()) for a in args), z=d(c["q_z"][:, :, tk].contiguous()))
         assert st2 is st_dev
-        want, want_state = oupd.quant_sscan_update(want_state, args[0], c["s_u"], args[1], c["s_delta"], c["q_A"], c["s_A"],
+        want, _ = oupd.quant_sscan_update(want_state, args[0], c["s_u"], args[1], c["s_delta"], c["q_A"], c["s_A"],
                                                    c["s_state"], args[2], c["s_B"], args[3], c["s_C"], c["q_D"], c["s_D"],
                                                    c["q_z"][:, :, tk], c["s_z"], c["q_bias"], c["s_bias"], True)
         _fp16(out, want, rtol=2e-2, atol_rel=2e-3)
@@ -316,12 +316,13 @@ def test_chunkscan_forward_and_update(grouped, dh):
     D2 = c["q_D"] if dh else c["q_D"][:, None].expand(-1, P)
     b2 = c["dt_bias"][:, None].expand(-1, P)
     dt3 = dt1[:, :, None].expand(-1, -1, P)
+    want_st = fq_ref.clone()                                     # the oracle updates its int8 state in place
     if grouped:
-        want, want_st = oupd.quamba2_sscan_update(fq_ref.clone(), c["q_x"][:, 0], c["x_scales"], c["hgr"], c["dgr"], dt3,
+        want, _ = oupd.quamba2_sscan_update(want_st, c["q_x"][:, 0], c["x_scales"], c["hgr"], c["dgr"], dt3,
                                                   c["s_dt"], A3, c["s_A"], c["state_scale"], c["q_B"][:, 0], c["s_B"],
                                                   c["q_C"][:, 0], c["s_C"], D2, c["s_D"], None, None, b2, True)
     else:
-        want, want_st = oupd.quant_sscan_update(fq_ref.clone(), c["q_x"][:, 0], c["x_scales"], dt3, c["s_dt"], A3, c["s_A"],
+        want, _ = oupd.quant_sscan_update(want_st, c["q_x"][:, 0], c["x_scales"], dt3, c["s_dt"], A3, c["s_A"],
                                                 c["state_scale"], c["q_B"][:, 0], c["s_B"], c["q_C"][:, 0], c["s_C"], D2,
                                                 c["s_D"], None, None, b2, None, True)
     _fp16(out, want, rtol=2e-2, atol_rel=2e-3)
