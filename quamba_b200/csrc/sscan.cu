@@ -8,7 +8,9 @@
 //
 // Update: eight lanes share one (batch, head, channel) row of the int8 state (16 bytes each),
 // the y reduction is a 3-step shuffle.
+#include <algorithm>
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace qb {
 namespace {
@@ -362,6 +364,205 @@ sscan_update_stream_kernel(qb_sscan_update_args a, int iters) {
   }
 }
 
+
+// Pipelined form of the streaming decode step for a fully contiguous state (B, H, P, N): the state is a flat matrix of
+// rows, so a tile of consecutive rows is one contiguous 8 KB block.  A persistent CTA walks a contiguous range of tiles
+// through a four-slot shared-memory ring: bulk-copy loads run two tiles ahead (completion on an mbarrier), the tile is
+// updated in place in shared memory, and a bulk-copy store drains it while the next tile is computed.  Memory-level
+// parallelism is therefore set by the ring, not by registers.  LPR = 16-byte pieces per state row (dstate = 16 * LPR).
+constexpr int kUpdTileBytes = 8192;
+constexpr int kUpdSlots = 4;
+constexpr int kStatusUpdateLoad = 301;
+
+template <int LPR, bool kTied, bool kGrouped>
+__global__ void __launch_bounds__(256)
+sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, int* status) {
+  using namespace tc;
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr int kDstate = 16 * LPR;
+  constexpr int kTileRows = kUpdTileBytes / kDstate;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(16) float sB[256];   // B[n] * B_scale (/ state_scale when it is one number)
+  __shared__ __align__(16) float sC[256];   // C[n] * C_scale (* state_scale when it is one number)
+  __shared__ float sLut[256];               // -exp(A_scale * q) * log2(e), q = index - 128
+  __shared__ float rX[kTileRows], rDtx[kTileRows], rDt[kTileRows], rdA[kTileRows], rY[kTileRows];
+  __shared__ int rScaleOfs[kTileRows];      // grouped scales: offset of the row's [dstate] state-scale vector
+  __shared__ __align__(8) uint64_t full[kUpdSlots];
+  const int tid = threadIdx.x;
+  const int t_begin = blockIdx.x * tiles_per_cta;
+  const int t_end = min(tiles, t_begin + tiles_per_cta);
+  if (t_begin >= t_end) return;
+  if (tid == 0) {
+    for (int i = 0; i < kUpdSlots; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+  }
+  sLut[tid] = -__expf((*a.A_scale) * (float)(tid - 128)) * kLog2e;
+  __syncthreads();
+  auto issue_load = [&](int t) {
+    const int slot = (t - t_begin) & (kUpdSlots - 1);
+    mbar_arrive_expect_tx(&full[slot], kUpdTileBytes);
+    bulk_load(ring + slot * kUpdTileBytes, a.state + (int64_t)t * kUpdTileBytes, kUpdTileBytes, &full[slot]);
+  };
+  if (tid == 0) {
+    issue_load(t_begin);
+    if (t_begin + 1 < t_end) issue_load(t_begin + 1);
+  }
+  const int hpg = a.nheads / a.ngroups;
+  constexpr bool tied = kTied;        // A_log has one value per row (stride 0 along dstate)
+  const float ss0 = kGrouped ? 1.0f : a.state_scale[0];
+  const int n0 = (tid % LPR) * 16;    // both pieces of a thread, in every tile, cover the same 16 states
+  float bb[16], cc[16];               // this thread's slice of sB / sC, refreshed when (batch, group) changes
+  // (batch, head, row-in-head) of the tile's first row, advanced incrementally: no 64-bit division in the tile loop
+  int b, hd0, p0;
+  {
+    const int64_t rows_per_b = (int64_t)a.nheads * a.headdim;
+    const int64_t row0 = (int64_t)t_begin * kTileRows;
+    b = (int)(row0 / rows_per_b);
+    const int rem = (int)(row0 % rows_per_b);
+    hd0 = rem / a.headdim;
+    p0 = rem % a.headdim;
+  }
+  int cur_bg = -1;
+  int prev_b = 0, prev_hd0 = 0, prev_p0 = 0;
+  // y of the previous tile: D skip term, z gate, fp16 store, one thread per row
+  auto finish_rows = [&](int fb, int fhd0, int fp0) {
+    for (int r = tid; r < kTileRows; r += 256) {
+      const unsigned pr = (unsigned)(fp0 + r);
+      const int hd = fhd0 + (int)(pr / (unsigned)a.headdim);
+      const int p = (int)(pr % (unsigned)a.headdim);
+      float y = rY[r];
+      if (a.D != nullptr) y = fmaf(rX[r], (*a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp], y);
+      if (a.z != nullptr) {
+        const float z = (*a.z_scale) * (float)a.z[(int64_t)fb * a.z_sb + (int64_t)hd * a.z_sh + p];
+        y *= silu_exact(z);
+      }
+      static_cast<__half*>(a.out)[(int64_t)fb * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
+    }
+  };
+  bool ok = true;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int k = t - t_begin;
+    const int slot = k & (kUpdSlots - 1);
+    if (k > 0) {
+      finish_rows(prev_b, prev_hd0, prev_p0);
+      p0 += kTileRows;
+      while (p0 >= a.headdim) { p0 -= a.headdim; ++hd0; }
+      while (hd0 >= a.nheads) { hd0 -= a.nheads; ++b; }
+      __syncthreads();  // rX / rY of the previous tile are consumed before they are overwritten
+    }
+    prev_b = b; prev_hd0 = hd0; prev_p0 = p0;
+    const int g = hd0 / hpg;
+    const bool restage = b * a.ngroups + g != cur_bg;  // block-uniform: the tile enters a new (batch, group)
+    if (restage) {
+      cur_bg = b * a.ngroups + g;
+      if (tid < kDstate) {
+        const float Bs = kGrouped ? a.B_scale[g] : a.B_scale[0];
+        const float Cs = kGrouped ? a.C_scale[g] : a.C_scale[0];
+        sB[tid] = Bs * (float)a.Bm[(int64_t)b * a.B_sb + (int64_t)g * a.B_sg + tid] / ss0;
+        sC[tid] = Cs * (float)a.Cm[(int64_t)b * a.C_sb + (int64_t)g * a.C_sg + tid] * ss0;
+      }
+    }
+    // per-row scalars, one thread per row, while the tile is still in flight
+    for (int r = tid; r < kTileRows; r += 256) {
+      const unsigned pr = (unsigned)(p0 + r);
+      const int hd = hd0 + (int)(pr / (unsigned)a.headdim);
+      const int p = (int)(pr % (unsigned)a.headdim);
+      float xs;
+      if (kGrouped) {
+        const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, hd % hpg);
+        const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
+        const int cell = (g * a.nhead_groups + hg) * a.ndim_groups + dg;
+        xs = a.x_scales[cell];
+        rScaleOfs[r] = cell * a.dstate;
+      } else {
+        xs = a.x_scales[0];
+      }
+      const float x = xs * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
+      float dt = (*a.dt_scale) * (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp];
+      if (a.dt_bias != nullptr) {
+        const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
+        if (a.dt_bias_is_half) dt += __half2float(static_cast<const __half*>(a.dt_bias)[bi]);
+        else dt += (*a.dt_bias_scale) * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
+      }
+      if (a.dt_softplus) dt = softplus_f(dt);
+      rX[r] = x;
+      rDt[r] = dt;
+      rDtx[r] = dt * x;
+      if (tied) rdA[r] = fast_exp2(sLut[(int)a.A_log[(int64_t)hd * a.A_sh + (int64_t)p * a.A_sp] + 128] * dt);
+    }
+    __syncthreads();
+    if (restage) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 bf = *reinterpret_cast<const float4*>(sB + n0 + 4 * i);
+        const float4 cf = *reinterpret_cast<const float4*>(sC + n0 + 4 * i);
+        bb[4 * i] = bf.x; bb[4 * i + 1] = bf.y; bb[4 * i + 2] = bf.z; bb[4 * i + 3] = bf.w;
+        cc[4 * i] = cf.x; cc[4 * i + 1] = cf.y; cc[4 * i + 2] = cf.z; cc[4 * i + 3] = cf.w;
+      }
+    }
+    if (!mbar_wait(&full[slot], (uint32_t)((k / kUpdSlots) & 1), status, kStatusUpdateLoad)) { ok = false; break; }
+    uint8_t* tile = ring + slot * kUpdTileBytes;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int piece = tid + e * 256;
+      const int r = piece / LPR;
+      uint4* cell = reinterpret_cast<uint4*>(tile + piece * 16);
+      const uint4 raw = *cell;
+      const uint32_t w[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+      const float dtx = rDtx[r];
+      const float dA_row = tied ? rdA[r] : 0.0f;
+      const float dt = tied ? 0.0f : rDt[r];
+      const int8_t* Aq = nullptr;
+      if (!tied) {
+        const unsigned pr = (unsigned)(p0 + r);
+        Aq = a.A_log + (int64_t)(hd0 + (int)(pr / (unsigned)a.headdim)) * a.A_sh + (int64_t)(pr % (unsigned)a.headdim) * a.A_sp +
+             (int64_t)n0 * a.A_sn;
+      }
+      const float* ssn = kGrouped ? a.state_scale + rScaleOfs[r] + n0 : nullptr;
+      uint32_t ow[4];
+      float y = 0.0f;
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        float bs[4], cs[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { bs[j] = bb[4 * k4 + j]; cs[j] = cc[4 * k4 + j]; }
+        if (kGrouped) {  // per-state scales: fold them into this piece's B and C values
+          const float4 sc = __ldg(reinterpret_cast<const float4*>(ssn + 4 * k4));
+          const float sv4[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { bs[j] *= __frcp_rn(sv4[j]); cs[j] *= sv4[j]; }
+        }
+        int q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // bytes [0, v + 128, 0, 0x47] read as a float = 32768 + (v + 128); v is the state in units of its scale
+          const float sv = __uint_as_float(__byte_perm(w[k4], 0x47000000u, 0x7404 | (j << 4))) - 32896.0f;
+          float dA = dA_row;
+          if (!tied) dA = fast_exp2(sLut[(int)Aq[(int64_t)(4 * k4 + j) * a.A_sn] + 128] * dt);
+          const float v = fmaf(bs[j], dtx, sv * dA);  // new state / state_scale
+          q[j] = __float2int_rn(v);
+          y = fmaf(v, cs[j], y);
+        }
+        ow[k4] = pack4_sat_s8(q[0], q[1], q[2], q[3]);
+      }
+      *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+#pragma unroll
+      for (int m = 1; m < LPR; m <<= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
+      if (piece % LPR == 0) rY[r] = y;
+    }
+    fence_proxy_async_smem();  // the tile was rewritten through the generic proxy; the bulk store reads it through the async one
+    __syncthreads();
+    if (tid == 0) {
+      bulk_store(a.state + (int64_t)t * kUpdTileBytes, tile, kUpdTileBytes);
+      bulk_commit();
+      bulk_wait_read<1>();  // every store but the newest has finished reading its slot
+      if (t + 2 < t_end) issue_load(t + 2);
+    }
+  }
+  if (ok) finish_rows(prev_b, prev_hd0, prev_p0);
+  if (tid == 0) bulk_wait_all<0>();
+}
+
 }  // namespace
 }  // namespace qb
 
@@ -419,6 +620,44 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
   QB_REQUIRE(a->nheads % a->ngroups == 0, QB_ERR_INVALID_ARG, "nheads must be divisible by ngroups");
   QB_REQUIRE(!a->grouped || (a->head_group_range && a->dim_group_range && a->nhead_groups > 0 && a->ndim_groups > 0),
              QB_ERR_INVALID_ARG, "sscan_update: grouped scales need the range tables");
+  // pipelined kernel: fully contiguous state, dstate in {16, 32, 64, 128, 256}, whole 8 KB tiles inside one (batch, group)
+  {
+    const int lpr = a->dstate / 16;
+    const bool pow2 = a->dstate % 16 == 0 && lpr >= 1 && lpr <= 16 && (lpr & (lpr - 1)) == 0;
+    const int64_t rows = (int64_t)a->batch * a->nheads * a->headdim;
+    const int64_t rows_per_group = (int64_t)(a->nheads / a->ngroups) * a->headdim;
+    if (pow2 && aligned(a->state, 16) && a->state_sp == a->dstate && a->state_sh == (int64_t)a->headdim * a->dstate &&
+        a->state_sb == (int64_t)a->nheads * a->headdim * a->dstate && (!a->grouped || aligned(a->state_scale, 16)) &&
+        rows_per_group % (kUpdTileBytes / a->dstate) == 0) {
+      const int tiles = (int)(rows * a->dstate / kUpdTileBytes);
+      const int ctas = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * 4);
+      const int tiles_per_cta = (int)ceil_div(tiles, ctas);
+      const unsigned grid = (unsigned)ceil_div(tiles, tiles_per_cta);
+      const size_t smem = (size_t)kUpdSlots * kUpdTileBytes;
+      cudaStream_t st = (cudaStream_t)stream;
+      int* status = device_status_ptr();
+      QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "sscan_update: device status word unavailable");
+      const bool tied = a->A_sn == 0;
+      const bool grp = a->grouped != 0;
+#define QB_UPD_LAUNCH(L)                                                                                           \
+  do {                                                                                                             \
+    if (tied && !grp) sscan_update_bulk_kernel<L, true, false><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);      \
+    else if (tied && grp) sscan_update_bulk_kernel<L, true, true><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);   \
+    else if (!grp) sscan_update_bulk_kernel<L, false, false><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);        \
+    else sscan_update_bulk_kernel<L, false, true><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);                   \
+  } while (0)
+      switch (lpr) {
+        case 1: QB_UPD_LAUNCH(1); break;
+        case 2: QB_UPD_LAUNCH(2); break;
+        case 4: QB_UPD_LAUNCH(4); break;
+        case 8: QB_UPD_LAUNCH(8); break;
+        default: QB_UPD_LAUNCH(16); break;
+      }
+#undef QB_UPD_LAUNCH
+      QB_LAUNCH_OK("sscan_update_bulk_kernel");
+      return QB_OK;
+    }
+  }
   // streaming kernel: 16-byte pieces of aligned state rows, every CTA inside one (batch, SSD group)
   if (a->dstate % 16 == 0 && a->dstate <= 256 && aligned(a->state, 16) && a->state_sp % 16 == 0 && a->state_sh % 16 == 0 &&
       a->state_sb % 16 == 0 && (!a->grouped || aligned(a->state_scale, 16))) {

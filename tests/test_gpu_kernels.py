@@ -358,3 +358,53 @@ def test_to_seqlen_last_operand_swap():
 def test_no_device_wait_timed_out():
     from quamba_b200 import _lib
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+
+
+# ---- state update: the three kernels behind qb_sscan_update (pipelined bulk-copy, streaming, generic) ----------------
+@pytest.mark.parametrize("Bsz,H,P,G,N,grouped,layout", [
+    (3, 8, 64, 1, 128, False, "contig"),     # pipelined: 8 KB tiles of 64 rows
+    (2, 8, 64, 2, 128, True, "contig"),      # pipelined, grouped scales
+    (2, 4, 64, 1, 256, False, "contig"),     # pipelined, 16 pieces per row
+    (5, 1, 1024, 1, 16, False, "contig"),    # pipelined, Mamba1 shape (one piece per row), A not tied
+    (2, 8, 64, 1, 128, False, "padded"),     # rows 16-byte aligned but not contiguous -> streaming kernel
+    (2, 1, 256, 1, 16, False, "contig"),     # too few rows per group for a tile -> streaming kernel
+    (2, 3, 24, 1, 40, False, "contig"),      # dstate not a multiple of 16 -> generic kernel
+])
+def test_update_kernel_variants_against_oracle(Bsz, H, P, G, N, grouped, layout):
+    gen = torch.Generator().manual_seed(Bsz * 1000 + N)
+    ri8 = lambda *s: torch.randint(-127, 128, s, generator=gen, dtype=torch.int32).to(torch.int8)
+    state = ri8(Bsz, H, P, N)
+    x, dt, Bm, Cm = ri8(Bsz, H, P), ri8(Bsz, H, P), ri8(Bsz, G, N), ri8(Bsz, G, N)
+    tied = H > 1
+    A = ri8(H)[:, None, None].expand(H, P, N) if tied else ri8(H, P, N)
+    Dq, bias = ri8(H, P), (torch.rand(H, P, generator=gen) * 2 - 4).half()
+    s_dt, s_A, s_D = torch.tensor(0.02), torch.tensor(0.015), torch.tensor(0.01)
+    if grouped:
+        HG, DG = 2, 4
+        hgr = torch.tensor([[H // G // 2, H // G]] * G, dtype=torch.int32)
+        dgr = torch.tensor([[[P // 4, P // 2, 3 * P // 4, P]] * HG] * G, dtype=torch.int32)
+        xs = torch.rand(G, HG, DG, generator=gen) * 0.02 + 0.01
+        ss = torch.rand(G, HG, DG, N, generator=gen) * 0.01 + 0.005
+        sB, sC = torch.rand(G, generator=gen) * 0.02 + 0.01, torch.rand(G, generator=gen) * 0.02 + 0.01
+        st_ref = state.clone()
+        y_ref, _ = oupd.quamba2_sscan_update(st_ref, x, xs, hgr, dgr, dt, s_dt, A, s_A, ss, Bm, sB, Cm, sC, Dq, s_D, None, None, bias, True)
+    else:
+        xs, ss, sB, sC = torch.tensor([0.02]), torch.tensor([0.01]), torch.tensor([0.015]), torch.tensor([0.017])
+        st_ref = state.clone()
+        y_ref, _ = oupd.quant_sscan_update(st_ref, x, xs, dt, s_dt, A, s_A, ss, Bm, sB, Cm, sC, Dq, s_D, None, None, bias, None, True)
+    if layout == "padded":
+        buf = torch.zeros(Bsz, H, P, N + 16, dtype=torch.int8, device=DEV)
+        st = buf[..., :N]
+        st.copy_(state)
+    else:
+        st = state.clone().to(DEV)
+    A_dev = dev(A.contiguous()) if not tied else dev(A[:, 0, 0].contiguous())[:, None, None].expand(H, P, N)
+    if grouped:
+        out = ops().quamba2_sscan_update_triton(st, dev(x), dev(xs), dev(hgr), dev(dgr), dev(dt), dev(s_dt), A_dev, dev(s_A), dev(ss),
+                                                dev(Bm), dev(sB), dev(Cm), dev(sC), dev(Dq), dev(s_D), None, None, dev(bias), True)
+    else:
+        out = ops().quant_sscan_update_triton(st, dev(x), dev(xs), dev(dt), dev(s_dt), A_dev, dev(s_A), dev(ss), dev(Bm), dev(sB),
+                                              dev(Cm), dev(sC), dev(Dq), dev(s_D), None, None, dev(bias), None, True)
+    assert_fp16(out, y_ref)
+    assert_lsb(st, st_ref, max_frac=0.02)
+    ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)      # raises if a device-side wait timed out
