@@ -381,12 +381,14 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
   constexpr float kLog2e = 1.4426950408889634f;
   constexpr int kDstate = 16 * LPR;
   constexpr int kTileRows = kUpdTileBytes / kDstate;
+  constexpr int kRowIters = (kTileRows + 255) / 256;  // rows a thread prepares per tile
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(16) float sB[256];   // B[n] * B_scale (/ state_scale when it is one number)
   __shared__ __align__(16) float sC[256];   // C[n] * C_scale (* state_scale when it is one number)
   __shared__ float sLut[256];               // -exp(A_scale * q) * log2(e), q = index - 128
-  __shared__ float rX[kTileRows], rDtx[kTileRows], rDt[kTileRows], rdA[kTileRows], rY[kTileRows];
-  __shared__ int rScaleOfs[kTileRows];      // grouped scales: offset of the row's [dstate] state-scale vector
+  // per-row scalars, double-buffered: tile k uses buffer k & 1 while buffer (k + 1) & 1 is filled for the next tile
+  __shared__ float rX[2][kTileRows], rDtx[2][kTileRows], rDt[2][kTileRows], rdA[2][kTileRows], rY[2][kTileRows];
+  __shared__ int rScaleOfs[2][kTileRows];   // grouped scales: offset of the row's [dstate] state-scale vector
   __shared__ __align__(8) uint64_t full[kUpdSlots];
   const int tid = threadIdx.x;
   const int t_begin = blockIdx.x * tiles_per_cta;
@@ -408,89 +410,117 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
     if (t_begin + 1 < t_end) issue_load(t_begin + 1);
   }
   const int hpg = a.nheads / a.ngroups;
-  constexpr bool tied = kTied;        // A_log has one value per row (stride 0 along dstate)
   const float ss0 = kGrouped ? 1.0f : a.state_scale[0];
+  const float dt_scale = *a.dt_scale;
+  const float bias_scale = (a.dt_bias != nullptr && !a.dt_bias_is_half) ? *a.dt_bias_scale : 0.0f;
   const int n0 = (tid % LPR) * 16;    // both pieces of a thread, in every tile, cover the same 16 states
   float bb[16], cc[16];               // this thread's slice of sB / sC, refreshed when (batch, group) changes
-  // (batch, head, row-in-head) of the tile's first row, advanced incrementally: no 64-bit division in the tile loop
-  int b, hd0, p0;
+
+  struct Coord { int b, hd0, p0; };   // (batch, head, row-in-head) of a tile's first row
+  auto advance = [&](Coord c) {       // the next tile's first row: no 64-bit division in the tile loop
+    c.p0 += kTileRows;
+    while (c.p0 >= a.headdim) { c.p0 -= a.headdim; ++c.hd0; }
+    while (c.hd0 >= a.nheads) { c.hd0 -= a.nheads; ++c.b; }
+    return c;
+  };
+  Coord cur;
   {
     const int64_t rows_per_b = (int64_t)a.nheads * a.headdim;
     const int64_t row0 = (int64_t)t_begin * kTileRows;
-    b = (int)(row0 / rows_per_b);
+    cur.b = (int)(row0 / rows_per_b);
     const int rem = (int)(row0 % rows_per_b);
-    hd0 = rem / a.headdim;
-    p0 = rem % a.headdim;
+    cur.hd0 = rem / a.headdim;
+    cur.p0 = rem % a.headdim;
   }
-  int cur_bg = -1;
-  int prev_b = 0, prev_hd0 = 0, prev_p0 = 0;
-  // y of the previous tile: D skip term, z gate, fp16 store, one thread per row
-  auto finish_rows = [&](int fb, int fhd0, int fp0) {
-    for (int r = tid; r < kTileRows; r += 256) {
-      const unsigned pr = (unsigned)(fp0 + r);
-      const int hd = fhd0 + (int)(pr / (unsigned)a.headdim);
-      const int p = (int)(pr % (unsigned)a.headdim);
-      float y = rY[r];
-      if (a.D != nullptr) y = fmaf(rX[r], (*a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp], y);
-      if (a.z != nullptr) {
-        const float z = (*a.z_scale) * (float)a.z[(int64_t)fb * a.z_sb + (int64_t)hd * a.z_sh + p];
-        y *= silu_exact(z);
+
+  // Raw inputs of the rows this thread prepares (global loads issued early, consumed after the tile's arithmetic).
+  struct RowRaw { int hd, p, xq, dtq, aq; float bias; };
+  auto rows_fetch = [&](const Coord& c, RowRaw (&raw)[kRowIters]) {
+#pragma unroll
+    for (int i = 0; i < kRowIters; ++i) {
+      const int r = tid + i * 256;
+      if (r < kTileRows) {
+        const unsigned pr = (unsigned)(c.p0 + r);
+        const int hd = c.hd0 + (int)(pr / (unsigned)a.headdim);
+        const int p = (int)(pr % (unsigned)a.headdim);
+        raw[i].hd = hd; raw[i].p = p;
+        raw[i].xq = a.x[(int64_t)c.b * a.x_sb + (int64_t)hd * a.x_sh + p];
+        raw[i].dtq = a.dt[(int64_t)c.b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp];
+        raw[i].aq = kTied ? (int)a.A_log[(int64_t)hd * a.A_sh + (int64_t)p * a.A_sp] : 0;
+        raw[i].bias = 0.0f;
+        if (a.dt_bias != nullptr) {
+          const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
+          raw[i].bias = a.dt_bias_is_half ? __half2float(static_cast<const __half*>(a.dt_bias)[bi])
+                                          : bias_scale * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
+        }
       }
-      static_cast<__half*>(a.out)[(int64_t)fb * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
     }
   };
-  bool ok = true;
+  auto rows_finish = [&](const Coord& c, const RowRaw (&raw)[kRowIters], int buf) {
+#pragma unroll
+    for (int i = 0; i < kRowIters; ++i) {
+      const int r = tid + i * 256;
+      if (r < kTileRows) {
+        float xs;
+        if (kGrouped) {
+          const int g = c.hd0 / hpg;
+          const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, raw[i].hd % hpg);
+          const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, raw[i].p);
+          const int cell = (g * a.nhead_groups + hg) * a.ndim_groups + dg;
+          xs = a.x_scales[cell];
+          rScaleOfs[buf][r] = cell * a.dstate;
+        } else {
+          xs = a.x_scales[0];
+        }
+        const float x = xs * (float)raw[i].xq;
+        float dt = fmaf(dt_scale, (float)raw[i].dtq, raw[i].bias);
+        if (a.dt_softplus) dt = softplus_f(dt);
+        rX[buf][r] = x;
+        rDt[buf][r] = dt;
+        rDtx[buf][r] = dt * x;
+        if (kTied) rdA[buf][r] = fast_exp2(sLut[raw[i].aq + 128] * dt);
+      }
+    }
+  };
+  // y of a finished tile: D skip term, z gate, fp16 store, one thread per row
+  auto rows_store = [&](const Coord& c, int buf) {
+    for (int r = tid; r < kTileRows; r += 256) {
+      const unsigned pr = (unsigned)(c.p0 + r);
+      const int hd = c.hd0 + (int)(pr / (unsigned)a.headdim);
+      const int p = (int)(pr % (unsigned)a.headdim);
+      float y = rY[buf][r];
+      if (a.D != nullptr) y = fmaf(rX[buf][r], (*a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp], y);
+      if (a.z != nullptr) {
+        const float z = (*a.z_scale) * (float)a.z[(int64_t)c.b * a.z_sb + (int64_t)hd * a.z_sh + p];
+        y *= silu_exact(z);
+      }
+      static_cast<__half*>(a.out)[(int64_t)c.b * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
+    }
+  };
+
+  RowRaw raw[kRowIters];
+  rows_fetch(cur, raw);
+  rows_finish(cur, raw, 0);
+  int cur_bg = -1;
   for (int t = t_begin; t < t_end; ++t) {
     const int k = t - t_begin;
     const int slot = k & (kUpdSlots - 1);
-    if (k > 0) {
-      finish_rows(prev_b, prev_hd0, prev_p0);
-      p0 += kTileRows;
-      while (p0 >= a.headdim) { p0 -= a.headdim; ++hd0; }
-      while (hd0 >= a.nheads) { hd0 -= a.nheads; ++b; }
-      __syncthreads();  // rX / rY of the previous tile are consumed before they are overwritten
-    }
-    prev_b = b; prev_hd0 = hd0; prev_p0 = p0;
-    const int g = hd0 / hpg;
-    const bool restage = b * a.ngroups + g != cur_bg;  // block-uniform: the tile enters a new (batch, group)
+    const int buf = k & 1;
+    const Coord nxt = advance(cur);
+    const bool has_next = t + 1 < t_end;
+    if (has_next) rows_fetch(nxt, raw);  // in flight during this tile's arithmetic
+    const int g = cur.hd0 / hpg;
+    const bool restage = cur.b * a.ngroups + g != cur_bg;  // block-uniform: the tile enters a new (batch, group)
     if (restage) {
-      cur_bg = b * a.ngroups + g;
+      cur_bg = cur.b * a.ngroups + g;
       if (tid < kDstate) {
         const float Bs = kGrouped ? a.B_scale[g] : a.B_scale[0];
         const float Cs = kGrouped ? a.C_scale[g] : a.C_scale[0];
-        sB[tid] = Bs * (float)a.Bm[(int64_t)b * a.B_sb + (int64_t)g * a.B_sg + tid] / ss0;
-        sC[tid] = Cs * (float)a.Cm[(int64_t)b * a.C_sb + (int64_t)g * a.C_sg + tid] * ss0;
+        sB[tid] = Bs * (float)a.Bm[(int64_t)cur.b * a.B_sb + (int64_t)g * a.B_sg + tid] / ss0;
+        sC[tid] = Cs * (float)a.Cm[(int64_t)cur.b * a.C_sb + (int64_t)g * a.C_sg + tid] * ss0;
       }
     }
-    // per-row scalars, one thread per row, while the tile is still in flight
-    for (int r = tid; r < kTileRows; r += 256) {
-      const unsigned pr = (unsigned)(p0 + r);
-      const int hd = hd0 + (int)(pr / (unsigned)a.headdim);
-      const int p = (int)(pr % (unsigned)a.headdim);
-      float xs;
-      if (kGrouped) {
-        const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, hd % hpg);
-        const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
-        const int cell = (g * a.nhead_groups + hg) * a.ndim_groups + dg;
-        xs = a.x_scales[cell];
-        rScaleOfs[r] = cell * a.dstate;
-      } else {
-        xs = a.x_scales[0];
-      }
-      const float x = xs * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
-      float dt = (*a.dt_scale) * (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp];
-      if (a.dt_bias != nullptr) {
-        const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
-        if (a.dt_bias_is_half) dt += __half2float(static_cast<const __half*>(a.dt_bias)[bi]);
-        else dt += (*a.dt_bias_scale) * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
-      }
-      if (a.dt_softplus) dt = softplus_f(dt);
-      rX[r] = x;
-      rDt[r] = dt;
-      rDtx[r] = dt * x;
-      if (tied) rdA[r] = fast_exp2(sLut[(int)a.A_log[(int64_t)hd * a.A_sh + (int64_t)p * a.A_sp] + 128] * dt);
-    }
-    __syncthreads();
+    __syncthreads();  // row scalars of this tile (written last iteration) and sB / sC are visible
     if (restage) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -500,25 +530,26 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
         cc[4 * i] = cf.x; cc[4 * i + 1] = cf.y; cc[4 * i + 2] = cf.z; cc[4 * i + 3] = cf.w;
       }
     }
-    if (!mbar_wait(&full[slot], (uint32_t)((k / kUpdSlots) & 1), status, kStatusUpdateLoad)) { ok = false; break; }
+    const bool ok = mbar_wait(&full[slot], (uint32_t)((k / kUpdSlots) & 1), status, kStatusUpdateLoad);
+    if (!ok) break;  // every thread waits on the same barrier, so all leave together
     uint8_t* tile = ring + slot * kUpdTileBytes;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int piece = tid + e * 256;
       const int r = piece / LPR;
       uint4* cell = reinterpret_cast<uint4*>(tile + piece * 16);
-      const uint4 raw = *cell;
-      const uint32_t w[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
-      const float dtx = rDtx[r];
-      const float dA_row = tied ? rdA[r] : 0.0f;
-      const float dt = tied ? 0.0f : rDt[r];
+      const uint4 rawst = *cell;
+      const uint32_t w[4] = {rawst.x ^ 0x80808080u, rawst.y ^ 0x80808080u, rawst.z ^ 0x80808080u, rawst.w ^ 0x80808080u};
+      const float dtx = rDtx[buf][r];
+      const float dA_row = kTied ? rdA[buf][r] : 0.0f;
+      const float dt = kTied ? 0.0f : rDt[buf][r];
       const int8_t* Aq = nullptr;
-      if (!tied) {
-        const unsigned pr = (unsigned)(p0 + r);
-        Aq = a.A_log + (int64_t)(hd0 + (int)(pr / (unsigned)a.headdim)) * a.A_sh + (int64_t)(pr % (unsigned)a.headdim) * a.A_sp +
-             (int64_t)n0 * a.A_sn;
+      if (!kTied) {
+        const unsigned pr = (unsigned)(cur.p0 + r);
+        Aq = a.A_log + (int64_t)(cur.hd0 + (int)(pr / (unsigned)a.headdim)) * a.A_sh +
+             (int64_t)(pr % (unsigned)a.headdim) * a.A_sp + (int64_t)n0 * a.A_sn;
       }
-      const float* ssn = kGrouped ? a.state_scale + rScaleOfs[r] + n0 : nullptr;
+      const float* ssn = kGrouped ? a.state_scale + rScaleOfs[buf][r] + n0 : nullptr;
       uint32_t ow[4];
       float y = 0.0f;
 #pragma unroll
@@ -538,7 +569,7 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
           // bytes [0, v + 128, 0, 0x47] read as a float = 32768 + (v + 128); v is the state in units of its scale
           const float sv = __uint_as_float(__byte_perm(w[k4], 0x47000000u, 0x7404 | (j << 4))) - 32896.0f;
           float dA = dA_row;
-          if (!tied) dA = fast_exp2(sLut[(int)Aq[(int64_t)(4 * k4 + j) * a.A_sn] + 128] * dt);
+          if (!kTied) dA = fast_exp2(sLut[(int)Aq[(int64_t)(4 * k4 + j) * a.A_sn] + 128] * dt);
           const float v = fmaf(bs[j], dtx, sv * dA);  // new state / state_scale
           q[j] = __float2int_rn(v);
           y = fmaf(v, cs[j], y);
@@ -548,8 +579,9 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
       *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
 #pragma unroll
       for (int m = 1; m < LPR; m <<= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
-      if (piece % LPR == 0) rY[r] = y;
+      if (piece % LPR == 0) rY[buf][r] = y;
     }
+    if (has_next) rows_finish(nxt, raw, buf ^ 1);
     fence_proxy_async_smem();  // the tile was rewritten through the generic proxy; the bulk store reads it through the async one
     __syncthreads();
     if (tid == 0) {
@@ -558,8 +590,9 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
       bulk_wait_read<1>();  // every store but the newest has finished reading its slot
       if (t + 2 < t_end) issue_load(t + 2);
     }
+    rows_store(cur, buf);  // buffer `buf` is next written two iterations from now, after two more barriers
+    cur = nxt;
   }
-  if (ok) finish_rows(prev_b, prev_hd0, prev_p0);
   if (tid == 0) bulk_wait_all<0>();
 }
 
@@ -630,7 +663,7 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
         a->state_sb == (int64_t)a->nheads * a->headdim * a->dstate && (!a->grouped || aligned(a->state_scale, 16)) &&
         rows_per_group % (kUpdTileBytes / a->dstate) == 0) {
       const int tiles = (int)(rows * a->dstate / kUpdTileBytes);
-      const int ctas = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * 4);
+      const int ctas = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * 3);
       const int tiles_per_cta = (int)ceil_div(tiles, ctas);
       const unsigned grid = (unsigned)ceil_div(tiles, tiles_per_cta);
       const size_t smem = (size_t)kUpdSlots * kUpdTileBytes;
@@ -641,6 +674,14 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
       const bool grp = a->grouped != 0;
 #define QB_UPD_LAUNCH(L)                                                                                           \
   do {                                                                                                             \
+    static bool attr_done = false; /* static + dynamic shared memory exceeds 48 KB for small dstate */            \
+    if (!attr_done) {                                                                                              \
+      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);   \
+      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);    \
+      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);  \
+      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);   \
+      attr_done = true;                                                                                            \
+    }                                                                                                              \
     if (tied && !grp) sscan_update_bulk_kernel<L, true, false><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);      \
     else if (tied && grp) sscan_update_bulk_kernel<L, true, true><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);   \
     else if (!grp) sscan_update_bulk_kernel<L, false, false><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);        \
