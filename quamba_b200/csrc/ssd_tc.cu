@@ -13,12 +13,24 @@
 // is <= 0.  Two small preparation kernels run first: one widens B and C (shared by all heads of a
 // group) to fp16 once -- values stay the raw integers, scales are applied in the epilogues -- the
 // other evaluates softplus / the running sums and leaves, per (batch, head, block), the vectors
-// a[128] and bk[128] = a - log2(dt) - log2(sC sB).  Every CTA TMA-loads 128-byte-swizzled B / C
-// tiles that serve as K-major operands (CB, D1) and as the MN-major A operand of S_loc without any
-// reshuffling, plus the 1 KB a/bk vector.  x is read straight from global memory by the thread that
-// converts it (int8 -> fp16 with integer/half ALU ops only).  Warp 0 issues TMA, warp 1 issues MMAs
-// and owns TMEM, warps 2..17 (four per TMEM lane quarter, one column quarter each) build the fp16
-// operands, keep the state, and write y.  All waits are bounded.
+// a[128], bk[128] = a - log2(dt) - log2(sC sB) and ec[128] (column factors of the off-diagonal
+// 32 x 32 chunks of Lm: there 2^(a_m - bk_k) = 2^(a_m - a_end(chunk)) * ec[k], two multiplies
+// instead of an ex2 per element; the diagonal chunks keep the exact per-element exponent).  When D
+// has one value per head it is added on the diagonal of Lm, so the output step needs no x.
+// Every CTA TMA-loads 128-byte-swizzled B / C tiles that serve as K-major operands (CB, D1) and as
+// the MN-major A operand of S_loc without any reshuffling, plus the 1.5 KB of vectors.  x is read
+// straight from global memory by the thread that converts it (int8 -> fp16 with integer / half
+// ALU ops only).
+//
+// 640 threads: warp 0 issues TMA, warp 1 issues the MMAs and owns TMEM; warps 4..11 (group A) turn
+// CB(j) into the Lm tile; warps 12..19 (group B) write the x operands of block k, then the output
+// of block k - 1 (accumulators -> registers -> 4 x 4 shuffle transpose -> 64-byte row pieces straight
+// to global memory), then fold S_loc(k) into the state they keep in registers.  TMEM (512 columns):
+// CB and D1 double-buffered, D2, S.  Every barrier is waited on by each of its consumers once per
+// phase and in order, no phase can complete twice before a consumer has looked at it, and all waits
+// are bounded.  Two lessons are built into the code: setmaxnreg.inc blocks without a time limit when
+// the pool is short (the 40 / 64 / 152 split leaves room for the allocation granularity), and the
+// B / C stage is handed back to the TMA producer only at the end of an iteration (see below).
 #include "tc_common.cuh"
 
 namespace qb {
@@ -28,6 +40,10 @@ __device__ long long g_trace[2][64][16];
 #define TRACE(role, j, slot) do { if (blockIdx.x == 0 && (j) < 64) g_trace[role][j][slot] = clock64(); } while (0)
 #else
 #define TRACE(role, j, slot) do { } while (0)
+#endif
+
+#ifdef QB_DUMP
+__device__ float* g_dump = nullptr;
 #endif
 
 namespace {
@@ -51,17 +67,26 @@ constexpr int kOffS16 = 12 * kAtom;            // 1 atom
 constexpr int kOffMisc = 13 * kAtom;           // vectors + barriers
 constexpr int kMiscBytes = 4096;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;
-constexpr int kAbBytes = 2 * T * 4;            // a[128] then bk[128], fp32
+constexpr int kAbVecs = 3;                     // a[128], bk[128], ec[128] per block, fp32
+constexpr int kAbBytes = kAbVecs * T * 4;
 
-constexpr uint32_t kColCB = 0, kColD1 = 128, kColD2 = 192, kColS = 256, kTmemCols = 512;
+// CB is double-buffered (block j in buffer j & 1) so that C.B^T of the next block is computed while the Lm tile of the
+// current one is still being built from the other buffer.
+// D1 (the carried-in term C S_prev) is double-buffered as well: GEMM2(j) only needs the state of block j - 1, so it is
+// issued while the x operands of block j are still being prepared and the tensor pipe would otherwise idle.
+constexpr uint32_t kColCB = 0, kColD1 = 128, kColD2 = 192, kColS = 256, kColCB1 = 320, kColD1b = 448, kTmemCols = 512;
 
 struct Misc {
-  float ab[2][2 * T];  // per stage: a (inclusive running sum of dt*A*log2e), then bk (+inf where dt == 0)
+  // per stage: a (inclusive running sum of dt*A*log2e), bk (+inf where dt == 0), ec (column factor of the off-diagonal
+  // 32 x 32 chunks of Lm, see ssd_dt_kernel).  Both compute groups release a
+  // stage right after their last read of it (group B copies what it needs into registers at the top of a block).
+  float ab[2][kAbVecs * T];
   float sx[P];         // x scale per channel
   float dsx[P];        // D * sx per channel
   float sbx[P];        // sB * sx per channel
+  float dfold;         // D of this head when it is one value per head (added on the diagonal of Lm), else 0
   uint64_t bc_full[2], bc_empty[2], ab_empty[2];
-  uint64_t cb_ready, s_ready, y_ready, xops_ready, lm_ready, s16_ready, y_free;
+  uint64_t cb_ready[2], s_ready, y_ready, d1_ready, xops_ready, lm_ready, s16_ready, y_free;  // cb_ready / s_ready: one per TMEM buffer
   uint32_t tmem_slot;
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc does not fit");
@@ -111,6 +136,27 @@ __device__ __forceinline__ uint4 ldg_nc_now(const void* p) {
 }
 __device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<const uint32_t*>(&v); }
 
+// 4 x 4 transpose of 16-byte pieces across the four lanes of a quad (lanes 4q .. 4q + 3): on entry lane i holds the
+// pieces c[0..3] of "its" row; on exit lane i holds piece i of the rows of lanes 4q + 0 .. 4q + 3, in c[0..3].
+__device__ __forceinline__ uint4 shfl_xor_u4(uint4 v, int m) {
+  v.x = __shfl_xor_sync(0xffffffffu, v.x, m); v.y = __shfl_xor_sync(0xffffffffu, v.y, m);
+  v.z = __shfl_xor_sync(0xffffffffu, v.z, m); v.w = __shfl_xor_sync(0xffffffffu, v.w, m);
+  return v;
+}
+__device__ __forceinline__ void quad_transpose(uint4 (&c)[4], int lane) {
+  const bool odd = (lane & 1) != 0, hi = (lane & 2) != 0;
+  {
+    const uint4 r0 = shfl_xor_u4(odd ? c[0] : c[1], 1);
+    const uint4 r1 = shfl_xor_u4(odd ? c[2] : c[3], 1);
+    if (odd) { c[0] = r0; c[2] = r1; } else { c[1] = r0; c[3] = r1; }
+  }
+  {
+    const uint4 r0 = shfl_xor_u4(hi ? c[0] : c[2], 2);
+    const uint4 r1 = shfl_xor_u4(hi ? c[1] : c[3], 2);
+    if (hi) { c[0] = r0; c[1] = r1; } else { c[2] = r0; c[3] = r1; }
+  }
+}
+
 // One K = 128 contraction as eight K = 16 instructions.
 //   K-major operand (two 64-element atoms along K):   address = base + (ks / 4) * 16 KB + (ks % 4) * 32
 //   MN-major operand (rows are K):                    address = base + ks * 16 rows * 128 B
@@ -142,7 +188,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 2); }
-    mbar_init(&ms.cb_ready, 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.y_ready, 1);
+    mbar_init(&ms.cb_ready[0], 1); mbar_init(&ms.cb_ready[1], 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.y_ready, 1); mbar_init(&ms.d1_ready, 1);
     mbar_init(&ms.xops_ready, 1); mbar_init(&ms.lm_ready, 1); mbar_init(&ms.s16_ready, 1); mbar_init(&ms.y_free, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_b16);
@@ -167,6 +213,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     ms.sx[p] = sx;
     ms.dsx[p] = dv * sx;
     ms.sbx[p] = sB * sx;
+    if (p == 0) ms.dfold = (a.D != nullptr && !a.D_has_hdim) ? (*a.D_scale) * (float)a.D[h] : 0.0f;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -177,7 +224,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const float* ab_src = ab_ws + ((int64_t)b * a.nheads + h) * nb * (2 * T);
+      const float* ab_src = ab_ws + ((int64_t)b * a.nheads + h) * nb * (kAbVecs * T);
       for (int j = 0; j < nb; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
@@ -186,7 +233,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes);
         uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
         uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
-        bulk_load(ms.ab[st], ab_src + (int64_t)j * (2 * T), kAbBytes, &ms.bc_full[st]);
+        bulk_load(ms.ab[st], ab_src + (int64_t)j * (kAbVecs * T), kAbBytes, &ms.bc_full[st]);
         tma_load_4d(dB, &tm_b16, &ms.bc_full[st], 0, g, j * T, b);
         tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, j * T, b);
         tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, j * T, b);
@@ -206,27 +253,36 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       if (ok) {
         tc_fence_after_sync();
         issue_gemm(tmem + kColCB, sC16, false, 16, sB16, false, id_cb);
-        umma_commit(&ms.cb_ready);
+        umma_commit(&ms.cb_ready[0]);
       }
       for (int j = 0; j < nb && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = j & 1;
         const uint32_t bB = sB16 + st * 2 * kAtom, bC = sC16 + st * 2 * kAtom;
         if (j > 0) {
-          ok = mbar_wait(&ms.s16_ready, (j - 1) & 1, status, QB_ERR_TIMEOUT) &&
-               mbar_wait(&ms.y_free, (j - 1) & 1, status, QB_ERR_TIMEOUT);
+          // GEMM2(j): D1[j & 1] = C(j) S_prev.  Needs the fp16 state of block j - 1; the buffer was last read by the
+          // output step of block j - 2, whose y_free this thread observed before GEMM3(j - 1).  s16_ready also says that
+          // the state update of block j - 1 has read the S accumulator, which GEMM4(j) overwrites below.
+          ok = mbar_wait(&ms.s16_ready, (j - 1) & 1, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
           TRACE(1, j, 0);
-          issue_gemm(tmem + kColD1, bC, false, 16, sS16, true, id_kn);
+          issue_gemm(tmem + (st ? kColD1b : kColD1), bC, false, 16, sS16, true, id_kn);
+          umma_commit(&ms.d1_ready);   // the state tile may be rewritten once this has fired
         }
+        // GEMM4(j): local state of the block, S = (x w)^T B
         ok = mbar_wait(&ms.xops_ready, ph, status, QB_ERR_TIMEOUT);
         if (!ok) break;
         tc_fence_after_sync();
         TRACE(1, j, 1);
         issue_gemm(tmem + kColS, bB, true, kAtom, sXw, true, id_mn);
         umma_commit(&ms.s_ready);
-        umma_commit(&ms.bc_empty[st]);
+        // GEMM3(j) overwrites D2: the output step of block j - 1 must have loaded it
+        if (j > 0) {
+          ok = mbar_wait(&ms.y_free, (j - 1) & 1, status, QB_ERR_TIMEOUT);
+          if (!ok) break;
+        }
+        // GEMM3(j): D2 = Lm X
         ok = mbar_wait(&ms.lm_ready, ph, status, QB_ERR_TIMEOUT);
         if (!ok) break;
         tc_fence_after_sync();
@@ -235,21 +291,27 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         umma_commit(&ms.y_ready);
         TRACE(1, j, 3);
         if (j + 1 < nb) {
+          // C.B^T of the next block into the other CB buffer (group A released it when it signalled lm_ready(j - 1)).
+          // Issued after GEMM3(j) on purpose: it then runs while group B prepares the x operands of block j + 1 and the
+          // tensor pipe would otherwise idle; ahead of GEMM3(j) it only delays the output of block j.
           const int sn = (j + 1) & 1;
           ok = mbar_wait(&ms.bc_full[sn], ((j + 1) >> 1) & 1, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_gemm(tmem + kColCB, sC16 + sn * 2 * kAtom, false, 16, sB16 + sn * 2 * kAtom, false, id_cb);
-          umma_commit(&ms.cb_ready);
+          issue_gemm(tmem + (sn ? kColCB1 : kColCB), sC16 + sn * 2 * kAtom, false, 16, sB16 + sn * 2 * kAtom, false, id_cb);
+          umma_commit(&ms.cb_ready[sn]);
         }
+        // Release the B/C stage of block j last.  Its readers were CB(j), GEMM4(j) and GEMM2(j); releasing it right
+        // after GEMM2(j) let the refill for block j + 2 run concurrently with GEMM3(j), and with that timing results
+        // were not reproducible from run to run.  The refill has a whole block of slack, so nothing is lost here.
+        umma_commit(&ms.bc_empty[st]);
       }
     }
   } else if (warp >= 4) {
     // ---------------- compute warps ----------------
     // Two groups of eight warps run concurrently on different parts of the pipeline:
     //   group A (warps 4..11)  builds Lm for block j as soon as CB(j) is ready and GEMM3(j-1) has released the tile;
-    //   group B (warps 12..19) converts x (block j), then folds S_loc into the state and publishes its fp16 copy,
-    //                          then writes y(j) -- so x(j+1) / state(j+1) work overlaps Lm(j+1).
+    //   group B (warps 12..19) per step k: x operands of block k, output of block k - 1, state of block k.
     // Inside a group a thread owns one row (TMEM lane) and one half of the columns.
     const int cw = warp - 4;
     const int grp = cw >> 3;           // 0 = A, 1 = B
@@ -278,18 +340,38 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       return r != 0;
     };
 
+    // Several mbarriers, one group barrier: the lead thread waits for each in turn.
+    auto gwait3 = [&](uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2) -> bool {
+      uint32_t ok = 1;
+      if (lead) {
+        ok = mbar_wait(b0, p0, status, QB_ERR_TIMEOUT) ? 1u : 0u;
+        if (ok && b1 != nullptr) ok = mbar_wait(b1, p1, status, QB_ERR_TIMEOUT) ? 1u : 0u;
+        if (ok && b2 != nullptr) ok = mbar_wait(b2, p2, status, QB_ERR_TIMEOUT) ? 1u : 0u;
+      }
+      uint32_t r;
+      if (grp == 0)
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                     : "=r"(r) : "r"(ok) : "memory");
+      else
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                     : "=r"(r) : "r"(ok) : "memory");
+      return r != 0;
+    };
+
     if (grp == 0) {
       reg_dec<kRegsA>();
-      // ================= group A: Lm ===================================================================
+      // ================= group A: Lm[t, s] = CB[t, s] 2^(a_t - bk_s) for s <= t (+ D on the diagonal) =================
+      const float dfold = ms.dfold;
       for (int j = 0; j < nb; ++j) {
         const int st = j & 1;
-        if (!gwait(&ms.bc_full[st], (j >> 1) & 1)) break;     // a / bk vectors of this block
-        if (!gwait(&ms.cb_ready, j & 1)) break;               // CB(j) in TMEM
-        if (j > 0 && !gwait(&ms.y_ready, (j - 1) & 1)) break; // GEMM3(j-1) no longer reads the Lm tile
+        // the vectors of this block have landed, CB(j) is in TMEM buffer j & 1, GEMM3(j-1) no longer reads the Lm tile
+        if (!gwait3(&ms.bc_full[st], (j >> 1) & 1, &ms.cb_ready[st], (j >> 1) & 1, j > 0 ? &ms.y_ready : nullptr, (j - 1) & 1))
+          break;
         tc_fence_after_sync();
         if (lead) TRACE(0, j, 3);
-        const float* bkv = ms.ab[st] + T;
-        const float a_row = ms.ab[st][row];
+        const float* av = ms.ab[st];
+        const float* bkv = av + T;
+        const float a_row = av[row];
 #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
           const int c = hsel + 2 * i;  // 32-column chunk of k
@@ -300,31 +382,53 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
               *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(0, 0, 0, 0);
           } else {
             uint32_t cb[32];
-            tmem_ld_32x32(tmem + tlane + kColCB + 32 * c, cb);
-            tmem_ld_wait();
-            const float4* bk4 = reinterpret_cast<const float4*>(bkv + 32 * c);
-            const bool diag = c == q;  // only the diagonal chunk needs the k <= m mask (k - 32c <= lane)
+            tmem_ld_32x32(tmem + tlane + ((j & 1) ? kColCB1 : kColCB) + 32 * c, cb);
+            if (c == q) {
+              // diagonal chunk: exact exponent per element, the k <= m mask (k - 32c <= lane), and the skip weight D
+              // on the diagonal itself (y = sx (Lm + D I) x) when D has one value per head
+              tmem_ld_wait();
+              const float4* bk4 = reinterpret_cast<const float4*>(bkv + 32 * c);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              uint32_t o[4];
+              for (int u = 0; u < 4; ++u) {
+                uint32_t o[4];
 #pragma unroll
-              for (int v = 0; v < 2; ++v) {
-                const float4 bb = bk4[2 * u + v];
-                const int t0 = 8 * u + 4 * v;
-                float e0 = __uint_as_float(cb[t0 + 0]) * fast_exp2(a_row - bb.x);
-                float e1 = __uint_as_float(cb[t0 + 1]) * fast_exp2(a_row - bb.y);
-                float e2 = __uint_as_float(cb[t0 + 2]) * fast_exp2(a_row - bb.z);
-                float e3 = __uint_as_float(cb[t0 + 3]) * fast_exp2(a_row - bb.w);
-                if (diag) {
-                  e0 = t0 + 0 <= lane ? e0 : 0.0f;
-                  e1 = t0 + 1 <= lane ? e1 : 0.0f;
-                  e2 = t0 + 2 <= lane ? e2 : 0.0f;
-                  e3 = t0 + 3 <= lane ? e3 : 0.0f;
+                for (int v = 0; v < 2; ++v) {
+                  const float4 bb = bk4[2 * u + v];
+                  const int t0 = 8 * u + 4 * v;
+                  float e0 = __uint_as_float(cb[t0 + 0]) * fast_exp2(a_row - bb.x);
+                  float e1 = __uint_as_float(cb[t0 + 1]) * fast_exp2(a_row - bb.y);
+                  float e2 = __uint_as_float(cb[t0 + 2]) * fast_exp2(a_row - bb.z);
+                  float e3 = __uint_as_float(cb[t0 + 3]) * fast_exp2(a_row - bb.w);
+                  e0 = t0 + 0 < lane ? e0 : (t0 + 0 == lane ? e0 + dfold : 0.0f);
+                  e1 = t0 + 1 < lane ? e1 : (t0 + 1 == lane ? e1 + dfold : 0.0f);
+                  e2 = t0 + 2 < lane ? e2 : (t0 + 2 == lane ? e2 + dfold : 0.0f);
+                  e3 = t0 + 3 < lane ? e3 : (t0 + 3 == lane ? e3 + dfold : 0.0f);
+                  o[2 * v] = pack_h2(e0, e1);
+                  o[2 * v + 1] = pack_h2(e2, e3);
                 }
-                o[2 * v] = pack_h2(e0, e1);
-                o[2 * v + 1] = pack_h2(e2, e3);
+                *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
               }
-              *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
+              // chunk below the diagonal: 2^(a_t - bk_s) = 2^(a_t - m) * ec[s], m = a at the end of chunk c
+              const float e_row = fast_exp2(a_row - av[32 * c + 31]);
+              tmem_ld_wait();
+              const float4* ec4 = reinterpret_cast<const float4*>(av + 2 * T + 32 * c);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                uint32_t o[4];
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                  const float4 ee = ec4[2 * u + v];
+                  const int t0 = 8 * u + 4 * v;
+                  const float e0 = __uint_as_float(cb[t0 + 0]) * (e_row * ee.x);
+                  const float e1 = __uint_as_float(cb[t0 + 1]) * (e_row * ee.y);
+                  const float e2 = __uint_as_float(cb[t0 + 2]) * (e_row * ee.z);
+                  const float e3 = __uint_as_float(cb[t0 + 3]) * (e_row * ee.w);
+                  o[2 * v] = pack_h2(e0, e1);
+                  o[2 * v + 1] = pack_h2(e2, e3);
+                }
+                *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
             }
           }
         }
@@ -335,9 +439,12 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       }
     } else {
       reg_inc<kRegsB>();
-      // ================= group B: x operands, state, output ==============================================
+      // ================= group B: x operands of block k, output of block k - 1, state of block k =================
       const float lscb = fast_log2(sC * sB);
+      const bool d_per_channel = a.D != nullptr && a.D_has_hdim;   // then the skip term is added here, from a re-read of x
       const int8_t* xrow_base = a.x + (int64_t)b * a.x_sb + (int64_t)h * a.x_sh + 32 * hsel;
+      __half* out_base = static_cast<__half*>(a.out) + ((int64_t)b * a.seqlen * a.nheads + h) * P + 32 * hsel + 8 * (lane & 3);
+      const int64_t out_pitch = (int64_t)a.nheads * P;
       float s_reg[32];
 #pragma unroll
       for (int t = 0; t < 32; ++t) s_reg[t] = 0.0f;
@@ -346,57 +453,134 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         const uint4* src = reinterpret_cast<const uint4*>(xrow_base + (int64_t)row * a.x_sl);
         xn0 = ldg_nc_now(src); xn1 = ldg_nc_now(src + 1);
       }
-      for (int j = 0; j < nb; ++j) {
-        const uint32_t ph = j & 1;
-        const int st = j & 1;
-        const int l = j * T + row;
-        const bool valid = l < a.seqlen;
-        const uint4 xq0 = xn0, xq1 = xn1;
-        if (l + T < a.seqlen) {
-          const uint4* src = reinterpret_cast<const uint4*>(xrow_base + (int64_t)(l + T) * a.x_sl);
-          xn0 = ldg_nc_now(src); xn1 = ldg_nc_now(src + 1);
-        } else {
-          xn0 = make_uint4(0, 0, 0, 0); xn1 = make_uint4(0, 0, 0, 0);
-        }
-        if (lead) TRACE(1, j, 4);
-        if (!gwait(&ms.bc_full[st], (j >> 1) & 1)) break;
-        if (lead) TRACE(1, j, 13);
-        const float a_row = ms.ab[st][row];
-        const float r_tot = ms.ab[st][T - 1];
-        // w_l = dt_l 2^(r - a_l) and dt_l = 2^(a_l - bk_l - lscb), hence w_l = 2^(r - bk_l - lscb) (0 where dt_l = 0)
-        const __half2 w2 = __float2half2_rn(fast_exp2(r_tot - ms.ab[st][T + row] - lscb));
-
-        // ---- x -> fp16 operands (raw, and scaled by w); the tiles are free: y_ready(j-1), s_ready(j-1) were awaited
-        {
-          const uint32_t xwd[8] = {xq0.x, xq0.y, xq0.z, xq0.w, xq1.x, xq1.y, xq1.z, xq1.w};
-          uint8_t* rowp_raw = smem + kOffXraw + row * 128;
-          uint8_t* rowp_w = smem + kOffXw + row * 128;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            __half2 r0, r1, r2, r3;
-            s8x4_to_h2x2(xwd[2 * c], r0, r1);
-            s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
-            const int chunk = ((4 * hsel + c) ^ sw) << 4;
-            *reinterpret_cast<uint4*>(rowp_raw + chunk) = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
-            *reinterpret_cast<uint4*>(rowp_w + chunk) =
-                make_uint4(h2_bits(__hmul2(r0, w2)), h2_bits(__hmul2(r1, w2)), h2_bits(__hmul2(r2, w2)), h2_bits(__hmul2(r3, w2)));
+      float e_prev = 0.0f;   // sC 2^(a_row) of the previous block: weight of its carried-in term
+      float r_tot = 0.0f;
+      for (int k = 0; k <= nb; ++k) {
+        const int st = k & 1;
+        if (k < nb) {
+          // ---- x(k) -> fp16 operands: raw, and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) (0 where dt_l = 0).
+          // The raw tile is free once GEMM3(k-1) is done (y_ready); the scaled tile was released by GEMM4(k-1),
+          // whose completion this group observed before its previous state update.
+          const int l = k * T + row;
+          const uint4 xq0 = xn0, xq1 = xn1;
+          if (l + T < a.seqlen) {  // the x rows of the next block: a whole block of work covers their latency
+            const uint4* src = reinterpret_cast<const uint4*>(xrow_base + (int64_t)(l + T) * a.x_sl);
+            xn0 = ldg_nc_now(src); xn1 = ldg_nc_now(src + 1);
+          } else {
+            xn0 = make_uint4(0, 0, 0, 0); xn1 = make_uint4(0, 0, 0, 0);
           }
+          if (lead) TRACE(1, k, 4);
+          // int8 -> fp16 happens before the wait: only the stores depend on the tiles being free
+          uint4 xr[4];
+          {
+            const uint32_t xwd[8] = {xq0.x, xq0.y, xq0.z, xq0.w, xq1.x, xq1.y, xq1.z, xq1.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              __half2 r0, r1, r2, r3;
+              s8x4_to_h2x2(xwd[2 * c], r0, r1);
+              s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
+              xr[c] = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
+            }
+          }
+          if (!gwait3(&ms.bc_full[st], (k >> 1) & 1, k > 0 ? &ms.y_ready : nullptr, (k - 1) & 1, nullptr, 0)) break;
+          if (lead) TRACE(1, k, 13);
+          const float* av = ms.ab[st];
+          const float a_row = av[row];
+          r_tot = av[T - 1];
+          const __half2 w2 = __float2half2_rn(fast_exp2(r_tot - av[T + row] - lscb));
+          const float e_now = k > 0 ? sC * fast_exp2(a_row) : 0.0f;
+          {
+            uint8_t* rowp_raw = smem + kOffXraw + row * 128;
+            uint8_t* rowp_w = smem + kOffXw + row * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int chunk = ((4 * hsel + c) ^ sw) << 4;
+              const uint4 v = xr[c];
+              *reinterpret_cast<uint4*>(rowp_raw + chunk) = v;
+              *reinterpret_cast<uint4*>(rowp_w + chunk) =
+                  make_uint4(h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.x), w2)),
+                             h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.y), w2)),
+                             h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.z), w2)),
+                             h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.w), w2)));
+            }
+          }
+          fence_proxy_async_smem();
+          gsync();
+          if (lead) { mbar_arrive(&ms.xops_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(1, k, 5); }
+          // swap: e_prev must describe block k - 1 in the output step below, block k afterwards
+          const float t = e_prev; e_prev = e_now;
+          if (k > 0) {
+            // ---- output of block k - 1 (weight t) ----
+#define QB_SSD_OUTPUT_STEP(EW)                                                                                               \
+            {                                                                                                                \
+              const int jj = k - 1;                                                                                          \
+              tc_fence_after_sync();                                                                                         \
+              uint32_t d2[32], d1[32];                                                                                       \
+              tmem_ld_32x32(tmem + tlane + kColD2 + 32 * hsel, d2);                                                          \
+              if (jj > 0) tmem_ld_32x32(tmem + tlane + ((jj & 1) ? kColD1b : kColD1) + 32 * hsel, d1);                       \
+              tmem_ld_wait();                                                                                                \
+              tc_fence_before_sync();                                                                                        \
+              gsync();                                                                                                       \
+              if (lead) { mbar_arrive(&ms.y_free); TRACE(1, jj, 9); } /* both accumulators are in registers */               \
+              const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 32 * hsel);                                        \
+              uint4 c4[4];                                                                                                   \
+              _Pragma("unroll") for (int t8 = 0; t8 < 4; ++t8) {                                                             \
+                uint32_t o[4];                                                                                               \
+                _Pragma("unroll") for (int v = 0; v < 2; ++v) {                                                              \
+                  const int t4 = 2 * t8 + v;                                                                                 \
+                  const float4 sx = sx4[t4];                                                                                 \
+                  float y0 = sx.x * __uint_as_float(d2[4 * t4 + 0]);                                                         \
+                  float y1 = sx.y * __uint_as_float(d2[4 * t4 + 1]);                                                         \
+                  float y2 = sx.z * __uint_as_float(d2[4 * t4 + 2]);                                                         \
+                  float y3 = sx.w * __uint_as_float(d2[4 * t4 + 3]);                                                         \
+                  if (jj > 0) {                                                                                              \
+                    y0 = fmaf(EW, __uint_as_float(d1[4 * t4 + 0]), y0);                                                      \
+                    y1 = fmaf(EW, __uint_as_float(d1[4 * t4 + 1]), y1);                                                      \
+                    y2 = fmaf(EW, __uint_as_float(d1[4 * t4 + 2]), y2);                                                      \
+                    y3 = fmaf(EW, __uint_as_float(d1[4 * t4 + 3]), y3);                                                      \
+                  }                                                                                                          \
+                  if (d_per_channel) {                                                                                       \
+                    const int lr = jj * T + row;                                                                             \
+                    uint32_t xw = 0;                                                                                         \
+                    if (lr < a.seqlen) xw = __ldg(reinterpret_cast<const uint32_t*>(xrow_base + (int64_t)lr * a.x_sl) + t4); \
+                    const float4 dx = reinterpret_cast<const float4*>(ms.dsx + 32 * hsel)[t4];                               \
+                    __half2 h01, h23;                                                                                        \
+                    s8x4_to_h2x2(xw, h01, h23);                                                                              \
+                    const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);                                       \
+                    y0 = fmaf(dx.x, x01.x, y0); y1 = fmaf(dx.y, x01.y, y1);                                                  \
+                    y2 = fmaf(dx.z, x23.x, y2); y3 = fmaf(dx.w, x23.y, y3);                                                  \
+                  }                                                                                                          \
+                  o[2 * v] = pack_h2(y0, y1);                                                                                \
+                  o[2 * v + 1] = pack_h2(y2, y3);                                                                            \
+                }                                                                                                            \
+                c4[t8] = make_uint4(o[0], o[1], o[2], o[3]);                                                                 \
+              }                                                                                                              \
+              /* 4 x 4 transpose of 16-byte pieces inside each quad of lanes: afterwards lane i of a quad holds piece i of  \
+                 the quad's four rows, so one store instruction writes 64 contiguous bytes per row */                        \
+              quad_transpose(c4, lane);                                                                                      \
+              const int r0 = jj * T + (row & ~3);                                                                            \
+              _Pragma("unroll") for (int m = 0; m < 4; ++m)                                                                  \
+                if (r0 + m < a.seqlen) *reinterpret_cast<uint4*>(out_base + (int64_t)(r0 + m) * out_pitch) = c4[m];          \
+            }
+            QB_SSD_OUTPUT_STEP(t)
+          }
+        } else {
+          if (!gwait(&ms.y_ready, (nb - 1) & 1)) break;
+          QB_SSD_OUTPUT_STEP(e_prev)
+          break;
         }
-        if (lead) TRACE(1, j, 14);
-        fence_proxy_async_smem();
-        gsync();
-        if (lead) { mbar_arrive(&ms.xops_ready); TRACE(1, j, 5); }
+#undef QB_SSD_OUTPUT_STEP
 
         // ---- state: s <- 2^r s + sB sx S_loc ; publish its fp16 copy for the next block -----------
-        if (!gwait(&ms.s_ready, ph)) break;
+        // GEMM4(k) done; GEMM2(k) done, so the fp16 state tile it read may be rewritten
+        if (!gwait3(&ms.s_ready, k & 1, k > 0 ? &ms.d1_ready : nullptr, (k - 1) & 1, nullptr, 0)) break;
         tc_fence_after_sync();
-        if (lead) TRACE(1, j, 6);
+        if (lead) TRACE(1, k, 6);
         {
           const float dec = fast_exp2(r_tot);
           uint32_t sl[32];
           tmem_ld_32x32(tmem + tlane + kColS + 32 * hsel, sl);
           tmem_ld_wait();
-          if (lead) TRACE(1, j, 10);
           const float4* sb4 = reinterpret_cast<const float4*>(ms.sbx + 32 * hsel);
 #pragma unroll
           for (int t4 = 0; t4 < 8; ++t4) {
@@ -406,7 +590,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
             s_reg[4 * t4 + 2] = fmaf(dec, s_reg[4 * t4 + 2], sc.z * __uint_as_float(sl[4 * t4 + 2]));
             s_reg[4 * t4 + 3] = fmaf(dec, s_reg[4 * t4 + 3], sc.w * __uint_as_float(sl[4 * t4 + 3]));
           }
-          if (j + 1 < nb) {
+          if (k + 1 < nb) {
             uint8_t* dst = smem + kOffS16 + row * 128;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -416,76 +600,14 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
             }
           }
         }
-        if (lead) TRACE(1, j, 11);
         tc_fence_before_sync();
         fence_proxy_async_smem();
-        if (lead) TRACE(1, j, 12);
         gsync();
-        if (lead && j + 1 < nb) mbar_arrive(&ms.s16_ready);
-        if (lead) TRACE(1, j, 7);
-
-        // ---- output ------------------------------------------------------------------------------------
-        if (!gwait(&ms.y_ready, ph)) break;
-        tc_fence_after_sync();
-        if (lead) TRACE(1, j, 8);
-        {
-          const float e_row = j > 0 ? sC * fast_exp2(a_row) : 0.0f;
-          const uint32_t xwd[8] = {xq0.x, xq0.y, xq0.z, xq0.w, xq1.x, xq1.y, xq1.z, xq1.w};
-          uint32_t d2[32], d1[32];
-          tmem_ld_32x32(tmem + tlane + kColD2 + 32 * hsel, d2);
-          if (j > 0) tmem_ld_32x32(tmem + tlane + kColD1 + 32 * hsel, d1);
-          tmem_ld_wait();
-          const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 32 * hsel);
-          const float4* dx4 = reinterpret_cast<const float4*>(ms.dsx + 32 * hsel);
-          // Stage the y tile in shared memory (the x*w operand tile is idle: GEMM4(j) has completed), then
-          // write it out so that every warp store covers four complete 128-byte rows of y.
-          uint8_t* stage_row = smem + kOffXw + row * 128;
-#pragma unroll
-          for (int t8 = 0; t8 < 4; ++t8) {
-            uint32_t o[4];
-#pragma unroll
-            for (int v = 0; v < 2; ++v) {
-              const int t4 = 2 * t8 + v;
-              const float4 sx = sx4[t4], dx = dx4[t4];
-              __half2 h01, h23;
-              s8x4_to_h2x2(xwd[t4], h01, h23);
-              const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);
-              float y0 = fmaf(sx.x, __uint_as_float(d2[4 * t4 + 0]), dx.x * x01.x);
-              float y1 = fmaf(sx.y, __uint_as_float(d2[4 * t4 + 1]), dx.y * x01.y);
-              float y2 = fmaf(sx.z, __uint_as_float(d2[4 * t4 + 2]), dx.z * x23.x);
-              float y3 = fmaf(sx.w, __uint_as_float(d2[4 * t4 + 3]), dx.w * x23.y);
-              if (j > 0) {
-                y0 = fmaf(e_row, __uint_as_float(d1[4 * t4 + 0]), y0);
-                y1 = fmaf(e_row, __uint_as_float(d1[4 * t4 + 1]), y1);
-                y2 = fmaf(e_row, __uint_as_float(d1[4 * t4 + 2]), y2);
-                y3 = fmaf(e_row, __uint_as_float(d1[4 * t4 + 3]), y3);
-              }
-              o[2 * v] = pack_h2(y0, y1);
-              o[2 * v + 1] = pack_h2(y2, y3);
-            }
-            *reinterpret_cast<uint4*>(stage_row + (((4 * hsel + t8) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        }
-        tc_fence_before_sync();
-        gsync();
-        {
-          const int gt = threadIdx.x - (kLead + 256);   // 0..255 inside group B
-          __half* out_blk = static_cast<__half*>(a.out) + ((int64_t)b * a.seqlen * a.nheads + h) * P;
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int item = it * 256 + gt;
-            const int r = item >> 3, ch = item & 7;
-            const int lr = j * T + r;
-            const uint4 v = *reinterpret_cast<const uint4*>(smem + kOffXw + r * 128 + ((ch ^ (r & 7)) << 4));
-            if (lr < a.seqlen) *(reinterpret_cast<uint4*>(out_blk + (int64_t)lr * a.nheads * P) + ch) = v;
-          }
-        }
-        tc_fence_before_sync();
-        gsync();
-        if (lead) { mbar_arrive(&ms.y_free); mbar_arrive(&ms.ab_empty[st]); TRACE(1, j, 9); }
+        if (lead && k + 1 < nb) mbar_arrive(&ms.s16_ready);   // also: the S accumulator has been read
+        if (lead) TRACE(1, k, 7);
 
         // ---- final state -> int8 after the last block -----------------------------------------------------
-        if (j + 1 == nb) {
+        if (k + 1 == nb) {
           int hg = 0;
           if (a.grouped) hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
           int8_t* fs = a.final_states + ((int64_t)b * a.nheads + h) * P * N + row;
@@ -580,7 +702,7 @@ __global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb) 
     if (lane >= o) incl += u;
   }
   const float pre = incl - run;
-  float* dst = ab_ws + unit * (2 * T);
+  float* dst = ab_ws + unit * (kAbVecs * T);
   float4 av, bv;
   float* ap = reinterpret_cast<float*>(&av);
   float* bp = reinterpret_cast<float*>(&bv);
@@ -589,8 +711,16 @@ __global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb) 
     ap[i] = pre + cs[i];
     bp[i] = dt[i] > 0.0f ? ap[i] - fast_log2(dt[i]) - lscb : __int_as_float(0x7f800000);
   }
+  // ec[s] = 2^(m - bk[s]) with m = a at the end of the 32-token chunk of s (<= a[s], so the exponent is <= log2 of
+  // dt sC sB: no overflow).  For a row t of a LATER chunk, Lm[t, s] = CB[t, s] 2^(a[t] - m) ec[s], both factors <= 1.
+  const float m = __shfl_sync(0xffffffffu, ap[3], (lane & ~7) | 7);
+  float4 ev;
+  float* ep = reinterpret_cast<float*>(&ev);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) ep[i] = fast_exp2(m - bp[i]);
   reinterpret_cast<float4*>(dst)[lane] = av;
   reinterpret_cast<float4*>(dst + T)[lane] = bv;
+  reinterpret_cast<float4*>(dst + 2 * T)[lane] = ev;
 }
 
 int64_t align256l(int64_t v) { return (v + 255) & ~(int64_t)255; }
@@ -609,7 +739,7 @@ bool ssd_tc_eligible(const qb_ssd_args* a) {
 
 int64_t ssd_tc_workspace_bytes(int B, int L, int H, int G) {
   const int64_t nb = (L + T - 1) / T;
-  return 2 * align256l((int64_t)B * L * G * N * 2) + align256l((int64_t)B * H * nb * 2 * T * 4);
+  return 2 * align256l((int64_t)B * L * G * N * 2) + align256l((int64_t)B * H * nb * kAbVecs * T * 4);
 }
 
 int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
@@ -652,6 +782,11 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
 
 }  // namespace qb
 
+#ifdef QB_DUMP
+extern "C" int qb_debug_set_dump(float* p) {  // development builds only
+  return cudaMemcpyToSymbol(qb::g_dump, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
+}
+#endif
 #ifdef QB_TRACE
 extern "C" int qb_debug_read_trace(long long* out) {  // 2 x 64 x 16 clock64 stamps of CTA 0 (development builds only)
   return cudaMemcpyFromSymbol(out, qb::g_trace, sizeof(qb::g_trace)) == cudaSuccess ? 0 : -1;
