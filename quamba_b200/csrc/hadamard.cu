@@ -6,6 +6,7 @@
 // memory, the special 12/20/28/40 part is a dense +-1 product whose signs sit in constant
 // memory (so each term is one FFMA with a constant-bank operand), and the result leaves as
 // 16-byte int8 stores.  Global traffic is exactly one read and one write of the row.
+#include <cstdlib>
 #include "common.cuh"
 #include "hadamard_tables.inc"
 
@@ -181,6 +182,8 @@ int dispatch_special(const qb_hadamard_quant_args* a, int log_p2, int vec_ok, cu
 
 using namespace qb;
 
+namespace qb { int hadamard_tc_launch(const qb_hadamard_quant_args* a, cudaStream_t st); }
+
 extern "C" int qb_hadamard_quant(const qb_hadamard_quant_args* a, void* stream) {
   QB_REQUIRE(a != nullptr && a->x && a->out, QB_ERR_INVALID_ARG, "hadamard_quant: null pointer");
   QB_REQUIRE(a->rows >= 0 && a->dim > 0, QB_ERR_INVALID_ARG, "hadamard_quant: bad shape");
@@ -197,11 +200,18 @@ extern "C" int qb_hadamard_quant(const qb_hadamard_quant_args* a, void* stream) 
   const int esz = a->in_dtype == 2 ? 4 : 2;
   const int vec_ok = (a->dim % 16 == 0) && aligned(a->x, 16) && aligned(a->out, 16) &&
                      ((a->x_row_stride * esz) % 16 == 0) && (a->out_row_stride % 16 == 0);
+  cudaStream_t st = (cudaStream_t)stream;
+  {  // tensor-core path (fp16 rows of S * 128 elements, contiguous); the kernels below are the general fallback
+    static const bool force_simt = getenv("QB_HADAMARD_SIMT") != nullptr;
+    if (!force_simt && aligned(a->out, 1)) {
+      const int rc = hadamard_tc_launch(a, st);
+      if (rc != QB_ERR_UNSUPPORTED) return rc;
+    }
+  }
   if (a->special > 1) {
     int rc = upload_tables();
     if (rc != QB_OK) return rc;
   }
-  cudaStream_t st = (cudaStream_t)stream;
   switch (a->in_dtype) {
     case 0: return dispatch_special<__half>(a, log_p2, vec_ok, st);
     case 1: return dispatch_special<__nv_bfloat16>(a, log_p2, vec_ok, st);

@@ -15,14 +15,15 @@
 namespace qb {
 namespace {
 
-constexpr int kRows = 64;    // (b, d) rows per CTA == threads per CTA
+// (b, d) rows per CTA == threads per CTA: 128 while the fp32 B / C tiles are small, 64 for the wide states
+constexpr int rows_per_cta(int dstate) { return dstate <= 16 ? 64 : 64; }
 constexpr int kTile = 64;    // time steps per shared-memory tile
 constexpr int kRowPad = 68;  // bytes per staged int8 row: 17 words, conflict-free column reads
 constexpr int kChunk = 2048; // the reference stores the state after every 2048 steps
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int N>
+template <int N, int kRows>
 __global__ void __launch_bounds__(kRows)
 sscan_fwd_kernel(qb_sscan_fwd_args a, int has_z, int vec_ok) {
   __shared__ __align__(16) int8_t s_u[kRows * kRowPad];
@@ -62,7 +63,7 @@ sscan_fwd_kernel(qb_sscan_fwd_args a, int has_z, int vec_ok) {
 
   // stage one 16-byte piece (or its in-range bytes) of a row into a padded shared row
   auto stage = [&](const int8_t* base, int64_t row_stride, int8_t* dst, int l0) {
-    // kRows rows x 4 pieces; 64 threads -> 4 iterations
+    // kRows rows x 4 pieces of 16 steps; one thread per row -> 4 iterations
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
       const int item = it * kRows + tid;
@@ -118,11 +119,12 @@ sscan_fwd_kernel(qb_sscan_fwd_args a, int has_z, int vec_ok) {
       for (int k = 0; k < 4; ++k) {
         const int t = t4 + k;
         if (t < steps) {
-          const float u = s_u_ * (float)(int8_t)((wu >> (8 * k)) & 0xff);
-          float delta = fmaf(s_d_, (float)(int8_t)((wd >> (8 * k)) & 0xff), bias);
-          if (a.delta_softplus) delta = softplus_f(delta);
+          // int8 -> float without a conversion instruction: the biased byte spliced into the mantissa of 2^15
+          const float u = s_u_ * (__uint_as_float(__byte_perm(wu ^ 0x80808080u, 0x47000000u, 0x7404 | (k << 4))) - 32896.0f);
+          float delta = fmaf(s_d_, __uint_as_float(__byte_perm(wd ^ 0x80808080u, 0x47000000u, 0x7404 | (k << 4))) - 32896.0f, bias);
+          if (a.delta_softplus) delta = softplus_fast(delta);
           const float du = delta * u;
-          float y = Dv * u;
+          float y4[4] = {Dv * u, 0.0f, 0.0f, 0.0f};  // four partial sums: the y chain is not one serial dependency
           const float4* Bt = reinterpret_cast<const float4*>(s_B + t * N);
           const float4* Ct = reinterpret_cast<const float4*>(s_C + t * N);
 #pragma unroll
@@ -134,12 +136,13 @@ sscan_fwd_kernel(qb_sscan_fwd_args a, int has_z, int vec_ok) {
             for (int j = 0; j < 4; ++j) {
               const int n = n4 * 4 + j;
               h[n] = fmaf(fast_exp2(delta * A2[n]), h[n], bb[j] * du);
-              y = fmaf(h[n], cc[j], y);
+              y4[j] = fmaf(h[n], cc[j], y4[j]);
             }
           }
+          float y = (y4[0] + y4[1]) + (y4[2] + y4[3]);
           if (has_z) {
-            const float z = s_z_ * (float)(int8_t)((wz >> (8 * k)) & 0xff);
-            y = y * silu_exact(z);
+            const float z = s_z_ * (__uint_as_float(__byte_perm(wz ^ 0x80808080u, 0x47000000u, 0x7404 | (k << 4))) - 32896.0f);
+            y = y * silu_mufu(z);
           }
           const int l = l0 + t;
           if (row_ok) out[(int64_t)l * a.dim] = __float2half_rn(y);
@@ -614,6 +617,7 @@ extern "C" int qb_sscan_fwd(const qb_sscan_fwd_args* a, void* stream) {
   QB_REQUIRE(a->batch > 0 && a->dim > 0 && a->seqlen > 0 && a->n_groups > 0, QB_ERR_INVALID_ARG, "sscan_fwd: empty shape");
   QB_REQUIRE(a->dstate <= 256, QB_ERR_INVALID_ARG, "quant_sscan only supports state dimension <= 256");
   QB_REQUIRE(a->dim % a->n_groups == 0, QB_ERR_INVALID_ARG, "sscan_fwd: dim not divisible by n_groups");
+  const int kRows = rows_per_cta(a->dstate);
   QB_REQUIRE(a->n_groups == 1 || (a->dim / a->n_groups) % kRows == 0, QB_ERR_UNSUPPORTED,
              "sscan_fwd: channels per group must be a multiple of %d", kRows);
   const int vec_ok = aligned(a->u, 16) && aligned(a->delta, 16) && (a->z == nullptr || aligned(a->z, 16)) &&
@@ -626,10 +630,10 @@ extern "C" int qb_sscan_fwd(const qb_sscan_fwd_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const int has_z = a->z != nullptr;
   switch (a->dstate) {
-    case 8: sscan_fwd_kernel<8><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
-    case 16: sscan_fwd_kernel<16><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
-    case 32: sscan_fwd_kernel<32><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
-    case 64: sscan_fwd_kernel<64><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 8: sscan_fwd_kernel<8, rows_per_cta(8)><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 16: sscan_fwd_kernel<16, rows_per_cta(16)><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 32: sscan_fwd_kernel<32, rows_per_cta(32)><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
+    case 64: sscan_fwd_kernel<64, rows_per_cta(64)><<<grid, kRows, 0, st>>>(*a, has_z, vec_ok); break;
     default:
       set_error("sscan_fwd: dstate %d not built (8, 16, 32, 64 are)", a->dstate);
       return QB_ERR_UNSUPPORTED;

@@ -131,6 +131,21 @@ def test_hadamard_quant(rows, dim, special, dtype):
     assert_lsb(got, want)
 
 
+@pytest.mark.parametrize("rows,dim,special", [(19, 5120, 40), (9, 1536, 12), (6, 2560, 20), (5, 3584, 28), (11, 256, 1), (3, 512, 1),
+                                              (17, 2048, 1), (5, 4096, 1), (300, 5120, 40)])
+def test_hadamard_tensor_core_path(rows, dim, special, monkeypatch):
+    """fp16 rows of S * 128 elements take the tcgen05 path (odd row counts exercise the ragged last unit); the result must
+    match the oracle and the SIMT kernel, which the environment switch selects."""
+    x = (torch.randn(rows, dim, generator=torch.Generator().manual_seed(rows + dim)) * 3).to(torch.float16)
+    scale = (1.0 / dim ** 0.5) / 0.05
+    want, _ = ohad.quant_hadamard(x.float(), scale, special)
+    fn = {1: "fast_hadamard_transform", 12: "fast_hadamard_transform_12N", 20: "fast_hadamard_transform_20N",
+          28: "fast_hadamard_transform_28N", 40: "fast_hadamard_transform_40N"}[special]
+    got = getattr(ops().quant_hadamard, fn)(x.to(DEV), scale)
+    assert_lsb(got, want, max_frac=0.002)
+    ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+
+
 def test_hadamard_saturates():
     x = torch.full((1, 128), 50.0, dtype=torch.float16)
     got = ops().quant_hadamard.fast_hadamard_transform(x.to(DEV), 1.0).cpu()
