@@ -11,6 +11,8 @@
 // and masked in the epilogue, so M, N and K need no padding (K and the row pitches only have to be
 // multiples of 16 bytes, the TMA rule).  Every wait is bounded; on expiry the kernel records
 // QB_ERR_TIMEOUT in the device status word, frees its TMEM and returns.
+#include <algorithm>
+#include <cstdlib>
 #include "tc_common.cuh"
 #include "linear_epilogue.cuh"
 
@@ -26,6 +28,50 @@ constexpr int kSmemBytes = kStages * 2 * kTileBytes + 1024 /*alignment slack*/ +
 constexpr uint32_t kTmemCols = 128;
 
 using namespace tc;
+
+// 32 consecutive accumulator columns of one output row -> scaled, converted, stored (16-byte stores when the layout allows).
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int m, int nb, int M, int N, const Epilogue& ep) {
+  if (nb >= N) return;  // whole warp agrees
+  if (ep.transpose) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (m < M && nb + j < N) ep.store((int)r[j], m, nb + j);
+  } else if (m < M) {
+    const bool full = nb + 32 <= N;
+    if (ep.out_kind == kOutF16 && full && (ep.out_stride % 8 == 0) &&
+        ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) && (nb % 8 == 0)) {
+      __half* dst = static_cast<__half*>(ep.out) + (int64_t)m * ep.out_stride + nb;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        __align__(16) __half2 h[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          h[t] = __floats2half2_rn(ep.scaled((int)r[j + 2 * t], m, nb + j + 2 * t),
+                                   ep.scaled((int)r[j + 2 * t + 1], m, nb + j + 2 * t + 1));
+        *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(h);
+      }
+    } else if ((ep.out_kind == kOutS8Rne || ep.out_kind == kOutS8Away) && full && (ep.out_stride % 16 == 0) &&
+               ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) && (nb % 16 == 0)) {
+      int8_t* dst = static_cast<int8_t*>(ep.out) + (int64_t)m * ep.out_stride + nb;
+#pragma unroll
+      for (int j = 0; j < 32; j += 16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int b = j + 4 * t;
+          w[t] = pack4_s8(ep.to_s8(ep.scaled((int)r[b], m, nb + b)), ep.to_s8(ep.scaled((int)r[b + 1], m, nb + b + 1)),
+                          ep.to_s8(ep.scaled((int)r[b + 2], m, nb + b + 2)),
+                          ep.to_s8(ep.scaled((int)r[b + 3], m, nb + b + 3)));
+        }
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < N) ep.store((int)r[j], m, nb + j);
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kThreads)
 gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
@@ -106,47 +152,7 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
         tmem_ld_wait();
-        const int nb = n0 + c;
-        if (nb >= N) continue;  // whole warp agrees
-        if (ep.transpose) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (m < M && nb + j < N) ep.store((int)r[j], m, nb + j);
-        } else if (m < M) {
-          const bool full = nb + 32 <= N;
-          if (ep.out_kind == kOutF16 && full && (ep.out_stride % 8 == 0) &&
-              ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) && (nb % 8 == 0)) {
-            __half* dst = static_cast<__half*>(ep.out) + (int64_t)m * ep.out_stride + nb;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              __align__(16) __half2 h[4];
-#pragma unroll
-              for (int t = 0; t < 4; ++t)
-                h[t] = __floats2half2_rn(ep.scaled((int)r[j + 2 * t], m, nb + j + 2 * t),
-                                         ep.scaled((int)r[j + 2 * t + 1], m, nb + j + 2 * t + 1));
-              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(h);
-            }
-          } else if ((ep.out_kind == kOutS8Rne || ep.out_kind == kOutS8Away) && full && (ep.out_stride % 16 == 0) &&
-                     ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) && (nb % 16 == 0)) {
-            int8_t* dst = static_cast<int8_t*>(ep.out) + (int64_t)m * ep.out_stride + nb;
-#pragma unroll
-            for (int j = 0; j < 32; j += 16) {
-              uint32_t w[4];
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                const int b = j + 4 * t;
-                w[t] = pack4_s8(ep.to_s8(ep.scaled((int)r[b], m, nb + b)), ep.to_s8(ep.scaled((int)r[b + 1], m, nb + b + 1)),
-                                ep.to_s8(ep.scaled((int)r[b + 2], m, nb + b + 2)),
-                                ep.to_s8(ep.scaled((int)r[b + 3], m, nb + b + 3)));
-              }
-              *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < N) ep.store((int)r[j], m, nb + j);
-          }
-        }
+        store_chunk(r, m, n0 + c, M, N, ep);
       }
     }
   }
@@ -155,6 +161,139 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- persistent variant for large problems -------------------------------------------------------------------------------
+// 128 x 256 tiles (one W tile byte feeds twice the MACs of the 128 x 128 kernel, which keeps the MMAs fed from shared
+// memory at tensor speed), four 48 KB stages, one CTA per SM walking tiles round-robin, and two 256-column accumulators in
+// TMEM so that the epilogue of a tile (warps 2..5) overlaps the main loop of the next one.  Tiles are ordered M-fastest:
+// CTAs that run at the same time read the same W tile, which then comes from L2.
+constexpr int PBN = 256;
+constexpr int kPStages = 4;
+constexpr int kPStageBytes = BM * BK + PBN * BK;   // 16 KB of A + 32 KB of W
+constexpr int kPSmemBytes = kPStages * kPStageBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                                  int M, int N, int K, Epilogue ep, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStages * kPStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kPStages;
+  uint64_t* acc_full = bars + 2 * kPStages;       // [2]
+  uint64_t* acc_empty = bars + 2 * kPStages + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPStages + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + PBN - 1) / PBN;
+  const int tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 1); }
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;  // k-iterations issued so far, over all tiles: the stage ring runs through tile boundaries
+      for (int i = 0; i < my_tiles; ++i) {
+        const int t = blockIdx.x + i * gridDim.x;
+        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * PBN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPStages;
+          ok = mbar_wait(&empty_bar[s], (uint32_t)(((it / kPStages) & 1) ^ 1), status, QB_ERR_TIMEOUT);
+          if (!ok) break;
+          uint8_t* stage = smem + s * kPStageBytes;
+          mbar_arrive_expect_tx(&full_bar[s], kPStageBytes);
+          tma_load_2d(stage, &tmap_a, &full_bar[s], kb * BK, m0);
+          tma_load_2d(stage + BM * BK, &tmap_w, &full_bar[s], kb * BK, n0);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, PBN);
+      int it = 0;
+      bool ok = true;
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int b = i & 1;
+        ok = mbar_wait(&acc_empty[b], (uint32_t)(((i >> 1) & 1) ^ 1), status, QB_ERR_TIMEOUT);  // epilogue has drained it
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_base + (uint32_t)(b * PBN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPStages;
+          ok = mbar_wait(&full_bar[s], (uint32_t)((it / kPStages) & 1), status, QB_ERR_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * kPStageBytes);
+          const uint32_t w_addr = a_addr + BM * BK;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            const uint64_t da = make_smem_desc(a_addr + k * 32, 16, 1024, kSwizzle128B);
+            const uint64_t dw = make_smem_desc(w_addr + k * 32, 16, 1024, kSwizzle128B);
+            umma_i8(acc, da, dw, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        umma_commit(&acc_full[b]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const bool lead = warp == 2 && lane == 0;
+    for (int i = 0; i < my_tiles; ++i) {
+      const int b = i & 1;
+      const int t = blockIdx.x + i * gridDim.x;
+      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * PBN;
+      // one thread polls, the four warps meet at a named barrier that also carries the outcome
+      uint32_t ok = 1;
+      if (lead) ok = mbar_wait(&acc_full[b], (uint32_t)((i >> 1) & 1), status, QB_ERR_TIMEOUT) ? 1u : 0u;
+      uint32_t all_ok;
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                   : "=r"(all_ok) : "r"(ok) : "memory");
+      if (!all_ok) break;
+      tc_fence_after_sync();
+      const int m = m0 + q * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * PBN);
+#pragma unroll 1
+      for (int c = 0; c < PBN; c += 64) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(acc + (uint32_t)c, r0);
+        tmem_ld_32x32(acc + (uint32_t)c + 32, r1);
+        tmem_ld_wait();
+        if (c + 64 >= PBN) {  // the last columns are in registers: hand the accumulator back before storing them
+          tc_fence_before_sync();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (lead) mbar_arrive(&acc_empty[b]);
+        }
+        store_chunk(r0, m, n0 + c, M, N, ep);
+        store_chunk(r1, m, n0 + c + 32, M, N, ep);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -214,18 +353,33 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
   CUtensorMap ta, tw;
   int rc = encode_tmap_2d_u8(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
   if (rc != QB_OK) return rc;
-  rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, BK);
-  if (rc != QB_OK) return rc;
+  int* status = device_status_ptr();
+  QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "device status word unavailable");
   static bool attr_set[64] = {};
   int dev = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
+  static const bool no_persistent = getenv("QB_GEMM_SMALL_TILES") != nullptr;
+  const int64_t ptiles = ceil_div(M, BM) * ceil_div(N, PBN);
+  if (!no_persistent && ptiles >= sm_count()) {   // enough 128 x 256 tiles to give every SM at least one
+    rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, PBN, BK);
+    if (rc != QB_OK) return rc;
+    static bool pattr_set[64] = {};
+    if (dev >= 64 || !pattr_set[dev]) {
+      QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes));
+      if (dev < 64) pattr_set[dev] = true;
+    }
+    const unsigned grid = (unsigned)std::min<int64_t>(ptiles, sm_count());
+    gemm_s8_tcgen05_persistent_kernel<<<grid, kThreads, kPSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
+    QB_LAUNCH_OK("gemm_s8_tcgen05_persistent_kernel");
+    return QB_OK;
+  }
+  rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, BK);
+  if (rc != QB_OK) return rc;
   if (dev >= 64 || !attr_set[dev]) {
     QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     if (dev < 64) attr_set[dev] = true;
   }
   dim3 grid((unsigned)ceil_div(M, BM), (unsigned)ceil_div(N, BN));
-  int* status = device_status_ptr();
-  QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "device status word unavailable");
   gemm_s8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
   QB_LAUNCH_OK("gemm_s8_tcgen05_kernel");
   return QB_OK;

@@ -224,27 +224,33 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
       // ---- GEMM1 result -> fp16 pair (hi, lo) -> A operand of GEMM2, in tensor memory ----
       if (!gwait(&bars.d1_ready[g], ph)) break;
       tc_fence_after_sync();
+      {
+        // all loads of the unit first, one wait: the accumulators of R rows are R * SPAD registers
+        uint32_t v[R][SPAD / 16][16];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int c16 = 0; c16 < SPAD / 16; ++c16) {
-          uint32_t v[16];
-          tmem_ld16(base + r * S + c16 * 16, v);
-          tmem_ld_wait();
-          uint32_t hi[8], lo[8];
+          for (int c16 = 0; c16 < SPAD / 16; ++c16) tmem_ld16(base + r * S + c16 * 16, v[r][c16]);
+        tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int c = c16 * 16 + 2 * e;
-            const float f0 = c < S ? __uint_as_float(v[2 * e]) : 0.0f;          // columns past S belong to the next row
-            const float f1 = c + 1 < S ? __uint_as_float(v[2 * e + 1]) : 0.0f;
-            const __half2 h = __floats2half2_rn(f0, f1);
-            const float2 hf = __half22float2(h);
-            const __half2 l = __floats2half2_rn(f0 - hf.x, f1 - hf.y);
-            hi[e] = *reinterpret_cast<const uint32_t*>(&h);
-            lo[e] = *reinterpret_cast<const uint32_t*>(&l);
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+          for (int c16 = 0; c16 < SPAD / 16; ++c16) {
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int c = c16 * 16 + 2 * e;
+              const float f0 = c < S ? __uint_as_float(v[r][c16][2 * e]) : 0.0f;      // columns past S belong to the next row
+              const float f1 = c + 1 < S ? __uint_as_float(v[r][c16][2 * e + 1]) : 0.0f;
+              const __half2 h = __floats2half2_rn(f0, f1);
+              const float2 hf = __half22float2(h);
+              const __half2 l = __floats2half2_rn(f0 - hf.x, f1 - hf.y);
+              hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+              lo[e] = *reinterpret_cast<const uint32_t*>(&l);
+            }
+            tmem_st8(base + kColHi + r * (SPAD / 2) + c16 * 8, hi);
+            tmem_st8(base + kColLo + r * (SPAD / 2) + c16 * 8, lo);
           }
-          tmem_st8(base + kColHi + r * (SPAD / 2) + c16 * 8, hi);
-          tmem_st8(base + kColLo + r * (SPAD / 2) + c16 * 8, lo);
         }
       }
       tmem_st_wait();
@@ -254,32 +260,38 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
       // ---- GEMM2 result -> int8 ----
       if (!gwait(&bars.d2_ready[g], ph)) break;
       tc_fence_after_sync();
+      {
+        uint32_t v[R][SPAD / 16][16];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int64_t row = u * R + r;
-        int8_t* dst = out + row * out_rs + jrow;
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int c16 = 0; c16 < SPAD / 16; ++c16) {
-          uint32_t v[16];
-          tmem_ld16(base + r * SPAD + c16 * 16, v);
-          tmem_ld_wait();
+          for (int c16 = 0; c16 < SPAD / 16; ++c16) tmem_ld16(base + r * SPAD + c16 * 16, v[r][c16]);
+        tmem_ld_wait();
+        // the accumulators are in registers: hand the buffer back before the stores
+        tc_fence_before_sync();
+        gsync();
+        if (lead) mbar_arrive(&bars.buf_free[g]);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int64_t row = u * R + r;
+          int8_t* dst = out + row * out_rs + jrow;
           if (row < rows) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int c = c16 * 16 + e;
-              if (c < S) {
-                const float y = __uint_as_float(v[e]) * scale128;
-                int qv;
-                asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(qv) : "f"(y + copysignf(0.5f, y)));
-                dst[c * 128] = (int8_t)qv;
+            for (int c16 = 0; c16 < SPAD / 16; ++c16) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const int c = c16 * 16 + e;
+                if (c < S) {
+                  const float y = __uint_as_float(v[r][c16][e]) * scale128;
+                  int qv;
+                  asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(qv) : "f"(y + copysignf(0.5f, y)));
+                  dst[c * 128] = (int8_t)qv;
+                }
               }
             }
           }
         }
       }
-      tc_fence_before_sync();
-      gsync();
-      if (lead) mbar_arrive(&bars.buf_free[g]);
     }
   }
   tc_fence_before_sync();

@@ -423,3 +423,28 @@ def test_update_kernel_variants_against_oracle(Bsz, H, P, G, N, grouped, layout)
     assert_fp16(out, y_ref)
     assert_lsb(st, st_ref, max_frac=0.02)
     ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)      # raises if a device-side wait timed out
+
+
+# ---- large GEMMs: the persistent 128 x 256 tensor-core kernel (needs at least one tile per SM) ---------------------
+@pytest.mark.parametrize("M,K,N,out_dtype", [(2000, 528, 3000, torch.int8), (2048, 1024, 5120, torch.float16),
+                                             (4100, 272, 2304, torch.int8)])
+def test_w8a8_gemm_large_against_exact_float_matmul(M, K, N, out_dtype):
+    """|acc| <= K * 127^2 < 2^24 for K <= 1040, so an fp32 matmul of the int8 values is exact and serves as the accumulator
+    reference at sizes the CPU oracle would take minutes for; the epilogue is then restated with the oracle's operation order."""
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int32).to(torch.int8).to(DEV)
+    w = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int32).to(torch.int8).to(DEV)   # (N, K) K-contiguous
+    a_s = (torch.rand(M, 1, generator=g) * 0.01 + 0.001).to(DEV)
+    b_s = (torch.rand(1, N, generator=g) * 0.01 + 0.001).to(DEV)
+    acc = a.float() @ w.float().t()
+    assert acc.abs().max().item() < 2 ** 24
+    res = a_s * (b_s * acc)
+    want = torch.clamp(torch.round(res), -128, 127).to(torch.int8) if out_dtype == torch.int8 else res.to(torch.float16)
+    c = torch.empty((M, N), dtype=out_dtype, device=DEV)
+    ops().quant_linear_cuda.cutlass_scaled_mm_dq(c, a, w.t(), a_s.reshape(-1), b_s.reshape(-1))
+    if out_dtype == torch.int8:
+        d = (c.int() - want.int()).abs()
+        assert d.max().item() <= 1 and (d > 0).float().mean().item() < 1e-4    # fp32 product order at exact ties only
+    else:
+        assert torch.equal(c, want)
+    ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)
