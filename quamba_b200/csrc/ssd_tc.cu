@@ -60,7 +60,7 @@ constexpr int kRegsCtl = 40, kRegsA = 64, kRegsB = 152;
 constexpr int kAtom = T * 128;                 // 16 KB: 128 rows x 128 bytes
 constexpr int kOffB16 = 0;                     // 2 stages x 2 atoms
 constexpr int kOffC16 = 4 * kAtom;             // 2 stages x 2 atoms
-constexpr int kOffLm = 8 * kAtom;              // 2 atoms
+constexpr int kOffLm = 8 * kAtom;              // 2 atoms, unused since Lm lives in tensor memory (kept: tile offsets unchanged)
 constexpr int kOffXraw = 10 * kAtom;           // 1 atom
 constexpr int kOffXw = 11 * kAtom;             // 1 atom
 constexpr int kOffS16 = 12 * kAtom;            // 1 atom
@@ -108,6 +108,21 @@ __device__ __forceinline__ float fast_log2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 16 consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -247,7 +262,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       constexpr uint32_t id_kn = make_idesc(1, 0, 0, 0, 1, 128, 64);   // K-major A x MN-major B
       constexpr uint32_t id_mn = make_idesc(1, 0, 0, 1, 1, 128, 64);   // MN-major A x MN-major B
       const uint32_t sB16 = smem_u32(smem + kOffB16), sC16 = smem_u32(smem + kOffC16);
-      const uint32_t sLm = smem_u32(smem + kOffLm), sXraw = smem_u32(smem + kOffXraw);
+      const uint32_t sXraw = smem_u32(smem + kOffXraw);
       const uint32_t sXw = smem_u32(smem + kOffXw), sS16 = smem_u32(smem + kOffS16);
       bool ok = mbar_wait(&ms.bc_full[0], 0, status, QB_ERR_TIMEOUT);
       if (ok) {
@@ -287,7 +302,14 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (!ok) break;
         tc_fence_after_sync();
         TRACE(1, j, 2);
-        issue_gemm(tmem + kColD2, sLm, false, 16, sXraw, true, id_kn);
+        {
+          const uint32_t lm = tmem + (st ? kColCB1 : kColCB);   // packed fp16 Lm, 8 columns per K = 16 step
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t db = make_smem_desc(sXraw + ks * 2048, 16, 1024, kSwizzle128B);
+            umma_f16_ta(tmem + kColD2, lm + ks * 8, db, id_kn, ks != 0 ? 1u : 0u);
+          }
+        }
         umma_commit(&ms.y_ready);
         TRACE(1, j, 3);
         if (j + 1 < nb) {
@@ -364,76 +386,76 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       const float dfold = ms.dfold;
       for (int j = 0; j < nb; ++j) {
         const int st = j & 1;
-        // the vectors of this block have landed, CB(j) is in TMEM buffer j & 1, GEMM3(j-1) no longer reads the Lm tile
-        if (!gwait3(&ms.bc_full[st], (j >> 1) & 1, &ms.cb_ready[st], (j >> 1) & 1, j > 0 ? &ms.y_ready : nullptr, (j - 1) & 1))
-          break;
+        // the vectors of this block have landed and CB(j) is in TMEM buffer j & 1.  Lm(j) overwrites that buffer, which
+        // GEMM3(j - 2) read long before CB(j) was issued into it, so nothing else has to be waited for.
+        if (!gwait3(&ms.bc_full[st], (j >> 1) & 1, &ms.cb_ready[st], (j >> 1) & 1, nullptr, 0)) break;
         tc_fence_after_sync();
         if (lead) TRACE(0, j, 3);
         const float* av = ms.ab[st];
         const float* bkv = av + T;
         const float a_row = av[row];
+        // Lm goes back into tensor memory, packed fp16, over the first 64 columns of the CB buffer it is computed from,
+        // and GEMM3 reads it from there as its A operand: 32 KB of shared-memory stores and 32 KB of MMA operand reads
+        // per block never happen.  Chunk c (fp32 columns 32c .. 32c + 31) becomes columns 16c .. 16c + 15.  The first
+        // pass (chunks 0 and 1) writes columns 0 .. 31, which hold chunk 0's fp32 data, so a group barrier separates the
+        // loads of that pass from its stores; the second pass (chunks 2, 3) writes columns 32 .. 63 = chunk 1's data,
+        // consumed in the first pass.
+        const uint32_t cbcol = tmem + tlane + ((j & 1) ? kColCB1 : kColCB);
 #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
           const int c = hsel + 2 * i;  // 32-column chunk of k
-          uint8_t* dst = smem + kOffLm + (c >> 1) * kAtom + row * 128;
+          uint32_t o[16];
           if (c > q) {  // entirely above the diagonal for every row of this warp
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < 16; ++u) o[u] = 0u;
+            if (i == 0) { gsync(); tc_fence_after_sync(); }
           } else {
             uint32_t cb[32];
-            tmem_ld_32x32(tmem + tlane + ((j & 1) ? kColCB1 : kColCB) + 32 * c, cb);
+            tmem_ld_32x32(cbcol + 32 * c, cb);
             if (c == q) {
               // diagonal chunk: exact exponent per element, the k <= m mask (k - 32c <= lane), and the skip weight D
               // on the diagonal itself (y = sx (Lm + D I) x) when D has one value per head
               tmem_ld_wait();
+              if (i == 0) { tc_fence_before_sync(); gsync(); tc_fence_after_sync(); }
               const float4* bk4 = reinterpret_cast<const float4*>(bkv + 32 * c);
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                uint32_t o[4];
-#pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                  const float4 bb = bk4[2 * u + v];
-                  const int t0 = 8 * u + 4 * v;
-                  float e0 = __uint_as_float(cb[t0 + 0]) * fast_exp2(a_row - bb.x);
-                  float e1 = __uint_as_float(cb[t0 + 1]) * fast_exp2(a_row - bb.y);
-                  float e2 = __uint_as_float(cb[t0 + 2]) * fast_exp2(a_row - bb.z);
-                  float e3 = __uint_as_float(cb[t0 + 3]) * fast_exp2(a_row - bb.w);
-                  e0 = t0 + 0 < lane ? e0 : (t0 + 0 == lane ? e0 + dfold : 0.0f);
-                  e1 = t0 + 1 < lane ? e1 : (t0 + 1 == lane ? e1 + dfold : 0.0f);
-                  e2 = t0 + 2 < lane ? e2 : (t0 + 2 == lane ? e2 + dfold : 0.0f);
-                  e3 = t0 + 3 < lane ? e3 : (t0 + 3 == lane ? e3 + dfold : 0.0f);
-                  o[2 * v] = pack_h2(e0, e1);
-                  o[2 * v + 1] = pack_h2(e2, e3);
-                }
-                *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              for (int u = 0; u < 8; ++u) {
+                const float4 bb = bk4[u];
+                const int t0 = 4 * u;
+                float e0 = __uint_as_float(cb[t0 + 0]) * fast_exp2(a_row - bb.x);
+                float e1 = __uint_as_float(cb[t0 + 1]) * fast_exp2(a_row - bb.y);
+                float e2 = __uint_as_float(cb[t0 + 2]) * fast_exp2(a_row - bb.z);
+                float e3 = __uint_as_float(cb[t0 + 3]) * fast_exp2(a_row - bb.w);
+                e0 = t0 + 0 < lane ? e0 : (t0 + 0 == lane ? e0 + dfold : 0.0f);
+                e1 = t0 + 1 < lane ? e1 : (t0 + 1 == lane ? e1 + dfold : 0.0f);
+                e2 = t0 + 2 < lane ? e2 : (t0 + 2 == lane ? e2 + dfold : 0.0f);
+                e3 = t0 + 3 < lane ? e3 : (t0 + 3 == lane ? e3 + dfold : 0.0f);
+                o[2 * u] = pack_h2(e0, e1);
+                o[2 * u + 1] = pack_h2(e2, e3);
               }
             } else {
               // chunk below the diagonal: 2^(a_t - bk_s) = 2^(a_t - m) * ec[s], m = a at the end of chunk c
               const float e_row = fast_exp2(a_row - av[32 * c + 31]);
               tmem_ld_wait();
+              if (i == 0) { tc_fence_before_sync(); gsync(); tc_fence_after_sync(); }
               const float4* ec4 = reinterpret_cast<const float4*>(av + 2 * T + 32 * c);
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                uint32_t o[4];
-#pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                  const float4 ee = ec4[2 * u + v];
-                  const int t0 = 8 * u + 4 * v;
-                  const float e0 = __uint_as_float(cb[t0 + 0]) * (e_row * ee.x);
-                  const float e1 = __uint_as_float(cb[t0 + 1]) * (e_row * ee.y);
-                  const float e2 = __uint_as_float(cb[t0 + 2]) * (e_row * ee.z);
-                  const float e3 = __uint_as_float(cb[t0 + 3]) * (e_row * ee.w);
-                  o[2 * v] = pack_h2(e0, e1);
-                  o[2 * v + 1] = pack_h2(e2, e3);
-                }
-                *reinterpret_cast<uint4*>(dst + (((4 * (c & 1) + u) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              for (int u = 0; u < 8; ++u) {
+                const float4 ee = ec4[u];
+                const int t0 = 4 * u;
+                const float e0 = __uint_as_float(cb[t0 + 0]) * (e_row * ee.x);
+                const float e1 = __uint_as_float(cb[t0 + 1]) * (e_row * ee.y);
+                const float e2 = __uint_as_float(cb[t0 + 2]) * (e_row * ee.z);
+                const float e3 = __uint_as_float(cb[t0 + 3]) * (e_row * ee.w);
+                o[2 * u] = pack_h2(e0, e1);
+                o[2 * u + 1] = pack_h2(e2, e3);
               }
             }
           }
+          tmem_st16(cbcol + 16 * c, o);
         }
+        tmem_st_wait();
         tc_fence_before_sync();
-        fence_proxy_async_smem();
         gsync();
         if (lead) { mbar_arrive(&ms.lm_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(0, j, 4); }
       }

@@ -1,0 +1,232 @@
+"""The reference's own acceptance tests, restated for this implementation.
+
+The reference checks its CUDA / Triton kernels against floating-point PyTorch layers with loose, explicit
+criteria (quamba/tests/test_causal_conv1d.py, test_qsscan.py, test_ssd_combined.py, test_qlinear.py):
+quantise float inputs per tensor, run the quantised op, de-quantise, and require `allclose(rtol 1e-2, atol 1e-1)` or
+`r2 < 1e-3` (relative squared error) / `mean|diff| / mean|ref| < 0.08`.  These tests build the same situations on
+seeded inputs at the reference's model shapes and apply the same criteria to the modules of this package, so that a
+maintainer can read them next to the originals.  The floating-point references are plain torch (conv1d + SiLU, the
+selective-scan recurrence, the SSD recurrence, dense Hadamard matrices, nn.Linear)."""
+import math
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from oracle import hadamard as ohad
+from quamba_b200 import modules as M
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def q8t(x):
+    s = x.abs().max() / 127
+    return (x / s).round().clamp(-128, 127).to(torch.int8), s.float()
+
+
+def r2(y_hat, y):
+    return ((y_hat.float() - y.float()).pow(2).mean() / y.float().pow(2).mean()).item()
+
+
+# ---- causal conv1d (test_causal_conv1d.py: seqlast / channellast forward, update) --------------------------------
+@pytest.mark.parametrize("batch,d_inner,seqlen,layout", [(1, 1536, 1024, "seqlast"), (2, 5120, 33, "seqlast"),
+                                                         (1, 1536, 1024, "channellast"), (2, 5120, 32, "channellast")])
+def test_qcausalconv1d_forward_like_reference(batch, d_inner, seqlen, layout):
+    torch.manual_seed(0)
+    x = torch.rand(batch, d_inner, seqlen, device=DEV)
+    conv = nn.Conv1d(d_inner, d_inner, 4, groups=d_inner, padding=3, bias=True).to(DEV)
+    y = F.silu(conv(x)[..., :seqlen])
+    y_scale = y.abs().max() / 127
+    qy = (y / y_scale).round() * y_scale
+    qx, x_scale = q8t(x)
+    if layout == "channellast":
+        qx = qx.transpose(1, 2).contiguous().transpose(1, 2)
+    qconv = M.QCausalConv1D.from_fp16(conv, input_scale=x_scale, output_scale=y_scale)
+    y_ = qconv(qx).float() * y_scale
+    assert torch.allclose(qy, y_, rtol=1e-2, atol=1e-1)
+    assert r2(y_, y) < 1e-3
+
+
+def test_qcausalconv1d_update_like_reference():
+    torch.manual_seed(1)
+    batch, d_inner = 4, 1536
+    conv = nn.Conv1d(d_inner, d_inner, 4, groups=d_inner, padding=3, bias=True).to(DEV)
+    hist = torch.rand(batch, d_inner, 8, device=DEV)
+    y = F.silu(conv(hist)[..., :8])
+    y_scale = y.abs().max() / 127
+    qx, x_scale = q8t(hist)
+    qconv = M.QCausalConv1D.from_fp16(conv, input_scale=x_scale, output_scale=y_scale)
+    state = torch.zeros(batch, d_inner, 4, dtype=torch.int8, device=DEV)
+    for t in range(8):
+        yt = qconv.update(qx[:, :, t].contiguous(), state).float() * y_scale
+        assert torch.allclose(y[:, :, t], yt, rtol=1e-2, atol=1e-1)
+
+
+@pytest.mark.parametrize("batch,x_dim,d_state,n_groups,seqlen", [(1, 1536, 128, 1, 512), (2, 8192, 128, 8, 64)])
+def test_quamb2conv1d_forward_and_update_like_reference(batch, x_dim, d_state, n_groups, seqlen):
+    """Per-tensor output scales (test_quamba2_conv1d_channellast_fwd / test_quamba2_conv1d_update)."""
+    torch.manual_seed(2)
+    gn = d_state * n_groups
+    d = x_dim + 2 * gn
+    conv = nn.Conv1d(d, d, 4, groups=d, padding=3, bias=True).to(DEV)
+    xBC = torch.rand(batch, seqlen, d, device=DEV)
+    y = F.silu(conv(xBC.transpose(1, 2))[..., :seqlen]).transpose(1, 2)          # (b, l, d)
+    x_ref, B_ref, C_ref = torch.split(y, [x_dim, gn, gn], dim=-1)
+    x_in, B_in, C_in = torch.split(xBC, [x_dim, gn, gn], dim=-1)
+    sx, sB, sC = (t.abs().max() / 127 for t in (x_in, B_in, C_in))
+    q_in = torch.cat([(x_in / sx).round(), (B_in / sB).round(), (C_in / sC).round()], dim=-1).clamp(-128, 127).to(torch.int8)
+    # without head / dim groups the reference takes ONE output scale for each of x, B and C (quamba2_conv1d.cpp:195-198)
+    x_out_scale, B_out, C_out = ((t.abs().max() / 127).reshape(1).float() for t in (x_ref, B_ref, C_ref))
+    q = M.Quamb2Conv1D.from_fp16(conv, x_dim, 64, d_state, n_groups, sx, sB, sC, x_out_scale, B_out, C_out, None, None)
+    qx, qB, qC = q(q_in.transpose(1, 2))
+    assert r2(qx.float() * x_out_scale, x_ref) < 1e-3
+    assert r2(qB.float() * B_out, B_ref) < 1e-3
+    assert r2(qC.float() * C_out, C_ref) < 1e-3
+    state = torch.zeros(batch, d, 4, dtype=torch.int8, device=DEV)
+    for t in range(4):
+        ux, uB, uC = q.update(q_in[:, t].contiguous(), state)
+        assert torch.equal(ux.reshape(batch, -1), qx[:, t].reshape(batch, -1))
+        assert torch.equal(uB.reshape(batch, -1), qB[:, t].reshape(batch, -1))
+
+
+# ---- Mamba1 selective scan (test_qsscan.py) ---------------------------------------------------------------------
+def selective_scan_float(u, delta, A, B, C, D, z, softplus):
+    """The selective-scan recurrence in fp32: h <- exp(delta A) h + delta B u; y = C.h + D u; y *= silu(z)."""
+    b, d, L = u.shape
+    if softplus:
+        delta = F.softplus(delta)
+    h = torch.zeros(b, d, A.shape[1], device=u.device)
+    ys = []
+    for t in range(L):
+        dA = torch.exp(delta[:, :, t, None] * A[None])
+        h = dA * h + delta[:, :, t, None] * B[:, None, :, t] * u[:, :, t, None]
+        ys.append((h * C[:, None, :, t]).sum(-1) + D[None] * u[:, :, t])
+    y = torch.stack(ys, dim=-1)
+    return (y * F.silu(z)).transpose(1, 2), h
+
+
+@pytest.mark.parametrize("batch,seqlen,d_ssm,d_state", [(1, 512, 1536, 16), (2, 65, 5120, 16)])
+def test_qsscan_forward_and_update_like_reference(batch, seqlen, d_ssm, d_state):
+    torch.manual_seed(3)
+    A_log = torch.log(torch.arange(1, d_state + 1, dtype=torch.float32, device=DEV)).repeat(d_ssm, 1)
+    A = -torch.exp(A_log)
+    D = torch.ones(d_ssm, device=DEV)
+    x, z, dt = (torch.rand(batch, d_ssm, seqlen, device=DEV) for _ in range(3))
+    Bm, Cm = (torch.rand(batch, d_state, seqlen, device=DEV) for _ in range(2))
+    y, last = selective_scan_float(x, dt, A, Bm, Cm, D, z, True)
+    (qx, sx), (qz, sz), (qdt, sdt), (qB, sB), (qC, sC) = (q8t(t) for t in (x, z, dt, Bm, Cm))
+    s_state = last.abs().max() / 127
+    qs = M.QSScan.from_fp16(d_state, d_ssm, A_log.clone(), D.clone(), dt_bias=None, delta_softplus=True,
+                            ssm_state_scale=s_state, u_scale=sx, dt_scale=sdt, B_scale=sB, C_scale=sC, z_scale=sz)
+    y_, last_ = qs(qx, qdt, qB, qC, z=qz, return_last_state=True)
+    assert r2(y_, y) < 1e-3
+    assert r2(last_.float() * s_state, last) < 1e-3
+    # one decode step from the quantised last state against the float recurrence continued by one token
+    x1, z1, dt1 = (torch.rand(batch, d_ssm, device=DEV) for _ in range(3))
+    B1, C1 = (torch.rand(batch, d_state, device=DEV) for _ in range(2))
+    d1 = F.softplus(dt1)
+    h1 = torch.exp(d1[..., None] * A[None]) * last + d1[..., None] * B1[:, None] * x1[..., None]
+    y1 = ((h1 * C1[:, None]).sum(-1) + D[None] * x1) * F.silu(z1)
+    q = lambda t, s: (t / s).round().clamp(-128, 127).to(torch.int8)
+    state = last_.clone()
+    yq, _ = qs.update(state, q(x1, sx), q(dt1, sdt), q(B1, sB), q(C1, sC), z=q(z1, sz))
+    assert r2(yq, y1) < 1e-3
+    assert r2(state.float() * s_state, h1) < 1e-3
+
+
+# ---- Mamba2 SSD (test_ssd_combined.py) --------------------------------------------------------------------------
+def ssd_float(x, dt, A, B, C, D, dt_bias):
+    """Mamba2 recurrence in fp32 (state per head p x n): the sequential definition the chunked kernels implement."""
+    b, L, h, p = x.shape
+    g = B.shape[2]
+    dt = F.softplus(dt + dt_bias[None, None])
+    Bh, Ch = B.repeat_interleave(h // g, dim=2), C.repeat_interleave(h // g, dim=2)
+    s = torch.zeros(b, h, p, B.shape[-1], device=x.device)
+    ys = []
+    for t in range(L):
+        dA = torch.exp(dt[:, t] * A[None])[:, :, None, None]
+        s = dA * s + (dt[:, t, :, None] * x[:, t])[..., None] * Bh[:, t, :, None, :]
+        ys.append((s * Ch[:, t, :, None, :]).sum(-1) + D[None, :, None] * x[:, t])
+    return torch.stack(ys, dim=1), s
+
+
+@pytest.mark.parametrize("batch,seqlen,d_ssm,ngroups", [(1, 512, 1536, 1), (2, 300, 4096, 8)])
+def test_qchunkscan_forward_and_update_like_reference(batch, seqlen, d_ssm, ngroups):
+    torch.manual_seed(4)
+    headdim, dstate, chunk = 64, 128, 256
+    h = d_ssm // headdim
+    x = torch.rand(batch, seqlen, h, headdim, device=DEV) - 0.5
+    dt = torch.rand(batch, seqlen, h, device=DEV)
+    dt_bias = torch.rand(h, device=DEV) - 4.0
+    A_log = torch.log(torch.rand(h, device=DEV) * 15 + 1)
+    A = -torch.exp(A_log)
+    Bm, Cm = (torch.rand(batch, seqlen, ngroups, dstate, device=DEV) - 0.5 for _ in range(2))
+    D = torch.ones(h, device=DEV)
+    y, s_last = ssd_float(x, dt, A, Bm, Cm, D, dt_bias)
+    (qx, sx), (qdt, sdt), (qB, sB), (qC, sC) = (q8t(t) for t in (x, dt, Bm, Cm))
+    s_state = (s_last.abs().max() / 127).reshape(1)
+    qcs = M.Quamba2ChunkScan.from_fp16(d_ssm, headdim, dstate, ngroups, sx.reshape(1), None, None, A_log.clone(), chunk,
+                                       s_state, D=D.clone(), D_has_hdim=False, dt_bias=dt_bias.clone(), delta_softplus=True,
+                                       dt_scale=sdt, B_scale=sB.reshape(1), C_scale=sC.reshape(1), z_scale=None)
+    # the float reference sees the same quantised A_log / D the module holds? no: like the reference test, it is the
+    # unquantised float model, and the criterion absorbs the parameter quantisation error
+    y_, fs = qcs(qx, qdt, qB, qC, return_final_states=True)
+    assert r2(y_, y) < 1e-3
+    assert r2(fs.float() * s_state, s_last) < 1e-3
+    x1, dt1 = torch.rand(batch, d_ssm, device=DEV) - 0.5, torch.rand(batch, h, device=DEV)
+    B1, C1 = (torch.rand(batch, ngroups * dstate, device=DEV) - 0.5 for _ in range(2))
+    d1 = F.softplus(dt1 + dt_bias[None])
+    Bh = B1.reshape(batch, ngroups, dstate).repeat_interleave(h // ngroups, dim=1)
+    Ch = C1.reshape(batch, ngroups, dstate).repeat_interleave(h // ngroups, dim=1)
+    s1 = torch.exp(d1 * A[None])[:, :, None, None] * s_last + (d1[..., None] * x1.reshape(batch, h, headdim))[..., None] * Bh[:, :, None]
+    y1 = (s1 * Ch[:, :, None]).sum(-1) + D[None, :, None] * x1.reshape(batch, h, headdim)
+    q = lambda t, s: (t / s).round().clamp(-128, 127).to(torch.int8)
+    state = fs.clone()
+    yq = qcs.update(state, q(x1, sx), q(dt1, sdt), q(B1, sB), q(C1, sC))
+    assert r2(yq, y1) < 1e-3
+    assert r2(state.float() * s_state, s1) < 1e-3
+
+
+# ---- Hadamard -----------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dim", [1536, 5120, 2048])
+def test_qhadamard_against_dense_matrix(dim):
+    torch.manual_seed(5)
+    x = torch.randn(4, 37, dim, device=DEV).half()
+    special = 12 if dim % 12 == 0 else (40 if dim % 40 == 0 else None)
+    H = ohad.hadamard_matrix(dim, special).to(DEV)
+    y = (x.float() @ H.t()) / math.sqrt(dim)
+    s = y.abs().max() / 127
+    qh = M.QHadamard(dim, x_H_scale=s.item())
+    y_ = qh(x).float() * s
+    assert r2(y_, y) < 1e-3 and (y_ - y).abs().max() <= 0.51 * s
+
+
+# ---- linears (test_qlinear.py) -----------------------------------------------------------------------------------
+@pytest.mark.parametrize("batch,seqlen,hidden,model", [(4, 89, 768, 1536), (1, 128, 2560, 5120), (1, 1, 768, 1536)])
+def test_linear_modules_like_reference(batch, seqlen, hidden, model):
+    torch.manual_seed(6)
+    d_in_proj = 2 * model + 2 * 128 + 24
+    x = torch.randn(batch, seqlen, hidden, device=DEV).half()
+    lin = nn.Linear(hidden, d_in_proj, bias=False, dtype=torch.float16).to(DEV)
+    y_gt = lin(x).float()
+    qx, x_scale = q8t(x.float())
+    y_scale = y_gt.abs().max() / 127
+    # W8A8 -> fp16 and -> int8: r2 < 1e-3 and max error < 0.1
+    for mod, deq in ((M.W8A8B16O16Linear.from_fp16(lin, x_scale), 1.0), (M.W8A8B8O8Linear.from_fp16(lin, x_scale, y_scale), y_scale)):
+        y_hat = mod(qx).float() * deq
+        assert r2(y_hat, y_gt) < 1e-3 and (y_gt - y_hat).abs().max() < 0.1
+    if batch * seqlen > 1:
+        y_hat = (M.W8A8B8O8Linear.from_fp16(lin, x_scale, y_scale).to_seqlen_last(qx).float() * y_scale).transpose(1, 2)
+        assert r2(y_hat, y_gt) < 1e-3 and (y_gt - y_hat).abs().max() < 0.1
+    # W4A8: mean|diff| / mean|ref| < 0.08 against the layer evaluated on the quantised activations
+    y_q_in = lin(qx.half() * x_scale.half()).float()
+    w4 = M.W4A8B16O16Linear.from_fp16(lin, x_scale)
+    y_hat = w4(qx).float()
+    assert ((y_hat - y_q_in).abs().mean() / y_q_in.abs().mean()).item() < 0.08
+    s_o = y_q_in.abs().max() / 127
+    y_ref8 = (y_q_in / s_o).round().clamp(-128, 127) * s_o
+    w48 = M.W4A8B8O8Linear.from_fp16(lin, x_scale, s_o)
+    y_hat8 = w48(qx).float() * s_o
+    assert ((y_hat8 - y_ref8).abs().mean() / y_ref8.abs().mean()).item() < 0.08
