@@ -121,6 +121,10 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, BN);
+      // descriptor words of stage 0; a stage / K step is one 32-bit add away (the issuer's instruction count per MMA
+      // decides whether the tensor pipe stays fed)
+      const SmemDesc da0 = make_smem_desc2(smem_u32(sA), 16, 1024, kSwizzle128B);
+      const SmemDesc dw0 = make_smem_desc2(smem_u32(sW), 16, 1024, kSwizzle128B);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % kStages;
@@ -128,14 +132,11 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         ok = mbar_wait(&full_bar[s], ph, status, QB_ERR_TIMEOUT);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(sA + s * kTileBytes);
-        const uint32_t w_addr = smem_u32(sW + s * kTileBytes);
+        const SmemDesc da = desc_advance(da0, (uint32_t)s * kTileBytes);
+        const SmemDesc dw = desc_advance(dw0, (uint32_t)s * kTileBytes);
 #pragma unroll
-        for (int k = 0; k < BK / 32; ++k) {
-          const uint64_t da = make_smem_desc(a_addr + k * 32, 16, 1024, kSwizzle128B);
-          const uint64_t dw = make_smem_desc(w_addr + k * 32, 16, 1024, kSwizzle128B);
-          umma_i8(tmem_base, da, dw, idesc, (kb | k) != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < BK / 32; ++k)
+          umma_i8(tmem_base, desc_advance(da, k * 32), desc_advance(dw, k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
         umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
       }
       umma_commit(accum_bar);  // accumulator complete (arrives even after an aborted loop)
@@ -230,6 +231,7 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, PBN);
+      const SmemDesc da0 = make_smem_desc2(smem_u32(smem), 16, 1024, kSwizzle128B);
       int it = 0;
       bool ok = true;
       for (int i = 0; i < my_tiles && ok; ++i) {
@@ -243,14 +245,11 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
           ok = mbar_wait(&full_bar[s], (uint32_t)((it / kPStages) & 1), status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * kPStageBytes);
-          const uint32_t w_addr = a_addr + BM * BK;
+          const SmemDesc da = desc_advance(da0, (uint32_t)s * kPStageBytes);
+          const SmemDesc dw = desc_advance(da, BM * BK);
 #pragma unroll
-          for (int k = 0; k < BK / 32; ++k) {
-            const uint64_t da = make_smem_desc(a_addr + k * 32, 16, 1024, kSwizzle128B);
-            const uint64_t dw = make_smem_desc(w_addr + k * 32, 16, 1024, kSwizzle128B);
-            umma_i8(acc, da, dw, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 32; ++k)
+            umma_i8(acc, desc_advance(da, k * 32), desc_advance(dw, k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);
         }
         umma_commit(&acc_full[b]);

@@ -40,13 +40,6 @@ struct HadBars {
   uint32_t tmem_slot;
 };
 
-__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -153,7 +146,11 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
     if (lane == 0) {
       constexpr uint32_t id1 = make_idesc(1, 0, 0, 0, 0, 128, N1);
       constexpr uint32_t id2 = make_idesc(1, 0, 0, 0, 0, 128, SPAD);
-      const uint32_t sH = smem_u32(smem + kOffH128), sHS = smem_u32(smem + kOffHS);
+      // descriptor words built once; per instruction only a 32-bit add remains (the issuing thread's instruction
+      // count per MMA, not the tensor pipe, limits these small MMAs)
+      const SmemDesc dH = make_smem_desc2(smem_u32(smem + kOffH128), 16, 1024, kSwizzle128B);
+      const SmemDesc dHS = make_smem_desc2(smem_u32(smem + kOffHS), 16, 1024, kSwizzle128B);
+      const SmemDesc dX0 = make_smem_desc2(smem_u32(smem + kOffX), 16, 1024, kSwizzle128B);
       auto second = [&](int64_t i) -> bool {   // GEMM2 of local unit i: per row, hi then lo
         const int g = (int)(i & 1);
         if (!mbar_wait(&bars.a_ready[g], (uint32_t)((i >> 1) & 1), status, kStatusHad)) return false;
@@ -166,8 +163,7 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
 #pragma unroll
             for (int ks = 0; ks < SPAD / 16; ++ks) {
               const uint32_t a_t = base + (part ? kColLo : kColHi) + r * (SPAD / 2) + ks * 8;
-              const uint64_t db = make_smem_desc(sHS + ks * 32, 16, 1024, kSwizzle128B);
-              umma_f16_ta(base + r * SPAD, a_t, db, id2, (part | ks) != 0 ? 1u : 0u);
+              umma_f16_ta(base + r * SPAD, a_t, desc_advance(dHS, ks * 32), id2, (part | ks) != 0 ? 1u : 0u);
             }
           }
         }
@@ -181,13 +177,11 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
              mbar_wait(&bars.buf_free[g], (uint32_t)(((i >> 1) & 1) ^ 1), status, kStatusHad);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t sX = smem_u32(smem + kOffX + stg * kStageBytes);
+        const SmemDesc dX = desc_advance(dX0, (uint32_t)stg * kStageBytes);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t da = make_smem_desc(sH + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSwizzle128B);
-          const uint64_t db = make_smem_desc(sX + (ks >> 2) * (N1 * 128) + (ks & 3) * 32, 16, 1024, kSwizzle128B);
-          umma_f16(tmem + g * 256, da, db, id1, ks != 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma_f16(tmem + g * 256, desc_advance(dH, (ks >> 2) * 16384 + (ks & 3) * 32),
+                   desc_advance(dX, (ks >> 2) * (N1 * 128) + (ks & 3) * 32), id1, ks != 0 ? 1u : 0u);
         umma_commit(&bars.d1_ready[g]);
         umma_commit(&bars.x_empty[stg]);
         if (i > 0) ok = second(i - 1);

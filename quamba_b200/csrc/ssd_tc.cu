@@ -108,13 +108,6 @@ __device__ __forceinline__ float fast_log2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -172,18 +165,18 @@ __device__ __forceinline__ void quad_transpose(uint4 (&c)[4], int lane) {
   }
 }
 
-// One K = 128 contraction as eight K = 16 instructions.
+// One K = 128 contraction as eight K = 16 instructions.  The descriptors come in as two 32-bit words each and a K step
+// is one add on the low word: the issuing thread must spend only a handful of instructions per MMA, or the tensor pipe
+// waits for it (48 to 64 cycles of tensor work per instruction here).
 //   K-major operand (two 64-element atoms along K):   address = base + (ks / 4) * 16 KB + (ks % 4) * 32
 //   MN-major operand (rows are K):                    address = base + ks * 16 rows * 128 B
-__device__ __forceinline__ void issue_gemm(uint32_t d_tmem, uint32_t a_base, bool a_mn, uint32_t a_lbo, uint32_t b_base, bool b_mn,
-                                           uint32_t idesc) {
+template <bool kAMn, bool kBMn>
+__device__ __forceinline__ void issue_gemm(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc) {
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    const uint32_t aa = a_mn ? a_base + ks * 2048 : a_base + (ks >> 2) * kAtom + (ks & 3) * 32;
-    const uint32_t bb = b_mn ? b_base + ks * 2048 : b_base + (ks >> 2) * kAtom + (ks & 3) * 32;
-    const uint64_t da = make_smem_desc(aa, a_lbo, 1024, kSwizzle128B);
-    const uint64_t db = make_smem_desc(bb, 16, 1024, kSwizzle128B);
-    umma_f16(d_tmem, da, db, idesc, ks != 0 ? 1u : 0u);
+    const uint32_t ao = kAMn ? ks * 2048 : (ks >> 2) * kAtom + (ks & 3) * 32;
+    const uint32_t bo = kBMn ? ks * 2048 : (ks >> 2) * kAtom + (ks & 3) * 32;
+    umma_f16(d_tmem, desc_advance(a, ao), desc_advance(b, bo), idesc, ks != 0 ? 1u : 0u);
   }
 }
 
@@ -261,19 +254,23 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       constexpr uint32_t id_cb = make_idesc(1, 0, 0, 0, 0, 128, 128);  // C (K-major) x B (K-major)
       constexpr uint32_t id_kn = make_idesc(1, 0, 0, 0, 1, 128, 64);   // K-major A x MN-major B
       constexpr uint32_t id_mn = make_idesc(1, 0, 0, 1, 1, 128, 64);   // MN-major A x MN-major B
-      const uint32_t sB16 = smem_u32(smem + kOffB16), sC16 = smem_u32(smem + kOffC16);
-      const uint32_t sXraw = smem_u32(smem + kOffXraw);
-      const uint32_t sXw = smem_u32(smem + kOffXw), sS16 = smem_u32(smem + kOffS16);
+      // descriptor words of every operand tile, built once (stage 1 of B / C is 2 atoms further)
+      const SmemDesc dBk = make_smem_desc2(smem_u32(smem + kOffB16), 16, 1024, kSwizzle128B);      // B, K-major (CB)
+      const SmemDesc dBm = make_smem_desc2(smem_u32(smem + kOffB16), kAtom, 1024, kSwizzle128B);   // B, MN-major A of GEMM4
+      const SmemDesc dCk = make_smem_desc2(smem_u32(smem + kOffC16), 16, 1024, kSwizzle128B);      // C, K-major
+      const SmemDesc dXraw = make_smem_desc2(smem_u32(smem + kOffXraw), 16, 1024, kSwizzle128B);
+      const SmemDesc dXw = make_smem_desc2(smem_u32(smem + kOffXw), 16, 1024, kSwizzle128B);
+      const SmemDesc dS16 = make_smem_desc2(smem_u32(smem + kOffS16), 16, 1024, kSwizzle128B);
       bool ok = mbar_wait(&ms.bc_full[0], 0, status, QB_ERR_TIMEOUT);
       if (ok) {
         tc_fence_after_sync();
-        issue_gemm(tmem + kColCB, sC16, false, 16, sB16, false, id_cb);
+        issue_gemm<false, false>(tmem + kColCB, dCk, dBk, id_cb);
         umma_commit(&ms.cb_ready[0]);
       }
       for (int j = 0; j < nb && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = j & 1;
-        const uint32_t bB = sB16 + st * 2 * kAtom, bC = sC16 + st * 2 * kAtom;
+        const SmemDesc bBm = desc_advance(dBm, st * 2 * kAtom), bC = desc_advance(dCk, st * 2 * kAtom);
         if (j > 0) {
           // GEMM2(j): D1[j & 1] = C(j) S_prev.  Needs the fp16 state of block j - 1; the buffer was last read by the
           // output step of block j - 2, whose y_free this thread observed before GEMM3(j - 1).  s16_ready also says that
@@ -282,7 +279,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           if (!ok) break;
           tc_fence_after_sync();
           TRACE(1, j, 0);
-          issue_gemm(tmem + (st ? kColD1b : kColD1), bC, false, 16, sS16, true, id_kn);
+          issue_gemm<false, true>(tmem + (st ? kColD1b : kColD1), bC, dS16, id_kn);
           umma_commit(&ms.d1_ready);   // the state tile may be rewritten once this has fired
         }
         // GEMM4(j): local state of the block, S = (x w)^T B
@@ -290,7 +287,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (!ok) break;
         tc_fence_after_sync();
         TRACE(1, j, 1);
-        issue_gemm(tmem + kColS, bB, true, kAtom, sXw, true, id_mn);
+        issue_gemm<true, true>(tmem + kColS, bBm, dXw, id_mn);
         umma_commit(&ms.s_ready);
         // GEMM3(j) overwrites D2: the output step of block j - 1 must have loaded it
         if (j > 0) {
@@ -305,10 +302,8 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         {
           const uint32_t lm = tmem + (st ? kColCB1 : kColCB);   // packed fp16 Lm, 8 columns per K = 16 step
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t db = make_smem_desc(sXraw + ks * 2048, 16, 1024, kSwizzle128B);
-            umma_f16_ta(tmem + kColD2, lm + ks * 8, db, id_kn, ks != 0 ? 1u : 0u);
-          }
+          for (int ks = 0; ks < 8; ++ks)
+            umma_f16_ta(tmem + kColD2, lm + ks * 8, desc_advance(dXraw, ks * 2048), id_kn, ks != 0 ? 1u : 0u);
         }
         umma_commit(&ms.y_ready);
         TRACE(1, j, 3);
@@ -320,7 +315,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           ok = mbar_wait(&ms.bc_full[sn], ((j + 1) >> 1) & 1, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_gemm(tmem + (sn ? kColCB1 : kColCB), sC16 + sn * 2 * kAtom, false, 16, sB16 + sn * 2 * kAtom, false, id_cb);
+          issue_gemm<false, false>(tmem + (sn ? kColCB1 : kColCB), desc_advance(dCk, sn * 2 * kAtom), desc_advance(dBk, sn * 2 * kAtom), id_cb);
           umma_commit(&ms.cb_ready[sn]);
         }
         // Release the B/C stage of block j last.  Its readers were CB(j), GEMM4(j) and GEMM2(j); releasing it right

@@ -167,6 +167,45 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// The same descriptor as two 32-bit words.  The issuing thread is a single warp whose dependent instructions cost
+// several cycles each, and at 32 to 128 cycles of tensor work per tcgen05.mma a dozen instructions of descriptor
+// arithmetic per MMA leave the tensor pipe waiting for the issuer (measured: 116 to 310 cycles per MMA with
+// descriptors built per instruction, against 48 to 128 with the form below).  So: build the words once per tile,
+// advance along K with ONE 32-bit add on the low word (the start-address field sits in bits 0..13 and never carries
+// while the address stays inside shared memory), and let the asm block pair the words into the 64-bit operand.
+struct SmemDesc { uint32_t lo, hi; };
+__device__ __forceinline__ SmemDesc make_smem_desc2(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, Swizzle sw) {
+  SmemDesc d;
+  d.lo = ((smem_addr >> 4) & 0x3fff) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | ((uint32_t)sw << 29);
+  return d;
+}
+// byte_offset must be a multiple of 16
+__device__ __forceinline__ SmemDesc desc_advance(SmemDesc d, uint32_t byte_offset) { d.lo += byte_offset >> 4; return d; }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// A operand from tensor memory (fp16 packed two per 32-bit column: eight columns per K = 16 step)
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Instruction descriptor (32 bit).  c_format: 1 = f32, 2 = s32.  a/b format: kind::f16: 0 = f16,
 // 1 = bf16; kind::i8: 0 = u8, 1 = s8.  major: 0 = K-major, 1 = MN-major.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_format, uint32_t a_format, uint32_t b_format, uint32_t a_major,

@@ -80,7 +80,7 @@ def test_quamb2conv1d_forward_and_update_like_reference(batch, x_dim, d_state, n
     # without head / dim groups the reference takes ONE output scale for each of x, B and C (quamba2_conv1d.cpp:195-198)
     x_out_scale, B_out, C_out = ((t.abs().max() / 127).reshape(1).float() for t in (x_ref, B_ref, C_ref))
     q = M.Quamb2Conv1D.from_fp16(conv, x_dim, 64, d_state, n_groups, sx, sB, sC, x_out_scale, B_out, C_out, None, None)
-    qx, qB, qC = q(q_in.transpose(1, 2))
+    qx, qB, qC = (t.transpose(1, 2) for t in q(q_in.transpose(1, 2)))     # (b, dim, l) views -> (b, l, dim)
     assert r2(qx.float() * x_out_scale, x_ref) < 1e-3
     assert r2(qB.float() * B_out, B_ref) < 1e-3
     assert r2(qC.float() * C_out, C_ref) < 1e-3
@@ -196,11 +196,11 @@ def test_qhadamard_against_dense_matrix(dim):
     x = torch.randn(4, 37, dim, device=DEV).half()
     special = 12 if dim % 12 == 0 else (40 if dim % 40 == 0 else None)
     H = ohad.hadamard_matrix(dim, special).to(DEV)
-    y = (x.float() @ H.t()) / math.sqrt(dim)
+    y = ((x.double() @ H.double().t()) / math.sqrt(dim)).float()
     s = y.abs().max() / 127
     qh = M.QHadamard(dim, x_H_scale=s.item())
     y_ = qh(x).float() * s
-    assert r2(y_, y) < 1e-3 and (y_ - y).abs().max() <= 0.51 * s
+    assert r2(y_, y) < 1e-3 and (y_ - y).abs().max() <= 1.01 * s      # at most one quantisation step anywhere
 
 
 # ---- linears (test_qlinear.py) -----------------------------------------------------------------------------------
