@@ -1,7 +1,7 @@
 // Mamba2 SSD chunk scan on the Blackwell tensor cores (headdim 64, d_state 128).
 //
-// One CTA owns one (batch, head) pair and walks the sequence in blocks of T = 128 tokens, carrying
-// the 64 x 128 SSM state in registers (fp32), so nothing but inputs and outputs ever touches HBM:
+// The sequence of one (batch, head) pair is walked in blocks of T = 128 tokens with the 64 x 128 SSM state carried in
+// registers (fp32), so nothing but inputs and outputs ever touches HBM.  Per block:
 //
 //   CB    = C . B^T                         128 x 128 x 128   tcgen05 f16 (integer-valued operands: exact)
 //   D1    = C . s                           128 x  64 x 128   state entering the block, fp16 copy
@@ -9,28 +9,35 @@
 //   D2    = Lm . x                          128 x  64 x 128   Lm[m,k] = CB[m,k] 2^(a_m - a_k) dt_k, k <= m
 //   y[m,p]   = sC 2^(a_m) D1 + sx[p] (D2 + D x)            s <- 2^r s + sB sx[p] S_loc
 //
-// a_l is the running sum of dt*A*log2(e) inside the block and r its last value, so every exponent
-// is <= 0.  Two small preparation kernels run first: one widens B and C (shared by all heads of a
-// group) to fp16 once -- values stay the raw integers, scales are applied in the epilogues -- the
-// other evaluates softplus / the running sums and leaves, per (batch, head, block), the vectors
-// a[128], bk[128] = a - log2(dt) - log2(sC sB) and ec[128] (column factors of the off-diagonal
-// 32 x 32 chunks of Lm: there 2^(a_m - bk_k) = 2^(a_m - a_end(chunk)) * ec[k], two multiplies
-// instead of an ex2 per element; the diagonal chunks keep the exact per-element exponent).  When D
-// has one value per head it is added on the diagonal of Lm, so the output step needs no x.
-// Every CTA TMA-loads 128-byte-swizzled B / C tiles that serve as K-major operands (CB, D1) and as
-// the MN-major A operand of S_loc without any reshuffling, plus the 1.5 KB of vectors.  x is read
-// straight from global memory by the thread that converts it (int8 -> fp16 with integer / half
-// ALU ops only).
+// a_l is the running sum of dt*A*log2(e) inside the block and r its last value, so every exponent is <= 0.  Two small
+// preparation kernels run first: one widens B and C (shared by all heads of a group) to fp16 once -- values stay the
+// raw integers, scales are applied in the epilogues -- the other evaluates softplus / the running sums and leaves, per
+// (batch, head, block), the vectors a[128], bk[128] = a - log2(dt) - log2(sC sB) and ec[128] (column factors of the
+// off-diagonal 32 x 32 chunks of Lm: there 2^(a_m - bk_k) = 2^(a_m - a_end(chunk)) * ec[k], two multiplies instead of
+// an ex2 per element; the diagonal chunks keep the exact per-element exponent).  When D has one value per head it is
+// added on the diagonal of Lm, so the output step needs no x.
 //
-// 640 threads: warp 0 issues TMA, warp 1 issues the MMAs and owns TMEM; warps 4..11 (group A) turn
-// CB(j) into the Lm tile; warps 12..19 (group B) write the x operands of block k, then the output
-// of block k - 1 (accumulators -> registers -> 4 x 4 shuffle transpose -> 64-byte row pieces straight
-// to global memory), then fold S_loc(k) into the state they keep in registers.  TMEM (512 columns):
-// CB and D1 double-buffered, D2, S.  Every barrier is waited on by each of its consumers once per
-// phase and in order, no phase can complete twice before a consumer has looked at it, and all waits
-// are bounded.  Two lessons are built into the code: setmaxnreg.inc blocks without a time limit when
-// the pool is short (the 40 / 64 / 152 split leaves room for the allocation granularity), and the
-// B / C stage is handed back to the TMA producer only at the end of an iteration (see below).
+// The kernel is persistent: one CTA per SM, and the (batch, head, block) list is cut into equal contiguous ranges, one
+// per CTA, so that the SMs finish together whatever the number of pairs (320 pairs on 148 SMs would otherwise run as
+// three waves of which the last is 16 % full).  A range covers the tail of one pair, whole pairs, and the head of
+// another.  A CTA runs the head part FIRST (it depends on nothing) and hands the fp32 state after it to the next CTA
+// through global memory (release / acquire on a flag); it runs its own tail part LAST, by which time the previous CTA
+// has long published the state it needs.  A head part never waits, so the scheme cannot deadlock; the wait is bounded
+// all the same.  The arithmetic per pair is the same sequence of operations wherever the cut falls, so results do not
+// depend on the number of SMs.
+//
+// 640 threads: warp 0 issues TMA (128-byte-swizzled B / C tiles that serve as K-major operands of CB and D1 and as the
+// MN-major A operand of S_loc without reshuffling, plus the 1.5 KB of vectors), warp 1 issues the MMAs and owns TMEM,
+// warps 4..19 compute.  All 16 compute warps walk the same four phases per block, a thread owning one row (TMEM lane)
+// and one quarter of the columns:
+//   P1  x(k) -> fp16 operands (raw, and scaled by w) in shared memory            -> GEMM4(k) = S_loc
+//   P2  CB(k) -> Lm(k), written back to tensor memory as packed fp16 (A operand)  -> GEMM3(k) = D2, then CB(k+1)
+//   P3  state update from S_loc(k), fp16 copy of the state to shared memory      -> GEMM2(k+1) = D1
+//   P4  y(k) from D2(k), D1(k): straight to global memory
+// so every GEMM runs while the compute warps are busy with the next phase, and program order plus one group barrier
+// per phase is what frees each buffer (noted at each wait).  Every mbarrier completes exactly once per block, is waited
+// on by each consumer once per phase and in order, and all waits are bounded.  The B / C stage is handed back to the
+// TMA producer only at the end of an MMA iteration.
 #include "tc_common.cuh"
 
 namespace qb {
@@ -42,54 +49,84 @@ __device__ long long g_trace[2][64][16];
 #define TRACE(role, j, slot) do { } while (0)
 #endif
 
-#ifdef QB_DUMP
-__device__ float* g_dump = nullptr;
-#endif
-
 namespace {
 using namespace tc;
 
 constexpr int T = 128, P = 64, N = 128;
-// Warpgroup 0 (warps 0..3): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..3 idle.
-// Warpgroups 1..2 (warps 4..11) = compute group A, warpgroups 3..4 (warps 12..19) = compute group B.
-// Registers are rebalanced between the warpgroups with setmaxnreg (the kernel launches at 96 per thread).
+// Warps 0..3: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..3 idle.  Warps 4..19 compute.
 constexpr int kThreads = 640;
 constexpr int kLead = 128;                     // first compute thread
-constexpr int kRegsCtl = 40, kRegsA = 64, kRegsB = 152;
+constexpr int kCompute = kThreads - kLead;     // 512
 
 constexpr int kAtom = T * 128;                 // 16 KB: 128 rows x 128 bytes
 constexpr int kOffB16 = 0;                     // 2 stages x 2 atoms
 constexpr int kOffC16 = 4 * kAtom;             // 2 stages x 2 atoms
-constexpr int kOffLm = 8 * kAtom;              // 2 atoms, unused since Lm lives in tensor memory (kept: tile offsets unchanged)
-constexpr int kOffXraw = 10 * kAtom;           // 1 atom
-constexpr int kOffXw = 11 * kAtom;             // 1 atom
-constexpr int kOffS16 = 12 * kAtom;            // 1 atom
-constexpr int kOffMisc = 13 * kAtom;           // vectors + barriers
+constexpr int kOffXraw = 8 * kAtom;            // 1 atom
+constexpr int kOffXw = 9 * kAtom;              // 1 atom
+constexpr int kOffS16 = 10 * kAtom;            // 1 atom
+constexpr int kOffMisc = 11 * kAtom;           // vectors + barriers
 constexpr int kMiscBytes = 4096;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;
 constexpr int kAbVecs = 3;                     // a[128], bk[128], ec[128] per block, fp32
 constexpr int kAbBytes = kAbVecs * T * 4;
+constexpr int kHandoffFloats = kCompute * 16;  // one fp32 state (64 x 128) per CTA, thread-major
 
-// CB is double-buffered (block j in buffer j & 1) so that C.B^T of the next block is computed while the Lm tile of the
-// current one is still being built from the other buffer.
-// D1 (the carried-in term C S_prev) is double-buffered as well: GEMM2(j) only needs the state of block j - 1, so it is
-// issued while the x operands of block j are still being prepared and the tensor pipe would otherwise idle.
-constexpr uint32_t kColCB = 0, kColD1 = 128, kColD2 = 192, kColS = 256, kColCB1 = 320, kColD1b = 448, kTmemCols = 512;
+// Tensor memory: CB (fp32), Lm (packed fp16, 64 columns), D2, S, and D1 double-buffered (GEMM2(k+1) is issued while the
+// output step of block k still has D1(k) to read).
+constexpr uint32_t kColCB = 0, kColLm = 128, kColD2 = 192, kColS = 256, kColD1 = 320, kColD1b = 384, kTmemCols = 512;
 
 struct Misc {
-  // per stage: a (inclusive running sum of dt*A*log2e), bk (+inf where dt == 0), ec (column factor of the off-diagonal
-  // 32 x 32 chunks of Lm, see ssd_dt_kernel).  Both compute groups release a
-  // stage right after their last read of it (group B copies what it needs into registers at the top of a block).
-  float ab[2][kAbVecs * T];
-  float sx[P];         // x scale per channel
-  float dsx[P];        // D * sx per channel
-  float sbx[P];        // sB * sx per channel
-  float dfold;         // D of this head when it is one value per head (added on the diagonal of Lm), else 0
+  float ab[2][kAbVecs * T];   // per stage: a, bk, ec of the block (see ssd_dt_kernel)
+  float sx[P];                // x scale per channel
+  float dsx[P];               // D * sx per channel
+  float sbx[P];               // sB * sx per channel
+  float dfold;                // D of this head when it is one value per head (added on the diagonal of Lm), else 0
   uint64_t bc_full[2], bc_empty[2], ab_empty[2];
-  uint64_t cb_ready[2], s_ready, y_ready, d1_ready, xops_ready, lm_ready, s16_ready, y_free;  // cb_ready / s_ready: one per TMEM buffer
+  uint64_t cb_ready, xops_ready, s_ready, lm_ready, y_ready, s16_ready, d1_ready;
   uint32_t tmem_slot;
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc does not fit");
+
+// The work of one CTA: blocks [s, e) of the list (pair-major, block-minor), as up to three kinds of item.
+struct Plan {
+  int n_items;      // head part + whole pairs + tail part
+  int total;        // blocks in all items
+  int head_unit, head_len;     // head part: blocks [0, head_len) of head_unit (0 = none); runs first, publishes its state
+  int whole_first, n_whole;    // whole pairs (strided by whole_step)
+  int whole_step;
+  int tail_unit, tail_from;    // tail part: blocks [tail_from, nb) of tail_unit (tail_from = 0: none); runs last
+};
+struct Item { int unit, jb, je; bool has_init, publish; };
+
+__device__ __forceinline__ Plan make_plan(int cta, int grid, int units, int nb, int split) {
+  Plan p;
+  if (!split) {   // whole pairs only, round robin
+    p.head_len = 0; p.tail_from = 0; p.head_unit = p.tail_unit = 0;
+    p.whole_first = cta; p.whole_step = grid;
+    p.n_whole = cta < units ? (units - cta + grid - 1) / grid : 0;
+  } else {
+    const long long tb = (long long)units * nb;
+    const long long s = tb * cta / grid, e = tb * (cta + 1) / grid;
+    const int us = (int)(s / nb), js = (int)(s % nb), ue = (int)(e / nb), je = (int)(e % nb);
+    p.tail_unit = us; p.tail_from = js;
+    p.head_unit = ue; p.head_len = je;
+    p.whole_first = js != 0 ? us + 1 : us; p.whole_step = 1;
+    p.n_whole = ue - p.whole_first;   // >= 0 because a range is at least nb blocks long
+  }
+  p.n_items = p.n_whole + (p.head_len != 0) + (p.tail_from != 0);
+  p.total = p.n_whole * nb + p.head_len + (p.tail_from != 0 ? nb - p.tail_from : 0);
+  return p;
+}
+__device__ __forceinline__ Item get_item(const Plan& p, int idx, int nb) {
+  Item im;
+  if (p.head_len != 0) {
+    if (idx == 0) { im.unit = p.head_unit; im.jb = 0; im.je = p.head_len; im.has_init = false; im.publish = true; return im; }
+    --idx;
+  }
+  if (idx < p.n_whole) { im.unit = p.whole_first + idx * p.whole_step; im.jb = 0; im.je = nb; im.has_init = false; im.publish = false; return im; }
+  im.unit = p.tail_unit; im.jb = p.tail_from; im.je = nb; im.has_init = true; im.publish = false;
+  return im;
+}
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -97,8 +134,6 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
-template <int R> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R)); }
-template <int R> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R)); }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -144,25 +179,10 @@ __device__ __forceinline__ uint4 ldg_nc_now(const void* p) {
 }
 __device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<const uint32_t*>(&v); }
 
-// 4 x 4 transpose of 16-byte pieces across the four lanes of a quad (lanes 4q .. 4q + 3): on entry lane i holds the
-// pieces c[0..3] of "its" row; on exit lane i holds piece i of the rows of lanes 4q + 0 .. 4q + 3, in c[0..3].
 __device__ __forceinline__ uint4 shfl_xor_u4(uint4 v, int m) {
   v.x = __shfl_xor_sync(0xffffffffu, v.x, m); v.y = __shfl_xor_sync(0xffffffffu, v.y, m);
   v.z = __shfl_xor_sync(0xffffffffu, v.z, m); v.w = __shfl_xor_sync(0xffffffffu, v.w, m);
   return v;
-}
-__device__ __forceinline__ void quad_transpose(uint4 (&c)[4], int lane) {
-  const bool odd = (lane & 1) != 0, hi = (lane & 2) != 0;
-  {
-    const uint4 r0 = shfl_xor_u4(odd ? c[0] : c[1], 1);
-    const uint4 r1 = shfl_xor_u4(odd ? c[2] : c[3], 1);
-    if (odd) { c[0] = r0; c[2] = r1; } else { c[1] = r0; c[3] = r1; }
-  }
-  {
-    const uint4 r0 = shfl_xor_u4(hi ? c[0] : c[2], 2);
-    const uint4 r1 = shfl_xor_u4(hi ? c[1] : c[3], 2);
-    if (hi) { c[0] = r0; c[1] = r1; } else { c[2] = r0; c[3] = r1; }
-  }
 }
 
 // One K = 128 contraction as eight K = 16 instructions.  The descriptors come in as two 32-bit words each and a K step
@@ -182,22 +202,19 @@ __device__ __forceinline__ void issue_gemm(uint32_t d_tmem, SmemDesc a, SmemDesc
 
 __global__ void __launch_bounds__(kThreads, 1)
 ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant__ CUtensorMap tm_c16, qb_ssd_args a,
-              const float* __restrict__ ab_ws, int* status) {
+              const float* __restrict__ ab_ws, float* __restrict__ handoff, int* __restrict__ flags, int split, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Misc& ms = *reinterpret_cast<Misc*>(smem + kOffMisc);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x / a.nheads, h = blockIdx.x % a.nheads;
   const int hpg = a.nheads / a.ngroups;
-  const int g = h / hpg;
   const int nb = (a.seqlen + T - 1) / T;
-  const float sB = a.grouped ? a.B_scale[g] : a.B_scale[0];
-  const float sC = a.grouped ? a.C_scale[g] : a.C_scale[0];
+  const Plan plan = make_plan((int)blockIdx.x, (int)gridDim.x, a.batch * a.nheads, nb, split);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 2); }
-    mbar_init(&ms.cb_ready[0], 1); mbar_init(&ms.cb_ready[1], 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.y_ready, 1); mbar_init(&ms.d1_ready, 1);
-    mbar_init(&ms.xops_ready, 1); mbar_init(&ms.lm_ready, 1); mbar_init(&ms.s16_ready, 1); mbar_init(&ms.y_free, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 1); }
+    mbar_init(&ms.cb_ready, 1); mbar_init(&ms.xops_ready, 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.lm_ready, 1);
+    mbar_init(&ms.y_ready, 1); mbar_init(&ms.s16_ready, 1); mbar_init(&ms.d1_ready, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_b16);
     prefetch_tensormap(&tm_c16);
@@ -206,53 +223,41 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     tmem_alloc(&ms.tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  if (threadIdx.x >= kLead && threadIdx.x < kLead + P) {
-    const int p = threadIdx.x - kLead;
-    float sx;
-    if (!a.grouped) {
-      sx = a.x_scales[0];
-    } else {
-      const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
-      const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
-      sx = a.x_scales[(g * a.nhead_groups + hg) * a.ndim_groups + dg];
-    }
-    float dv = 0.0f;
-    if (a.D != nullptr) dv = (*a.D_scale) * (float)(a.D_has_hdim ? a.D[h * P + p] : a.D[h]);
-    ms.sx[p] = sx;
-    ms.dsx[p] = dv * sx;
-    ms.sbx[p] = sB * sx;
-    if (p == 0) ms.dfold = (a.D != nullptr && !a.D_has_hdim) ? (*a.D_scale) * (float)a.D[h] : 0.0f;
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ms.tmem_slot;
 
-  if (warp < 4) reg_dec<kRegsCtl>();
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const float* ab_src = ab_ws + ((int64_t)b * a.nheads + h) * nb * (kAbVecs * T);
-      for (int j = 0; j < nb; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait(&ms.bc_empty[st], par, status, QB_ERR_TIMEOUT)) break;
-        if (!mbar_wait(&ms.ab_empty[st], par, status, QB_ERR_TIMEOUT)) break;
-        mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes);
-        uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
-        uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
-        bulk_load(ms.ab[st], ab_src + (int64_t)j * (kAbVecs * T), kAbBytes, &ms.bc_full[st]);
-        tma_load_4d(dB, &tm_b16, &ms.bc_full[st], 0, g, j * T, b);
-        tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, j * T, b);
-        tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, j * T, b);
-        tma_load_4d(dC + kAtom, &tm_c16, &ms.bc_full[st], 64, g, j * T, b);
+      int it = 0;
+      bool ok = true;
+      for (int ii = 0; ii < plan.n_items && ok; ++ii) {
+        const Item im = get_item(plan, ii, nb);
+        const int b = im.unit / a.nheads, h = im.unit % a.nheads, g = h / hpg;
+        const float* ab_src = ab_ws + (int64_t)im.unit * nb * (kAbVecs * T);
+        for (int j = im.jb; j < im.je; ++j, ++it) {
+          const int st = it & 1;
+          const uint32_t par = ((it >> 1) & 1) ^ 1;
+          ok = mbar_wait(&ms.bc_empty[st], par, status, QB_ERR_TIMEOUT) && mbar_wait(&ms.ab_empty[st], par, status, QB_ERR_TIMEOUT);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes);
+          uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
+          uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
+          bulk_load(ms.ab[st], ab_src + (int64_t)j * (kAbVecs * T), kAbBytes, &ms.bc_full[st]);
+          tma_load_4d(dB, &tm_b16, &ms.bc_full[st], 0, g, j * T, b);
+          tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, j * T, b);
+          tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, j * T, b);
+          tma_load_4d(dC + kAtom, &tm_c16, &ms.bc_full[st], 64, g, j * T, b);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    if (lane == 0 && plan.total > 0) {
       constexpr uint32_t id_cb = make_idesc(1, 0, 0, 0, 0, 128, 128);  // C (K-major) x B (K-major)
-      constexpr uint32_t id_kn = make_idesc(1, 0, 0, 0, 1, 128, 64);   // K-major A x MN-major B
+      constexpr uint32_t id_kn = make_idesc(1, 0, 0, 0, 1, 128, 64);   // K-major (or tensor-memory) A x MN-major B
       constexpr uint32_t id_mn = make_idesc(1, 0, 0, 1, 1, 128, 64);   // MN-major A x MN-major B
       // descriptor words of every operand tile, built once (stage 1 of B / C is 2 atoms further)
       const SmemDesc dBk = make_smem_desc2(smem_u32(smem + kOffB16), 16, 1024, kSwizzle128B);      // B, K-major (CB)
@@ -265,154 +270,230 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       if (ok) {
         tc_fence_after_sync();
         issue_gemm<false, false>(tmem + kColCB, dCk, dBk, id_cb);
-        umma_commit(&ms.cb_ready[0]);
+        umma_commit(&ms.cb_ready);
       }
-      for (int j = 0; j < nb && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = j & 1;
-        const SmemDesc bBm = desc_advance(dBm, st * 2 * kAtom), bC = desc_advance(dCk, st * 2 * kAtom);
-        if (j > 0) {
-          // GEMM2(j): D1[j & 1] = C(j) S_prev.  Needs the fp16 state of block j - 1; the buffer was last read by the
-          // output step of block j - 2, whose y_free this thread observed before GEMM3(j - 1).  s16_ready also says that
-          // the state update of block j - 1 has read the S accumulator, which GEMM4(j) overwrites below.
-          ok = mbar_wait(&ms.s16_ready, (j - 1) & 1, status, QB_ERR_TIMEOUT);
+      int it = 0;
+      for (int ii = 0; ii < plan.n_items && ok; ++ii) {
+        const Item im = get_item(plan, ii, nb);
+        for (int j = im.jb; j < im.je; ++j, ++it) {
+          const int st = it & 1;
+          const uint32_t ph = it & 1;
+          const bool use_d1 = j > im.jb || im.has_init;
+          // GEMM2(it): D1[it & 1] = C(it) S_prev.  s16_ready says that the fp16 state entering this block is in shared
+          // memory (nothing to multiply when a pair starts from the zero state), that the compute warps have read the
+          // S accumulator of the previous block (GEMM4 below overwrites it) and, by program order, D1[it & 1] of two
+          // blocks ago.
+          ok = mbar_wait(&ms.s16_ready, ph, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          TRACE(1, j, 0);
-          issue_gemm<false, true>(tmem + (st ? kColD1b : kColD1), bC, dS16, id_kn);
-          umma_commit(&ms.d1_ready);   // the state tile may be rewritten once this has fired
-        }
-        // GEMM4(j): local state of the block, S = (x w)^T B
-        ok = mbar_wait(&ms.xops_ready, ph, status, QB_ERR_TIMEOUT);
-        if (!ok) break;
-        tc_fence_after_sync();
-        TRACE(1, j, 1);
-        issue_gemm<true, true>(tmem + kColS, bBm, dXw, id_mn);
-        umma_commit(&ms.s_ready);
-        // GEMM3(j) overwrites D2: the output step of block j - 1 must have loaded it
-        if (j > 0) {
-          ok = mbar_wait(&ms.y_free, (j - 1) & 1, status, QB_ERR_TIMEOUT);
+          TRACE(1, it, 0);
+          if (use_d1) issue_gemm<false, true>(tmem + (st ? kColD1b : kColD1), desc_advance(dCk, st * 2 * kAtom), dS16, id_kn);
+          umma_commit(&ms.d1_ready);   // the fp16 state tile may be rewritten once this has fired
+          // GEMM4(it): local state of the block, S = B^T (x w)
+          ok = mbar_wait(&ms.xops_ready, ph, status, QB_ERR_TIMEOUT);
           if (!ok) break;
-        }
-        // GEMM3(j): D2 = Lm X
-        ok = mbar_wait(&ms.lm_ready, ph, status, QB_ERR_TIMEOUT);
-        if (!ok) break;
-        tc_fence_after_sync();
-        TRACE(1, j, 2);
-        {
-          const uint32_t lm = tmem + (st ? kColCB1 : kColCB);   // packed fp16 Lm, 8 columns per K = 16 step
+          tc_fence_after_sync();
+          TRACE(1, it, 1);
+          issue_gemm<true, true>(tmem + kColS, desc_advance(dBm, st * 2 * kAtom), dXw, id_mn);
+          umma_commit(&ms.s_ready);
+          // GEMM3(it): D2 = Lm X, Lm from tensor memory.  lm_ready also says (program order of the compute warps) that
+          // the output step of the previous block has read D2.
+          ok = mbar_wait(&ms.lm_ready, ph, status, QB_ERR_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after_sync();
+          TRACE(1, it, 2);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_f16_ta(tmem + kColD2, lm + ks * 8, desc_advance(dXraw, ks * 2048), id_kn, ks != 0 ? 1u : 0u);
+            umma_f16_ta(tmem + kColD2, tmem + kColLm + ks * 8, desc_advance(dXraw, ks * 2048), id_kn, ks != 0 ? 1u : 0u);
+          umma_commit(&ms.y_ready);
+          TRACE(1, it, 3);
+          if (it + 1 < plan.total) {
+            // C.B^T of the next block (of this pair or the next one): the compute warps have finished reading CB(it)
+            const int sn = (it + 1) & 1;
+            ok = mbar_wait(&ms.bc_full[sn], ((it + 1) >> 1) & 1, status, QB_ERR_TIMEOUT);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_gemm<false, false>(tmem + kColCB, desc_advance(dCk, sn * 2 * kAtom), desc_advance(dBk, sn * 2 * kAtom), id_cb);
+            umma_commit(&ms.cb_ready);
+          }
+          // Release the B/C stage of this block last.  Its readers were CB(it), GEMM2(it) and GEMM4(it); releasing it
+          // earlier let the refill run concurrently with the remaining MMAs of the block, and with that timing results
+          // were not reproducible from run to run.  The refill has a whole block of slack, so nothing is lost here.
+          umma_commit(&ms.bc_empty[st]);
         }
-        umma_commit(&ms.y_ready);
-        TRACE(1, j, 3);
-        if (j + 1 < nb) {
-          // C.B^T of the next block into the other CB buffer (group A released it when it signalled lm_ready(j - 1)).
-          // Issued after GEMM3(j) on purpose: it then runs while group B prepares the x operands of block j + 1 and the
-          // tensor pipe would otherwise idle; ahead of GEMM3(j) it only delays the output of block j.
-          const int sn = (j + 1) & 1;
-          ok = mbar_wait(&ms.bc_full[sn], ((j + 1) >> 1) & 1, status, QB_ERR_TIMEOUT);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_gemm<false, false>(tmem + (sn ? kColCB1 : kColCB), desc_advance(dCk, sn * 2 * kAtom), desc_advance(dBk, sn * 2 * kAtom), id_cb);
-          umma_commit(&ms.cb_ready[sn]);
-        }
-        // Release the B/C stage of block j last.  Its readers were CB(j), GEMM4(j) and GEMM2(j); releasing it right
-        // after GEMM2(j) let the refill for block j + 2 run concurrently with GEMM3(j), and with that timing results
-        // were not reproducible from run to run.  The refill has a whole block of slack, so nothing is lost here.
-        umma_commit(&ms.bc_empty[st]);
       }
     }
   } else if (warp >= 4) {
     // ---------------- compute warps ----------------
-    // Two groups of eight warps run concurrently on different parts of the pipeline:
-    //   group A (warps 4..11)  builds Lm for block j as soon as CB(j) is ready and GEMM3(j-1) has released the tile;
-    //   group B (warps 12..19) per step k: x operands of block k, output of block k - 1, state of block k.
-    // Inside a group a thread owns one row (TMEM lane) and one half of the columns.
     const int cw = warp - 4;
-    const int grp = cw >> 3;           // 0 = A, 1 = B
     const int q = warp & 3;            // TMEM lane quarter this warp may touch
-    const int hsel = (cw >> 2) & 1;    // column half
+    const int sub = cw >> 2;           // quarter of the columns: channels 16 sub .. 16 sub + 15, chunk sub of Lm
     const int row = q * 32 + lane;
+    const int ctid = threadIdx.x - kLead;
     const uint32_t tlane = (uint32_t)(q * 32) << 16;
     const int sw = row & 7;
-    const bool lead = (threadIdx.x == kLead + grp * 256);
-    auto gsync = [&]() {
-      if (grp == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-      else asm volatile("bar.sync 2, 256;" ::: "memory");
-    };
-    // One thread of the group polls the mbarrier, the others park at the group's hardware barrier, which
-    // also ANDs the outcome so that a timed-out wait makes the whole group leave its loop together.
-    auto gwait = [&](uint64_t* bar, uint32_t parity) -> bool {
-      uint32_t ok = 1;
-      if (lead) ok = mbar_wait(bar, parity, status, QB_ERR_TIMEOUT) ? 1u : 0u;
+    const bool lead = (threadIdx.x == kLead);
+    auto gsync = [&]() { asm volatile("bar.sync 1, 512;" ::: "memory"); };
+    auto gand = [&](uint32_t ok) -> bool {   // group barrier that ANDs a flag: a timed-out wait makes all warps leave together
       uint32_t r;
-      if (grp == 0)
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                     : "=r"(r) : "r"(ok) : "memory");
-      else
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                     : "=r"(r) : "r"(ok) : "memory");
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 512, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                   : "=r"(r) : "r"(ok) : "memory");
       return r != 0;
     };
-
-    // Several mbarriers, one group barrier: the lead thread waits for each in turn.
-    auto gwait3 = [&](uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2) -> bool {
+    // One thread polls the mbarrier(s), the others park at the group's hardware barrier.
+    auto gwait = [&](uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1) -> bool {
       uint32_t ok = 1;
       if (lead) {
         ok = mbar_wait(b0, p0, status, QB_ERR_TIMEOUT) ? 1u : 0u;
         if (ok && b1 != nullptr) ok = mbar_wait(b1, p1, status, QB_ERR_TIMEOUT) ? 1u : 0u;
-        if (ok && b2 != nullptr) ok = mbar_wait(b2, p2, status, QB_ERR_TIMEOUT) ? 1u : 0u;
       }
-      uint32_t r;
-      if (grp == 0)
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                     : "=r"(r) : "r"(ok) : "memory");
-      else
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                     : "=r"(r) : "r"(ok) : "memory");
-      return r != 0;
+      return gand(ok);
     };
-
-    if (grp == 0) {
-      reg_dec<kRegsA>();
-      // ================= group A: Lm[t, s] = CB[t, s] 2^(a_t - bk_s) for s <= t (+ D on the diagonal) =================
+    float s_reg[16];
+    auto store_s16 = [&]() {   // fp16 copy of this thread's 16 state values: row n, channels 16 sub .. (MN-major B of GEMM2)
+      uint8_t* dst = smem + kOffS16 + row * 128;
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        *reinterpret_cast<uint4*>(dst + (((2 * sub + u) ^ sw) << 4)) =
+            make_uint4(pack_h2(s_reg[8 * u], s_reg[8 * u + 1]), pack_h2(s_reg[8 * u + 2], s_reg[8 * u + 3]),
+                       pack_h2(s_reg[8 * u + 4], s_reg[8 * u + 5]), pack_h2(s_reg[8 * u + 6], s_reg[8 * u + 7]));
+    };
+    const bool d_per_channel = a.D != nullptr && a.D_has_hdim;   // then the skip term is added in the output step
+    const int64_t out_pitch = (int64_t)a.nheads * P;
+    int it = 0;
+    bool ok = true;
+    for (int ii = 0; ii < plan.n_items && ok; ++ii) {
+      const Item im = get_item(plan, ii, nb);
+      const int b = im.unit / a.nheads, h = im.unit % a.nheads, g = h / hpg;
+      const float sB = a.grouped ? a.B_scale[g] : a.B_scale[0];
+      const float sC = a.grouped ? a.C_scale[g] : a.C_scale[0];
+      const float lscb = fast_log2(sC * sB);
+      const int8_t* xrow_base = a.x + (int64_t)b * a.x_sb + (int64_t)h * a.x_sh + 16 * sub;
+      __half* out_base = static_cast<__half*>(a.out) + ((int64_t)b * a.seqlen * a.nheads + h) * P + 16 * sub;
+      // the x row of the first block: requested before anything else of this item
+      uint4 xn = make_uint4(0, 0, 0, 0);
+      if (im.jb * T + row < a.seqlen) xn = ldg_nc_now(xrow_base + (int64_t)(im.jb * T + row) * a.x_sl);
+      gsync();   // every warp is past its last read of the per-head vectors of the previous item
+      if (ctid < P) {
+        const int p = ctid;
+        float sx;
+        if (!a.grouped) {
+          sx = a.x_scales[0];
+        } else {
+          const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
+          const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
+          sx = a.x_scales[(g * a.nhead_groups + hg) * a.ndim_groups + dg];
+        }
+        float dv = 0.0f;
+        if (a.D != nullptr) dv = (*a.D_scale) * (float)(a.D_has_hdim ? a.D[h * P + p] : a.D[h]);
+        ms.sx[p] = sx;
+        ms.dsx[p] = dv * sx;
+        ms.sbx[p] = sB * sx;
+        if (p == 0) ms.dfold = (a.D != nullptr && !a.D_has_hdim) ? (*a.D_scale) * (float)a.D[h] : 0.0f;
+      }
+      if (im.has_init) {
+        // the state after the head part of this pair, published by the previous CTA early in its life
+        uint32_t got = 1;
+        if (lead) {
+          const long long t0 = clock64();
+          for (;;) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + blockIdx.x) : "memory");
+            if (v != 0) break;
+            __nanosleep(256);
+            if (clock64() - t0 > kWaitBudgetCycles) { atomicCAS(status, 0, QB_ERR_TIMEOUT); got = 0; break; }
+          }
+        }
+        ok = gand(got);
+        if (!ok) break;
+        const float4* src = reinterpret_cast<const float4*>(handoff + (int64_t)blockIdx.x * kHandoffFloats);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float4 f = __ldcg(src + v * kCompute + ctid);
+          s_reg[4 * v] = f.x; s_reg[4 * v + 1] = f.y; s_reg[4 * v + 2] = f.z; s_reg[4 * v + 3] = f.w;
+        }
+        store_s16();   // GEMM2 of the previous block has completed: the state step that followed it waited for d1_ready
+        fence_proxy_async_smem();
+      } else {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) s_reg[t] = 0.0f;
+      }
+      gsync();
+      if (lead) mbar_arrive(&ms.s16_ready);
       const float dfold = ms.dfold;
-      for (int j = 0; j < nb; ++j) {
-        const int st = j & 1;
-        // the vectors of this block have landed and CB(j) is in TMEM buffer j & 1.  Lm(j) overwrites that buffer, which
-        // GEMM3(j - 2) read long before CB(j) was issued into it, so nothing else has to be waited for.
-        if (!gwait3(&ms.bc_full[st], (j >> 1) & 1, &ms.cb_ready[st], (j >> 1) & 1, nullptr, 0)) break;
-        tc_fence_after_sync();
-        if (lead) TRACE(0, j, 3);
+
+      for (int j = im.jb; j < im.je; ++j, ++it) {
+        const int st = it & 1;
+        const uint32_t ph = it & 1;
+        const bool use_d1 = j > im.jb || im.has_init;
+        const int l = j * T + row;
+        // ================= P1: x(j) -> fp16 operands: raw, and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) =====
+        // (0 where dt_l = 0).  Both tiles are free: the state step of the previous block waited for GEMM4 and its
+        // output step for GEMM3.
+        const uint4 xq = xn;
+        if (j + 1 < im.je && l + T < a.seqlen) xn = ldg_nc_now(xrow_base + (int64_t)(l + T) * a.x_sl);   // a block of work covers its latency
+        else xn = make_uint4(0, 0, 0, 0);
+        if (lead) TRACE(0, it, 0);
+        uint4 xr[2];
+        {
+          const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            __half2 r0, r1, r2, r3;
+            s8x4_to_h2x2(xwd[2 * c], r0, r1);
+            s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
+            xr[c] = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
+          }
+        }
+        ok = gwait(&ms.bc_full[st], (it >> 1) & 1, nullptr, 0);   // the vectors of this block have landed
+        if (!ok) break;
+        if (lead) TRACE(0, it, 1);
         const float* av = ms.ab[st];
-        const float* bkv = av + T;
         const float a_row = av[row];
-        // Lm goes back into tensor memory, packed fp16, over the first 64 columns of the CB buffer it is computed from,
-        // and GEMM3 reads it from there as its A operand: 32 KB of shared-memory stores and 32 KB of MMA operand reads
-        // per block never happen.  Chunk c (fp32 columns 32c .. 32c + 31) becomes columns 16c .. 16c + 15.  The first
-        // pass (chunks 0 and 1) writes columns 0 .. 31, which hold chunk 0's fp32 data, so a group barrier separates the
-        // loads of that pass from its stores; the second pass (chunks 2, 3) writes columns 32 .. 63 = chunk 1's data,
-        // consumed in the first pass.
-        const uint32_t cbcol = tmem + tlane + ((j & 1) ? kColCB1 : kColCB);
-#pragma unroll 1
-        for (int i = 0; i < 2; ++i) {
-          const int c = hsel + 2 * i;  // 32-column chunk of k
+        const float r_tot = av[T - 1];
+        const float e_out = use_d1 ? sC * fast_exp2(a_row) : 0.0f;   // weight of the carried-in term in the output
+        {
+          const __half2 w2 = __float2half2_rn(fast_exp2(r_tot - av[T + row] - lscb));
+          uint8_t* rowp_raw = smem + kOffXraw + row * 128;
+          uint8_t* rowp_w = smem + kOffXw + row * 128;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int chunk = ((2 * sub + c) ^ sw) << 4;
+            const uint4 v = xr[c];
+            *reinterpret_cast<uint4*>(rowp_raw + chunk) = v;
+            *reinterpret_cast<uint4*>(rowp_w + chunk) =
+                make_uint4(h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.x), w2)),
+                           h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.y), w2)),
+                           h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.z), w2)),
+                           h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.w), w2)));
+          }
+        }
+        fence_proxy_async_smem();
+        gsync();
+        if (lead) { mbar_arrive(&ms.xops_ready); TRACE(0, it, 2); }
+
+        // ================= P2: Lm[t, s] = CB[t, s] 2^(a_t - bk_s) for s <= t (+ D on the diagonal), chunk sub =============
+        // Written as packed fp16 into its own tensor-memory columns, which GEMM3 of the previous block has finished
+        // reading (its output step waited for y_ready).
+        ok = gwait(&ms.cb_ready, ph, nullptr, 0);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lead) TRACE(0, it, 3);
+        {
+          const int c = sub;
           uint32_t o[16];
           if (c > q) {  // entirely above the diagonal for every row of this warp
 #pragma unroll
             for (int u = 0; u < 16; ++u) o[u] = 0u;
-            if (i == 0) { gsync(); tc_fence_after_sync(); }
           } else {
             uint32_t cb[32];
-            tmem_ld_32x32(cbcol + 32 * c, cb);
+            tmem_ld_32x32(tmem + tlane + kColCB + 32 * c, cb);
             if (c == q) {
               // diagonal chunk: exact exponent per element, the k <= m mask (k - 32c <= lane), and the skip weight D
               // on the diagonal itself (y = sx (Lm + D I) x) when D has one value per head
+              const float* bkv = av + T + 32 * c;
               tmem_ld_wait();
-              if (i == 0) { tc_fence_before_sync(); gsync(); tc_fence_after_sync(); }
-              const float4* bk4 = reinterpret_cast<const float4*>(bkv + 32 * c);
+              const float4* bk4 = reinterpret_cast<const float4*>(bkv);
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
                 const float4 bb = bk4[u];
@@ -432,7 +513,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
               // chunk below the diagonal: 2^(a_t - bk_s) = 2^(a_t - m) * ec[s], m = a at the end of chunk c
               const float e_row = fast_exp2(a_row - av[32 * c + 31]);
               tmem_ld_wait();
-              if (i == 0) { tc_fence_before_sync(); gsync(); tc_fence_after_sync(); }
               const float4* ec4 = reinterpret_cast<const float4*>(av + 2 * T + 32 * c);
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
@@ -447,200 +527,130 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
               }
             }
           }
-          tmem_st16(cbcol + 16 * c, o);
+          tmem_st16(tmem + tlane + kColLm + 16 * c, o);
         }
         tmem_st_wait();
         tc_fence_before_sync();
         gsync();
-        if (lead) { mbar_arrive(&ms.lm_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(0, j, 4); }
-      }
-    } else {
-      reg_inc<kRegsB>();
-      // ================= group B: x operands of block k, output of block k - 1, state of block k =================
-      const float lscb = fast_log2(sC * sB);
-      const bool d_per_channel = a.D != nullptr && a.D_has_hdim;   // then the skip term is added here, from a re-read of x
-      const int8_t* xrow_base = a.x + (int64_t)b * a.x_sb + (int64_t)h * a.x_sh + 32 * hsel;
-      __half* out_base = static_cast<__half*>(a.out) + ((int64_t)b * a.seqlen * a.nheads + h) * P + 32 * hsel + 8 * (lane & 3);
-      const int64_t out_pitch = (int64_t)a.nheads * P;
-      float s_reg[32];
-#pragma unroll
-      for (int t = 0; t < 32; ++t) s_reg[t] = 0.0f;
-      uint4 xn0 = make_uint4(0, 0, 0, 0), xn1 = make_uint4(0, 0, 0, 0);
-      if (row < a.seqlen) {
-        const uint4* src = reinterpret_cast<const uint4*>(xrow_base + (int64_t)row * a.x_sl);
-        xn0 = ldg_nc_now(src); xn1 = ldg_nc_now(src + 1);
-      }
-      float e_prev = 0.0f;   // sC 2^(a_row) of the previous block: weight of its carried-in term
-      float r_tot = 0.0f;
-      for (int k = 0; k <= nb; ++k) {
-        const int st = k & 1;
-        if (k < nb) {
-          // ---- x(k) -> fp16 operands: raw, and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) (0 where dt_l = 0).
-          // The raw tile is free once GEMM3(k-1) is done (y_ready); the scaled tile was released by GEMM4(k-1),
-          // whose completion this group observed before its previous state update.
-          const int l = k * T + row;
-          const uint4 xq0 = xn0, xq1 = xn1;
-          if (l + T < a.seqlen) {  // the x rows of the next block: a whole block of work covers their latency
-            const uint4* src = reinterpret_cast<const uint4*>(xrow_base + (int64_t)(l + T) * a.x_sl);
-            xn0 = ldg_nc_now(src); xn1 = ldg_nc_now(src + 1);
-          } else {
-            xn0 = make_uint4(0, 0, 0, 0); xn1 = make_uint4(0, 0, 0, 0);
-          }
-          if (lead) TRACE(1, k, 4);
-          // int8 -> fp16 happens before the wait: only the stores depend on the tiles being free
-          uint4 xr[4];
-          {
-            const uint32_t xwd[8] = {xq0.x, xq0.y, xq0.z, xq0.w, xq1.x, xq1.y, xq1.z, xq1.w};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              __half2 r0, r1, r2, r3;
-              s8x4_to_h2x2(xwd[2 * c], r0, r1);
-              s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
-              xr[c] = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
-            }
-          }
-          if (!gwait3(&ms.bc_full[st], (k >> 1) & 1, k > 0 ? &ms.y_ready : nullptr, (k - 1) & 1, nullptr, 0)) break;
-          if (lead) TRACE(1, k, 13);
-          const float* av = ms.ab[st];
-          const float a_row = av[row];
-          r_tot = av[T - 1];
-          const __half2 w2 = __float2half2_rn(fast_exp2(r_tot - av[T + row] - lscb));
-          const float e_now = k > 0 ? sC * fast_exp2(a_row) : 0.0f;
-          {
-            uint8_t* rowp_raw = smem + kOffXraw + row * 128;
-            uint8_t* rowp_w = smem + kOffXw + row * 128;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int chunk = ((4 * hsel + c) ^ sw) << 4;
-              const uint4 v = xr[c];
-              *reinterpret_cast<uint4*>(rowp_raw + chunk) = v;
-              *reinterpret_cast<uint4*>(rowp_w + chunk) =
-                  make_uint4(h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.x), w2)),
-                             h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.y), w2)),
-                             h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.z), w2)),
-                             h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.w), w2)));
-            }
-          }
-          fence_proxy_async_smem();
-          gsync();
-          if (lead) { mbar_arrive(&ms.xops_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(1, k, 5); }
-          // swap: e_prev must describe block k - 1 in the output step below, block k afterwards
-          const float t = e_prev; e_prev = e_now;
-          if (k > 0) {
-            // ---- output of block k - 1 (weight t) ----
-#define QB_SSD_OUTPUT_STEP(EW)                                                                                               \
-            {                                                                                                                \
-              const int jj = k - 1;                                                                                          \
-              tc_fence_after_sync();                                                                                         \
-              uint32_t d2[32], d1[32];                                                                                       \
-              tmem_ld_32x32(tmem + tlane + kColD2 + 32 * hsel, d2);                                                          \
-              if (jj > 0) tmem_ld_32x32(tmem + tlane + ((jj & 1) ? kColD1b : kColD1) + 32 * hsel, d1);                       \
-              tmem_ld_wait();                                                                                                \
-              tc_fence_before_sync();                                                                                        \
-              gsync();                                                                                                       \
-              if (lead) { mbar_arrive(&ms.y_free); TRACE(1, jj, 9); } /* both accumulators are in registers */               \
-              const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 32 * hsel);                                        \
-              uint4 c4[4];                                                                                                   \
-              _Pragma("unroll") for (int t8 = 0; t8 < 4; ++t8) {                                                             \
-                uint32_t o[4];                                                                                               \
-                _Pragma("unroll") for (int v = 0; v < 2; ++v) {                                                              \
-                  const int t4 = 2 * t8 + v;                                                                                 \
-                  const float4 sx = sx4[t4];                                                                                 \
-                  float y0 = sx.x * __uint_as_float(d2[4 * t4 + 0]);                                                         \
-                  float y1 = sx.y * __uint_as_float(d2[4 * t4 + 1]);                                                         \
-                  float y2 = sx.z * __uint_as_float(d2[4 * t4 + 2]);                                                         \
-                  float y3 = sx.w * __uint_as_float(d2[4 * t4 + 3]);                                                         \
-                  if (jj > 0) {                                                                                              \
-                    y0 = fmaf(EW, __uint_as_float(d1[4 * t4 + 0]), y0);                                                      \
-                    y1 = fmaf(EW, __uint_as_float(d1[4 * t4 + 1]), y1);                                                      \
-                    y2 = fmaf(EW, __uint_as_float(d1[4 * t4 + 2]), y2);                                                      \
-                    y3 = fmaf(EW, __uint_as_float(d1[4 * t4 + 3]), y3);                                                      \
-                  }                                                                                                          \
-                  if (d_per_channel) {                                                                                       \
-                    const int lr = jj * T + row;                                                                             \
-                    uint32_t xw = 0;                                                                                         \
-                    if (lr < a.seqlen) xw = __ldg(reinterpret_cast<const uint32_t*>(xrow_base + (int64_t)lr * a.x_sl) + t4); \
-                    const float4 dx = reinterpret_cast<const float4*>(ms.dsx + 32 * hsel)[t4];                               \
-                    __half2 h01, h23;                                                                                        \
-                    s8x4_to_h2x2(xw, h01, h23);                                                                              \
-                    const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);                                       \
-                    y0 = fmaf(dx.x, x01.x, y0); y1 = fmaf(dx.y, x01.y, y1);                                                  \
-                    y2 = fmaf(dx.z, x23.x, y2); y3 = fmaf(dx.w, x23.y, y3);                                                  \
-                  }                                                                                                          \
-                  o[2 * v] = pack_h2(y0, y1);                                                                                \
-                  o[2 * v + 1] = pack_h2(y2, y3);                                                                            \
-                }                                                                                                            \
-                c4[t8] = make_uint4(o[0], o[1], o[2], o[3]);                                                                 \
-              }                                                                                                              \
-              /* 4 x 4 transpose of 16-byte pieces inside each quad of lanes: afterwards lane i of a quad holds piece i of  \
-                 the quad's four rows, so one store instruction writes 64 contiguous bytes per row */                        \
-              quad_transpose(c4, lane);                                                                                      \
-              const int r0 = jj * T + (row & ~3);                                                                            \
-              _Pragma("unroll") for (int m = 0; m < 4; ++m)                                                                  \
-                if (r0 + m < a.seqlen) *reinterpret_cast<uint4*>(out_base + (int64_t)(r0 + m) * out_pitch) = c4[m];          \
-            }
-            QB_SSD_OUTPUT_STEP(t)
-          }
-        } else {
-          if (!gwait(&ms.y_ready, (nb - 1) & 1)) break;
-          QB_SSD_OUTPUT_STEP(e_prev)
-          break;
-        }
-#undef QB_SSD_OUTPUT_STEP
+        if (lead) { mbar_arrive(&ms.lm_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(0, it, 4); }
 
-        // ---- state: s <- 2^r s + sB sx S_loc ; publish its fp16 copy for the next block -----------
-        // GEMM4(k) done; GEMM2(k) done, so the fp16 state tile it read may be rewritten
-        if (!gwait3(&ms.s_ready, k & 1, k > 0 ? &ms.d1_ready : nullptr, (k - 1) & 1, nullptr, 0)) break;
+        // ================= P3: state: s <- 2^r s + sB sx S_loc ; publish its fp16 copy for the next block ==============
+        // s_ready: GEMM4(it) done.  d1_ready: GEMM2(it) done, so the fp16 state tile it read may be rewritten.
+        ok = gwait(&ms.s_ready, ph, &ms.d1_ready, ph);
+        if (!ok) break;
         tc_fence_after_sync();
-        if (lead) TRACE(1, k, 6);
+        if (lead) TRACE(0, it, 5);
         {
           const float dec = fast_exp2(r_tot);
-          uint32_t sl[32];
-          tmem_ld_32x32(tmem + tlane + kColS + 32 * hsel, sl);
+          uint32_t sl[16];
+          tmem_ld_32x16(tmem + tlane + kColS + 16 * sub, sl);
           tmem_ld_wait();
-          const float4* sb4 = reinterpret_cast<const float4*>(ms.sbx + 32 * hsel);
+          const float4* sb4 = reinterpret_cast<const float4*>(ms.sbx + 16 * sub);
 #pragma unroll
-          for (int t4 = 0; t4 < 8; ++t4) {
+          for (int t4 = 0; t4 < 4; ++t4) {
             const float4 sc = sb4[t4];
             s_reg[4 * t4 + 0] = fmaf(dec, s_reg[4 * t4 + 0], sc.x * __uint_as_float(sl[4 * t4 + 0]));
             s_reg[4 * t4 + 1] = fmaf(dec, s_reg[4 * t4 + 1], sc.y * __uint_as_float(sl[4 * t4 + 1]));
             s_reg[4 * t4 + 2] = fmaf(dec, s_reg[4 * t4 + 2], sc.z * __uint_as_float(sl[4 * t4 + 2]));
             s_reg[4 * t4 + 3] = fmaf(dec, s_reg[4 * t4 + 3], sc.w * __uint_as_float(sl[4 * t4 + 3]));
           }
-          if (k + 1 < nb) {
-            uint8_t* dst = smem + kOffS16 + row * 128;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              *reinterpret_cast<uint4*>(dst + (((4 * hsel + u) ^ sw) << 4)) =
-                  make_uint4(pack_h2(s_reg[8 * u], s_reg[8 * u + 1]), pack_h2(s_reg[8 * u + 2], s_reg[8 * u + 3]),
-                             pack_h2(s_reg[8 * u + 4], s_reg[8 * u + 5]), pack_h2(s_reg[8 * u + 6], s_reg[8 * u + 7]));
-            }
-          }
         }
         tc_fence_before_sync();
-        fence_proxy_async_smem();
-        gsync();
-        if (lead && k + 1 < nb) mbar_arrive(&ms.s16_ready);   // also: the S accumulator has been read
-        if (lead) TRACE(1, k, 7);
+        if (j + 1 < im.je) {   // the next item prepares the tile itself (zero state or a state from another CTA)
+          store_s16();
+          fence_proxy_async_smem();
+          gsync();
+          if (lead) { mbar_arrive(&ms.s16_ready); TRACE(0, it, 6); }
+        }
 
-        // ---- final state -> int8 after the last block -----------------------------------------------------
-        if (k + 1 == nb) {
-          int hg = 0;
-          if (a.grouped) hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
-          int8_t* fs = a.final_states + ((int64_t)b * a.nheads + h) * P * N + row;
+        // ================= P4: y(j) = sC 2^(a_m) D1 + sx (D2 + D x) ======================================================
+        ok = gwait(&ms.y_ready, ph, nullptr, 0);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lead) TRACE(0, it, 7);
+        {
+          uint32_t d2[16], d1[16];
+          tmem_ld_32x16(tmem + tlane + kColD2 + 16 * sub, d2);
+          if (use_d1) tmem_ld_32x16(tmem + tlane + (st ? kColD1b : kColD1) + 16 * sub, d1);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 16 * sub);
+          const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
+          uint4 c2[2];
 #pragma unroll
-          for (int t = 0; t < 32; ++t) {  // fully unrolled: s_reg must never be indexed dynamically
-            const int p = 32 * hsel + t;
-            float ss;
-            if (!a.grouped) {
-              ss = a.ssm_state_scale[0];
-            } else {
-              const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
-              ss = a.ssm_state_scale[((int64_t)(g * a.nhead_groups + hg) * a.ndim_groups + dg) * N + row];
+          for (int t8 = 0; t8 < 2; ++t8) {
+            uint32_t o[4];
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              const int t4 = 2 * t8 + v;
+              const float4 sx = sx4[t4];
+              float y0 = sx.x * __uint_as_float(d2[4 * t4 + 0]);
+              float y1 = sx.y * __uint_as_float(d2[4 * t4 + 1]);
+              float y2 = sx.z * __uint_as_float(d2[4 * t4 + 2]);
+              float y3 = sx.w * __uint_as_float(d2[4 * t4 + 3]);
+              if (use_d1) {
+                y0 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 0]), y0);
+                y1 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 1]), y1);
+                y2 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 2]), y2);
+                y3 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 3]), y3);
+              }
+              if (d_per_channel) {
+                const float4 dx = reinterpret_cast<const float4*>(ms.dsx + 16 * sub)[t4];
+                __half2 h01, h23;
+                s8x4_to_h2x2(xwd[t4], h01, h23);
+                const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);
+                y0 = fmaf(dx.x, x01.x, y0); y1 = fmaf(dx.y, x01.y, y1);
+                y2 = fmaf(dx.z, x23.x, y2); y3 = fmaf(dx.w, x23.y, y3);
+              }
+              o[2 * v] = pack_h2(y0, y1);
+              o[2 * v + 1] = pack_h2(y2, y3);
             }
-            const float fin = __half2float(__float2half_rn(s_reg[t]));
-            fs[(int64_t)p * N] = (int8_t)rint_s8(fin / ss);
+            c2[t8] = make_uint4(o[0], o[1], o[2], o[3]);
           }
+          // Lanes 2i and 2i + 1 swap one 16-byte piece so that each store instruction writes whole 32-byte sectors:
+          // first the 32 bytes of row 2i (even lane: bytes 0..15, odd lane: 16..31), then those of row 2i + 1.
+          const bool odd = (lane & 1) != 0;
+          const uint4 got = shfl_xor_u4(odd ? c2[0] : c2[1], 1);
+          const uint4 first = odd ? got : c2[0];     // piece (lane & 1) of row 2i
+          const uint4 second = odd ? c2[1] : got;    // piece (lane & 1) of row 2i + 1
+          const int r0 = j * T + (row & ~1);
+          __half* o0 = out_base + (int64_t)r0 * out_pitch + 8 * (lane & 1);
+          if (r0 < a.seqlen) *reinterpret_cast<uint4*>(o0) = first;
+          if (r0 + 1 < a.seqlen) *reinterpret_cast<uint4*>(o0 + out_pitch) = second;
+        }
+        if (lead) TRACE(0, it, 8);
+      }
+      if (!ok) break;
+
+      if (im.publish) {
+        // ---- the state after the head part of a pair: to the CTA that runs the rest of it ------------------------
+        float4* dst = reinterpret_cast<float4*>(handoff + (int64_t)(blockIdx.x + 1) * kHandoffFloats);
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          __stcg(dst + v * kCompute + ctid, make_float4(s_reg[4 * v], s_reg[4 * v + 1], s_reg[4 * v + 2], s_reg[4 * v + 3]));
+        __threadfence();
+        gsync();
+        if (lead) {
+          const int one = 1;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + blockIdx.x + 1), "r"(one) : "memory");
+        }
+      } else {
+        // ---- final state -> int8 after the last block ------------------------------------------------------------
+        int hg = 0;
+        if (a.grouped) hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
+        int8_t* fs = a.final_states + ((int64_t)b * a.nheads + h) * P * N + row;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {  // fully unrolled: s_reg must never be indexed dynamically
+          const int p = 16 * sub + t;
+          float ss;
+          if (!a.grouped) {
+            ss = a.ssm_state_scale[0];
+          } else {
+            const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
+            ss = a.ssm_state_scale[((int64_t)(g * a.nhead_groups + hg) * a.ndim_groups + dg) * N + row];
+          }
+          const float fin = __half2float(__float2half_rn(s_reg[t]));
+          fs[(int64_t)p * N] = (int8_t)rint_s8(fin / ss);
         }
       }
     }
@@ -683,7 +693,9 @@ __global__ void ssd_widen_bc_kernel(const int8_t* __restrict__ Bq, int64_t B_sb,
 // Per (batch, head, 128-token block): dt = clamp(softplus(s_dt q + bias)); a = inclusive running sum of
 // dt * A * log2(e) inside the block; bk = a - log2(dt) - log2(sC sB) (+inf where dt == 0, i.e. past the
 // end of the sequence).  One warp per block, four tokens per lane.
-__global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb) {
+__global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb, int* __restrict__ flags, int nflags) {
+  if (blockIdx.x == 0)   // the hand-off flags of the main kernel, which follows on the same stream
+    for (int i = threadIdx.x; i < nflags; i += blockDim.x) flags[i] = 0;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int64_t units = (int64_t)a.batch * a.nheads * nb;
@@ -741,6 +753,7 @@ __global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb) 
 }
 
 int64_t align256l(int64_t v) { return (v + 255) & ~(int64_t)255; }
+constexpr int kMaxCtas = 256;   // hand-off slots in the workspace (one per CTA of the persistent kernel)
 
 }  // namespace
 
@@ -756,15 +769,20 @@ bool ssd_tc_eligible(const qb_ssd_args* a) {
 
 int64_t ssd_tc_workspace_bytes(int B, int L, int H, int G) {
   const int64_t nb = (L + T - 1) / T;
-  return 2 * align256l((int64_t)B * L * G * N * 2) + align256l((int64_t)B * H * nb * kAbVecs * T * 4);
+  return 2 * align256l((int64_t)B * L * G * N * 2) + align256l((int64_t)B * H * nb * kAbVecs * T * 4) +
+         align256l((int64_t)kMaxCtas * kHandoffFloats * 4) + align256l(kMaxCtas * 4);
 }
 
 int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   const int64_t half_bytes = align256l((int64_t)a->batch * a->seqlen * a->ngroups * N * 2);
   const int nb = (int)ceil_div(a->seqlen, T);
-  __half* B16 = reinterpret_cast<__half*>(static_cast<char*>(a->workspace));
-  __half* C16 = reinterpret_cast<__half*>(static_cast<char*>(a->workspace) + half_bytes);
-  float* ab_ws = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 2 * half_bytes);
+  const int64_t ab_bytes = align256l((int64_t)a->batch * a->nheads * nb * kAbVecs * T * 4);
+  char* ws = static_cast<char*>(a->workspace);
+  __half* B16 = reinterpret_cast<__half*>(ws);
+  __half* C16 = reinterpret_cast<__half*>(ws + half_bytes);
+  float* ab_ws = reinterpret_cast<float*>(ws + 2 * half_bytes);
+  float* handoff = reinterpret_cast<float*>(ws + 2 * half_bytes + ab_bytes);
+  int* flags = reinterpret_cast<int*>(ws + 2 * half_bytes + ab_bytes + align256l((int64_t)kMaxCtas * kHandoffFloats * 4));
   {
     const int64_t total = (int64_t)a->batch * a->seqlen * a->ngroups * (N / 16);
     ssd_widen_bc_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(a->Bm, a->B_sb, a->B_sl, a->B_sg, a->Cm, a->C_sb,
@@ -772,7 +790,7 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
                                                                        a->ngroups);
     QB_LAUNCH_OK("ssd_widen_bc_kernel");
     const int64_t units = (int64_t)a->batch * a->nheads * nb;
-    ssd_dt_kernel<<<(unsigned)ceil_div(units, 4), 128, 0, st>>>(*a, ab_ws, nb);
+    ssd_dt_kernel<<<(unsigned)ceil_div(units, 4), 128, 0, st>>>(*a, ab_ws, nb, flags, kMaxCtas);
     QB_LAUNCH_OK("ssd_dt_kernel");
   }
   CUtensorMap tb, tcm;
@@ -792,18 +810,19 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   }
   int* status = device_status_ptr();
   QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "device status word unavailable");
-  ssd_tc_kernel<<<(unsigned)(a->batch * a->nheads), kThreads, kSmemBytes, st>>>(tb, tcm, *a, ab_ws, status);
+  // One CTA per SM.  With at least as many (batch, head) pairs as CTAs the block list is cut into equal ranges (a range
+  // is then at least one whole pair long, which is what the head-first / tail-last order of the kernel relies on);
+  // with fewer, every CTA takes one whole pair.
+  const int pairs = a->batch * a->nheads;
+  const int ctas = std::min(std::min(sm_count(), kMaxCtas), pairs);
+  const int split = pairs >= ctas && ctas == std::min(sm_count(), kMaxCtas) ? 1 : 0;
+  ssd_tc_kernel<<<(unsigned)ctas, kThreads, kSmemBytes, st>>>(tb, tcm, *a, ab_ws, handoff, flags, split, status);
   QB_LAUNCH_OK("ssd_tc_kernel");
   return QB_OK;
 }
 
 }  // namespace qb
 
-#ifdef QB_DUMP
-extern "C" int qb_debug_set_dump(float* p) {  // development builds only
-  return cudaMemcpyToSymbol(qb::g_dump, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
-}
-#endif
 #ifdef QB_TRACE
 extern "C" int qb_debug_read_trace(long long* out) {  // 2 x 64 x 16 clock64 stamps of CTA 0 (development builds only)
   return cudaMemcpyFromSymbol(out, qb::g_trace, sizeof(qb::g_trace)) == cudaSuccess ? 0 : -1;
