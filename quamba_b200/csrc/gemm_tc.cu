@@ -329,19 +329,25 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   return QB_OK;
 }
 
-int encode_tmap_f16_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
-                       const uint32_t box[4]) {
+int encode_tmap_4d(CUtensorMap* out, bool f16, bool swizzle128, const void* base, const uint64_t dims[4],
+                   const uint64_t strides_bytes[3], const uint32_t box[4]) {
   EncodeTiledFn enc = get_encoder();
   QB_REQUIRE(enc != nullptr, QB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
   const cuuint64_t gstride[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
   const cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), gdim, gstride, bx, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  QB_REQUIRE(r == CUDA_SUCCESS, QB_ERR_CUDA, "cuTensorMapEncodeTiled (4-D fp16) failed with code %d", (int)r);
+  const CUresult r = enc(out, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base),
+                         gdim, gstride, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  QB_REQUIRE(r == CUDA_SUCCESS, QB_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with code %d", (int)r);
   return QB_OK;
+}
+
+int encode_tmap_f16_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                       const uint32_t box[4]) {
+  return encode_tmap_4d(out, true, true, base, dims, strides_bytes, box);
 }
 
 int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K,

@@ -44,7 +44,7 @@ namespace qb {
 
 #ifdef QB_TRACE
 __device__ long long g_trace[2][64][16];
-#define TRACE(role, j, slot) do { if (blockIdx.x == 0 && (j) < 64) g_trace[role][j][slot] = clock64(); } while (0)
+#define TRACE(role, j, slot) do { asm volatile("" ::: "memory"); if (blockIdx.x == 0 && (j) < 64) g_trace[role][j][slot] = clock64(); asm volatile("" ::: "memory"); } while (0)
 #else
 #define TRACE(role, j, slot) do { } while (0)
 #endif
@@ -64,7 +64,10 @@ constexpr int kOffC16 = 4 * kAtom;             // 2 stages x 2 atoms
 constexpr int kOffXraw = 8 * kAtom;            // 1 atom
 constexpr int kOffXw = 9 * kAtom;              // 1 atom
 constexpr int kOffS16 = 10 * kAtom;            // 1 atom
-constexpr int kOffMisc = 11 * kAtom;           // vectors + barriers
+constexpr int kOffY = 11 * kAtom;              // output staging: one 1 KB tile (32 rows x 32 bytes) per compute warp
+constexpr int kOffX8 = 12 * kAtom;             // 2 stages x 8 KB: the int8 x tile of a block (128 rows x 64 bytes)
+constexpr int kXBytes = T * P;
+constexpr int kOffMisc = 13 * kAtom;           // vectors + barriers
 constexpr int kMiscBytes = 4096;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;
 constexpr int kAbVecs = 3;                     // a[128], bk[128], ec[128] per block, fp32
@@ -134,6 +137,11 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -179,11 +187,6 @@ __device__ __forceinline__ uint4 ldg_nc_now(const void* p) {
 }
 __device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<const uint32_t*>(&v); }
 
-__device__ __forceinline__ uint4 shfl_xor_u4(uint4 v, int m) {
-  v.x = __shfl_xor_sync(0xffffffffu, v.x, m); v.y = __shfl_xor_sync(0xffffffffu, v.y, m);
-  v.z = __shfl_xor_sync(0xffffffffu, v.z, m); v.w = __shfl_xor_sync(0xffffffffu, v.w, m);
-  return v;
-}
 
 // One K = 128 contraction as eight K = 16 instructions.  The descriptors come in as two 32-bit words each and a K step
 // is one add on the low word: the issuing thread must spend only a handful of instructions per MMA, or the tensor pipe
@@ -201,7 +204,8 @@ __device__ __forceinline__ void issue_gemm(uint32_t d_tmem, SmemDesc a, SmemDesc
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant__ CUtensorMap tm_c16, qb_ssd_args a,
+ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant__ CUtensorMap tm_c16,
+              const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_out, qb_ssd_args a,
               const float* __restrict__ ab_ws, float* __restrict__ handoff, int* __restrict__ flags, int split, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -218,6 +222,8 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     fence_barrier_init();
     prefetch_tensormap(&tm_b16);
     prefetch_tensormap(&tm_c16);
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
     tmem_alloc(&ms.tmem_slot, kTmemCols);
@@ -242,7 +248,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           const uint32_t par = ((it >> 1) & 1) ^ 1;
           ok = mbar_wait(&ms.bc_empty[st], par, status, QB_ERR_TIMEOUT) && mbar_wait(&ms.ab_empty[st], par, status, QB_ERR_TIMEOUT);
           if (!ok) break;
-          mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes);
+          mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes + kXBytes);
           uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
           uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
           bulk_load(ms.ab[st], ab_src + (int64_t)j * (kAbVecs * T), kAbBytes, &ms.bc_full[st]);
@@ -250,6 +256,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, j * T, b);
           tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, j * T, b);
           tma_load_4d(dC + kAtom, &tm_c16, &ms.bc_full[st], 64, g, j * T, b);
+          tma_load_4d(smem + kOffX8 + st * kXBytes, &tm_x, &ms.bc_full[st], 0, h, j * T, b);   // rows past the end read as 0
         }
       }
     }
@@ -333,6 +340,9 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     const uint32_t tlane = (uint32_t)(q * 32) << 16;
     const int sw = row & 7;
     const bool lead = (threadIdx.x == kLead);
+    // the x operands (P1) touch no tensor memory, so there a warp takes eight whole rows: lane -> (row, 16-byte piece)
+    const int prow = 8 * cw + (lane >> 2), piece = lane & 3;
+    uint8_t* ytile = smem + kOffY + cw * 1024;
     auto gsync = [&]() { asm volatile("bar.sync 1, 512;" ::: "memory"); };
     auto gand = [&](uint32_t ok) -> bool {   // group barrier that ANDs a flag: a timed-out wait makes all warps leave together
       uint32_t r;
@@ -359,7 +369,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
                        pack_h2(s_reg[8 * u + 4], s_reg[8 * u + 5]), pack_h2(s_reg[8 * u + 6], s_reg[8 * u + 7]));
     };
     const bool d_per_channel = a.D != nullptr && a.D_has_hdim;   // then the skip term is added in the output step
-    const int64_t out_pitch = (int64_t)a.nheads * P;
     int it = 0;
     bool ok = true;
     for (int ii = 0; ii < plan.n_items && ok; ++ii) {
@@ -369,10 +378,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       const float sC = a.grouped ? a.C_scale[g] : a.C_scale[0];
       const float lscb = fast_log2(sC * sB);
       const int8_t* xrow_base = a.x + (int64_t)b * a.x_sb + (int64_t)h * a.x_sh + 16 * sub;
-      __half* out_base = static_cast<__half*>(a.out) + ((int64_t)b * a.seqlen * a.nheads + h) * P + 16 * sub;
-      // the x row of the first block: requested before anything else of this item
-      uint4 xn = make_uint4(0, 0, 0, 0);
-      if (im.jb * T + row < a.seqlen) xn = ldg_nc_now(xrow_base + (int64_t)(im.jb * T + row) * a.x_sl);
       gsync();   // every warp is past its last read of the per-head vectors of the previous item
       if (ctid < P) {
         const int p = ctid;
@@ -430,44 +435,31 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         // ================= P1: x(j) -> fp16 operands: raw, and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) =====
         // (0 where dt_l = 0).  Both tiles are free: the state step of the previous block waited for GEMM4 and its
         // output step for GEMM3.
-        const uint4 xq = xn;
-        if (j + 1 < im.je && l + T < a.seqlen) xn = ldg_nc_now(xrow_base + (int64_t)(l + T) * a.x_sl);   // a block of work covers its latency
-        else xn = make_uint4(0, 0, 0, 0);
         if (lead) TRACE(0, it, 0);
-        uint4 xr[2];
+        ok = gwait(&ms.bc_full[st], (it >> 1) & 1, nullptr, 0);   // x, B, C and the vectors of this block have landed
+        if (!ok) break;
+        if (lead) TRACE(0, it, 1);
+        const float* av = ms.ab[st];
         {
+          const uint4 xq = *reinterpret_cast<const uint4*>(smem + kOffX8 + st * kXBytes + prow * P + piece * 16);
           const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
+          const __half2 w2 = __float2half2_rn(fast_exp2(av[T - 1] - av[T + prow] - lscb));
+          uint8_t* rowp_raw = smem + kOffXraw + prow * 128;
+          uint8_t* rowp_w = smem + kOffXw + prow * 128;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             __half2 r0, r1, r2, r3;
             s8x4_to_h2x2(xwd[2 * c], r0, r1);
             s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
-            xr[c] = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
+            const int chunk = ((2 * piece + c) ^ (prow & 7)) << 4;
+            *reinterpret_cast<uint4*>(rowp_raw + chunk) = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
+            *reinterpret_cast<uint4*>(rowp_w + chunk) = make_uint4(h2_bits(__hmul2(r0, w2)), h2_bits(__hmul2(r1, w2)),
+                                                                   h2_bits(__hmul2(r2, w2)), h2_bits(__hmul2(r3, w2)));
           }
         }
-        ok = gwait(&ms.bc_full[st], (it >> 1) & 1, nullptr, 0);   // the vectors of this block have landed
-        if (!ok) break;
-        if (lead) TRACE(0, it, 1);
-        const float* av = ms.ab[st];
         const float a_row = av[row];
         const float r_tot = av[T - 1];
         const float e_out = use_d1 ? sC * fast_exp2(a_row) : 0.0f;   // weight of the carried-in term in the output
-        {
-          const __half2 w2 = __float2half2_rn(fast_exp2(r_tot - av[T + row] - lscb));
-          uint8_t* rowp_raw = smem + kOffXraw + row * 128;
-          uint8_t* rowp_w = smem + kOffXw + row * 128;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const int chunk = ((2 * sub + c) ^ sw) << 4;
-            const uint4 v = xr[c];
-            *reinterpret_cast<uint4*>(rowp_raw + chunk) = v;
-            *reinterpret_cast<uint4*>(rowp_w + chunk) =
-                make_uint4(h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.x), w2)),
-                           h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.y), w2)),
-                           h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.z), w2)),
-                           h2_bits(__hmul2(*reinterpret_cast<const __half2*>(&v.w), w2)));
-          }
-        }
         fence_proxy_async_smem();
         gsync();
         if (lead) { mbar_arrive(&ms.xops_ready); TRACE(0, it, 2); }
@@ -569,6 +561,8 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 7);
         {
+          uint4 xq = make_uint4(0, 0, 0, 0);
+          if (d_per_channel && l < a.seqlen) xq = ldg_nc_now(xrow_base + (int64_t)l * a.x_sl);   // own 16 channels of x
           uint32_t d2[16], d1[16];
           tmem_ld_32x16(tmem + tlane + kColD2 + 16 * sub, d2);
           if (use_d1) tmem_ld_32x16(tmem + tlane + (st ? kColD1b : kColD1) + 16 * sub, d1);
@@ -607,16 +601,19 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
             }
             c2[t8] = make_uint4(o[0], o[1], o[2], o[3]);
           }
-          // Lanes 2i and 2i + 1 swap one 16-byte piece so that each store instruction writes whole 32-byte sectors:
-          // first the 32 bytes of row 2i (even lane: bytes 0..15, odd lane: 16..31), then those of row 2i + 1.
-          const bool odd = (lane & 1) != 0;
-          const uint4 got = shfl_xor_u4(odd ? c2[0] : c2[1], 1);
-          const uint4 first = odd ? got : c2[0];     // piece (lane & 1) of row 2i
-          const uint4 second = odd ? c2[1] : got;    // piece (lane & 1) of row 2i + 1
-          const int r0 = j * T + (row & ~1);
-          __half* o0 = out_base + (int64_t)r0 * out_pitch + 8 * (lane & 1);
-          if (r0 < a.seqlen) *reinterpret_cast<uint4*>(o0) = first;
-          if (r0 + 1 < a.seqlen) *reinterpret_cast<uint4*>(o0 + out_pitch) = second;
+          // The warp's 32 rows x 32 bytes go to its staging tile (dense rows, unswizzled tensor map) and
+          // leave as one TMA store: rows past the end of the sequence are clipped by the hardware, and the LSU sees
+          // two shared-memory stores per thread instead of scattered 16-byte global stores.
+          if (lane == 0) bulk_wait_read<0>();   // the previous store of this warp has read the tile
+          __syncwarp();
+          reinterpret_cast<uint4*>(ytile + lane * 32)[0] = c2[0];
+          reinterpret_cast<uint4*>(ytile + lane * 32)[1] = c2[1];
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && j * T + q * 32 < a.seqlen) {
+            tma_store_4d(&tm_out, ytile, 16 * sub, h, j * T + q * 32, b);
+            bulk_commit();
+          }
         }
         if (lead) TRACE(0, it, 8);
       }
@@ -655,6 +652,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       }
     }
   }
+  if (warp >= 4 && lane == 0) bulk_wait_all<0>();   // the output stores of this warp are complete
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -801,6 +799,21 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   if (rc != QB_OK) return rc;
   rc = encode_tmap_f16_4d(&tcm, C16, dims, strides, box);
   if (rc != QB_OK) return rc;
+  CUtensorMap tx, tout;
+  {
+    // x int8 (P, H, L, B): one 128-row x 64-byte tile per block, unswizzled
+    const uint64_t xd[4] = {(uint64_t)P, (uint64_t)a->nheads, (uint64_t)a->seqlen, (uint64_t)a->batch};
+    const uint64_t xs[3] = {(uint64_t)a->x_sh, (uint64_t)a->x_sl, (uint64_t)a->x_sb};
+    const uint32_t xb[4] = {(uint32_t)P, 1, (uint32_t)T, 1};
+    rc = encode_tmap_4d(&tx, false, false, a->x, xd, xs, xb);
+    if (rc != QB_OK) return rc;
+    // out fp16 (P, H, L, B) contiguous: 32 rows x 16 channels per store, dense 32-byte rows on the shared-memory side
+    const uint64_t od[4] = {(uint64_t)P, (uint64_t)a->nheads, (uint64_t)a->seqlen, (uint64_t)a->batch};
+    const uint64_t os[3] = {(uint64_t)P * 2, (uint64_t)a->nheads * P * 2, (uint64_t)a->seqlen * a->nheads * P * 2};
+    const uint32_t ob[4] = {16, 1, 32, 1};
+    rc = encode_tmap_4d(&tout, true, false, a->out, od, os, ob);
+    if (rc != QB_OK) return rc;
+  }
   static bool attr_set[64] = {};
   int dev = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
@@ -816,7 +829,7 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   const int pairs = a->batch * a->nheads;
   const int ctas = std::min(std::min(sm_count(), kMaxCtas), pairs);
   const int split = pairs >= ctas && ctas == std::min(sm_count(), kMaxCtas) ? 1 : 0;
-  ssd_tc_kernel<<<(unsigned)ctas, kThreads, kSmemBytes, st>>>(tb, tcm, *a, ab_ws, handoff, flags, split, status);
+  ssd_tc_kernel<<<(unsigned)ctas, kThreads, kSmemBytes, st>>>(tb, tcm, tx, tout, *a, ab_ws, handoff, flags, split, status);
   QB_LAUNCH_OK("ssd_tc_kernel");
   return QB_OK;
 }

@@ -224,5 +224,9 @@ int encode_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // Host: 4-D fp16 tensor map, dims / box innermost first, strides (bytes) for dims 1..3, 128-byte swizzle.
 int encode_tmap_f16_4d(CUtensorMap* out, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
                        const uint32_t box[4]);
+// Host: 4-D tensor map of fp16 or byte elements (dims / strides / box counted in elements resp. bytes as above), with
+// 128-byte swizzle or none.
+int encode_tmap_4d(CUtensorMap* out, bool f16, bool swizzle128, const void* base, const uint64_t dims[4],
+                   const uint64_t strides_bytes[3], const uint32_t box[4]);
 
 }  // namespace qb
