@@ -76,6 +76,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
 }
 
+// The same without the back-off, for a thread whose wake-up latency is on the critical path (an MMA issuer: one thread,
+// and try_wait itself suspends it for a while, so it does not spin hot).
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+
 // 2-D TMA tile load, completion on an mbarrier of this CTA.  x = innermost coordinate.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
