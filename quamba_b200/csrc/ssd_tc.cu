@@ -33,9 +33,12 @@
 //   P1  x(k) -> fp16 operands (raw, and scaled by w) in shared memory            -> GEMM4(k) = S_loc
 //   P2  CB(k) -> Lm(k), written back to tensor memory as packed fp16 (A operand)  -> GEMM3(k) = D2, then CB(k+1)
 //   P3  state update from S_loc(k), fp16 copy of the state to shared memory      -> GEMM2(k+1) = D1
-//   P4  y(k) from D2(k), D1(k): straight to global memory
-// so every GEMM runs while the compute warps are busy with the next phase, and program order plus one group barrier
-// per phase is what frees each buffer (noted at each wait).  Every mbarrier completes exactly once per block, is waited
+//   P4  y(k) from D2(k), D1(k): to a per-warp staging tile and out by TMA store
+// so every GEMM runs while the compute warps are busy with the next phase, and program order plus the group barriers
+// of each phase is what frees each buffer (noted at each wait).  The warps are kept in lock step on purpose: variants
+// in which they synchronised through mbarriers only and drifted apart (each thread polling, or one barrier per phase
+// with per-warp arrivals) were 10 to 30 % slower although they wait less -- with every warp in the same phase the
+// unrolled code of that phase is fetched once for all of them.  Every mbarrier completes exactly once per block, is waited
 // on by each consumer once per phase and in order, and all waits are bounded.  The B / C stage is handed back to the
 // TMA producer only at the end of an MMA iteration.
 #include "tc_common.cuh"
@@ -74,9 +77,9 @@ constexpr int kAbVecs = 3;                     // a[128], bk[128], ec[128] per b
 constexpr int kAbBytes = kAbVecs * T * 4;
 constexpr int kHandoffFloats = kCompute * 16;  // one fp32 state (64 x 128) per CTA, thread-major
 
-// Tensor memory: CB (fp32), Lm (packed fp16, 64 columns), S, and D1 / D2 double-buffered: the output step of block k runs
-// one step late (after the Lm of block k + 1 has been handed to the tensor cores), so that no GEMM is ever waited for.
-constexpr uint32_t kColCB = 0, kColLm = 128, kColD2 = 192, kColS = 256, kColD1 = 320, kColD1b = 384, kColD2b = 448, kTmemCols = 512;
+// Tensor memory: CB (fp32), Lm (packed fp16, 64 columns), D2, S, and D1 double-buffered (GEMM2(k+1) is issued while the
+// output step of block k still has D1(k) to read).
+constexpr uint32_t kColCB = 0, kColLm = 128, kColD2 = 192, kColS = 256, kColD1 = 320, kColD1b = 384, kTmemCols = 512;
 
 struct Misc {
   float ab[2][kAbVecs * T];   // per stage: a, bk, ec of the block (see ssd_dt_kernel)
@@ -86,9 +89,7 @@ struct Misc {
   float dfold;                // D of this head when it is one value per head (added on the diagonal of Lm), else 0
   uint64_t bc_full[2], bc_empty[2], ab_empty[2];
   uint64_t cb_ready, xops_ready, s_ready, lm_ready, y_ready, s16_ready, d1_ready;
-  uint64_t item_bar;          // the compute warps meet here between two items (bounded like every other wait)
   uint32_t tmem_slot;
-  int abort;                  // set when the hand-off state never arrived
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc does not fit");
 
@@ -218,11 +219,9 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
   const Plan plan = make_plan((int)blockIdx.x, (int)gridDim.x, a.batch * a.nheads, nb, split);
 
   if (threadIdx.x == 0) {
-    // barriers the compute warps arrive on count one arrival per warp (16); the others one TMA / commit arrival
-    for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 16); }
-    mbar_init(&ms.cb_ready, 1); mbar_init(&ms.xops_ready, 16); mbar_init(&ms.s_ready, 1); mbar_init(&ms.lm_ready, 16);
-    mbar_init(&ms.y_ready, 1); mbar_init(&ms.s16_ready, 16); mbar_init(&ms.d1_ready, 1); mbar_init(&ms.item_bar, 16);
-    ms.abort = 0;
+    for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 1); }
+    mbar_init(&ms.cb_ready, 1); mbar_init(&ms.xops_ready, 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.lm_ready, 1);
+    mbar_init(&ms.y_ready, 1); mbar_init(&ms.s16_ready, 1); mbar_init(&ms.d1_ready, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_b16);
     prefetch_tensormap(&tm_c16);
@@ -307,15 +306,15 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           TRACE(1, it, 1);
           issue_gemm<true, true>(tmem + kColS, desc_advance(dBm, st * 2 * kAtom), dXw, id_mn);
           umma_commit(&ms.s_ready);
-          // GEMM3(it): D2[it & 1] = Lm X, Lm from tensor memory.  lm_ready also says (program order of the compute
-          // warps) that the output step of block it - 2 has read this D2 buffer.
+          // GEMM3(it): D2 = Lm X, Lm from tensor memory.  lm_ready also says (program order of the compute warps) that
+          // the output step of the previous block has read D2.
           ok = mbar_wait_spin(&ms.lm_ready, ph, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
           TRACE(1, it, 2);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_f16_ta(tmem + (st ? kColD2b : kColD2), tmem + kColLm + ks * 8, desc_advance(dXraw, ks * 2048), id_kn, ks != 0 ? 1u : 0u);
+            umma_f16_ta(tmem + kColD2, tmem + kColLm + ks * 8, desc_advance(dXraw, ks * 2048), id_kn, ks != 0 ? 1u : 0u);
           umma_commit(&ms.y_ready);
           TRACE(1, it, 3);
           if (it + 1 < plan.total) {
@@ -347,17 +346,21 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     // the x operands (P1) touch no tensor memory, so there a warp takes eight whole rows: lane -> (row, 16-byte piece)
     const int prow = 8 * cw + (lane >> 2), piece = lane & 3;
     uint8_t* ytile = smem + kOffY + cw * 1024;
-    // No hardware barrier in the steady state: every thread waits on the mbarrier it needs itself, and a warp tells the
-    // MMA issuer (or the TMA producer) that it is done with one arrival after a __syncwarp.  Warps therefore drift
-    // apart as far as the data dependencies allow and fill each other's stalls.
-    auto twait = [&](uint64_t* bar, uint32_t parity) -> bool { return mbar_wait(bar, parity, status, QB_ERR_TIMEOUT); };
-    auto warrive = [&](uint64_t* bar) { __syncwarp(); if (lane == 0) mbar_arrive(bar); };
-    uint32_t ib_phase = 0;
-    auto soft_sync = [&]() -> bool {   // all 16 compute warps; between items only
-      warrive(&ms.item_bar);
-      const bool r = twait(&ms.item_bar, ib_phase);
-      ib_phase ^= 1;
-      return r;
+    auto gsync = [&]() { asm volatile("bar.sync 1, 512;" ::: "memory"); };
+    auto gand = [&](uint32_t ok) -> bool {   // group barrier that ANDs a flag: a timed-out wait makes all warps leave together
+      uint32_t r;
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 512, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                   : "=r"(r) : "r"(ok) : "memory");
+      return r != 0;
+    };
+    // One thread polls the mbarrier(s), the others park at the group's hardware barrier.
+    auto gwait = [&](uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1) -> bool {
+      uint32_t ok = 1;
+      if (lead) {
+        ok = mbar_wait(b0, p0, status, QB_ERR_TIMEOUT) ? 1u : 0u;
+        if (ok && b1 != nullptr) ok = mbar_wait(b1, p1, status, QB_ERR_TIMEOUT) ? 1u : 0u;
+      }
+      return gand(ok);
     };
     float s_reg[16];
     auto store_s16 = [&]() {   // fp16 copy of this thread's 16 state values: row n, channels 16 sub .. (MN-major B of GEMM2)
@@ -378,8 +381,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       const float sC = a.grouped ? a.C_scale[g] : a.C_scale[0];
       const float lscb = fast_log2(sC * sB);
       const int8_t* xrow_base = a.x + (int64_t)b * a.x_sb + (int64_t)h * a.x_sh + 16 * sub;
-      ok = soft_sync();   // every warp is past its last read of the per-head vectors of the previous item
-      if (!ok) break;
+      gsync();   // every warp is past its last read of the per-head vectors of the previous item
       if (ctid < P) {
         const int p = ctid;
         float sx;
@@ -397,21 +399,21 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         ms.sbx[p] = sB * sx;
         if (p == 0) ms.dfold = (a.D != nullptr && !a.D_has_hdim) ? (*a.D_scale) * (float)a.D[h] : 0.0f;
       }
-      if (im.has_init && lead) {
-        // the state after the head part of this pair, published by the previous CTA early in its life
-        const long long t0 = clock64();
-        for (;;) {
-          int v;
-          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + blockIdx.x) : "memory");
-          if (v != 0) break;
-          __nanosleep(256);
-          if (clock64() - t0 > kWaitBudgetCycles) { atomicCAS(status, 0, QB_ERR_TIMEOUT); ms.abort = 1; break; }
-        }
-      }
-      ok = soft_sync();   // the vectors are written, and the lead thread has seen the flag
-      if (ok && ms.abort != 0) ok = false;
-      if (!ok) break;
       if (im.has_init) {
+        // the state after the head part of this pair, published by the previous CTA early in its life
+        uint32_t got = 1;
+        if (lead) {
+          const long long t0 = clock64();
+          for (;;) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + blockIdx.x) : "memory");
+            if (v != 0) break;
+            __nanosleep(256);
+            if (clock64() - t0 > kWaitBudgetCycles) { atomicCAS(status, 0, QB_ERR_TIMEOUT); got = 0; break; }
+          }
+        }
+        ok = gand(got);
+        if (!ok) break;
         const float4* src = reinterpret_cast<const float4*>(handoff + (int64_t)blockIdx.x * kHandoffFloats);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -424,80 +426,20 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
 #pragma unroll
         for (int t = 0; t < 16; ++t) s_reg[t] = 0.0f;
       }
-      warrive(&ms.s16_ready);
+      gsync();
+      if (lead) mbar_arrive(&ms.s16_ready);
       const float dfold = ms.dfold;
 
-      // ---- output step of block jj (pipeline position itt): y = sC 2^(a_m) D1 + sx (D2 + D x).  Both accumulators are
-      // complete when it is called (see the call sites); the warp's 32 rows x 32 bytes go to its staging tile (dense
-      // rows) and leave as one TMA store: rows past the end of the sequence are clipped by the hardware, and the LSU
-      // sees two shared-memory stores per thread instead of scattered 16-byte global stores.
-      auto output_step = [&](int jj, int itt, float ew, bool used1) {
-        const int l = jj * T + row;
-        uint4 xq = make_uint4(0, 0, 0, 0);
-        if (d_per_channel && l < a.seqlen) xq = ldg_nc_now(xrow_base + (int64_t)l * a.x_sl);   // own 16 channels of x
-        tc_fence_after_sync();
-        uint32_t d2[16], d1[16];
-        tmem_ld_32x16(tmem + tlane + ((itt & 1) ? kColD2b : kColD2) + 16 * sub, d2);
-        if (used1) tmem_ld_32x16(tmem + tlane + ((itt & 1) ? kColD1b : kColD1) + 16 * sub, d1);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 16 * sub);
-        const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
-        uint4 c2[2];
-#pragma unroll
-        for (int t8 = 0; t8 < 2; ++t8) {
-          uint32_t o[4];
-#pragma unroll
-          for (int v = 0; v < 2; ++v) {
-            const int t4 = 2 * t8 + v;
-            const float4 sx = sx4[t4];
-            float y0 = sx.x * __uint_as_float(d2[4 * t4 + 0]);
-            float y1 = sx.y * __uint_as_float(d2[4 * t4 + 1]);
-            float y2 = sx.z * __uint_as_float(d2[4 * t4 + 2]);
-            float y3 = sx.w * __uint_as_float(d2[4 * t4 + 3]);
-            if (used1) {
-              y0 = fmaf(ew, __uint_as_float(d1[4 * t4 + 0]), y0);
-              y1 = fmaf(ew, __uint_as_float(d1[4 * t4 + 1]), y1);
-              y2 = fmaf(ew, __uint_as_float(d1[4 * t4 + 2]), y2);
-              y3 = fmaf(ew, __uint_as_float(d1[4 * t4 + 3]), y3);
-            }
-            if (d_per_channel) {
-              const float4 dx = reinterpret_cast<const float4*>(ms.dsx + 16 * sub)[t4];
-              __half2 h01, h23;
-              s8x4_to_h2x2(xwd[t4], h01, h23);
-              const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);
-              y0 = fmaf(dx.x, x01.x, y0); y1 = fmaf(dx.y, x01.y, y1);
-              y2 = fmaf(dx.z, x23.x, y2); y3 = fmaf(dx.w, x23.y, y3);
-            }
-            o[2 * v] = pack_h2(y0, y1);
-            o[2 * v + 1] = pack_h2(y2, y3);
-          }
-          c2[t8] = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-        if (lane == 0) bulk_wait_read<0>();   // the previous store of this warp has read the tile
-        __syncwarp();
-        reinterpret_cast<uint4*>(ytile + lane * 32)[0] = c2[0];
-        reinterpret_cast<uint4*>(ytile + lane * 32)[1] = c2[1];
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && jj * T + q * 32 < a.seqlen) {
-          tma_store_4d(&tm_out, ytile, 16 * sub, h, jj * T + q * 32, b);
-          bulk_commit();
-        }
-      };
-
-      float e_prev = 0.0f;
-      bool used1_prev = false;
       for (int j = im.jb; j < im.je; ++j, ++it) {
         const int st = it & 1;
         const uint32_t ph = it & 1;
         const bool use_d1 = j > im.jb || im.has_init;
+        const int l = j * T + row;
         // ================= P1: x(j) -> fp16 operands: raw, and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) =====
-        // (0 where dt_l = 0).  The scaled tile is free because this thread's state step of the previous block waited
-        // for GEMM4; the raw tile (and the Lm columns, below) once GEMM3 of the previous block is complete.
+        // (0 where dt_l = 0).  Both tiles are free: the state step of the previous block waited for GEMM4 and its
+        // output step for GEMM3.
         if (lead) TRACE(0, it, 0);
-        ok = twait(&ms.bc_full[st], (it >> 1) & 1);   // x, B, C and the vectors of this block have landed
-        if (ok && it > 0) ok = twait(&ms.y_ready, (it - 1) & 1);
+        ok = gwait(&ms.bc_full[st], (it >> 1) & 1, nullptr, 0);   // x, B, C and the vectors of this block have landed
         if (!ok) break;
         if (lead) TRACE(0, it, 1);
         const float* av = ms.ab[st];
@@ -518,16 +460,17 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
                                                                    h2_bits(__hmul2(r2, w2)), h2_bits(__hmul2(r3, w2)));
           }
         }
-        fence_proxy_async_smem();
-        warrive(&ms.xops_ready);
-        if (lead) TRACE(0, it, 2);
         const float a_row = av[row];
         const float r_tot = av[T - 1];
         const float e_out = use_d1 ? sC * fast_exp2(a_row) : 0.0f;   // weight of the carried-in term in the output
+        fence_proxy_async_smem();
+        gsync();
+        if (lead) { mbar_arrive(&ms.xops_ready); TRACE(0, it, 2); }
 
         // ================= P2: Lm[t, s] = CB[t, s] 2^(a_t - bk_s) for s <= t (+ D on the diagonal), chunk sub =============
-        // Written as packed fp16 into its own tensor-memory columns (GEMM3 of the previous block is complete, see P1).
-        ok = twait(&ms.cb_ready, ph);
+        // Written as packed fp16 into its own tensor-memory columns, which GEMM3 of the previous block has finished
+        // reading (its output step waited for y_ready).
+        ok = gwait(&ms.cb_ready, ph, nullptr, 0);
         if (!ok) break;
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 3);
@@ -583,17 +526,12 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         }
         tmem_st_wait();
         tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) { mbar_arrive(&ms.lm_ready); mbar_arrive(&ms.ab_empty[st]); }
-        if (lead) TRACE(0, it, 4);
-
-        // ================= P4 of the previous block: its GEMM3 was waited for in P1 above, its GEMM2 in its state step ==
-        if (j > im.jb) output_step(j - 1, it - 1, e_prev, used1_prev);
-        if (lead) TRACE(0, it, 8);
+        gsync();
+        if (lead) { mbar_arrive(&ms.lm_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(0, it, 4); }
 
         // ================= P3: state: s <- 2^r s + sB sx S_loc ; publish its fp16 copy for the next block ==============
         // s_ready: GEMM4(it) done.  d1_ready: GEMM2(it) done, so the fp16 state tile it read may be rewritten.
-        ok = twait(&ms.s_ready, ph) && twait(&ms.d1_ready, ph);
+        ok = gwait(&ms.s_ready, ph, &ms.d1_ready, ph);
         if (!ok) break;
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 5);
@@ -616,17 +554,73 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (j + 1 < im.je) {   // the next item prepares the tile itself (zero state or a state from another CTA)
           store_s16();
           fence_proxy_async_smem();
-          warrive(&ms.s16_ready);
+          gsync();
+          if (lead) { mbar_arrive(&ms.s16_ready); TRACE(0, it, 6); }
         }
-        if (lead) TRACE(0, it, 6);
-        e_prev = e_out;
-        used1_prev = use_d1;
+
+        // ================= P4: y(j) = sC 2^(a_m) D1 + sx (D2 + D x) ======================================================
+        ok = gwait(&ms.y_ready, ph, nullptr, 0);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lead) TRACE(0, it, 7);
+        {
+          uint4 xq = make_uint4(0, 0, 0, 0);
+          if (d_per_channel && l < a.seqlen) xq = ldg_nc_now(xrow_base + (int64_t)l * a.x_sl);   // own 16 channels of x
+          uint32_t d2[16], d1[16];
+          tmem_ld_32x16(tmem + tlane + kColD2 + 16 * sub, d2);
+          if (use_d1) tmem_ld_32x16(tmem + tlane + (st ? kColD1b : kColD1) + 16 * sub, d1);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 16 * sub);
+          const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
+          uint4 c2[2];
+#pragma unroll
+          for (int t8 = 0; t8 < 2; ++t8) {
+            uint32_t o[4];
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              const int t4 = 2 * t8 + v;
+              const float4 sx = sx4[t4];
+              float y0 = sx.x * __uint_as_float(d2[4 * t4 + 0]);
+              float y1 = sx.y * __uint_as_float(d2[4 * t4 + 1]);
+              float y2 = sx.z * __uint_as_float(d2[4 * t4 + 2]);
+              float y3 = sx.w * __uint_as_float(d2[4 * t4 + 3]);
+              if (use_d1) {
+                y0 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 0]), y0);
+                y1 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 1]), y1);
+                y2 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 2]), y2);
+                y3 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 3]), y3);
+              }
+              if (d_per_channel) {
+                const float4 dx = reinterpret_cast<const float4*>(ms.dsx + 16 * sub)[t4];
+                __half2 h01, h23;
+                s8x4_to_h2x2(xwd[t4], h01, h23);
+                const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);
+                y0 = fmaf(dx.x, x01.x, y0); y1 = fmaf(dx.y, x01.y, y1);
+                y2 = fmaf(dx.z, x23.x, y2); y3 = fmaf(dx.w, x23.y, y3);
+              }
+              o[2 * v] = pack_h2(y0, y1);
+              o[2 * v + 1] = pack_h2(y2, y3);
+            }
+            c2[t8] = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          // The warp's 32 rows x 32 bytes go to its staging tile (dense rows, unswizzled tensor map) and
+          // leave as one TMA store: rows past the end of the sequence are clipped by the hardware, and the LSU sees
+          // two shared-memory stores per thread instead of scattered 16-byte global stores.
+          if (lane == 0) bulk_wait_read<0>();   // the previous store of this warp has read the tile
+          __syncwarp();
+          reinterpret_cast<uint4*>(ytile + lane * 32)[0] = c2[0];
+          reinterpret_cast<uint4*>(ytile + lane * 32)[1] = c2[1];
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && j * T + q * 32 < a.seqlen) {
+            tma_store_4d(&tm_out, ytile, 16 * sub, h, j * T + q * 32, b);
+            bulk_commit();
+          }
+        }
+        if (lead) TRACE(0, it, 8);
       }
       if (!ok) break;
-      // ---- the output of the item's last block: here its GEMM3 is waited for ----------------------------------------
-      ok = twait(&ms.y_ready, (it - 1) & 1);
-      if (!ok) break;
-      output_step(im.je - 1, it - 1, e_prev, used1_prev);
 
       if (im.publish) {
         // ---- the state after the head part of a pair: to the CTA that runs the rest of it ------------------------
@@ -635,8 +629,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         for (int v = 0; v < 4; ++v)
           __stcg(dst + v * kCompute + ctid, make_float4(s_reg[4 * v], s_reg[4 * v + 1], s_reg[4 * v + 2], s_reg[4 * v + 3]));
         __threadfence();
-        ok = soft_sync();
-        if (!ok) break;
+        gsync();
         if (lead) {
           const int one = 1;
           asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + blockIdx.x + 1), "r"(one) : "memory");
