@@ -331,8 +331,8 @@ def main():
                    "sharding": "independent batches per GPU, no collective on this path"},
         "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": int(sets[0]["host_xBC"].numel() + sets[0]["host_dt"].numel()),
                 "d2h_bytes_per_step": int(host_y.numel() * 2 + host_f.numel())},
-        "gpu_launches": 4 * steps,
-        "roofline": {"kernel": "ssd_tc_kernel (+ ssd_widen_bc_kernel, ssd_dt_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
+        "gpu_launches": 3 * steps,
+        "roofline": {"kernel": "ssd_tc_kernel (+ ssd_prep_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
                      "frac": ssd_gbs / hbm_peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
                      "algorithmic_bytes": ssd_bytes, "ms": ssd_ms,
                      "conv1d": {"achieved": conv_gbs, "frac": conv_gbs / hbm_peak, "algorithmic_bytes": conv_bytes, "ms": conv_ms}},

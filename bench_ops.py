@@ -151,7 +151,7 @@ def op_ssd(dev, gen, ops):
                                                                 None, None, True)
     fl = 2 * B * H * L * 128 * (N + P + 2 * P)          # per 128-token block: C.B^T, Lm.X, C.S, Xw^T.B
     return dict(workload=f"Mamba2 int8 SSD chunk scan B{B} L{L} H{H} P{P} G{G} N{N} Q{Q}", bytes=by, flops=fl, nsets=n, make=mk,
-                kernel="ssd_tc_kernel (+ ssd_widen_bc_kernel, ssd_dt_kernel)", launches=3)
+                kernel="ssd_tc_kernel (+ ssd_prep_kernel)", launches=2)
 
 
 def op_ssd_update(dev, gen, ops):

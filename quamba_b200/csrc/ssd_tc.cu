@@ -9,9 +9,9 @@
 //   D2    = Lm . x                          128 x  64 x 128   Lm[m,k] = CB[m,k] 2^(a_m - a_k) dt_k, k <= m
 //   y[m,p]   = sC 2^(a_m) D1 + sx[p] (D2 + D x)            s <- 2^r s + sB sx[p] S_loc
 //
-// a_l is the running sum of dt*A*log2(e) inside the block and r its last value, so every exponent is <= 0.  Two small
-// preparation kernels run first: one widens B and C (shared by all heads of a group) to fp16 once -- values stay the
-// raw integers, scales are applied in the epilogues -- the other evaluates softplus / the running sums and leaves, per
+// a_l is the running sum of dt*A*log2(e) inside the block and r its last value, so every exponent is <= 0.  One small
+// preparation kernel runs first: some of its blocks widen B and C (shared by all heads of a group) to fp16 once -- values
+// stay the raw integers, scales are applied in the epilogues -- the others evaluate softplus / the running sums and leave, per
 // (batch, head, block), the vectors a[128], bk[128] = a - log2(dt) - log2(sC sB) and ec[128] (column factors of the
 // off-diagonal 32 x 32 chunks of Lm: there 2^(a_m - bk_k) = 2^(a_m - a_end(chunk)) * ec[k], two multiplies instead of
 // an ex2 per element; the diagonal chunks keep the exact per-element exponent).  When D has one value per head it is
@@ -82,7 +82,7 @@ constexpr int kHandoffFloats = kCompute * 16;  // one fp32 state (64 x 128) per 
 constexpr uint32_t kColCB = 0, kColLm = 128, kColD2 = 192, kColS = 256, kColD1 = 320, kColD1b = 384, kTmemCols = 512;
 
 struct Misc {
-  float ab[2][kAbVecs * T];   // per stage: a, bk, ec of the block (see ssd_dt_kernel)
+  float ab[2][kAbVecs * T];   // per stage: a, bk, ec of the block (see ssd_dt)
   float sx[P];                // x scale per channel
   float dsx[P];               // D * sx per channel
   float sbx[P];               // sB * sx per channel
@@ -665,10 +665,10 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
 }
 
 // B, C int8 (B, L, G, N) -> fp16 [B][L][G][N] contiguous (values unchanged).
-__global__ void ssd_widen_bc_kernel(const int8_t* __restrict__ Bq, int64_t B_sb, int64_t B_sl, int64_t B_sg,
-                                    const int8_t* __restrict__ Cq, int64_t C_sb, int64_t C_sl, int64_t C_sg,
-                                    __half* __restrict__ B16, __half* __restrict__ C16, int batch, int seqlen, int ngroups) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 16-element piece
+__device__ __forceinline__ void ssd_widen_bc(int64_t block, const int8_t* __restrict__ Bq, int64_t B_sb, int64_t B_sl, int64_t B_sg,
+                                             const int8_t* __restrict__ Cq, int64_t C_sb, int64_t C_sl, int64_t C_sg,
+                                             __half* __restrict__ B16, __half* __restrict__ C16, int batch, int seqlen, int ngroups) {
+  const int64_t idx = block * blockDim.x + threadIdx.x;  // one 16-element piece
   const int pieces = N / 16;
   const int64_t total = (int64_t)batch * seqlen * ngroups * pieces;
   if (idx >= total) return;
@@ -694,15 +694,18 @@ __global__ void ssd_widen_bc_kernel(const int8_t* __restrict__ Bq, int64_t B_sb,
 // Per (batch, head, 128-token block): dt = clamp(softplus(s_dt q + bias)); a = inclusive running sum of
 // dt * A * log2(e) inside the block; bk = a - log2(dt) - log2(sC sB) (+inf where dt == 0, i.e. past the
 // end of the sequence).  One warp per block, four tokens per lane.
-__global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb, int* __restrict__ flags, int nflags) {
-  if (blockIdx.x == 0)   // the hand-off flags of the main kernel, which follows on the same stream
+__device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, float* __restrict__ ab_ws, int nb, int* __restrict__ flags,
+                                       int nflags) {
+  if (block == 0)   // the hand-off flags of the main kernel, which follows on the same stream
     for (int i = threadIdx.x; i < nflags; i += blockDim.x) flags[i] = 0;
-  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t unit = block * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int64_t units = (int64_t)a.batch * a.nheads * nb;
   if (unit >= units) return;
-  const int j = (int)(unit % nb);
-  const int h = (int)((unit / nb) % a.nheads);
+  // heads vary fastest across the warps of a block: dt is (batch, seqlen, nheads) with the head innermost, so the eight
+  // warps of a block read neighbouring bytes of the same sectors
+  const int h = (int)(unit % a.nheads);
+  const int j = (int)((unit / a.nheads) % nb);
   const int b = (int)(unit / ((int64_t)nb * a.nheads));
   const int g = h / (a.nheads / a.ngroups);
   const float A2 = -__expf((*a.A_scale) * (float)a.A_log[h]) * 1.4426950408889634f;
@@ -732,7 +735,7 @@ __global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb, 
     if (lane >= o) incl += u;
   }
   const float pre = incl - run;
-  float* dst = ab_ws + unit * (kAbVecs * T);
+  float* dst = ab_ws + (((int64_t)b * a.nheads + h) * nb + j) * (kAbVecs * T);
   float4 av, bv;
   float* ap = reinterpret_cast<float*>(&av);
   float* bp = reinterpret_cast<float*>(&bv);
@@ -751,6 +754,17 @@ __global__ void ssd_dt_kernel(qb_ssd_args a, float* __restrict__ ab_ws, int nb, 
   reinterpret_cast<float4*>(dst)[lane] = av;
   reinterpret_cast<float4*>(dst + T)[lane] = bv;
   reinterpret_cast<float4*>(dst + 2 * T)[lane] = ev;
+}
+
+// Both preparation steps in one launch (256 threads per block): the first widen_blocks blocks widen B and C, the rest
+// evaluate the per-block vectors, eight (batch, head, block) units per block.
+__global__ void __launch_bounds__(256) ssd_prep_kernel(qb_ssd_args a, __half* __restrict__ B16, __half* __restrict__ C16,
+                                                       float* __restrict__ ab_ws, int nb, int* __restrict__ flags, int nflags,
+                                                       int widen_blocks) {
+  if ((int)blockIdx.x < widen_blocks)
+    ssd_widen_bc(blockIdx.x, a.Bm, a.B_sb, a.B_sl, a.B_sg, a.Cm, a.C_sb, a.C_sl, a.C_sg, B16, C16, a.batch, a.seqlen, a.ngroups);
+  else
+    ssd_dt((int64_t)blockIdx.x - widen_blocks, a, ab_ws, nb, flags, nflags);
 }
 
 int64_t align256l(int64_t v) { return (v + 255) & ~(int64_t)255; }
@@ -785,14 +799,11 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   float* handoff = reinterpret_cast<float*>(ws + 2 * half_bytes + ab_bytes);
   int* flags = reinterpret_cast<int*>(ws + 2 * half_bytes + ab_bytes + align256l((int64_t)kMaxCtas * kHandoffFloats * 4));
   {
-    const int64_t total = (int64_t)a->batch * a->seqlen * a->ngroups * (N / 16);
-    ssd_widen_bc_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(a->Bm, a->B_sb, a->B_sl, a->B_sg, a->Cm, a->C_sb,
-                                                                       a->C_sl, a->C_sg, B16, C16, a->batch, a->seqlen,
-                                                                       a->ngroups);
-    QB_LAUNCH_OK("ssd_widen_bc_kernel");
+    const int64_t pieces = (int64_t)a->batch * a->seqlen * a->ngroups * (N / 16);
     const int64_t units = (int64_t)a->batch * a->nheads * nb;
-    ssd_dt_kernel<<<(unsigned)ceil_div(units, 4), 128, 0, st>>>(*a, ab_ws, nb, flags, kMaxCtas);
-    QB_LAUNCH_OK("ssd_dt_kernel");
+    const int widen_blocks = (int)ceil_div(pieces, 256);
+    ssd_prep_kernel<<<(unsigned)(widen_blocks + ceil_div(units, 8)), 256, 0, st>>>(*a, B16, C16, ab_ws, nb, flags, kMaxCtas, widen_blocks);
+    QB_LAUNCH_OK("ssd_prep_kernel");
   }
   CUtensorMap tb, tcm;
   const uint64_t dims[4] = {(uint64_t)N, (uint64_t)a->ngroups, (uint64_t)a->seqlen, (uint64_t)a->batch};
