@@ -35,6 +35,12 @@ WORKLOAD = ("configs[1]: Mamba2 int8 causal_conv1d + SSD chunk scan, batch 4, se
             "ngroups 1, d_state 128, chunk 256, d_conv 4")
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one ssd_tc_kernel launch, from an ncu pass over this very benchmark
+# (batch 4: 66.0 MB read + 51.9 MB written; it grows with the number of (batch, head) pairs, hence per batch row).  Reads
+# are the inputs plus the widened B / C; of the 86 MB the kernel writes, part is still dirty in the 126 MB L2 when it ends.
+SSD_TRAFFIC_PER_BATCH_ROW = (65.99e6 + 51.86e6) / 4
+
+
 def algorithmic_bytes():
     B, L, H, P, G, N, W = (CFG[k] for k in "BLHPGNW")
     C = H * P + 2 * G * N
@@ -333,7 +339,7 @@ def main():
                 "d2h_bytes_per_step": int(host_y.numel() * 2 + host_f.numel())},
         "gpu_launches": 3 * steps,
         "roofline": {"kernel": "ssd_tc_kernel (+ ssd_prep_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": ssd_gbs / hbm_peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     "frac": ssd_gbs / hbm_peak, "traffic": SSD_TRAFFIC_PER_BATCH_ROW * B, "peak_source": "measured" if peaks else "fallback",
                      "algorithmic_bytes": ssd_bytes, "ms": ssd_ms,
                      "conv1d": {"achieved": conv_gbs, "frac": conv_gbs / hbm_peak, "algorithmic_bytes": conv_bytes, "ms": conv_ms}},
         "clocks": clocks,
