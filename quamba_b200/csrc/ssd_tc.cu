@@ -71,11 +71,15 @@ constexpr int kOffY = 11 * kAtom;              // output staging: one 1 KB tile 
 constexpr int kOffX8 = 12 * kAtom;             // 2 stages x 8 KB: the int8 x tile of a block (128 rows x 64 bytes)
 constexpr int kXBytes = T * P;
 constexpr int kOffMisc = 13 * kAtom;           // vectors + barriers
-constexpr int kMiscBytes = 4096;
+constexpr int kMiscBytes = 8192;
 constexpr int kSmemBytes = kOffMisc + kMiscBytes + 1024;
 constexpr int kAbVecs = 3;                     // a[128], bk[128], ec[128] per block, fp32
 constexpr int kAbBytes = kAbVecs * T * 4;
 constexpr int kHandoffFloats = kCompute * 16;  // one fp32 state (64 x 128) per CTA, thread-major
+// Per (batch, head) constants, written by the preparation kernel and delivered with every block's stage, so that moving
+// on to another pair costs the compute warps nothing: sx[64], D sx[64], sB sx[64], then the scalars below.
+constexpr int kHcFloats = 256, kHcBytes = kHcFloats * 4;
+constexpr int kHcSx = 0, kHcDsx = 64, kHcSbx = 128, kHcDfold = 192, kHcSC = 193, kHcLscb = 194, kHcStateScale = 195;
 
 // Tensor memory: CB (fp32), Lm (packed fp16, 64 columns), D2, S, and D1 double-buffered (GEMM2(k+1) is issued while the
 // output step of block k still has D1(k) to read).
@@ -83,10 +87,7 @@ constexpr uint32_t kColCB = 0, kColLm = 128, kColD2 = 192, kColS = 256, kColD1 =
 
 struct Misc {
   float ab[2][kAbVecs * T];   // per stage: a, bk, ec of the block (see ssd_dt)
-  float sx[P];                // x scale per channel
-  float dsx[P];               // D * sx per channel
-  float sbx[P];               // sB * sx per channel
-  float dfold;                // D of this head when it is one value per head (added on the diagonal of Lm), else 0
+  float hc[2][kHcFloats];     // per stage: the constants of the block's (batch, head) pair (kHc* offsets)
   uint64_t bc_full[2], bc_empty[2], ab_empty[2];
   uint64_t cb_ready, xops_ready, s_ready, lm_ready, y_ready, s16_ready, d1_ready;
   uint32_t tmem_slot;
@@ -209,7 +210,7 @@ __device__ __forceinline__ void issue_gemm(uint32_t d_tmem, SmemDesc a, SmemDesc
 __global__ void __launch_bounds__(kThreads, 1)
 ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant__ CUtensorMap tm_c16,
               const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_out, qb_ssd_args a,
-              const float* __restrict__ ab_ws, float* __restrict__ handoff, int* __restrict__ flags, int split, int* status) {
+              const float* __restrict__ ab_ws, const float* __restrict__ hc_ws, float* __restrict__ handoff, int* __restrict__ flags, int split, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Misc& ms = *reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -251,10 +252,11 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           const uint32_t par = ((it >> 1) & 1) ^ 1;
           ok = mbar_wait(&ms.bc_empty[st], par, status, QB_ERR_TIMEOUT) && mbar_wait(&ms.ab_empty[st], par, status, QB_ERR_TIMEOUT);
           if (!ok) break;
-          mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes + kXBytes);
+          mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes + kXBytes + kHcBytes);
           uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
           uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
           bulk_load(ms.ab[st], ab_src + (int64_t)j * (kAbVecs * T), kAbBytes, &ms.bc_full[st]);
+          bulk_load(ms.hc[st], hc_ws + (int64_t)im.unit * kHcFloats, kHcBytes, &ms.bc_full[st]);
           tma_load_4d(dB, &tm_b16, &ms.bc_full[st], 0, g, j * T, b);
           tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, j * T, b);
           tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, j * T, b);
@@ -377,28 +379,9 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     for (int ii = 0; ii < plan.n_items && ok; ++ii) {
       const Item im = get_item(plan, ii, nb);
       const int b = im.unit / a.nheads, h = im.unit % a.nheads, g = h / hpg;
-      const float sB = a.grouped ? a.B_scale[g] : a.B_scale[0];
-      const float sC = a.grouped ? a.C_scale[g] : a.C_scale[0];
-      const float lscb = fast_log2(sC * sB);
       const int8_t* xrow_base = a.x + (int64_t)b * a.x_sb + (int64_t)h * a.x_sh + 16 * sub;
-      gsync();   // every warp is past its last read of the per-head vectors of the previous item
-      if (ctid < P) {
-        const int p = ctid;
-        float sx;
-        if (!a.grouped) {
-          sx = a.x_scales[0];
-        } else {
-          const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
-          const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
-          sx = a.x_scales[(g * a.nhead_groups + hg) * a.ndim_groups + dg];
-        }
-        float dv = 0.0f;
-        if (a.D != nullptr) dv = (*a.D_scale) * (float)(a.D_has_hdim ? a.D[h * P + p] : a.D[h]);
-        ms.sx[p] = sx;
-        ms.dsx[p] = dv * sx;
-        ms.sbx[p] = sB * sx;
-        if (p == 0) ms.dfold = (a.D != nullptr && !a.D_has_hdim) ? (*a.D_scale) * (float)a.D[h] : 0.0f;
-      }
+      // The constants of the pair arrive with every block's stage, so nothing has to be set up here for a pair that
+      // starts from the zero state: no barrier, no global loads, no cold code.
       if (im.has_init) {
         // the state after the head part of this pair, published by the previous CTA early in its life
         uint32_t got = 1;
@@ -422,13 +405,14 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         }
         store_s16();   // GEMM2 of the previous block has completed: the state step that followed it waited for d1_ready
         fence_proxy_async_smem();
+        gsync();
       } else {
 #pragma unroll
         for (int t = 0; t < 16; ++t) s_reg[t] = 0.0f;
       }
-      gsync();
+      // s16_ready also tells the MMA issuer that the S accumulator of the previous block has been read: every warp did
+      // that before the barrier that opened its output step.
       if (lead) mbar_arrive(&ms.s16_ready);
-      const float dfold = ms.dfold;
 
       for (int j = im.jb; j < im.je; ++j, ++it) {
         const int st = it & 1;
@@ -441,8 +425,13 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (lead) TRACE(0, it, 0);
         ok = gwait(&ms.bc_full[st], (it >> 1) & 1, nullptr, 0);   // x, B, C and the vectors of this block have landed
         if (!ok) break;
+        // The vectors and constants of the previous block are read up to the end of its output step, which every warp
+        // has left by now; its B / C / x tiles were released by the MMA issuer.
+        if (lead && it > 0) mbar_arrive(&ms.ab_empty[(it - 1) & 1]);
         if (lead) TRACE(0, it, 1);
         const float* av = ms.ab[st];
+        const float* hc = ms.hc[st];
+        const float lscb = hc[kHcLscb], sC = hc[kHcSC], dfold = hc[kHcDfold];
         {
           const uint4 xq = *reinterpret_cast<const uint4*>(smem + kOffX8 + st * kXBytes + prow * P + piece * 16);
           const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
@@ -527,7 +516,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         tmem_st_wait();
         tc_fence_before_sync();
         gsync();
-        if (lead) { mbar_arrive(&ms.lm_ready); mbar_arrive(&ms.ab_empty[st]); TRACE(0, it, 4); }
+        if (lead) { mbar_arrive(&ms.lm_ready); TRACE(0, it, 4); }
 
         // ================= P3: state: s <- 2^r s + sB sx S_loc ; publish its fp16 copy for the next block ==============
         // s_ready: GEMM4(it) done.  d1_ready: GEMM2(it) done, so the fp16 state tile it read may be rewritten.
@@ -540,7 +529,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           uint32_t sl[16];
           tmem_ld_32x16(tmem + tlane + kColS + 16 * sub, sl);
           tmem_ld_wait();
-          const float4* sb4 = reinterpret_cast<const float4*>(ms.sbx + 16 * sub);
+          const float4* sb4 = reinterpret_cast<const float4*>(hc + kHcSbx + 16 * sub);
 #pragma unroll
           for (int t4 = 0; t4 < 4; ++t4) {
             const float4 sc = sb4[t4];
@@ -571,7 +560,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           if (use_d1) tmem_ld_32x16(tmem + tlane + (st ? kColD1b : kColD1) + 16 * sub, d1);
           tmem_ld_wait();
           tc_fence_before_sync();
-          const float4* sx4 = reinterpret_cast<const float4*>(ms.sx + 16 * sub);
+          const float4* sx4 = reinterpret_cast<const float4*>(hc + kHcSx + 16 * sub);
           const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
           uint4 c2[2];
 #pragma unroll
@@ -592,7 +581,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
                 y3 = fmaf(e_out, __uint_as_float(d1[4 * t4 + 3]), y3);
               }
               if (d_per_channel) {
-                const float4 dx = reinterpret_cast<const float4*>(ms.dsx + 16 * sub)[t4];
+                const float4 dx = reinterpret_cast<const float4*>(hc + kHcDsx + 16 * sub)[t4];
                 __half2 h01, h23;
                 s8x4_to_h2x2(xwd[t4], h01, h23);
                 const float2 x01 = __half22float2(h01), x23 = __half22float2(h23);
@@ -644,7 +633,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           const int p = 16 * sub + t;
           float ss;
           if (!a.grouped) {
-            ss = a.ssm_state_scale[0];
+            ss = ms.hc[(it - 1) & 1][kHcStateScale];   // the stage of the item's last block is still in place
           } else {
             const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
             ss = a.ssm_state_scale[((int64_t)(g * a.nhead_groups + hg) * a.ndim_groups + dg) * N + row];
@@ -694,8 +683,8 @@ __device__ __forceinline__ void ssd_widen_bc(int64_t block, const int8_t* __rest
 // Per (batch, head, 128-token block): dt = clamp(softplus(s_dt q + bias)); a = inclusive running sum of
 // dt * A * log2(e) inside the block; bk = a - log2(dt) - log2(sC sB) (+inf where dt == 0, i.e. past the
 // end of the sequence).  One warp per block, four tokens per lane.
-__device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, float* __restrict__ ab_ws, int nb, int* __restrict__ flags,
-                                       int nflags) {
+__device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, float* __restrict__ ab_ws, float* __restrict__ hc_ws, int nb,
+                                       int* __restrict__ flags, int nflags) {
   if (block == 0)   // the hand-off flags of the main kernel, which follows on the same stream
     for (int i = threadIdx.x; i < nflags; i += blockDim.x) flags[i] = 0;
   const int64_t unit = block * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -711,7 +700,36 @@ __device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, floa
   const float A2 = -__expf((*a.A_scale) * (float)a.A_log[h]) * 1.4426950408889634f;
   const float s_dt = *a.dt_scale;
   const float bias = a.dt_bias != nullptr ? __half2float(static_cast<const __half*>(a.dt_bias)[h]) : 0.0f;
-  const float lscb = fast_log2((a.grouped ? a.C_scale[g] : a.C_scale[0]) * (a.grouped ? a.B_scale[g] : a.B_scale[0]));
+  const float sBg = a.grouped ? a.B_scale[g] : a.B_scale[0], sCg = a.grouped ? a.C_scale[g] : a.C_scale[0];
+  const float lscb = fast_log2(sCg * sBg);
+  if (j == 0) {
+    // the constants of this (batch, head) pair: two channels per lane, the scalars by lane 0
+    float* hc = hc_ws + ((int64_t)b * a.nheads + h) * kHcFloats;
+    const int hpg = a.nheads / a.ngroups;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int p = lane + 32 * i;
+      float sx;
+      if (!a.grouped) {
+        sx = a.x_scales[0];
+      } else {
+        const int hg = group_lookup(a.head_group_range + g * a.nhead_groups, a.nhead_groups, h % hpg);
+        const int dg = group_lookup(a.dim_group_range + (g * a.nhead_groups + hg) * a.ndim_groups, a.ndim_groups, p);
+        sx = a.x_scales[(g * a.nhead_groups + hg) * a.ndim_groups + dg];
+      }
+      float dv = 0.0f;
+      if (a.D != nullptr) dv = (*a.D_scale) * (float)(a.D_has_hdim ? a.D[h * P + p] : a.D[h]);
+      hc[kHcSx + p] = sx;
+      hc[kHcDsx + p] = dv * sx;
+      hc[kHcSbx + p] = sBg * sx;
+    }
+    if (lane == 0) {
+      hc[kHcDfold] = (a.D != nullptr && !a.D_has_hdim) ? (*a.D_scale) * (float)a.D[h] : 0.0f;
+      hc[kHcSC] = sCg;
+      hc[kHcLscb] = lscb;
+      hc[kHcStateScale] = a.grouped ? 1.0f : a.ssm_state_scale[0];
+    }
+  }
   const int8_t* dtp = a.dt + (int64_t)b * a.dt_sb + h;
   float dt[4], cs[4];
   float run = 0.0f;
@@ -759,12 +777,12 @@ __device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, floa
 // Both preparation steps in one launch (256 threads per block): the first widen_blocks blocks widen B and C, the rest
 // evaluate the per-block vectors, eight (batch, head, block) units per block.
 __global__ void __launch_bounds__(256) ssd_prep_kernel(qb_ssd_args a, __half* __restrict__ B16, __half* __restrict__ C16,
-                                                       float* __restrict__ ab_ws, int nb, int* __restrict__ flags, int nflags,
-                                                       int widen_blocks) {
+                                                       float* __restrict__ ab_ws, float* __restrict__ hc_ws, int nb,
+                                                       int* __restrict__ flags, int nflags, int widen_blocks) {
   if ((int)blockIdx.x < widen_blocks)
     ssd_widen_bc(blockIdx.x, a.Bm, a.B_sb, a.B_sl, a.B_sg, a.Cm, a.C_sb, a.C_sl, a.C_sg, B16, C16, a.batch, a.seqlen, a.ngroups);
   else
-    ssd_dt((int64_t)blockIdx.x - widen_blocks, a, ab_ws, nb, flags, nflags);
+    ssd_dt((int64_t)blockIdx.x - widen_blocks, a, ab_ws, hc_ws, nb, flags, nflags);
 }
 
 int64_t align256l(int64_t v) { return (v + 255) & ~(int64_t)255; }
@@ -785,7 +803,7 @@ bool ssd_tc_eligible(const qb_ssd_args* a) {
 int64_t ssd_tc_workspace_bytes(int B, int L, int H, int G) {
   const int64_t nb = (L + T - 1) / T;
   return 2 * align256l((int64_t)B * L * G * N * 2) + align256l((int64_t)B * H * nb * kAbVecs * T * 4) +
-         align256l((int64_t)kMaxCtas * kHandoffFloats * 4) + align256l(kMaxCtas * 4);
+         align256l((int64_t)kMaxCtas * kHandoffFloats * 4) + align256l(kMaxCtas * 4) + align256l((int64_t)B * H * kHcBytes);
 }
 
 int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
@@ -798,11 +816,12 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   float* ab_ws = reinterpret_cast<float*>(ws + 2 * half_bytes);
   float* handoff = reinterpret_cast<float*>(ws + 2 * half_bytes + ab_bytes);
   int* flags = reinterpret_cast<int*>(ws + 2 * half_bytes + ab_bytes + align256l((int64_t)kMaxCtas * kHandoffFloats * 4));
+  float* hc_ws = reinterpret_cast<float*>(reinterpret_cast<char*>(flags) + align256l(kMaxCtas * 4));
   {
     const int64_t pieces = (int64_t)a->batch * a->seqlen * a->ngroups * (N / 16);
     const int64_t units = (int64_t)a->batch * a->nheads * nb;
     const int widen_blocks = (int)ceil_div(pieces, 256);
-    ssd_prep_kernel<<<(unsigned)(widen_blocks + ceil_div(units, 8)), 256, 0, st>>>(*a, B16, C16, ab_ws, nb, flags, kMaxCtas, widen_blocks);
+    ssd_prep_kernel<<<(unsigned)(widen_blocks + ceil_div(units, 8)), 256, 0, st>>>(*a, B16, C16, ab_ws, hc_ws, nb, flags, kMaxCtas, widen_blocks);
     QB_LAUNCH_OK("ssd_prep_kernel");
   }
   CUtensorMap tb, tcm;
@@ -843,7 +862,7 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   const int pairs = a->batch * a->nheads;
   const int ctas = std::min(std::min(sm_count(), kMaxCtas), pairs);
   const int split = pairs >= ctas && ctas == std::min(sm_count(), kMaxCtas) ? 1 : 0;
-  ssd_tc_kernel<<<(unsigned)ctas, kThreads, kSmemBytes, st>>>(tb, tcm, tx, tout, *a, ab_ws, handoff, flags, split, status);
+  ssd_tc_kernel<<<(unsigned)ctas, kThreads, kSmemBytes, st>>>(tb, tcm, tx, tout, *a, ab_ws, hc_ws, handoff, flags, split, status);
   QB_LAUNCH_OK("ssd_tc_kernel");
   return QB_OK;
 }
