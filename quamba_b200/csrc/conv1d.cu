@@ -271,13 +271,15 @@ conv1d_update_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd,
 }
 
 int pick_tl(int64_t rows_of_vectors, int seqlen) {
-  // Largest time tile that still gives every SM ~32 resident warps; the 3-row halo re-read costs 3/TL extra L2
-  // traffic, so prefer long tiles when the problem is large enough.
-  const int64_t want = (int64_t)sm_count() * 32 * 32;
-  for (int tl = 128; tl >= 8; tl >>= 1) {
-    if (rows_of_vectors * ceil_div(seqlen, tl) >= want) return tl;
-  }
-  return 8;
+  // The time tile that fills ONE wave: at 64 registers an SM holds four 256-thread CTAs, and a grid of 1.1 waves runs
+  // as long as one of 2 (a 672-CTA launch on 592 slots spent half its time on the last 80 CTAs).  So: as many segments
+  // as fit in one wave, tiles rounded up to the unroll factor; larger problems than one wave take whole sequences.
+  const int64_t wave_threads = (int64_t)sm_count() * 4 * kClBlock;
+  int64_t nseg = wave_threads / rows_of_vectors;
+  if (nseg < 1) nseg = 1;
+  int tl = (int)ceil_div((int64_t)seqlen, nseg);
+  tl = (tl + 7) & ~7;
+  return tl < 8 ? 8 : tl;
 }
 
 int launch_channel_last(const int8_t* in, int64_t in_sb, int64_t in_sl, const int8_t* weight, const int8_t* bias,
