@@ -174,8 +174,11 @@ constexpr int PBN = 256;
 constexpr int kPStages = 4;
 constexpr int kPStageBytes = BM * BK + PBN * BK;   // 16 KB of A + 32 KB of W
 constexpr int kPSmemBytes = kPStages * kPStageBytes + 1024 + 256;
+// Eight epilogue warps (two per TMEM lane quarter, 128 columns each): with four, converting and storing a 128 x 256
+// tile took about as long as the main loop of a K = 2560 tile and the MMA issuer waited for its accumulator.
+constexpr int kPThreads = 64 + 256;
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kPThreads, 1)
 gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                                   int M, int N, int K, Epilogue ep, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -257,30 +260,32 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;   // which 128 columns of the tile
     const bool lead = warp == 2 && lane == 0;
     for (int i = 0; i < my_tiles; ++i) {
       const int b = i & 1;
       const int t = blockIdx.x + i * gridDim.x;
       const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * PBN;
-      // one thread polls, the four warps meet at a named barrier that also carries the outcome
+      // one thread polls, the eight warps meet at a named barrier that also carries the outcome
       uint32_t ok = 1;
       if (lead) ok = mbar_wait(&acc_full[b], (uint32_t)((i >> 1) & 1), status, QB_ERR_TIMEOUT) ? 1u : 0u;
       uint32_t all_ok;
-      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                    : "=r"(all_ok) : "r"(ok) : "memory");
       if (!all_ok) break;
       tc_fence_after_sync();
       const int m = m0 + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * PBN);
+      const int c_end = half * (PBN / 2) + PBN / 2;
 #pragma unroll 1
-      for (int c = 0; c < PBN; c += 64) {
+      for (int c = half * (PBN / 2); c < c_end; c += 64) {
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(acc + (uint32_t)c, r0);
         tmem_ld_32x32(acc + (uint32_t)c + 32, r1);
         tmem_ld_wait();
-        if (c + 64 >= PBN) {  // the last columns are in registers: hand the accumulator back before storing them
+        if (c + 64 >= c_end) {  // the last columns are in registers: hand the accumulator back before storing them
           tc_fence_before_sync();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync 1, 256;" ::: "memory");
           if (lead) mbar_arrive(&acc_empty[b]);
         }
         store_chunk(r0, m, n0 + c, M, N, ep);
@@ -374,7 +379,7 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
       if (dev < 64) pattr_set[dev] = true;
     }
     const unsigned grid = (unsigned)std::min<int64_t>(ptiles, sm_count());
-    gemm_s8_tcgen05_persistent_kernel<<<grid, kThreads, kPSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
+    gemm_s8_tcgen05_persistent_kernel<<<grid, kPThreads, kPSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
     QB_LAUNCH_OK("gemm_s8_tcgen05_persistent_kernel");
     return QB_OK;
   }
