@@ -16,8 +16,9 @@
 // B operand is H_S, zero-padded to Spad = ceil16(S).  The same four warps then scale, round half away from zero,
 // saturate and store the bytes: lane j' holds out[r, c' * 128 + j'], so a warp writes one full 32-byte sector per store.
 //
-// One persistent CTA per SM, 320 threads: warp 0 = TMA producer (three stages), warp 1 = MMA issuer and TMEM owner,
-// warps 2..5 and 6..9 = two converter / epilogue groups, each with its own half of TMEM (D, hi, lo), working on
+// One persistent CTA per SM, 576 threads: warp 0 = TMA producer (three stages), warp 1 = MMA issuer and TMEM owner,
+// warps 2..9 and 10..17 = two converter / epilogue groups (two warps per TMEM lane quarter, half of the rows each),
+// each group with its own half of TMEM (D, hi, lo), working on
 // alternating units of R rows.  Every mbarrier wait is bounded.
 #include <algorithm>
 #include "tc_common.cuh"
@@ -27,7 +28,7 @@ namespace qb {
 namespace {
 using namespace tc;
 
-constexpr int kThreadsH = 320;
+constexpr int kThreadsH = 64 + 512;   // TMA warp, MMA warp, two converter / epilogue groups of eight warps
 constexpr int kStages = 3;
 constexpr int kOffH128 = 0;                    // 2 atoms: 128 rows x 128 B each (K 0..63, 64..127)
 constexpr int kOffHS = 32768;                  // 1 atom: up to 64 rows x 128 B
@@ -190,24 +191,27 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
     }
   } else {
     // ---------------- converter / epilogue groups ----------------
-    const int g = (warp - 2) >> 2;                 // 0 or 1
+    const int g = (warp - 2) >> 3;                 // 0 or 1
+    const int sub = ((warp - 2) >> 2) & 1;         // which half of the unit's R rows (two warps share a TMEM lane quarter)
     const int q = warp & 3;                        // TMEM lane quarter this warp may touch
+    constexpr int RH = R / 2;
+    static_assert(R % 2 == 0, "the rows of a unit are split between two warps");
     const int jrow = q * 32 + lane;                // j' : lane of TMEM = position inside a 128-chunk of the output row
     const uint32_t tl = (uint32_t)(q * 32) << 16;
-    const bool lead = (warp - 2) % 4 == 0 && lane == 0;
+    const bool lead = (warp - 2) % 8 == 0 && lane == 0;
     auto gsync = [&]() {
-      if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-      else asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (g == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
     };
     auto gwait = [&](uint64_t* bar, uint32_t parity) -> bool {
       uint32_t ok = 1;
       if (lead) ok = mbar_wait(bar, parity, status, kStatusHad) ? 1u : 0u;
       uint32_t r;
       if (g == 0)
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                      : "=r"(r) : "r"(ok) : "memory");
       else
-        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                      : "=r"(r) : "r"(ok) : "memory");
       return r != 0;
     };
@@ -220,22 +224,23 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
       tc_fence_after_sync();
       {
         // all loads of the unit first, one wait: the accumulators of R rows are R * SPAD registers
-        uint32_t v[R][SPAD / 16][16];
+        uint32_t v[RH][SPAD / 16][16];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+        for (int rr = 0; rr < RH; ++rr)
 #pragma unroll
-          for (int c16 = 0; c16 < SPAD / 16; ++c16) tmem_ld16(base + r * S + c16 * 16, v[r][c16]);
+          for (int c16 = 0; c16 < SPAD / 16; ++c16) tmem_ld16(base + (sub * RH + rr) * S + c16 * 16, v[rr][c16]);
         tmem_ld_wait();
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
+        for (int rr = 0; rr < RH; ++rr) {
+          const int r = sub * RH + rr;
 #pragma unroll
           for (int c16 = 0; c16 < SPAD / 16; ++c16) {
             uint32_t hi[8], lo[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               const int c = c16 * 16 + 2 * e;
-              const float f0 = c < S ? __uint_as_float(v[r][c16][2 * e]) : 0.0f;      // columns past S belong to the next row
-              const float f1 = c + 1 < S ? __uint_as_float(v[r][c16][2 * e + 1]) : 0.0f;
+              const float f0 = c < S ? __uint_as_float(v[rr][c16][2 * e]) : 0.0f;     // columns past S belong to the next row
+              const float f1 = c + 1 < S ? __uint_as_float(v[rr][c16][2 * e + 1]) : 0.0f;
               const __half2 h = __floats2half2_rn(f0, f1);
               const float2 hf = __half22float2(h);
               const __half2 l = __floats2half2_rn(f0 - hf.x, f1 - hf.y);
@@ -255,19 +260,19 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
       if (!gwait(&bars.d2_ready[g], ph)) break;
       tc_fence_after_sync();
       {
-        uint32_t v[R][SPAD / 16][16];
+        uint32_t v[RH][SPAD / 16][16];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+        for (int rr = 0; rr < RH; ++rr)
 #pragma unroll
-          for (int c16 = 0; c16 < SPAD / 16; ++c16) tmem_ld16(base + r * SPAD + c16 * 16, v[r][c16]);
+          for (int c16 = 0; c16 < SPAD / 16; ++c16) tmem_ld16(base + (sub * RH + rr) * SPAD + c16 * 16, v[rr][c16]);
         tmem_ld_wait();
         // the accumulators are in registers: hand the buffer back before the stores
         tc_fence_before_sync();
         gsync();
         if (lead) mbar_arrive(&bars.buf_free[g]);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const int64_t row = u * R + r;
+        for (int rr = 0; rr < RH; ++rr) {
+          const int64_t row = u * R + sub * RH + rr;
           int8_t* dst = out + row * out_rs + jrow;
           if (row < rows) {
 #pragma unroll
@@ -276,7 +281,7 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
               for (int e = 0; e < 16; ++e) {
                 const int c = c16 * 16 + e;
                 if (c < S) {
-                  const float y = __uint_as_float(v[r][c16][e]) * scale128;
+                  const float y = __uint_as_float(v[rr][c16][e]) * scale128;
                   int qv;
                   asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(qv) : "f"(y + copysignf(0.5f, y)));
                   dst[c * 128] = (int8_t)qv;
