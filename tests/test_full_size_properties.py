@@ -81,6 +81,24 @@ def test_ssd_full_size_tensor_core_path_equals_portable_path(monkeypatch):
     assert d.max().item() <= 1 and (d > 0).float().mean().item() <= 0.03
 
 
+@pytest.mark.parametrize("Bsz,Ls,Hs", [(8, 300, 80), (64, 100, 16), (2, 700, 80), (5, 1025, 37)])
+def test_ssd_range_cuts_at_other_shapes(Bsz, Ls, Hs, monkeypatch):
+    """More (batch, head) pairs than SMs with 1, 3, 6 and 9 blocks per pair: the equal ranges then start and end in the
+    middle of pairs at other places than in the benchmark shape (one block per pair: no cut inside a pair at all)."""
+    c = make_ssd_case(Bsz, Ls, Hs, P, G, N, Q, seed=Ls)
+    y_tc, f_tc = run_ssd(c)
+    y_1, f_1 = run_ssd(c, slice(Bsz - 1, Bsz))          # fewer pairs than SMs: whole pairs per CTA
+    assert torch.equal(y_tc[Bsz - 1], y_1[0]) and torch.equal(f_tc[Bsz - 1], f_1[0])
+    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
+    y_pt, f_pt = run_ssd(c)
+    monkeypatch.delenv("QB_SSD_PORTABLE")
+    err = (y_tc.float() - y_pt.float()).abs()
+    tol = 1e-2 * y_pt.float().abs() + 1e-3 * y_pt.float().abs().max()
+    assert (err <= tol).all(), f"max err {err.max().item()}"
+    d = (f_tc.int() - f_pt.int()).abs()
+    assert d.max().item() <= 1 and (d > 0).float().mean().item() <= 0.03
+
+
 def run_conv(c, xBC):
     o = ops().quamba2_conv1d_cuda.fwd(dev(xBC), c["sx"], c["sB"], c["sC"], c["x_dim"], P, N, G, dev(c["hgr"]), dev(c["dgr"]),
                                       dev(c["x_scales"]), dev(c["B_scales"]), dev(c["C_scales"]), dev(c["weight"]), c["swx"], c["swB"],
