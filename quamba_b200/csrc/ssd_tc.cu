@@ -67,7 +67,7 @@ constexpr int kOffC16 = 4 * kAtom;             // 2 stages x 2 atoms
 constexpr int kOffXraw = 8 * kAtom;            // 1 atom
 constexpr int kOffXw = 9 * kAtom;              // 1 atom
 constexpr int kOffS16 = 10 * kAtom;            // 1 atom
-constexpr int kOffY = 11 * kAtom;              // output staging: one 1 KB tile (32 rows x 32 bytes) per compute warp
+constexpr int kOffY = 11 * kAtom;              // output staging: the fp16 y tile of a block, 128 rows x 128 bytes, swizzled
 constexpr int kOffX8 = 12 * kAtom;             // 2 stages x 8 KB: the int8 x tile of a block (128 rows x 64 bytes)
 constexpr int kXBytes = T * P;
 constexpr int kOffMisc = 13 * kAtom;           // vectors + barriers
@@ -90,6 +90,7 @@ struct Misc {
   float hc[2][kHcFloats];     // per stage: the constants of the block's (batch, head) pair (kHc* offsets)
   uint64_t bc_full[2], bc_empty[2], ab_empty[2];
   uint64_t cb_ready, xops_ready, s_ready, lm_ready, y_ready, s16_ready, d1_ready;
+  uint64_t y_full, y_empty;   // output staging tile: written by the 16 compute warps, stored (and released) by warp 2
   uint32_t tmem_slot;
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc does not fit");
@@ -223,6 +224,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 1); }
     mbar_init(&ms.cb_ready, 1); mbar_init(&ms.xops_ready, 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.lm_ready, 1);
     mbar_init(&ms.y_ready, 1); mbar_init(&ms.s16_ready, 1); mbar_init(&ms.d1_ready, 1);
+    mbar_init(&ms.y_full, 16); mbar_init(&ms.y_empty, 1);
     fence_barrier_init();
     prefetch_tensormap(&tm_b16);
     prefetch_tensormap(&tm_c16);
@@ -335,6 +337,28 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         }
       }
     }
+  } else if (warp == 2) {
+    // ---------------- output store ----------------
+    // One thread sends each block's y tile to global memory with a single TMA store (rows past the end of the sequence
+    // are clipped by the hardware) and hands the staging tile back once the store has read it.  The compute warps only
+    // write the tile: issuing the store and waiting for its read cost each of them several hundred cycles per block.
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int ii = 0; ii < plan.n_items && ok; ++ii) {
+        const Item im = get_item(plan, ii, nb);
+        const int b = im.unit / a.nheads, h = im.unit % a.nheads;
+        for (int j = im.jb; j < im.je; ++j, ++it) {
+          ok = mbar_wait(&ms.y_full, it & 1, status, QB_ERR_TIMEOUT);
+          if (!ok) break;
+          tma_store_4d(&tm_out, smem + kOffY, 0, h, j * T, b);
+          bulk_commit();
+          bulk_wait_read<0>();
+          mbar_arrive(&ms.y_empty);
+        }
+      }
+      bulk_wait_all<0>();   // every store is complete before the CTA exits
+    }
   } else if (warp >= 4) {
     // ---------------- compute warps ----------------
     const int cw = warp - 4;
@@ -347,7 +371,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     const bool lead = (threadIdx.x == kLead);
     // the x operands (P1) touch no tensor memory, so there a warp takes eight whole rows: lane -> (row, 16-byte piece)
     const int prow = 8 * cw + (lane >> 2), piece = lane & 3;
-    uint8_t* ytile = smem + kOffY + cw * 1024;
     auto gsync = [&]() { asm volatile("bar.sync 1, 512;" ::: "memory"); };
     auto gand = [&](uint32_t ok) -> bool {   // group barrier that ANDs a flag: a timed-out wait makes all warps leave together
       uint32_t r;
@@ -593,20 +616,19 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
             }
             c2[t8] = make_uint4(o[0], o[1], o[2], o[3]);
           }
-          // The warp's 32 rows x 32 bytes go to its staging tile (dense rows, unswizzled tensor map) and
-          // leave as one TMA store: rows past the end of the sequence are clipped by the hardware, and the LSU sees
-          // two shared-memory stores per thread instead of scattered 16-byte global stores.
-          if (lane == 0) bulk_wait_read<0>();   // the previous store of this warp has read the tile
-          __syncwarp();
-          reinterpret_cast<uint4*>(ytile + lane * 32)[0] = c2[0];
-          reinterpret_cast<uint4*>(ytile + lane * 32)[1] = c2[1];
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && j * T + q * 32 < a.seqlen) {
-            tma_store_4d(&tm_out, ytile, 16 * sub, h, j * T + q * 32, b);
-            bulk_commit();
+          // This thread's 32 bytes of the row go to the staging tile (128-byte swizzle, as the tensor map expects); the
+          // tile is free once the store of the previous block has read it, which happened a block ago.
+          if (it > 0 && !mbar_wait(&ms.y_empty, (it - 1) & 1, status, QB_ERR_TIMEOUT)) { ok = false; }
+          if (ok) {
+            uint8_t* yrow = smem + kOffY + row * 128;
+            *reinterpret_cast<uint4*>(yrow + (((2 * sub) ^ sw) << 4)) = c2[0];
+            *reinterpret_cast<uint4*>(yrow + (((2 * sub + 1) ^ sw) << 4)) = c2[1];
+            fence_proxy_async_smem();
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ms.y_full);
         }
+        if (!ok) break;
         if (lead) TRACE(0, it, 8);
       }
       if (!ok) break;
@@ -644,7 +666,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
       }
     }
   }
-  if (warp >= 4 && lane == 0) bulk_wait_all<0>();   // the output stores of this warp are complete
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -840,11 +861,11 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
     const uint32_t xb[4] = {(uint32_t)P, 1, (uint32_t)T, 1};
     rc = encode_tmap_4d(&tx, false, false, a->x, xd, xs, xb);
     if (rc != QB_OK) return rc;
-    // out fp16 (P, H, L, B) contiguous: 32 rows x 16 channels per store, dense 32-byte rows on the shared-memory side
+    // out fp16 (P, H, L, B) contiguous: one 128-row x 64-channel tile per store, 128-byte swizzle on the shared-memory side
     const uint64_t od[4] = {(uint64_t)P, (uint64_t)a->nheads, (uint64_t)a->seqlen, (uint64_t)a->batch};
     const uint64_t os[3] = {(uint64_t)P * 2, (uint64_t)a->nheads * P * 2, (uint64_t)a->seqlen * a->nheads * P * 2};
-    const uint32_t ob[4] = {16, 1, 32, 1};
-    rc = encode_tmap_4d(&tout, true, false, a->out, od, os, ob);
+    const uint32_t ob[4] = {(uint32_t)P, 1, (uint32_t)T, 1};
+    rc = encode_tmap_4d(&tout, true, true, a->out, od, os, ob);
     if (rc != QB_OK) return rc;
   }
   static bool attr_set[64] = {};
