@@ -239,6 +239,9 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ms.tmem_slot;
+  // The kernel is launched as a programmatic dependent of the preparation kernel: everything above overlaps its tail;
+  // from here on its results (widened B / C, vectors, constants, cleared flags) are read.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -800,6 +803,8 @@ __device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, floa
 __global__ void __launch_bounds__(256) ssd_prep_kernel(qb_ssd_args a, __half* __restrict__ B16, __half* __restrict__ C16,
                                                        float* __restrict__ ab_ws, float* __restrict__ hc_ws, int nb,
                                                        int* __restrict__ flags, int nflags, int widen_blocks) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the main kernel may start its prologue
+  asm volatile("griddepcontrol.wait;" ::: "memory");                // this kernel's inputs come from whatever ran before it
   if ((int)blockIdx.x < widen_blocks)
     ssd_widen_bc(blockIdx.x, a.Bm, a.B_sb, a.B_sl, a.B_sg, a.Cm, a.C_sb, a.C_sl, a.C_sg, B16, C16, a.batch, a.seqlen, a.ngroups);
   else
@@ -842,8 +847,16 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
     const int64_t pieces = (int64_t)a->batch * a->seqlen * a->ngroups * (N / 16);
     const int64_t units = (int64_t)a->batch * a->nheads * nb;
     const int widen_blocks = (int)ceil_div(pieces, 256);
-    ssd_prep_kernel<<<(unsigned)(widen_blocks + ceil_div(units, 8)), 256, 0, st>>>(*a, B16, C16, ab_ws, hc_ws, nb, flags, kMaxCtas, widen_blocks);
-    QB_LAUNCH_OK("ssd_prep_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(widen_blocks + ceil_div(units, 8)));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // its launch overlaps the tail of the kernel before it
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_prep_kernel, *a, B16, C16, ab_ws, hc_ws, nb, flags, (int)kMaxCtas, widen_blocks));
   }
   CUtensorMap tb, tcm;
   const uint64_t dims[4] = {(uint64_t)N, (uint64_t)a->ngroups, (uint64_t)a->seqlen, (uint64_t)a->batch};
@@ -883,8 +896,21 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   const int pairs = a->batch * a->nheads;
   const int ctas = std::min(std::min(sm_count(), kMaxCtas), pairs);
   const int split = pairs >= ctas && ctas == std::min(sm_count(), kMaxCtas) ? 1 : 0;
-  ssd_tc_kernel<<<(unsigned)ctas, kThreads, kSmemBytes, st>>>(tb, tcm, tx, tout, *a, ab_ws, hc_ws, handoff, flags, split, status);
-  QB_LAUNCH_OK("ssd_tc_kernel");
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may begin while ssd_prep_kernel drains
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* ab_c = ab_ws;
+    const float* hc_c = hc_ws;
+    QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status));
+  }
   return QB_OK;
 }
 
