@@ -44,28 +44,30 @@ def _sets_for(footprint_bytes, cap=48):
 
 
 def time_graphs(make_call, nsets, steps, warmup, stream):
-    """make_call(i) -> zero-argument callable running the op on input set i."""
+    """make_call(i) -> zero-argument callable running the op on input set i.  One CUDA graph holds one call per input
+    set, back to back (as the ops sit in a model's captured step), so that a replay's launch cost is shared by nsets
+    invocations; the figure returned is the time per invocation."""
     calls = [make_call(i) for i in range(nsets)]
     with torch.cuda.stream(stream):
         for c in calls:
             c()
         stream.synchronize()
-        graphs, keep = [], []
-        for c in calls:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
+        keep = []
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for c in calls:
                 keep.append(c())
-            graphs.append(g)
         for i in range(max(warmup, 3)):
-            graphs[i % nsets].replay()
+            g.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stream.synchronize()
+        replays = max(1, -(-steps // nsets))
         e0.record(stream)
-        for i in range(steps):
-            graphs[i % nsets].replay()
+        for i in range(replays):
+            g.replay()
         e1.record(stream)
         e1.synchronize()
-    return e0.elapsed_time(e1) / steps
+    return e0.elapsed_time(e1) / (replays * nsets)
 
 
 # ---------------------------------------------------------------------------------------------------------------------

@@ -230,23 +230,8 @@ struct UpdSegments {
   int grouped;
 };
 
-__global__ void __launch_bounds__(128)
-conv1d_update_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd,
-                     int8_t* __restrict__ state, int64_t st_sb, int64_t st_sd, int64_t st_sw,
-                     const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
-                     UpdSegments seg, int batch, int dim, int width, int silu) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)batch * dim) return;
-  const int c = (int)(idx % dim);
-  const int b = (int)(idx / dim);
-  int8_t* st = state + (int64_t)b * st_sb + (int64_t)c * st_sd;
-  float acc = 0.0f;
-  // shift left by one, append x, accumulate the dot product in the same pass
-  for (int i = 0; i < width; ++i) {
-    const int8_t v = (i < width - 1) ? st[(int64_t)(i + 1) * st_sw] : x[(int64_t)b * x_sb + (int64_t)c * x_sd];
-    st[(int64_t)i * st_sw] = v;
-    acc += (float)weight[(int64_t)c * width + i] * (float)v;
-  }
+// Output scale lookup, bias, SiLU, re-quantisation and store of one (batch, channel) of a decode step.
+__device__ __forceinline__ void update_finish(float acc, int b, int c, const int8_t* __restrict__ bias, const UpdSegments& seg, int silu) {
   const int s = c < seg.end0 ? 0 : (c < seg.end1 ? 1 : 2);
   const int cbase = s == 0 ? 0 : (s == 1 ? seg.end0 : seg.end1);
   float so;
@@ -268,6 +253,48 @@ conv1d_update_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd,
   float v = seg.scale_in[s] * acc + (bias != nullptr ? seg.scale_bias[s] * (float)bias[c] : 0.0f);
   if (silu) v = silu_fast(v);
   seg.dst[s][(int64_t)b * seg.dst_sb[s] + (int64_t)(c - cbase) * seg.dst_sd[s]] = (int8_t)round_away_s8(v / so);
+}
+
+__global__ void __launch_bounds__(128)
+conv1d_update_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd,
+                     int8_t* __restrict__ state, int64_t st_sb, int64_t st_sd, int64_t st_sw,
+                     const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
+                     UpdSegments seg, int batch, int dim, int width, int silu) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)batch * dim) return;
+  const int c = (int)(idx % dim);
+  const int b = (int)(idx / dim);
+  int8_t* st = state + (int64_t)b * st_sb + (int64_t)c * st_sd;
+  float acc = 0.0f;
+  // shift left by one, append x, accumulate the dot product in the same pass
+  for (int i = 0; i < width; ++i) {
+    const int8_t v = (i < width - 1) ? st[(int64_t)(i + 1) * st_sw] : x[(int64_t)b * x_sb + (int64_t)c * x_sd];
+    st[(int64_t)i * st_sw] = v;
+    acc += (float)weight[(int64_t)c * width + i] * (float)v;
+  }
+  update_finish(acc, b, c, bias, seg, silu);
+}
+
+// The common layout -- width 4, state (batch, dim, 4) contiguous -- as one 32-bit word per channel: the window slides by
+// a funnel shift, the four taps are one dp4a, state and weight accesses are one coalesced word per thread.
+__global__ void __launch_bounds__(256)
+conv1d_update_w4_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd, uint32_t* __restrict__ state, int64_t st_sb_words,
+                        const uint32_t* __restrict__ weight, const int8_t* __restrict__ bias, UpdSegments seg, int batch, int dim,
+                        int silu) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)batch * dim) return;
+  const int c = (int)(idx % dim);
+  const int b = (int)(idx / dim);
+  uint32_t* st = state + (int64_t)b * st_sb_words + c;
+  const uint32_t xv = (uint32_t)(uint8_t)x[(int64_t)b * x_sb + (int64_t)c * x_sd];
+  const uint32_t win = (*st >> 8) | (xv << 24);   // drop the oldest sample, append the new one
+  *st = win;
+  const float acc = (float)__dp4a((int)win, (int)__ldg(weight + c), 0);
+  update_finish(acc, b, c, bias, seg, silu);
+}
+
+bool update_w4_ok(int width, const void* state, int64_t sb, int64_t sd, int64_t sw, const void* weight) {
+  return width == 4 && sw == 1 && sd == 4 && sb % 4 == 0 && aligned(state, 4) && aligned(weight, 4);
 }
 
 int pick_tl(int64_t rows_of_vectors, int seqlen) {
@@ -390,6 +417,13 @@ extern "C" int qb_causal_conv1d_update(const qb_conv1d_update_args* a, void* str
   seg.out_scale_value = a->scale_out;
   seg.end0 = seg.end1 = a->dim;
   const int64_t total = (int64_t)a->batch * a->dim;
+  if (update_w4_ok(a->width, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight)) {
+    conv1d_update_w4_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        a->x, a->x_sb, a->x_sd, reinterpret_cast<uint32_t*>(a->conv_state), a->state_sb / 4,
+        reinterpret_cast<const uint32_t*>(a->weight), a->bias, seg, a->batch, a->dim, a->silu);
+    QB_LAUNCH_OK("conv1d_update_w4_kernel");
+    return QB_OK;
+  }
   conv1d_update_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
       a->x, a->x_sb, a->x_sd, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight, a->bias, seg,
       a->batch, a->dim, a->width, a->silu);
@@ -423,6 +457,13 @@ extern "C" int qb_quamba2_conv1d_update(const qb_quamba2_conv1d_update_args* a, 
   seg.nhead_groups = a->nhead_groups; seg.ndim_groups = a->ndim_groups; seg.headdim = a->x_headdim;
   seg.x_group_size = a->x_dim / a->n_groups; seg.d_state = a->d_state; seg.grouped = grouped ? 1 : 0;
   const int64_t total = (int64_t)a->batch * a->dim;
+  if (update_w4_ok(a->width, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight)) {
+    conv1d_update_w4_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        a->xBC, a->xBC_sb, 1, reinterpret_cast<uint32_t*>(a->conv_state), a->state_sb / 4,
+        reinterpret_cast<const uint32_t*>(a->weight), a->bias, seg, a->batch, a->dim, a->silu);
+    QB_LAUNCH_OK("conv1d_update_w4_kernel");
+    return QB_OK;
+  }
   conv1d_update_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, (cudaStream_t)stream>>>(
       a->xBC, a->xBC_sb, 1, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight, a->bias, seg,
       a->batch, a->dim, a->width, a->silu);
