@@ -41,6 +41,28 @@ void set_error(const char* fmt, ...);
     }                                                                            \
   } while (0)
 
+#ifdef __CUDACC__
+// Programmatic dependent launch, for the small kernels of a decode step whose cost is mostly the gap between launches:
+// the kernel may be scheduled while its predecessor on the stream is still draining, and waits (grid_dependency_wait,
+// before its first access to global memory) until that predecessor has completed and its writes are visible.  The
+// error of a failed launch is picked up by QB_LAUNCH_OK like that of a <<<>>> launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

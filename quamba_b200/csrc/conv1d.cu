@@ -281,6 +281,7 @@ __global__ void __launch_bounds__(256)
 conv1d_update_w4_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd, uint32_t* __restrict__ state, int64_t st_sb_words,
                         const uint32_t* __restrict__ weight, const int8_t* __restrict__ bias, UpdSegments seg, int batch, int dim,
                         int silu) {
+  grid_dependency_wait();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)batch * dim) return;
   const int c = (int)(idx % dim);
@@ -418,9 +419,9 @@ extern "C" int qb_causal_conv1d_update(const qb_conv1d_update_args* a, void* str
   seg.end0 = seg.end1 = a->dim;
   const int64_t total = (int64_t)a->batch * a->dim;
   if (update_w4_ok(a->width, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight)) {
-    conv1d_update_w4_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
-        a->x, a->x_sb, a->x_sd, reinterpret_cast<uint32_t*>(a->conv_state), a->state_sb / 4,
-        reinterpret_cast<const uint32_t*>(a->weight), a->bias, seg, a->batch, a->dim, a->silu);
+    launch_dependent(conv1d_update_w4_kernel, dim3((unsigned)ceil_div(total, 256)), dim3(256), 0, (cudaStream_t)stream,
+                     a->x, a->x_sb, a->x_sd, reinterpret_cast<uint32_t*>(a->conv_state), a->state_sb / 4,
+                     reinterpret_cast<const uint32_t*>(a->weight), a->bias, seg, a->batch, a->dim, a->silu);
     QB_LAUNCH_OK("conv1d_update_w4_kernel");
     return QB_OK;
   }
@@ -458,9 +459,9 @@ extern "C" int qb_quamba2_conv1d_update(const qb_quamba2_conv1d_update_args* a, 
   seg.x_group_size = a->x_dim / a->n_groups; seg.d_state = a->d_state; seg.grouped = grouped ? 1 : 0;
   const int64_t total = (int64_t)a->batch * a->dim;
   if (update_w4_ok(a->width, a->conv_state, a->state_sb, a->state_sd, a->state_sw, a->weight)) {
-    conv1d_update_w4_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
-        a->xBC, a->xBC_sb, 1, reinterpret_cast<uint32_t*>(a->conv_state), a->state_sb / 4,
-        reinterpret_cast<const uint32_t*>(a->weight), a->bias, seg, a->batch, a->dim, a->silu);
+    launch_dependent(conv1d_update_w4_kernel, dim3((unsigned)ceil_div(total, 256)), dim3(256), 0, (cudaStream_t)stream,
+                     a->xBC, a->xBC_sb, (int64_t)1, reinterpret_cast<uint32_t*>(a->conv_state), a->state_sb / 4,
+                     reinterpret_cast<const uint32_t*>(a->weight), a->bias, seg, a->batch, a->dim, a->silu);
     QB_LAUNCH_OK("conv1d_update_w4_kernel");
     return QB_OK;
   }

@@ -161,6 +161,7 @@ template <int MB>
 __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restrict__ W, int64_t ldw, int M, int N, int K,
                Epilogue ep) {
+  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
   const int lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW;
   if (n0 >= N) return;
@@ -210,10 +211,10 @@ int launch_gemv(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int 
                 cudaStream_t st) {
   if (K % 16 != 0 || lda % 16 != 0 || ldw % 16 != 0 || !aligned(A, 16) || !aligned(W, 16)) return QB_ERR_UNSUPPORTED;
   const unsigned grid = (unsigned)ceil_div(N, kGemvWarps * kNW);
-  if (M == 1) gemv_s8_kernel<1><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
-  else if (M == 2) gemv_s8_kernel<2><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
-  else if (M <= 4) gemv_s8_kernel<4><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
-  else gemv_s8_kernel<8><<<grid, kGemvWarps * 32, 0, st>>>(A, lda, W, ldw, M, N, K, ep);
+  if (M == 1) launch_dependent(gemv_s8_kernel<1>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
+  else if (M == 2) launch_dependent(gemv_s8_kernel<2>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
+  else if (M <= 4) launch_dependent(gemv_s8_kernel<4>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
+  else launch_dependent(gemv_s8_kernel<8>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
   QB_LAUNCH_OK("gemv_s8_kernel");
   return QB_OK;
 }

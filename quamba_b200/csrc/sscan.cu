@@ -393,6 +393,7 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
   __shared__ float rX[2][kTileRows], rDtx[2][kTileRows], rDt[2][kTileRows], rdA[2][kTileRows], rY[2][kTileRows];
   __shared__ int rScaleOfs[2][kTileRows];   // grouped scales: offset of the row's [dstate] state-scale vector
   __shared__ __align__(8) uint64_t full[kUpdSlots];
+  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
   const int tid = threadIdx.x;
   const int t_begin = blockIdx.x * tiles_per_cta;
   const int t_end = min(tiles, t_begin + tiles_per_cta);
@@ -686,10 +687,10 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
       cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);   \
       attr_done = true;                                                                                            \
     }                                                                                                              \
-    if (tied && !grp) sscan_update_bulk_kernel<L, true, false><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);      \
-    else if (tied && grp) sscan_update_bulk_kernel<L, true, true><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);   \
-    else if (!grp) sscan_update_bulk_kernel<L, false, false><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);        \
-    else sscan_update_bulk_kernel<L, false, true><<<grid, 256, smem, st>>>(*a, tiles, tiles_per_cta, status);                   \
+    if (tied && !grp) launch_dependent(sscan_update_bulk_kernel<L, true, false>, dim3(grid), dim3(256), smem, st, *a, tiles, tiles_per_cta, status);      \
+    else if (tied && grp) launch_dependent(sscan_update_bulk_kernel<L, true, true>, dim3(grid), dim3(256), smem, st, *a, tiles, tiles_per_cta, status);   \
+    else if (!grp) launch_dependent(sscan_update_bulk_kernel<L, false, false>, dim3(grid), dim3(256), smem, st, *a, tiles, tiles_per_cta, status);        \
+    else launch_dependent(sscan_update_bulk_kernel<L, false, true>, dim3(grid), dim3(256), smem, st, *a, tiles, tiles_per_cta, status);                   \
   } while (0)
       switch (lpr) {
         case 1: QB_UPD_LAUNCH(1); break;
