@@ -126,6 +126,7 @@ hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = bars.tmem_slot;
+  grid_dependency_wait();   // launched as a programmatic dependent: the set-up above overlaps the predecessor's tail
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -322,7 +323,7 @@ int launch_one(const qb_hadamard_quant_args* a, const unsigned long long* masks,
   QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "hadamard: device status word unavailable");
   const int64_t units = ceil_div(a->rows, R);
   const unsigned grid = (unsigned)std::min<int64_t>(units, sm_count());
-  kern<<<grid, kThreadsH, kSmem, st>>>(tm, a->out, a->out_row_stride, a->rows, a->scale * 128.0f, masks, status);
+  launch_dependent(kern, dim3(grid), dim3(kThreadsH), (size_t)kSmem, st, tm, a->out, a->out_row_stride, a->rows, a->scale * 128.0f, masks, status);
   QB_LAUNCH_OK("hadamard_tc_kernel");
   return QB_OK;
 }
