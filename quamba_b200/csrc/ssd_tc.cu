@@ -26,21 +26,22 @@
 // all the same.  The arithmetic per pair is the same sequence of operations wherever the cut falls, so results do not
 // depend on the number of SMs.
 //
-// 640 threads: warp 0 issues TMA (128-byte-swizzled B / C tiles that serve as K-major operands of CB and D1 and as the
-// MN-major A operand of S_loc without reshuffling, plus the 1.5 KB of vectors), warp 1 issues the MMAs and owns TMEM,
-// warps 4..19 compute.  All 16 compute warps walk the same four phases per block, a thread owning one row (TMEM lane)
-// and one quarter of the columns:
-//   P1  x(k) -> fp16 operands (raw, and scaled by w) in shared memory            -> GEMM4(k) = S_loc
+// 640 threads.  Warp 3: one thread serves the TMA queues (loads of 128-byte-swizzled B / C tiles that serve as K-major
+// operands of CB and D1 and as the MN-major A operand of S_loc without reshuffling, the int8 x tile, the vectors and the
+// per-pair constants; and the output store of each block).  Warp 1 issues the MMAs and owns TMEM.  Warps 0 and 2 turn
+// the int8 x tile of block k + 1 into the two fp16 operand tiles (raw, and scaled by w) while the compute warps are
+// still on block k: that work needs no tensor memory.  Warps 4..19 compute; all 16 walk the same three phases per
+// block, a thread owning one row (TMEM lane) and one quarter of the columns:
 //   P2  CB(k) -> Lm(k), written back to tensor memory as packed fp16 (A operand)  -> GEMM3(k) = D2, then CB(k+1)
 //   P3  state update from S_loc(k), fp16 copy of the state to shared memory      -> GEMM2(k+1) = D1
-//   P4  y(k) from D2(k), D1(k): to a per-warp staging tile and out by TMA store
+//   P4  y(k) from D2(k), D1(k): to a swizzled staging tile, stored by warp 3 with one TMA store
 // so every GEMM runs while the compute warps are busy with the next phase, and program order plus the group barriers
 // of each phase is what frees each buffer (noted at each wait).  The warps are kept in lock step on purpose: variants
 // in which they synchronised through mbarriers only and drifted apart (each thread polling, or one barrier per phase
 // with per-warp arrivals) were 10 to 30 % slower although they wait less -- with every warp in the same phase the
-// unrolled code of that phase is fetched once for all of them.  Every mbarrier completes exactly once per block, is waited
-// on by each consumer once per phase and in order, and all waits are bounded.  The B / C stage is handed back to the
-// TMA producer only at the end of an MMA iteration.
+// unrolled code of that phase is fetched once for all of them.  Every mbarrier completes exactly once per block, is
+// waited on by each consumer once per phase and in order, and all waits are bounded.  The B / C stage is handed back to
+// the TMA producer only at the end of an MMA iteration.
 #include "tc_common.cuh"
 
 namespace qb {
@@ -56,8 +57,8 @@ namespace {
 using namespace tc;
 
 constexpr int T = 128, P = 64, N = 128;
-// Warps 0..3: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..3 idle.  Warps 4..19 compute.
-constexpr int kThreads = 640;
+// Warps 0 and 2: x operands; warp 1: MMA issuer; warp 3: TMA loads and stores.  Warps 4..19 compute.
+constexpr int kThreads = 640;                  // 4 control warps + 16 compute warps (a 21st warp would cap registers at 80)
 constexpr int kLead = 128;                     // first compute thread
 constexpr int kCompute = kThreads - kLead;     // 512
 
@@ -222,7 +223,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) { mbar_init(&ms.bc_full[s], 1); mbar_init(&ms.bc_empty[s], 1); mbar_init(&ms.ab_empty[s], 1); }
-    mbar_init(&ms.cb_ready, 1); mbar_init(&ms.xops_ready, 1); mbar_init(&ms.s_ready, 1); mbar_init(&ms.lm_ready, 1);
+    mbar_init(&ms.cb_ready, 1); mbar_init(&ms.xops_ready, 2); mbar_init(&ms.s_ready, 1); mbar_init(&ms.lm_ready, 1);
     mbar_init(&ms.y_ready, 1); mbar_init(&ms.s16_ready, 1); mbar_init(&ms.d1_ready, 1);
     mbar_init(&ms.y_full, 16); mbar_init(&ms.y_empty, 1);
     fence_barrier_init();
@@ -243,32 +244,60 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
   // from here on its results (widened B / C, vectors, constants, cleared flags) are read.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
+  if (warp == 3) {
+    // ---------------- TMA: loads and output stores ----------------
+    // One thread serves two queues in an event loop of non-blocking tests: the loads of block k + 2 as soon as its stage
+    // has been released (by the MMA issuer and by the compute warps), and the store of block k as soon as the compute
+    // warps have filled the staging tile (one TMA store per block; rows past the end of the sequence are clipped by the
+    // hardware; the tile is handed back once the store has read it).
     if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      for (int ii = 0; ii < plan.n_items && ok; ++ii) {
-        const Item im = get_item(plan, ii, nb);
-        const int b = im.unit / a.nheads, h = im.unit % a.nheads, g = h / hpg;
-        const float* ab_src = ab_ws + (int64_t)im.unit * nb * (kAbVecs * T);
-        for (int j = im.jb; j < im.je; ++j, ++it) {
-          const int st = it & 1;
-          const uint32_t par = ((it >> 1) & 1) ^ 1;
-          ok = mbar_wait(&ms.bc_empty[st], par, status, QB_ERR_TIMEOUT) && mbar_wait(&ms.ab_empty[st], par, status, QB_ERR_TIMEOUT);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes + kXBytes + kHcBytes);
-          uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
-          uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
-          bulk_load(ms.ab[st], ab_src + (int64_t)j * (kAbVecs * T), kAbBytes, &ms.bc_full[st]);
-          bulk_load(ms.hc[st], hc_ws + (int64_t)im.unit * kHcFloats, kHcBytes, &ms.bc_full[st]);
-          tma_load_4d(dB, &tm_b16, &ms.bc_full[st], 0, g, j * T, b);
-          tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, j * T, b);
-          tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, j * T, b);
-          tma_load_4d(dC + kAtom, &tm_c16, &ms.bc_full[st], 64, g, j * T, b);
-          tma_load_4d(smem + kOffX8 + st * kXBytes, &tm_x, &ms.bc_full[st], 0, h, j * T, b);   // rows past the end read as 0
+      struct Cursor { int ii, j, it; Item im; };
+      auto start = [&](Cursor& c) { c.ii = 0; c.it = 0; if (plan.n_items > 0) { c.im = get_item(plan, 0, nb); c.j = c.im.jb; } };
+      auto step = [&](Cursor& c) {
+        ++c.it;
+        if (++c.j >= c.im.je) { if (++c.ii < plan.n_items) { c.im = get_item(plan, c.ii, nb); c.j = c.im.jb; } }
+      };
+      Cursor ld, stc;
+      start(ld); start(stc);
+      long long t_last = clock64();
+      while (stc.it < plan.total) {
+        bool progress = false;
+        if (ld.it < plan.total) {
+          const int st = ld.it & 1;
+          const uint32_t par = ((ld.it >> 1) & 1) ^ 1;
+          if (mbar_test_wait(&ms.bc_empty[st], par) && mbar_test_wait(&ms.ab_empty[st], par)) {
+            const int b = ld.im.unit / a.nheads, h = ld.im.unit % a.nheads, g = h / hpg;
+            const float* ab_src = ab_ws + ((int64_t)ld.im.unit * nb + ld.j) * (kAbVecs * T);
+            mbar_arrive_expect_tx(&ms.bc_full[st], 4 * kAtom + kAbBytes + kXBytes + kHcBytes);
+            uint8_t* dB = smem + kOffB16 + st * 2 * kAtom;
+            uint8_t* dC = smem + kOffC16 + st * 2 * kAtom;
+            bulk_load(ms.ab[st], ab_src, kAbBytes, &ms.bc_full[st]);
+            bulk_load(ms.hc[st], hc_ws + (int64_t)ld.im.unit * kHcFloats, kHcBytes, &ms.bc_full[st]);
+            tma_load_4d(dB, &tm_b16, &ms.bc_full[st], 0, g, ld.j * T, b);
+            tma_load_4d(dB + kAtom, &tm_b16, &ms.bc_full[st], 64, g, ld.j * T, b);
+            tma_load_4d(dC, &tm_c16, &ms.bc_full[st], 0, g, ld.j * T, b);
+            tma_load_4d(dC + kAtom, &tm_c16, &ms.bc_full[st], 64, g, ld.j * T, b);
+            tma_load_4d(smem + kOffX8 + st * kXBytes, &tm_x, &ms.bc_full[st], 0, h, ld.j * T, b);   // rows past the end read as 0
+            step(ld);
+            progress = true;
+          }
+        }
+        if (mbar_test_wait(&ms.y_full, stc.it & 1)) {
+          tma_store_4d(&tm_out, smem + kOffY, 0, stc.im.unit % a.nheads, stc.j * T, stc.im.unit / a.nheads);
+          bulk_commit();
+          bulk_wait_read<0>();
+          mbar_arrive(&ms.y_empty);
+          step(stc);
+          progress = true;
+        }
+        if (progress) {
+          t_last = clock64();
+        } else {
+          __nanosleep(64);
+          if (clock64() - t_last > kWaitBudgetCycles) { atomicCAS(status, 0, QB_ERR_TIMEOUT); break; }   // bounded like every wait
         }
       }
+      bulk_wait_all<0>();   // every store is complete before the CTA exits
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -340,27 +369,51 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         }
       }
     }
-  } else if (warp == 2) {
-    // ---------------- output store ----------------
-    // One thread sends each block's y tile to global memory with a single TMA store (rows past the end of the sequence
-    // are clipped by the hardware) and hands the staging tile back once the store has read it.  The compute warps only
-    // write the tile: issuing the store and waiting for its read cost each of them several hundred cycles per block.
-    if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      for (int ii = 0; ii < plan.n_items && ok; ++ii) {
-        const Item im = get_item(plan, ii, nb);
-        const int b = im.unit / a.nheads, h = im.unit % a.nheads;
-        for (int j = im.jb; j < im.je; ++j, ++it) {
-          ok = mbar_wait(&ms.y_full, it & 1, status, QB_ERR_TIMEOUT);
-          if (!ok) break;
-          tma_store_4d(&tm_out, smem + kOffY, 0, h, j * T, b);
-          bulk_commit();
-          bulk_wait_read<0>();
-          mbar_arrive(&ms.y_empty);
+  } else if (warp == 0 || warp == 2) {
+    // ---------------- x operands ----------------
+    // x(k) -> the two fp16 operand tiles: raw (B of GEMM3) and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) (B of
+    // GEMM4; 0 where dt_l = 0).  This needs no tensor memory, so one warp outside the 16 compute warps does it a block
+    // ahead of them: the tiles may be rewritten once GEMM4 and GEMM3 of the previous block are complete, and the
+    // deadlines (GEMM4 / GEMM3 of this block) lie a whole Lm phase later.  Two warps share the tile, 64 rows each; both
+    // sit on the scheduler whose compute warps have the least Lm work.
+    const int xhalf = warp == 2 ? 8 : 0;
+    int it = 0;
+    bool ok = true;
+    for (int ii = 0; ii < plan.n_items && ok; ++ii) {
+      const Item im = get_item(plan, ii, nb);
+      for (int j = im.jb; j < im.je; ++j, ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(&ms.bc_full[st], (it >> 1) & 1, status, QB_ERR_TIMEOUT);                 // x tile, vectors, constants
+        if (ok && it > 0) ok = mbar_wait(&ms.s_ready, (it - 1) & 1, status, QB_ERR_TIMEOUT);     // GEMM4 of the previous block
+        if (ok && it > 0) ok = mbar_wait(&ms.y_ready, (it - 1) & 1, status, QB_ERR_TIMEOUT);     // GEMM3 of the previous block
+        if (!ok) break;
+        const float* av = ms.ab[st];
+        const float base = av[T - 1] - ms.hc[st][kHcLscb];
+        const uint8_t* xs = smem + kOffX8 + st * kXBytes;
+        const int piece = lane & 3;
+#pragma unroll 4
+        for (int i = xhalf; i < xhalf + 8; ++i) {
+          const int r = 8 * i + (lane >> 2);      // a warp reads 512 contiguous bytes of the tile per step
+          const uint4 xq = *reinterpret_cast<const uint4*>(xs + r * P + piece * 16);
+          const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
+          const __half2 w2 = __float2half2_rn(fast_exp2(base - av[T + r]));
+          uint8_t* rowp_raw = smem + kOffXraw + r * 128;
+          uint8_t* rowp_w = smem + kOffXw + r * 128;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            __half2 r0, r1, r2, r3;
+            s8x4_to_h2x2(xwd[2 * c], r0, r1);
+            s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
+            const int chunk = ((2 * piece + c) ^ (r & 7)) << 4;
+            *reinterpret_cast<uint4*>(rowp_raw + chunk) = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
+            *reinterpret_cast<uint4*>(rowp_w + chunk) = make_uint4(h2_bits(__hmul2(r0, w2)), h2_bits(__hmul2(r1, w2)),
+                                                                   h2_bits(__hmul2(r2, w2)), h2_bits(__hmul2(r3, w2)));
+          }
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ms.xops_ready);
       }
-      bulk_wait_all<0>();   // every store is complete before the CTA exits
     }
   } else if (warp >= 4) {
     // ---------------- compute warps ----------------
@@ -372,8 +425,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
     const uint32_t tlane = (uint32_t)(q * 32) << 16;
     const int sw = row & 7;
     const bool lead = (threadIdx.x == kLead);
-    // the x operands (P1) touch no tensor memory, so there a warp takes eight whole rows: lane -> (row, 16-byte piece)
-    const int prow = 8 * cw + (lane >> 2), piece = lane & 3;
     auto gsync = [&]() { asm volatile("bar.sync 1, 512;" ::: "memory"); };
     auto gand = [&](uint32_t ok) -> bool {   // group barrier that ANDs a flag: a timed-out wait makes all warps leave together
       uint32_t r;
@@ -445,11 +496,10 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         const uint32_t ph = it & 1;
         const bool use_d1 = j > im.jb || im.has_init;
         const int l = j * T + row;
-        // ================= P1: x(j) -> fp16 operands: raw, and scaled by w_l = dt_l 2^(r - a_l) = 2^(r - bk_l - lscb) =====
-        // (0 where dt_l = 0).  Both tiles are free: the state step of the previous block waited for GEMM4 and its
-        // output step for GEMM3.
+        // The x operands of this block are written by warp 0.  Here: the vectors and constants have landed (bc_full) and
+        // C.B^T of this block is in tensor memory (cb_ready).
         if (lead) TRACE(0, it, 0);
-        ok = gwait(&ms.bc_full[st], (it >> 1) & 1, nullptr, 0);   // x, B, C and the vectors of this block have landed
+        ok = gwait(&ms.bc_full[st], (it >> 1) & 1, &ms.cb_ready, ph);
         if (!ok) break;
         // The vectors and constants of the previous block are read up to the end of its output step, which every warp
         // has left by now; its B / C / x tiles were released by the MMA issuer.
@@ -457,36 +507,14 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (lead) TRACE(0, it, 1);
         const float* av = ms.ab[st];
         const float* hc = ms.hc[st];
-        const float lscb = hc[kHcLscb], sC = hc[kHcSC], dfold = hc[kHcDfold];
-        {
-          const uint4 xq = *reinterpret_cast<const uint4*>(smem + kOffX8 + st * kXBytes + prow * P + piece * 16);
-          const uint32_t xwd[4] = {xq.x, xq.y, xq.z, xq.w};
-          const __half2 w2 = __float2half2_rn(fast_exp2(av[T - 1] - av[T + prow] - lscb));
-          uint8_t* rowp_raw = smem + kOffXraw + prow * 128;
-          uint8_t* rowp_w = smem + kOffXw + prow * 128;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            __half2 r0, r1, r2, r3;
-            s8x4_to_h2x2(xwd[2 * c], r0, r1);
-            s8x4_to_h2x2(xwd[2 * c + 1], r2, r3);
-            const int chunk = ((2 * piece + c) ^ (prow & 7)) << 4;
-            *reinterpret_cast<uint4*>(rowp_raw + chunk) = make_uint4(h2_bits(r0), h2_bits(r1), h2_bits(r2), h2_bits(r3));
-            *reinterpret_cast<uint4*>(rowp_w + chunk) = make_uint4(h2_bits(__hmul2(r0, w2)), h2_bits(__hmul2(r1, w2)),
-                                                                   h2_bits(__hmul2(r2, w2)), h2_bits(__hmul2(r3, w2)));
-          }
-        }
+        const float sC = hc[kHcSC], dfold = hc[kHcDfold];
         const float a_row = av[row];
         const float r_tot = av[T - 1];
         const float e_out = use_d1 ? sC * fast_exp2(a_row) : 0.0f;   // weight of the carried-in term in the output
-        fence_proxy_async_smem();
-        gsync();
-        if (lead) { mbar_arrive(&ms.xops_ready); TRACE(0, it, 2); }
 
         // ================= P2: Lm[t, s] = CB[t, s] 2^(a_t - bk_s) for s <= t (+ D on the diagonal), chunk sub =============
         // Written as packed fp16 into its own tensor-memory columns, which GEMM3 of the previous block has finished
         // reading (its output step waited for y_ready).
-        ok = gwait(&ms.cb_ready, ph, nullptr, 0);
-        if (!ok) break;
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 3);
         {
