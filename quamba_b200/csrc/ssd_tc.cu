@@ -165,6 +165,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
 // 32 lanes x 16 consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -518,54 +529,64 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 3);
         {
-          const int c = sub;
-          uint32_t o[16];
-          if (c > q) {  // entirely above the diagonal for every row of this warp
-#pragma unroll
-            for (int u = 0; u < 16; ++u) o[u] = 0u;
-          } else {
-            uint32_t cb[32];
+          // Work split inside a lane quarter q (rows 32q .. 32q + 31, four warps): the chunks c < q lie below the
+          // diagonal and cost two multiplies per element, the chunk c = q holds the diagonal and costs an ex2 and the
+          // mask per element, the chunks c > q are zero.  Warp `sub` takes the whole chunk c = sub when it is below the
+          // diagonal, and every warp takes eight columns (8 sub .. 8 sub + 7) of the diagonal chunk, so that the
+          // expensive chunk is shared by four warps instead of being one warp's critical path.
+          uint32_t dg[8];
+          tmem_ld_32x8(tmem + tlane + kColCB + 32 * q + 8 * sub, dg);
+          if (sub < q) {
+            const int c = sub;
+            uint32_t cb[32], o[16];
             tmem_ld_32x32(tmem + tlane + kColCB + 32 * c, cb);
-            if (c == q) {
-              // diagonal chunk: exact exponent per element, the k <= m mask (k - 32c <= lane), and the skip weight D
-              // on the diagonal itself (y = sx (Lm + D I) x) when D has one value per head
-              const float* bkv = av + T + 32 * c;
-              tmem_ld_wait();
-              const float4* bk4 = reinterpret_cast<const float4*>(bkv);
+            // chunk below the diagonal: 2^(a_t - bk_s) = 2^(a_t - m) * ec[s], m = a at the end of chunk c
+            const float e_row = fast_exp2(a_row - av[32 * c + 31]);
+            tmem_ld_wait();
+            const float4* ec4 = reinterpret_cast<const float4*>(av + 2 * T + 32 * c);
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const float4 bb = bk4[u];
-                const int t0 = 4 * u;
-                float e0 = __uint_as_float(cb[t0 + 0]) * fast_exp2(a_row - bb.x);
-                float e1 = __uint_as_float(cb[t0 + 1]) * fast_exp2(a_row - bb.y);
-                float e2 = __uint_as_float(cb[t0 + 2]) * fast_exp2(a_row - bb.z);
-                float e3 = __uint_as_float(cb[t0 + 3]) * fast_exp2(a_row - bb.w);
-                e0 = t0 + 0 < lane ? e0 : (t0 + 0 == lane ? e0 + dfold : 0.0f);
-                e1 = t0 + 1 < lane ? e1 : (t0 + 1 == lane ? e1 + dfold : 0.0f);
-                e2 = t0 + 2 < lane ? e2 : (t0 + 2 == lane ? e2 + dfold : 0.0f);
-                e3 = t0 + 3 < lane ? e3 : (t0 + 3 == lane ? e3 + dfold : 0.0f);
-                o[2 * u] = pack_h2(e0, e1);
-                o[2 * u + 1] = pack_h2(e2, e3);
-              }
-            } else {
-              // chunk below the diagonal: 2^(a_t - bk_s) = 2^(a_t - m) * ec[s], m = a at the end of chunk c
-              const float e_row = fast_exp2(a_row - av[32 * c + 31]);
-              tmem_ld_wait();
-              const float4* ec4 = reinterpret_cast<const float4*>(av + 2 * T + 32 * c);
+            for (int u = 0; u < 8; ++u) {
+              const float4 ee = ec4[u];
+              const int t0 = 4 * u;
+              const float e0 = __uint_as_float(cb[t0 + 0]) * (e_row * ee.x);
+              const float e1 = __uint_as_float(cb[t0 + 1]) * (e_row * ee.y);
+              const float e2 = __uint_as_float(cb[t0 + 2]) * (e_row * ee.z);
+              const float e3 = __uint_as_float(cb[t0 + 3]) * (e_row * ee.w);
+              o[2 * u] = pack_h2(e0, e1);
+              o[2 * u + 1] = pack_h2(e2, e3);
+            }
+            tmem_st16(tmem + tlane + kColLm + 16 * c, o);
+          } else {
+            tmem_ld_wait();
+            if (sub > q) {  // this warp's own chunk is entirely above the diagonal
+              uint32_t z[16];
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const float4 ee = ec4[u];
-                const int t0 = 4 * u;
-                const float e0 = __uint_as_float(cb[t0 + 0]) * (e_row * ee.x);
-                const float e1 = __uint_as_float(cb[t0 + 1]) * (e_row * ee.y);
-                const float e2 = __uint_as_float(cb[t0 + 2]) * (e_row * ee.z);
-                const float e3 = __uint_as_float(cb[t0 + 3]) * (e_row * ee.w);
-                o[2 * u] = pack_h2(e0, e1);
-                o[2 * u + 1] = pack_h2(e2, e3);
-              }
+              for (int u = 0; u < 16; ++u) z[u] = 0u;
+              tmem_st16(tmem + tlane + kColLm + 16 * sub, z);
             }
           }
-          tmem_st16(tmem + tlane + kColLm + 16 * c, o);
+          {
+            // eight columns of the diagonal chunk: exact exponent per element, the k <= m mask (k - 32q <= lane), and the
+            // skip weight D on the diagonal itself (y = sx (Lm + D I) x) when D has one value per head
+            const float4* bk4 = reinterpret_cast<const float4*>(av + T + 32 * q + 8 * sub);
+            uint32_t o[4];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const float4 bb = bk4[u];
+              const int t0 = 8 * sub + 4 * u;
+              float e0 = __uint_as_float(dg[4 * u + 0]) * fast_exp2(a_row - bb.x);
+              float e1 = __uint_as_float(dg[4 * u + 1]) * fast_exp2(a_row - bb.y);
+              float e2 = __uint_as_float(dg[4 * u + 2]) * fast_exp2(a_row - bb.z);
+              float e3 = __uint_as_float(dg[4 * u + 3]) * fast_exp2(a_row - bb.w);
+              e0 = t0 + 0 < lane ? e0 : (t0 + 0 == lane ? e0 + dfold : 0.0f);
+              e1 = t0 + 1 < lane ? e1 : (t0 + 1 == lane ? e1 + dfold : 0.0f);
+              e2 = t0 + 2 < lane ? e2 : (t0 + 2 == lane ? e2 + dfold : 0.0f);
+              e3 = t0 + 3 < lane ? e3 : (t0 + 3 == lane ? e3 + dfold : 0.0f);
+              o[2 * u] = pack_h2(e0, e1);
+              o[2 * u + 1] = pack_h2(e2, e3);
+            }
+            tmem_st4(tmem + tlane + kColLm + 16 * q + 4 * sub, o);
+          }
         }
         tmem_st_wait();
         tc_fence_before_sync();
