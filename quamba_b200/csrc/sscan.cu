@@ -377,6 +377,155 @@ constexpr int kUpdTileBytes = 8192;
 constexpr int kUpdSlots = 4;
 constexpr int kStatusUpdateLoad = 301;
 
+// Warp-autonomous variant for the Mamba2 decode shape (d_state 128, A tied across the state, per-tensor scales): every
+// warp owns a ring of four 2 KB slots and walks its own list of 16-row tiles -- bulk load two tiles ahead, update in
+// place, bulk store -- so no CTA-wide barrier exists after the set-up (the 256-thread kernel below spends a third of
+// its stall cycles at its two __syncthreads per tile).  Lane l covers the 16 states n0 = 16 (l & 7) of the rows
+// (l >> 3) + 4 e, e = 0..3; the row scalars (x, dt, exp2(A dt), ...) are computed once by lanes 0..15 and passed round
+// by shuffles; the eight lanes of a row reduce y by shuffles.
+constexpr int kWTileRows = 16, kWTileBytes = kWTileRows * 128, kWSlots = 4;
+__global__ void __launch_bounds__(256, 3)
+sscan_update_warp_kernel(qb_sscan_update_args a, int tiles, int* status) {
+  using namespace tc;
+  constexpr float kLog2e = 1.4426950408889634f;
+  extern __shared__ __align__(128) uint8_t ring_all[];
+  __shared__ __align__(8) uint64_t full_all[8][kWSlots];
+  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* ring = ring_all + warp * (kWSlots * kWTileBytes);
+  uint64_t* full = full_all[warp];
+  const int gw = blockIdx.x * 8 + warp, nw = gridDim.x * 8;
+  const int per = tiles / nw, extra = tiles % nw;            // contiguous tiles per warp: neighbours share (batch, head)
+  const int t_begin = gw * per + min(gw, extra);
+  const int t_end = t_begin + per + (gw < extra ? 1 : 0);
+  if (t_begin >= t_end) return;
+  if (lane == 0) {
+    for (int i = 0; i < kWSlots; ++i) mbar_init(&full[i], 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  auto issue_load = [&](int t) {
+    const int slot = (t - t_begin) & (kWSlots - 1);
+    mbar_arrive_expect_tx(&full[slot], kWTileBytes);
+    bulk_load(ring + slot * kWTileBytes, a.state + (int64_t)t * kWTileBytes, kWTileBytes, &full[slot]);
+  };
+  if (lane == 0) {
+    issue_load(t_begin);
+    if (t_begin + 1 < t_end) issue_load(t_begin + 1);
+  }
+  const int hpg = a.nheads / a.ngroups;
+  const float ss0 = a.state_scale[0];
+  const float xs0 = a.x_scales[0];
+  const float dt_scale = *a.dt_scale;
+  const float A_scale = *a.A_scale;
+  const float bias_scale = (a.dt_bias != nullptr && !a.dt_bias_is_half) ? *a.dt_bias_scale : 0.0f;
+  const float D_scale = a.D != nullptr ? *a.D_scale : 0.0f;
+  const float z_scale = a.z != nullptr ? *a.z_scale : 0.0f;
+  const int n0 = (lane & 7) * 16;
+  const int tiles_per_head = a.headdim / kWTileRows;
+  float bb[16], cc[16];
+  int cur_bg = -1;
+  // row scalars of one tile, held by lanes 0..15 (lane = row)
+  struct Row { float x, dtx, dA, dsk; int hd, p; };
+  auto row_prepare = [&](int t) -> Row {
+    Row r{0.f, 0.f, 0.f, 0.f, 0, 0};
+    const int head_lin = t / tiles_per_head;                  // (batch, head) index
+    const int b = head_lin / a.nheads, hd = head_lin % a.nheads;
+    const int p = (t % tiles_per_head) * kWTileRows + (lane & 15);
+    r.hd = hd; r.p = p;
+    if (lane < 16) {
+      const float x = xs0 * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
+      float bias = 0.0f;
+      if (a.dt_bias != nullptr) {
+        const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
+        bias = a.dt_bias_is_half ? __half2float(static_cast<const __half*>(a.dt_bias)[bi])
+                                 : bias_scale * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
+      }
+      float dt = fmaf(dt_scale, (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp], bias);
+      if (a.dt_softplus) dt = softplus_f(dt);
+      const float A2 = -__expf(A_scale * (float)a.A_log[(int64_t)hd * a.A_sh + (int64_t)p * a.A_sp]) * kLog2e;
+      r.x = x;
+      r.dtx = dt * x;
+      r.dA = fast_exp2(A2 * dt);
+      r.dsk = a.D != nullptr ? x * D_scale * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp] : 0.0f;
+    }
+    return r;
+  };
+  Row nxt = row_prepare(t_begin);
+  for (int t = t_begin; t < t_end; ++t) {
+    const int k = t - t_begin;
+    const int slot = k & (kWSlots - 1);
+    const Row cur = nxt;
+    if (t + 1 < t_end) nxt = row_prepare(t + 1);              // global loads in flight during this tile's arithmetic
+    const int head_lin = t / tiles_per_head;
+    const int b = head_lin / a.nheads, hd = head_lin % a.nheads;
+    const int g = hd / hpg;
+    if (b * a.ngroups + g != cur_bg) {                        // warp-uniform: this lane's slices of B and C
+      cur_bg = b * a.ngroups + g;
+      const float Bs = a.B_scale[0] / ss0, Cs = a.C_scale[0] * ss0;
+      const uint4 bq = __ldg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0));
+      const uint4 cq = __ldg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0));
+      const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w}, cw[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        bb[i] = Bs * (float)(int8_t)(bw[i >> 2] >> (8 * (i & 3)));
+        cc[i] = Cs * (float)(int8_t)(cw[i >> 2] >> (8 * (i & 3)));
+      }
+    }
+    if (!mbar_wait(&full[slot], (uint32_t)((k / kWSlots) & 1), status, kStatusUpdateLoad)) break;   // all lanes wait on it
+    uint8_t* tile = ring + slot * kWTileBytes;
+    float ykeep = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = (lane >> 3) + 4 * e;                      // row of this piece inside the tile
+      const float dtx = __shfl_sync(0xffffffffu, cur.dtx, r);
+      const float dA = __shfl_sync(0xffffffffu, cur.dA, r);
+      uint4* cell = reinterpret_cast<uint4*>(tile + r * 128 + n0);
+      const uint4 rawst = *cell;
+      const uint32_t w[4] = {rawst.x ^ 0x80808080u, rawst.y ^ 0x80808080u, rawst.z ^ 0x80808080u, rawst.w ^ 0x80808080u};
+      uint32_t ow[4];
+      float y = 0.0f;
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        int q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // bytes [0, v + 128, 0, 0x47] read as a float = 32768 + (v + 128); v is the state in units of its scale
+          const float sv = __uint_as_float(__byte_perm(w[k4], 0x47000000u, 0x7404 | (j << 4))) - 32896.0f;
+          const float v = fmaf(bb[4 * k4 + j], dtx, sv * dA);   // new state / state_scale
+          q[j] = __float2int_rn(v);
+          y = fmaf(v, cc[4 * k4 + j], y);
+        }
+        ow[k4] = pack4_sat_s8(q[0], q[1], q[2], q[3]);
+      }
+      *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      y += __shfl_xor_sync(0xffffffffu, y, 1);
+      y += __shfl_xor_sync(0xffffffffu, y, 2);
+      y += __shfl_xor_sync(0xffffffffu, y, 4);
+      // the lane that prepared row r (lane r) keeps its y: rows 4 e + (lane >> 3) live in lanes 8 (r & 3) .. of this step
+      const float yrow = __shfl_sync(0xffffffffu, y, ((lane & 3) << 3));
+      if ((lane >> 2) == e && lane < 16) ykeep = yrow;        // lane = 4 e + (lane & 3)
+    }
+    fence_proxy_async_smem();   // the tile was rewritten through the generic proxy; the bulk store reads it through the async one
+    __syncwarp();
+    if (lane == 0) {
+      bulk_store(a.state + (int64_t)t * kWTileBytes, tile, kWTileBytes);
+      bulk_commit();
+      bulk_wait_read<1>();      // every store but the newest has finished reading its slot
+      if (t + 2 < t_end) issue_load(t + 2);
+    }
+    if (lane < 16) {            // y of row `lane`: D skip term, z gate, fp16 store
+      float y = ykeep + cur.dsk;
+      if (a.z != nullptr) {
+        const float z = z_scale * (float)a.z[(int64_t)b * a.z_sb + (int64_t)cur.hd * a.z_sh + cur.p];
+        y *= silu_exact(z);
+      }
+      static_cast<__half*>(a.out)[(int64_t)b * a.out_sb + (int64_t)cur.hd * a.out_sh + cur.p] = __float2half_rn(y);
+    }
+  }
+  if (lane == 0) bulk_wait_all<0>();
+}
+
 template <int LPR, bool kTied, bool kGrouped>
 __global__ void __launch_bounds__(256)
 sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, int* status) {
@@ -658,6 +807,28 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
   QB_REQUIRE(a->nheads % a->ngroups == 0, QB_ERR_INVALID_ARG, "nheads must be divisible by ngroups");
   QB_REQUIRE(!a->grouped || (a->head_group_range && a->dim_group_range && a->nhead_groups > 0 && a->ndim_groups > 0),
              QB_ERR_INVALID_ARG, "sscan_update: grouped scales need the range tables");
+  // warp-autonomous kernel: the Mamba2 decode shape (d_state 128, A tied across the state, per-tensor scales), fully
+  // contiguous state, 16-row tiles inside one head
+  if (a->dstate == 128 && a->A_sn == 0 && !a->grouped && a->headdim % kWTileRows == 0 && aligned(a->state, 16) &&
+      a->state_sp == a->dstate && a->state_sh == (int64_t)a->headdim * a->dstate &&
+      a->state_sb == (int64_t)a->nheads * a->headdim * a->dstate && aligned(a->Bm, 16) && aligned(a->Cm, 16) &&
+      a->B_sb % 16 == 0 && a->B_sg % 16 == 0 && a->C_sb % 16 == 0 && a->C_sg % 16 == 0 &&
+      getenv("QB_UPDATE_CTA_TILES") == nullptr) {
+    int* status = device_status_ptr();
+    QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "sscan_update: device status word unavailable");
+    static bool wattr = false;
+    const size_t wsmem = (size_t)8 * kWSlots * kWTileBytes;
+    if (!wattr) {
+      cudaFuncSetAttribute(sscan_update_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
+      wattr = true;
+    }
+    const int64_t rows = (int64_t)a->batch * a->nheads * a->headdim;
+    const int wtiles = (int)(rows / kWTileRows);
+    const int wctas = (int)std::min<int64_t>(ceil_div(wtiles, 8), (int64_t)sm_count() * 3);
+    launch_dependent(sscan_update_warp_kernel, dim3((unsigned)wctas), dim3(256), wsmem, (cudaStream_t)stream, *a, wtiles, status);
+    QB_LAUNCH_OK("sscan_update_warp_kernel");
+    return QB_OK;
+  }
   // pipelined kernel: fully contiguous state, dstate in {16, 32, 64, 128, 256}, whole 8 KB tiles inside one (batch, group)
   {
     const int lpr = a->dstate / 16;

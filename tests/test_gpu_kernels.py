@@ -375,9 +375,11 @@ def test_no_device_wait_timed_out():
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
 
 
-# ---- state update: the three kernels behind qb_sscan_update (pipelined bulk-copy, streaming, generic) ----------------
+# ---- state update: the kernels behind qb_sscan_update (warp-autonomous, pipelined bulk-copy, streaming, generic) -----
 @pytest.mark.parametrize("Bsz,H,P,G,N,grouped,layout", [
-    (3, 8, 64, 1, 128, False, "contig"),     # pipelined: 8 KB tiles of 64 rows
+    (3, 8, 64, 1, 128, False, "contig"),     # Mamba2 decode shape: warp-autonomous kernel (16-row tiles)
+    (7, 5, 48, 1, 128, False, "contig"),     # the same kernel: three tiles per head, 105 tiles over the warps
+    (4, 6, 32, 2, 128, False, "contig"),     # the same kernel: two SSD groups
     (2, 8, 64, 2, 128, True, "contig"),      # pipelined, grouped scales
     (2, 4, 64, 1, 256, False, "contig"),     # pipelined, 16 pieces per row
     (5, 1, 1024, 1, 16, False, "contig"),    # pipelined, Mamba1 shape (one piece per row), A not tied
@@ -394,6 +396,7 @@ def test_update_kernel_variants_against_oracle(Bsz, H, P, G, N, grouped, layout)
     A = ri8(H)[:, None, None].expand(H, P, N) if tied else ri8(H, P, N)
     Dq, bias = ri8(H, P), (torch.rand(H, P, generator=gen) * 2 - 4).half()
     s_dt, s_A, s_D = torch.tensor(0.02), torch.tensor(0.015), torch.tensor(0.01)
+    zq, s_z = (ri8(Bsz, H, P), torch.tensor(0.03)) if Bsz == 4 else (None, None)     # one case runs with the z gate
     if grouped:
         HG, DG = 2, 4
         hgr = torch.tensor([[H // G // 2, H // G]] * G, dtype=torch.int32)
@@ -406,7 +409,7 @@ def test_update_kernel_variants_against_oracle(Bsz, H, P, G, N, grouped, layout)
     else:
         xs, ss, sB, sC = torch.tensor([0.02]), torch.tensor([0.01]), torch.tensor([0.015]), torch.tensor([0.017])
         st_ref = state.clone()
-        y_ref, _ = oupd.quant_sscan_update(st_ref, x, xs, dt, s_dt, A, s_A, ss, Bm, sB, Cm, sC, Dq, s_D, None, None, bias, None, True)
+        y_ref, _ = oupd.quant_sscan_update(st_ref, x, xs, dt, s_dt, A, s_A, ss, Bm, sB, Cm, sC, Dq, s_D, zq, s_z, bias, None, True)
     if layout == "padded":
         buf = torch.zeros(Bsz, H, P, N + 16, dtype=torch.int8, device=DEV)
         st = buf[..., :N]
@@ -419,7 +422,7 @@ def test_update_kernel_variants_against_oracle(Bsz, H, P, G, N, grouped, layout)
                                                 dev(Bm), dev(sB), dev(Cm), dev(sC), dev(Dq), dev(s_D), None, None, dev(bias), True)
     else:
         out = ops().quant_sscan_update_triton(st, dev(x), dev(xs), dev(dt), dev(s_dt), A_dev, dev(s_A), dev(ss), dev(Bm), dev(sB),
-                                              dev(Cm), dev(sC), dev(Dq), dev(s_D), None, None, dev(bias), None, True)
+                                              dev(Cm), dev(sC), dev(Dq), dev(s_D), dev(zq), dev(s_z), dev(bias), None, True)
     assert_fp16(out, y_ref)
     assert_lsb(st, st_ref, max_frac=0.02)
     ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)      # raises if a device-side wait timed out
