@@ -99,6 +99,35 @@ def test_ssd_range_cuts_at_other_shapes(Bsz, Ls, Hs, monkeypatch):
     assert d.max().item() <= 1 and (d > 0).float().mean().item() <= 0.03
 
 
+def test_ssd_range_cuts_with_grouped_scales_and_per_channel_D(monkeypatch):
+    """192 pairs (more than SMs, so ranges are cut inside pairs), four SSD groups with grouped scale tables, D per channel
+    (the output step then re-reads x), 700 tokens (the last block of every pair is ragged)."""
+    Bsz, Ls, Hs, Gs = 6, 700, 32, 4
+    c = make_ssd_case(Bsz, Ls, Hs, P, Gs, N, Q, grouped=True, seed=77, d_has_hdim=True)
+
+    def run(sl=slice(None)):
+        y, fs = ops()._quamba2_mamba_chunk_scan_combined_fwd(
+            dev(c["q_x"][sl]), dev(c["x_scales"]), dev(c["hgr"]), dev(c["dgr"]), dev(c["q_dt"][sl]), dev(c["s_dt"]), dev(c["q_A_log"]),
+            dev(c["s_A"]), dev(c["q_B"][sl]), dev(c["s_B"]), dev(c["q_C"][sl]), dev(c["s_C"]), dev(c["state_scale"]), c["chunk"],
+            dev(c["q_D"]), dev(c["s_D"]), None, None, dev(c["dt_bias"]), None, None, None, True)
+        torch.cuda.synchronize()
+        from quamba_b200 import _lib
+        _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+        return y, fs
+
+    y_tc, f_tc = run()
+    y_1, f_1 = run(slice(2, 3))
+    assert torch.equal(y_tc[2], y_1[0]) and torch.equal(f_tc[2], f_1[0])
+    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
+    y_pt, f_pt = run()
+    monkeypatch.delenv("QB_SSD_PORTABLE")
+    err = (y_tc.float() - y_pt.float()).abs()
+    tol = 1e-2 * y_pt.float().abs() + 1e-3 * y_pt.float().abs().max()
+    assert (err <= tol).all(), f"max err {err.max().item()}"
+    d = (f_tc.int() - f_pt.int()).abs()
+    assert d.max().item() <= 1 and (d > 0).float().mean().item() <= 0.03
+
+
 def run_conv(c, xBC):
     o = ops().quamba2_conv1d_cuda.fwd(dev(xBC), c["sx"], c["sB"], c["sC"], c["x_dim"], P, N, G, dev(c["hgr"]), dev(c["dgr"]),
                                       dev(c["x_scales"]), dev(c["B_scales"]), dev(c["C_scales"]), dev(c["weight"]), c["swx"], c["swB"],
