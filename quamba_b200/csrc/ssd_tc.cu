@@ -618,13 +618,16 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (j + 1 < im.je) {   // the next item prepares the tile itself (zero state or a state from another CTA)
           store_s16();
           fence_proxy_async_smem();
-          gsync();
-          if (lead) { mbar_arrive(&ms.s16_ready); TRACE(0, it, 6); }
         }
+        // One barrier closes the state step and opens the output step: the polling thread waits for GEMM3 of this block
+        // (which never depends on the arrival below) and for the store of the previous block to have read the staging
+        // tile, all warps meet, and then the fp16 state is announced to the MMA issuer.
+        ok = gwait(&ms.y_ready, ph, it > 0 ? &ms.y_empty : nullptr, (it - 1) & 1);
+        if (lead && j + 1 < im.je) mbar_arrive(&ms.s16_ready);
+        if (lead) TRACE(0, it, 6);
+        if (!ok) break;
 
         // ================= P4: y(j) = sC 2^(a_m) D1 + sx (D2 + D x) ======================================================
-        ok = gwait(&ms.y_ready, ph, nullptr, 0);
-        if (!ok) break;
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 7);
         {
@@ -669,9 +672,8 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
             c2[t8] = make_uint4(o[0], o[1], o[2], o[3]);
           }
           // This thread's 32 bytes of the row go to the staging tile (128-byte swizzle, as the tensor map expects); the
-          // tile is free once the store of the previous block has read it, which happened a block ago.
-          if (it > 0 && !mbar_wait(&ms.y_empty, (it - 1) & 1, status, QB_ERR_TIMEOUT)) { ok = false; }
-          if (ok) {
+          // tile is free: the barrier that opened this step also waited for the previous block's store to have read it.
+          {
             uint8_t* yrow = smem + kOffY + row * 128;
             *reinterpret_cast<uint4*>(yrow + (((2 * sub) ^ sw) << 4)) = c2[0];
             *reinterpret_cast<uint4*>(yrow + (((2 * sub + 1) ^ sw) << 4)) = c2[1];
