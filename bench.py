@@ -354,6 +354,8 @@ def main():
     if pk.exists():
         peaks = json.loads(pk.read_text())
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    tensor_peak = float(peaks.get("bf16_tflops", 1590.0))
+    ssd_flops = float(B * H * ((L + 127) // 128) * (2 * 128 * 128 * 128 + 3 * 2 * 128 * 64 * 128))
     ssd_gbs = ssd_bytes / (ssd_ms * 1e-3) / 1e9
     conv_gbs = conv_bytes / (conv_ms * 1e-3) / 1e9
     line = {
@@ -369,6 +371,10 @@ def main():
         "roofline": {"kernel": "ssd_tc_kernel (+ ssd_prep_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
                      "frac": ssd_gbs / hbm_peak, "traffic": SSD_TRAFFIC_PER_BATCH_ROW * B, "peak_source": "measured" if peaks else "fallback",
                      "algorithmic_bytes": ssd_bytes, "ms": ssd_ms,
+                     # the same kernel against the tensor roofline (the op is balanced between the two): dense fp16 MMA
+                     # flops it issues per 128-token block (C.B^T 128x128x128 + three 128x64x128) over the measured bf16 peak
+                     "tensor": {"flops": ssd_flops, "achieved_tflops": ssd_flops / (ssd_ms * 1e-3) / 1e12,
+                                "peak_tflops": tensor_peak, "frac": ssd_flops / (ssd_ms * 1e-3) / 1e12 / tensor_peak},
                      "conv1d": {"achieved": conv_gbs, "frac": conv_gbs / hbm_peak, "algorithmic_bytes": conv_bytes, "ms": conv_ms}},
         "clocks": clocks,
     }
