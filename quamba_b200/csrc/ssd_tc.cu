@@ -599,10 +599,12 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         if (!ok) break;
         tc_fence_after_sync();
         if (lead) TRACE(0, it, 5);
+        uint32_t d1[16];   // C.S of this block, complete since GEMM2 (d1_ready): fetched here, one TMEM round trip early
         {
           const float dec = fast_exp2(r_tot);
           uint32_t sl[16];
           tmem_ld_32x16(tmem + tlane + kColS + 16 * sub, sl);
+          if (use_d1) tmem_ld_32x16(tmem + tlane + (st ? kColD1b : kColD1) + 16 * sub, d1);
           tmem_ld_wait();
           const float4* sb4 = reinterpret_cast<const float4*>(hc + kHcSbx + 16 * sub);
 #pragma unroll
@@ -633,9 +635,8 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         {
           uint4 xq = make_uint4(0, 0, 0, 0);
           if (d_per_channel && l < a.seqlen) xq = ldg_nc_now(xrow_base + (int64_t)l * a.x_sl);   // own 16 channels of x
-          uint32_t d2[16], d1[16];
+          uint32_t d2[16];
           tmem_ld_32x16(tmem + tlane + kColD2 + 16 * sub, d2);
-          if (use_d1) tmem_ld_32x16(tmem + tlane + (st ? kColD1b : kColD1) + 16 * sub, d1);
           tmem_ld_wait();
           tc_fence_before_sync();
           const float4* sx4 = reinterpret_cast<const float4*>(hc + kHcSx + 16 * sub);
