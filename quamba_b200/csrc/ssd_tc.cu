@@ -220,6 +220,9 @@ __device__ __forceinline__ void issue_gemm(uint32_t d_tmem, SmemDesc a, SmemDesc
   }
 }
 
+// kDPerChannel: D has one value per (head, channel) and is added in the output step (from a re-read of x); the common
+// case (one value per head, folded into the diagonal of Lm) compiles without that code.
+template <bool kDPerChannel>
 __global__ void __launch_bounds__(kThreads, 1)
 ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant__ CUtensorMap tm_c16,
               const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_out, qb_ssd_args a,
@@ -461,7 +464,7 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
             make_uint4(pack_h2(s_reg[8 * u], s_reg[8 * u + 1]), pack_h2(s_reg[8 * u + 2], s_reg[8 * u + 3]),
                        pack_h2(s_reg[8 * u + 4], s_reg[8 * u + 5]), pack_h2(s_reg[8 * u + 6], s_reg[8 * u + 7]));
     };
-    const bool d_per_channel = a.D != nullptr && a.D_has_hdim;   // then the skip term is added in the output step
+    constexpr bool d_per_channel = kDPerChannel;
     int it = 0;
     bool ok = true;
     for (int ii = 0; ii < plan.n_items && ok; ++ii) {
@@ -937,7 +940,8 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
   int dev = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
   if (dev >= 64 || !attr_set[dev]) {
-    QB_CUDA_OK(cudaFuncSetAttribute(ssd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    QB_CUDA_OK(cudaFuncSetAttribute(ssd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    QB_CUDA_OK(cudaFuncSetAttribute(ssd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     if (dev < 64) attr_set[dev] = true;
   }
   int* status = device_status_ptr();
@@ -961,7 +965,11 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
     cfg.numAttrs = 1;
     const float* ab_c = ab_ws;
     const float* hc_c = hc_ws;
-    QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status));
+    if (a->D != nullptr && a->D_has_hdim) {
+      QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel<true>, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status));
+    } else {
+      QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel<false>, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status));
+    }
   }
   return QB_OK;
 }
