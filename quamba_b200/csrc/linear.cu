@@ -158,14 +158,15 @@ constexpr int kGemvWarps = 8;
 constexpr int kNW = 2;
 
 template <int MB>
-__global__ void __launch_bounds__(kGemvWarps * 32)
+__global__ void __launch_bounds__(kGemvWarps * 32, 3)
 gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restrict__ W, int64_t ldw, int M, int N, int K,
                Epilogue ep) {
   grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
   const int lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW;
-  if (n0 >= N) return;
   const int chunks = K / 16;
+  // The grid is one wave of CTAs (three per SM); a warp walks its column pairs with the grid's stride.  One CTA per 16
+  // columns was 664 CTAs for the 2.7B in_proj: 1.5 to 2.2 waves of very short CTAs.
+  for (int n0 = (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW; n0 < N; n0 += (int)gridDim.x * kGemvWarps * kNW)
   for (int m0 = 0; m0 < M; m0 += MB) {
     int acc[MB][kNW];
 #pragma unroll
@@ -210,7 +211,7 @@ gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restri
 int launch_gemv(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K, const Epilogue& ep,
                 cudaStream_t st) {
   if (K % 16 != 0 || lda % 16 != 0 || ldw % 16 != 0 || !aligned(A, 16) || !aligned(W, 16)) return QB_ERR_UNSUPPORTED;
-  const unsigned grid = (unsigned)ceil_div(N, kGemvWarps * kNW);
+  const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(N, kGemvWarps * kNW), (int64_t)sm_count() * 3);
   if (M == 1) launch_dependent(gemv_s8_kernel<1>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
   else if (M == 2) launch_dependent(gemv_s8_kernel<2>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
   else if (M <= 4) launch_dependent(gemv_s8_kernel<4>, dim3(grid), dim3(kGemvWarps * 32), 0, st, A, lda, W, ldw, M, N, K, ep);
