@@ -175,17 +175,17 @@ def op_ssd_update(dev, gen, ops):
                 kernel="sscan_update_kernel", launches=1)
 
 
-def _w4a8(dev, gen, ops, M, K, N, out_int8, tag):
+def _w4a8(dev, gen, ops, M, K, N, out_int8, tag, group=128):
     from quamba_b200.packing import w4a8_quantize
     g = torch.Generator().manual_seed(1)
     w = (torch.randn(K, N, generator=g) * 0.02).half()
-    _, packed, sg, sc = w4a8_quantize(w, 4, 128)
+    _, packed, sg, sc = w4a8_quantize(w, 4, group)
     packed, sg, sc = packed.to(dev), sg.to(dev), sc.to(dev)
     by = M * K + K * N // 2 + M * N * (1 if out_int8 else 2)
     # The weights dominate the footprint of a decode-sized call: every input set then gets its own copy of them (the
     # int8 expansion the kernel streams is 2 bytes per packed byte), so that they come from HBM as they do in a model
     # whose layers each have their own weights, not from L2.
-    n = _sets_for(by if M >= 32 else M * K + K * N + M * N)
+    n = _sets_for(by if M >= 32 else M * K + (K * N if group > 0 else K * N // 2) + M * N)
     packs = [packed] if M >= 32 else [packed.clone() for _ in range(n)]
     xs = [_i8((M, K), dev, gen) for _ in range(n)]
     st = torch.tensor(0.03, device=dev)
@@ -194,7 +194,7 @@ def _w4a8(dev, gen, ops, M, K, N, out_int8, tag):
 
     def mk(i):
         return lambda: fn(xs[i], packs[i % len(packs)], st, sc, sg, ws, M, N, K, False)
-    return dict(workload=f"W4A8 GEMM {tag}: M{M} K{K} N{N}, int4 group-128 weights, {'int8' if out_int8 else 'fp16'} out",
+    return dict(workload=f"W4A8 GEMM {tag}: M{M} K{K} N{N}, int4 {'group-128' if group > 0 else 'per-channel'} weights, {'int8' if out_int8 else 'fp16'} out",
                 bytes=by, flops=2 * M * N * K, nsets=n, make=mk, kernel="gemm_s8_tcgen05_kernel", launches=1,
                 note="weights unpacked to int8 once at first use (cached); the timed GEMM streams int8 weights")
 
@@ -209,6 +209,10 @@ def op_w4a8_out(dev, gen, ops):
 
 def op_w4a8_decode(dev, gen, ops):
     return _w4a8(dev, gen, ops, 1, 2560, 10624, True, "Mamba2-2.7B in_proj, one token")
+
+
+def op_w4a8_decode_pc(dev, gen, ops):
+    return _w4a8(dev, gen, ops, 1, 2560, 10624, True, "Mamba2-2.7B in_proj, one token", group=-1)
 
 
 def op_w4a8_decode_b64(dev, gen, ops):
@@ -231,7 +235,7 @@ def op_w8a8(dev, gen, ops):
 
 
 OPS = {"conv": op_conv, "conv_update": op_conv_update, "hadamard": op_hadamard, "sscan": op_sscan, "ssd": op_ssd,
-       "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out, "w4a8_decode": op_w4a8_decode, "w4a8_decode_b64": op_w4a8_decode_b64,
+       "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out, "w4a8_decode": op_w4a8_decode, "w4a8_decode_pc": op_w4a8_decode_pc, "w4a8_decode_b64": op_w4a8_decode_b64,
        "w8a8": op_w8a8}
 
 

@@ -459,6 +459,30 @@ typedef struct {
 } qb_w4a8_gemm_args;
 int qb_w4a8_gemm(const qb_w4a8_gemm_args* a, void* stream);
 
+/* Decode-sized W4A8 product (1 <= m < 32) straight from 4-bit weights, for per-channel quantised weights (no group
+ * scales): the same result as qb_w4a8_gemm, bit for bit, from half the weight bytes.  (The reference has one kernel for
+ * all m, marlin_qqq_gemm_kernel.cuh:1187-1314; this is the small-m case of the same call.)
+ * qb_w4a8_pack_nibbles builds the weight copy it reads from the int8 copy qb_w4a8_unpack made: w4 (n, k / 2) bytes;
+ * 32-bit word i of a row covers k = 8 i .. 8 i + 7, value + 8 of k = 8 i + b in the low and of k = 8 i + 4 + b in the high
+ * nibble of byte b.  k must be a multiple of 32, a rows 16-byte aligned. */
+typedef struct {
+  const int8_t* a;
+  const uint8_t* w4;
+  const float* s_channel_nat;
+  const float* s_tok;
+  void* out;
+  int64_t a_row_stride;
+  int64_t out_row_stride;
+  int32_t m;
+  int32_t n;
+  int32_t k;
+  int32_t s_tok_per_row;
+  int32_t out_int8;
+  int32_t output_transpose;
+} qb_w4a8_gemv_s4_args;
+int qb_w4a8_pack_nibbles(const int8_t* w8, uint8_t* w4, int32_t n, int32_t k, void* stream);
+int qb_w4a8_gemv_s4(const qb_w4a8_gemv_s4_args* a, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * W8A8 linears.
  * Replaces quant_linear_cuda.cutlass_scaled_mm_dq / cutlass_scaled_mv_dq / w8a8o8_gemv

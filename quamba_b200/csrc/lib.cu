@@ -72,6 +72,7 @@ extern "C" int64_t qb_sizeof(const char* name) {
   QB_SZ(qb_ssd_args);
   QB_SZ(qb_w4a8_unpack_args);
   QB_SZ(qb_w4a8_gemm_args);
+  QB_SZ(qb_w4a8_gemv_s4_args);
   QB_SZ(qb_w8a8_gemm_args);
 #undef QB_SZ
   return -1;

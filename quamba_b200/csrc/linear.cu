@@ -208,6 +208,90 @@ gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restri
   }
 }
 
+// ---- decode-sized product straight from 4-bit weights ------------------------------------------------------------
+// Per-channel quantised W4A8 weights are 16 * s with s the signed nibble, so the int8 copy the other kernels stream
+// carries only four bits of information per byte.  For weight-streaming shapes (M < 32) this kernel reads a nibble-packed
+// copy instead: row n holds K / 2 bytes; 32-bit word i of a row covers k = 8 i .. 8 i + 7 with u[8 i + b] in the low and
+// u[8 i + 4 + b] in the high nibble of byte b, u = s + 8 in 0..15, so that (word & 0x0f0f0f0f) and (word >> 4) & 0x0f0f0f0f
+// line up with two consecutive words of the activation row for dp4a.  sum_k a s = sum_k a u - 8 sum_k a, times 16: the
+// same integer the int8 path accumulates, hence bit-identical outputs.
+__global__ void w4a8_pack_nibbles_kernel(const int8_t* __restrict__ w8, uint32_t* __restrict__ w4, int64_t words) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one output word = 8 weights
+  if (i >= words) return;
+  const uint2 v = *reinterpret_cast<const uint2*>(w8 + i * 8);
+  uint32_t out = 0;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int lo = ((int)(int8_t)(v.x >> (8 * b)) >> 4) + 8;   // 16 s -> s + 8
+    const int hi = ((int)(int8_t)(v.y >> (8 * b)) >> 4) + 8;
+    out |= (uint32_t)(lo | (hi << 4)) << (8 * b);
+  }
+  w4[i] = out;
+}
+
+template <int MB>
+__global__ void __launch_bounds__(kGemvWarps * 32, 3)
+gemv_s4_kernel(const int8_t* __restrict__ A, int64_t lda, const uint8_t* __restrict__ W4, int M, int N, int K, Epilogue ep) {
+  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
+  const int lane = threadIdx.x & 31;
+  const int chunks = K / 32;              // 16 bytes of weights = 32 values per lane and step
+  const int64_t ldw = K / 2;
+  for (int n0 = (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW; n0 < N; n0 += (int)gridDim.x * kGemvWarps * kNW)
+  for (int m0 = 0; m0 < M; m0 += MB) {
+    int acc[MB][kNW], sa[MB];
+#pragma unroll
+    for (int i = 0; i < MB; ++i) {
+      sa[i] = 0;
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) acc[i][j] = 0;
+    }
+#pragma unroll 2
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 w[kNW];
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) {
+        const int n = min(n0 + j, N - 1);
+        w[j] = __ldg(reinterpret_cast<const uint4*>(W4 + (int64_t)n * ldw) + c);
+      }
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const int m = min(m0 + i, M - 1);
+        const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + 2 * c);
+        const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + 2 * c + 1);
+        const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+        int s = sa[i];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) s = __dp4a(av[t], 0x01010101, s);
+        sa[i] = s;
+#pragma unroll
+        for (int j = 0; j < kNW; ++j) {
+          const uint32_t ww[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+          int t = acc[i][j];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            t = __dp4a(av[2 * q], (int)(ww[q] & 0x0f0f0f0fu), t);
+            t = __dp4a(av[2 * q + 1], (int)((ww[q] >> 4) & 0x0f0f0f0fu), t);
+          }
+          acc[i][j] = t;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MB; ++i) {
+      int s = sa[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) {
+        int t = acc[i][j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0 && m0 + i < M && n0 + j < N) ep.store(16 * (t - 8 * s), m0 + i, n0 + j);
+      }
+    }
+  }
+}
+
 int launch_gemv(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K, const Epilogue& ep,
                 cudaStream_t st) {
   if (K % 16 != 0 || lda % 16 != 0 || ldw % 16 != 0 || !aligned(A, 16) || !aligned(W, 16)) return QB_ERR_UNSUPPORTED;
@@ -305,4 +389,36 @@ extern "C" int qb_w8a8_gemm(const qb_w8a8_gemm_args* a, void* stream) {
   ep.out_kind = a->out_dtype == 0 ? (a->round_half_away ? kOutS8Away : kOutS8Rne) : (a->out_dtype == 1 ? kOutF16 : kOutBF16);
   ep.transpose = 0;
   return run_gemm(a->a, a->a_row_stride, a->b, a->b_col_stride, a->m, a->n, a->k, ep, (cudaStream_t)stream);
+}
+
+extern "C" int qb_w4a8_pack_nibbles(const int8_t* w8, uint8_t* w4, int32_t n, int32_t k, void* stream) {
+  QB_REQUIRE(w8 != nullptr && w4 != nullptr && n > 0 && k > 0, QB_ERR_INVALID_ARG, "w4a8_pack_nibbles: null pointer or empty shape");
+  QB_REQUIRE(k % 8 == 0 && aligned(w8, 8) && aligned(w4, 4), QB_ERR_INVALID_ARG, "w4a8_pack_nibbles: k must be a multiple of 8");
+  const int64_t words = (int64_t)n * k / 8;
+  w4a8_pack_nibbles_kernel<<<(unsigned)ceil_div(words, 256), 256, 0, (cudaStream_t)stream>>>(w8, reinterpret_cast<uint32_t*>(w4), words);
+  QB_LAUNCH_OK("w4a8_pack_nibbles_kernel");
+  return QB_OK;
+}
+
+extern "C" int qb_w4a8_gemv_s4(const qb_w4a8_gemv_s4_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr && a->a && a->w4 && a->s_channel_nat && a->s_tok && a->out, QB_ERR_INVALID_ARG, "w4a8_gemv_s4: null pointer");
+  QB_REQUIRE(a->m > 0 && a->m < 32 && a->n > 0 && a->k > 0, QB_ERR_INVALID_ARG, "w4a8_gemv_s4: m must be in 1..31");
+  QB_REQUIRE(a->k % 32 == 0 && a->a_row_stride % 16 == 0 && a->a_row_stride >= a->k && aligned(a->a, 16) && aligned(a->w4, 16),
+             QB_ERR_INVALID_ARG, "w4a8_gemv_s4: k must be a multiple of 32 and the rows 16-byte aligned");
+  QB_REQUIRE(a->out_row_stride >= (a->output_transpose ? a->m : a->n), QB_ERR_INVALID_ARG, "w4a8_gemv_s4: out_row_stride too small");
+  Epilogue ep{};
+  ep.row_scale = a->s_tok; ep.row_per = a->s_tok_per_row;
+  ep.col_scale = a->s_channel_nat; ep.col_per = 1;
+  ep.out = a->out; ep.out_stride = a->out_row_stride;
+  ep.out_kind = a->out_int8 ? kOutS8Rne : kOutF16;
+  ep.transpose = a->output_transpose;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(a->n, kGemvWarps * kNW), (int64_t)sm_count() * 3);
+  const int M = a->m;
+  if (M == 1) launch_dependent(gemv_s4_kernel<1>, dim3(grid), dim3(kGemvWarps * 32), 0, st, a->a, a->a_row_stride, a->w4, M, a->n, a->k, ep);
+  else if (M == 2) launch_dependent(gemv_s4_kernel<2>, dim3(grid), dim3(kGemvWarps * 32), 0, st, a->a, a->a_row_stride, a->w4, M, a->n, a->k, ep);
+  else if (M <= 4) launch_dependent(gemv_s4_kernel<4>, dim3(grid), dim3(kGemvWarps * 32), 0, st, a->a, a->a_row_stride, a->w4, M, a->n, a->k, ep);
+  else launch_dependent(gemv_s4_kernel<8>, dim3(grid), dim3(kGemvWarps * 32), 0, st, a->a, a->a_row_stride, a->w4, M, a->n, a->k, ep);
+  QB_LAUNCH_OK("gemv_s4_kernel");
+  return QB_OK;
 }

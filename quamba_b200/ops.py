@@ -18,6 +18,8 @@ Reference interfaces mirrored (paths inside the reference project):
 """
 import math
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -486,6 +488,26 @@ def prepare_w4a8_weight(b_q_weight, s_ch, s_group, size_n, size_k):
     return w8, sc
 
 
+_W4A8_NIBBLES = {}
+
+
+def _w4a8_nibbles(w8, size_n, size_k):
+    """The nibble-packed copy of a per-channel weight's int8 expansion, built once (cached by the expansion's storage)."""
+    key = (w8.data_ptr(), size_n, size_k)
+    hit = _W4A8_NIBBLES.get(key)
+    if hit is not None and hit[0] is w8:
+        return hit[1]
+    w4 = torch.empty((size_n, size_k // 2), dtype=torch.uint8, device=w8.device)
+    with torch.cuda.device(w8.device):
+        f = _lib.lib().qb_w4a8_pack_nibbles
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+        _lib.check(f(w8.data_ptr(), w4.data_ptr(), size_n, size_k, ctypes.c_void_p(_stream(w8))))
+    if len(_W4A8_NIBBLES) > 4096:
+        _W4A8_NIBBLES.clear()
+    _W4A8_NIBBLES[key] = (w8, w4)
+    return w4
+
+
 def _w4a8(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k, output_transpose, out_int8):
     _cuda_i8(a, "a")
     _req(a.dim() == 2 and a.stride(1) == 1, "a must be a row-major (m, k) matrix")
@@ -498,6 +520,15 @@ def _w4a8(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k
     shape = (size_n, size_m) if output_transpose else (size_m, size_n)
     out = torch.empty(shape, dtype=dt, device=a.device)
     if size_m == 0:
+        return out
+    if (0 < size_m < 32 and s_group.numel() == 0 and size_k % 32 == 0 and a.stride(0) % 16 == 0 and a.data_ptr() % 16 == 0):
+        # decode-sized call on per-channel weights: stream a nibble-packed copy (half the bytes, identical results)
+        w4 = _w4a8_nibbles(w8, size_n, size_k)
+        args = _lib.make("qb_w4a8_gemv_s4_args", a=_p(a), w4=_p(w4), s_channel_nat=_p(sc), s_tok=_p(s_tok), out=_p(out),
+                         a_row_stride=a.stride(0), out_row_stride=out.stride(0), m=size_m, n=size_n, k=size_k,
+                         s_tok_per_row=int(s_tok.numel() != 1), out_int8=int(out_int8),
+                         output_transpose=int(bool(output_transpose)))
+        _run("qb_w4a8_gemv_s4", args, a)
         return out
     args = _lib.make("qb_w4a8_gemm_args", a=_p(a), w8=_p(w8), s_channel_nat=_p(sc), s_tok=_p(s_tok), out=_p(out),
                      a_row_stride=a.stride(0), out_row_stride=out.stride(0), m=size_m, n=size_n, k=size_k,

@@ -43,7 +43,7 @@ def test_workspace_size_formula():
     ("qb_quamba2_conv1d_fwd", "qb_quamba2_conv1d_fwd_args"), ("qb_quamba2_conv1d_update", "qb_quamba2_conv1d_update_args"),
     ("qb_hadamard_quant", "qb_hadamard_quant_args"), ("qb_sscan_fwd", "qb_sscan_fwd_args"),
     ("qb_sscan_update", "qb_sscan_update_args"), ("qb_ssd_chunk_scan_fwd", "qb_ssd_args"),
-    ("qb_w4a8_unpack", "qb_w4a8_unpack_args"), ("qb_w4a8_gemm", "qb_w4a8_gemm_args"), ("qb_w8a8_gemm", "qb_w8a8_gemm_args")])
+    ("qb_w4a8_unpack", "qb_w4a8_unpack_args"), ("qb_w4a8_gemm", "qb_w4a8_gemm_args"), ("qb_w4a8_gemv_s4", "qb_w4a8_gemv_s4_args"), ("qb_w8a8_gemm", "qb_w8a8_gemm_args")])
 def test_null_arguments_are_rejected_on_the_host(fn, struct):
     lib = _lib.lib()
     args = _lib.make(struct)  # all pointers null, all sizes zero
