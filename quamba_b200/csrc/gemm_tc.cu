@@ -73,22 +73,28 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int m, int 
   }
 }
 
+// kBN: tile width.  128 for general shapes; 64 for a single row of tiles (M <= 128, weight streaming), where narrower
+// tiles put a CTA on every SM -- 83 CTAs of 128 columns cannot pull the weights of the 2.7B in_proj at HBM speed.
+// a_rows: rows of A that exist (the TMA box of A; the MMA still multiplies 128 rows, the rest of the tile is whatever
+// shared memory held, and those output rows are masked in the epilogue).
+template <int kBN>
 __global__ void __launch_bounds__(kThreads)
 gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                       int M, int N, int K, Epilogue ep, int* status) {
+                       int M, int N, int K, int a_rows, Epilogue ep, int* status) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
+  constexpr int kWBytes = kBN * BK;
   uint8_t* sW = smem + kStages * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kStages * kTileBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (kTileBytes + kWBytes));
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* accum_bar = bars + 2 * kStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * kBN;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -113,14 +119,14 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const int s = kb % kStages;
         const uint32_t ph = (kb / kStages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, status, QB_ERR_TIMEOUT)) break;
-        mbar_arrive_expect_tx(&full_bar[s], 2 * kTileBytes);
+        mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(a_rows * BK + kWBytes));
         tma_load_2d(sA + s * kTileBytes, &tmap_a, &full_bar[s], kb * BK, m0);
-        tma_load_2d(sW + s * kTileBytes, &tmap_w, &full_bar[s], kb * BK, n0);
+        tma_load_2d(sW + s * kWBytes, &tmap_w, &full_bar[s], kb * BK, n0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, BN);
+      constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, kBN);
       // descriptor words of stage 0; a stage / K step is one 32-bit add away (the issuer's instruction count per MMA
       // decides whether the tensor pipe stays fed)
       const SmemDesc da0 = make_smem_desc2(smem_u32(sA), 16, 1024, kSwizzle128B);
@@ -133,7 +139,7 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (!ok) break;
         tc_fence_after_sync();
         const SmemDesc da = desc_advance(da0, (uint32_t)s * kTileBytes);
-        const SmemDesc dw = desc_advance(dw0, (uint32_t)s * kTileBytes);
+        const SmemDesc dw = desc_advance(dw0, (uint32_t)s * kWBytes);
 #pragma unroll
         for (int k = 0; k < BK / 32; ++k)
           umma_i8(tmem_base, desc_advance(da, k * 32), desc_advance(dw, k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
@@ -149,7 +155,7 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     if (ok) {
       const int m = m0 + q * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < kBN; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
         tmem_ld_wait();
@@ -383,14 +389,24 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
     QB_LAUNCH_OK("gemm_s8_tcgen05_persistent_kernel");
     return QB_OK;
   }
-  rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, BK);
+  // a single row of tiles with too few 128-column tiles to occupy the GPU: 64-column tiles, and only the rows of A that exist
+  const bool narrow = M <= BM && ceil_div(N, BN) < sm_count();
+  const int bn = narrow ? 64 : BN;   // (32-column tiles were slower: every CTA re-reads the A tile)
+  const int a_rows = narrow ? (int)std::min<int64_t>(BM, ceil_div(M, 8) * 8) : BM;
+  if (narrow) {
+    rc = encode_tmap_2d_u8(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, a_rows, BK);
+    if (rc != QB_OK) return rc;
+  }
+  rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, bn, BK);
   if (rc != QB_OK) return rc;
   if (dev >= 64 || !attr_set[dev]) {
-    QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     if (dev < 64) attr_set[dev] = true;
   }
-  dim3 grid((unsigned)ceil_div(M, BM), (unsigned)ceil_div(N, BN));
-  gemm_s8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
+  dim3 grid((unsigned)ceil_div(M, BM), (unsigned)ceil_div(N, bn));
+  if (bn == 64) gemm_s8_tcgen05_kernel<64><<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, a_rows, ep, status);
+  else gemm_s8_tcgen05_kernel<128><<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, a_rows, ep, status);
   QB_LAUNCH_OK("gemm_s8_tcgen05_kernel");
   return QB_OK;
 }
