@@ -1,28 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized Mamba2 mixer hot path on B200.
+"""Benchmark: Quamba2 Mamba2-2.7B W4A8, prefill tok/s (L = 2048) and decode TPOT, on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --op NAME|all      # per-kernel lines (bench_ops.py), one GPU
+    python bench.py --op NAME|all        # one kernel of the path on its own (bench_ops.py), one GPU
+    python bench.py --op mixer_core      # the conv1d + SSD op-level configuration (bench_mixer_core.py)
 
-One "step" = one pass of the hot path over one batch of synthetic input:
-int8 causal conv1d over xBC (+SiLU, requant, x/B/C split) followed by the int8 SSD chunk scan with
-inter-chunk state passing, at the op configuration B4 L2048 H80 P64 G1 N128 Q256 W4 (the conv + SSD
-shapes of one Mamba2-2.7B layer at batch 4).  Prints ONE JSON line (see the keys below).
+Workload (one "step" = one prefill): d_model 2560, 64 layers, expand 2 (80 heads x 64), ngroups 1, d_state 128,
+d_conv 4, vocab 50288, random-init weights N(0, 0.02) quantized to int4 (per output channel; ``--group-size 128`` for
+the per-group format), int8 activations with static per-tensor scales calibrated on 4 random sequences, batch 1,
+2048 uniform-random token ids, then 256 greedy decode steps.  Prints ONE JSON line:
 
-  value     tokens/s with inputs resident in HBM (device-timed, CUDA events around CUDA-graph replays of the step, max over ranks)
-  e2e       the same through the public ops API with pinned HOST buffers: H2D of the int8 inputs and
-            D2H of y + final states inside the timed region
-  roofline  SSD forward (the dominant part): algorithmic bytes / its CUDA-event time vs measured HBM peak
-  cpu_baseline  the CPU oracle (torch fp32, all host threads) on a bounded sample, rank 0, N = 1 only
-  --impl reference  times that CPU path alone (the reference has no CPU implementation of its own and
-            its CUDA/Triton extensions cannot be installed offline; the oracle restates them)
+  value     prefill tokens/s, token ids resident on the device, the whole prefill replayed from one CUDA graph, CUDA
+            events on the replay stream, max over ranks
+  decode    TPOT: the decode step (embedding ... lm_head, greedy argmax, token fed back on the device) replayed 256 times
+  e2e       the same prefill from token ids in pinned HOST memory to last-token logits in HOST memory
+  roofline  the dominant kernel of the prefill (from a per-call CUDA-event trace of one eager prefill) against its roofline,
+            with every entry point's share of the step
+  cpu_baseline / --impl reference   the dequantise-then-fp32 torch path of oracle/ on the host cores, bounded sample
 """
 import argparse
 import json
 import os
-import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -30,360 +29,308 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
-CFG = dict(B=4, L=2048, H=80, P=64, G=1, N=128, Q=256, W=4)
-WORKLOAD = ("configs[1]: Mamba2 int8 causal_conv1d + SSD chunk scan, batch 4, seqlen 2048, nheads 80, headdim 64, "
-            "ngroups 1, d_state 128, chunk 256, d_conv 4")
+MODEL = dict(d_model=2560, n_layer=64, vocab_size=50288, d_state=128, d_conv=4, expand=2, headdim=64, ngroups=1, chunk_size=256)
+PROMPT, DECODE_TOKENS, CALIB_SEQS = 2048, 256, 4
+WORKLOAD = ("configs[2]: Quamba2 Mamba2-2.7B W4A8 (d_model 2560, 64 layers, 80 heads x 64, ngroups 1, d_state 128, d_conv 4, "
+            "vocab 50288), batch 1, prefill 2048 token ids, then 256 greedy decode tokens")
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one ssd_tc_kernel launch, from an ncu pass over this very benchmark
-# (batch 4: 65.2 MB read + 47.3 MB written; it grows with the number of (batch, head) pairs, hence per batch row).  Reads
-# are the inputs plus the widened B / C; of the 86 MB the kernel writes, part is still dirty in the 126 MB L2 when it ends.
-SSD_TRAFFIC_PER_BATCH_ROW = (65.17e6 + 47.30e6) / 4
+def peaks():
+    pk = ROOT / "MEASURED_PEAKS.json"
+    p = json.loads(pk.read_text()) if pk.exists() else {}
+    out = dict(hbm=float(p.get("hbm_gbs", 6650.0)), bf16=float(p.get("bf16_tflops", 1590.0)), source="measured" if p else "fallback")
+    i8 = ROOT / "profiles" / "int8_mma_peak.json"
+    if i8.exists():         # written from a run of `bench.py --op i8_peak` (a tcgen05 kind::i8 issue-rate measurement)
+        out["i8"], out["i8_source"] = float(json.loads(i8.read_text())["tops"]), "measured tcgen05 kind::i8 issue rate"
+    else:
+        out["i8"], out["i8_source"] = 2.0 * out["bf16"], "2 x the measured bf16 cuBLAS peak"
+    return out
 
 
-def algorithmic_bytes():
-    B, L, H, P, G, N, W = (CFG[k] for k in "BLHPGNW")
-    C = H * P + 2 * G * N
-    conv = 2 * B * C * L + C * (W + 1)
-    ssd = B * L * (H * P + H + 2 * G * N) + 2 * B * L * H * P + B * H * P * N
-    return conv, ssd
+def model_flops_and_bytes(m, L, group_size):
+    """Algorithmic int8 flops of one prefill and HBM bytes of one decode token (weights + states + head + embedding row)."""
+    D, H, P, G, N = m["d_model"] * m["expand"], m["d_model"] * m["expand"] // m["headdim"], m["headdim"], m["ngroups"], m["d_state"]
+    d_in_proj = 2 * D + 2 * G * N + H
+    gemm = 2 * L * m["d_model"] * (d_in_proj + D)
+    prefill_flops = m["n_layer"] * gemm + 2 * m["d_model"] * m["vocab_size"]
+    wbytes = lambda k, n: k * n // 2 + 4 * n + (0 if group_size < 0 else (k // 128) * n * 2)
+    layer = (wbytes(m["d_model"], d_in_proj) + wbytes(D, m["d_model"]) + 2 * H * P * N + 2 * 4 * (D + 2 * G * N) +
+             2 * m["d_model"] * 4 + 2 * D)
+    decode_bytes = m["n_layer"] * layer + wbytes(m["d_model"], m["vocab_size"]) + m["d_model"] // 2
+    return prefill_flops, decode_bytes, gemm
 
 
-class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
-
-    def __init__(self, index):
-        self.index = index
-        self.proc = None
-        self.lines = []
-
-    def start(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
-        except OSError:
-            self.proc = None
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0])); mx = float(parts[1])
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
-
-
-def make_inputs(seed, B=None):
-    from helpers import make_conv2_case, make_ssd_case
-    B = B or CFG["B"]
-    conv = make_conv2_case(B, CFG["L"], CFG["H"], CFG["P"], CFG["G"], CFG["N"], W=CFG["W"], seed=seed)
-    ssd = make_ssd_case(B, CFG["L"], CFG["H"], CFG["P"], CFG["G"], CFG["N"], CFG["Q"], seed=seed + 100)
-    return conv, ssd
-
-
-def cpu_step(conv, ssd):
-    """The CPU oracle's pass over one batch (dequantise -> fp32 torch)."""
+# ---- the CPU arm -----------------------------------------------------------------------------------------------------------
+def cpu_sample(layers=1, L=512, vocab=4096):
+    """oracle/'s dequantise-then-fp32 path on a bounded sample: ``layers`` layers at full width over ``L`` tokens, scaled
+    to 64 layers (every layer has the same shapes), plus the final norm and the head on the last token (vocabulary cut to
+    ``vocab`` rows to keep the set-up short; the head's share of a prefill is far below a percent)."""
     import torch
-    from oracle import conv1d as oconv, ssd as ossd
-    c = conv
-    x, Bm, Cm = oconv.quamba2_conv1d_fwd(c["xBC"], c["sx"], c["sB"], c["sC"], c["x_dim"], CFG["P"], CFG["N"], CFG["G"], None, None,
-                                         c["x_scales"], c["B_scales"], c["C_scales"], c["weight"], c["swx"], c["swB"], c["swC"],
-                                         c["bias"], c["sbx"], c["sbB"], c["sbC"])
-    Bsz, L = x.shape[0], x.shape[2]
-    qx = x.transpose(1, 2).reshape(Bsz, L, CFG["H"], CFG["P"])
-    qB = Bm.transpose(1, 2).reshape(Bsz, L, CFG["G"], CFG["N"])
-    qC = Cm.transpose(1, 2).reshape(Bsz, L, CFG["G"], CFG["N"])
-    s = ssd
-    return ossd.chunk_scan_faithful(qx, c["x_scales"], None, None, s["q_dt"], s["s_dt"], s["q_A_log"], s["s_A"], qB, c["B_scales"], qC,
-                                    c["C_scales"], s["state_scale"], CFG["Q"], s["q_D"], s["s_D"], None, None, s["dt_bias"], True)
-
-
-def time_cpu(steps, warmup):
-    import torch
+    from oracle import model as omodel
+    from quamba_b200 import calibrate as cal
     torch.set_num_threads(os.cpu_count() or 1)
-    conv, ssd = make_inputs(0, B=1)  # bounded sample: one of the four sequences
-    for _ in range(warmup):
-        cpu_step(conv, ssd)
+    cfg = dict(MODEL, n_layer=layers, vocab_size=vocab)
+    fm = cal.Mamba2LMFloat(**cfg, w4_group_size=-1, seed=0, device="cpu")
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, vocab, (1, L), generator=g)
+    q = cal.quantize_model(fm, cal.calibrate(fm, [ids[:, :128]]))
+    del fm
+    fp = omodel.FloatPath(q)
+    fp.prefill(ids[:, :64])
     t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_step(conv, ssd)
-    dt = (time.perf_counter() - t0) / steps
-    return CFG["L"] / dt, dt, "1 of the 4 sequences (batch 1, seqlen 2048, all 80 heads)"
+    fp.prefill(ids)
+    t_all = time.perf_counter() - t0
+    saved, fp.layers = fp.layers, []
+    t0 = time.perf_counter()
+    fp.prefill(ids)                                   # embedding + final norm + head only
+    t_rest = time.perf_counter() - t0
+    fp.layers = saved
+    per_layer = (t_all - t_rest) / layers
+    t_full = per_layer * MODEL["n_layer"] + t_rest
+    sample = (f"{layers} of the 64 layers at full width over {L} of the 2048 prompt tokens (batch 1), time scaled to 64 layers, "
+              f"vocabulary cut to {vocab}; torch fp32 on dequantised weights")
+    return L / t_full, t_full, sample
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank):
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    tok_s, dt, sample = time_cpu(steps, min(args.warmup, 1))
+    tok_s, t_full, sample = cpu_sample()
     cores = os.cpu_count() or 1
-    line = {"impl": "reference", "metric": "prefill_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
-            "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+    line = {"impl": "reference", "metric": "prefill_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": 1,
+            "warmup": 1, "ms_per_step": t_full * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
             "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--batch", type=int, default=CFG["B"],
-                    help="sequences per GPU; anything but the default is a reduced case for profiler captures, "
-                         "not the benchmark workload")
-    ap.add_argument("--op", default=None,
-                    help="measure one kernel of the path instead of the mixer step (see bench_ops.OPS; 'all' runs each); "
-                         "prints one JSON line per op")
-    args = ap.parse_args()
-    if args.op is not None:
-        import bench_ops
-        for line in bench_ops.run(args.op, args.steps, args.warmup):
-            print(json.dumps(line), flush=True)
-        return
-    global WORKLOAD
-    if args.batch != CFG["B"]:
-        WORKLOAD = WORKLOAD.replace("batch 4", f"batch {args.batch} (REDUCED from 4: profiling case)")
-        CFG["B"] = args.batch
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
+# ---- the GPU arm -----------------------------------------------------------------------------------------------------------
+def build_model(dev, group_size, seed, n_layer):
+    """Float model (fp16, torch) -> absmax calibration on 4 random sequences -> quantized model.  Offline work."""
+    import torch
+    from quamba_b200 import calibrate as cal
+    cfg = dict(MODEL, n_layer=n_layer)
+    fm = cal.Mamba2LMFloat(**cfg, w4_group_size=group_size, seed=seed, device=dev, dtype=torch.float16)
+    g = torch.Generator(device=dev).manual_seed(seed + 1)
+    seqs = [torch.randint(0, MODEL["vocab_size"], (1, PROMPT), generator=g, device=dev) for _ in range(CALIB_SEQS)]
+    q = cal.quantize_model(fm, cal.calibrate(fm, seqs))
+    del fm
+    torch.cuda.empty_cache()
+    return q
 
+
+def trace_shares(run, stream):
+    """One eager pass of ``run`` with a CUDA-event pair around every C-ABI call: {entry point: (calls, total ms)}."""
+    import torch
+    from quamba_b200 import _lib
+    sink = []
+    with torch.cuda.stream(stream):
+        run()
+        stream.synchronize()
+        _lib.set_call_trace(sink)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        run()
+        t1.record(stream)
+        _lib.set_call_trace(None)
+        stream.synchronize()
+    agg = {}
+    for fn, e0, e1 in sink:
+        c, ms = agg.get(fn, (0, 0.0))
+        agg[fn] = (c + 1, ms + e0.elapsed_time(e1))
+    return agg, t0.elapsed_time(t1)
+
+
+def measure(model, args, dev, rank, world, group_size):
     import torch
     import torch.distributed as dist
-    from quamba_b200 import ops, _lib
+    from quamba_b200 import _lib, ops
     from quamba_b200.sharding import max_over_ranks
-
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    warmup = max(args.warmup, 3)
-    steps = args.steps
-    to = lambda t: None if t is None else t.to(dev)
-
-    # ---- inputs: NSETS rotating sets so that consecutive steps never re-read L2-resident data ----
-    NSETS = 3
-    sets = []
-    for i in range(NSETS):
-        conv, ssd = make_inputs(1000 * rank + i)
-        C = conv["xBC"].shape[1]
-        host_xBC = conv["xBC"].transpose(1, 2).contiguous().pin_memory()       # (B, L, C) int8
-        host_dt = ssd["q_dt"].contiguous().pin_memory()
-        d = dict(conv=conv, ssd=ssd, host_xBC=host_xBC, host_dt=host_dt, xBC=host_xBC.to(dev).transpose(1, 2), q_dt=host_dt.to(dev),
-                 weight=to(conv["weight"]), bias=to(conv["bias"]), x_scales=to(conv["x_scales"]), B_scales=to(conv["B_scales"]),
-                 C_scales=to(conv["C_scales"]), s_dt=to(ssd["s_dt"]), q_A=to(ssd["q_A_log"]), s_A=to(ssd["s_A"]), q_D=to(ssd["q_D"]),
-                 s_D=to(ssd["s_D"]), dt_bias=to(ssd["dt_bias"]), state_scale=to(ssd["state_scale"]))
-        sets.append(d)
-    B, L, H, P, G, N, Q = (CFG[k] for k in "BLHPGNQ")
-
-    def conv_call(d, xBC):
-        c = d["conv"]
-        return ops.quamba2_conv1d_cuda.fwd(xBC, c["sx"], c["sB"], c["sC"], c["x_dim"], P, N, G, None, None, d["x_scales"], d["B_scales"],
-                                           d["C_scales"], d["weight"], c["swx"], c["swB"], c["swC"], d["bias"], c["sbx"], c["sbB"],
-                                           c["sbC"], None, None, None, True)
-
-    def ssd_call(d, x, Bm, Cm, q_dt):
-        qx = x.transpose(1, 2).reshape(B, L, H, P)
-        qB = Bm.transpose(1, 2).reshape(B, L, G, N)
-        qC = Cm.transpose(1, 2).reshape(B, L, G, N)
-        return ops._quant_mamba_chunk_scan_combined_fwd(qx, d["x_scales"], q_dt, d["s_dt"], d["q_A"], d["s_A"], qB, d["B_scales"], qC,
-                                                        d["C_scales"], d["state_scale"], Q, d["q_D"], d["s_D"], None, None, d["dt_bias"],
-                                                        None, None, None, True)
-
-    def step(d):
-        x, Bm, Cm = conv_call(d, d["xBC"])
-        return ssd_call(d, x, Bm, Cm, d["q_dt"])
+    steps, warmup = args.steps, max(args.warmup, 3)
+    L, ntok = args.seqlen, args.decode_tokens
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # Everything below runs on one side stream (CUDA-graph capture needs a non-default stream).
-    torch.cuda.synchronize()
-    stream = torch.cuda.Stream(device=dev)
-    torch.cuda.set_stream(stream)
-    for i in range(warmup):
-        step(sets[i % NSETS])
+    g = torch.Generator().manual_seed(1234 + rank)
+    host_ids = [torch.randint(0, MODEL["vocab_size"], (1, L), generator=g).pin_memory() for _ in range(3)]
+    dev_ids = [t.to(dev) for t in host_ids]
+    pre = model.capture_prefill(1, L)
+    st = pre.stream
+    with torch.cuda.stream(st):
+        for i in range(warmup):
+            pre.input_ids.copy_(dev_ids[i % 3]); pre.replay()
     barrier()
-    _lib.read_device_status(stream.cuda_stream)
+    _lib.read_device_status(st.cuda_stream)
 
-    # ---- CUDA graphs: the step, and its two parts, captured once per input set so that the timed region
-    # contains only device work (the Python/ctypes marshalling of each call is tens of microseconds) ----
-    graphs, conv_graphs, ssd_graphs, keep = [], [], [], []
-    for d in sets:
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
-            keep.append(step(d))
-        graphs.append(g)
-        gc = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gc, stream=stream):
-            xbc = conv_call(d, d["xBC"])
-        conv_graphs.append(gc)
-        gs = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gs, stream=stream):
-            keep.append(ssd_call(d, xbc[0], xbc[1], xbc[2], d["q_dt"]))
-        ssd_graphs.append(gs)
-        keep.append(xbc)
-    for i in range(warmup):
-        graphs[i % NSETS].replay()
-    barrier()
-
-    # ---- timed region: whole step, device timed ----
-    sampler = ClockSampler(local_rank)
+    # ---- timed region: K prefills, device timed ----
+    from bench_mixer_core import ClockSampler
+    sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    e0.record(stream)
-    for i in range(steps):
-        graphs[i % NSETS].replay()
-    e1.record(stream)
+    with torch.cuda.stream(st):
+        e0.record(st)
+        for i in range(steps):
+            pre.input_ids.copy_(dev_ids[i % 3], non_blocking=True); pre.replay()
+        e1.record(st)
     barrier()
-    ms_total = e0.elapsed_time(e1)
+    ms_prefill = e0.elapsed_time(e1) / steps
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- per-part timings for the roofline (same stream, CUDA events around K replays of each part) ----
-    def time_graphs(gl):
-        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for i in range(3):
-            gl[i % NSETS].replay()
-        a.record(stream)
-        for i in range(steps):
-            gl[i % NSETS].replay()
-        b_.record(stream)
-        b_.synchronize()
-        return a.elapsed_time(b_) / steps
-    conv_ms = time_graphs(conv_graphs)
-    ssd_ms = time_graphs(ssd_graphs)
-
-    # ---- end to end: pinned host inputs -> device -> hot path -> host outputs ----
-    # Every step copies its own inputs from pinned host memory and its own outputs back; the three stages (H2D, the two
-    # ops, D2H) run on three streams over two sets of buffers, so that the copies of neighbouring steps overlap with the
-    # kernels and with each other (PCIe is full duplex).  The timed region ends when the last output has reached the host.
-    NBUF = 2
-    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    slots = []
-    for _ in range(NBUF):
-        slots.append({
-            "host_y": torch.empty((B, L, H, P), dtype=torch.float16).pin_memory(),
-            "host_f": torch.empty((B, H, P, N), dtype=torch.int8).pin_memory(),
-            "dxBC": torch.empty_like(sets[0]["host_xBC"], device=dev), "ddt": torch.empty_like(sets[0]["host_dt"], device=dev),
-            "ev_in": torch.cuda.Event(), "ev_done": torch.cuda.Event(), "ev_out": torch.cuda.Event(), "y": None, "f": None})
-    host_y, host_f = slots[0]["host_y"], slots[0]["host_f"]
-
-    def e2e_run(n):
-        for i in range(n):
-            d, sl = sets[i % NSETS], slots[i % NBUF]
-            with torch.cuda.stream(s_in):
-                if i >= NBUF:
-                    s_in.wait_event(sl["ev_done"])          # the kernels of step i - NBUF have read these input buffers
-                sl["dxBC"].copy_(d["host_xBC"], non_blocking=True)
-                sl["ddt"].copy_(d["host_dt"], non_blocking=True)
-                sl["ev_in"].record(s_in)
-            with torch.cuda.stream(stream):
-                stream.wait_event(sl["ev_in"])
-                if i >= NBUF:
-                    stream.wait_event(sl["ev_out"])         # the outputs of step i - NBUF have left the device
-                x, Bm, Cm = conv_call(d, sl["dxBC"].transpose(1, 2))
-                sl["y"], sl["f"] = ssd_call(d, x, Bm, Cm, sl["ddt"])
-                sl["ev_done"].record(stream)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(sl["ev_done"])
-                sl["host_y"].copy_(sl["y"], non_blocking=True)
-                sl["host_f"].copy_(sl["f"], non_blocking=True)
-                sl["ev_out"].record(s_out)
-        for sl in slots[:min(n, NBUF)]:
-            stream.wait_event(sl["ev_out"])
-
-    with torch.cuda.stream(stream):
-        e2e_run(2)
-    torch.cuda.synchronize()
-    barrier()
+    # ---- end to end: pinned host token ids -> device -> prefill -> last-token logits in pinned host memory ----
+    host_logits = torch.empty((1, model.lm_head.out_features), dtype=torch.float16).pin_memory()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e2.record(stream)
-        e2e_run(steps)
-        e3.record(stream)
-    torch.cuda.synchronize()
     barrier()
-    ms_e2e = e2.elapsed_time(e3)
-    _lib.read_device_status(stream.cuda_stream)
+    with torch.cuda.stream(st):
+        e2.record(st)
+        for i in range(steps):
+            pre.input_ids.copy_(host_ids[i % 3], non_blocking=True)
+            pre.replay()
+            host_logits.copy_(pre.logits, non_blocking=True)
+        e3.record(st)
+    barrier()
+    ms_e2e = e2.elapsed_time(e3) / steps
 
-    ms_total, ms_e2e, conv_ms, ssd_ms = max_over_ranks([ms_total, ms_e2e, conv_ms, ssd_ms], device=dev)
+    # ---- decode: 256 greedy tokens from the prefill's caches, one CUDA graph per step ----
+    params = pre.inference_params
+    params.seqlen_offset = L
+    dec = model.capture_decode(1, L + ntok, inference_params=params)
+    with torch.cuda.stream(st):
+        dec.stream.wait_stream(st)
+    with torch.cuda.stream(dec.stream):
+        ops.greedy_next_token(pre.logits.contiguous(), out=dec.input_ids.view(-1))
+        for _ in range(8):
+            dec.replay()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dec.stream.synchronize()
+    barrier()
+    with torch.cuda.stream(dec.stream):
+        d0.record(dec.stream)
+        for _ in range(ntok):
+            dec.replay()
+        d1.record(dec.stream)
+    barrier()
+    tpot_ms = d0.elapsed_time(d1) / ntok
+    _lib.read_device_status(dec.stream.cuda_stream)
+
+    # ---- per entry point: CUDA events around every call of one eager prefill and one eager decode step ----
+    pparams = type(params)(max_seqlen=L + 1, max_batch_size=1, key_value_memory_dict=params.key_value_memory_dict)
+    shares_p, eager_ms = trace_shares(lambda: model(dev_ids[0], inference_params=pparams, num_last_tokens=1), st)
+    params.seqlen_offset = L
+    tok = dec.input_ids.clone()
+    shares_d, _ = trace_shares(lambda: model(tok, inference_params=params), st)
+    ms_prefill, ms_e2e, tpot_ms = max_over_ranks([ms_prefill, ms_e2e, tpot_ms], device=dev)
+    return dict(ms_prefill=ms_prefill, ms_e2e=ms_e2e, tpot_ms=tpot_ms, clocks=clocks, shares_p=shares_p, shares_d=shares_d,
+                eager_ms=eager_ms, h2d=host_ids[0].numel() * 8, d2h=host_logits.numel() * 2, L=L, ntok=ntok)
+
+
+def shares_table(agg):
+    total = sum(ms for _, ms in agg.values()) or 1.0
+    return {fn: {"calls": c, "ms": round(ms, 4), "share": round(ms / total, 4)} for fn, (c, ms) in
+            sorted(agg.items(), key=lambda kv: -kv[1][1])}
+
+
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+    model = build_model(dev, args.group_size, seed=rank, n_layer=args.layers)
+    r = measure(model, args, dev, rank, world, args.group_size)
+    extra = None
+    if args.also_group128 and args.group_size != 128:
+        del model
+        torch.cuda.empty_cache()
+        model = build_model(dev, 128, seed=rank, n_layer=args.layers)
+        extra = measure(model, args, dev, rank, world, 128)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-
-    tokens = B * L * world
-    ms_step = ms_total / steps
-    value = tokens / (ms_step * 1e-3)
-    e2e_val = tokens / (ms_e2e / steps * 1e-3)
-    conv_bytes, ssd_bytes = algorithmic_bytes()
-    peaks = {}
-    pk = ROOT / "MEASURED_PEAKS.json"
-    if pk.exists():
-        peaks = json.loads(pk.read_text())
-    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-    tensor_peak = float(peaks.get("bf16_tflops", 1590.0))
-    ssd_flops = float(B * H * ((L + 127) // 128) * (2 * 128 * 128 * 128 + 3 * 2 * 128 * 64 * 128))
-    ssd_gbs = ssd_bytes / (ssd_ms * 1e-3) / 1e9
-    conv_gbs = conv_bytes / (conv_ms * 1e-3) / 1e9
+    m = dict(MODEL, n_layer=args.layers)
+    flops, dbytes, gemm_flops_layer = model_flops_and_bytes(m, r["L"], args.group_size)
+    tokens = r["L"] * world
+    value = tokens / (r["ms_prefill"] * 1e-3)
+    sp = shares_table(r["shares_p"])
+    top = next(iter(sp))
+    top_ms = sp[top]["ms"]
+    if top in ("qb_w4a8_gemm", "qb_w8a8_gemm"):
+        achieved = m["n_layer"] * gemm_flops_layer / (top_ms * 1e-3) / 1e12
+        roof = {"kernel": "gemm_s8_tcgen05 (in_proj + out_proj of 64 layers)", "bound": "tensor", "achieved": achieved, "peak": pk["i8"],
+                "unit": "TOP/s", "frac": achieved / pk["i8"], "traffic": None, "peak_source": pk["i8_source"],
+                "algorithmic_flops": m["n_layer"] * gemm_flops_layer, "ms": top_ms}
+    else:
+        roof = {"kernel": top, "bound": "hbm", "achieved": None, "peak": pk["hbm"], "unit": "GB/s", "frac": None, "traffic": None,
+                "ms": top_ms}
+    roof["shares_prefill"] = sp
+    roof["shares_decode_step"] = shares_table(r["shares_d"])
+    roof["model_tensor_bound_ms"] = flops / (pk["i8"] * 1e12) * 1e3
+    reduced = args.layers != MODEL["n_layer"] or r["L"] != PROMPT
     line = {
-        "metric": "prefill_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 in / fp16+fp32 math",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": f"{NSETS} rotating input sets; per-step footprint exceeds the 126 MB L2",
-                   "sharding": "independent batches per GPU, no collective on this path",
-                   "e2e_pipeline": "H2D, kernels and D2H of neighbouring steps overlap (three streams, two buffer sets)"},
-        "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": int(sets[0]["host_xBC"].numel() + sets[0]["host_dt"].numel()),
-                "d2h_bytes_per_step": int(host_y.numel() * 2 + host_f.numel())},
-        "gpu_launches": 3 * steps,
-        "roofline": {"kernel": "ssd_tc_kernel (+ ssd_prep_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": ssd_gbs / hbm_peak, "traffic": SSD_TRAFFIC_PER_BATCH_ROW * B, "peak_source": "measured" if peaks else "fallback",
-                     "algorithmic_bytes": ssd_bytes, "ms": ssd_ms,
-                     # the same kernel against the tensor roofline (the op is balanced between the two): dense fp16 MMA
-                     # flops it issues per 128-token block (C.B^T 128x128x128 + three 128x64x128) over the measured bf16 peak
-                     "tensor": {"flops": ssd_flops, "achieved_tflops": ssd_flops / (ssd_ms * 1e-3) / 1e12,
-                                "peak_tflops": tensor_peak, "frac": ssd_flops / (ssd_ms * 1e-3) / 1e12 / tensor_peak},
-                     "conv1d": {"achieved": conv_gbs, "frac": conv_gbs / hbm_peak, "algorithmic_bytes": conv_bytes, "ms": conv_ms}},
-        "clocks": clocks,
+        "metric": "prefill_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": r["ms_prefill"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 (int4 weights, int8 activations, int32 accumulate; fp16 / fp32 scan and norm math)", "data": "synthetic",
+        "config": {"workload": WORKLOAD if not reduced else f"REDUCED (profiling case): {args.layers} layers, prompt {r['L']}; " + WORKLOAD,
+                   "weights": "int4 per output channel" if args.group_size < 0 else "int4 group 128",
+                   "l2": "every step streams 64 layers' weights (2.6 GB of int8 expansions) and rotates among 3 prompts: far beyond the 126 MB L2",
+                   "sharding": "one prompt per GPU, no collective (replicas)" if world > 1 else "single GPU",
+                   "graphs": "prefill and decode step replayed from CUDA graphs"},
+        "decode": {"tpot_ms": r["tpot_ms"], "tokens": r["ntok"], "tok_per_s": world * 1e3 / r["tpot_ms"],
+                   "hbm_bytes_per_token": dbytes, "hbm_bound_ms": dbytes / (pk["hbm"] * 1e9) * 1e3,
+                   "frac_of_hbm_bound": dbytes / (pk["hbm"] * 1e9) * 1e3 / r["tpot_ms"]},
+        "e2e": {"value": tokens / (r["ms_e2e"] * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+        "gpu_launches": args.steps * sum(c + (c if fn == "qb_ssd_chunk_scan_fwd" else 0) for fn, (c, _) in r["shares_p"].items()),
+        "roofline": roof, "eager_prefill_ms": r["eager_ms"], "clocks": r["clocks"],
     }
+    if extra is not None:
+        line["group128"] = {"value": tokens / (extra["ms_prefill"] * 1e-3), "unit": "tok/s", "tpot_ms": extra["tpot_ms"],
+                            "e2e": tokens / (extra["ms_e2e"] * 1e-3), "shares_decode_step": shares_table(extra["shares_d"])}
     if world == 1 and not args.no_cpu_baseline:
-        tok_s, dt, sample = time_cpu(1, 1)
+        tok_s, t_full, sample = cpu_sample()
         line["cpu_baseline"] = {"value": tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--op", default=None, help="'mixer_core' (conv1d + SSD op-level line) or one kernel of bench_ops.OPS / 'all'")
+    ap.add_argument("--batch", type=int, default=0, help="--op mixer_core only: sequences per GPU (reduced profiling case)")
+    ap.add_argument("--group-size", type=int, default=-1, choices=[-1, 128], help="int4 weight format: per output channel or group 128")
+    ap.add_argument("--also-group128", action="store_true", help="measure the group-128 weight format too (second model build)")
+    ap.add_argument("--layers", type=int, default=MODEL["n_layer"], help="fewer layers = a reduced profiling case, flagged in config")
+    ap.add_argument("--seqlen", type=int, default=PROMPT)
+    ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.op == "mixer_core":
+        import bench_mixer_core
+        bench_mixer_core.run(args)
+    elif args.op is not None:
+        import bench_ops
+        for line in bench_ops.run(args.op, args.steps, args.warmup):
+            print(json.dumps(line), flush=True)
+    elif args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, local_rank, world)
 
 
 if __name__ == "__main__":

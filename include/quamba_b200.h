@@ -514,6 +514,78 @@ typedef struct {
 } qb_w8a8_gemm_args;
 int qb_w8a8_gemm(const qb_w8a8_gemm_args* a, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Quantised RMSNorm with residual add, and gated grouped RMSNorm.
+ * qb_rmsnorm_quant replaces _qlayer_norm_fwd (quamba/triton/quant_norm.py:68-206, called by
+ *   QRMSNorm.forward, quamba/qNorm.py:52-87): h = x (+ residual); residual_out = h (stored in its
+ *   own dtype); y = h * rstd * weight (+ bias), rstd = 1 / sqrt(mean(h^2) + eps) (is_rms_norm != 0;
+ *   otherwise the mean is removed first); ngroups must be 1, z null.
+ * qb_rmsnorm_gated replaces _qlayer_normgated_fwd (quamba/triton/quant_normgated.py:11-132, called
+ *   by QRMSNormGated.forward, quamba/qNorm.py:145-174): each row is ngroups segments of group_size
+ *   elements normalised on their own; z int8 (nullable) gates with g = z_scale*z, silu(g) = g*sigmoid(g):
+ *   x*silu(g) before the norm (norm_before_gate == 0) or y*silu(g) after it; no residual.
+ * x, weight, bias fp16; residual / residual_out fp16 or fp32 (the *_is_f32 flags).
+ * out_kind 0: int8 = clamp(rint(y / out_scale));  1: int8 with one scale per (group, row),
+ * scale = max(y) / 127 written to dyn_scale[group * rows + row] (the reference takes the maximum of y,
+ * not of |y|, over a power-of-two block padded with zeros; reproduced);  2: fp16.
+ * Row strides in elements.  group_size * 2 must stay below 64 KB as in the reference.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const void* x;
+  const void* residual;
+  void* residual_out;
+  const int8_t* z;
+  const void* weight;
+  const void* bias;
+  void* out;
+  float* dyn_scale;
+  int64_t x_row_stride;
+  int64_t residual_row_stride;
+  int64_t residual_out_row_stride;
+  int64_t z_row_stride;
+  int64_t out_row_stride;
+  int32_t rows;
+  int32_t group_size;
+  int32_t ngroups;
+  int32_t residual_is_f32;
+  int32_t residual_out_is_f32;
+  int32_t out_kind;
+  int32_t norm_before_gate;
+  int32_t is_rms_norm;
+  float eps;
+  float out_scale;
+  float z_scale;
+} qb_rmsnorm_args;
+int qb_rmsnorm_quant(const qb_rmsnorm_args* a, void* stream);
+int qb_rmsnorm_gated(const qb_rmsnorm_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Token embedding gather with fp16 output.
+ * Replaces quant_embedding_cuda.w4a16_embedding_lookup / w8a16_embedding_lookup
+ *   (csrc/embedding/quant_embedding_kernel.cuh:47-139, :172-260) and torch's fp16 nn.Embedding.
+ * kind 0: table fp16 (vocab, dim).  kind 1: table int8 (vocab, dim), scales fp16 (vocab):
+ * out = scale * half(q).  kind 2: table int32 (vocab, dim / 8), eight 4-bit values (+8) per word
+ * with nibble i holding element [0,2,4,6,1,3,5,7][i], scales fp16 (vocab): out = half(q - 8) * scale.
+ * tokens int64 (n_tokens); out fp16 (n_tokens, dim) contiguous.  A token id outside [0, vocab)
+ * reads row 0 and is reported by qb_read_device_status.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const void* table;
+  const void* scales;
+  const int64_t* tokens;
+  void* out;
+  int64_t n_tokens;
+  int32_t dim;
+  int32_t vocab;
+  int32_t kind;
+} qb_embedding_args;
+int qb_embedding_lookup(const qb_embedding_args* a, void* stream);
+
+/* Greedy next token: out[r] = index of the largest of the n fp16 logits of row r (lowest index among equals).
+ * Replaces the logits.argmax(dim=-1) of the reference's greedy decode loop (profile_mamba.py:317-392), so that a
+ * captured decode step can feed its own next input.  row_stride in elements. */
+int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t n, int64_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,8 @@ reference's own extension-level and module-level interfaces:
     from quamba_b200 import ops                 # quant_sscan_cuda, quamba2_conv1d_cuda, ...
     from quamba_b200 import QSScan, Quamba2ChunkScan, QCausalConv1D, Quamb2Conv1D, QHadamard, \
         W4A8B16O16Linear, W4A8B8O8Linear, W4A8B8O8LinearParallel, W8A8B8O8Linear, \
-        W8A8B8O8LinearParallel, W8A8B16O16Linear
+        W8A8B8O8LinearParallel, W8A8B16O16Linear, QRMSNorm, QRMSNormGated, W4O16Embedding, W8O16Embedding, \
+        W4A8QMamba2, W8A8QMamba2, QuambaLMHeadModel
 
 Importing the package does not touch the GPU; the shared library is loaded on first use and
 its absence is an error (there is no CPU or PyTorch fallback).
@@ -17,5 +18,9 @@ from .modules import (QCausalConv1D, QHadamard, QSScan, Quamb2Conv1D, Quamba2Chu
                       W4A8B8O8Linear, W4A8B8O8LinearParallel, W4A8B16O16Linear, W8A8B8O8Linear,
                       W8A8B8O8LinearParallel, W8A8B16O16Linear)
 from .packing import w4a8_quantize  # noqa: F401
+from .norm import QRMSNorm, QRMSNormGated  # noqa: F401
+from .embedding import W4O16Embedding, W8O16Embedding  # noqa: F401
+from .mixer import W4A8QMamba2, W8A8QMamba2  # noqa: F401
+from .model import InferenceParams, QuambaConfig, QuambaLMHeadModel, QuambaMixerModel  # noqa: F401
 
 __version__ = "0.1.0"

@@ -94,9 +94,29 @@ def check(status: int):
         raise RuntimeError(f"quamba_b200 error {status}: {msg}")
 
 
+# Optional per-call trace for benchmarks: when a list is installed with set_call_trace(), every C-ABI call appends
+# (entry point, start, end) with two CUDA events recorded on the call's stream right around the launch.
+_trace = None
+
+
+def set_call_trace(sink):
+    """``sink``: a list to append (fn, start_event, end_event) to, or None to switch tracing off."""
+    global _trace
+    _trace = sink
+
+
 def call(fn: str, args, stream: int):
     f = getattr(lib(), fn)
+    if _trace is None:
+        check(f(ctypes.byref(args), ctypes.c_void_p(stream)))
+        return
+    import torch
+    ext = torch.cuda.ExternalStream(stream)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ext)
     check(f(ctypes.byref(args), ctypes.c_void_p(stream)))
+    e1.record(ext)
+    _trace.append((fn, e0, e1))
 
 
 def read_device_status(stream: int):

@@ -49,8 +49,12 @@ extern "C" int qb_read_device_status(void* stream) {
   QB_CUDA_OK(cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost));
   if (v != 0) {
     QB_CUDA_OK(cudaMemset(p, 0, sizeof(int)));
+    if (v == 501) {
+      qb::set_error("embedding_lookup met a token id outside the table (code %d)", v);
+      return QB_ERR_INVALID_ARG;
+    }
     qb::set_error("a bounded device-side wait expired (code %d)", v);
-    return v;
+    return QB_ERR_TIMEOUT;
   }
   return QB_OK;
 }
@@ -74,6 +78,8 @@ extern "C" int64_t qb_sizeof(const char* name) {
   QB_SZ(qb_w4a8_gemm_args);
   QB_SZ(qb_w4a8_gemv_s4_args);
   QB_SZ(qb_w8a8_gemm_args);
+  QB_SZ(qb_rmsnorm_args);
+  QB_SZ(qb_embedding_args);
 #undef QB_SZ
   return -1;
 }

@@ -1,0 +1,361 @@
+// Quantised RMSNorm (+ residual add) and gated, grouped RMSNorm for sm_100a.
+//
+// Both are one streaming pass: a normalised segment (a row, or one group of a row) is held in registers by
+// 32 * WPR threads (16-byte loads, eight fp16 values per chunk), reduced with shuffles (and one shared-memory
+// hop when several warps share a segment), scaled, and written as int8 (static or per-token scale) or fp16.
+// Arithmetic follows the reference's Triton kernels: fp32 throughout, rstd = 1 / sqrt(mean(x^2) + eps),
+// y = x * rstd * w (+ b), int8 = clamp(rint(y / scale)).
+#include "common.cuh"
+
+namespace qb {
+namespace {
+
+enum { kOutS8Static = 0, kOutS8Dynamic = 1, kOutF16 = 2 };
+
+struct NormParams {
+  const __half* x;
+  const void* residual;
+  void* residual_out;
+  const int8_t* z;
+  const __half* w;
+  const __half* bias;
+  void* y;
+  float* dyn_scale;
+  int64_t x_stride, res_stride, res_out_stride, z_stride, y_stride;
+  int M, N, ngroups;      // N: elements per normalised segment
+  int res_f32, res_out_f32, out_kind, gate_first, rms, pad_zero;
+  float eps, out_scale, z_scale;
+};
+
+constexpr int kCH = 8;           // 16-byte chunks per thread, at most
+constexpr int kNormWarps = 8;    // warps per CTA (16 when one segment needs 16 warps)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Reduction over the WPR warps of one segment.  Every thread of the CTA calls it (segments past the end carry
+// neutral values), so the barrier is CTA-wide.
+template <int WPR, bool MAX>
+__device__ __forceinline__ float seg_reduce(float v, float* red, int warp, int lane) {
+  v = MAX ? warp_max(v) : warp_sum(v);
+  if (WPR == 1) return v;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int base = (warp / WPR) * WPR;
+  float r = red[base];
+#pragma unroll
+  for (int i = 1; i < WPR; ++i) r = MAX ? fmaxf(r, red[base + i]) : r + red[base + i];
+  return r;
+}
+
+// GATE: 0 no gate, 1 x * silu(z) before the norm, 2 y * silu(z) after it (z is then read a second time).
+template <int WPR, int GATE>
+__global__ void __launch_bounds__((WPR > kNormWarps ? WPR : kNormWarps) * 32)
+norm_quant_kernel(const NormParams p) {
+  constexpr int WARPS = WPR > kNormWarps ? WPR : kNormWarps;
+  constexpr int T = 32 * WPR;                 // threads per segment
+  __shared__ float red[WARPS];
+  grid_dependency_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (WARPS / WPR) + warp / WPR;
+  const bool live = unit < (int64_t)p.M * p.ngroups;
+  const int row = live ? (int)(unit / p.ngroups) : 0;
+  const int grp = live ? (int)(unit % p.ngroups) : 0;
+  const int t = (warp % WPR) * 32 + lane;
+  const int chunks = p.N >> 3;
+  const int64_t col0 = (int64_t)grp * p.N;
+
+  float v[kCH][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kCH; ++i) {
+    const int c = t + i * T;
+    const bool on = live && c < chunks;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+    if (on) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + col0) + c);
+      const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y;
+      }
+      if (GATE == 0 && p.residual != nullptr) {
+        if (p.res_f32) {
+          const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + (int64_t)row * p.res_stride + col0) + 2 * c;
+          const float4 a = __ldg(r), b = __ldg(r + 1);
+          v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
+          v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
+        } else {
+          const uint4 rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(p.residual) + (int64_t)row * p.res_stride + col0) + c);
+          const __half2* rh = reinterpret_cast<const __half2*>(&rr);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(rh[e]);
+            v[i][2 * e] += f.x; v[i][2 * e + 1] += f.y;
+          }
+        }
+      }
+      if (GATE == 0 && p.residual_out != nullptr) {
+        if (p.res_out_f32) {
+          float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.residual_out) + (int64_t)row * p.res_out_stride + col0) + 2 * c;
+          o[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          o[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        } else {
+          uint4 o;
+          __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(v[i][2 * e], v[i][2 * e + 1]);
+          *(reinterpret_cast<uint4*>(static_cast<__half*>(p.residual_out) + (int64_t)row * p.res_out_stride + col0) + c) = o;
+        }
+      }
+      if (GATE == 1) {
+        const uint2 zr = __ldg(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + c);
+        const uint32_t zw[2] = {zr.x, zr.y};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float zf = (float)(int8_t)(zw[e >> 2] >> (8 * (e & 3))) * p.z_scale;
+          v[i][e] *= zf * (1.0f / (1.0f + __expf(-zf)));
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += p.rms ? v[i][e] * v[i][e] : v[i][e];
+    }
+  }
+  const float inv_n = 1.0f / (float)p.N;
+  float mean = 0.f, var;
+  if (p.rms) {
+    var = seg_reduce<WPR, false>(sum, red, warp, lane) * inv_n;
+  } else {
+    mean = seg_reduce<WPR, false>(sum, red, warp, lane) * inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCH; ++i)
+      if (live && t + i * T < chunks) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { const float d = v[i][e] - mean; sq += d * d; }
+      }
+    var = seg_reduce<WPR, false>(sq, red, warp, lane) * inv_n;
+  }
+  const float rstd = 1.0f / sqrtf(var + p.eps);
+
+  float mx = p.pad_zero ? 0.f : -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kCH; ++i) {
+    const int c = t + i * T;
+    if (live && c < chunks) {
+      const uint4 wr = __ldg(reinterpret_cast<const uint4*>(p.w + col0) + c);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+      uint4 br = make_uint4(0, 0, 0, 0);
+      if (p.bias != nullptr) br = __ldg(reinterpret_cast<const uint4*>(p.bias + col0) + c);
+      const __half2* bh = reinterpret_cast<const __half2*>(&br);
+      uint32_t zw[2] = {0, 0};
+      if (GATE == 2) {
+        const uint2 zr = __ldg(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + c);
+        zw[0] = zr.x; zw[1] = zr.y;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 w2 = __half22float2(wh[e]);
+        const float2 b2 = __half22float2(bh[e]);
+        float y0 = (v[i][2 * e] - mean) * rstd * w2.x;
+        float y1 = (v[i][2 * e + 1] - mean) * rstd * w2.y;
+        if (p.bias != nullptr) { y0 += b2.x; y1 += b2.y; }
+        if (GATE == 2) {
+          const float z0 = (float)(int8_t)(zw[e >> 1] >> (16 * (e & 1))) * p.z_scale;
+          const float z1 = (float)(int8_t)(zw[e >> 1] >> (16 * (e & 1) + 8)) * p.z_scale;
+          y0 *= z0 * (1.0f / (1.0f + __expf(-z0)));
+          y1 *= z1 * (1.0f / (1.0f + __expf(-z1)));
+        }
+        v[i][2 * e] = y0; v[i][2 * e + 1] = y1;
+        mx = fmaxf(mx, fmaxf(y0, y1));
+      }
+    }
+  }
+  float scale = p.out_scale;
+  if (p.out_kind == kOutS8Dynamic) {
+    scale = seg_reduce<WPR, true>(mx, red, warp, lane) / 127.0f;
+    if (live && t == 0) p.dyn_scale[(int64_t)grp * p.M + row] = scale;
+  }
+#pragma unroll
+  for (int i = 0; i < kCH; ++i) {
+    const int c = t + i * T;
+    if (live && c < chunks) {
+      if (p.out_kind == kOutF16) {
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(v[i][2 * e], v[i][2 * e + 1]);
+        *(reinterpret_cast<uint4*>(static_cast<__half*>(p.y) + (int64_t)row * p.y_stride + col0) + c) = o;
+      } else {
+        int q[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[e] = __float2int_rn(__fdiv_rn(v[i][e], scale));
+        uint2 o;
+        o.x = pack4_sat_s8(q[0], q[1], q[2], q[3]);
+        o.y = pack4_sat_s8(q[4], q[5], q[6], q[7]);
+        *(reinterpret_cast<uint2*>(static_cast<int8_t*>(p.y) + (int64_t)row * p.y_stride + col0) + c) = o;
+      }
+    }
+  }
+}
+
+// Any segment length and alignment: one CTA per segment, three strided passes over global memory.
+__global__ void __launch_bounds__(256) norm_quant_generic_kernel(const NormParams p) {
+  __shared__ float red[8];
+  grid_dependency_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x / p.ngroups, grp = blockIdx.x % p.ngroups;
+  const int64_t col0 = (int64_t)grp * p.N;
+  auto load = [&](int j, float& zsig) {
+    float x = __half2float(p.x[(int64_t)row * p.x_stride + col0 + j]);
+    if (p.residual != nullptr)
+      x += p.res_f32 ? static_cast<const float*>(p.residual)[(int64_t)row * p.res_stride + col0 + j]
+                     : __half2float(static_cast<const __half*>(p.residual)[(int64_t)row * p.res_stride + col0 + j]);
+    zsig = 1.f;
+    if (p.z != nullptr) {
+      const float zf = (float)p.z[(int64_t)row * p.z_stride + col0 + j] * p.z_scale;
+      zsig = zf * (1.0f / (1.0f + __expf(-zf)));
+      if (p.gate_first) x *= zsig;
+    }
+    return x;
+  };
+  auto reduce = [&](float v, bool is_max) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int i = 1; i < 8; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+    return r;
+  };
+  float s = 0.f, zsig;
+  for (int j = threadIdx.x; j < p.N; j += 256) {
+    const float x = load(j, zsig);
+    if (p.residual_out != nullptr) {
+      if (p.res_out_f32) static_cast<float*>(p.residual_out)[(int64_t)row * p.res_out_stride + col0 + j] = x;
+      else static_cast<__half*>(p.residual_out)[(int64_t)row * p.res_out_stride + col0 + j] = __float2half_rn(x);
+    }
+    s += p.rms ? x * x : x;
+  }
+  const float inv_n = 1.0f / (float)p.N;
+  float mean = 0.f, var;
+  if (p.rms) {
+    var = reduce(s, false) * inv_n;
+  } else {
+    mean = reduce(s, false) * inv_n;
+    float sq = 0.f;
+    for (int j = threadIdx.x; j < p.N; j += 256) { const float d = load(j, zsig) - mean; sq += d * d; }
+    var = reduce(sq, false) * inv_n;
+  }
+  const float rstd = 1.0f / sqrtf(var + p.eps);
+  auto value = [&](int j) {
+    float zg;
+    float y = (load(j, zg) - mean) * rstd * __half2float(p.w[col0 + j]);
+    if (p.bias != nullptr) y += __half2float(p.bias[col0 + j]);
+    if (p.z != nullptr && !p.gate_first) y *= zg;
+    return y;
+  };
+  float scale = p.out_scale;
+  if (p.out_kind == kOutS8Dynamic) {
+    float mx = p.pad_zero ? 0.f : -INFINITY;
+    for (int j = threadIdx.x; j < p.N; j += 256) mx = fmaxf(mx, value(j));
+    scale = reduce(mx, true) / 127.0f;
+    if (threadIdx.x == 0) p.dyn_scale[(int64_t)grp * p.M + row] = scale;
+  }
+  for (int j = threadIdx.x; j < p.N; j += 256) {
+    const float y = value(j);
+    if (p.out_kind == kOutF16) static_cast<__half*>(p.y)[(int64_t)row * p.y_stride + col0 + j] = __float2half_rn(y);
+    else static_cast<int8_t*>(p.y)[(int64_t)row * p.y_stride + col0 + j] = (int8_t)rint_s8(__fdiv_rn(y, scale));
+  }
+}
+
+template <int WPR>
+void launch_norm(const NormParams& p, int64_t units, cudaStream_t st) {
+  constexpr int WARPS = WPR > kNormWarps ? WPR : kNormWarps;
+  const dim3 grid((unsigned)ceil_div(units, WARPS / WPR)), block(WARPS * 32);
+  if (p.z == nullptr) launch_dependent(norm_quant_kernel<WPR, 0>, grid, block, 0, st, p);
+  else if (p.gate_first) launch_dependent(norm_quant_kernel<WPR, 1>, grid, block, 0, st, p);
+  else launch_dependent(norm_quant_kernel<WPR, 2>, grid, block, 0, st, p);
+}
+
+int run_norm(const NormParams& p, cudaStream_t st) {
+  const int64_t units = (int64_t)p.M * p.ngroups;
+  if (units == 0) return QB_OK;
+  bool vec = p.N % 8 == 0 && p.N <= 8 * kCH * 32 * 16 && aligned(p.x, 16) && p.x_stride % 8 == 0 && aligned(p.w, 16) &&
+             aligned(p.y, 16) && p.y_stride % 16 == 0 && (p.bias == nullptr || aligned(p.bias, 16));
+  if (p.residual) vec = vec && aligned(p.residual, 16) && p.res_stride % 8 == 0;
+  if (p.residual_out) vec = vec && aligned(p.residual_out, 16) && p.res_out_stride % 8 == 0;
+  if (p.z) vec = vec && aligned(p.z, 8) && p.z_stride % 8 == 0;
+  if (!vec) {
+    QB_REQUIRE(units < (1ll << 31), QB_ERR_TOO_LARGE, "norm: too many rows");
+    launch_dependent(norm_quant_generic_kernel, dim3((unsigned)units), dim3(256), 0, st, p);
+    QB_LAUNCH_OK("norm_quant_generic_kernel");
+    return QB_OK;
+  }
+  const int chunks = p.N / 8;
+  int wpr = 1;
+  while (wpr * 32 * kCH < chunks) wpr *= 2;                 // fewest warps that hold the segment in registers
+  // few segments (decode): spread each over more warps, down to two chunks per thread, to shorten the dependent chain
+  while (wpr < 8 && wpr * 64 < chunks && units * (2 * wpr) <= (int64_t)sm_count() * 2 * kNormWarps) wpr *= 2;
+  switch (wpr) {
+    case 1: launch_norm<1>(p, units, st); break;
+    case 2: launch_norm<2>(p, units, st); break;
+    case 4: launch_norm<4>(p, units, st); break;
+    case 8: launch_norm<8>(p, units, st); break;
+    default: launch_norm<16>(p, units, st); break;
+  }
+  QB_LAUNCH_OK("norm_quant_kernel");
+  return QB_OK;
+}
+
+int check_and_run(const qb_rmsnorm_args* a, bool gated, void* stream) {
+  const char* who = gated ? "rmsnorm_gated" : "rmsnorm_quant";
+  QB_REQUIRE(a != nullptr && a->x && a->weight && a->out, QB_ERR_INVALID_ARG, "%s: null pointer", who);
+  QB_REQUIRE(a->rows >= 0 && a->group_size > 0 && a->ngroups > 0, QB_ERR_INVALID_ARG, "%s: bad shape", who);
+  QB_REQUIRE(a->out_kind >= 0 && a->out_kind <= 2, QB_ERR_INVALID_ARG, "%s: out_kind must be 0, 1 or 2", who);
+  QB_REQUIRE(a->out_kind != kOutS8Dynamic || a->dyn_scale != nullptr, QB_ERR_INVALID_ARG, "%s: per-token scales need dyn_scale", who);
+  QB_REQUIRE(a->out_kind != kOutS8Static || a->out_scale != 0.0f, QB_ERR_INVALID_ARG, "%s: static output scale is zero", who);
+  QB_REQUIRE((int64_t)a->group_size * 2 < 65536, QB_ERR_UNSUPPORTED, "This layer norm doesn't support feature dim >= 64KB.");
+  const int64_t width = (int64_t)a->group_size * a->ngroups;
+  QB_REQUIRE(a->x_row_stride >= width && a->out_row_stride >= width, QB_ERR_INVALID_ARG, "%s: row stride smaller than the row", who);
+  if (gated) {
+    QB_REQUIRE(a->residual == nullptr && a->residual_out == nullptr, QB_ERR_INVALID_ARG, "%s: takes no residual", who);
+    QB_REQUIRE(a->z == nullptr || a->z_row_stride >= width, QB_ERR_INVALID_ARG, "%s: z row stride smaller than the row", who);
+  } else {
+    QB_REQUIRE(a->z == nullptr && a->ngroups == 1, QB_ERR_INVALID_ARG, "%s: takes no gate and one group", who);
+    QB_REQUIRE(a->residual == nullptr || a->residual_row_stride >= width, QB_ERR_INVALID_ARG, "%s: residual row stride smaller than the row", who);
+    QB_REQUIRE(a->residual_out == nullptr || a->residual_out_row_stride >= width, QB_ERR_INVALID_ARG,
+               "%s: residual_out row stride smaller than the row", who);
+  }
+  NormParams p{};
+  p.x = static_cast<const __half*>(a->x); p.residual = a->residual; p.residual_out = a->residual_out; p.z = a->z;
+  p.w = static_cast<const __half*>(a->weight); p.bias = static_cast<const __half*>(a->bias); p.y = a->out; p.dyn_scale = a->dyn_scale;
+  p.x_stride = a->x_row_stride; p.res_stride = a->residual_row_stride; p.res_out_stride = a->residual_out_row_stride;
+  p.z_stride = a->z_row_stride; p.y_stride = a->out_row_stride;
+  p.M = a->rows; p.N = a->group_size; p.ngroups = a->ngroups;
+  p.res_f32 = a->residual_is_f32; p.res_out_f32 = a->residual_out_is_f32; p.out_kind = a->out_kind;
+  p.gate_first = a->z != nullptr && !a->norm_before_gate; p.rms = a->is_rms_norm != 0;
+  // The reference reduces max(y) over a power-of-two block whose padding lanes hold 0.
+  p.pad_zero = (a->group_size & (a->group_size - 1)) != 0;
+  p.eps = a->eps; p.out_scale = a->out_scale; p.z_scale = a->z_scale;
+  return run_norm(p, (cudaStream_t)stream);
+}
+
+}  // namespace
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qb_rmsnorm_quant(const qb_rmsnorm_args* a, void* stream) { return check_and_run(a, false, stream); }
+extern "C" int qb_rmsnorm_gated(const qb_rmsnorm_args* a, void* stream) { return check_and_run(a, true, stream); }

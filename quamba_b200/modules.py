@@ -561,28 +561,43 @@ class _W4A8Base(nn.Module):
         assert originalLayer.bias is None, "bias is not supported"
         bits, group_scale = 4, None
         group_size = 128 if originalLayer.in_features > 128 else -1
+        # a float layer may ask for per-output-channel int4 (group -1) with a ``w4_group_size`` attribute
+        group_size = getattr(originalLayer, "w4_group_size", group_size)
         if getattr(originalLayer, "apply_gptq", False):        # a GPTQ-processed layer carries its own grid
             bits, group_size = originalLayer.bits, originalLayer.group_size
-            group_scale = originalLayer.group_scale.to(torch.float16).cpu()
+            group_scale = originalLayer.group_scale.to(torch.float16)
         assert bits == 4, "only 4-bit weights are supported"
         if group_size not in (-1, 128):
             raise ValueError("Only groupsize -1 and 128 are supported.")
         dev = originalLayer.weight.device
         q = cls(originalLayer.in_features, originalLayer.out_features, group_size=128, device=dev)
         W = originalLayer.weight.detach()                       # (N, K), possibly already fake-quantised
-        ch_scale = (W.abs().amax(dim=1, keepdim=True) / 127.0).reshape(1, -1).float().cpu()
+        ch_scale = (W.abs().amax(dim=1, keepdim=True) / 127.0).reshape(1, -1).float()
         w_ref, packed, s_group, s_channel = w4a8_quantize(
-            W.cpu().to(torch.float16).t().contiguous(), bits, group_size, group_scale, ch_scale,
+            W.to(torch.float16).t().contiguous(), bits, group_size, group_scale, ch_scale,
             out_scales=out_scales, pad_out=q.pad_out)
         q.size_k, q.size_n = w_ref.shape
         q.weight, q.input_scale = packed.to(dev), input_scale.to(dev).float().reshape(())
         q.s_group, q.s_channel = s_group.to(dev), s_channel.to(dev)
         return q
 
+    def prepared(self):
+        """The streaming copies of this layer's weight (:class:`quamba_b200.ops.W4A8Prepared`), owned by the
+        module: built on first use, rebuilt when a buffer is replaced (``.to()``, ``load_state_dict``) or written
+        in place, freed with the module.  ``release_prepared()`` drops them early."""
+        prep = self.__dict__.get("_prep")
+        if prep is None or prep.stale(self.weight, self.s_channel, self.s_group):
+            prep = ops.prepare_w4a8_weight(self.weight, self.s_channel, self.s_group, self.size_n, self.size_k)
+            self.__dict__["_prep"] = prep
+        return prep
+
+    def release_prepared(self, w8=True, w4=True):
+        prep = self.__dict__.get("_prep")
+        if prep is not None:
+            prep.release(w8, w4)
+
     def _gemm(self, x2, transpose):
-        fn = ops.quant_linear_cuda.w4a8o8_gemm if self._out_int8 else ops.quant_linear_cuda.w4a8o16_gemm
-        return fn(x2, self.weight, self.input_scale, self.s_channel, self.s_group, self.workspace, x2.shape[0],
-                  self.size_n, self.size_k, transpose)
+        return ops.w4a8_linear(x2, self.prepared(), self.input_scale, transpose, self._out_int8)
 
     @torch.no_grad()
     def forward(self, x):

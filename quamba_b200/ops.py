@@ -15,10 +15,13 @@ Reference interfaces mirrored (paths inside the reference project):
   quant_linear_cuda.*                       csrc/linear/quant_linear.cpp:62-75
   _quant_/_quamba2_mamba_chunk_scan_combined_fwd   quamba/triton/quant_ssd_combined.py:11-166
   quant_/quamba2_sscan_update_triton        quamba/triton/selective_state_update.py:129-478
+  _qlayer_norm_fwd / _qlayer_normgated_fwd  quamba/triton/quant_norm.py:134-206, quant_normgated.py:85-132
+  quant_embedding_cuda.*                    csrc/embedding/quant_embedding_kernel.cuh:87-139, :207-260
 """
 import math
 
 import ctypes
+import weakref
 
 import torch
 
@@ -26,7 +29,8 @@ from . import _lib
 
 __all__ = ["quant_sscan_cuda", "quant_causal_conv1d_cuda", "quamba2_conv1d_cuda", "quant_hadamard",
            "quant_linear_cuda", "_quant_mamba_chunk_scan_combined_fwd", "_quamba2_mamba_chunk_scan_combined_fwd",
-           "quant_sscan_update_triton", "quamba2_sscan_update_triton", "prepare_w4a8_weight"]
+           "quant_sscan_update_triton", "quamba2_sscan_update_triton", "prepare_w4a8_weight", "_qlayer_norm_fwd",
+           "_qlayer_normgated_fwd", "quant_embedding_cuda"]
 
 
 def _p(t):
@@ -454,88 +458,130 @@ def _quamba2_mamba_chunk_scan_combined_fwd(q_x, x_scales, x_head_group_range, x_
 
 
 # ------------------------------------------------------------------------------------------------
-_W4A8_CACHE = {}
+class W4A8Prepared:
+    """The streaming copies of one Marlin-QQQ packed weight, owned by whoever prepared it (a linear module keeps
+    one; nothing global holds it).  ``sc`` fp32 (N) channel scales in natural order; ``w8`` int8 (N, K) the values
+    the reference kernel multiplies with; ``w4`` uint8 (N, K / 2) nibble copy of a per-channel weight for
+    decode-sized calls.  ``w8`` and ``w4`` are built on first use and can be dropped with :meth:`release`."""
+
+    def __init__(self, b_q_weight, s_ch, s_group, size_n, size_k):
+        _req(b_q_weight.is_cuda and b_q_weight.dtype == torch.int32, "b_q_weight must be an int32 CUDA tensor")
+        _req(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_size = 16")
+        _req(b_q_weight.shape[0] == size_k // 16, "Shape mismatch: b_q_weight.size(0) != size_k / tile_size")
+        _req(b_q_weight.shape[1] == size_n * 2, "Shape mismatch: b_q_weight.size(1) != size_n * tile_size / pack_factor")
+        _req(s_ch.numel() == size_n, f"Shape mismatch: s_ch.numel() = {s_ch.numel()}, size_n = {size_n}")
+        self.per_channel = s_group.numel() == 0
+        self.group = -1 if self.per_channel else size_k // s_group.shape[0]
+        _req(self.group in (-1, 128), f"Unexpected groupsize = {self.group}")
+        if not self.per_channel:
+            _req(s_group.dtype == torch.float16 and s_group.shape[1] == size_n, "s_group must be fp16 (K/128, N)")
+        # weak references: the prepared copies must not keep a deleted layer's buffers alive
+        self._src = tuple(weakref.ref(t) for t in (b_q_weight, s_ch, s_group))
+        self.size_n, self.size_k = size_n, size_k
+        self.versions = (b_q_weight._version, s_ch._version, s_group._version)
+        self.w8 = self.w4 = self.sc = None
+
+    def stale(self, b_q_weight, s_ch, s_group):
+        live = tuple(r() for r in self._src)
+        return (live[0] is not b_q_weight or live[1] is not s_ch or live[2] is not s_group
+                or self.versions != (b_q_weight._version, s_ch._version, s_group._version))
+
+    def _unpack(self):
+        packed, s_ch, s_group = (r() for r in self._src)
+        _req(packed is not None and s_ch is not None and s_group is not None, "the packed weight was freed")
+        dev = packed.device
+        w8 = torch.empty((self.size_n, self.size_k), dtype=torch.int8, device=dev)
+        sc = torch.empty((self.size_n,), dtype=torch.float32, device=dev)
+        args = _lib.make("qb_w4a8_unpack_args", packed=_p(packed.contiguous()),
+                         s_group=None if self.per_channel else _p(s_group.contiguous()),
+                         s_channel=_p(s_ch.contiguous().float()), w8=_p(w8), s_channel_nat=_p(sc),
+                         size_k=self.size_k, size_n=self.size_n, group_size=self.group if self.group > 0 else self.size_k)
+        _run("qb_w4a8_unpack", args, packed)
+        return w8, sc
+
+    def need_w8(self):
+        if self.w8 is None:
+            self.w8, self.sc = self._unpack()
+        return self.w8
+
+    def need_w4(self):
+        """Nibble copy (per-channel weights only); the int8 expansion it is built from is not kept unless it
+        already exists."""
+        if self.w4 is None:
+            w8 = self.w8
+            if w8 is None:
+                w8, self.sc = self._unpack()
+            w4 = torch.empty((self.size_n, self.size_k // 2), dtype=torch.uint8, device=w8.device)
+            with torch.cuda.device(w8.device):
+                f = _lib.lib().qb_w4a8_pack_nibbles
+                f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+                _lib.check(f(w8.data_ptr(), w4.data_ptr(), self.size_n, self.size_k, ctypes.c_void_p(_stream(w8))))
+            self.w4 = w4
+        return self.w4
+
+    def release(self, w8=True, w4=True):
+        if w8:
+            self.w8 = None
+        if w4:
+            self.w4 = None
+
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w8, self.w4, self.sc) if t is not None)
 
 
 def prepare_w4a8_weight(b_q_weight, s_ch, s_group, size_n, size_k):
-    """Unpack a Marlin-QQQ packed weight once into the streaming layout (int8 (N, K) + natural-order
-    channel scales).  Cached per (storage, version) so module forwards pay for it once."""
-    key = (b_q_weight.data_ptr(), b_q_weight._version, s_ch.data_ptr(), s_ch._version,
-           s_group.data_ptr() if s_group.numel() else 0, size_n, size_k)
-    hit = _W4A8_CACHE.get(key)
-    if hit is not None:
+    """Wrap a Marlin-QQQ packed weight for the B200 kernels.  The caller owns the result (and with it the
+    streaming copies); nothing is cached globally."""
+    return W4A8Prepared(b_q_weight, s_ch, s_group, size_n, size_k)
+
+
+# Extension-level calls receive raw tensors on every call.  Their prepared copies are remembered per weight
+# OBJECT (id of the packed tensor, checked against a weak reference, dropped by a finalizer when the tensor
+# dies), so an address re-used by the allocator can never hit another weight's entry.
+_W4A8_BY_ID = {}
+
+
+def _prepared_for(b_q_weight, s_ch, s_group, size_n, size_k):
+    key = id(b_q_weight)
+    hit = _W4A8_BY_ID.get(key)
+    if hit is not None and not hit.stale(b_q_weight, s_ch, s_group) and (hit.size_n, hit.size_k) == (size_n, size_k):
         return hit
-    _req(b_q_weight.is_cuda and b_q_weight.dtype == torch.int32, "b_q_weight must be an int32 CUDA tensor")
-    _req(size_k % 16 == 0, f"size_k = {size_k} is not divisible by tile_size = 16")
-    _req(b_q_weight.shape[0] == size_k // 16, "Shape mismatch: b_q_weight.size(0) != size_k / tile_size")
-    _req(b_q_weight.shape[1] == size_n * 2, "Shape mismatch: b_q_weight.size(1) != size_n * tile_size / pack_factor")
-    _req(s_ch.numel() == size_n, f"Shape mismatch: s_ch.numel() = {s_ch.numel()}, size_n = {size_n}")
-    per_channel = s_group.numel() == 0
-    group = -1 if per_channel else size_k // s_group.shape[0]
-    _req(group in (-1, 128), f"Unexpected groupsize = {group}")
-    if not per_channel:
-        _req(s_group.dtype == torch.float16 and s_group.shape[1] == size_n, "s_group must be fp16 (K/128, N)")
-    w8 = torch.empty((size_n, size_k), dtype=torch.int8, device=b_q_weight.device)
-    sc = torch.empty((size_n,), dtype=torch.float32, device=b_q_weight.device)
-    args = _lib.make("qb_w4a8_unpack_args", packed=_p(b_q_weight.contiguous()),
-                     s_group=None if per_channel else _p(s_group.contiguous()),
-                     s_channel=_p(s_ch.contiguous().float()), w8=_p(w8), s_channel_nat=_p(sc), size_k=size_k,
-                     size_n=size_n, group_size=group if group > 0 else size_k)
-    _run("qb_w4a8_unpack", args, b_q_weight)
-    if len(_W4A8_CACHE) > 4096:
-        _W4A8_CACHE.clear()
-    _W4A8_CACHE[key] = (w8, sc)
-    return w8, sc
+    prep = W4A8Prepared(b_q_weight, s_ch, s_group, size_n, size_k)
+    _W4A8_BY_ID[key] = prep
+    weakref.finalize(b_q_weight, _W4A8_BY_ID.pop, key, None)
+    return prep
 
 
-_W4A8_NIBBLES = {}
-
-
-def _w4a8_nibbles(w8, size_n, size_k):
-    """The nibble-packed copy of a per-channel weight's int8 expansion, built once (cached by the expansion's storage)."""
-    key = (w8.data_ptr(), size_n, size_k)
-    hit = _W4A8_NIBBLES.get(key)
-    if hit is not None and hit[0] is w8:
-        return hit[1]
-    w4 = torch.empty((size_n, size_k // 2), dtype=torch.uint8, device=w8.device)
-    with torch.cuda.device(w8.device):
-        f = _lib.lib().qb_w4a8_pack_nibbles
-        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
-        _lib.check(f(w8.data_ptr(), w4.data_ptr(), size_n, size_k, ctypes.c_void_p(_stream(w8))))
-    if len(_W4A8_NIBBLES) > 4096:
-        _W4A8_NIBBLES.clear()
-    _W4A8_NIBBLES[key] = (w8, w4)
-    return w4
-
-
-def _w4a8(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k, output_transpose, out_int8):
+def _w4a8(a, prep, s_tok, size_m, size_n, size_k, output_transpose, out_int8):
     _cuda_i8(a, "a")
     _req(a.dim() == 2 and a.stride(1) == 1, "a must be a row-major (m, k) matrix")
     _req(size_m == a.shape[0], f"Shape mismatch: a.size(0) = {a.shape[0]}, size_m = {size_m}")
     _req(size_k == a.shape[1], f"Shape mismatch: a.size(1) = {a.shape[1]}, size_k = {size_k}")
     _req(s_tok.numel() in (1, size_m), f"s_tok.numel() = {s_tok.numel()} is not 1 or equal to size_m = {size_m}")
     _scale_t(s_tok, "s_tok", a.device)
-    w8, sc = prepare_w4a8_weight(b_q_weight, s_ch, s_group, size_n, size_k)
     dt = torch.int8 if out_int8 else torch.float16
     shape = (size_n, size_m) if output_transpose else (size_m, size_n)
     out = torch.empty(shape, dtype=dt, device=a.device)
     if size_m == 0:
         return out
-    if (0 < size_m < 32 and s_group.numel() == 0 and size_k % 32 == 0 and a.stride(0) % 16 == 0 and a.data_ptr() % 16 == 0):
-        # decode-sized call on per-channel weights: stream a nibble-packed copy (half the bytes, identical results)
-        w4 = _w4a8_nibbles(w8, size_n, size_k)
-        args = _lib.make("qb_w4a8_gemv_s4_args", a=_p(a), w4=_p(w4), s_channel_nat=_p(sc), s_tok=_p(s_tok), out=_p(out),
-                         a_row_stride=a.stride(0), out_row_stride=out.stride(0), m=size_m, n=size_n, k=size_k,
-                         s_tok_per_row=int(s_tok.numel() != 1), out_int8=int(out_int8),
-                         output_transpose=int(bool(output_transpose)))
+    common = dict(s_tok=_p(s_tok), out=_p(out), a_row_stride=a.stride(0), out_row_stride=out.stride(0), m=size_m, n=size_n,
+                  k=size_k, s_tok_per_row=int(s_tok.numel() != 1), out_int8=int(out_int8),
+                  output_transpose=int(bool(output_transpose)))
+    if (0 < size_m < 32 and prep.per_channel and size_k % 32 == 0 and a.stride(0) % 16 == 0 and a.data_ptr() % 16 == 0):
+        # decode-sized call on per-channel weights: stream the nibble copy (half the bytes, identical results)
+        w4 = prep.need_w4()
+        args = _lib.make("qb_w4a8_gemv_s4_args", a=_p(a), w4=_p(w4), s_channel_nat=_p(prep.sc), **common)
         _run("qb_w4a8_gemv_s4", args, a)
         return out
-    args = _lib.make("qb_w4a8_gemm_args", a=_p(a), w8=_p(w8), s_channel_nat=_p(sc), s_tok=_p(s_tok), out=_p(out),
-                     a_row_stride=a.stride(0), out_row_stride=out.stride(0), m=size_m, n=size_n, k=size_k,
-                     s_tok_per_row=int(s_tok.numel() != 1), out_int8=int(out_int8),
-                     output_transpose=int(bool(output_transpose)))
+    w8 = prep.need_w8()
+    args = _lib.make("qb_w4a8_gemm_args", a=_p(a), w8=_p(w8), s_channel_nat=_p(prep.sc), **common)
     _run("qb_w4a8_gemm", args, a)
     return out
+
+
+def w4a8_linear(a, prep, s_tok, output_transpose=False, out_int8=False):
+    """The W4A8 product on a weight prepared once with :func:`prepare_w4a8_weight` (what the linear modules call)."""
+    return _w4a8(a, prep, s_tok, a.shape[0], prep.size_n, prep.size_k, output_transpose, out_int8)
 
 
 _OUT_DTYPE = {torch.int8: 0, torch.float16: 1, torch.bfloat16: 2}
@@ -544,11 +590,13 @@ _OUT_DTYPE = {torch.int8: 0, torch.float16: 1, torch.bfloat16: 2}
 class quant_linear_cuda:
     @staticmethod
     def w4a8o16_gemm(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k, output_transpose=False):
-        return _w4a8(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k, output_transpose, False)
+        prep = _prepared_for(b_q_weight, s_ch, s_group, size_n, size_k)
+        return _w4a8(a, prep, s_tok, size_m, size_n, size_k, output_transpose, False)
 
     @staticmethod
     def w4a8o8_gemm(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k, output_transpose=False):
-        return _w4a8(a, b_q_weight, s_tok, s_ch, s_group, workspace, size_m, size_n, size_k, output_transpose, True)
+        prep = _prepared_for(b_q_weight, s_ch, s_group, size_n, size_k)
+        return _w4a8(a, prep, s_tok, size_m, size_n, size_k, output_transpose, True)
 
     @staticmethod
     def cutlass_scaled_mm_dq(c, a, b, a_scales, b_scales):
@@ -602,3 +650,122 @@ class quant_linear_cuda:
                          round_half_away=1, alpha=0.0)
         _run("qb_w8a8_gemm", args, a)
         return c
+
+
+# ------------------------------------------------------------------------------------------------
+def _norm_call(fn, x, weight, bias, eps, residual, residual_out, q_z, z_scale, out, dyn, group_size, ngroups, out_kind,
+               out_scale, norm_before_gate, is_rms_norm):
+    args = _lib.make(
+        "qb_rmsnorm_args", x=_p(x), residual=_p(residual), residual_out=_p(residual_out), z=_p(q_z), weight=_p(weight),
+        bias=_p(bias), out=_p(out), dyn_scale=_p(dyn), x_row_stride=x.stride(0),
+        residual_row_stride=residual.stride(0) if residual is not None else 0,
+        residual_out_row_stride=residual_out.stride(0) if residual_out is not None else 0,
+        z_row_stride=q_z.stride(0) if q_z is not None else 0, out_row_stride=out.stride(0), rows=x.shape[0],
+        group_size=group_size, ngroups=ngroups,
+        residual_is_f32=int(residual is not None and residual.dtype == torch.float32),
+        residual_out_is_f32=int(residual_out is not None and residual_out.dtype == torch.float32), out_kind=out_kind,
+        norm_before_gate=int(bool(norm_before_gate)), is_rms_norm=int(bool(is_rms_norm)), eps=float(eps),
+        out_scale=float(out_scale), z_scale=float(z_scale))
+    _run(fn, args, x)
+
+
+def _qlayer_norm_fwd(x, weight, bias, eps, residual=None, static_out_scale=None, residual_dtype=None, is_rms_norm=False):
+    """quamba/triton/quant_norm.py:134-206: returns (y int8, residual_out, per_token_scale or None)."""
+    _req(x.is_cuda and x.dtype == torch.float16 and x.dim() == 2, "x must be a 2-D float16 CUDA tensor")
+    _req(x.stride(-1) == 1, "x must be contiguous in its last dim")
+    M, N = x.shape
+    _req(tuple(weight.shape) == (N,) and weight.stride(-1) == 1 and weight.dtype == torch.float16, "weight must be fp16 (N,)")
+    if bias is not None:
+        _req(tuple(bias.shape) == (N,) and bias.stride(-1) == 1 and bias.dtype == torch.float16, "bias must be fp16 (N,)")
+    if residual is not None:
+        _req(residual.shape == x.shape and residual.stride(-1) == 1, "residual must have the shape of x")
+        _req(residual.dtype in (torch.float16, torch.float32), "residual must be float16 or float32")
+        residual_dtype = residual.dtype
+    _req(N * x.element_size() < 65536, "This layer norm doesn't support feature dim >= 64KB.")
+    y = torch.empty((M, N), dtype=torch.int8, device=x.device)
+    residual_out = None
+    if residual is not None or (residual_dtype is not None and residual_dtype != x.dtype):
+        _req(residual_dtype in (torch.float16, torch.float32), "residual_dtype must be float16 or float32")
+        residual_out = torch.empty((M, N), dtype=residual_dtype, device=x.device)
+    static = bool(static_out_scale)       # the reference tests truthiness: None and 0.0 both mean per-token scales
+    dyn = None if static else torch.empty((M,), dtype=torch.float32, device=x.device)
+    if M > 0:
+        _norm_call("qb_rmsnorm_quant", x, weight, bias, eps, residual, residual_out, None, 0.0, y, dyn, N, 1,
+                   0 if static else 1, static_out_scale if static else 0.0, True, is_rms_norm)
+    return y, (residual_out if residual_out is not None else x), dyn
+
+
+def _qlayer_normgated_fwd(x, weight, bias, eps, q_z=None, z_scale=None, static_out_scale=None, use_float16_output=False,
+                          group_size=None, norm_before_gate=True, is_rms_norm=False):
+    """quamba/triton/quant_normgated.py:85-132: returns (out fp16 or int8, per_token_scale (ngroups * M))."""
+    _req(x.is_cuda and x.dtype == torch.float16 and x.dim() == 2, "x must be a 2-D float16 CUDA tensor")
+    _req(x.stride(-1) == 1, "x must be contiguous in its last dim")
+    M, N = x.shape
+    group_size = N if group_size is None else group_size
+    _req(N % group_size == 0, "the feature dim must be divisible by group_size")
+    ngroups = N // group_size
+    if q_z is not None:
+        _cuda_i8(q_z, "q_z")
+        _req(q_z.shape == x.shape and q_z.stride(-1) == 1, "q_z must have the shape of x")
+        _req(z_scale is not None, "q_z needs z_scale")
+    _req(tuple(weight.shape) == (N,) and weight.stride(-1) == 1 and weight.dtype == torch.float16, "weight must be fp16 (N,)")
+    if bias is not None:
+        _req(tuple(bias.shape) == (N,) and bias.stride(-1) == 1 and bias.dtype == torch.float16, "bias must be fp16 (N,)")
+    _req(group_size * x.element_size() < 65536, "This layer norm doesn't support feature dim >= 64KB.")
+    out = torch.empty((M, N), dtype=torch.float16 if use_float16_output else torch.int8, device=x.device)
+    per_token = torch.empty((ngroups * M,), dtype=torch.float32, device=x.device)
+    kind = 2 if use_float16_output else (0 if static_out_scale is not None else 1)
+    if M > 0:
+        _norm_call("qb_rmsnorm_gated", x, weight, bias, eps, None, None, q_z, z_scale or 0.0, out, per_token, group_size,
+                   ngroups, kind, static_out_scale if kind == 0 else 0.0, norm_before_gate, is_rms_norm)
+    return out, per_token
+
+
+class quant_embedding_cuda:
+    """csrc/embedding/quant_embedding.cpp: w4a16_embedding_lookup / w8a16_embedding_lookup (+ the fp16 table)."""
+
+    @staticmethod
+    def _lookup(input, weight, scale, kind, dim):
+        _req(weight.dim() == 2 and weight.is_cuda, "weight must be a 2-D CUDA tensor")
+        _req(input.dim() in (1, 2), "input must be a 1D or 2D tensor")
+        _req(input.is_cuda and input.dtype == torch.int64, "input must be an int64 CUDA tensor")
+        vocab = weight.shape[0]
+        if kind:
+            _req(scale.dim() == 1 and scale.is_cuda and scale.dtype == torch.float16 and scale.numel() == vocab,
+                 "scale must be a float16 CUDA tensor with one entry per row")
+        tokens = input.contiguous()
+        out = torch.empty((*tokens.shape, dim), dtype=torch.float16, device=input.device)
+        args = _lib.make("qb_embedding_args", table=_p(weight.contiguous()), scales=_p(scale) if kind else None,
+                         tokens=_p(tokens), out=_p(out), n_tokens=tokens.numel(), dim=dim, vocab=vocab, kind=kind)
+        _run("qb_embedding_lookup", args, input)
+        return out
+
+    @staticmethod
+    def w4a16_embedding_lookup(input, weight, scale):
+        _req(weight.dtype == torch.int32, "weight's dtype must be int32")
+        return quant_embedding_cuda._lookup(input, weight, scale, 2, weight.shape[1] * 8)
+
+    @staticmethod
+    def w8a16_embedding_lookup(input, weight, scale):
+        _req(weight.dtype == torch.int8, "weight's dtype must be int8")
+        return quant_embedding_cuda._lookup(input, weight, scale, 1, weight.shape[1])
+
+    @staticmethod
+    def f16_embedding_lookup(input, weight):
+        _req(weight.dtype == torch.float16, "weight's dtype must be float16")
+        return quant_embedding_cuda._lookup(input, weight, None, 0, weight.shape[1])
+
+
+def greedy_next_token(logits, out=None):
+    """Row-wise argmax of fp16 logits (rows, vocab) -> int64 (rows); ``out`` lets a captured step write in place."""
+    _req(logits.is_cuda and logits.dtype == torch.float16 and logits.dim() == 2 and logits.stride(1) == 1,
+         "logits must be a 2-D float16 CUDA tensor, contiguous in its last dim")
+    rows, n = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int64, device=logits.device)
+    _req(out.dtype == torch.int64 and out.numel() == rows and out.is_contiguous(), "out must be int64 (rows,)")
+    f = _lib.lib().qb_argmax_rows
+    f.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    with torch.cuda.device(logits.device):
+        _lib.check(f(logits.data_ptr(), logits.stride(0), rows, n, out.data_ptr(), ctypes.c_void_p(_stream(logits))))
+    return out

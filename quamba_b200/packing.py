@@ -40,17 +40,17 @@ def pack_int4(q: torch.Tensor, per_channel: bool) -> torch.Tensor:
     K, N = q.shape
     assert K % TILE == 0 and N % 64 == 0, "K must be a multiple of 16 and N of 64"
     t = q.reshape(K // TILE, TILE, N // TILE, TILE).permute(0, 2, 1, 3).reshape(K // TILE, N * TILE)
-    perm = _weight_perm(per_channel)
+    perm = _weight_perm(per_channel).to(q.device)
     t = t.reshape(-1, perm.numel())[:, perm].reshape(K // TILE, N * TILE).to(torch.int64) & 0xF
     t = t.reshape(K // TILE, N * TILE // 8, 8)
-    shifts = (4 * torch.arange(8, dtype=torch.int64))
+    shifts = 4 * torch.arange(8, dtype=torch.int64, device=q.device)
     word = (t << shifts).sum(-1)
     word = torch.where(word >= 2 ** 31, word - 2 ** 32, word)
     return word.to(torch.int32).contiguous()
 
 
 def permute_scales(s_group: torch.Tensor, s_channel: torch.Tensor, N: int, per_channel: bool):
-    gp, sp = _scale_perms()
+    gp, sp = (t.to(s_channel.device) for t in _scale_perms())
     s_channel = s_channel.reshape(-1, sp.numel())[:, sp].reshape(-1, N).contiguous()
     if not per_channel:
         s_group = s_group.reshape(-1, gp.numel())[:, gp].reshape(-1, N).contiguous()
@@ -83,7 +83,7 @@ def quantize_w4(w: torch.Tensor, group_size: int = -1):
         s_channel = w.abs().amax(dim=0, keepdim=True) / 7.0
         q = torch.clamp(torch.round(w / s_channel).int(), -7, 7)
         w_ref = q.to(torch.float16) * s_channel
-        s_group = torch.tensor([], dtype=torch.float16)
+        s_group = torch.tensor([], dtype=torch.float16, device=w.device)
         s_channel = (s_channel / 16.0).reshape(-1, N).float()
     return w_ref, q, s_group, s_channel
 
@@ -116,6 +116,6 @@ def w4a8_quantize(w: torch.Tensor, num_bits: int = 4, group_size: int = -1, s_gr
             s_group = F.pad(s_group, (0, pad_out))
         s_channel = F.pad(s_channel, (0, pad_out), value=1e-6)
         N += pad_out
-    packed = pack_int4(q.cpu(), per_channel)
+    packed = pack_int4(q, per_channel)       # on the weight's device: the index arithmetic is the same on CPU and GPU
     s_group, s_channel = permute_scales(s_group, s_channel, N, per_channel)
     return [t.to(w.device) for t in (w_ref, packed, s_group, s_channel)]
