@@ -186,7 +186,7 @@ def _w4a8(dev, gen, ops, M, K, N, out_int8, tag, group=128):
     # int8 expansion the kernel streams is 2 bytes per packed byte), so that they come from HBM as they do in a model
     # whose layers each have their own weights, not from L2.
     n = _sets_for(by if M >= 32 else M * K + (K * N if group > 0 else K * N // 2) + M * N)
-    packs = [packed] if M >= 32 else [packed.clone() for _ in range(n)]
+    packs = [packed] if M >= 4096 else [packed.clone() for _ in range(n)]
     xs = [_i8((M, K), dev, gen) for _ in range(n)]
     st = torch.tensor(0.03, device=dev)
     ws = torch.zeros(N // 64 * 16, dtype=torch.int32, device=dev)
@@ -195,7 +195,9 @@ def _w4a8(dev, gen, ops, M, K, N, out_int8, tag, group=128):
     def mk(i):
         return lambda: fn(xs[i], packs[i % len(packs)], st, sc, sg, ws, M, N, K, False)
     return dict(workload=f"W4A8 GEMM {tag}: M{M} K{K} N{N}, int4 {'group-128' if group > 0 else 'per-channel'} weights, {'int8' if out_int8 else 'fp16'} out",
-                bytes=by, flops=2 * M * N * K, nsets=n, make=mk, kernel="gemm_s8_tcgen05_kernel", launches=1,
+                bytes=by, flops=2 * M * N * K, nsets=n, make=mk, launches=1,
+                kernel=("gemm_s8_tcgen05_persistent_kernel" if M >= 128 else "gemm_s8_tcgen05_kernel<64>" if M >= 32 else
+                        "gemv_s4_kernel" if group < 0 else "gemv_s8_kernel"),
                 note="weights unpacked to int8 once at first use (cached); the timed GEMM streams int8 weights")
 
 
@@ -205,6 +207,43 @@ def op_w4a8_in(dev, gen, ops):
 
 def op_w4a8_out(dev, gen, ops):
     return _w4a8(dev, gen, ops, 8192, 5120, 2560, False, "Mamba2-2.7B out_proj, 4 x 2048 tokens")
+
+
+def op_w4a8_in_b1(dev, gen, ops):
+    return _w4a8(dev, gen, ops, 2048, 2560, 10624, True, "Mamba2-2.7B in_proj, 1 x 2048 tokens", group=-1)
+
+
+def op_w4a8_out_b1(dev, gen, ops):
+    return _w4a8(dev, gen, ops, 2048, 5120, 2560, False, "Mamba2-2.7B out_proj, 1 x 2048 tokens", group=-1)
+
+
+def op_rmsnorm(dev, gen, ops):
+    M, N = 2048, 2560
+    by = M * N * (2 + 4 + 4 + 1)
+    n = _sets_for(by)
+    w = torch.ones(N, dtype=torch.float16, device=dev)
+    xs = [torch.randn((M, N), device=dev, generator=gen).half() for _ in range(n)]
+    rs = [torch.randn((M, N), device=dev, generator=gen) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops._qlayer_norm_fwd(xs[i], w, None, 1e-5, rs[i], static_out_scale=0.03, is_rms_norm=True)
+    return dict(workload=f"QRMSNorm + residual add, Mamba2-2.7B block norm at 1 x 2048 tokens: M{M} N{N}, fp16 x, fp32 residual in and out, int8 out",
+                bytes=by, flops=0, nsets=n, make=mk, kernel="norm_quant_kernel<2, 0, 5>", launches=1)
+
+
+def op_rmsnorm_gated(dev, gen, ops):
+    M, N = 2048, 5120
+    by = M * N * (2 + 1 + 2)
+    n = _sets_for(by)
+    w = torch.ones(N, dtype=torch.float16, device=dev)
+    xs = [torch.randn((M, N), device=dev, generator=gen).half() for _ in range(n)]
+    zs = [_i8((M, N), dev, gen) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops._qlayer_normgated_fwd(xs[i], w, None, 1e-5, q_z=zs[i], z_scale=0.02, use_float16_output=True,
+                                                 group_size=N, norm_before_gate=False, is_rms_norm=True)
+    return dict(workload=f"gated RMSNorm, Mamba2-2.7B at 1 x 2048 tokens: M{M} N{N}, fp16 x, int8 gate, fp16 out",
+                bytes=by, flops=0, nsets=n, make=mk, kernel="norm_quant_kernel<4, 1, 5>", launches=1)
 
 
 def op_w4a8_decode(dev, gen, ops):
@@ -235,7 +274,8 @@ def op_w8a8(dev, gen, ops):
 
 
 OPS = {"conv": op_conv, "conv_update": op_conv_update, "hadamard": op_hadamard, "sscan": op_sscan, "ssd": op_ssd,
-       "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out, "w4a8_decode": op_w4a8_decode, "w4a8_decode_pc": op_w4a8_decode_pc, "w4a8_decode_b64": op_w4a8_decode_b64,
+       "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out,
+       "w4a8_in_proj_b1": op_w4a8_in_b1, "w4a8_out_proj_b1": op_w4a8_out_b1, "rmsnorm": op_rmsnorm, "rmsnorm_gated": op_rmsnorm_gated, "w4a8_decode": op_w4a8_decode, "w4a8_decode_pc": op_w4a8_decode_pc, "w4a8_decode_b64": op_w4a8_decode_b64,
        "w8a8": op_w8a8}
 
 

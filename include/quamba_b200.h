@@ -586,6 +586,92 @@ int qb_embedding_lookup(const qb_embedding_args* a, void* stream);
  * captured decode step can feed its own next input.  row_stride in elements. */
 int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t n, int64_t* out, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Fused decode-step kernels for 1 to 4 rows (one token per sequence).  The reference launches these ops one by one
+ * (block QRMSNorm, quamba/qNorm.py:52-87, then W4A8QMamba2.step, quamba/qMamba2.py:997-1020); here three launches cover
+ * a layer, each bit-compatible with the separate entry points above up to their stated tolerances.
+ *
+ * qb_decode_norm_linear: h = x (+ residual); residual_out = h; a = int8(rmsnorm(h) * norm_weight / norm_out_scale);
+ *   out (rows, n) = a @ W^T scaled by s_channel_nat[n] * s_tok, int8 (rint, saturating) or fp16.  W is the int8 copy
+ *   qb_w4a8_unpack makes (n, k), or with w_is_s4 != 0 the nibble copy qb_w4a8_pack_nibbles makes (per-channel weights).
+ *   With conv_state != null the columns [conv_col0, conv_col0 + conv_dim) are not stored: each is fed to that channel's
+ *   quamba2_conv1d update (width 4, per-tensor output scales; state element (b, c, w) at b*sb + c*sd + w*sw shifted in
+ *   place) and the conv results go to conv_x (rows, conv_x_dim), conv_B / conv_C (rows, conv_gn).
+ *   conv_scale_in_* = weight scale * input scale of the segment; conv_scale_bias_* = bias scale.
+ * qb_decode_gate_had_linear: g = y * silu(z_scale * z); grouped rmsnorm(g) * norm_weight rounded to fp16; Hadamard
+ *   rotation of length d = k (d / 128 in {12, 20, 28, 40} or a power of two <= 64); a = sat_int8(roundf(. * had_scale));
+ *   out (rows, n) fp16 = a @ W^T scaled by s_channel_nat[n] * s_tok.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const void* x;
+  const void* residual;
+  void* residual_out;
+  const void* norm_weight;
+  const void* w;
+  const float* s_channel_nat;
+  const float* s_tok;
+  void* out;
+  int8_t* conv_state;
+  const int8_t* conv_weight;
+  const int8_t* conv_bias;
+  int8_t* conv_x;
+  int8_t* conv_B;
+  int8_t* conv_C;
+  const float* x_out_scale;
+  const float* B_out_scale;
+  const float* C_out_scale;
+  int64_t x_row_stride;
+  int64_t residual_row_stride;
+  int64_t residual_out_row_stride;
+  int64_t out_row_stride;
+  int64_t conv_state_sb;
+  int64_t conv_state_sd;
+  int64_t conv_state_sw;
+  int32_t rows;
+  int32_t n;
+  int32_t k;
+  int32_t w_is_s4;
+  int32_t out_int8;
+  int32_t residual_is_f32;
+  int32_t residual_out_is_f32;
+  int32_t conv_col0;
+  int32_t conv_dim;
+  int32_t conv_x_dim;
+  int32_t conv_gn;
+  float eps;
+  float norm_out_scale;
+  float conv_scale_in_x;
+  float conv_scale_in_B;
+  float conv_scale_in_C;
+  float conv_scale_bias_x;
+  float conv_scale_bias_B;
+  float conv_scale_bias_C;
+} qb_decode_norm_linear_args;
+int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* stream);
+
+typedef struct {
+  const void* y;
+  const int8_t* z;
+  const void* norm_weight;
+  const void* w;
+  const float* s_channel_nat;
+  const float* s_tok;
+  void* out;
+  int64_t y_row_stride;
+  int64_t z_row_stride;
+  int64_t out_row_stride;
+  int32_t rows;
+  int32_t d;
+  int32_t group_size;
+  int32_t n;
+  int32_t k;
+  int32_t w_is_s4;
+  float z_scale;
+  float eps;
+  float had_scale;
+} qb_decode_gate_had_linear_args;
+int qb_decode_gate_had_linear(const qb_decode_gate_had_linear_args* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,11 +63,11 @@ def mixer_step(m, u_int8, conv_state, ssm_state):
     D2 = s.D[:, None].expand(-1, p)
     bias = s.dt_bias[:, None].expand(-1, p)
     if s.x_head_group_range is None:
-        y, new_state = oupd.quant_sscan_update(ssm_state, *args, *common, D2, s.D_scale, None, None, bias.float(), None, True)
+        y, _ = oupd.quant_sscan_update(ssm_state, *args, *common, D2, s.D_scale, None, None, bias.float(), None, True)
     else:
-        y, new_state = oupd.quamba2_sscan_update(ssm_state, *args, s.x_head_group_range, s.x_dim_group_range, *common, D2,
-                                                 s.D_scale, None, None, bias.float(), True)
-    ssm_state.copy_(new_state)
+        y, _ = oupd.quamba2_sscan_update(ssm_state, *args, s.x_head_group_range, s.x_dim_group_range, *common, D2,
+                                         s.D_scale, None, None, bias.float(), True)
+    # (the int8 state was requantised in place; the second return value is the fp32 state the output was formed from)
     return _gate_rotate_project(m, y.reshape(b, -1), z.contiguous())
 
 

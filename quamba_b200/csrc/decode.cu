@@ -1,0 +1,542 @@
+// Fused kernels of the Mamba2 decode step for small batches (sm_100a).
+//
+// A decode step of one layer is seven tiny ops in the reference (block norm, in_proj, conv update, state update, gated
+// norm, Hadamard + quantise, out_proj), each far below the launch-to-launch gap of a captured graph.  Three launches do
+// the same work here:
+//   1. qb_decode_norm_linear: residual add + RMSNorm + int8 quantise (re-done by every CTA in shared memory, it is 5 KB of
+//      input) -> weight-streaming W4A8 product -> optional conv1d update of the xBC columns in the product's epilogue
+//      (the warp that owns an output column also owns that channel's conv window).
+//   2. the state update (qb_sscan_update, unchanged).
+//   3. qb_decode_gate_had_linear: y * silu(z) -> grouped RMSNorm -> Hadamard rotation -> int8 quantise (again per CTA in
+//      shared memory) -> weight-streaming W4A8 product with fp16 output.
+// Arithmetic, rounding and operation order are those of the separate kernels (norm.cu, hadamard.cu, conv1d.cu,
+// linear.cu), so results agree with the unfused path to the same tolerances.
+#include <algorithm>
+#include "common.cuh"
+#include "hadamard_tables.inc"
+
+namespace qb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kNW = 2;              // output columns per warp and pass
+constexpr int kMaxRows = 4;         // batch rows a launch takes
+
+__constant__ float c_dec_had[4][40 * 40];      // the order-12 / 20 / 28 / 40 matrices as +-1.0f, row-major
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum_f(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int i = 0; i < kWarps; ++i) r += red[i];
+  return r;
+}
+__device__ __forceinline__ float s8f(uint32_t w_biased, int k) {      // byte k of (w ^ 0x80808080) as a float
+  return __uint_as_float(__byte_perm(w_biased, 0x4B000000u, 0x7650 + k)) - 8388736.0f;
+}
+
+struct Linear {
+  const uint8_t* w;        // int8 (n, k) rows, or the nibble copy (n, k / 2) when s4
+  const float* s_ch;       // channel scales in natural order
+  const float* s_tok;      // input scale, one element
+  void* out;
+  int64_t out_stride;
+  int n, k, out_int8;
+};
+
+// The conv1d update done in the product's epilogue for columns [c0, c0 + dim) of the output.
+struct ConvEpi {
+  int8_t* state;           // element (b, c, w) at b * sb + c * sd + w * sw
+  int64_t sb, sd, sw;
+  const int8_t* weight;    // (dim, 4)
+  const int8_t* bias;      // (dim) or null
+  int8_t* dst[3];          // x (B, x_dim), Bm, Cm (B, gn)
+  const float* out_scale[3];
+  float scale_in[3], scale_bias[3];
+  int c0, dim, end0, end1;  // column of channel 0; segment ends in channels
+  int enabled;
+};
+
+// dot products of the int8 rows in shared memory (MB rows of k bytes) with weight columns n0 .. n0 + kNW - 1
+template <int MB, bool S4>
+__device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][kNW]) {
+  int sa[MB];
+#pragma unroll
+  for (int i = 0; i < MB; ++i) {
+    sa[i] = 0;
+#pragma unroll
+    for (int j = 0; j < kNW; ++j) acc[i][j] = 0;
+  }
+  if (!S4) {
+    const int chunks = L.k / 16;
+#pragma unroll 4
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 w[kNW];
+#pragma unroll
+      for (int j = 0; j < kNW; ++j)
+        w[j] = __ldg(reinterpret_cast<const uint4*>(L.w + (int64_t)min(n0 + j, L.n - 1) * L.k) + c);
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const uint4 a = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + c);
+#pragma unroll
+        for (int j = 0; j < kNW; ++j) {
+          int t = acc[i][j];
+          t = __dp4a((int)a.x, (int)w[j].x, t); t = __dp4a((int)a.y, (int)w[j].y, t);
+          t = __dp4a((int)a.z, (int)w[j].z, t); t = __dp4a((int)a.w, (int)w[j].w, t);
+          acc[i][j] = t;
+        }
+      }
+    }
+  } else {
+    const int chunks = L.k / 32;            // 16 bytes of nibbles = 32 values
+    const int64_t ldw = L.k / 2;
+#pragma unroll 4
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 w[kNW];
+#pragma unroll
+      for (int j = 0; j < kNW; ++j) w[j] = __ldg(reinterpret_cast<const uint4*>(L.w + (int64_t)min(n0 + j, L.n - 1) * ldw) + c);
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const uint4 a0 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c);
+        const uint4 a1 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c + 1);
+        const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+        int s = sa[i];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) s = __dp4a(av[t], 0x01010101, s);
+        sa[i] = s;
+#pragma unroll
+        for (int j = 0; j < kNW; ++j) {
+          const uint32_t ww[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+          int t = acc[i][j];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            t = __dp4a(av[2 * q], (int)(ww[q] & 0x0f0f0f0fu), t);
+            t = __dp4a(av[2 * q + 1], (int)((ww[q] >> 4) & 0x0f0f0f0fu), t);
+          }
+          acc[i][j] = t;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MB; ++i) {
+    const int s = S4 ? warp_sum_i(sa[i]) : 0;
+#pragma unroll
+    for (int j = 0; j < kNW; ++j) {
+      const int t = warp_sum_i(acc[i][j]);
+      acc[i][j] = S4 ? 16 * (t - 8 * s) : t;      // nibbles hold value + 8; the int8 weight is 16 x the value
+    }
+  }
+}
+
+// scale, convert and store one output element; when the column is a conv channel, run that channel's decode step
+__device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, int acc, int m, int n) {
+  const float r = ((float)acc * L.s_ch[n]) * L.s_tok[0];
+  if (!L.out_int8) {
+    static_cast<__half*>(L.out)[(int64_t)m * L.out_stride + n] = __float2half_rn(r);
+    return;
+  }
+  const int q = rint_s8(r);
+  const int c = n - cv.c0;
+  if (!cv.enabled || c < 0 || c >= cv.dim) {
+    static_cast<int8_t*>(L.out)[(int64_t)m * L.out_stride + n] = (int8_t)q;
+    return;
+  }
+  int8_t* st = cv.state + (int64_t)m * cv.sb + (int64_t)c * cv.sd;
+  const int w0 = st[cv.sw], w1 = st[2 * cv.sw], w2 = st[3 * cv.sw];
+  st[0] = (int8_t)w0; st[cv.sw] = (int8_t)w1; st[2 * cv.sw] = (int8_t)w2; st[3 * cv.sw] = (int8_t)q;
+  const int8_t* wt = cv.weight + (int64_t)c * 4;
+  const float dot = (float)((int)wt[0] * w0 + (int)wt[1] * w1 + (int)wt[2] * w2 + (int)wt[3] * q);
+  const int s = c < cv.end0 ? 0 : (c < cv.end1 ? 1 : 2);
+  const int cbase = s == 0 ? 0 : (s == 1 ? cv.end0 : cv.end1);
+  const int width = s == 0 ? cv.end0 : cv.end1 - cv.end0;
+  float v = cv.scale_in[s] * dot + (cv.bias != nullptr ? cv.scale_bias[s] * (float)cv.bias[c] : 0.0f);
+  v = silu_fast(v);
+  cv.dst[s][(int64_t)m * width + (c - cbase)] = (int8_t)round_away_s8(v / cv.out_scale[s][0]);
+}
+
+// Ask L2 for the weight rows of this warp's first pass.  Weights do not depend on the kernel before this one, so the call
+// sits ahead of the dependency wait and of the shared-memory prologue: HBM delivers while the prologue computes.
+template <bool S4>
+__device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * kWarps + warp) * kNW;
+  const int64_t row_bytes = S4 ? L.k / 2 : L.k;
+  for (int j = 0; j < kNW; ++j) {
+    if (n0 + j >= L.n) break;
+    const uint8_t* rowp = L.w + (int64_t)(n0 + j) * row_bytes;
+    for (int64_t off = (int64_t)lane * 128; off < row_bytes; off += 32 * 128)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + off));
+  }
+}
+
+template <int MB, bool S4>
+__device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int n0 = (blockIdx.x * kWarps + warp) * kNW; n0 < L.n; n0 += (int)gridDim.x * kWarps * kNW) {
+    int acc[MB][kNW];
+    dot_columns<MB, S4>(L, sA, n0, lane, acc);
+    // lanes 0 .. MB * kNW - 1 finish one (row, column) each, so that the conv windows of a warp's columns move in parallel
+    if (lane < MB * kNW) {
+      const int i = lane / kNW, j = lane % kNW;
+      int v = 0;
+#pragma unroll
+      for (int ii = 0; ii < MB; ++ii)
+#pragma unroll
+        for (int jj = 0; jj < kNW; ++jj)
+          if (ii == i && jj == j) v = acc[ii][jj];
+      if (i < rows && n0 + j < L.n) finish(L, cv, v, i, n0 + j);
+    }
+  }
+}
+
+// ---- launch 1: residual add + RMSNorm + quantise -> product (+ conv update) -------------------------------------------
+struct NormIn {
+  const __half* x;          // (rows, k)
+  const void* residual;     // fp32 or fp16 (rows, k), nullable
+  void* residual_out;       // nullable
+  const __half* weight;     // (k)
+  int64_t x_stride, res_stride, res_out_stride;
+  int res_f32, res_out_f32;
+  float eps, out_scale;
+};
+
+template <int MB, bool S4>
+__global__ void __launch_bounds__(kThreads, 3)
+decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  __shared__ float red[kWarps];
+  int8_t* sA = reinterpret_cast<int8_t*>(dsm);                 // MB rows of k int8
+  const int K = L.k;
+  prefetch_first_columns<S4>(L);
+  grid_dependency_wait();
+  const int chunks = K / 8;
+  const float inv_scale = 1.0f / nin.out_scale;
+  for (int m = 0; m < MB; ++m) {
+    const int row = min(m, rows - 1);
+    // a thread keeps its (at most four) chunks of eight values in registers between the two passes
+    float v[4][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = threadIdx.x + i * kThreads;
+      if (c < chunks) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(nin.x + (int64_t)row * nin.x_stride) + c);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y; }
+        if (nin.residual != nullptr) {
+          if (nin.res_f32) {
+            const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(nin.residual) + (int64_t)row * nin.res_stride) + 2 * c;
+            const float4 a = __ldg(r), b = __ldg(r + 1);
+            v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
+            v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
+          } else {
+            const uint4 rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(nin.residual) + (int64_t)row * nin.res_stride) + c);
+            const __half2* rh = reinterpret_cast<const __half2*>(&rr);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); v[i][2 * e] += f.x; v[i][2 * e + 1] += f.y; }
+          }
+        }
+        if (nin.residual_out != nullptr && blockIdx.x == 0 && m < rows) {
+          if (nin.res_out_f32) {
+            float4* o = reinterpret_cast<float4*>(static_cast<float*>(nin.residual_out) + (int64_t)row * nin.res_out_stride) + 2 * c;
+            o[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+            o[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+          } else {
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(v[i][2 * e], v[i][2 * e + 1]);
+            *(reinterpret_cast<uint4*>(static_cast<__half*>(nin.residual_out) + (int64_t)row * nin.res_out_stride) + c) = o;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v[i][e] * v[i][e];
+      }
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(sum, red) / (float)K + nin.eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = threadIdx.x + i * kThreads;
+      if (c < chunks) {
+        const uint4 wr = __ldg(reinterpret_cast<const uint4*>(nin.weight) + c);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+        int q[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 w2 = __half22float2(wh[e]);
+          q[2 * e] = __float2int_rn(v[i][2 * e] * rstd * w2.x * inv_scale);
+          q[2 * e + 1] = __float2int_rn(v[i][2 * e + 1] * rstd * w2.y * inv_scale);
+        }
+        uint2 o;
+        o.x = pack4_sat_s8(q[0], q[1], q[2], q[3]);
+        o.y = pack4_sat_s8(q[4], q[5], q[6], q[7]);
+        *(reinterpret_cast<uint2*>(sA + (int64_t)m * K) + c) = o;
+      }
+    }
+  }
+  __syncthreads();
+  stream_columns<MB, S4>(L, cv, sA, rows);
+}
+
+// ---- launch 3: gate, grouped RMSNorm, Hadamard rotation, quantise -> product -------------------------------------------
+struct GateIn {
+  const __half* y;          // (rows, d)
+  const int8_t* z;          // (rows, d) with row stride z_stride
+  const __half* weight;     // (d)
+  int64_t y_stride, z_stride;
+  int d, group_size, special, table;    // d = special_rows * 128; table: index into c_dec_had, or -1 for Sylvester rows
+  float z_scale, eps, had_scale;        // had_scale: (1 / sqrt(d)) / x_H_scale
+};
+
+constexpr int kMaxRowsPerWarp = 8;      // d / 128 <= 64 rows of 128 over 8 warps
+
+template <int MB, bool S4>
+__global__ void __launch_bounds__(kThreads, 2)
+decode_gate_had_linear_kernel(GateIn gin, Linear L, ConvEpi cv, int rows) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  __shared__ float gsum[64];
+  const int D = gin.d, S = D / 128;
+  float* buf = reinterpret_cast<float*>(dsm);                         // d floats: the row after the 128-point stage
+  int8_t* sA = reinterpret_cast<int8_t*>(dsm + (size_t)D * 4);        // MB rows of d int8
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  prefetch_first_columns<S4>(L);
+  grid_dependency_wait();
+  for (int m = 0; m < MB; ++m) {
+    const int row = min(m, rows - 1);
+    if (threadIdx.x < 64) gsum[threadIdx.x] = 0.f;
+    __syncthreads();
+    // A warp owns rows r = warp, warp + 8, ... of the (S x 128) view; a lane holds four neighbours of each.
+    // gate: v = y * silu(z); sum of squares per norm group (a group is a whole number of 128-element rows)
+    float f[kMaxRowsPerWarp][4];
+    uint2 yr[kMaxRowsPerWarp];
+    uint32_t zr[kMaxRowsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+      const int r = min(warp + i * kWarps, S - 1);
+      yr[i] = __ldg(reinterpret_cast<const uint2*>(gin.y + (int64_t)row * gin.y_stride + r * 128) + lane);
+      zr[i] = __ldg(reinterpret_cast<const uint32_t*>(gin.z + (int64_t)row * gin.z_stride + r * 128) + lane);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+      const int r = warp + i * kWarps;
+      const __half2* h = reinterpret_cast<const __half2*>(&yr[i]);
+      const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+      f[i][0] = a.x; f[i][1] = a.y; f[i][2] = b.x; f[i][3] = b.y;
+      const uint32_t zw = zr[i] ^ 0x80808080u;
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float hz = s8f(zw, e) * (0.5f * gin.z_scale);
+        f[i][e] *= fmaf(hz, tanh_approx(hz), hz);
+        ss += f[i][e] * f[i][e];
+      }
+      ss = warp_sum_f(ss);
+      if (lane == 0 && r < S) atomicAdd(&gsum[(r * 128) / gin.group_size], ss);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+      const int r = warp + i * kWarps;
+      if (r < S) {          // warp-uniform
+        // normalise and round to fp16 as the separate norm kernel stores it
+        const float rstd = 1.0f / sqrtf(gsum[(r * 128) / gin.group_size] / (float)gin.group_size + gin.eps);
+        const uint2 wr = __ldg(reinterpret_cast<const uint2*>(gin.weight + r * 128) + lane);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+        const float2 w0 = __half22float2(wh[0]), w1 = __half22float2(wh[1]);
+        const float t0 = __half2float(__float2half_rn(f[i][0] * rstd * w0.x)), t1 = __half2float(__float2half_rn(f[i][1] * rstd * w0.y));
+        const float t2 = __half2float(__float2half_rn(f[i][2] * rstd * w1.x)), t3 = __half2float(__float2half_rn(f[i][3] * rstd * w1.y));
+        // H_128 along the row: strides 1 and 2 inside the lane, 4 .. 64 through shuffles
+        const float e0 = t0 + t1, e1 = t0 - t1, e2 = t2 + t3, e3 = t2 - t3;
+        float g[4] = {e0 + e2, e1 + e3, e0 - e2, e1 - e3};
+#pragma unroll
+        for (int mk = 1; mk < 32; mk <<= 1) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float o = __shfl_xor_sync(0xffffffffu, g[k], mk);
+            g[k] = (lane & mk) ? o - g[k] : g[k] + o;
+          }
+        }
+        *reinterpret_cast<float4*>(buf + r * 128 + 4 * lane) = make_float4(g[0], g[1], g[2], g[3]);
+      }
+    }
+    __syncthreads();
+    // H_S across the rows: thread (column, half of the output rows), four outputs at a time so that one shared-memory
+    // read feeds four independent accumulators; the sign is uniform over a warp (a constant-bank operand)
+    {
+      const int col = threadIdx.x & 127, ih = threadIdx.x >> 7;
+      const int per = (S + 1) / 2;
+      const int i0 = ih * per, i1 = min(S, i0 + per);
+      const float* tab = gin.table >= 0 ? c_dec_had[gin.table] : nullptr;
+      for (int i = i0; i < i1; i += 4) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        const int r1 = min(i + 1, S - 1), r2 = min(i + 2, S - 1), r3 = min(i + 3, S - 1);
+        if (tab != nullptr) {
+#pragma unroll 4
+          for (int j = 0; j < S; ++j) {
+            const float b = buf[j * 128 + col];
+            a0 = fmaf(tab[i * S + j], b, a0); a1 = fmaf(tab[r1 * S + j], b, a1);
+            a2 = fmaf(tab[r2 * S + j], b, a2); a3 = fmaf(tab[r3 * S + j], b, a3);
+          }
+        } else {
+#pragma unroll 4
+          for (int j = 0; j < S; ++j) {
+            const float b = buf[j * 128 + col];
+            a0 += (__popc(i & j) & 1) ? -b : b; a1 += (__popc(r1 & j) & 1) ? -b : b;
+            a2 += (__popc(r2 & j) & 1) ? -b : b; a3 += (__popc(r3 & j) & 1) ? -b : b;
+          }
+        }
+        int8_t* o = sA + (int64_t)m * D + col;
+        o[i * 128] = (int8_t)round_away_s8(a0 * gin.had_scale);
+        if (i + 1 < i1) o[(i + 1) * 128] = (int8_t)round_away_s8(a1 * gin.had_scale);
+        if (i + 2 < i1) o[(i + 2) * 128] = (int8_t)round_away_s8(a2 * gin.had_scale);
+        if (i + 3 < i1) o[(i + 3) * 128] = (int8_t)round_away_s8(a3 * gin.had_scale);
+      }
+    }
+    __syncthreads();
+  }
+  stream_columns<MB, S4>(L, cv, sA, rows);
+}
+
+int upload_tables() {
+  static bool done[64] = {};
+  int dev = 0;
+  QB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && done[dev]) return QB_OK;
+  static float host[4][40 * 40];
+  const unsigned long long* masks[4] = {kHadNeg12, kHadNeg20, kHadNeg28, kHadNeg40};
+  const int order[4] = {12, 20, 28, 40};
+  for (int t = 0; t < 4; ++t)
+    for (int i = 0; i < order[t]; ++i)
+      for (int j = 0; j < order[t]; ++j) host[t][i * order[t] + j] = ((masks[t][i] >> j) & 1ull) ? -1.0f : 1.0f;
+  QB_CUDA_OK(cudaMemcpyToSymbol(c_dec_had, host, sizeof(host)));
+  if (dev < 64) done[dev] = true;
+  return QB_OK;
+}
+
+int fill_linear(Linear& L, const void* w, const float* s_ch, const float* s_tok, void* out, int64_t out_stride, int n, int k,
+                int s4, int out_int8, const char* who) {
+  QB_REQUIRE(w && s_ch && s_tok && out, QB_ERR_INVALID_ARG, "%s: null pointer", who);
+  QB_REQUIRE(n > 0 && k > 0 && k % 32 == 0 && aligned(w, 16), QB_ERR_INVALID_ARG, "%s: k must be a multiple of 32 and the weights 16-byte aligned", who);
+  QB_REQUIRE(out_stride >= n, QB_ERR_INVALID_ARG, "%s: out_row_stride smaller than n", who);
+  L.w = static_cast<const uint8_t*>(w); L.s_ch = s_ch; L.s_tok = s_tok; L.out = out; L.out_stride = out_stride;
+  L.n = n; L.k = k; L.out_int8 = out_int8;
+  (void)s4;
+  return QB_OK;
+}
+
+unsigned grid_for(int n, int ctas_per_sm) {
+  return (unsigned)std::min<int64_t>(ceil_div(n, kWarps * kNW), (int64_t)sm_count() * ctas_per_sm);
+}
+
+template <typename K>
+int opt_in_smem(K kernel, size_t bytes) {
+  // per device and per kernel: the attribute is set on every launch that needs it (a cheap host-side call)
+  if (bytes > 48 * 1024) QB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return QB_OK;
+}
+
+}  // namespace
+}  // namespace qb
+
+using namespace qb;
+
+#define QB_DISPATCH_MB_S4(KERNEL, rows, s4, grid, smem, st, ...)                                                          \
+  do {                                                                                                                    \
+    int rc__ = QB_OK;                                                                                                     \
+    if (rows == 1 && s4) { rc__ = opt_in_smem(KERNEL<1, true>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<1, true>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }        \
+    else if (rows == 1) { rc__ = opt_in_smem(KERNEL<1, false>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<1, false>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }      \
+    else if (rows == 2 && s4) { rc__ = opt_in_smem(KERNEL<2, true>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<2, true>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }   \
+    else if (rows == 2) { rc__ = opt_in_smem(KERNEL<2, false>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<2, false>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }      \
+    else if (s4) { rc__ = opt_in_smem(KERNEL<4, true>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<4, true>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }               \
+    else { rc__ = opt_in_smem(KERNEL<4, false>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<4, false>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }                     \
+    if (rc__ != QB_OK) return rc__;                                                                                       \
+  } while (0)
+
+extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr && a->x && a->norm_weight, QB_ERR_INVALID_ARG, "decode_norm_linear: null pointer");
+  QB_REQUIRE(a->rows >= 1 && a->rows <= kMaxRows, QB_ERR_UNSUPPORTED, "decode_norm_linear: 1 to %d rows", kMaxRows);
+  QB_REQUIRE(a->k <= 8192 && a->k % 32 == 0, QB_ERR_UNSUPPORTED, "decode_norm_linear: k must be a multiple of 32, at most 8192");
+  QB_REQUIRE(a->norm_out_scale != 0.0f, QB_ERR_INVALID_ARG, "decode_norm_linear: the norm's output scale is zero");
+  QB_REQUIRE(aligned(a->x, 16) && a->x_row_stride % 8 == 0 && aligned(a->norm_weight, 16) &&
+             (a->residual == nullptr || (aligned(a->residual, 16) && a->residual_row_stride % 8 == 0)) &&
+             (a->residual_out == nullptr || (aligned(a->residual_out, 16) && a->residual_out_row_stride % 8 == 0)),
+             QB_ERR_INVALID_ARG, "decode_norm_linear: rows must be 16-byte aligned");
+  Linear L{};
+  int rc = fill_linear(L, a->w, a->s_channel_nat, a->s_tok, a->out, a->out_row_stride, a->n, a->k, a->w_is_s4, a->out_int8,
+                       "decode_norm_linear");
+  if (rc != QB_OK) return rc;
+  NormIn nin{};
+  nin.x = static_cast<const __half*>(a->x); nin.residual = a->residual; nin.residual_out = a->residual_out;
+  nin.weight = static_cast<const __half*>(a->norm_weight);
+  nin.x_stride = a->x_row_stride; nin.res_stride = a->residual_row_stride; nin.res_out_stride = a->residual_out_row_stride;
+  nin.res_f32 = a->residual_is_f32; nin.res_out_f32 = a->residual_out_is_f32; nin.eps = a->eps; nin.out_scale = a->norm_out_scale;
+  ConvEpi cv{};
+  if (a->conv_state != nullptr) {
+    QB_REQUIRE(a->out_int8 && a->conv_weight && a->conv_x && a->conv_B && a->conv_C && a->x_out_scale && a->B_out_scale && a->C_out_scale,
+               QB_ERR_INVALID_ARG, "decode_norm_linear: the conv epilogue needs an int8 product and all conv pointers");
+    QB_REQUIRE(a->conv_dim == a->conv_x_dim + 2 * a->conv_gn && a->conv_col0 >= 0 && a->conv_col0 + a->conv_dim <= a->n,
+               QB_ERR_INVALID_ARG, "decode_norm_linear: conv channels out of the product's columns");
+    cv.enabled = 1; cv.state = a->conv_state; cv.sb = a->conv_state_sb; cv.sd = a->conv_state_sd; cv.sw = a->conv_state_sw;
+    cv.weight = a->conv_weight; cv.bias = a->conv_bias; cv.dst[0] = a->conv_x; cv.dst[1] = a->conv_B; cv.dst[2] = a->conv_C;
+    cv.out_scale[0] = a->x_out_scale; cv.out_scale[1] = a->B_out_scale; cv.out_scale[2] = a->C_out_scale;
+    cv.scale_in[0] = a->conv_scale_in_x; cv.scale_in[1] = a->conv_scale_in_B; cv.scale_in[2] = a->conv_scale_in_C;
+    cv.scale_bias[0] = a->conv_scale_bias_x; cv.scale_bias[1] = a->conv_scale_bias_B; cv.scale_bias[2] = a->conv_scale_bias_C;
+    cv.c0 = a->conv_col0; cv.dim = a->conv_dim; cv.end0 = a->conv_x_dim; cv.end1 = a->conv_x_dim + a->conv_gn;
+  }
+  const int mb = a->rows <= 2 ? a->rows : 4;
+  const size_t smem = (size_t)mb * a->k;
+  const dim3 grid(grid_for(a->n, 3));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rows = a->rows;
+  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, a->w_is_s4 != 0, grid, smem, st, nin, L, cv, rows);
+  QB_LAUNCH_OK("decode_norm_linear_kernel");
+  return QB_OK;
+}
+
+extern "C" int qb_decode_gate_had_linear(const qb_decode_gate_had_linear_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr && a->y && a->z && a->norm_weight, QB_ERR_INVALID_ARG, "decode_gate_had_linear: null pointer");
+  QB_REQUIRE(a->rows >= 1 && a->rows <= kMaxRows, QB_ERR_UNSUPPORTED, "decode_gate_had_linear: 1 to %d rows", kMaxRows);
+  QB_REQUIRE(a->d > 0 && a->d % 128 == 0 && a->d == a->k, QB_ERR_UNSUPPORTED, "decode_gate_had_linear: d must be a multiple of 128 and equal k");
+  const int S = a->d / 128;
+  int table = -1;
+  if (S == 12 || S == 20 || S == 28 || S == 40) table = S == 12 ? 0 : (S == 20 ? 1 : (S == 28 ? 2 : 3));
+  else QB_REQUIRE(S >= 1 && S <= 64 && (S & (S - 1)) == 0, QB_ERR_UNSUPPORTED, "decode_gate_had_linear: d / 128 must be 12, 20, 28, 40 or a power of two <= 64");
+  QB_REQUIRE(a->group_size > 0 && a->d % a->group_size == 0 && a->group_size % 128 == 0 && a->d / a->group_size <= 64, QB_ERR_UNSUPPORTED,
+             "decode_gate_had_linear: the norm group size must be a multiple of 128 that divides d");
+  QB_REQUIRE(aligned(a->y, 16) && a->y_row_stride % 8 == 0 && aligned(a->z, 8) && a->z_row_stride % 8 == 0 && aligned(a->norm_weight, 16),
+             QB_ERR_INVALID_ARG, "decode_gate_had_linear: rows must be 16-byte aligned (z: 8)");
+  Linear L{};
+  int rc = fill_linear(L, a->w, a->s_channel_nat, a->s_tok, a->out, a->out_row_stride, a->n, a->k, a->w_is_s4, 0, "decode_gate_had_linear");
+  if (rc != QB_OK) return rc;
+  rc = upload_tables();
+  if (rc != QB_OK) return rc;
+  GateIn gin{};
+  gin.y = static_cast<const __half*>(a->y); gin.z = a->z; gin.weight = static_cast<const __half*>(a->norm_weight);
+  gin.y_stride = a->y_row_stride; gin.z_stride = a->z_row_stride; gin.d = a->d; gin.group_size = a->group_size; gin.special = S;
+  gin.table = table; gin.z_scale = a->z_scale; gin.eps = a->eps; gin.had_scale = a->had_scale;
+  ConvEpi cv{};
+  const int mb = a->rows <= 2 ? a->rows : 4;
+  const size_t smem = (size_t)a->d * 4 + (size_t)mb * a->d;
+  const dim3 grid(grid_for(a->n, 2));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rows = a->rows;
+  QB_DISPATCH_MB_S4(decode_gate_had_linear_kernel, mb, a->w_is_s4 != 0, grid, smem, st, gin, L, cv, rows);
+  QB_LAUNCH_OK("decode_gate_had_linear_kernel");
+  return QB_OK;
+}

@@ -184,9 +184,13 @@ constexpr int kPSmemBytes = kPStages * kPStageBytes + 1024 + 256;
 // tile took about as long as the main loop of a K = 2560 tile and the MMA issuer waited for its accumulator.
 constexpr int kPThreads = 64 + 256;
 
+// bn: tile width actually used (a multiple of 16, <= 256; the TMA box of W has bn rows).  The host picks the width whose
+// tile count fills whole rounds of the grid best: at 2048 rows the 2.7B out_proj (N = 2560) is 160 tiles of 256 columns on
+// 148 SMs, two rounds with the second almost empty, or 224 tiles of 192 columns, two rounds of cheaper tiles.  Shared-memory
+// slots and the TMEM accumulators keep their 256-column size.
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                                  int M, int N, int K, Epilogue ep, int* status) {
+                                  int M, int N, int K, int bn, Epilogue ep, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStages * kPStageBytes);
@@ -197,7 +201,7 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPStages + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + PBN - 1) / PBN;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   const int tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
   const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -223,14 +227,14 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
       int it = 0;  // k-iterations issued so far, over all tiles: the stage ring runs through tile boundaries
       for (int i = 0; i < my_tiles; ++i) {
         const int t = blockIdx.x + i * gridDim.x;
-        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * PBN;
+        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * bn;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kPStages;
           ok = mbar_wait(&empty_bar[s], (uint32_t)(((it / kPStages) & 1) ^ 1), status, QB_ERR_TIMEOUT);
           if (!ok) break;
           uint8_t* stage = smem + s * kPStageBytes;
-          mbar_arrive_expect_tx(&full_bar[s], kPStageBytes);
+          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)((BM + bn) * BK));
           tma_load_2d(stage, &tmap_a, &full_bar[s], kb * BK, m0);
           tma_load_2d(stage + BM * BK, &tmap_w, &full_bar[s], kb * BK, n0);
         }
@@ -239,7 +243,7 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, PBN);
+      const uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, 0, 0, BM, (uint32_t)bn);
       const SmemDesc da0 = make_smem_desc2(smem_u32(smem), 16, 1024, kSwizzle128B);
       int it = 0;
       bool ok = true;
@@ -266,12 +270,16 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
     }
   } else {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;   // which 128 columns of the tile
+    const int half = (warp - 2) >> 2;   // which half of the tile's 32-column chunks
     const bool lead = warp == 2 && lane == 0;
+    const int nchunks = (bn + 31) / 32;
+    const int c_begin = half == 0 ? 0 : ((nchunks + 1) / 2) * 32;
+    const int c_end = half == 0 ? ((nchunks + 1) / 2) * 32 : nchunks * 32;
     for (int i = 0; i < my_tiles; ++i) {
       const int b = i & 1;
       const int t = blockIdx.x + i * gridDim.x;
-      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * PBN;
+      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * bn;
+      const int n_end = min(N, n0 + bn);      // columns past the tile belong to the next one (or to nobody)
       // one thread polls, the eight warps meet at a named barrier that also carries the outcome
       uint32_t ok = 1;
       if (lead) ok = mbar_wait(&acc_full[b], (uint32_t)((i >> 1) & 1), status, QB_ERR_TIMEOUT) ? 1u : 0u;
@@ -282,20 +290,27 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
       tc_fence_after_sync();
       const int m = m0 + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * PBN);
-      const int c_end = half * (PBN / 2) + PBN / 2;
+      bool released = false;
 #pragma unroll 1
-      for (int c = half * (PBN / 2); c < c_end; c += 64) {
+      for (int c = c_begin; c < c_end; c += 64) {
         uint32_t r0[32], r1[32];
+        const bool two = c + 32 < c_end;
         tmem_ld_32x32(acc + (uint32_t)c, r0);
-        tmem_ld_32x32(acc + (uint32_t)c + 32, r1);
+        if (two) tmem_ld_32x32(acc + (uint32_t)c + 32, r1);
         tmem_ld_wait();
         if (c + 64 >= c_end) {  // the last columns are in registers: hand the accumulator back before storing them
           tc_fence_before_sync();
           asm volatile("bar.sync 1, 256;" ::: "memory");
           if (lead) mbar_arrive(&acc_empty[b]);
+          released = true;
         }
-        store_chunk(r0, m, n0 + c, M, N, ep);
-        store_chunk(r1, m, n0 + c + 32, M, N, ep);
+        store_chunk(r0, m, n0 + c, M, n_end, ep);
+        if (two) store_chunk(r1, m, n0 + c + 32, M, n_end, ep);
+      }
+      if (!released) {          // a half without chunks (tile narrower than 64 columns) still takes part in the hand-over
+        tc_fence_before_sync();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (lead) mbar_arrive(&acc_empty[b]);
       }
     }
   }
@@ -377,15 +392,25 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
   static const bool no_persistent = getenv("QB_GEMM_SMALL_TILES") != nullptr;
   const int64_t ptiles = ceil_div(M, BM) * ceil_div(N, PBN);
   if (!no_persistent && ptiles >= sm_count()) {   // enough 128 x 256 tiles to give every SM at least one
-    rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, PBN, BK);
+    // tile width: the one whose rounds of the grid cost least (rounds x width); ties go to the wider tile.  Only multiples
+    // of 64 columns: 144 .. 240 in steps of 16 were measured too, and every width that is not a multiple of 64 ran 25-90 %
+    // slower per column than its neighbours.
+    int bn = PBN;
+    int64_t best = INT64_MAX;
+    for (int cand = PBN; cand >= 192; cand -= 64) {
+      const int64_t t = ceil_div(M, BM) * ceil_div(N, cand);
+      const int64_t cost = ceil_div(t, sm_count()) * cand;
+      if (cost < best) { best = cost; bn = cand; }
+    }
+    rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, BK);
     if (rc != QB_OK) return rc;
     static bool pattr_set[64] = {};
     if (dev >= 64 || !pattr_set[dev]) {
       QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes));
       if (dev < 64) pattr_set[dev] = true;
     }
-    const unsigned grid = (unsigned)std::min<int64_t>(ptiles, sm_count());
-    gemm_s8_tcgen05_persistent_kernel<<<grid, kPThreads, kPSmemBytes, st>>>(ta, tw, M, N, K, ep, status);
+    const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(M, BM) * ceil_div(N, bn), sm_count());
+    gemm_s8_tcgen05_persistent_kernel<<<grid, kPThreads, kPSmemBytes, st>>>(ta, tw, M, N, K, bn, ep, status);
     QB_LAUNCH_OK("gemm_s8_tcgen05_persistent_kernel");
     return QB_OK;
   }

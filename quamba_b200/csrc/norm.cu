@@ -57,77 +57,107 @@ __device__ __forceinline__ float seg_reduce(float v, float* red, int warp, int l
   return r;
 }
 
-// GATE: 0 no gate, 1 x * silu(z) before the norm, 2 y * silu(z) after it (z is then read a second time).
-template <int WPR, int GATE>
+// int8 -> float without a conversion instruction: byte k of w (biased by 128) under the exponent of 2^23.
+__device__ __forceinline__ float s8_to_float(uint32_t w_biased, int k) {
+  const uint32_t bits = __byte_perm(w_biased, 0x4B000000u, 0x7650 + k);   // {b_k, 0x00, 0x00, 0x4B}
+  return __uint_as_float(bits) - 8388736.0f;                                // 2^23 + 128
+}
+
+// GATE: 0 no gate, 1 x * silu(z) before the norm, 2 y * silu(z) after it.  CH: 16-byte chunks per thread.
+// Every global load of the segment is issued before the first use (clamped addresses, no branches around the loads),
+// so a thread has all its chunks in flight at once.
+template <int WPR, int GATE, int CH>
 __global__ void __launch_bounds__((WPR > kNormWarps ? WPR : kNormWarps) * 32)
 norm_quant_kernel(const NormParams p) {
   constexpr int WARPS = WPR > kNormWarps ? WPR : kNormWarps;
   constexpr int T = 32 * WPR;                 // threads per segment
   __shared__ float red[WARPS];
-  grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t unit = (int64_t)blockIdx.x * (WARPS / WPR) + warp / WPR;
-  const bool live = unit < (int64_t)p.M * p.ngroups;
-  const int row = live ? (int)(unit / p.ngroups) : 0;
-  const int grp = live ? (int)(unit % p.ngroups) : 0;
+  const int64_t units = (int64_t)p.M * p.ngroups;
+  const int64_t unit_raw = (int64_t)blockIdx.x * (WARPS / WPR) + warp / WPR;
+  const bool live = unit_raw < units;
+  const int64_t unit = live ? unit_raw : units - 1;
+  const int row = (int)(unit / p.ngroups), grp = (int)(unit % p.ngroups);
   const int t = (warp % WPR) * 32 + lane;
   const int chunks = p.N >> 3;
   const int64_t col0 = (int64_t)grp * p.N;
+  int cc[CH];
+  bool on[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) { const int c = t + i * T; on[i] = c < chunks; cc[i] = on[i] ? c : chunks - 1; }
 
-  float v[kCH][8];
+  // weights do not depend on the kernel before this one: fetch them ahead of the dependency wait
+  uint4 wr[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) wr[i] = __ldg(reinterpret_cast<const uint4*>(p.w + col0) + cc[i]);
+  grid_dependency_wait();
+
+  uint4 xr[CH];
+  uint2 zr[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) xr[i] = __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + col0) + cc[i]);
+  if (GATE != 0) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) zr[i] = __ldg(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + cc[i]);
+  }
+  float v[CH][8];
+  if (GATE == 0 && p.residual != nullptr && p.res_f32) {
+    float4 ra[CH], rb[CH];
+    const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + (int64_t)row * p.res_stride + col0);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) { ra[i] = __ldg(r + 2 * cc[i]); rb[i] = __ldg(r + 2 * cc[i] + 1); }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      v[i][0] = ra[i].x; v[i][1] = ra[i].y; v[i][2] = ra[i].z; v[i][3] = ra[i].w;
+      v[i][4] = rb[i].x; v[i][5] = rb[i].y; v[i][6] = rb[i].z; v[i][7] = rb[i].w;
+    }
+  } else if (GATE == 0 && p.residual != nullptr) {
+    uint4 rr[CH];
+    const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.residual) + (int64_t)row * p.res_stride + col0);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) rr[i] = __ldg(r + cc[i]);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const __half2* rh = reinterpret_cast<const __half2*>(&rr[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y; }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CH; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+  }
   float sum = 0.f;
+  float gate[GATE == 2 ? CH : 1][8];
 #pragma unroll
-  for (int i = 0; i < kCH; ++i) {
-    const int c = t + i * T;
-    const bool on = live && c < chunks;
+  for (int i = 0; i < CH; ++i) {
+    const __half2* h = reinterpret_cast<const __half2*>(&xr[i]);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
-    if (on) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + col0) + c);
-      const __half2* h = reinterpret_cast<const __half2*>(&raw);
+    for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); v[i][2 * e] += f.x; v[i][2 * e + 1] += f.y; }
+    if (GATE == 0 && p.residual_out != nullptr && live && on[i]) {
+      if (p.res_out_f32) {
+        float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.residual_out) + (int64_t)row * p.res_out_stride + col0) + 2 * cc[i];
+        o[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+        o[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+      } else {
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __half22float2(h[e]);
-        v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y;
+        for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(v[i][2 * e], v[i][2 * e + 1]);
+        *(reinterpret_cast<uint4*>(static_cast<__half*>(p.residual_out) + (int64_t)row * p.res_out_stride + col0) + cc[i]) = o;
       }
-      if (GATE == 0 && p.residual != nullptr) {
-        if (p.res_f32) {
-          const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + (int64_t)row * p.res_stride + col0) + 2 * c;
-          const float4 a = __ldg(r), b = __ldg(r + 1);
-          v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
-          v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
-        } else {
-          const uint4 rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(p.residual) + (int64_t)row * p.res_stride + col0) + c);
-          const __half2* rh = reinterpret_cast<const __half2*>(&rr);
+    }
+    if (GATE != 0) {
+      const uint32_t zw[2] = {zr[i].x ^ 0x80808080u, zr[i].y ^ 0x80808080u};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(rh[e]);
-            v[i][2 * e] += f.x; v[i][2 * e + 1] += f.y;
-          }
-        }
+      for (int e = 0; e < 8; ++e) {
+        const float hz = s8_to_float(zw[e >> 2], e & 3) * (0.5f * p.z_scale);      // z / 2
+        const float sg = fmaf(hz, tanh_approx(hz), hz);                               // z * sigmoid(z)
+        if (GATE == 1) v[i][e] *= sg; else gate[GATE == 2 ? i : 0][e] = sg;
       }
-      if (GATE == 0 && p.residual_out != nullptr) {
-        if (p.res_out_f32) {
-          float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.residual_out) + (int64_t)row * p.res_out_stride + col0) + 2 * c;
-          o[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-          o[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
-        } else {
-          uint4 o;
-          __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(v[i][2 * e], v[i][2 * e + 1]);
-          *(reinterpret_cast<uint4*>(static_cast<__half*>(p.residual_out) + (int64_t)row * p.res_out_stride + col0) + c) = o;
-        }
-      }
-      if (GATE == 1) {
-        const uint2 zr = __ldg(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + c);
-        const uint32_t zw[2] = {zr.x, zr.y};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float zf = (float)(int8_t)(zw[e >> 2] >> (8 * (e & 3))) * p.z_scale;
-          v[i][e] *= zf * (1.0f / (1.0f + __expf(-zf)));
-        }
-      }
+    }
+    if (on[i]) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) sum += p.rms ? v[i][e] * v[i][e] : v[i][e];
     }
@@ -140,8 +170,8 @@ norm_quant_kernel(const NormParams p) {
     mean = seg_reduce<WPR, false>(sum, red, warp, lane) * inv_n;
     float sq = 0.f;
 #pragma unroll
-    for (int i = 0; i < kCH; ++i)
-      if (live && t + i * T < chunks) {
+    for (int i = 0; i < CH; ++i)
+      if (on[i]) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) { const float d = v[i][e] - mean; sq += d * d; }
       }
@@ -151,60 +181,47 @@ norm_quant_kernel(const NormParams p) {
 
   float mx = p.pad_zero ? 0.f : -INFINITY;
 #pragma unroll
-  for (int i = 0; i < kCH; ++i) {
-    const int c = t + i * T;
-    if (live && c < chunks) {
-      const uint4 wr = __ldg(reinterpret_cast<const uint4*>(p.w + col0) + c);
-      const __half2* wh = reinterpret_cast<const __half2*>(&wr);
-      uint4 br = make_uint4(0, 0, 0, 0);
-      if (p.bias != nullptr) br = __ldg(reinterpret_cast<const uint4*>(p.bias + col0) + c);
-      const __half2* bh = reinterpret_cast<const __half2*>(&br);
-      uint32_t zw[2] = {0, 0};
-      if (GATE == 2) {
-        const uint2 zr = __ldg(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + c);
-        zw[0] = zr.x; zw[1] = zr.y;
-      }
+  for (int i = 0; i < CH; ++i) {
+    const __half2* wh = reinterpret_cast<const __half2*>(&wr[i]);
+    uint4 br = make_uint4(0, 0, 0, 0);
+    if (p.bias != nullptr) br = __ldg(reinterpret_cast<const uint4*>(p.bias + col0) + cc[i]);
+    const __half2* bh = reinterpret_cast<const __half2*>(&br);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 w2 = __half22float2(wh[e]);
-        const float2 b2 = __half22float2(bh[e]);
-        float y0 = (v[i][2 * e] - mean) * rstd * w2.x;
-        float y1 = (v[i][2 * e + 1] - mean) * rstd * w2.y;
-        if (p.bias != nullptr) { y0 += b2.x; y1 += b2.y; }
-        if (GATE == 2) {
-          const float z0 = (float)(int8_t)(zw[e >> 1] >> (16 * (e & 1))) * p.z_scale;
-          const float z1 = (float)(int8_t)(zw[e >> 1] >> (16 * (e & 1) + 8)) * p.z_scale;
-          y0 *= z0 * (1.0f / (1.0f + __expf(-z0)));
-          y1 *= z1 * (1.0f / (1.0f + __expf(-z1)));
-        }
-        v[i][2 * e] = y0; v[i][2 * e + 1] = y1;
-        mx = fmaxf(mx, fmaxf(y0, y1));
-      }
+    for (int e = 0; e < 4; ++e) {
+      const float2 w2 = __half22float2(wh[e]);
+      float y0 = (v[i][2 * e] - mean) * rstd * w2.x;
+      float y1 = (v[i][2 * e + 1] - mean) * rstd * w2.y;
+      if (p.bias != nullptr) { const float2 b2 = __half22float2(bh[e]); y0 += b2.x; y1 += b2.y; }
+      if (GATE == 2) { y0 *= gate[GATE == 2 ? i : 0][2 * e]; y1 *= gate[GATE == 2 ? i : 0][2 * e + 1]; }
+      v[i][2 * e] = y0; v[i][2 * e + 1] = y1;
+      if (on[i]) mx = fmaxf(mx, fmaxf(y0, y1));
     }
   }
-  float scale = p.out_scale;
-  if (p.out_kind == kOutS8Dynamic) {
-    scale = seg_reduce<WPR, true>(mx, red, warp, lane) / 127.0f;
+  float inv_scale = 0.f;
+  if (p.out_kind == kOutS8Static) {
+    inv_scale = 1.0f / p.out_scale;
+  } else if (p.out_kind == kOutS8Dynamic) {
+    const float scale = seg_reduce<WPR, true>(mx, red, warp, lane) / 127.0f;
     if (live && t == 0) p.dyn_scale[(int64_t)grp * p.M + row] = scale;
+    inv_scale = 1.0f / scale;
   }
 #pragma unroll
-  for (int i = 0; i < kCH; ++i) {
-    const int c = t + i * T;
-    if (live && c < chunks) {
+  for (int i = 0; i < CH; ++i) {
+    if (live && on[i]) {
       if (p.out_kind == kOutF16) {
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
         for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(v[i][2 * e], v[i][2 * e + 1]);
-        *(reinterpret_cast<uint4*>(static_cast<__half*>(p.y) + (int64_t)row * p.y_stride + col0) + c) = o;
+        *(reinterpret_cast<uint4*>(static_cast<__half*>(p.y) + (int64_t)row * p.y_stride + col0) + cc[i]) = o;
       } else {
         int q[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) q[e] = __float2int_rn(__fdiv_rn(v[i][e], scale));
+        for (int e = 0; e < 8; ++e) q[e] = __float2int_rn(v[i][e] * inv_scale);
         uint2 o;
         o.x = pack4_sat_s8(q[0], q[1], q[2], q[3]);
         o.y = pack4_sat_s8(q[4], q[5], q[6], q[7]);
-        *(reinterpret_cast<uint2*>(static_cast<int8_t*>(p.y) + (int64_t)row * p.y_stride + col0) + c) = o;
+        *(reinterpret_cast<uint2*>(static_cast<int8_t*>(p.y) + (int64_t)row * p.y_stride + col0) + cc[i]) = o;
       }
     }
   }
@@ -280,13 +297,24 @@ __global__ void __launch_bounds__(256) norm_quant_generic_kernel(const NormParam
   }
 }
 
-template <int WPR>
+template <int WPR, int CH>
 void launch_norm(const NormParams& p, int64_t units, cudaStream_t st) {
   constexpr int WARPS = WPR > kNormWarps ? WPR : kNormWarps;
   const dim3 grid((unsigned)ceil_div(units, WARPS / WPR)), block(WARPS * 32);
-  if (p.z == nullptr) launch_dependent(norm_quant_kernel<WPR, 0>, grid, block, 0, st, p);
-  else if (p.gate_first) launch_dependent(norm_quant_kernel<WPR, 1>, grid, block, 0, st, p);
-  else launch_dependent(norm_quant_kernel<WPR, 2>, grid, block, 0, st, p);
+  if (p.z == nullptr) launch_dependent(norm_quant_kernel<WPR, 0, CH>, grid, block, 0, st, p);
+  else if (p.gate_first) launch_dependent(norm_quant_kernel<WPR, 1, CH>, grid, block, 0, st, p);
+  else launch_dependent(norm_quant_kernel<WPR, 2, CH>, grid, block, 0, st, p);
+}
+
+template <int WPR>
+void launch_norm_ch(const NormParams& p, int64_t units, int ch, cudaStream_t st) {
+  if (ch <= 1) launch_norm<WPR, 1>(p, units, st);
+  else if (ch <= 2) launch_norm<WPR, 2>(p, units, st);
+  else if (ch <= 3) launch_norm<WPR, 3>(p, units, st);
+  else if (ch <= 4) launch_norm<WPR, 4>(p, units, st);
+  else if (ch <= 5) launch_norm<WPR, 5>(p, units, st);
+  else if (ch <= 6) launch_norm<WPR, 6>(p, units, st);
+  else launch_norm<WPR, 8>(p, units, st);
 }
 
 int run_norm(const NormParams& p, cudaStream_t st) {
@@ -304,16 +332,18 @@ int run_norm(const NormParams& p, cudaStream_t st) {
     return QB_OK;
   }
   const int chunks = p.N / 8;
+  // Warps per segment: the fewest that keep a thread at six chunks or less (registers), more when there are few
+  // segments (decode), down to two chunks per thread, to shorten the dependent chain.
   int wpr = 1;
-  while (wpr * 32 * kCH < chunks) wpr *= 2;                 // fewest warps that hold the segment in registers
-  // few segments (decode): spread each over more warps, down to two chunks per thread, to shorten the dependent chain
+  while (wpr < 16 && wpr * 32 * 6 < chunks) wpr *= 2;
   while (wpr < 8 && wpr * 64 < chunks && units * (2 * wpr) <= (int64_t)sm_count() * 2 * kNormWarps) wpr *= 2;
+  const int ch = (int)ceil_div(chunks, wpr * 32);
   switch (wpr) {
-    case 1: launch_norm<1>(p, units, st); break;
-    case 2: launch_norm<2>(p, units, st); break;
-    case 4: launch_norm<4>(p, units, st); break;
-    case 8: launch_norm<8>(p, units, st); break;
-    default: launch_norm<16>(p, units, st); break;
+    case 1: launch_norm_ch<1>(p, units, ch, st); break;
+    case 2: launch_norm_ch<2>(p, units, ch, st); break;
+    case 4: launch_norm_ch<4>(p, units, ch, st); break;
+    case 8: launch_norm_ch<8>(p, units, ch, st); break;
+    default: launch_norm_ch<16>(p, units, ch, st); break;
   }
   QB_LAUNCH_OK("norm_quant_kernel");
   return QB_OK;

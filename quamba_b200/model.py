@@ -25,6 +25,9 @@ from .norm import QRMSNorm
 __all__ = ["QuambaConfig", "InferenceParams", "Block", "QuambaMixerModel", "QuambaLMHeadModel", "GraphRunner"]
 
 CausalLMOutput = namedtuple("CausalLMOutput", ["logits"])
+# Development switch: QB_UNFUSED_DECODE=1 keeps the decode step on the one-op-per-launch path (for A/B comparisons).
+import os as _os
+_UNFUSED_DECODE = bool(_os.environ.get("QB_UNFUSED_DECODE"))
 
 
 @dataclass
@@ -126,6 +129,46 @@ class QuambaMixerModel(nn.Module):
         return {i: layer.allocate_inference_cache(batch_size, max_seqlen, dtype=dtype, **kwargs)
                 for i, layer in enumerate(self.layers)}
 
+    # ---- fused decode step (1 to 4 sequences): three launches per layer instead of seven ------------------------
+    def _decode_fusable(self, batch, lm_head):
+        ok = self.__dict__.get("_fusable")
+        if ok is None:
+            from .mixer import W4A8QMamba2
+            from .modules import W4A8B16O16Linear
+            ok = isinstance(lm_head, W4A8B16O16Linear) and self.norm_f.output_scale and self.embedding.embedding_dim <= 8192
+            for layer in self.layers:
+                m = layer.mixer
+                s = m.d_inner // 128 if isinstance(m, W4A8QMamba2) else 0
+                ok = bool(ok and isinstance(m, W4A8QMamba2) and layer.norm.output_scale and m.conv1d.x_head_group_range is None
+                          and m.d_conv == 4 and m.d_inner == m.d_ssm and m.d_inner % 128 == 0 and not m.D_has_hdim
+                          and (s in (12, 20, 28, 40) or (s & (s - 1)) == 0 and s <= 64)
+                          and m.d_model % 32 == 0 and m.d_ssm // m.ngroups % 128 == 0 and m.ngroups <= 64)
+            self.__dict__["_fusable"] = ok
+        return ok and 1 <= batch <= 4 and not _UNFUSED_DECODE
+
+    def decode_step_fused(self, input_ids, inference_params, lm_head):
+        """One token per sequence through all layers and the head; returns logits fp16 (batch, vocab)."""
+        h = self.embedding(input_ids[:, 0])
+        residual = None
+        for layer in self.layers:
+            m, c, s = layer.mixer, layer.mixer.conv1d, layer.mixer.qchunk_scan
+            conv_state, ssm_state = m._get_states_from_cache(inference_params, h.shape[0])
+            gn = m.ngroups * m.d_state
+            conv = dict(state=conv_state, weight=c.weight, bias=c.bias, col0=m.d_ssm, x_dim=m.d_ssm, gn=gn,
+                        scale_in=(c.wx_scale * c.x_scale, c.wB_scale * c.B_scale, c.wC_scale * c.C_scale),
+                        scale_bias=(c.bx_scale or 0.0, c.bB_scale or 0.0, c.bC_scale or 0.0),
+                        out_scales=(c.x_out_scales, c.B_out_scales, c.C_out_scales))
+            zxbcdt, residual = ops.decode_norm_linear(h, residual, layer.norm.weight, layer.norm.eps, layer.norm.output_scale,
+                                                      m.in_proj.prepared(), m.in_proj.input_scale, True, self.residual_in_fp32, conv)
+            dt = zxbcdt[:, 2 * m.d_ssm + 2 * gn:2 * m.d_ssm + 2 * gn + m.nheads]
+            y = s.update(ssm_state, conv["x"], dt, conv["B"], conv["C"], z=None)
+            h = ops.decode_gate_had_linear(y.flatten(-2), zxbcdt[:, :m.d_ssm], m.norm.z_scale, m.norm.weight, m.norm.eps,
+                                           m.norm.group_size or m.d_ssm, m.had.had_scale / m.had.x_H_scale,
+                                           m.out_proj.prepared(), m.out_proj.input_scale)[:, :m.d_model]
+        logits, _ = ops.decode_norm_linear(h, residual, self.norm_f.weight, self.norm_f.eps, self.norm_f.output_scale,
+                                           lm_head.prepared(), lm_head.input_scale, False, self.residual_in_fp32)
+        return logits[:, :lm_head.out_features]
+
     def forward(self, input_ids, inference_params=None, num_last_tokens=0, **mixer_kwargs):
         hidden_states = self.embedding(input_ids)
         residual = None
@@ -161,8 +204,11 @@ class QuambaLMHeadModel(nn.Module):
         """input_ids int64 (batch, seqlen).  Prefill when ``inference_params.seqlen_offset == 0`` (the layers then also
         fill their conv / ssm caches), one decode step otherwise.  ``logits`` fp16 (batch, seqlen or num_last_tokens,
         vocab)."""
-        hidden_states = self.backbone(input_ids, inference_params=inference_params, num_last_tokens=num_last_tokens,
-                                      **mixer_kwargs)
+        bb = self.backbone
+        if (inference_params is not None and inference_params.seqlen_offset > 0 and input_ids.shape[1] == 1
+                and bb._decode_fusable(input_ids.shape[0], self.lm_head)):
+            return CausalLMOutput(logits=bb.decode_step_fused(input_ids, inference_params, self.lm_head)[:, None])
+        hidden_states = bb(input_ids, inference_params=inference_params, num_last_tokens=num_last_tokens, **mixer_kwargs)
         return CausalLMOutput(logits=self.lm_head(hidden_states))
 
     # ---- CUDA-graph runners ------------------------------------------------------------------------------------------

@@ -769,3 +769,59 @@ def greedy_next_token(logits, out=None):
     with torch.cuda.device(logits.device):
         _lib.check(f(logits.data_ptr(), logits.stride(0), rows, n, out.data_ptr(), ctypes.c_void_p(_stream(logits))))
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Fused decode-step launches (1 to 4 rows).  ``prep`` is a W4A8Prepared; per-channel weights stream their nibble copy.
+def _decode_weight(prep):
+    if prep.per_channel and prep.size_k % 32 == 0:
+        return prep.need_w4(), 1
+    return prep.need_w8(), 0
+
+
+def decode_norm_linear(x, residual, norm_weight, eps, norm_out_scale, prep, s_tok, out_int8, residual_in_fp32=True, conv=None):
+    """residual add + RMSNorm + quantise + W4A8 product for (rows, k) fp16 ``x``.  Returns (out (rows, n) int8 or fp16,
+    residual_out).  ``conv``: dict(state, weight, bias, col0, x_dim, gn, scale_in, scale_bias, out_scales) runs the conv1d
+    decode step on columns [col0, col0 + x_dim + 2 gn) in the epilogue and adds ``x``, ``B``, ``C`` int8 outputs to it."""
+    rows, k = x.shape
+    w, s4 = _decode_weight(prep)
+    dt = torch.int8 if out_int8 else torch.float16
+    out = torch.empty((rows, prep.size_n), dtype=dt, device=x.device)
+    res_dtype = residual.dtype if residual is not None else (torch.float32 if residual_in_fp32 else torch.float16)
+    residual_out = torch.empty((rows, k), dtype=res_dtype, device=x.device)
+    kw = {}
+    if conv is not None:
+        st = conv["state"]
+        conv["x"] = torch.empty((rows, conv["x_dim"]), dtype=torch.int8, device=x.device)
+        conv["B"] = torch.empty((rows, conv["gn"]), dtype=torch.int8, device=x.device)
+        conv["C"] = torch.empty((rows, conv["gn"]), dtype=torch.int8, device=x.device)
+        so = conv["out_scales"]
+        kw = dict(conv_state=_p(st), conv_weight=_p(conv["weight"]), conv_bias=_p(conv["bias"]), conv_x=_p(conv["x"]),
+                  conv_B=_p(conv["B"]), conv_C=_p(conv["C"]), x_out_scale=_p(so[0]), B_out_scale=_p(so[1]), C_out_scale=_p(so[2]),
+                  conv_state_sb=st.stride(0), conv_state_sd=st.stride(1), conv_state_sw=st.stride(2), conv_col0=conv["col0"],
+                  conv_dim=conv["x_dim"] + 2 * conv["gn"], conv_x_dim=conv["x_dim"], conv_gn=conv["gn"],
+                  conv_scale_in_x=conv["scale_in"][0], conv_scale_in_B=conv["scale_in"][1], conv_scale_in_C=conv["scale_in"][2],
+                  conv_scale_bias_x=conv["scale_bias"][0], conv_scale_bias_B=conv["scale_bias"][1],
+                  conv_scale_bias_C=conv["scale_bias"][2])
+    args = _lib.make("qb_decode_norm_linear_args", x=_p(x), residual=_p(residual), residual_out=_p(residual_out),
+                     norm_weight=_p(norm_weight), w=_p(w), s_channel_nat=_p(prep.sc), s_tok=_p(s_tok), out=_p(out),
+                     x_row_stride=x.stride(0), residual_row_stride=residual.stride(0) if residual is not None else 0,
+                     residual_out_row_stride=residual_out.stride(0), out_row_stride=out.stride(0), rows=rows, n=prep.size_n,
+                     k=k, w_is_s4=s4, out_int8=int(out_int8), residual_is_f32=int(residual is not None and residual.dtype == torch.float32),
+                     residual_out_is_f32=int(res_dtype == torch.float32), eps=float(eps), norm_out_scale=float(norm_out_scale), **kw)
+    _run("qb_decode_norm_linear", args, x)
+    return out, residual_out
+
+
+def decode_gate_had_linear(y, z, z_scale, norm_weight, eps, group_size, had_scale, prep, s_tok):
+    """y (rows, d) fp16, z (rows, d) int8 (a strided view is fine) -> gate, grouped RMSNorm, Hadamard, quantise, W4A8
+    product: (rows, n) fp16."""
+    rows, d = y.shape
+    w, s4 = _decode_weight(prep)
+    out = torch.empty((rows, prep.size_n), dtype=torch.float16, device=y.device)
+    args = _lib.make("qb_decode_gate_had_linear_args", y=_p(y), z=_p(z), norm_weight=_p(norm_weight), w=_p(w),
+                     s_channel_nat=_p(prep.sc), s_tok=_p(s_tok), out=_p(out), y_row_stride=y.stride(0), z_row_stride=z.stride(0),
+                     out_row_stride=out.stride(0), rows=rows, d=d, group_size=group_size, n=prep.size_n, k=prep.size_k,
+                     w_is_s4=s4, z_scale=float(z_scale), eps=float(eps), had_scale=float(had_scale))
+    _run("qb_decode_gate_had_linear", args, y)
+    return out

@@ -27,7 +27,9 @@ import torch
 import triton
 import triton.language as tl
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: %s <path to the reference checkout>" % sys.argv[0])
+REF = Path(sys.argv[1])
 OUT = Path(__file__).resolve().parent
 
 
@@ -59,7 +61,7 @@ def q8(x):
     return torch.clamp(torch.round(x / s), -128, 127).to(torch.int8), s.float().reshape(1)
 
 
-def run_case(tag, Bsz, L, H, P, G, N, Q, grouped, seed):
+def run_case(tag, Bsz, L, H, P, G, N, Q, grouped, seed, slim=False):
     torch.manual_seed(seed)
     cum, cst, spz, bmm, csc = (_load(n) for n in ("quant_chunk_cumsum", "quant_chunk_state", "quant_state_passing",
                                                    "quant_bmm_chunk", "quant_chunk_scan"))
@@ -194,6 +196,9 @@ def run_case(tag, Bsz, L, H, P, G, N, Q, grouped, seed):
                 ref_final_f16=final.reshape(Bsz, H, P, N), ref_CB=CB, ref_out=out)
     if grouped:
         save.update(head_group_range=hgr, dim_group_range=dgr)
+    if slim:        # keep the fixture small: inputs, the cumulative sums, the outputs
+        for k in ("ref_states", "ref_prev_states", "ref_CB"):
+            save.pop(k)
     np.savez_compressed(OUT / f"ssd_{tag}.npz", **{k: v.numpy() for k, v in save.items()})
     print("wrote", OUT / f"ssd_{tag}.npz")
 
@@ -202,3 +207,6 @@ if __name__ == "__main__":
     _install_stubs()
     run_case("pertensor", Bsz=2, L=96, H=4, P=64, G=1, N=64, Q=64, grouped=False, seed=0)
     run_case("grouped", Bsz=1, L=128, H=8, P=64, G=2, N=64, Q=64, grouped=True, seed=1)
+    # headdim 64, d_state 128, chunk 256: the shape family the tensor-core SSD kernel serves (ragged length: 300 = 256 + 44)
+    # (three chunks, five 128-token blocks, ragged tail: 600 = 256 + 256 + 88)
+    run_case("n128", Bsz=1, L=600, H=2, P=64, G=1, N=128, Q=256, grouped=False, seed=2, slim=True)

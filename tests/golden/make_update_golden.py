@@ -18,7 +18,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: %s <path to the reference checkout>" % sys.argv[0])
+REF = Path(sys.argv[1])
 OUT = Path(__file__).resolve().parent
 
 

@@ -1,9 +1,10 @@
 """GPU parity tests: every call goes through the C ABI (ctypes -> libquamba_b200.so) and is compared
 with the CPU oracle on the same seeded inputs, or with the committed golden vectors.
 
-Tolerances (from the scope statement): re-quantised int8 activations within +-1 LSB; integer GEMM
-results exact; fp16 scan / SSD outputs within 1e-2 relative + 1e-3 absolute (absolute measured on
-the output scale, i.e. 1e-3 * max|ref|)."""
+Tolerances: re-quantised int8 activations within +-1 LSB; integer GEMM results exact; fp16 scan / SSD
+outputs within 1e-2 relative + 1e-3 absolute, the absolute term measured on the output's scale
+(1e-3 * max|ref|; outputs here have max|ref| of 3 to 30, and the achieved absolute error is printed by the
+reference-golden tests)."""
 import pytest
 import torch
 
@@ -234,8 +235,10 @@ def _run_ssd(c, grouped):
         dev(c["dt_bias"]), None, None, None, True)
 
 
-@pytest.mark.parametrize("tag", ["pertensor", "grouped"])
+@pytest.mark.parametrize("tag", ["pertensor", "grouped", "n128"])
 def test_ssd_against_reference_triton_golden(tag):
+    """Outputs of the reference's own Triton kernels (interpreter mode).  "n128" (headdim 64, d_state 128, chunk 256, 600
+    tokens) is the shape family of the tensor-core kernel, the other two reach the portable path."""
     g = load_golden(f"ssd_{tag}.npz")
     grouped = tag == "grouped"
     G, N = g["q_B"].shape[2:]
@@ -245,6 +248,8 @@ def test_ssd_against_reference_triton_golden(tag):
              s_D=g["s_D"], dt_bias=g["dt_bias"])
     y, fs = _run_ssd(c, grouped)
     assert_fp16(y, g["ref_out"])
+    err = (y.cpu().float() - g["ref_out"].float()).abs().max().item()
+    print(f"ssd_{tag}: max |y - reference| = {err:.3e} with max |reference| = {g['ref_out'].float().abs().max().item():.3f}")
     want_q = torch.clamp(torch.round(g["ref_final_f16"].float() / 0.01), -128, 127).to(torch.int8)
     assert_lsb(fs, want_q, max_frac=0.02)
 
@@ -428,9 +433,11 @@ def test_update_kernel_variants_against_oracle(Bsz, H, P, G, N, grouped, layout)
     ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)      # raises if a device-side wait timed out
 
 
-# ---- large GEMMs: the persistent 128 x 256 tensor-core kernel (needs at least one tile per SM) ---------------------
+# ---- large GEMMs: the persistent tensor-core kernel (needs at least one 128 x 256 tile per SM; the tile width it then
+# uses, 192 or 256 columns, depends on the shape: the cases below reach both) ---------------------------
 @pytest.mark.parametrize("M,K,N,out_dtype", [(2000, 528, 3024, torch.int8), (2048, 1024, 5120, torch.float16),
-                                             (4100, 272, 2304, torch.int8)])
+                                             (4100, 272, 2304, torch.int8), (2048, 512, 2560, torch.float16),
+                                             (2048, 256, 10576, torch.int8), (8192, 128, 2560, torch.float16)])
 def test_w8a8_gemm_large_against_exact_float_matmul(M, K, N, out_dtype):
     """|acc| <= K * 127^2 < 2^24 for K <= 1040, so an fp32 matmul of the int8 values is exact and serves as the accumulator
     reference at sizes the CPU oracle would take minutes for; the epilogue is then restated with the oracle's operation order."""

@@ -227,7 +227,7 @@ def test_model_prefill_and_graph_decode_match_oracle():
     runner.input_ids.copy_(ids)
     got = runner.replay()
     torch.cuda.synchronize()
-    _close(got, want, "prefill logits", atol_rel=2e-2)
+    _close(got, want, "prefill logits", atol_rel=3e-2, max_frac=0.02)
     # decode from the prefill's caches under a CUDA graph; the oracle continues from the same (GPU) states
     params = runner.inference_params
     params.seqlen_offset = 200
@@ -238,7 +238,7 @@ def test_model_prefill_and_graph_decode_match_oracle():
         dec.input_ids.copy_(tok[:, None])
         logits = dec.replay().clone()
         want_step = omodel.model_step(q, tok.cpu(), cpu_states)
-        _close(logits, want_step, "decode logits", atol_rel=2e-2)
+        _close(logits, want_step, "decode logits", atol_rel=3e-2, max_frac=0.02)
         nxt = dec.input_ids[:, 0].clone()
         assert torch.equal(nxt.cpu(), logits.float().cpu().argmax(-1))
         tok = nxt
@@ -280,3 +280,41 @@ def olin_ref(ql, x):
     sg = ql.s_group.cpu() if ql.s_group.numel() else None
     return olin.w4a8_gemm(x.cpu(), ql.weight.cpu(), ql.input_scale.cpu().reshape(1), ql.s_channel.cpu(), sg, ql.size_n,
                           ql.size_k, False)[:, :ql.out_features]
+
+
+@pytest.mark.parametrize("group,batch", [(-1, 1), (None, 1), (-1, 2), (None, 3), (-1, 4)])
+def test_fused_decode_step_equals_the_op_by_op_step(group, batch, monkeypatch):
+    """The three-launch decode step against the seven-launch one on the same model, token and caches, and against the
+    CPU oracle's step: conv state bit for bit, int8 ssm state +-1 LSB, logits within the model-level tolerance."""
+    import copy
+    import quamba_b200.model as qmodel
+    from quamba_b200.model import InferenceParams
+    q, ids = _small(11 + batch, group, n_layer=2, L=40, batch=batch)
+    gq = copy.deepcopy(q).to(DEV)
+    params = InferenceParams(max_seqlen=64, max_batch_size=batch)
+    first = gq(ids.to(DEV), inference_params=params, num_last_tokens=1).logits[:, -1]
+    tok = ops().greedy_next_token(first.contiguous())
+    params.seqlen_offset = 40
+    base = {k: tuple(t.clone() for t in v) for k, v in params.key_value_memory_dict.items()}
+    cpu_states = {k: tuple(t.cpu().clone() for t in v) for k, v in base.items()}
+    assert gq.backbone._decode_fusable(batch, gq.lm_head)
+    fused = gq(tok[:, None], inference_params=params).logits[:, -1].clone()
+    fused_states = {k: tuple(t.clone() for t in v) for k, v in params.key_value_memory_dict.items()}
+    for k, v in base.items():
+        for dst, src in zip(params.key_value_memory_dict[k], v):
+            dst.copy_(src)
+    monkeypatch.setattr(qmodel, "_UNFUSED_DECODE", True)
+    plain = gq(tok[:, None], inference_params=params).logits[:, -1].clone()
+    want = omodel.model_step(q, tok.cpu(), cpu_states)
+    _close(fused, plain.cpu(), "fused vs op-by-op logits", atol_rel=3e-2, max_frac=0.02)
+    _close(fused, want, "fused vs oracle logits", atol_rel=3e-2, max_frac=0.02)
+    for k in base:
+        conv_f, ssm_f = fused_states[k]
+        conv_p, ssm_p = params.key_value_memory_dict[k]
+        if k == 0:      # the first layer sees identical inputs on both paths
+            assert torch.equal(conv_f, conv_p)
+            assert torch.equal(conv_f.cpu(), cpu_states[k][0])
+            assert (ssm_f.int() - ssm_p.int()).abs().max().item() <= 1
+        else:           # later layers inherit +-1 LSB differences of the layer before
+            assert (conv_f.int() - conv_p.int()).abs().float().mean().item() < 0.05
+            assert (ssm_f.int() - ssm_p.int()).abs().max().item() <= 2

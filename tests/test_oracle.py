@@ -9,7 +9,7 @@ from helpers import load_golden, make_conv2_case, make_ssd_case, make_sscan_case
 
 
 # ---- SSD: faithful oracle vs the reference's Triton kernels (interpreter-mode golden) -------------
-@pytest.mark.parametrize("tag", ["pertensor", "grouped"])
+@pytest.mark.parametrize("tag", ["pertensor", "grouped", "n128"])
 def test_ssd_oracle_matches_reference_triton(tag):
     g = load_golden(f"ssd_{tag}.npz")
     hgr, dgr = g.get("head_group_range"), g.get("dim_group_range")
@@ -20,20 +20,21 @@ def test_ssd_oracle_matches_reference_triton(tag):
                                         None, None, g["dt_bias"], True, return_intermediates=True)
     assert torch.allclose(im["dt"].permute(0, 3, 1, 2), g["ref_dt"], atol=1e-6)
     assert torch.allclose(im["dA_cs"].permute(0, 3, 1, 2), g["ref_dA_cs"], rtol=1e-6, atol=1e-4)
-    assert torch.allclose(im["states"], g["ref_states"], rtol=1e-4, atol=1e-4)
-    assert torch.allclose(im["prev_states"], g["ref_prev_states"].float(), rtol=2e-3, atol=2e-4)
+    if "ref_states" in g:       # the d_state-128 fixture stores inputs, cumulative sums and outputs only
+        assert torch.allclose(im["states"], g["ref_states"], rtol=1e-4, atol=1e-4)
+        assert torch.allclose(im["prev_states"], g["ref_prev_states"].float(), rtol=2e-3, atol=2e-4)
+        assert torch.allclose(im["CB"], g["ref_CB"], rtol=1e-5, atol=1e-4)
     assert torch.allclose(im["final_f16"], g["ref_final_f16"].float(), rtol=2e-3, atol=2e-4)
-    assert torch.allclose(im["CB"], g["ref_CB"], rtol=1e-5, atol=1e-4)
     assert torch.allclose(y.float(), g["ref_out"].float(), rtol=2e-3, atol=4e-3)
 
 
-@pytest.mark.parametrize("tag", ["pertensor", "grouped"])
+@pytest.mark.parametrize("tag", ["pertensor", "grouped", "n128"])
 def test_ssd_ideal_recurrence_agrees_with_reference(tag):
     g = load_golden(f"ssd_{tag}.npz")
     hgr, dgr = g.get("head_group_range"), g.get("dim_group_range")
     yi, hi = ossd.chunk_scan_ideal(g["q_x"], g["x_scales"], hgr, dgr, g["q_dt"], g["s_dt"], g["q_A_log"], g["s_A"],
                                    g["q_B"], g["s_B"], g["q_C"], g["s_C"], g["q_D"], g["s_D"], None, None, g["dt_bias"], True)
-    # the north-star tolerance: 1e-2 relative / 1e-3 absolute (on the output scale) in fp16
+    # fp16 tolerance: 1e-2 relative + 1e-3 of the output's largest magnitude absolute
     ref = g["ref_out"].float()
     assert ((yi.float() - ref).abs() <= 1e-3 * ref.abs().max() + 1e-2 * ref.abs()).all()
     assert torch.allclose(hi.float(), g["ref_final_f16"].float(), rtol=1e-2, atol=2e-3)

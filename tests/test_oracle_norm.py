@@ -120,7 +120,9 @@ def test_oracle_decode_step_continues_the_prefill():
     ids = seqs[0]
     states = {}
     lo = omodel.model_forward(q, ids[:, :-1], states=states)
+    before = states[0][1].clone()
     step = omodel.model_step(q, ids[:, -1], states)
+    assert states[0][1].abs().max().item() > 0 and not torch.equal(states[0][1], before)   # the int8 state moved on in place
     full = omodel.model_forward(q, ids)[:, -1]
     # the step starts from int8-rounded states, the prefill carries them in floating point
     assert (step.float() - full.float()).abs().max().item() < 0.05 * full.float().abs().max().item()
