@@ -588,8 +588,8 @@ int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t
 
 /* ------------------------------------------------------------------------------------------
  * Fused decode-step kernels for 1 to 4 rows (one token per sequence).  The reference launches these ops one by one
- * (block QRMSNorm, quamba/qNorm.py:52-87, then W4A8QMamba2.step, quamba/qMamba2.py:997-1020); here three launches cover
- * a layer, each bit-compatible with the separate entry points above up to their stated tolerances.
+ * (block QRMSNorm, quamba/qNorm.py:52-87, then W4A8QMamba2.step, quamba/qMamba2.py:997-1020); here four launches cover
+ * a layer (these two, the state update and the out_proj product), each bit-compatible with the separate entry points above up to their stated tolerances.
  *
  * qb_decode_norm_linear: h = x (+ residual); residual_out = h; a = int8(rmsnorm(h) * norm_weight / norm_out_scale);
  *   out (rows, n) = a @ W^T scaled by s_channel_nat[n] * s_tok, int8 (rint, saturating) or fp16.  W is the int8 copy
@@ -598,9 +598,10 @@ int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t
  *   quamba2_conv1d update (width 4, per-tensor output scales; state element (b, c, w) at b*sb + c*sd + w*sw shifted in
  *   place) and the conv results go to conv_x (rows, conv_x_dim), conv_B / conv_C (rows, conv_gn).
  *   conv_scale_in_* = weight scale * input scale of the segment; conv_scale_bias_* = bias scale.
- * qb_decode_gate_had_linear: g = y * silu(z_scale * z); grouped rmsnorm(g) * norm_weight rounded to fp16; Hadamard
- *   rotation of length d = k (d / 128 in {12, 20, 28, 40} or a power of two <= 64); a = sat_int8(roundf(. * had_scale));
- *   out (rows, n) fp16 = a @ W^T scaled by s_channel_nat[n] * s_tok.
+ * qb_decode_gate_had_quant: g = y * silu(z_scale * z); grouped rmsnorm(g) * norm_weight rounded to fp16; Hadamard
+ *   rotation of length d (d / 128 in {12, 20, 28, 40} or a power of two <= 64; the norm group size a multiple of 128);
+ *   out (rows, d) int8 = sat(roundf(. * had_scale)): QRMSNormGated + QHadamard (quamba/qNorm.py:145-174,
+ *   quamba/qHadamard.py:31-35) in one launch, for any number of rows.
  * ------------------------------------------------------------------------------------------ */
 typedef struct {
   const void* x;
@@ -653,24 +654,18 @@ typedef struct {
   const void* y;
   const int8_t* z;
   const void* norm_weight;
-  const void* w;
-  const float* s_channel_nat;
-  const float* s_tok;
-  void* out;
+  int8_t* out;
   int64_t y_row_stride;
   int64_t z_row_stride;
   int64_t out_row_stride;
   int32_t rows;
   int32_t d;
   int32_t group_size;
-  int32_t n;
-  int32_t k;
-  int32_t w_is_s4;
   float z_scale;
   float eps;
   float had_scale;
-} qb_decode_gate_had_linear_args;
-int qb_decode_gate_had_linear(const qb_decode_gate_had_linear_args* a, void* stream);
+} qb_decode_gate_had_quant_args;
+int qb_decode_gate_had_quant(const qb_decode_gate_had_quant_args* a, void* stream);
 
 #ifdef __cplusplus
 }

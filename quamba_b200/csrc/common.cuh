@@ -47,6 +47,10 @@ void set_error(const char* fmt, ...);
 // before its first access to global memory) until that predecessor has completed and its writes are visible.  The
 // error of a failed launch is picked up by QB_LAUNCH_OK like that of a <<<>>> launch.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the NEXT programmatic dependent on the stream be scheduled now: its CTAs then run up to their own
+// grid_dependency_wait (set-up, prefetch of weights) while this kernel is still working.  Only for kernels whose whole
+// grid is resident at once (the small kernels of a decode step): waiting dependents hold SM resources.
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 template <typename... KArgs, typename... Args>
 inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};

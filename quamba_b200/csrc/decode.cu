@@ -1,14 +1,14 @@
 // Fused kernels of the Mamba2 decode step for small batches (sm_100a).
 //
 // A decode step of one layer is seven tiny ops in the reference (block norm, in_proj, conv update, state update, gated
-// norm, Hadamard + quantise, out_proj), each far below the launch-to-launch gap of a captured graph.  Three launches do
+// norm, Hadamard + quantise, out_proj), each far below the launch-to-launch gap of a captured graph.  Four launches do
 // the same work here:
 //   1. qb_decode_norm_linear: residual add + RMSNorm + int8 quantise (re-done by every CTA in shared memory, it is 5 KB of
 //      input) -> weight-streaming W4A8 product -> optional conv1d update of the xBC columns in the product's epilogue
 //      (the warp that owns an output column also owns that channel's conv window).
 //   2. the state update (qb_sscan_update, unchanged).
-//   3. qb_decode_gate_had_linear: y * silu(z) -> grouped RMSNorm -> Hadamard rotation -> int8 quantise (again per CTA in
-//      shared memory) -> weight-streaming W4A8 product with fp16 output.
+//   3. qb_decode_gate_had_quant: y * silu(z) -> grouped RMSNorm -> Hadamard rotation -> int8 quantise, one CTA per block
+//      of 128 outputs; the out_proj product then runs as the ordinary weight-streaming kernel (a fourth launch).
 // Arithmetic, rounding and operation order are those of the separate kernels (norm.cu, hadamard.cu, conv1d.cu,
 // linear.cu), so results agree with the unfused path to the same tolerances.
 #include <algorithm>
@@ -222,6 +222,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   __shared__ float red[kWarps];
   int8_t* sA = reinterpret_cast<int8_t*>(dsm);                 // MB rows of k int8
   const int K = L.k;
+  grid_dependency_launch();
   prefetch_first_columns<S4>(L);
   grid_dependency_wait();
   const int chunks = K / 8;
@@ -304,113 +305,110 @@ struct GateIn {
   float z_scale, eps, had_scale;        // had_scale: (1 / sqrt(d)) / x_H_scale
 };
 
-constexpr int kMaxRowsPerWarp = 8;      // d / 128 <= 64 rows of 128 over 8 warps
+// The gated norm + Hadamard + quantise of one row, spread over S = d / 128 CTAs of 128 threads: every CTA gates,
+// normalises and runs the 128-point stage on the whole row (a few hundred instructions per thread, all in registers and
+// shuffles), then produces ONE block of 128 outputs of the S-point stage (S multiply-adds per thread).  Doing the S-point
+// stage for all S blocks in every CTA of the product kernel was tried first: 5 000 instructions per warp of serial
+// prologue, 28 us for a 6.6 MB product.
+constexpr int kHadThreads = 128;
+constexpr int kHadWarps = kHadThreads / 32;
+constexpr int kMaxRowsPerWarp = 16;      // d / 128 <= 64 rows of 128 over 4 warps
 
-template <int MB, bool S4>
-__global__ void __launch_bounds__(kThreads, 2)
-decode_gate_had_linear_kernel(GateIn gin, Linear L, ConvEpi cv, int rows) {
+__global__ void __launch_bounds__(kHadThreads)
+decode_gate_had_quant_kernel(GateIn gin, int8_t* __restrict__ out, int64_t out_stride) {
   extern __shared__ __align__(16) uint8_t dsm[];
-  __shared__ float gsum[64];
+  __shared__ float gsum[64], rowsum[64];
   const int D = gin.d, S = D / 128;
   float* buf = reinterpret_cast<float*>(dsm);                         // d floats: the row after the 128-point stage
-  int8_t* sA = reinterpret_cast<int8_t*>(dsm + (size_t)D * 4);        // MB rows of d int8
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  prefetch_first_columns<S4>(L);
+  const int row = blockIdx.y, iout = blockIdx.x;
+  grid_dependency_launch();
   grid_dependency_wait();
-  for (int m = 0; m < MB; ++m) {
-    const int row = min(m, rows - 1);
-    if (threadIdx.x < 64) gsum[threadIdx.x] = 0.f;
-    __syncthreads();
-    // A warp owns rows r = warp, warp + 8, ... of the (S x 128) view; a lane holds four neighbours of each.
-    // gate: v = y * silu(z); sum of squares per norm group (a group is a whole number of 128-element rows)
-    float f[kMaxRowsPerWarp][4];
-    uint2 yr[kMaxRowsPerWarp];
-    uint32_t zr[kMaxRowsPerWarp];
+  // A warp owns rows r = warp, warp + 4, ... of the (S x 128) view; a lane holds four neighbours of each.
+  float f[kMaxRowsPerWarp][4];
+  uint2 yr[kMaxRowsPerWarp];
+  uint32_t zr[kMaxRowsPerWarp];
 #pragma unroll
-    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
-      const int r = min(warp + i * kWarps, S - 1);
-      yr[i] = __ldg(reinterpret_cast<const uint2*>(gin.y + (int64_t)row * gin.y_stride + r * 128) + lane);
-      zr[i] = __ldg(reinterpret_cast<const uint32_t*>(gin.z + (int64_t)row * gin.z_stride + r * 128) + lane);
-    }
-#pragma unroll
-    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
-      const int r = warp + i * kWarps;
-      const __half2* h = reinterpret_cast<const __half2*>(&yr[i]);
-      const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
-      f[i][0] = a.x; f[i][1] = a.y; f[i][2] = b.x; f[i][3] = b.y;
-      const uint32_t zw = zr[i] ^ 0x80808080u;
-      float ss = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float hz = s8f(zw, e) * (0.5f * gin.z_scale);
-        f[i][e] *= fmaf(hz, tanh_approx(hz), hz);
-        ss += f[i][e] * f[i][e];
-      }
-      ss = warp_sum_f(ss);
-      if (lane == 0 && r < S) atomicAdd(&gsum[(r * 128) / gin.group_size], ss);
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < kMaxRowsPerWarp; ++i) {
-      const int r = warp + i * kWarps;
-      if (r < S) {          // warp-uniform
-        // normalise and round to fp16 as the separate norm kernel stores it
-        const float rstd = 1.0f / sqrtf(gsum[(r * 128) / gin.group_size] / (float)gin.group_size + gin.eps);
-        const uint2 wr = __ldg(reinterpret_cast<const uint2*>(gin.weight + r * 128) + lane);
-        const __half2* wh = reinterpret_cast<const __half2*>(&wr);
-        const float2 w0 = __half22float2(wh[0]), w1 = __half22float2(wh[1]);
-        const float t0 = __half2float(__float2half_rn(f[i][0] * rstd * w0.x)), t1 = __half2float(__float2half_rn(f[i][1] * rstd * w0.y));
-        const float t2 = __half2float(__float2half_rn(f[i][2] * rstd * w1.x)), t3 = __half2float(__float2half_rn(f[i][3] * rstd * w1.y));
-        // H_128 along the row: strides 1 and 2 inside the lane, 4 .. 64 through shuffles
-        const float e0 = t0 + t1, e1 = t0 - t1, e2 = t2 + t3, e3 = t2 - t3;
-        float g[4] = {e0 + e2, e1 + e3, e0 - e2, e1 - e3};
-#pragma unroll
-        for (int mk = 1; mk < 32; mk <<= 1) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float o = __shfl_xor_sync(0xffffffffu, g[k], mk);
-            g[k] = (lane & mk) ? o - g[k] : g[k] + o;
-          }
-        }
-        *reinterpret_cast<float4*>(buf + r * 128 + 4 * lane) = make_float4(g[0], g[1], g[2], g[3]);
-      }
-    }
-    __syncthreads();
-    // H_S across the rows: thread (column, half of the output rows), four outputs at a time so that one shared-memory
-    // read feeds four independent accumulators; the sign is uniform over a warp (a constant-bank operand)
-    {
-      const int col = threadIdx.x & 127, ih = threadIdx.x >> 7;
-      const int per = (S + 1) / 2;
-      const int i0 = ih * per, i1 = min(S, i0 + per);
-      const float* tab = gin.table >= 0 ? c_dec_had[gin.table] : nullptr;
-      for (int i = i0; i < i1; i += 4) {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        const int r1 = min(i + 1, S - 1), r2 = min(i + 2, S - 1), r3 = min(i + 3, S - 1);
-        if (tab != nullptr) {
-#pragma unroll 4
-          for (int j = 0; j < S; ++j) {
-            const float b = buf[j * 128 + col];
-            a0 = fmaf(tab[i * S + j], b, a0); a1 = fmaf(tab[r1 * S + j], b, a1);
-            a2 = fmaf(tab[r2 * S + j], b, a2); a3 = fmaf(tab[r3 * S + j], b, a3);
-          }
-        } else {
-#pragma unroll 4
-          for (int j = 0; j < S; ++j) {
-            const float b = buf[j * 128 + col];
-            a0 += (__popc(i & j) & 1) ? -b : b; a1 += (__popc(r1 & j) & 1) ? -b : b;
-            a2 += (__popc(r2 & j) & 1) ? -b : b; a3 += (__popc(r3 & j) & 1) ? -b : b;
-          }
-        }
-        int8_t* o = sA + (int64_t)m * D + col;
-        o[i * 128] = (int8_t)round_away_s8(a0 * gin.had_scale);
-        if (i + 1 < i1) o[(i + 1) * 128] = (int8_t)round_away_s8(a1 * gin.had_scale);
-        if (i + 2 < i1) o[(i + 2) * 128] = (int8_t)round_away_s8(a2 * gin.had_scale);
-        if (i + 3 < i1) o[(i + 3) * 128] = (int8_t)round_away_s8(a3 * gin.had_scale);
-      }
-    }
-    __syncthreads();
+  for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+    const int r = min(warp + i * kHadWarps, S - 1);
+    yr[i] = __ldg(reinterpret_cast<const uint2*>(gin.y + (int64_t)row * gin.y_stride + r * 128) + lane);
+    zr[i] = __ldg(reinterpret_cast<const uint32_t*>(gin.z + (int64_t)row * gin.z_stride + r * 128) + lane);
   }
-  stream_columns<MB, S4>(L, cv, sA, rows);
+#pragma unroll
+  for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+    const int r = warp + i * kHadWarps;
+    const __half2* h = reinterpret_cast<const __half2*>(&yr[i]);
+    const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+    f[i][0] = a.x; f[i][1] = a.y; f[i][2] = b.x; f[i][3] = b.y;
+    const uint32_t zw = zr[i] ^ 0x80808080u;
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float hz = s8f(zw, e) * (0.5f * gin.z_scale);
+      f[i][e] *= fmaf(hz, tanh_approx(hz), hz);           // y * silu(z)
+      ss += f[i][e] * f[i][e];
+    }
+    if (r < S) {                                           // warp-uniform
+      ss = warp_sum_f(ss);
+      if (lane == 0) rowsum[r] = ss;
+    }
+  }
+  __syncthreads();
+  // group sums in a fixed order (no atomics: the result must not depend on which warp arrives first)
+  if (threadIdx.x < D / gin.group_size) {
+    const int rows_per_group = gin.group_size / 128;
+    float t = 0.f;
+    for (int r = 0; r < rows_per_group; ++r) t += rowsum[threadIdx.x * rows_per_group + r];
+    gsum[threadIdx.x] = t;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kMaxRowsPerWarp; ++i) {
+    const int r = warp + i * kHadWarps;
+    if (r < S) {
+      // normalise and round to fp16 as the separate norm kernel stores it
+      const float rstd = 1.0f / sqrtf(gsum[(r * 128) / gin.group_size] / (float)gin.group_size + gin.eps);
+      const uint2 wr = __ldg(reinterpret_cast<const uint2*>(gin.weight + r * 128) + lane);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+      const float2 w0 = __half22float2(wh[0]), w1 = __half22float2(wh[1]);
+      const float t0 = __half2float(__float2half_rn(f[i][0] * rstd * w0.x)), t1 = __half2float(__float2half_rn(f[i][1] * rstd * w0.y));
+      const float t2 = __half2float(__float2half_rn(f[i][2] * rstd * w1.x)), t3 = __half2float(__float2half_rn(f[i][3] * rstd * w1.y));
+      // H_128 along the row: strides 1 and 2 inside the lane, 4 .. 64 through shuffles
+      const float e0 = t0 + t1, e1 = t0 - t1, e2 = t2 + t3, e3 = t2 - t3;
+      float g[4] = {e0 + e2, e1 + e3, e0 - e2, e1 - e3};
+#pragma unroll
+      for (int mk = 1; mk < 32; mk <<= 1) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float o = __shfl_xor_sync(0xffffffffu, g[k], mk);
+          g[k] = (lane & mk) ? o - g[k] : g[k] + o;
+        }
+      }
+      *reinterpret_cast<float4*>(buf + r * 128 + 4 * lane) = make_float4(g[0], g[1], g[2], g[3]);
+    }
+  }
+  __syncthreads();
+  // output block iout of the S-point stage: one column per thread, four partial sums for instruction-level parallelism
+  {
+    const int col = threadIdx.x;
+    const float* tab = gin.table >= 0 ? c_dec_had[gin.table] + iout * S : nullptr;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int j = 0;
+    for (; j + 4 <= S; j += 4) {
+      const float b0 = buf[j * 128 + col], b1 = buf[(j + 1) * 128 + col], b2 = buf[(j + 2) * 128 + col], b3 = buf[(j + 3) * 128 + col];
+      if (tab != nullptr) {
+        a0 = fmaf(tab[j], b0, a0); a1 = fmaf(tab[j + 1], b1, a1); a2 = fmaf(tab[j + 2], b2, a2); a3 = fmaf(tab[j + 3], b3, a3);
+      } else {
+        a0 += (__popc(iout & j) & 1) ? -b0 : b0; a1 += (__popc(iout & (j + 1)) & 1) ? -b1 : b1;
+        a2 += (__popc(iout & (j + 2)) & 1) ? -b2 : b2; a3 += (__popc(iout & (j + 3)) & 1) ? -b3 : b3;
+      }
+    }
+    for (; j < S; ++j) {
+      const float b0 = buf[j * 128 + col];
+      if (tab != nullptr) a0 = fmaf(tab[j], b0, a0); else a0 += (__popc(iout & j) & 1) ? -b0 : b0;
+    }
+    out[(int64_t)row * out_stride + iout * 128 + col] = (int8_t)round_away_s8(((a0 + a1) + (a2 + a3)) * gin.had_scale);
+  }
 }
 
 int upload_tables() {
@@ -509,34 +507,26 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
   return QB_OK;
 }
 
-extern "C" int qb_decode_gate_had_linear(const qb_decode_gate_had_linear_args* a, void* stream) {
-  QB_REQUIRE(a != nullptr && a->y && a->z && a->norm_weight, QB_ERR_INVALID_ARG, "decode_gate_had_linear: null pointer");
-  QB_REQUIRE(a->rows >= 1 && a->rows <= kMaxRows, QB_ERR_UNSUPPORTED, "decode_gate_had_linear: 1 to %d rows", kMaxRows);
-  QB_REQUIRE(a->d > 0 && a->d % 128 == 0 && a->d == a->k, QB_ERR_UNSUPPORTED, "decode_gate_had_linear: d must be a multiple of 128 and equal k");
+extern "C" int qb_decode_gate_had_quant(const qb_decode_gate_had_quant_args* a, void* stream) {
+  QB_REQUIRE(a != nullptr && a->y && a->z && a->norm_weight && a->out, QB_ERR_INVALID_ARG, "decode_gate_had_quant: null pointer");
+  QB_REQUIRE(a->rows >= 1 && a->rows <= 65535, QB_ERR_INVALID_ARG, "decode_gate_had_quant: bad row count");
+  QB_REQUIRE(a->d > 0 && a->d % 128 == 0, QB_ERR_UNSUPPORTED, "decode_gate_had_quant: d must be a multiple of 128");
   const int S = a->d / 128;
   int table = -1;
   if (S == 12 || S == 20 || S == 28 || S == 40) table = S == 12 ? 0 : (S == 20 ? 1 : (S == 28 ? 2 : 3));
-  else QB_REQUIRE(S >= 1 && S <= 64 && (S & (S - 1)) == 0, QB_ERR_UNSUPPORTED, "decode_gate_had_linear: d / 128 must be 12, 20, 28, 40 or a power of two <= 64");
+  else QB_REQUIRE(S >= 1 && S <= 64 && (S & (S - 1)) == 0, QB_ERR_UNSUPPORTED, "decode_gate_had_quant: d / 128 must be 12, 20, 28, 40 or a power of two <= 64");
   QB_REQUIRE(a->group_size > 0 && a->d % a->group_size == 0 && a->group_size % 128 == 0 && a->d / a->group_size <= 64, QB_ERR_UNSUPPORTED,
-             "decode_gate_had_linear: the norm group size must be a multiple of 128 that divides d");
-  QB_REQUIRE(aligned(a->y, 16) && a->y_row_stride % 8 == 0 && aligned(a->z, 8) && a->z_row_stride % 8 == 0 && aligned(a->norm_weight, 16),
-             QB_ERR_INVALID_ARG, "decode_gate_had_linear: rows must be 16-byte aligned (z: 8)");
-  Linear L{};
-  int rc = fill_linear(L, a->w, a->s_channel_nat, a->s_tok, a->out, a->out_row_stride, a->n, a->k, a->w_is_s4, 0, "decode_gate_had_linear");
-  if (rc != QB_OK) return rc;
-  rc = upload_tables();
+             "decode_gate_had_quant: the norm group size must be a multiple of 128 that divides d");
+  QB_REQUIRE(aligned(a->y, 8) && a->y_row_stride % 4 == 0 && aligned(a->z, 4) && a->z_row_stride % 4 == 0 && aligned(a->norm_weight, 8) &&
+             a->out_row_stride >= a->d, QB_ERR_INVALID_ARG, "decode_gate_had_quant: rows must be 8-byte aligned (z: 4)");
+  int rc = upload_tables();
   if (rc != QB_OK) return rc;
   GateIn gin{};
   gin.y = static_cast<const __half*>(a->y); gin.z = a->z; gin.weight = static_cast<const __half*>(a->norm_weight);
   gin.y_stride = a->y_row_stride; gin.z_stride = a->z_row_stride; gin.d = a->d; gin.group_size = a->group_size; gin.special = S;
   gin.table = table; gin.z_scale = a->z_scale; gin.eps = a->eps; gin.had_scale = a->had_scale;
-  ConvEpi cv{};
-  const int mb = a->rows <= 2 ? a->rows : 4;
-  const size_t smem = (size_t)a->d * 4 + (size_t)mb * a->d;
-  const dim3 grid(grid_for(a->n, 2));
-  cudaStream_t st = (cudaStream_t)stream;
-  const int rows = a->rows;
-  QB_DISPATCH_MB_S4(decode_gate_had_linear_kernel, mb, a->w_is_s4 != 0, grid, smem, st, gin, L, cv, rows);
-  QB_LAUNCH_OK("decode_gate_had_linear_kernel");
+  launch_dependent(decode_gate_had_quant_kernel, dim3((unsigned)S, (unsigned)a->rows), dim3(kHadThreads), (size_t)a->d * 4,
+                   (cudaStream_t)stream, gin, a->out, a->out_row_stride);
+  QB_LAUNCH_OK("decode_gate_had_quant_kernel");
   return QB_OK;
 }

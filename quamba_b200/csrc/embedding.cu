@@ -14,6 +14,7 @@ template <int KIND>
 __global__ void __launch_bounds__(256)
 embedding_kernel(const void* __restrict__ table, const __half* __restrict__ scales, const int64_t* __restrict__ tokens,
                  __half* __restrict__ out, int64_t n_tokens, int dim, int vocab, int* __restrict__ status) {
+  if (gridDim.x <= 64) grid_dependency_launch();    // decode-sized: the next kernel may start its set-up already
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t tok = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);

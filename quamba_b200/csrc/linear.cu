@@ -157,11 +157,25 @@ gemm_s8_dp4a_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __r
 constexpr int kGemvWarps = 8;
 constexpr int kNW = 2;
 
+// L2 prefetch of weight rows n0 .. n0 + kNW - 1 (row_bytes each): issued ahead of the dependency wait.
+__device__ __forceinline__ void prefetch_rows(const void* W, int64_t pitch, int n0, int N, int row_bytes) {
+  const int lane = threadIdx.x & 31;
+  for (int j = 0; j < kNW; ++j) {
+    if (n0 + j >= N) break;
+    const uint8_t* rowp = static_cast<const uint8_t*>(W) + (int64_t)(n0 + j) * pitch;
+    for (int off = lane * 128; off < row_bytes; off += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + off));
+  }
+}
+
 template <int MB>
 __global__ void __launch_bounds__(kGemvWarps * 32, 3)
 gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restrict__ W, int64_t ldw, int M, int N, int K,
                Epilogue ep) {
-  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
+  // launched as a programmatic dependent: the next kernel may be scheduled at once, and this warp's first weight rows
+  // are requested from HBM before the wait for the kernel that produces A
+  grid_dependency_launch();
+  prefetch_rows(W, ldw, (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW, N, K);
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int chunks = K / 16;
   // The grid is one wave of CTAs (three per SM); a warp walks its column pairs with the grid's stride.  One CTA per 16
@@ -232,7 +246,9 @@ __global__ void w4a8_pack_nibbles_kernel(const int8_t* __restrict__ w8, uint32_t
 template <int MB>
 __global__ void __launch_bounds__(kGemvWarps * 32, 3)
 gemv_s4_kernel(const int8_t* __restrict__ A, int64_t lda, const uint8_t* __restrict__ W4, int M, int N, int K, Epilogue ep) {
-  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
+  grid_dependency_launch();
+  prefetch_rows(W4, K / 2, (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW, N, K / 2);
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int chunks = K / 32;              // 16 bytes of weights = 32 values per lane and step
   const int64_t ldw = K / 2;

@@ -390,7 +390,8 @@ sscan_update_warp_kernel(qb_sscan_update_args a, int tiles, int* status) {
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(128) uint8_t ring_all[];
   __shared__ __align__(8) uint64_t full_all[8][kWSlots];
-  grid_dependency_wait();   // launched as a programmatic dependent (launch_dependent)
+  grid_dependency_launch();   // one wave of CTAs by construction: let the next dependent start its own set-up
+  grid_dependency_wait();     // launched as a programmatic dependent (launch_dependent)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* ring = ring_all + warp * (kWSlots * kWTileBytes);
   uint64_t* full = full_all[warp];

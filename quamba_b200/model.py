@@ -129,7 +129,7 @@ class QuambaMixerModel(nn.Module):
         return {i: layer.allocate_inference_cache(batch_size, max_seqlen, dtype=dtype, **kwargs)
                 for i, layer in enumerate(self.layers)}
 
-    # ---- fused decode step (1 to 4 sequences): three launches per layer instead of seven ------------------------
+    # ---- fused decode step (1 to 4 sequences): four launches per layer instead of seven -------------------------
     def _decode_fusable(self, batch, lm_head):
         ok = self.__dict__.get("_fusable")
         if ok is None:
@@ -162,9 +162,9 @@ class QuambaMixerModel(nn.Module):
                                                       m.in_proj.prepared(), m.in_proj.input_scale, True, self.residual_in_fp32, conv)
             dt = zxbcdt[:, 2 * m.d_ssm + 2 * gn:2 * m.d_ssm + 2 * gn + m.nheads]
             y = s.update(ssm_state, conv["x"], dt, conv["B"], conv["C"], z=None)
-            h = ops.decode_gate_had_linear(y.flatten(-2), zxbcdt[:, :m.d_ssm], m.norm.z_scale, m.norm.weight, m.norm.eps,
-                                           m.norm.group_size or m.d_ssm, m.had.had_scale / m.had.x_H_scale,
-                                           m.out_proj.prepared(), m.out_proj.input_scale)[:, :m.d_model]
+            a = ops.decode_gate_had_quant(y.flatten(-2), zxbcdt[:, :m.d_ssm], m.norm.z_scale, m.norm.weight, m.norm.eps,
+                                          m.norm.group_size or m.d_ssm, m.had.had_scale / m.had.x_H_scale)
+            h = m.out_proj(a)
         logits, _ = ops.decode_norm_linear(h, residual, self.norm_f.weight, self.norm_f.eps, self.norm_f.output_scale,
                                            lm_head.prepared(), lm_head.input_scale, False, self.residual_in_fp32)
         return logits[:, :lm_head.out_features]

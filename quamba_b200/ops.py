@@ -813,15 +813,13 @@ def decode_norm_linear(x, residual, norm_weight, eps, norm_out_scale, prep, s_to
     return out, residual_out
 
 
-def decode_gate_had_linear(y, z, z_scale, norm_weight, eps, group_size, had_scale, prep, s_tok):
-    """y (rows, d) fp16, z (rows, d) int8 (a strided view is fine) -> gate, grouped RMSNorm, Hadamard, quantise, W4A8
-    product: (rows, n) fp16."""
+def decode_gate_had_quant(y, z, z_scale, norm_weight, eps, group_size, had_scale):
+    """y (rows, d) fp16, z (rows, d) int8 (a strided view is fine) -> gate, grouped RMSNorm, Hadamard rotation, int8:
+    QRMSNormGated (fp16 output) followed by QHadamard in one launch.  Returns (rows, d) int8."""
     rows, d = y.shape
-    w, s4 = _decode_weight(prep)
-    out = torch.empty((rows, prep.size_n), dtype=torch.float16, device=y.device)
-    args = _lib.make("qb_decode_gate_had_linear_args", y=_p(y), z=_p(z), norm_weight=_p(norm_weight), w=_p(w),
-                     s_channel_nat=_p(prep.sc), s_tok=_p(s_tok), out=_p(out), y_row_stride=y.stride(0), z_row_stride=z.stride(0),
-                     out_row_stride=out.stride(0), rows=rows, d=d, group_size=group_size, n=prep.size_n, k=prep.size_k,
-                     w_is_s4=s4, z_scale=float(z_scale), eps=float(eps), had_scale=float(had_scale))
-    _run("qb_decode_gate_had_linear", args, y)
+    out = torch.empty((rows, d), dtype=torch.int8, device=y.device)
+    args = _lib.make("qb_decode_gate_had_quant_args", y=_p(y), z=_p(z), norm_weight=_p(norm_weight), out=_p(out),
+                     y_row_stride=y.stride(0), z_row_stride=z.stride(0), out_row_stride=out.stride(0), rows=rows, d=d,
+                     group_size=group_size, z_scale=float(z_scale), eps=float(eps), had_scale=float(had_scale))
+    _run("qb_decode_gate_had_quant", args, y)
     return out

@@ -119,3 +119,46 @@ def w4a8_quantize(w: torch.Tensor, num_bits: int = 4, group_size: int = -1, s_gr
     packed = pack_int4(q, per_channel)       # on the weight's device: the index arithmetic is the same on CPU and GPU
     s_group, s_channel = permute_scales(s_group, s_channel, N, per_channel)
     return [t.to(w.device) for t in (w_ref, packed, s_group, s_channel)]
+
+
+def unpack_int4(packed: torch.Tensor, K: int, N: int, per_channel: bool) -> torch.Tensor:
+    """Inverse of :func:`pack_int4`: int32 (K/16, N*2) -> integer codes (K, N), 0..15 (per-group) or -8..7
+    (per-channel)."""
+    dev = packed.device
+    shifts = 4 * torch.arange(8, dtype=torch.int64, device=dev)
+    t = ((packed.to(torch.int64)[..., None] >> shifts) & 0xF).reshape(K // TILE, N * TILE)
+    perm = _weight_perm(per_channel).to(dev)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(perm.numel(), device=dev)
+    t = t.reshape(-1, perm.numel())[:, inv].reshape(K // TILE, N // TILE, TILE, TILE).permute(0, 2, 1, 3).reshape(K, N)
+    if per_channel:
+        t = torch.where(t >= 8, t - 16, t)
+    return t.to(torch.int32)
+
+
+def unpermute_scales(s_group: torch.Tensor, s_channel: torch.Tensor, N: int, per_channel: bool):
+    """Inverse of :func:`permute_scales`: natural column order."""
+    gp, sp = (t.to(s_channel.device) for t in _scale_perms())
+    inv_sp = torch.empty_like(sp); inv_sp[sp] = torch.arange(sp.numel(), device=sp.device)
+    s_channel = s_channel.reshape(-1, sp.numel())[:, inv_sp].reshape(-1, N).contiguous()
+    if not per_channel:
+        inv_gp = torch.empty_like(gp); inv_gp[gp] = torch.arange(gp.numel(), device=gp.device)
+        s_group = s_group.reshape(-1, gp.numel())[:, inv_gp].reshape(-1, N).contiguous()
+    return s_group, s_channel
+
+
+def repack(q: torch.Tensor, s_group: torch.Tensor, s_channel: torch.Tensor, per_channel: bool, pad_to: int = 64):
+    """Codes (K, N) + natural-order scales -> the packed buffers of a (possibly sliced) weight, N padded to a multiple
+    of ``pad_to`` with zero weights and 1e-6 channel scales as the reference pads (quamba/marlin_utils.py:258-263)."""
+    K, N = q.shape
+    pad = (pad_to - N % pad_to) % pad_to
+    if pad:
+        F = torch.nn.functional
+        q = F.pad(q, (0, pad), value=0 if per_channel else 8)
+        s_channel = F.pad(s_channel, (0, pad), value=1e-6)
+        if not per_channel:
+            s_group = F.pad(s_group, (0, pad))
+        N += pad
+    packed = pack_int4(q, per_channel)
+    s_group, s_channel = permute_scales(s_group, s_channel, N, per_channel)
+    return packed, s_group, s_channel, pad
