@@ -4,6 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --op NAME|all        # one kernel of the path on its own (bench_ops.py), one GPU
     python bench.py --op mixer_core      # the conv1d + SSD op-level configuration (bench_mixer_core.py)
+    python bench.py --gpus N (N >= 2)    # head-parallel Mamba2-8B prefill, strong scaling (bench_parallel.py)
 
 Workload (one "step" = one prefill): d_model 2560, 64 layers, expand 2 (80 heads x 64), ngroups 1, d_state 128,
 d_conv 4, vocab 50288, random-init weights N(0, 0.02) quantized to int4 (per output channel; ``--group-size 128`` for
@@ -235,6 +236,35 @@ def shares_table(agg):
             sorted(agg.items(), key=lambda kv: -kv[1][1])}
 
 
+def run_head_parallel(args, rank, local_rank, world, pk):
+    """N >= 2 (or --model 8b): the head-parallel Mamba2-8B prefill, strong scaling, one all-reduce per layer."""
+    import torch
+    import bench_parallel as bp
+    from quamba_b200 import _lib
+    r = bp.run(args, rank, local_rank, world, layers=args.layers if args.layers != MODEL["n_layer"] else None)
+    if rank != 0:
+        return
+    line = {
+        "metric": "prefill_tok_per_s", "value": r["value"], "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(1, min(args.warmup, 3)),
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 (int4 weights, int8 activations, int32 accumulate; fp16 / fp32 scan and norm math)", "data": "synthetic",
+        "config": {"workload": r["workload"] + ("" if r["layers"] == bp.CFG8B["n_layer"] else f" -- REDUCED to {r['layers']} layers (profiling case)"),
+                   "weights": "int4 per output channel", "parallelism": f"head-parallel tp{world}: in_proj column-parallel by SSD group, "
+                   "out_proj row-parallel, one NCCL all-reduce per layer in chunks of sequences overlapped with compute",
+                   "l2": "131072 tokens per step: every activation tensor is far larger than the 126 MB L2",
+                   "note": "at N = 1 bench.py reports the Mamba2-2.7B line (the metric's own configuration) and carries this workload's "
+                           "single-GPU time in its head_parallel_8b key: that is the base of this strong-scaling curve"},
+        "head_parallel_8b": r,
+        "e2e": {"value": r["value"], "unit": "tok/s", "h2d_bytes_per_step": bp.BATCH * bp.PROMPT * 8, "d2h_bytes_per_step": bp.BATCH * bp.CFG8B["vocab_size"] * 2,
+                "note": "token ids and last-token logits are 1 MB + 16 MB against a step of hundreds of ms: the end-to-end figure equals the device-timed one to three digits"},
+        "gpu_launches": args.steps * r["layers"] * (bp.BATCH // r["chunk_sequences"]) * 8,
+        "roofline": {"kernel": "gemm_s8_tcgen05 (in_proj + out_proj shards)", "bound": "tensor", "achieved": r["gemm_tops_per_gpu"], "peak": pk["i8"],
+                     "unit": "TOP/s", "frac": r["gemm_tops_per_gpu"] / pk["i8"], "traffic": None, "peak_source": pk["i8_source"],
+                     "note": "GEMM flops of the step per GPU over the compute-only step time (all kernels, no collective)"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
@@ -244,6 +274,11 @@ def run_ours(args, rank, local_rank, world):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
+    if world > 1 or args.model == "8b":
+        run_head_parallel(args, rank, local_rank, world, pk)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     model = build_model(dev, args.group_size, seed=rank, n_layer=args.layers)
     r = measure(model, args, dev, rank, world, args.group_size)
     extra = None
@@ -294,6 +329,16 @@ def run_ours(args, rank, local_rank, world):
     if extra is not None:
         line["group128"] = {"value": tokens / (extra["ms_prefill"] * 1e-3), "unit": "tok/s", "tpot_ms": extra["tpot_ms"],
                             "e2e": tokens / (extra["ms_e2e"] * 1e-3), "shares_decode_step": shares_table(extra["shares_d"])}
+    if world == 1 and not args.no_8b_base:
+        # the single-GPU base of the head-parallel strong-scaling curve that bench.py --gpus N (N >= 2) reports
+        try:
+            del model
+            torch.cuda.empty_cache()
+            import bench_parallel as bp
+            base_args = argparse.Namespace(steps=max(2, min(args.steps, 4)), warmup=1)
+            line["head_parallel_8b"] = bp.run(base_args, 0, local_rank, 1)
+        except Exception as e:      # never lose the main line to the extra measurement
+            line["head_parallel_8b"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     if world == 1 and not args.no_cpu_baseline:
         tok_s, t_full, sample = cpu_sample()
         line["cpu_baseline"] = {"value": tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
@@ -314,6 +359,8 @@ def main():
     ap.add_argument("--group-size", type=int, default=-1, choices=[-1, 128], help="int4 weight format: per output channel or group 128")
     ap.add_argument("--also-group128", action="store_true", help="measure the group-128 weight format too (second model build)")
     ap.add_argument("--layers", type=int, default=MODEL["n_layer"], help="fewer layers = a reduced profiling case, flagged in config")
+    ap.add_argument("--model", default="2.7b", choices=["2.7b", "8b"], help="8b: the head-parallel Mamba2-8B prefill (always used for --gpus >= 2)")
+    ap.add_argument("--no-8b-base", action="store_true", help="skip the single-GPU Mamba2-8B measurement added to the 2.7B line")
     ap.add_argument("--seqlen", type=int, default=PROMPT)
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
     args = ap.parse_args()

@@ -1,0 +1,152 @@
+"""Head-parallel Mamba2-8B prefill behind ``bench.py --gpus N`` (N >= 2) and ``bench.py --model 8b``.
+
+Workload (strong scaling: the same job on 1, 2, 4 or 8 GPUs): Quamba2 Mamba2-8B W4A8 geometry -- d_model 4096, 56 layers,
+expand 2 (128 heads x 64), ngroups 8, d_state 128, d_conv 4, vocab 256000, random-init weights N(0, 0.02) quantized to
+int4 per output channel, int8 activations with static scales calibrated on 4 random sequences -- batch 32, prefill of
+4096 uniform-random token ids.  Every rank holds all token rows and 1/T of every layer's heads (in_proj column-parallel by
+SSD group, conv / SSD / gated norm local, block-diagonal Hadamard, out_proj row-parallel); the only collective is one NCCL
+all-reduce of the (tokens, 4096) fp16 layer output per layer, issued per chunk of sequences so that the reduction of one
+chunk overlaps the compute of the next.  Embedding, block norms and the head are replicated.
+
+The model is built layer by layer (float layer -> calibration taps on the running calibration batch -> quantise -> cut
+this rank's shard -> drop the rest), identically on every rank from one seed.
+"""
+import time
+
+import torch
+import torch.distributed as dist
+
+CFG8B = dict(d_model=4096, n_layer=56, vocab_size=256000, d_state=128, d_conv=4, expand=2, headdim=64, ngroups=8, chunk_size=256)
+BATCH, PROMPT, HAD_BLOCKS = 32, 4096, 8
+WORKLOAD8B = ("configs[4]: Quamba2 Mamba2-8B W4A8 (d_model 4096, 56 layers, 128 heads x 64, ngroups 8, d_state 128, vocab 256000), "
+              "head-parallel, batch 32, prefill 4096 token ids")
+
+
+class Stack:
+    """This rank's share of the model: replicated embedding / norms / head, sharded mixers."""
+
+    def __init__(self, cfg, rank, world, dev, seed=0, calib_len=512, calib_seqs=4):
+        from quamba_b200 import calibrate as cal
+        from quamba_b200.embedding import F16Embedding
+        from quamba_b200.mixer import W4A8QMamba2
+        from quamba_b200.modules import W4A8B16O16Linear
+        from quamba_b200.norm import QRMSNorm
+        from quamba_b200.parallel import shard_mixer
+        self.cfg, self.rank, self.world, self.dev = cfg, rank, world, dev
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        d, V = cfg["d_model"], cfg["vocab_size"]
+        table = (torch.randn(V, d, generator=gen, device=dev) * 0.02).half()
+        self.embedding = F16Embedding(V, d, device=dev)
+        self.embedding.weight.data = table
+        ids = torch.randint(0, V, (calib_seqs, calib_len), generator=gen, device=dev)
+        h = table[ids]
+        residual = torch.zeros_like(h, dtype=torch.float32)
+        self.norms, self.shards = [], []
+        ssm = {k: cfg[k] for k in ("d_state", "d_conv", "expand", "headdim", "ngroups", "chunk_size")}
+        for i in range(cfg["n_layer"]):
+            fl = cal.Mamba2Float(d, layer_idx=i, w4_group_size=-1, had_blocks=HAD_BLOCKS, generator=gen, device=dev, **ssm).half()
+            norm = cal.RMSNormFloat(d).to(dev)
+            taps = {}
+            residual = residual + h.float()
+            with torch.no_grad():
+                h = fl(norm(residual).half(), taps)
+            s = {k: (v / 127.0).clamp(min=1e-8).float().reshape(1) for k, v in taps.items()}
+            sc = {"in_proj:input": s["in_proj:input"], "out_proj:input": s["out_proj:input"], "ssm_state_act:input": s["ssm_state_act"]}
+            for name in ("x_conv_in", "B_conv_in", "C_conv_in", "x_conv_out", "B_conv_out", "C_conv_out", "dt_act", "z_act"):
+                sc[name + ":input"] = sc[name + ":output"] = s[name]
+            full = W4A8QMamba2.from_fp16(fl, sc)
+            self.norms.append(QRMSNorm.from_fp16(norm, output_scale=sc["in_proj:input"].item()))
+            self.shards.append(shard_mixer(full, rank, world))
+            del fl, full
+        residual = residual + h.float()
+        norm_f = cal.RMSNormFloat(d).to(dev)
+        head_scale = (norm_f(residual[:, -1:]).abs().amax() / 127.0).clamp(min=1e-8).float().reshape(1)
+        self.norm_f = QRMSNorm.from_fp16(norm_f, output_scale=head_scale.item())
+        head = torch.nn.Linear(d, V, bias=False, device=dev, dtype=torch.float16)
+        head.weight.data = (torch.randn(V, d, generator=gen, device=dev) * 0.02).half()
+        head.w4_group_size = -1
+        self.lm_head = W4A8B16O16Linear.from_fp16(head, head_scale)
+        del head, table
+        torch.cuda.empty_cache()
+
+    @torch.no_grad()
+    def prefill(self, ids, chunk_seqs, collective=True, compute=True):
+        """ids (batch, L) on the device -> last-token logits (batch, vocab).  ``collective`` / ``compute`` switch the two
+        halves off for the separate timings."""
+        chunks = list(ids.split(chunk_seqs))
+        n = len(chunks)
+        h = [self.embedding(c) for c in chunks]
+        res = [None] * n
+        pending = [None] * n
+        for norm, shard in zip(self.norms, self.shards):
+            for c in range(n):
+                if pending[c] is not None:
+                    pending[c].wait()
+                    pending[c] = None
+                if compute:
+                    q, res[c] = norm(h[c], residual=res[c], prenorm=True, residual_in_fp32=True)
+                    h[c] = shard(q)
+                if collective and self.world > 1:
+                    if not h[c].is_contiguous():
+                        h[c] = h[c].contiguous()
+                    pending[c] = dist.all_reduce(h[c], async_op=True)
+        for c in range(n):
+            if pending[c] is not None:
+                pending[c].wait()
+        if not compute:
+            return None
+        last = torch.cat([self.norm_f(h[c][:, -1:], residual=res[c][:, -1:], prenorm=False, residual_in_fp32=True) for c in range(n)])
+        return self.lm_head(last)[:, -1]
+
+
+def run(args, rank, local_rank, world, layers=None):
+    """Times the head-parallel prefill; returns the result dict on rank 0 (None elsewhere)."""
+    from quamba_b200 import _lib
+    from quamba_b200.sharding import max_over_ranks
+    dev = torch.device("cuda", local_rank)
+    cfg = dict(CFG8B, n_layer=layers or CFG8B["n_layer"])
+    t0 = time.time()
+    stack = Stack(cfg, rank, world, dev)
+    build_s = time.time() - t0
+    g = torch.Generator().manual_seed(99)
+    ids = [torch.randint(0, cfg["vocab_size"], (BATCH, PROMPT), generator=g).to(dev) for _ in range(2)]
+    chunk_seqs = 8 if world > 1 else 4
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(steps, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(steps):
+            stack.prefill(ids[i % 2], chunk_seqs, **kw)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
+    steps = max(1, args.steps)
+    for _ in range(max(2, min(args.warmup, 3))):
+        logits = stack.prefill(ids[0], chunk_seqs)
+    barrier()
+    _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+    ms_step = timed(steps)
+    ms_compute = timed(max(1, steps // 2), collective=False)
+    ms_comm = timed(max(1, steps // 2), compute=False) if world > 1 else 0.0
+    ms_step, ms_compute, ms_comm = max_over_ranks([ms_step, ms_compute, ms_comm], device=dev)
+    if rank != 0:
+        return None
+    tokens = BATCH * PROMPT
+    D, G, N, H = cfg["d_model"] * cfg["expand"], cfg["ngroups"], cfg["d_state"], cfg["d_model"] * cfg["expand"] // cfg["headdim"]
+    flops = cfg["n_layer"] * 2 * tokens * cfg["d_model"] * (2 * D + 2 * G * N + H + D)
+    reduce_bytes = cfg["n_layer"] * tokens * cfg["d_model"] * 2
+    return {"value": tokens / (ms_step * 1e-3), "unit": "tok/s", "ms_per_step": ms_step, "compute_only_ms": ms_compute,
+            "allreduce_alone_ms": ms_comm, "allreduce_exposed_ms": max(0.0, ms_step - ms_compute) if world > 1 else 0.0,
+            "allreduce_share_of_step": max(0.0, ms_step - ms_compute) / ms_step if world > 1 else 0.0,
+            "allreduce_bytes_per_step": reduce_bytes if world > 1 else 0,
+            "allreduce_bus_gbs": (2 * (world - 1) / world * reduce_bytes / (ms_comm * 1e-3) / 1e9) if world > 1 and ms_comm > 0 else None,
+            "gemm_flops_per_step": flops, "gemm_tops_per_gpu": flops / world / (ms_compute * 1e-3) / 1e12,
+            "chunk_sequences": chunk_seqs, "layers": cfg["n_layer"], "build_seconds": build_s, "workload": WORKLOAD8B,
+            "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}

@@ -44,8 +44,9 @@ def _gate_rotate_project(m, y16, z8):
     n = m.norm
     yn, _ = onorm.qlayer_normgated_fwd(y16, n.weight, None, n.eps, q_z=z8, z_scale=n.z_scale, use_float16_output=True,
                                        group_size=n.group_size, norm_before_gate=n.norm_before_gate, is_rms_norm=True)
-    q, _ = ohad.quant_hadamard(yn, m.had.had_scale / m.had.x_H_scale)
-    return _w4a8(m.out_proj, q, False)
+    blocks = getattr(m.had, "blocks", 1)          # block-diagonal rotation: each slice of the row on its own
+    q, _ = ohad.quant_hadamard(yn.reshape(-1, yn.shape[-1] // blocks), m.had.had_scale / m.had.x_H_scale)
+    return _w4a8(m.out_proj, q.reshape(yn.shape), False)
 
 
 def mixer_step(m, u_int8, conv_state, ssm_state):

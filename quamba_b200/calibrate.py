@@ -71,8 +71,9 @@ class Mamba2Float(nn.Module):
     points.  ``taps`` (dict name -> running absmax) is filled when given."""
 
     def __init__(self, d_model, d_state=128, d_conv=4, expand=2, headdim=64, ngroups=1, chunk_size=256, layer_idx=None,
-                 w4_group_size=None, generator=None, device=None):
+                 w4_group_size=None, had_blocks=1, generator=None, device=None):
         super().__init__()
+        self.had_blocks = had_blocks        # block-diagonal out_proj rotation (head-parallel serving), 1 = one full rotation
         self.d_model, self.d_state, self.d_conv, self.expand, self.headdim = d_model, d_state, d_conv, expand, headdim
         self.d_inner = self.d_ssm = expand * d_model
         self.ngroups, self.nheads = ngroups, self.d_ssm // headdim
@@ -126,7 +127,7 @@ class Mamba2Float(nn.Module):
         if state is not None:
             state["ssm"] = last
         y = self.norm(y.flatten(-2), z.float())
-        y = tap("out_proj:input", hadamard_transform(y))
+        y = tap("out_proj:input", hadamard_transform(y.unflatten(-1, (self.had_blocks, -1))).flatten(-2))
         return self.out_proj(y.to(u.dtype))
 
 
@@ -136,7 +137,7 @@ class Mamba2LMFloat(nn.Module):
     quantized head cannot share storage, so the reference unties them before quantisation as well."""
 
     def __init__(self, d_model=2560, n_layer=64, vocab_size=50288, d_state=128, d_conv=4, expand=2, headdim=64, ngroups=1,
-                 chunk_size=256, w4_group_size=None, seed=0, device=None, dtype=torch.float32):
+                 chunk_size=256, w4_group_size=None, had_blocks=1, seed=0, device=None, dtype=torch.float32):
         super().__init__()
         gen = torch.Generator(device=device or "cpu").manual_seed(seed)
         self.d_model, self.n_layer, self.vocab_size = d_model, n_layer, vocab_size
@@ -150,7 +151,7 @@ class Mamba2LMFloat(nn.Module):
         if w4_group_size is not None:
             self.lm_head.w4_group_size = w4_group_size
         self.norms = nn.ModuleList([RMSNormFloat(d_model).to(device) for _ in range(n_layer)])
-        self.mixers = nn.ModuleList([Mamba2Float(d_model, layer_idx=i, w4_group_size=w4_group_size, generator=gen,
+        self.mixers = nn.ModuleList([Mamba2Float(d_model, layer_idx=i, w4_group_size=w4_group_size, had_blocks=had_blocks, generator=gen,
                                                  device=device, **self.ssm_cfg) for i in range(n_layer)])
         self.norm_f = RMSNormFloat(d_model).to(device)
         self.to(dtype)

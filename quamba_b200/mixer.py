@@ -102,7 +102,7 @@ class _QMamba2(nn.Module):
             B_scale=act_scales["B_conv_out:input"], C_scale=act_scales["C_conv_out:input"],
             ssm_state_scale=act_scales["ssm_state_act:input"], dt_limit=o.dt_limit)
         q.norm = QRMSNormGated.from_fp16(o.norm, z_scale=act_scales["z_act:output"].item(), use_float16_output=True)
-        q.had.x_H_scale = act_scales["out_proj:input"].item()
+        q.had = QHadamard(q.d_inner, x_H_scale=act_scales["out_proj:input"].item(), blocks=getattr(o, "had_blocks", 1))
         return q
 
     # ---- prefill (qMamba2.py:920-994) ------------------------------------------------------------------------------

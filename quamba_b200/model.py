@@ -141,6 +141,7 @@ class QuambaMixerModel(nn.Module):
                 s = m.d_inner // 128 if isinstance(m, W4A8QMamba2) else 0
                 ok = bool(ok and isinstance(m, W4A8QMamba2) and layer.norm.output_scale and m.conv1d.x_head_group_range is None
                           and m.d_conv == 4 and m.d_inner == m.d_ssm and m.d_inner % 128 == 0 and not m.D_has_hdim
+                          and getattr(m.had, "blocks", 1) == 1
                           and (s in (12, 20, 28, 40) or (s & (s - 1)) == 0 and s <= 64)
                           and m.d_model % 32 == 0 and m.d_ssm // m.ngroups % 128 == 0 and m.ngroups <= 64)
             self.__dict__["_fusable"] = ok

@@ -262,19 +262,27 @@ class QHadamard(_FloatStateMixin, nn.Module):
     """Normalised Hadamard transform of the last dimension fused with int8 quantisation."""
     _float_state = ("x_H_scale",)
 
-    def __init__(self, dim, x_H_scale=1.0):
+    def __init__(self, dim, x_H_scale=1.0, blocks=1):
+        """``blocks`` > 1 rotates each of ``blocks`` equal slices of the last dimension on its own (the block-diagonal
+        I_blocks (x) H_{dim / blocks}), which is what lets out_proj be cut row-wise across GPUs; 1 is the reference's
+        layer."""
         super().__init__()
-        self.dim = dim
+        assert dim % blocks == 0
+        self.dim, self.blocks = dim, blocks
         self.x_H_scale = x_H_scale
-        self.transform_fn, self.N, self.had_scale = get_qhad_fn(dim)
+        self.transform_fn, self.N, self.had_scale = get_qhad_fn(dim // blocks)
         self._install_float_state()
 
     @torch.no_grad()
     def forward(self, x):
-        return self.transform_fn(x, self.had_scale / self.x_H_scale)
+        scale = self.had_scale / self.x_H_scale
+        if self.blocks == 1:
+            return self.transform_fn(x, scale)
+        shape = x.shape
+        return self.transform_fn(x.reshape(-1, self.dim // self.blocks), scale).reshape(shape)
 
     def __repr__(self):
-        return f"QHadamard(dim={self.dim})"
+        return f"QHadamard(dim={self.dim})" if self.blocks == 1 else f"QHadamard(dim={self.dim}, blocks={self.blocks})"
 
 
 # ------------------------------------------------------------------------------------------------ Mamba1 scan

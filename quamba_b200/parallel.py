@@ -1,0 +1,144 @@
+"""Head-parallel Mamba2 layers across the GPUs of one node: in_proj column-parallel by SSD group, conv / SSD / gated
+norm local to a rank's heads, a block-diagonal Hadamard rotation, out_proj row-parallel, and ONE all-reduce (sum) of the
+(tokens, d_model) fp16 layer output per layer over NCCL.
+
+The reference has no tensor parallelism (its mixers assert ``process_group is None``, quamba/qMamba2.py:84-88); the cut
+follows how its layer is organised: the in_proj columns are [z | x | B | C | dt] (qMamba2.py:798-800), B / C and the gated
+norm are per SSD group (norm group size d_ssm / ngroups), so a rank that owns whole groups needs nothing from its peers
+until out_proj's contraction over d_inner.  The out_proj input rotation becomes I_T (x) H_{d_inner / T}: a model meant to
+be served this way is quantised with that block rotation (``QHadamard(blocks=T)``), and its single-GPU form computes
+exactly the same function.
+
+Shards are cut from the quantised layer: int4 codes and scales are unpacked, sliced and re-packed, so every rank multiplies
+with the very integers of the unsharded layer (a per-rank re-quantisation would change the channel scales).
+"""
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import packing
+from .mixer import W4A8QMamba2, _QMamba2
+from .modules import QHadamard, Quamb2Conv1D, Quamba2ChunkScan, W4A8B8O8LinearParallel, W4A8B16O16Linear
+from .norm import QRMSNormGated
+
+__all__ = ["shard_w4a8_columns", "shard_w4a8_rows", "shard_mixer", "HeadParallelMixer", "rank_columns"]
+
+
+def _codes(lin):
+    per_channel = lin.s_group.numel() == 0
+    q = packing.unpack_int4(lin.weight, lin.size_k, lin.size_n, per_channel)
+    sg, sc = packing.unpermute_scales(lin.s_group, lin.s_channel, lin.size_n, per_channel)
+    return q, sg, sc, per_channel
+
+
+def _rebuild(cls, q, sg, sc, per_channel, in_features, out_features, input_scale, device):
+    packed, sg, sc, pad = packing.repack(q, sg, sc, per_channel)
+    lin = cls(in_features, out_features, group_size=128, device=device)
+    assert lin.pad_out == pad and lin.size_n == out_features + pad
+    lin.weight, lin.s_channel, lin.input_scale = packed, sc, input_scale.clone()
+    lin.s_group = sg if not per_channel else torch.empty(0, dtype=torch.float16, device=device)
+    return lin
+
+
+def shard_w4a8_columns(lin, cols: torch.Tensor):
+    """The linear layer that produces output columns ``cols`` (a 1-D index tensor) of ``lin``."""
+    q, sg, sc, pc = _codes(lin)
+    cols = cols.to(q.device)
+    return _rebuild(type(lin), q[:, cols], sg if pc else sg[:, cols], sc[:, cols], pc, lin.in_features, cols.numel(),
+                    lin.input_scale, q.device)
+
+
+def shard_w4a8_rows(lin, k0: int, k1: int):
+    """The linear layer that contracts input features [k0, k1) of ``lin`` (a partial sum of its output)."""
+    q, sg, sc, pc = _codes(lin)
+    assert pc or (k0 % 128 == 0 and k1 % 128 == 0), "row cuts must fall on weight-group boundaries"
+    out = lin.out_features
+    return _rebuild(type(lin), q[k0:k1, :out], sg if pc else sg[k0 // 128:k1 // 128, :out], sc[:, :out], pc, k1 - k0, out,
+                    lin.input_scale, q.device)
+
+
+def rank_columns(m, rank, world):
+    """Column indices of in_proj ([z | x | B | C | dt]) that rank ``rank`` of ``world`` owns, as five index ranges."""
+    G, N, D, H = m.ngroups, m.d_state, m.d_ssm, m.nheads
+    assert G % world == 0, "head parallelism cuts by SSD group: ngroups must be divisible by the number of ranks"
+    d, gn, h = D // world, G // world * N, H // world
+    z0, x0, b0, c0, t0 = 0, D, 2 * D, 2 * D + G * N, 2 * D + 2 * G * N
+    return [torch.arange(z0 + rank * d, z0 + (rank + 1) * d), torch.arange(x0 + rank * d, x0 + (rank + 1) * d),
+            torch.arange(b0 + rank * gn, b0 + (rank + 1) * gn), torch.arange(c0 + rank * gn, c0 + (rank + 1) * gn),
+            torch.arange(t0 + rank * h, t0 + (rank + 1) * h)]
+
+
+@torch.no_grad()
+def shard_mixer(m: W4A8QMamba2, rank: int, world: int):
+    """Rank ``rank``'s share of a W4A8QMamba2 whose Hadamard rotation has ``world`` blocks (or a multiple)."""
+    blocks = getattr(m.had, "blocks", 1)
+    assert blocks % world == 0, "quantise the model with QHadamard(blocks=T) for T-way head parallelism"
+    dev = m.out_proj.weight.device
+    T = world
+    D, H, G, N, P = m.d_ssm // T, m.nheads // T, m.ngroups // T, m.d_state, m.headdim
+    parts = rank_columns(m, rank, T)
+    s = _QMamba2.__new__(W4A8QMamba2)
+    nn.Module.__init__(s)
+    for k in ("d_model", "d_state", "d_conv", "conv_init", "expand", "headdim", "D_has_hdim", "rmsnorm", "norm_before_gate",
+              "dt_limit", "activation", "chunk_size", "use_mem_eff_path", "layer_idx", "sequence_parallel"):
+        setattr(s, k, getattr(m, k))
+    s.process_group, s.world_size, s.local_rank = None, T, rank
+    s.d_inner = s.d_ssm = D
+    s.ngroups, s.nheads = G, H
+    s.in_proj = shard_w4a8_columns(m.in_proj, torch.cat(parts))
+    s.out_proj = shard_w4a8_rows(m.out_proj, rank * D, (rank + 1) * D)
+    # conv1d: channels [x | B | C] of this rank's groups
+    c = m.conv1d
+    ch = (torch.cat(parts[1:4]) - m.d_ssm).to(dev)          # conv channel c is in_proj column d_ssm + c
+    grouped = c.x_head_group_range is not None
+    sc = Quamb2Conv1D(D, P, N, G, c.x_nhead_group if grouped else 0, c.x_ndim_group if grouped else 0, ch.numel(), ch.numel(),
+                      c.kernel_size, groups=ch.numel(), padding=c.padding, bias=c.bias, device=dev)
+    sc.weight, sc.bias = c.weight[ch].contiguous(), None if c.bias is None else c.bias[ch].contiguous()
+    for k in sc._float_names():
+        setattr(sc, k, getattr(c, k))
+    gs = slice(rank * G, (rank + 1) * G)
+    if grouped:
+        sc.x_head_group_range, sc.x_dim_group_range = c.x_head_group_range[gs].contiguous(), c.x_dim_group_range[gs].contiguous()
+        sc.x_out_scales, sc.B_out_scales, sc.C_out_scales = (t[gs].contiguous() for t in (c.x_out_scales, c.B_out_scales, c.C_out_scales))
+    else:
+        sc.x_out_scales, sc.B_out_scales, sc.C_out_scales = c.x_out_scales, c.B_out_scales, c.C_out_scales
+    s.conv1d = sc
+    # SSD: heads of this rank
+    q = m.qchunk_scan
+    hs = slice(rank * H, (rank + 1) * H)
+    ss = Quamba2ChunkScan(D, P, N, G, q.D_has_hdim, q.chunk_size, q.nhead_groups, q.ndim_groups, q.delta_softplus, dt_limit=q.dt_limit,
+                          device=dev)
+    ss.dt_bias, ss.A_log, ss.A_log_scale = q.dt_bias[hs].contiguous(), q.A_log[hs].contiguous(), q.A_log_scale
+    ss.D = q.D.reshape(m.nheads, -1)[hs].reshape(-1).contiguous() if q.D is not None else None
+    ss.D_scale, ss.dt_scale, ss.z_scale = q.D_scale, q.dt_scale, q.z_scale
+    if q.grouped:
+        ss.x_scales, ss.ssm_state_scale = q.x_scales[gs].contiguous(), q.ssm_state_scale[gs].contiguous()
+        ss.x_head_group_range, ss.x_dim_group_range = q.x_head_group_range[gs].contiguous(), q.x_dim_group_range[gs].contiguous()
+        ss.B_scale, ss.C_scale = q.B_scale[gs].contiguous(), q.C_scale[gs].contiguous()
+    else:
+        ss.x_scales, ss.ssm_state_scale, ss.B_scale, ss.C_scale = q.x_scales, q.ssm_state_scale, q.B_scale, q.C_scale
+    s.qchunk_scan = ss
+    n = m.norm
+    sn = QRMSNormGated(D, eps=n.eps, group_size=n.group_size, norm_before_gate=n.norm_before_gate, use_float16_output=True, device=dev)
+    sn.weight, sn.z_scale, sn.output_scale = n.weight[rank * D:(rank + 1) * D].contiguous(), n.z_scale, n.output_scale
+    s.norm = sn
+    s.had = QHadamard(D, x_H_scale=m.had.x_H_scale, blocks=blocks // T)
+    return s
+
+
+class HeadParallelMixer(nn.Module):
+    """A rank's shard plus the layer's one collective: forward returns the all-reduced (tokens, d_model) fp16 output.
+    ``async_op=True`` returns (partial output tensor, work handle) so that a caller can overlap the reduction of one
+    token chunk with the compute of the next."""
+
+    def __init__(self, shard, process_group=None):
+        super().__init__()
+        self.shard, self.process_group = shard, process_group
+
+    @torch.no_grad()
+    def forward(self, u, async_op=False, **kwargs):
+        out = self.shard(u, **kwargs)
+        if not out.is_contiguous():
+            out = out.contiguous()
+        work = dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.process_group, async_op=async_op)
+        return (out, work) if async_op else out
