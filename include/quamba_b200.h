@@ -37,6 +37,14 @@ const char* qb_last_error(void);
 int qb_abi_version(void);
 /* sizeof() of an argument struct by name, for binding self-checks; -1 if unknown. */
 int64_t qb_sizeof(const char* struct_name);
+/* Cross-check switches: a bit set here sends the op to its portable twin (the five-stage SSD path, the SIMT Hadamard
+ * kernel, the 128 x 128 GEMM kernel, the CTA-tile state update) so that two implementations can be compared on one
+ * device.  Process-wide, off by default, never read from the environment.  Returns the previous mask. */
+#define QB_PATH_SSD_PORTABLE 1
+#define QB_PATH_HADAMARD_SIMT 2
+#define QB_PATH_GEMM_SMALL_TILES 4
+#define QB_PATH_UPDATE_CTA_TILES 8
+int qb_set_path_override(int mask);
 /* Synchronises `stream`, then returns and clears the device status word: QB_OK, or QB_ERR_TIMEOUT
  * if a kernel gave up on a bounded wait (its outputs are then undefined).  The only entry point
  * that blocks the host. */

@@ -119,5 +119,23 @@ def call(fn: str, args, stream: int):
     _trace.append((fn, e0, e1))
 
 
+PATH_SSD_PORTABLE, PATH_HADAMARD_SIMT, PATH_GEMM_SMALL_TILES, PATH_UPDATE_CTA_TILES = 1, 2, 4, 8
+
+
+class path_override:
+    """``with path_override(PATH_SSD_PORTABLE): ...`` runs the enclosed calls on the portable twin of an op (a
+    cross-check facility of the library, see qb_set_path_override in the header)."""
+
+    def __init__(self, mask):
+        self.mask = mask
+
+    def __enter__(self):
+        self.prev = lib().qb_set_path_override(self.mask)
+        return self
+
+    def __exit__(self, *exc):
+        lib().qb_set_path_override(self.prev)
+
+
 def read_device_status(stream: int):
     check(lib().qb_read_device_status(ctypes.c_void_p(stream)))

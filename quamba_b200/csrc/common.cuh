@@ -67,10 +67,28 @@ inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 }
 #endif
 
+// Cross-check switches (qb_set_path_override): each bit sends an op to its portable twin so that two implementations can be
+// compared on one device.  Off by default; set explicitly through the C ABI, never read from the environment.
+bool path_override(int bit);
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count();  // multiprocessor count of the current device (cached per device)
+
+// One-time-per-device guard for cudaFuncSetAttribute calls: kernel attributes belong to a device, so a process that
+// drives several GPUs must set them on each.  Returns true the first time it is asked about the current device.
+// (Two host threads asking at once may both get true: the attribute is then set twice to the same value, which is fine.)
+struct PerDeviceOnce {
+  bool done[64] = {};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
 
 // ---- device helpers ------------------------------------------------------------------------
 #ifdef __CUDACC__

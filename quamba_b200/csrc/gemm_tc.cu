@@ -389,7 +389,7 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
   static bool attr_set[64] = {};
   int dev = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
-  static const bool no_persistent = getenv("QB_GEMM_SMALL_TILES") != nullptr;
+  const bool no_persistent = path_override(QB_PATH_GEMM_SMALL_TILES);
   const int64_t ptiles = ceil_div(M, BM) * ceil_div(N, PBN);
   if (!no_persistent && ptiles >= sm_count()) {   // enough 128 x 256 tiles to give every SM at least one
     // tile width: the one whose rounds of the grid cost least (rounds x width); ties go to the wider tile.  Only multiples

@@ -202,8 +202,7 @@ extern "C" int qb_hadamard_quant(const qb_hadamard_quant_args* a, void* stream) 
                      ((a->x_row_stride * esz) % 16 == 0) && (a->out_row_stride % 16 == 0);
   cudaStream_t st = (cudaStream_t)stream;
   {  // tensor-core path (fp16 rows of S * 128 elements, contiguous); the kernels below are the general fallback
-    static const bool force_simt = getenv("QB_HADAMARD_SIMT") != nullptr;
-    if (!force_simt && aligned(a->out, 1)) {
+    if (!path_override(QB_PATH_HADAMARD_SIMT) && aligned(a->out, 1)) {
       const int rc = hadamard_tc_launch(a, st);
       if (rc != QB_ERR_UNSUPPORTED) return rc;
     }

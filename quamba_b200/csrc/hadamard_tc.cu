@@ -314,11 +314,8 @@ int launch_one(const qb_hadamard_quant_args* a, const unsigned long long* masks,
   int rc = encode_tmap_2d_u8(&tm, a->x, (uint64_t)a->rows * S, 256, 256, N1, 128);
   if (rc != QB_OK) return rc;
   auto kern = hadamard_tc_kernel<S, SPAD, R>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    QB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    attr_done = true;
-  }
+  static PerDeviceOnce attr_done;
+  if (attr_done.first()) QB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   int* status = device_status_ptr();
   QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "hadamard: device status word unavailable");
   const int64_t units = ceil_div(a->rows, R);

@@ -2,6 +2,7 @@
 #include "tc_common.cuh"
 
 #include <string.h>
+#include <atomic>
 
 namespace qb {
 
@@ -24,6 +25,9 @@ int sm_count() {
   if (dev < 64) cached[dev] = n;
   return n;
 }
+
+static std::atomic<int> g_path_override{0};
+bool path_override(int bit) { return (g_path_override.load(std::memory_order_relaxed) & bit) != 0; }
 
 static __device__ int g_device_status = 0;
 
@@ -57,6 +61,10 @@ extern "C" int qb_read_device_status(void* stream) {
     return QB_ERR_TIMEOUT;
   }
   return QB_OK;
+}
+
+extern "C" int qb_set_path_override(int mask) {
+  return qb::g_path_override.exchange(mask);
 }
 
 extern "C" const char* qb_last_error(void) { return qb::t_error; }

@@ -814,15 +814,13 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
       a->state_sp == a->dstate && a->state_sh == (int64_t)a->headdim * a->dstate &&
       a->state_sb == (int64_t)a->nheads * a->headdim * a->dstate && aligned(a->Bm, 16) && aligned(a->Cm, 16) &&
       a->B_sb % 16 == 0 && a->B_sg % 16 == 0 && a->C_sb % 16 == 0 && a->C_sg % 16 == 0 &&
-      getenv("QB_UPDATE_CTA_TILES") == nullptr) {
+      !path_override(QB_PATH_UPDATE_CTA_TILES)) {
     int* status = device_status_ptr();
     QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "sscan_update: device status word unavailable");
-    static bool wattr = false;
+    static PerDeviceOnce wattr;
     const size_t wsmem = (size_t)8 * kWSlots * kWTileBytes;
-    if (!wattr) {
-      cudaFuncSetAttribute(sscan_update_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
-      wattr = true;
-    }
+    if (wattr.first())
+      QB_CUDA_OK(cudaFuncSetAttribute(sscan_update_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem));
     const int64_t rows = (int64_t)a->batch * a->nheads * a->headdim;
     const int wtiles = (int)(rows / kWTileRows);
     const int wctas = (int)std::min<int64_t>(ceil_div(wtiles, 8), (int64_t)sm_count() * 3);
@@ -851,13 +849,12 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
       const bool grp = a->grouped != 0;
 #define QB_UPD_LAUNCH(L)                                                                                           \
   do {                                                                                                             \
-    static bool attr_done = false; /* static + dynamic shared memory exceeds 48 KB for small dstate */            \
-    if (!attr_done) {                                                                                              \
-      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);   \
-      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);    \
-      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);  \
-      cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);   \
-      attr_done = true;                                                                                            \
+    static PerDeviceOnce attr_done; /* static + dynamic shared memory exceeds 48 KB for small dstate */          \
+    if (attr_done.first()) {                                                                                       \
+      QB_CUDA_OK(cudaFuncSetAttribute(sscan_update_bulk_kernel<L, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));   \
+      QB_CUDA_OK(cudaFuncSetAttribute(sscan_update_bulk_kernel<L, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));    \
+      QB_CUDA_OK(cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));  \
+      QB_CUDA_OK(cudaFuncSetAttribute(sscan_update_bulk_kernel<L, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));   \
     }                                                                                                              \
     if (tied && !grp) launch_dependent(sscan_update_bulk_kernel<L, true, false>, dim3(grid), dim3(256), smem, st, *a, tiles, tiles_per_cta, status);      \
     else if (tied && grp) launch_dependent(sscan_update_bulk_kernel<L, true, true>, dim3(grid), dim3(256), smem, st, *a, tiles, tiles_per_cta, status);   \

@@ -325,9 +325,8 @@ int64_t ssd_tc_workspace_bytes(int B, int L, int H, int G);
 int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st);
 
 namespace {
-bool force_portable() {  // QB_SSD_PORTABLE=1 selects the five-stage path (used to cross-check the two on a device)
-  const char* e = getenv("QB_SSD_PORTABLE");
-  return e != nullptr && e[0] == '1';
+bool force_portable() {  // selects the five-stage path (used to cross-check the two on a device)
+  return path_override(QB_PATH_SSD_PORTABLE);
 }
 int64_t total_workspace(int B, int L, int H, int P, int G, int N, int Q) {
   const int64_t a = ws_layout(B, L, H, P, G, N, Q).total;
@@ -415,6 +414,8 @@ static __device__ __align__(256) unsigned char g_ssd_static_scratch[kStaticScrat
 
 // In host code `g_ssd_static_scratch` is only a host-side handle; the address a kernel can use has
 // to be asked for, once per device, with that device current.
+// The per-device cache is written without a lock: two host threads making their first call on one device may both
+// query the address and both store it; they store the same value, so the race is harmless.
 int static_scratch_ptr(char** out) {
   static char* cached[64] = {};
   int dev = 0;

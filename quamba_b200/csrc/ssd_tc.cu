@@ -46,13 +46,6 @@
 
 namespace qb {
 
-#ifdef QB_TRACE
-__device__ long long g_trace[2][64][16];
-#define TRACE(role, j, slot) do { asm volatile("" ::: "memory"); if (blockIdx.x == 0 && (j) < 64) g_trace[role][j][slot] = clock64(); asm volatile("" ::: "memory"); } while (0)
-#else
-#define TRACE(role, j, slot) do { } while (0)
-#endif
-
 namespace {
 using namespace tc;
 
@@ -346,14 +339,12 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           ok = mbar_wait_spin(&ms.s16_ready, ph, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          TRACE(1, it, 0);
           if (use_d1) issue_gemm<false, true>(tmem + (st ? kColD1b : kColD1), desc_advance(dCk, st * 2 * kAtom), dS16, id_kn);
           umma_commit(&ms.d1_ready);   // the fp16 state tile may be rewritten once this has fired
           // GEMM4(it): local state of the block, S = B^T (x w)
           ok = mbar_wait_spin(&ms.xops_ready, ph, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          TRACE(1, it, 1);
           issue_gemm<true, true>(tmem + kColS, desc_advance(dBm, st * 2 * kAtom), dXw, id_mn);
           umma_commit(&ms.s_ready);
           // GEMM3(it): D2 = Lm X, Lm from tensor memory.  lm_ready also says (program order of the compute warps) that
@@ -361,12 +352,10 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           ok = mbar_wait_spin(&ms.lm_ready, ph, status, QB_ERR_TIMEOUT);
           if (!ok) break;
           tc_fence_after_sync();
-          TRACE(1, it, 2);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_f16_ta(tmem + kColD2, tmem + kColLm + ks * 8, desc_advance(dXraw, ks * 2048), id_kn, ks != 0 ? 1u : 0u);
           umma_commit(&ms.y_ready);
-          TRACE(1, it, 3);
           if (it + 1 < plan.total) {
             // C.B^T of the next block (of this pair or the next one): the compute warps have finished reading CB(it)
             const int sn = (it + 1) & 1;
@@ -512,13 +501,11 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         const int l = j * T + row;
         // The x operands of this block are written by warp 0.  Here: the vectors and constants have landed (bc_full) and
         // C.B^T of this block is in tensor memory (cb_ready).
-        if (lead) TRACE(0, it, 0);
         ok = gwait(&ms.bc_full[st], (it >> 1) & 1, &ms.cb_ready, ph);
         if (!ok) break;
         // The vectors and constants of the previous block are read up to the end of its output step, which every warp
         // has left by now; its B / C / x tiles were released by the MMA issuer.
         if (lead && it > 0) mbar_arrive(&ms.ab_empty[(it - 1) & 1]);
-        if (lead) TRACE(0, it, 1);
         const float* av = ms.ab[st];
         const float* hc = ms.hc[st];
         const float sC = hc[kHcSC], dfold = hc[kHcDfold];
@@ -530,7 +517,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         // Written as packed fp16 into its own tensor-memory columns, which GEMM3 of the previous block has finished
         // reading (its output step waited for y_ready).
         tc_fence_after_sync();
-        if (lead) TRACE(0, it, 3);
         {
           // Work split inside a lane quarter q (rows 32q .. 32q + 31, four warps): the chunks c < q lie below the
           // diagonal and cost two multiplies per element, the chunk c = q holds the diagonal and costs an ex2 and the
@@ -594,14 +580,13 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         tmem_st_wait();
         tc_fence_before_sync();
         gsync();
-        if (lead) { mbar_arrive(&ms.lm_ready); TRACE(0, it, 4); }
+        if (lead) mbar_arrive(&ms.lm_ready);
 
         // ================= P3: state: s <- 2^r s + sB sx S_loc ; publish its fp16 copy for the next block ==============
         // s_ready: GEMM4(it) done.  d1_ready: GEMM2(it) done, so the fp16 state tile it read may be rewritten.
         ok = gwait(&ms.s_ready, ph, &ms.d1_ready, ph);
         if (!ok) break;
         tc_fence_after_sync();
-        if (lead) TRACE(0, it, 5);
         uint32_t d1[16];   // C.S of this block, complete since GEMM2 (d1_ready): fetched here, one TMEM round trip early
         {
           const float dec = fast_exp2(r_tot);
@@ -629,12 +614,10 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
         // tile, all warps meet, and then the fp16 state is announced to the MMA issuer.
         ok = gwait(&ms.y_ready, ph, it > 0 ? &ms.y_empty : nullptr, (it - 1) & 1);
         if (lead && j + 1 < im.je) mbar_arrive(&ms.s16_ready);
-        if (lead) TRACE(0, it, 6);
         if (!ok) break;
 
         // ================= P4: y(j) = sC 2^(a_m) D1 + sx (D2 + D x) ======================================================
         tc_fence_after_sync();
-        if (lead) TRACE(0, it, 7);
         {
           uint4 xq = make_uint4(0, 0, 0, 0);
           if (d_per_channel && l < a.seqlen) xq = ldg_nc_now(xrow_base + (int64_t)l * a.x_sl);   // own 16 channels of x
@@ -687,7 +670,6 @@ ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant_
           if (lane == 0) mbar_arrive(&ms.y_full);
         }
         if (!ok) break;
-        if (lead) TRACE(0, it, 8);
       }
       if (!ok) break;
 
@@ -975,9 +957,3 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
 }
 
 }  // namespace qb
-
-#ifdef QB_TRACE
-extern "C" int qb_debug_read_trace(long long* out) {  // 2 x 64 x 16 clock64 stamps of CTA 0 (development builds only)
-  return cudaMemcpyFromSymbol(out, qb::g_trace, sizeof(qb::g_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif

@@ -68,12 +68,12 @@ def test_ssd_full_size_is_causal():
     assert not torch.equal(y[:, cut:], y2[:, cut:])
 
 
-def test_ssd_full_size_tensor_core_path_equals_portable_path(monkeypatch):
+def test_ssd_full_size_tensor_core_path_equals_portable_path():
     c = make_ssd_case(B, L, H, P, G, N, Q, seed=13)
     y_tc, f_tc = run_ssd(c)
-    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
-    y_pt, f_pt = run_ssd(c)
-    monkeypatch.delenv("QB_SSD_PORTABLE")
+    from quamba_b200 import _lib as qlib
+    with qlib.path_override(qlib.PATH_SSD_PORTABLE):
+        y_pt, f_pt = run_ssd(c)
     err = (y_tc.float() - y_pt.float()).abs()
     tol = 1e-2 * y_pt.float().abs() + 1e-3 * y_pt.float().abs().max()
     assert (err <= tol).all(), f"max err {err.max().item()}"
@@ -82,16 +82,16 @@ def test_ssd_full_size_tensor_core_path_equals_portable_path(monkeypatch):
 
 
 @pytest.mark.parametrize("Bsz,Ls,Hs", [(8, 300, 80), (64, 100, 16), (2, 700, 80), (5, 1025, 37)])
-def test_ssd_range_cuts_at_other_shapes(Bsz, Ls, Hs, monkeypatch):
+def test_ssd_range_cuts_at_other_shapes(Bsz, Ls, Hs):
     """More (batch, head) pairs than SMs with 1, 3, 6 and 9 blocks per pair: the equal ranges then start and end in the
     middle of pairs at other places than in the benchmark shape (one block per pair: no cut inside a pair at all)."""
     c = make_ssd_case(Bsz, Ls, Hs, P, G, N, Q, seed=Ls)
     y_tc, f_tc = run_ssd(c)
     y_1, f_1 = run_ssd(c, slice(Bsz - 1, Bsz))          # fewer pairs than SMs: whole pairs per CTA
     assert torch.equal(y_tc[Bsz - 1], y_1[0]) and torch.equal(f_tc[Bsz - 1], f_1[0])
-    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
-    y_pt, f_pt = run_ssd(c)
-    monkeypatch.delenv("QB_SSD_PORTABLE")
+    from quamba_b200 import _lib as qlib
+    with qlib.path_override(qlib.PATH_SSD_PORTABLE):
+        y_pt, f_pt = run_ssd(c)
     err = (y_tc.float() - y_pt.float()).abs()
     tol = 1e-2 * y_pt.float().abs() + 1e-3 * y_pt.float().abs().max()
     assert (err <= tol).all(), f"max err {err.max().item()}"
@@ -99,7 +99,7 @@ def test_ssd_range_cuts_at_other_shapes(Bsz, Ls, Hs, monkeypatch):
     assert d.max().item() <= 1 and (d > 0).float().mean().item() <= 0.03
 
 
-def test_ssd_range_cuts_with_grouped_scales_and_per_channel_D(monkeypatch):
+def test_ssd_range_cuts_with_grouped_scales_and_per_channel_D():
     """192 pairs (more than SMs, so ranges are cut inside pairs), four SSD groups with grouped scale tables, D per channel
     (the output step then re-reads x), 700 tokens (the last block of every pair is ragged)."""
     Bsz, Ls, Hs, Gs = 6, 700, 32, 4
@@ -118,9 +118,9 @@ def test_ssd_range_cuts_with_grouped_scales_and_per_channel_D(monkeypatch):
     y_tc, f_tc = run()
     y_1, f_1 = run(slice(2, 3))
     assert torch.equal(y_tc[2], y_1[0]) and torch.equal(f_tc[2], f_1[0])
-    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
-    y_pt, f_pt = run()
-    monkeypatch.delenv("QB_SSD_PORTABLE")
+    from quamba_b200 import _lib as qlib
+    with qlib.path_override(qlib.PATH_SSD_PORTABLE):
+        y_pt, f_pt = run()
     err = (y_tc.float() - y_pt.float()).abs()
     tol = 1e-2 * y_pt.float().abs() + 1e-3 * y_pt.float().abs().max()
     assert (err <= tol).all(), f"max err {err.max().item()}"

@@ -134,9 +134,9 @@ def test_hadamard_quant(rows, dim, special, dtype):
 
 @pytest.mark.parametrize("rows,dim,special", [(19, 5120, 40), (9, 1536, 12), (6, 2560, 20), (5, 3584, 28), (11, 256, 1), (3, 512, 1),
                                               (17, 2048, 1), (5, 4096, 1), (300, 5120, 40)])
-def test_hadamard_tensor_core_path(rows, dim, special, monkeypatch):
+def test_hadamard_tensor_core_path(rows, dim, special):
     """fp16 rows of S * 128 elements take the tcgen05 path (odd row counts exercise the ragged last unit); the result must
-    match the oracle and the SIMT kernel, which the environment switch selects."""
+    match the oracle and the SIMT kernel (selected with the library's path override)."""
     x = (torch.randn(rows, dim, generator=torch.Generator().manual_seed(rows + dim)) * 3).to(torch.float16)
     scale = (1.0 / dim ** 0.5) / 0.05
     want, _ = ohad.quant_hadamard(x.float(), scale, special)
@@ -144,6 +144,10 @@ def test_hadamard_tensor_core_path(rows, dim, special, monkeypatch):
           28: "fast_hadamard_transform_28N", 40: "fast_hadamard_transform_40N"}[special]
     got = getattr(ops().quant_hadamard, fn)(x.to(DEV), scale)
     assert_lsb(got, want, max_frac=0.002)
+    from quamba_b200 import _lib as qlib
+    with qlib.path_override(qlib.PATH_HADAMARD_SIMT):
+        simt = getattr(ops().quant_hadamard, fn)(x.to(DEV), scale)
+    assert_lsb(got, simt.cpu(), max_frac=0.002)
     ops()._lib.read_device_status(torch.cuda.current_stream().cuda_stream)
 
 
@@ -292,13 +296,13 @@ def test_ssd_tensor_core_path_against_oracle(Bsz, L, H, G, grouped, dh):
     assert_lsb(fs, fq_ref, max_frac=0.03)
 
 
-def test_ssd_tensor_core_path_equals_portable_path_on_device(monkeypatch):
+def test_ssd_tensor_core_path_equals_portable_path_on_device():
     """Same inputs through both CUDA paths at a layer-sized shape (batch 1 of the benchmark configuration)."""
     c = make_ssd_case(1, 2048, 80, 64, 1, 128, 256, seed=7)
     y_tc, f_tc = _run_ssd(c, False)
-    monkeypatch.setenv("QB_SSD_PORTABLE", "1")
-    y_pt, f_pt = _run_ssd(c, False)
-    monkeypatch.delenv("QB_SSD_PORTABLE")
+    from quamba_b200 import _lib as qlib
+    with qlib.path_override(qlib.PATH_SSD_PORTABLE):
+        y_pt, f_pt = _run_ssd(c, False)
     torch.cuda.synchronize()
     assert_fp16(y_tc, y_pt.cpu())
     assert_lsb(f_tc, f_pt.cpu(), max_frac=0.03)

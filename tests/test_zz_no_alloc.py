@@ -29,8 +29,20 @@ def _args(lib_mod, c, dev_t, out, fin, ws, ws_bytes, Bsz, L, H, P, G, N, Q):
         dt_min=0.0, dt_max=3.0e38)
 
 
-def test_noalloc_entry_point_matches_regular_one_twice():
+@pytest.mark.parametrize("portable", [False, True])
+def test_noalloc_entry_point_matches_regular_one_twice(portable):
+    """``portable`` sends both entry points down the five-stage path (cumulative sums, C B^T, chunk states, state
+    passing, output), whose stages read back what earlier stages left in the scratch array; the default shapes take the
+    single tensor-core kernel."""
     from quamba_b200 import _lib
+    if portable:
+        with _lib.path_override(_lib.PATH_SSD_PORTABLE):
+            _twice(_lib)
+    else:
+        _twice(_lib)
+
+
+def _twice(_lib):
     lib = _lib.lib()
     dev = torch.device("cuda")
     stream = torch.cuda.current_stream().cuda_stream
