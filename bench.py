@@ -42,7 +42,10 @@ def peaks():
     out = dict(hbm=float(p.get("hbm_gbs", 6650.0)), bf16=float(p.get("bf16_tflops", 1590.0)), source="measured" if p else "fallback")
     i8 = ROOT / "profiles" / "int8_mma_peak.json"
     if i8.exists():         # written from a run of `bench.py --op i8_peak` (a tcgen05 kind::i8 issue-rate measurement)
-        out["i8"], out["i8_source"] = float(json.loads(i8.read_text())["tops"]), "measured tcgen05 kind::i8 issue rate"
+        d = json.loads(i8.read_text())
+        # the sustained figure: the GEMMs here are timed inside a step that runs for seconds under the power cap
+        out["i8"], out["i8_burst"] = float(d["tops_sustained"]), float(d["tops"])
+        out["i8_source"] = "measured tcgen05 kind::i8 issue rate, sustained (profiles/int8_mma_peak.json; burst %.0f)" % d["tops"]
     else:
         out["i8"], out["i8_source"] = 2.0 * out["bf16"], "2 x the measured bf16 cuBLAS peak"
     return out

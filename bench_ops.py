@@ -279,13 +279,38 @@ OPS = {"conv": op_conv, "conv_update": op_conv_update, "hadamard": op_hadamard, 
        "w8a8": op_w8a8}
 
 
+def i8_peak():
+    """The dense int8 rate of tcgen05.mma kind::i8 (qb_i8_mma_peak): a burst (about 5 ms) and a sustained run (about 2 s,
+    under the power cap), next to the measured bf16 cuBLAS peak."""
+    import ctypes
+    from quamba_b200 import _lib
+    f = _lib.lib().qb_i8_mma_peak
+    f.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+    for tag, groups, repeats in (("burst", 4096, 4), ("sustained", 65536, 100)):
+        tops, ms = ctypes.c_double(), ctypes.c_double()
+        _lib.check(f(groups, repeats, ctypes.c_void_p(st), ctypes.byref(tops), ctypes.byref(ms)))
+        out[tag] = {"tops": tops.value, "ms": ms.value}
+    _lib.read_device_status(st)
+    hbm, bf16, src = _peaks()
+    return {"op": "i8_peak", "metric": "int8_tensor_tops", "value": out["burst"]["tops"], "unit": "TOP/s", "n_gpus": 1,
+            "higher_is_better": True, "data": "synthetic", "sustained_tops": out["sustained"]["tops"],
+            "ms": {k: v["ms"] for k, v in out.items()}, "bf16_cublas_tflops": bf16, "ratio_to_bf16": out["burst"]["tops"] / bf16,
+            "config": {"workload": "tcgen05.mma kind::i8 M128 N256 K32, operands resident in shared memory, one CTA per SM, "
+                                   "two alternating TMEM accumulators, no loads and no epilogue"}}
+
+
 def run(name, steps, warmup):
     """Returns the list of JSON-able result lines for ``name`` ('all' runs every op)."""
     from quamba_b200 import _lib, ops
     assert torch.cuda.is_available(), "needs a CUDA device; there is no CPU fallback"
+    if name == "i8_peak":
+        return [i8_peak()]
     dev = torch.device("cuda", 0)
     hbm, bf16, src = _peaks()
-    int8_peak = 2.0 * bf16                                  # dense int8 tensor peak = 2 x the measured bf16 GEMM peak
+    i8_file = ROOT / "profiles" / "int8_mma_peak.json"      # a kernel timed alone: the burst figure
+    int8_peak = float(json.loads(i8_file.read_text())["tops"]) if i8_file.exists() else 2.0 * bf16
     stream = torch.cuda.Stream(device=dev)
     out = []
     for nm in (list(OPS) if name == "all" else [name]):
@@ -302,7 +327,8 @@ def run(name, steps, warmup):
         roof.update(kernel=spec["kernel"], traffic=None, peak_source=src, algorithmic_bytes=spec["bytes"], flops=spec["flops"],
                     ms=ms)
         if tensor_bound:
-            roof["peak_note"] = "2 x measured bf16 cuBLAS peak (dense int8 rate is twice bf16)"
+            roof["peak_note"] = ("measured tcgen05 kind::i8 issue rate, burst (profiles/int8_mma_peak.json)" if i8_file.exists()
+                                 else "2 x measured bf16 cuBLAS peak")
         line = {"op": nm, "metric": "kernel_time_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3),
                 "higher_is_better": False, "data": "synthetic", "config": {"workload": spec["workload"],
                                                                             "l2": f"{spec['nsets']} rotating input sets"},

@@ -522,6 +522,12 @@ typedef struct {
 } qb_w8a8_gemm_args;
 int qb_w8a8_gemm(const qb_w8a8_gemm_args* a, void* stream);
 
+/* Measurement aid (no counterpart in the reference): the dense int8 rate of tcgen05.mma kind::i8 on the current device,
+ * operands resident in shared memory, one CTA per SM, `repeats` launches of `groups` x four M128 N256 K32 MMAs each, timed
+ * with CUDA events.  *tops receives TOP/s (2 x MACs), *ms (nullable) the elapsed time.  Blocks the host.  The GEMM
+ * rooflines use this figure as their peak. */
+int qb_i8_mma_peak(int groups, int repeats, void* stream, double* tops, double* ms);
+
 /* ------------------------------------------------------------------------------------------
  * Quantised RMSNorm with residual add, and gated grouped RMSNorm.
  * qb_rmsnorm_quant replaces _qlayer_norm_fwd (quamba/triton/quant_norm.py:68-206, called by

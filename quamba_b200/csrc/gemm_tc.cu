@@ -322,6 +322,59 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
   }
 }
 
+// ---- issue-rate measurement of tcgen05.mma kind::i8 -------------------------------------------------------------------
+// One CTA per SM; operands (pseudo-random int8, the 128-byte-swizzled tile shapes of the GEMM above) sit in shared memory
+// and are never reloaded; one thread issues `groups` x four M128 N256 K32 MMAs into two alternating accumulators and
+// commits each group of four to a ring of mbarriers it waits on two groups behind, the way the GEMM's stage ring paces it.
+// What comes out is the tensor pipe's dense int8 rate with shared-memory operands and no epilogue: the denominator of the
+// GEMM rooflines.
+constexpr int kPeakRing = 4;
+__global__ void __launch_bounds__(128, 1) i8_mma_peak_kernel(int groups, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStageBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kPeakRing);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kPStageBytes / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(smem)[i] = (uint32_t)(i * 2654435761u) ^ (blockIdx.x * 40503u);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPeakRing; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes of the operands -> async proxy (MMA)
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  if (warp == 1 && lane == 0) {
+    constexpr uint32_t idesc = make_idesc(2, 1, 1, 0, 0, BM, PBN);
+    const SmemDesc da = make_smem_desc2(smem_u32(smem), 16, 1024, kSwizzle128B);
+    const SmemDesc dw = desc_advance(da, BM * BK);
+    bool ok = true;
+    for (int g = 0; g < groups && ok; ++g) {
+      if (g >= kPeakRing) ok = mbar_wait_spin(&bars[g % kPeakRing], (uint32_t)(((g / kPeakRing) - 1) & 1), status, QB_ERR_TIMEOUT);
+      if (!ok) break;
+      const uint32_t acc = tmem_base + (uint32_t)((g & 1) * PBN);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_i8(acc, desc_advance(da, k * 32), desc_advance(dw, k * 32), idesc, g >= 2 ? 1u : (k ? 1u : 0u));
+      umma_commit(&bars[g % kPeakRing]);
+    }
+    // drain: the last kPeakRing groups
+    for (int g = max(0, groups - kPeakRing); g < groups && ok; ++g)
+      ok = mbar_wait_spin(&bars[g % kPeakRing], (uint32_t)((g / kPeakRing) & 1), status, QB_ERR_TIMEOUT);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -438,3 +491,33 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
 
 }  // namespace qb
 
+// Measures the dense int8 tensor rate of the current device (see i8_mma_peak_kernel): runs `repeats` launches of `groups`
+// MMA groups per SM on `stream`, times them with CUDA events and returns TOP/s in *tops.  Blocks the host.
+extern "C" int qb_i8_mma_peak(int groups, int repeats, void* stream, double* tops, double* ms) {
+  using namespace qb;
+  QB_REQUIRE(groups > 0 && repeats > 0 && tops != nullptr, QB_ERR_INVALID_ARG, "i8_mma_peak: bad arguments");
+  int* status = device_status_ptr();
+  QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "device status word unavailable");
+  static PerDeviceOnce attr;
+  constexpr int smem = kPStageBytes + 1024 + 256;
+  if (attr.first()) QB_CUDA_OK(cudaFuncSetAttribute(i8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaEvent_t e0, e1;
+  QB_CUDA_OK(cudaEventCreate(&e0));
+  QB_CUDA_OK(cudaEventCreate(&e1));
+  const int sms = sm_count();
+  i8_mma_peak_kernel<<<sms, 128, smem, st>>>(groups, status);   // warm-up
+  QB_CUDA_OK(cudaEventRecord(e0, st));
+  for (int r = 0; r < repeats; ++r) i8_mma_peak_kernel<<<sms, 128, smem, st>>>(groups, status);
+  QB_CUDA_OK(cudaEventRecord(e1, st));
+  QB_CUDA_OK(cudaEventSynchronize(e1));
+  QB_LAUNCH_OK("i8_mma_peak_kernel");
+  float t = 0.f;
+  QB_CUDA_OK(cudaEventElapsedTime(&t, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  const double ops = 2.0 * BM * PBN * 32 * 4.0 * groups * (double)sms * repeats;
+  *tops = ops / (t * 1e-3) / 1e12;
+  if (ms != nullptr) *ms = t;
+  return QB_OK;
+}

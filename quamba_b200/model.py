@@ -200,6 +200,33 @@ class QuambaLMHeadModel(nn.Module):
     def allocate_inference_cache(self, batch_size, max_seqlen, dtype=None, **kwargs):
         return self.backbone.allocate_inference_cache(batch_size, max_seqlen, dtype=dtype, **kwargs)
 
+    # ---- checkpoints in the reference's layout (quamba/quamba_mixer_seq.py:423-449) --------------------------------------
+    def save_pretrained(self, save_directory):
+        """Writes ``pytorch_model.bin`` (the state dict: buffers plus the float scales the modules' hooks add) and
+        ``config.json`` (the config's fields)."""
+        import json
+        import os
+        os.makedirs(save_directory, exist_ok=True)
+        torch.save(self.state_dict(), os.path.join(save_directory, "pytorch_model.bin"))
+        with open(os.path.join(save_directory, "config.json"), "w") as f:
+            json.dump(self.config.__dict__, f, indent=4)
+
+    @classmethod
+    def from_pretrained(cls, pretrained_dir, device=None, **kwargs):
+        """Builds the model from a directory holding ``config.json`` + ``pytorch_model.bin`` as ``save_pretrained`` (here
+        or in the reference) writes them: constructed on the CPU, buffers resized to what the checkpoint holds (per-tensor
+        or head-grouped scale tables, per-channel or group-128 weights), loaded, then moved to ``device``."""
+        import json
+        import os
+        with open(os.path.join(pretrained_dir, "config.json")) as f:
+            data = json.load(f)
+        known = {k: v for k, v in data.items() if k in QuambaConfig.__dataclass_fields__}
+        model = cls(QuambaConfig(**known), device="cpu", **kwargs)
+        sd = torch.load(os.path.join(pretrained_dir, "pytorch_model.bin"), map_location="cpu", weights_only=True)
+        _fit_buffers_to(model, sd)
+        model.load_state_dict(sd)
+        return model.to(device) if device is not None else model
+
     @torch.no_grad()
     def forward(self, input_ids, position_ids=None, inference_params=None, num_last_tokens=0, **mixer_kwargs):
         """input_ids int64 (batch, seqlen).  Prefill when ``inference_params.seqlen_offset == 0`` (the layers then also
@@ -292,3 +319,26 @@ class GraphRunner:
     def replay(self):
         self.graph.replay()
         return self.logits
+
+
+def _fit_buffers_to(model, state_dict):
+    """Checkpoints differ in optional pieces the constructors cannot know: scale tables are per-tensor (1 element) or
+    head-grouped, the range tables exist only when grouped, per-channel weights carry an empty ``s_group``.  Give every
+    buffer the checkpoint's shape, drop the ones it does not hold, before ``load_state_dict``."""
+    for name, mod in model.named_modules():
+        prefix = name + "." if name else ""
+        for bname in list(mod._buffers):
+            key = prefix + bname
+            buf = mod._buffers[bname]
+            if key not in state_dict:
+                if buf is not None and bname in ("x_head_group_range", "x_dim_group_range"):
+                    del mod._buffers[bname]
+                    setattr(mod, bname, None)
+                continue
+            t = state_dict[key]
+            if buf is None or tuple(buf.shape) != tuple(t.shape) or buf.dtype != t.dtype:
+                mod._buffers[bname] = torch.empty(t.shape, dtype=t.dtype)
+        for pname, par in list(mod._parameters.items()):
+            key = prefix + pname
+            if key in state_dict and par is not None and tuple(par.shape) != tuple(state_dict[key].shape):
+                par.data = torch.empty(state_dict[key].shape, dtype=state_dict[key].dtype)
