@@ -608,6 +608,8 @@ int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t
  * qb_decode_norm_linear: h = x (+ residual); residual_out = h; a = int8(rmsnorm(h) * norm_weight / norm_out_scale);
  *   out (rows, n) = a @ W^T scaled by s_channel_nat[n] * s_tok, int8 (rint, saturating) or fp16.  W is the int8 copy
  *   qb_w4a8_unpack makes (n, k), or with w_is_s4 != 0 the nibble copy qb_w4a8_pack_nibbles makes (per-channel weights).
+ *   With a_int8 != null (rows x k int8, row stride x_row_stride) the norm is skipped and a_int8 is multiplied as it is:
+ *   the plain decode-sized product with this kernel's load scheduling.
  *   With conv_state != null the columns [conv_col0, conv_col0 + conv_dim) are not stored: each is fed to that channel's
  *   quamba2_conv1d update (width 4, per-tensor output scales; state element (b, c, w) at b*sb + c*sd + w*sw shifted in
  *   place) and the conv results go to conv_x (rows, conv_x_dim), conv_B / conv_C (rows, conv_gn).
@@ -619,6 +621,7 @@ int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t
  * ------------------------------------------------------------------------------------------ */
 typedef struct {
   const void* x;
+  const int8_t* a_int8;
   const void* residual;
   void* residual_out;
   const void* norm_weight;

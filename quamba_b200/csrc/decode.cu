@@ -71,7 +71,10 @@ struct ConvEpi {
   int enabled;
 };
 
-// dot products of the int8 rows in shared memory (MB rows of k bytes) with weight columns n0 .. n0 + kNW - 1
+// dot products of the int8 rows in shared memory (MB rows of k bytes) with weight columns n0 .. n0 + kNW - 1.
+// A lane loads kNB weight chunks per column BEFORE it uses any (clamped addresses, so the loads need no branches): at the
+// model's sizes that is the lane's whole share of a column in one round trip to L2 instead of one round trip per chunk.
+constexpr int kNB = 5;
 template <int MB, bool S4>
 __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][kNW]) {
   int sa[MB];
@@ -81,53 +84,54 @@ __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, i
 #pragma unroll
     for (int j = 0; j < kNW; ++j) acc[i][j] = 0;
   }
-  if (!S4) {
-    const int chunks = L.k / 16;
-#pragma unroll 4
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 w[kNW];
+  const int chunks = S4 ? L.k / 32 : L.k / 16;          // 16-byte weight chunks per column
+  const int64_t ldw = S4 ? L.k / 2 : L.k;
+  const uint4* wrow[kNW];
 #pragma unroll
-      for (int j = 0; j < kNW; ++j)
-        w[j] = __ldg(reinterpret_cast<const uint4*>(L.w + (int64_t)min(n0 + j, L.n - 1) * L.k) + c);
+  for (int j = 0; j < kNW; ++j) wrow[j] = reinterpret_cast<const uint4*>(L.w + (int64_t)min(n0 + j, L.n - 1) * ldw);
+  for (int c0 = lane; c0 < chunks; c0 += 32 * kNB) {
+    uint4 w[kNW][kNB];
 #pragma unroll
-      for (int i = 0; i < MB; ++i) {
-        const uint4 a = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + c);
+    for (int b = 0; b < kNB; ++b) {
+      const int c = min(c0 + 32 * b, chunks - 1);
 #pragma unroll
-        for (int j = 0; j < kNW; ++j) {
-          int t = acc[i][j];
-          t = __dp4a((int)a.x, (int)w[j].x, t); t = __dp4a((int)a.y, (int)w[j].y, t);
-          t = __dp4a((int)a.z, (int)w[j].z, t); t = __dp4a((int)a.w, (int)w[j].w, t);
-          acc[i][j] = t;
-        }
-      }
+      for (int j = 0; j < kNW; ++j) w[j][b] = __ldg(wrow[j] + c);
     }
-  } else {
-    const int chunks = L.k / 32;            // 16 bytes of nibbles = 32 values
-    const int64_t ldw = L.k / 2;
-#pragma unroll 4
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 w[kNW];
 #pragma unroll
-      for (int j = 0; j < kNW; ++j) w[j] = __ldg(reinterpret_cast<const uint4*>(L.w + (int64_t)min(n0 + j, L.n - 1) * ldw) + c);
+    for (int b = 0; b < kNB; ++b) {
+      const int c = c0 + 32 * b;
+      if (c < chunks) {
 #pragma unroll
-      for (int i = 0; i < MB; ++i) {
-        const uint4 a0 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c);
-        const uint4 a1 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c + 1);
-        const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
-        int s = sa[i];
+        for (int i = 0; i < MB; ++i) {
+          if (!S4) {
+            const uint4 a = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + c);
 #pragma unroll
-        for (int t = 0; t < 8; ++t) s = __dp4a(av[t], 0x01010101, s);
-        sa[i] = s;
+            for (int j = 0; j < kNW; ++j) {
+              int t = acc[i][j];
+              t = __dp4a((int)a.x, (int)w[j][b].x, t); t = __dp4a((int)a.y, (int)w[j][b].y, t);
+              t = __dp4a((int)a.z, (int)w[j][b].z, t); t = __dp4a((int)a.w, (int)w[j][b].w, t);
+              acc[i][j] = t;
+            }
+          } else {
+            const uint4 a0 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c);
+            const uint4 a1 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c + 1);
+            const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+            int sum = sa[i];
 #pragma unroll
-        for (int j = 0; j < kNW; ++j) {
-          const uint32_t ww[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
-          int t = acc[i][j];
+            for (int t = 0; t < 8; ++t) sum = __dp4a(av[t], 0x01010101, sum);
+            sa[i] = sum;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            t = __dp4a(av[2 * q], (int)(ww[q] & 0x0f0f0f0fu), t);
-            t = __dp4a(av[2 * q + 1], (int)((ww[q] >> 4) & 0x0f0f0f0fu), t);
+            for (int j = 0; j < kNW; ++j) {
+              const uint32_t ww[4] = {w[j][b].x, w[j][b].y, w[j][b].z, w[j][b].w};
+              int t = acc[i][j];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                t = __dp4a(av[2 * q], (int)(ww[q] & 0x0f0f0f0fu), t);
+                t = __dp4a(av[2 * q + 1], (int)((ww[q] >> 4) & 0x0f0f0f0fu), t);
+              }
+              acc[i][j] = t;
+            }
           }
-          acc[i][j] = t;
         }
       }
     }
@@ -143,30 +147,55 @@ __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, i
   }
 }
 
+// What a finishing lane needs beyond the accumulator.  Everything in it is either constant or was written by the previous
+// decode STEP (the conv window), never by the kernel just before this one, so it is loaded ahead of the dependency wait.
+struct FinishPre {
+  float s_ch, s_tok, so, bias_term;
+  int w0, w1, w2;          // the three newest samples of the conv window
+  int wt;                  // four conv taps, packed
+  int seg;                 // -1: not a conv column
+};
+
+__device__ __forceinline__ FinishPre finish_prefetch(const Linear& L, const ConvEpi& cv, int m, int n) {
+  FinishPre f;
+  f.s_ch = __ldg(L.s_ch + n);
+  f.s_tok = __ldg(L.s_tok);
+  f.seg = -1;
+  const int c = n - cv.c0;
+  if (L.out_int8 && cv.enabled && c >= 0 && c < cv.dim) {
+    const int s = c < cv.end0 ? 0 : (c < cv.end1 ? 1 : 2);
+    f.seg = s;
+    const int8_t* st = cv.state + (int64_t)m * cv.sb + (int64_t)c * cv.sd;
+    f.w0 = st[cv.sw]; f.w1 = st[2 * cv.sw]; f.w2 = st[3 * cv.sw];
+    f.wt = *reinterpret_cast<const int*>(cv.weight + (int64_t)c * 4);
+    f.so = __ldg(cv.out_scale[s]);
+    f.bias_term = cv.bias != nullptr ? cv.scale_bias[s] * (float)cv.bias[c] : 0.0f;
+  }
+  return f;
+}
+
 // scale, convert and store one output element; when the column is a conv channel, run that channel's decode step
-__device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, int acc, int m, int n) {
-  const float r = ((float)acc * L.s_ch[n]) * L.s_tok[0];
+__device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, const FinishPre& f, int acc, int m, int n) {
+  const float r = ((float)acc * f.s_ch) * f.s_tok;
   if (!L.out_int8) {
     static_cast<__half*>(L.out)[(int64_t)m * L.out_stride + n] = __float2half_rn(r);
     return;
   }
   const int q = rint_s8(r);
-  const int c = n - cv.c0;
-  if (!cv.enabled || c < 0 || c >= cv.dim) {
+  if (f.seg < 0) {
     static_cast<int8_t*>(L.out)[(int64_t)m * L.out_stride + n] = (int8_t)q;
     return;
   }
+  const int c = n - cv.c0, s = f.seg;
   int8_t* st = cv.state + (int64_t)m * cv.sb + (int64_t)c * cv.sd;
-  const int w0 = st[cv.sw], w1 = st[2 * cv.sw], w2 = st[3 * cv.sw];
-  st[0] = (int8_t)w0; st[cv.sw] = (int8_t)w1; st[2 * cv.sw] = (int8_t)w2; st[3 * cv.sw] = (int8_t)q;
-  const int8_t* wt = cv.weight + (int64_t)c * 4;
-  const float dot = (float)((int)wt[0] * w0 + (int)wt[1] * w1 + (int)wt[2] * w2 + (int)wt[3] * q);
-  const int s = c < cv.end0 ? 0 : (c < cv.end1 ? 1 : 2);
+  st[0] = (int8_t)f.w0; st[cv.sw] = (int8_t)f.w1; st[2 * cv.sw] = (int8_t)f.w2; st[3 * cv.sw] = (int8_t)q;
+  const int win = (f.w0 & 0xff) | ((f.w1 & 0xff) << 8) | ((f.w2 & 0xff) << 16) | (q << 24);
+  const float dot = (float)__dp4a(win, f.wt, 0);
   const int cbase = s == 0 ? 0 : (s == 1 ? cv.end0 : cv.end1);
   const int width = s == 0 ? cv.end0 : cv.end1 - cv.end0;
-  float v = cv.scale_in[s] * dot + (cv.bias != nullptr ? cv.scale_bias[s] * (float)cv.bias[c] : 0.0f);
+  float v = cv.scale_in[s] * dot + f.bias_term;
   v = silu_fast(v);
-  cv.dst[s][(int64_t)m * width + (c - cbase)] = (int8_t)round_away_s8(v / cv.out_scale[s][0]);
+  cv.dst[s][(int64_t)m * width + (c - cbase)] = (int8_t)round_away_s8(v / f.so);
 }
 
 // Ask L2 for the weight rows of this warp's first pass.  Weights do not depend on the kernel before this one, so the call
@@ -184,28 +213,43 @@ __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
   }
 }
 
+// `pre`: the finishing lane's constants of the first pass, loaded by the caller before the dependency wait.
 template <int MB, bool S4>
-__device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows) {
+__device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows, FinishPre pre) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int n0 = (blockIdx.x * kWarps + warp) * kNW; n0 < L.n; n0 += (int)gridDim.x * kWarps * kNW) {
+  const int i = lane / kNW, j = lane % kNW;
+  const int first = (blockIdx.x * kWarps + warp) * kNW;
+  for (int n0 = first; n0 < L.n; n0 += (int)gridDim.x * kWarps * kNW) {
+    const bool mine = lane < MB * kNW && i < rows && n0 + j < L.n;
+    if (n0 != first && mine) pre = finish_prefetch(L, cv, i, n0 + j);
     int acc[MB][kNW];
     dot_columns<MB, S4>(L, sA, n0, lane, acc);
     // lanes 0 .. MB * kNW - 1 finish one (row, column) each, so that the conv windows of a warp's columns move in parallel
-    if (lane < MB * kNW) {
-      const int i = lane / kNW, j = lane % kNW;
+    if (mine) {
       int v = 0;
 #pragma unroll
       for (int ii = 0; ii < MB; ++ii)
 #pragma unroll
         for (int jj = 0; jj < kNW; ++jj)
           if (ii == i && jj == j) v = acc[ii][jj];
-      if (i < rows && n0 + j < L.n) finish(L, cv, v, i, n0 + j);
+      finish(L, cv, pre, v, i, n0 + j);
     }
   }
 }
 
+template <int MB>
+__device__ __forceinline__ FinishPre first_pass_prefetch(const Linear& L, const ConvEpi& cv, int rows) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = lane / kNW, j = lane % kNW;
+  const int n0 = (blockIdx.x * kWarps + warp) * kNW;
+  FinishPre pre{};
+  if (lane < MB * kNW && i < rows && n0 + j < L.n) pre = finish_prefetch(L, cv, i, n0 + j);
+  return pre;
+}
+
 // ---- launch 1: residual add + RMSNorm + quantise -> product (+ conv update) -------------------------------------------
 struct NormIn {
+  const int8_t* a_int8;     // (rows, k) already quantised input (stride x_stride): the norm is skipped
   const __half* x;          // (rows, k)
   const void* residual;     // fp32 or fp16 (rows, k), nullable
   void* residual_out;       // nullable
@@ -216,7 +260,7 @@ struct NormIn {
 };
 
 template <int MB, bool S4>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 2)
 decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   extern __shared__ __align__(16) uint8_t dsm[];
   __shared__ float red[kWarps];
@@ -224,8 +268,24 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   const int K = L.k;
   grid_dependency_launch();
   prefetch_first_columns<S4>(L);
-  grid_dependency_wait();
+  const FinishPre pre = first_pass_prefetch<MB>(L, cv, rows);
   const int chunks = K / 8;
+  uint4 nw[4];               // the norm weights of this thread's chunks: constants, fetched ahead of the wait
+  if (nin.a_int8 == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) nw[i] = __ldg(reinterpret_cast<const uint4*>(nin.weight) + min(threadIdx.x + i * kThreads, chunks - 1));
+  }
+  grid_dependency_wait();
+  if (nin.a_int8 != nullptr) {
+    for (int m = 0; m < MB; ++m) {
+      const int row = min(m, rows - 1);
+      for (int c = threadIdx.x; c < K / 16; c += kThreads)
+        *(reinterpret_cast<uint4*>(sA + (int64_t)m * K) + c) = __ldg(reinterpret_cast<const uint4*>(nin.a_int8 + (int64_t)row * nin.x_stride) + c);
+    }
+    __syncthreads();
+    stream_columns<MB, S4>(L, cv, sA, rows, pre);
+    return;
+  }
   const float inv_scale = 1.0f / nin.out_scale;
   for (int m = 0; m < MB; ++m) {
     const int row = min(m, rows - 1);
@@ -275,8 +335,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
     for (int i = 0; i < 4; ++i) {
       const int c = threadIdx.x + i * kThreads;
       if (c < chunks) {
-        const uint4 wr = __ldg(reinterpret_cast<const uint4*>(nin.weight) + c);
-        const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+        const __half2* wh = reinterpret_cast<const __half2*>(&nw[i]);
         int q[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -292,7 +351,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
     }
   }
   __syncthreads();
-  stream_columns<MB, S4>(L, cv, sA, rows);
+  stream_columns<MB, S4>(L, cv, sA, rows, pre);
 }
 
 // ---- launch 3: gate, grouped RMSNorm, Hadamard rotation, quantise -> product -------------------------------------------
@@ -467,11 +526,13 @@ using namespace qb;
   } while (0)
 
 extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* stream) {
-  QB_REQUIRE(a != nullptr && a->x && a->norm_weight, QB_ERR_INVALID_ARG, "decode_norm_linear: null pointer");
+  QB_REQUIRE(a != nullptr && ((a->x && a->norm_weight) || a->a_int8), QB_ERR_INVALID_ARG, "decode_norm_linear: null pointer");
   QB_REQUIRE(a->rows >= 1 && a->rows <= kMaxRows, QB_ERR_UNSUPPORTED, "decode_norm_linear: 1 to %d rows", kMaxRows);
   QB_REQUIRE(a->k <= 8192 && a->k % 32 == 0, QB_ERR_UNSUPPORTED, "decode_norm_linear: k must be a multiple of 32, at most 8192");
-  QB_REQUIRE(a->norm_out_scale != 0.0f, QB_ERR_INVALID_ARG, "decode_norm_linear: the norm's output scale is zero");
-  QB_REQUIRE(aligned(a->x, 16) && a->x_row_stride % 8 == 0 && aligned(a->norm_weight, 16) &&
+  QB_REQUIRE(a->a_int8 != nullptr || a->norm_out_scale != 0.0f, QB_ERR_INVALID_ARG, "decode_norm_linear: the norm's output scale is zero");
+  QB_REQUIRE(a->a_int8 == nullptr || (aligned(a->a_int8, 16) && a->x_row_stride % 16 == 0), QB_ERR_INVALID_ARG,
+             "decode_norm_linear: int8 input rows must be 16-byte aligned");
+  QB_REQUIRE(a->a_int8 != nullptr || (aligned(a->x, 16) && a->x_row_stride % 8 == 0 && aligned(a->norm_weight, 16)) &&
              (a->residual == nullptr || (aligned(a->residual, 16) && a->residual_row_stride % 8 == 0)) &&
              (a->residual_out == nullptr || (aligned(a->residual_out, 16) && a->residual_out_row_stride % 8 == 0)),
              QB_ERR_INVALID_ARG, "decode_norm_linear: rows must be 16-byte aligned");
@@ -480,6 +541,7 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
                        "decode_norm_linear");
   if (rc != QB_OK) return rc;
   NormIn nin{};
+  nin.a_int8 = a->a_int8;
   nin.x = static_cast<const __half*>(a->x); nin.residual = a->residual; nin.residual_out = a->residual_out;
   nin.weight = static_cast<const __half*>(a->norm_weight);
   nin.x_stride = a->x_row_stride; nin.res_stride = a->residual_row_stride; nin.res_out_stride = a->residual_out_row_stride;
@@ -499,7 +561,7 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
   }
   const int mb = a->rows <= 2 ? a->rows : 4;
   const size_t smem = (size_t)mb * a->k;
-  const dim3 grid(grid_for(a->n, 3));
+  const dim3 grid(grid_for(a->n, 2));
   cudaStream_t st = (cudaStream_t)stream;
   const int rows = a->rows;
   QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, a->w_is_s4 != 0, grid, smem, st, nin, L, cv, rows);

@@ -368,6 +368,72 @@ sscan_update_stream_kernel(qb_sscan_update_args a, int iters) {
 }
 
 
+// Low-latency form for decode steps with few (batch, head) pairs (one token of one to a few sequences): one CTA per
+// pair, a thread owns 32 consecutive states of one row.  What makes a small decode kernel slow is not bandwidth but the
+// chain of dependent round trips to memory, so everything that the kernel before this one on the stream cannot have
+// written -- the state itself (last written by the previous decode step), A, D, dt_bias and the scales -- is loaded
+// BEFORE the dependency wait; after it come one round of loads (x, dt, B, C), the arithmetic of the streaming kernel
+// above, and the stores.  d_state 128, per-tensor scales, A / dt / D tied across the head.
+__global__ void __launch_bounds__(256)
+sscan_update_small_kernel(qb_sscan_update_args a) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  grid_dependency_launch();
+  const int hd = blockIdx.x, b = blockIdx.y;
+  const int sub = threadIdx.x & 3, n0 = sub * 32;
+  const int g = hd / (a.nheads / a.ngroups);
+  const float xs = __ldg(a.x_scales), ss = __ldg(a.state_scale), dts = __ldg(a.dt_scale), As = __ldg(a.A_scale);
+  const float Bs = __ldg(a.B_scale), Cs = __ldg(a.C_scale);
+  const float Dv = a.D != nullptr ? __ldg(a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh] : 0.0f;
+  float bias = 0.0f;
+  if (a.dt_bias != nullptr) {
+    const int64_t bi = (int64_t)hd * a.bias_sh;
+    bias = a.dt_bias_is_half ? __half2float(static_cast<const __half*>(a.dt_bias)[bi])
+                             : __ldg(a.dt_bias_scale) * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
+  }
+  const float nA = -__expf(As * (float)a.A_log[(int64_t)hd * a.A_sh]) * kLog2e;
+  const float inv = 1.0f / ss;
+  for (int p = threadIdx.x >> 2; p < a.headdim; p += 64) {
+    int8_t* st = a.state + (int64_t)b * a.state_sb + (int64_t)hd * a.state_sh + (int64_t)p * a.state_sp + n0;
+    const uint4 raw0 = *reinterpret_cast<const uint4*>(st), raw1 = *reinterpret_cast<const uint4*>(st + 16);
+    grid_dependency_wait();       // (a no-op from the second row tile on)
+    const float x = xs * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
+    float dt = dts * (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh] + bias;
+    const uint4 bq0 = __ldg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0));
+    const uint4 bq1 = __ldg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0 + 16));
+    const uint4 cq0 = __ldg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0));
+    const uint4 cq1 = __ldg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0 + 16));
+    if (a.dt_softplus) dt = softplus_f(dt);
+    const float dtx = dt * x, dA = fast_exp2(nA * dt);
+    const uint32_t sw[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+    const uint32_t bw[8] = {bq0.x, bq0.y, bq0.z, bq0.w, bq1.x, bq1.y, bq1.z, bq1.w};
+    const uint32_t cw[8] = {cq0.x, cq0.y, cq0.z, cq0.w, cq1.x, cq1.y, cq1.z, cq1.w};
+    uint32_t ow[8];
+    float y = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      int q[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float sv = (float)(int8_t)(sw[w] >> (8 * k));
+        const float bb = Bs * (float)(int8_t)(bw[w] >> (8 * k));
+        const float cc = Cs * (float)(int8_t)(cw[w] >> (8 * k));
+        const float snew = fmaf(bb, dtx, (ss * sv) * dA);
+        q[k] = __float2int_rn(snew * inv);
+        y = fmaf(snew, cc, y);
+      }
+      ow[w] = pack4_sat_s8(q[0], q[1], q[2], q[3]);
+    }
+    *reinterpret_cast<uint4*>(st) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    *reinterpret_cast<uint4*>(st + 16) = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+    y += __shfl_xor_sync(0xffffffffu, y, 1);
+    y += __shfl_xor_sync(0xffffffffu, y, 2);
+    if (sub == 0) {
+      if (a.D != nullptr) y = fmaf(x, Dv, y);
+      static_cast<__half*>(a.out)[(int64_t)b * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
+    }
+  }
+}
+
 // Pipelined form of the streaming decode step for a fully contiguous state (B, H, P, N): the state is a flat matrix of
 // rows, so a tile of consecutive rows is one contiguous 8 KB block.  A persistent CTA walks a contiguous range of tiles
 // through a four-slot shared-memory ring: bulk-copy loads run two tiles ahead (completion on an mbarrier), the tile is
@@ -809,6 +875,16 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
   QB_REQUIRE(!a->grouped || (a->head_group_range && a->dim_group_range && a->nhead_groups > 0 && a->ndim_groups > 0),
              QB_ERR_INVALID_ARG, "sscan_update: grouped scales need the range tables");
   // warp-autonomous kernel: the Mamba2 decode shape (d_state 128, A tied across the state, per-tensor scales), fully
+  // few (batch, head) pairs: the low-latency kernel, one CTA per pair
+  if (a->dstate == 128 && a->A_sn == 0 && a->A_sp == 0 && a->dt_sp == 0 && !a->grouped && a->z == nullptr && a->headdim % 64 == 0 &&
+      (a->D == nullptr || a->D_sp == 0) && (a->dt_bias == nullptr || a->bias_sp == 0) && a->state_sp % 16 == 0 && a->state_sh % 16 == 0 &&
+      a->state_sb % 16 == 0 && aligned(a->state, 16) && aligned(a->Bm, 16) && aligned(a->Cm, 16) && a->B_sb % 16 == 0 && a->B_sg % 16 == 0 &&
+      a->C_sb % 16 == 0 && a->C_sg % 16 == 0 && (int64_t)a->batch * a->nheads <= (int64_t)sm_count() * 4 && a->batch <= 65535 &&
+      !path_override(QB_PATH_UPDATE_CTA_TILES)) {
+    launch_dependent(sscan_update_small_kernel, dim3((unsigned)a->nheads, (unsigned)a->batch), dim3(256), 0, (cudaStream_t)stream, *a);
+    QB_LAUNCH_OK("sscan_update_small_kernel");
+    return QB_OK;
+  }
   // contiguous state, 16-row tiles inside one head
   if (a->dstate == 128 && a->A_sn == 0 && !a->grouped && a->headdim % kWTileRows == 0 && aligned(a->state, 16) &&
       a->state_sp == a->dstate && a->state_sh == (int64_t)a->headdim * a->dstate &&

@@ -165,7 +165,7 @@ class QuambaMixerModel(nn.Module):
             y = s.update(ssm_state, conv["x"], dt, conv["B"], conv["C"], z=None)
             a = ops.decode_gate_had_quant(y.flatten(-2), zxbcdt[:, :m.d_ssm], m.norm.z_scale, m.norm.weight, m.norm.eps,
                                           m.norm.group_size or m.d_ssm, m.had.had_scale / m.had.x_H_scale)
-            h = m.out_proj(a)
+            h = ops.decode_linear(a, m.out_proj.prepared(), m.out_proj.input_scale)[:, :m.d_model]
         logits, _ = ops.decode_norm_linear(h, residual, self.norm_f.weight, self.norm_f.eps, self.norm_f.output_scale,
                                            lm_head.prepared(), lm_head.input_scale, False, self.residual_in_fp32)
         return logits[:, :lm_head.out_features]

@@ -813,6 +813,18 @@ def decode_norm_linear(x, residual, norm_weight, eps, norm_out_scale, prep, s_to
     return out, residual_out
 
 
+def decode_linear(a, prep, s_tok, out_int8=False):
+    """Decode-sized W4A8 product of int8 rows ``a`` (1 to 4 rows) on the low-latency kernel: (rows, n) fp16 or int8."""
+    rows, k = a.shape
+    w, s4 = _decode_weight(prep)
+    out = torch.empty((rows, prep.size_n), dtype=torch.int8 if out_int8 else torch.float16, device=a.device)
+    args = _lib.make("qb_decode_norm_linear_args", a_int8=_p(a), w=_p(w), s_channel_nat=_p(prep.sc), s_tok=_p(s_tok), out=_p(out),
+                     x_row_stride=a.stride(0), out_row_stride=out.stride(0), rows=rows, n=prep.size_n, k=k, w_is_s4=s4,
+                     out_int8=int(out_int8))
+    _run("qb_decode_norm_linear", args, a)
+    return out
+
+
 def decode_gate_had_quant(y, z, z_scale, norm_weight, eps, group_size, had_scale):
     """y (rows, d) fp16, z (rows, d) int8 (a strided view is fine) -> gate, grouped RMSNorm, Hadamard rotation, int8:
     QRMSNormGated (fp16 output) followed by QHadamard in one launch.  Returns (rows, d) int8."""
