@@ -278,7 +278,8 @@ int qb_sscan_fwd(const qb_sscan_fwd_args* a, void* stream);
  * Scale layouts: per-tensor (grouped == 0: x_scales / state_scale / B_scale / C_scale point to
  * one float) or grouped (x_scales [G,HG,DG], state_scale [G,HG,DG,N], B_scale / C_scale [G],
  * ranges as in the conv).  State requantised with rint (half to even) + clamp; out (B, H, P)
- * fp16 uses the un-requantised fp32 state.
+ * fp16 uses the un-requantised fp32 state.  early_launch: see the decode entry points below; 0 unless the next kernel
+ * on the stream is one of them.
  * ------------------------------------------------------------------------------------------ */
 typedef struct {
   int8_t* state;
@@ -335,6 +336,7 @@ typedef struct {
   int32_t ndim_groups;
   int32_t dt_bias_is_half;
   int32_t dt_softplus;
+  int32_t early_launch;
 } qb_sscan_update_args;
 int qb_sscan_update(const qb_sscan_update_args* a, void* stream);
 
@@ -597,7 +599,9 @@ int qb_embedding_lookup(const qb_embedding_args* a, void* stream);
 
 /* Greedy next token: out[r] = index of the largest of the n fp16 logits of row r (lowest index among equals).
  * Replaces the logits.argmax(dim=-1) of the reference's greedy decode loop (profile_mamba.py:317-392), so that a
- * captured decode step can feed its own next input.  row_stride in elements. */
+ * captured decode step can feed its own next input.  row_stride in elements; at most 1024 rows per call.  The kernel
+ * keeps its partial results in a small array inside the library: calls that can overlap on the GPU (different streams)
+ * must not be issued concurrently. */
 int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t n, int64_t* out, void* stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -605,6 +609,10 @@ int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t
  * (block QRMSNorm, quamba/qNorm.py:52-87, then W4A8QMamba2.step, quamba/qMamba2.py:997-1020); here four launches cover
  * a layer (these two, the state update and the out_proj product), each bit-compatible with the separate entry points above up to their stated tolerances.
  *
+ * early_launch (here, in qb_decode_gate_had_quant_args and in qb_sscan_update_args): non-zero lets the NEXT kernel on the
+ *   stream start its own set-up while this one still runs (programmatic dependent launch).  Set it only when that next
+ *   kernel is one of these decode entry points (or qb_sscan_update on its one-CTA-per-head path, or qb_argmax_rows): they read
+ *   their producer's output past the L1 cache, which an early start requires; other kernels of the library do not.
  * qb_decode_norm_linear: h = x (+ residual); residual_out = h; a = int8(rmsnorm(h) * norm_weight / norm_out_scale);
  *   out (rows, n) = a @ W^T scaled by s_channel_nat[n] * s_tok, int8 (rint, saturating) or fp16.  W is the int8 copy
  *   qb_w4a8_unpack makes (n, k), or with w_is_s4 != 0 the nibble copy qb_w4a8_pack_nibbles makes (per-channel weights).
@@ -656,6 +664,7 @@ typedef struct {
   int32_t conv_dim;
   int32_t conv_x_dim;
   int32_t conv_gn;
+  int32_t early_launch;
   float eps;
   float norm_out_scale;
   float conv_scale_in_x;
@@ -678,6 +687,7 @@ typedef struct {
   int32_t rows;
   int32_t d;
   int32_t group_size;
+  int32_t early_launch;
   float z_scale;
   float eps;
   float had_scale;

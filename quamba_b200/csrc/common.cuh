@@ -48,8 +48,13 @@ void set_error(const char* fmt, ...);
 // error of a failed launch is picked up by QB_LAUNCH_OK like that of a <<<>>> launch.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Lets the NEXT programmatic dependent on the stream be scheduled now: its CTAs then run up to their own
-// grid_dependency_wait (set-up, prefetch of weights) while this kernel is still working.  Only for kernels whose whole
-// grid is resident at once (the small kernels of a decode step): waiting dependents hold SM resources.
+// grid_dependency_wait (set-up, prefetch of weights) while this kernel is still working.  Two conditions, both the
+// caller's to guarantee (hence an explicit flag on the entry points that offer it):
+//  * the whole grid is resident at once (the small kernels of a decode step): waiting dependents hold SM resources;
+//  * the dependent reads what this kernel writes with loads that bypass L1 (__ldcg).  An SM's L1 is not invalidated
+//    between a dependent's early start and its wait, so a cached (ld.global / __ldg) read after the wait can return a line
+//    that the SM cached before this kernel overwrote it: a captured decode step produced garbage that way, while the same
+//    launches issued one by one from the host, which never overlap, were correct.
 __device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 template <typename... KArgs, typename... Args>
 inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

@@ -23,7 +23,6 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kNW = 2;              // output columns per warp and pass
 constexpr int kMaxRows = 4;         // batch rows a launch takes
 
-__constant__ float c_dec_had[4][40 * 40];      // the order-12 / 20 / 28 / 40 matrices as +-1.0f, row-major
 
 __device__ __forceinline__ float warp_sum_f(float v) {
 #pragma unroll
@@ -166,7 +165,9 @@ __device__ __forceinline__ FinishPre finish_prefetch(const Linear& L, const Conv
     const int s = c < cv.end0 ? 0 : (c < cv.end1 ? 1 : 2);
     f.seg = s;
     const int8_t* st = cv.state + (int64_t)m * cv.sb + (int64_t)c * cv.sd;
-    f.w0 = st[cv.sw]; f.w1 = st[2 * cv.sw]; f.w2 = st[3 * cv.sw];
+    f.w0 = __ldcg(reinterpret_cast<const signed char*>(st) + cv.sw);      // rewritten every step: L2 reads
+    f.w1 = __ldcg(reinterpret_cast<const signed char*>(st) + 2 * cv.sw);
+    f.w2 = __ldcg(reinterpret_cast<const signed char*>(st) + 3 * cv.sw);
     f.wt = *reinterpret_cast<const int*>(cv.weight + (int64_t)c * 4);
     f.so = __ldg(cv.out_scale[s]);
     f.bias_term = cv.bias != nullptr ? cv.scale_bias[s] * (float)cv.bias[c] : 0.0f;
@@ -198,18 +199,20 @@ __device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, const
   cv.dst[s][(int64_t)m * width + (c - cbase)] = (int8_t)round_away_s8(v / f.so);
 }
 
-// Ask L2 for the weight rows of this warp's first pass.  Weights do not depend on the kernel before this one, so the call
-// sits ahead of the dependency wait and of the shared-memory prologue: HBM delivers while the prologue computes.
+// Ask L2 for every weight row this warp will stream (all its passes).  Weights do not depend on the kernel before this
+// one, so the call sits ahead of the dependency wait and of the shared-memory prologue: HBM delivers while the prologue
+// computes, and each pass then costs a round trip to L2 instead of one to HBM.
 template <bool S4>
 __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * kWarps + warp) * kNW;
   const int64_t row_bytes = S4 ? L.k / 2 : L.k;
-  for (int j = 0; j < kNW; ++j) {
-    if (n0 + j >= L.n) break;
-    const uint8_t* rowp = L.w + (int64_t)(n0 + j) * row_bytes;
-    for (int64_t off = (int64_t)lane * 128; off < row_bytes; off += 32 * 128)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + off));
+  for (int n0 = (blockIdx.x * kWarps + warp) * kNW; n0 < L.n; n0 += (int)gridDim.x * kWarps * kNW) {
+    for (int j = 0; j < kNW; ++j) {
+      if (n0 + j >= L.n) break;
+      const uint8_t* rowp = L.w + (int64_t)(n0 + j) * row_bytes;
+      for (int64_t off = (int64_t)lane * 128; off < row_bytes; off += 32 * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(rowp + off));
+    }
   }
 }
 
@@ -255,7 +258,7 @@ struct NormIn {
   void* residual_out;       // nullable
   const __half* weight;     // (k)
   int64_t x_stride, res_stride, res_out_stride;
-  int res_f32, res_out_f32;
+  int res_f32, res_out_f32, early_launch;
   float eps, out_scale;
 };
 
@@ -266,7 +269,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   __shared__ float red[kWarps];
   int8_t* sA = reinterpret_cast<int8_t*>(dsm);                 // MB rows of k int8
   const int K = L.k;
-  grid_dependency_launch();
+  if (nin.early_launch) grid_dependency_launch();
   prefetch_first_columns<S4>(L);
   const FinishPre pre = first_pass_prefetch<MB>(L, cv, rows);
   const int chunks = K / 8;
@@ -280,7 +283,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
     for (int m = 0; m < MB; ++m) {
       const int row = min(m, rows - 1);
       for (int c = threadIdx.x; c < K / 16; c += kThreads)
-        *(reinterpret_cast<uint4*>(sA + (int64_t)m * K) + c) = __ldg(reinterpret_cast<const uint4*>(nin.a_int8 + (int64_t)row * nin.x_stride) + c);
+        *(reinterpret_cast<uint4*>(sA + (int64_t)m * K) + c) = __ldcg(reinterpret_cast<const uint4*>(nin.a_int8 + (int64_t)row * nin.x_stride) + c);
     }
     __syncthreads();
     stream_columns<MB, S4>(L, cv, sA, rows, pre);
@@ -296,18 +299,19 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
     for (int i = 0; i < 4; ++i) {
       const int c = threadIdx.x + i * kThreads;
       if (c < chunks) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(nin.x + (int64_t)row * nin.x_stride) + c);
+        // x and the residual come from the kernels just before: L2 reads (__ldcg), see grid_dependency_launch
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(nin.x + (int64_t)row * nin.x_stride) + c);
         const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y; }
         if (nin.residual != nullptr) {
           if (nin.res_f32) {
             const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(nin.residual) + (int64_t)row * nin.res_stride) + 2 * c;
-            const float4 a = __ldg(r), b = __ldg(r + 1);
+            const float4 a = __ldcg(r), b = __ldcg(r + 1);
             v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
             v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
           } else {
-            const uint4 rr = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(nin.residual) + (int64_t)row * nin.res_stride) + c);
+            const uint4 rr = __ldcg(reinterpret_cast<const uint4*>(static_cast<const __half*>(nin.residual) + (int64_t)row * nin.res_stride) + c);
             const __half2* rh = reinterpret_cast<const __half2*>(&rr);
 #pragma unroll
             for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(rh[e]); v[i][2 * e] += f.x; v[i][2 * e + 1] += f.y; }
@@ -360,7 +364,8 @@ struct GateIn {
   const int8_t* z;          // (rows, d) with row stride z_stride
   const __half* weight;     // (d)
   int64_t y_stride, z_stride;
-  int d, group_size, special, table;    // d = special_rows * 128; table: index into c_dec_had, or -1 for Sylvester rows
+  int early_launch;
+  int d, group_size, special, table;    // d = special_rows * 128; table: index into c_dec_neg, or -1 for Sylvester rows
   float z_scale, eps, had_scale;        // had_scale: (1 / sqrt(d)) / x_H_scale
 };
 
@@ -369,9 +374,11 @@ struct GateIn {
 // shuffles), then produces ONE block of 128 outputs of the S-point stage (S multiply-adds per thread).  Doing the S-point
 // stage for all S blocks in every CTA of the product kernel was tried first: 5 000 instructions per warp of serial
 // prologue, 28 us for a 6.6 MB product.
-constexpr int kHadThreads = 128;
+constexpr int kHadThreads = 256;
 constexpr int kHadWarps = kHadThreads / 32;
-constexpr int kMaxRowsPerWarp = 16;      // d / 128 <= 64 rows of 128 over 4 warps
+constexpr int kMaxRowsPerWarp = 8;       // d / 128 <= 64 rows of 128 over 8 warps
+
+__constant__ unsigned long long c_dec_neg[4][40];     // row i of the order-12 / 20 / 28 / 40 matrix: bit j set <=> entry -1
 
 __global__ void __launch_bounds__(kHadThreads)
 decode_gate_had_quant_kernel(GateIn gin, int8_t* __restrict__ out, int64_t out_stride) {
@@ -381,17 +388,23 @@ decode_gate_had_quant_kernel(GateIn gin, int8_t* __restrict__ out, int64_t out_s
   float* buf = reinterpret_cast<float*>(dsm);                         // d floats: the row after the 128-point stage
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.y, iout = blockIdx.x;
-  grid_dependency_launch();
+  if (gin.early_launch) grid_dependency_launch();
+  // constants first (norm weights, the sign row of this CTA's output block): they do not depend on the kernel before
+  uint2 wr[kMaxRowsPerWarp];
+#pragma unroll
+  for (int i = 0; i < kMaxRowsPerWarp; ++i)
+    wr[i] = __ldg(reinterpret_cast<const uint2*>(gin.weight + min(warp + i * kHadWarps, S - 1) * 128) + lane);
+  const unsigned long long neg = gin.table >= 0 ? c_dec_neg[gin.table][iout] : 0ull;
   grid_dependency_wait();
-  // A warp owns rows r = warp, warp + 4, ... of the (S x 128) view; a lane holds four neighbours of each.
+  // A warp owns rows r = warp, warp + 8, ... of the (S x 128) view; a lane holds four neighbours of each.
   float f[kMaxRowsPerWarp][4];
   uint2 yr[kMaxRowsPerWarp];
   uint32_t zr[kMaxRowsPerWarp];
 #pragma unroll
   for (int i = 0; i < kMaxRowsPerWarp; ++i) {
     const int r = min(warp + i * kHadWarps, S - 1);
-    yr[i] = __ldg(reinterpret_cast<const uint2*>(gin.y + (int64_t)row * gin.y_stride + r * 128) + lane);
-    zr[i] = __ldg(reinterpret_cast<const uint32_t*>(gin.z + (int64_t)row * gin.z_stride + r * 128) + lane);
+    yr[i] = __ldcg(reinterpret_cast<const uint2*>(gin.y + (int64_t)row * gin.y_stride + r * 128) + lane);   // L2 reads:
+    zr[i] = __ldcg(reinterpret_cast<const uint32_t*>(gin.z + (int64_t)row * gin.z_stride + r * 128) + lane); // see grid_dependency_launch
   }
 #pragma unroll
   for (int i = 0; i < kMaxRowsPerWarp; ++i) {
@@ -413,12 +426,16 @@ decode_gate_had_quant_kernel(GateIn gin, int8_t* __restrict__ out, int64_t out_s
     }
   }
   __syncthreads();
-  // group sums in a fixed order (no atomics: the result must not depend on which warp arrives first)
-  if (threadIdx.x < D / gin.group_size) {
-    const int rows_per_group = gin.group_size / 128;
-    float t = 0.f;
-    for (int r = 0; r < rows_per_group; ++r) t += rowsum[threadIdx.x * rows_per_group + r];
-    gsum[threadIdx.x] = t;
+  // group sums in a fixed order (no atomics: the result must not depend on which warp arrives first): warp g adds the
+  // rows of group g, lane-strided partial sums then a shuffle tree
+  {
+    const int ngroups = D / gin.group_size, rows_per_group = gin.group_size / 128;
+    for (int g = warp; g < ngroups; g += kHadWarps) {
+      float t = 0.f;
+      for (int r = lane; r < rows_per_group; r += 32) t += rowsum[g * rows_per_group + r];
+      t = warp_sum_f(t);
+      if (lane == 0) gsum[g] = t;
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -427,8 +444,7 @@ decode_gate_had_quant_kernel(GateIn gin, int8_t* __restrict__ out, int64_t out_s
     if (r < S) {
       // normalise and round to fp16 as the separate norm kernel stores it
       const float rstd = 1.0f / sqrtf(gsum[(r * 128) / gin.group_size] / (float)gin.group_size + gin.eps);
-      const uint2 wr = __ldg(reinterpret_cast<const uint2*>(gin.weight + r * 128) + lane);
-      const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wr[i]);
       const float2 w0 = __half22float2(wh[0]), w1 = __half22float2(wh[1]);
       const float t0 = __half2float(__float2half_rn(f[i][0] * rstd * w0.x)), t1 = __half2float(__float2half_rn(f[i][1] * rstd * w0.y));
       const float t2 = __half2float(__float2half_rn(f[i][2] * rstd * w1.x)), t3 = __half2float(__float2half_rn(f[i][3] * rstd * w1.y));
@@ -447,26 +463,25 @@ decode_gate_had_quant_kernel(GateIn gin, int8_t* __restrict__ out, int64_t out_s
     }
   }
   __syncthreads();
-  // output block iout of the S-point stage: one column per thread, four partial sums for instruction-level parallelism
+  // output block iout of the S-point stage: threads (column, half of the terms); signs from the row's bit mask (order
+  // 12 .. 40) or the Sylvester rule (power-of-two S); two partial sums per thread, combined through shared memory
   {
-    const int col = threadIdx.x;
-    const float* tab = gin.table >= 0 ? c_dec_had[gin.table] + iout * S : nullptr;
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    int j = 0;
-    for (; j + 4 <= S; j += 4) {
-      const float b0 = buf[j * 128 + col], b1 = buf[(j + 1) * 128 + col], b2 = buf[(j + 2) * 128 + col], b3 = buf[(j + 3) * 128 + col];
-      if (tab != nullptr) {
-        a0 = fmaf(tab[j], b0, a0); a1 = fmaf(tab[j + 1], b1, a1); a2 = fmaf(tab[j + 2], b2, a2); a3 = fmaf(tab[j + 3], b3, a3);
-      } else {
-        a0 += (__popc(iout & j) & 1) ? -b0 : b0; a1 += (__popc(iout & (j + 1)) & 1) ? -b1 : b1;
-        a2 += (__popc(iout & (j + 2)) & 1) ? -b2 : b2; a3 += (__popc(iout & (j + 3)) & 1) ? -b3 : b3;
-      }
-    }
-    for (; j < S; ++j) {
+    const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
+    const int j0 = half * ((S + 1) / 2), j1 = min(S, j0 + (S + 1) / 2);
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = j0; j < j1; j += 2) {
       const float b0 = buf[j * 128 + col];
-      if (tab != nullptr) a0 = fmaf(tab[j], b0, a0); else a0 += (__popc(iout & j) & 1) ? -b0 : b0;
+      const float b1 = j + 1 < j1 ? buf[(j + 1) * 128 + col] : 0.f;
+      const uint32_t s0 = gin.table >= 0 ? (uint32_t)((neg >> j) & 1ull) : (uint32_t)(__popc(iout & j) & 1);
+      const uint32_t s1 = gin.table >= 0 ? (uint32_t)((neg >> (j + 1)) & 1ull) : (uint32_t)(__popc(iout & (j + 1)) & 1);
+      a0 += __uint_as_float(__float_as_uint(b0) ^ (s0 << 31));
+      a1 += __uint_as_float(__float_as_uint(b1) ^ (s1 << 31));
     }
-    out[(int64_t)row * out_stride + iout * 128 + col] = (int8_t)round_away_s8(((a0 + a1) + (a2 + a3)) * gin.had_scale);
+    __syncthreads();                       // all reads of buf are done: its first 128 floats carry the upper half's sums
+    if (half == 1) buf[col] = a0 + a1;
+    __syncthreads();
+    if (half == 0)
+      out[(int64_t)row * out_stride + iout * 128 + col] = (int8_t)round_away_s8(((a0 + a1) + buf[col]) * gin.had_scale);
   }
 }
 
@@ -475,13 +490,12 @@ int upload_tables() {
   int dev = 0;
   QB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && done[dev]) return QB_OK;
-  static float host[4][40 * 40];
   const unsigned long long* masks[4] = {kHadNeg12, kHadNeg20, kHadNeg28, kHadNeg40};
   const int order[4] = {12, 20, 28, 40};
+  static unsigned long long hmask[4][40];
   for (int t = 0; t < 4; ++t)
-    for (int i = 0; i < order[t]; ++i)
-      for (int j = 0; j < order[t]; ++j) host[t][i * order[t] + j] = ((masks[t][i] >> j) & 1ull) ? -1.0f : 1.0f;
-  QB_CUDA_OK(cudaMemcpyToSymbol(c_dec_had, host, sizeof(host)));
+    for (int i = 0; i < 40; ++i) hmask[t][i] = i < order[t] ? masks[t][i] : 0ull;
+  QB_CUDA_OK(cudaMemcpyToSymbol(c_dec_neg, hmask, sizeof(hmask)));
   if (dev < 64) done[dev] = true;
   return QB_OK;
 }
@@ -546,6 +560,7 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
   nin.weight = static_cast<const __half*>(a->norm_weight);
   nin.x_stride = a->x_row_stride; nin.res_stride = a->residual_row_stride; nin.res_out_stride = a->residual_out_row_stride;
   nin.res_f32 = a->residual_is_f32; nin.res_out_f32 = a->residual_out_is_f32; nin.eps = a->eps; nin.out_scale = a->norm_out_scale;
+  nin.early_launch = a->early_launch;
   ConvEpi cv{};
   if (a->conv_state != nullptr) {
     QB_REQUIRE(a->out_int8 && a->conv_weight && a->conv_x && a->conv_B && a->conv_C && a->x_out_scale && a->B_out_scale && a->C_out_scale,
@@ -586,7 +601,7 @@ extern "C" int qb_decode_gate_had_quant(const qb_decode_gate_had_quant_args* a, 
   GateIn gin{};
   gin.y = static_cast<const __half*>(a->y); gin.z = a->z; gin.weight = static_cast<const __half*>(a->norm_weight);
   gin.y_stride = a->y_row_stride; gin.z_stride = a->z_row_stride; gin.d = a->d; gin.group_size = a->group_size; gin.special = S;
-  gin.table = table; gin.z_scale = a->z_scale; gin.eps = a->eps; gin.had_scale = a->had_scale;
+  gin.table = table; gin.z_scale = a->z_scale; gin.eps = a->eps; gin.had_scale = a->had_scale; gin.early_launch = a->early_launch;
   launch_dependent(decode_gate_had_quant_kernel, dim3((unsigned)S, (unsigned)a->rows), dim3(kHadThreads), (size_t)a->d * 4,
                    (cudaStream_t)stream, gin, a->out, a->out_row_stride);
   QB_LAUNCH_OK("decode_gate_had_quant_kernel");

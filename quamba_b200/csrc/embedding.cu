@@ -14,7 +14,6 @@ template <int KIND>
 __global__ void __launch_bounds__(256)
 embedding_kernel(const void* __restrict__ table, const __half* __restrict__ scales, const int64_t* __restrict__ tokens,
                  __half* __restrict__ out, int64_t n_tokens, int dim, int vocab, int* __restrict__ status) {
-  if (gridDim.x <= 64) grid_dependency_launch();    // decode-sized: the next kernel may start its set-up already
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t tok = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -58,38 +57,49 @@ embedding_kernel(const void* __restrict__ table, const __half* __restrict__ scal
 }
 
 // Greedy sampling: index of the largest logit of each row (the lowest index among equals), as int64.
-__global__ void __launch_bounds__(1024)
+// A row is scanned by kArgBlocks CTAs; each folds its slice into one 64-bit key -- the value mapped to an order-preserving
+// unsigned integer in the high word, the bitwise complement of the index in the low word, so that the largest key is the
+// largest value at the lowest index -- and publishes it with atomicMax on a per-row word of library-owned scratch; the
+// last CTA to arrive (a ticket counter) writes the token and leaves both words zeroed for the next call.  Calls whose
+// kernels overlap on the GPU (different streams) would share that scratch: issue them on one stream.
+constexpr int kArgBlocks = 32;
+constexpr int kArgMaxRows = 1024;
+__device__ unsigned long long g_arg_key[kArgMaxRows];
+__device__ unsigned int g_arg_count[kArgMaxRows];
+
+__global__ void __launch_bounds__(256)
 argmax_rows_kernel(const __half* __restrict__ logits, int64_t row_stride, int n, int64_t* __restrict__ out) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+  __shared__ unsigned long long skey[8];
   grid_dependency_wait();
-  const __half* row = logits + (int64_t)blockIdx.x * row_stride;
-  float best = -INFINITY;
-  int idx = 0x7fffffff;
-  for (int j = threadIdx.x; j < n; j += blockDim.x) {
-    const float v = __half2float(row[j]);
-    if (v > best || (v == best && j < idx)) { best = v; idx = j; }
+  const int r = blockIdx.y;
+  const __half* row = logits + (int64_t)r * row_stride;
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int j0 = blockIdx.x * per, j1 = min(n, j0 + per);
+  unsigned long long best = 0ull;
+  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
+    const uint32_t bits = __float_as_uint(__half2float(__ldcg(row + j)));     // L2 read: the producer may have let this kernel start early
+    const uint32_t ord = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
+    const unsigned long long key = ((unsigned long long)ord << 32) | (uint32_t)(~(uint32_t)j);
+    best = key > best ? key : best;
   }
-  auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float v = __shfl_xor_sync(0xffffffffu, best, o);
-    const int i = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (better(v, i, best, idx)) { best = v; idx = i; }
+    const unsigned long long v = __shfl_xor_sync(0xffffffffu, best, o);
+    best = v > best ? v : best;
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) { sv[warp] = best; si[warp] = idx; }
+  if ((threadIdx.x & 31) == 0) skey[threadIdx.x >> 5] = best;
   __syncthreads();
-  if (warp == 0) {
-    best = lane < (int)(blockDim.x >> 5) ? sv[lane] : -INFINITY;
-    idx = lane < (int)(blockDim.x >> 5) ? si[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float v = __shfl_xor_sync(0xffffffffu, best, o);
-      const int i = __shfl_xor_sync(0xffffffffu, idx, o);
-      if (better(v, i, best, idx)) { best = v; idx = i; }
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) best = skey[i] > best ? skey[i] : best;
+    atomicMax(&g_arg_key[r], best);
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&g_arg_count[r], 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      const unsigned long long k = atomicExch(&g_arg_key[r], 0ull);
+      g_arg_count[r] = 0u;
+      out[r] = k == 0ull ? 0 : (int64_t)(uint32_t)(~(uint32_t)k);
     }
-    if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
   }
 }
 
@@ -126,7 +136,8 @@ extern "C" int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t ro
   QB_REQUIRE(logits != nullptr && out != nullptr, QB_ERR_INVALID_ARG, "argmax_rows: null pointer");
   QB_REQUIRE(rows >= 0 && n > 0 && row_stride >= n, QB_ERR_INVALID_ARG, "argmax_rows: bad shape");
   if (rows == 0) return QB_OK;
-  launch_dependent(argmax_rows_kernel, dim3((unsigned)rows), dim3(1024), 0, (cudaStream_t)stream,
+  QB_REQUIRE(rows <= kArgMaxRows, QB_ERR_TOO_LARGE, "argmax_rows: at most %d rows per call", kArgMaxRows);
+  launch_dependent(argmax_rows_kernel, dim3((unsigned)kArgBlocks, (unsigned)rows), dim3(256), 0, (cudaStream_t)stream,
                    static_cast<const __half*>(logits), row_stride, n, out);
   QB_LAUNCH_OK("argmax_rows_kernel");
   return QB_OK;

@@ -171,9 +171,8 @@ template <int MB>
 __global__ void __launch_bounds__(kGemvWarps * 32, 3)
 gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restrict__ W, int64_t ldw, int M, int N, int K,
                Epilogue ep) {
-  // launched as a programmatic dependent: the next kernel may be scheduled at once, and this warp's first weight rows
-  // are requested from HBM before the wait for the kernel that produces A
-  grid_dependency_launch();
+  // launched as a programmatic dependent: this warp's first weight rows are requested from HBM before the wait for the
+  // kernel that produces A
   prefetch_rows(W, ldw, (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW, N, K);
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
@@ -246,7 +245,6 @@ __global__ void w4a8_pack_nibbles_kernel(const int8_t* __restrict__ w8, uint32_t
 template <int MB>
 __global__ void __launch_bounds__(kGemvWarps * 32, 3)
 gemv_s4_kernel(const int8_t* __restrict__ A, int64_t lda, const uint8_t* __restrict__ W4, int M, int N, int K, Epilogue ep) {
-  grid_dependency_launch();
   prefetch_rows(W4, K / 2, (blockIdx.x * kGemvWarps + (threadIdx.x >> 5)) * kNW, N, K / 2);
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;

@@ -377,7 +377,7 @@ sscan_update_stream_kernel(qb_sscan_update_args a, int iters) {
 __global__ void __launch_bounds__(256)
 sscan_update_small_kernel(qb_sscan_update_args a) {
   constexpr float kLog2e = 1.4426950408889634f;
-  grid_dependency_launch();
+  if (a.early_launch) grid_dependency_launch();
   const int hd = blockIdx.x, b = blockIdx.y;
   const int sub = threadIdx.x & 3, n0 = sub * 32;
   const int g = hd / (a.nheads / a.ngroups);
@@ -394,14 +394,16 @@ sscan_update_small_kernel(qb_sscan_update_args a) {
   const float inv = 1.0f / ss;
   for (int p = threadIdx.x >> 2; p < a.headdim; p += 64) {
     int8_t* st = a.state + (int64_t)b * a.state_sb + (int64_t)hd * a.state_sh + (int64_t)p * a.state_sp + n0;
-    const uint4 raw0 = *reinterpret_cast<const uint4*>(st), raw1 = *reinterpret_cast<const uint4*>(st + 16);
+    // the state changes every step and is read once: L2 reads, so that no line an SM cached in an earlier step is served
+    const uint4 raw0 = __ldcg(reinterpret_cast<const uint4*>(st)), raw1 = __ldcg(reinterpret_cast<const uint4*>(st + 16));
     grid_dependency_wait();       // (a no-op from the second row tile on)
-    const float x = xs * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
-    float dt = dts * (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh] + bias;
-    const uint4 bq0 = __ldg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0));
-    const uint4 bq1 = __ldg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0 + 16));
-    const uint4 cq0 = __ldg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0));
-    const uint4 cq1 = __ldg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0 + 16));
+    // inputs written by the kernel before this one: L2 reads (__ldcg), see grid_dependency_launch
+    const float x = xs * (float)__ldcg(reinterpret_cast<const signed char*>(a.x) + (int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p);
+    float dt = dts * (float)__ldcg(reinterpret_cast<const signed char*>(a.dt) + (int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh) + bias;
+    const uint4 bq0 = __ldcg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0));
+    const uint4 bq1 = __ldcg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0 + 16));
+    const uint4 cq0 = __ldcg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0));
+    const uint4 cq1 = __ldcg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0 + 16));
     if (a.dt_softplus) dt = softplus_f(dt);
     const float dtx = dt * x, dA = fast_exp2(nA * dt);
     const uint32_t sw[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
@@ -456,7 +458,6 @@ sscan_update_warp_kernel(qb_sscan_update_args a, int tiles, int* status) {
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(128) uint8_t ring_all[];
   __shared__ __align__(8) uint64_t full_all[8][kWSlots];
-  grid_dependency_launch();   // one wave of CTAs by construction: let the next dependent start its own set-up
   grid_dependency_wait();     // launched as a programmatic dependent (launch_dependent)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* ring = ring_all + warp * (kWSlots * kWTileBytes);
@@ -885,6 +886,8 @@ extern "C" int qb_sscan_update(const qb_sscan_update_args* a, void* stream) {
     QB_LAUNCH_OK("sscan_update_small_kernel");
     return QB_OK;
   }
+  QB_REQUIRE(!a->early_launch, QB_ERR_UNSUPPORTED,
+             "sscan_update: early_launch is only offered on the one-CTA-per-head decode kernel, which this call is not eligible for");
   // contiguous state, 16-row tiles inside one head
   if (a->dstate == 128 && a->A_sn == 0 && !a->grouped && a->headdim % kWTileRows == 0 && aligned(a->state, 16) &&
       a->state_sp == a->dstate && a->state_sh == (int64_t)a->headdim * a->dstate &&

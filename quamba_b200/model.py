@@ -143,7 +143,9 @@ class QuambaMixerModel(nn.Module):
                           and m.d_conv == 4 and m.d_inner == m.d_ssm and m.d_inner % 128 == 0 and not m.D_has_hdim
                           and getattr(m.had, "blocks", 1) == 1
                           and (s in (12, 20, 28, 40) or (s & (s - 1)) == 0 and s <= 64)
-                          and m.d_model % 32 == 0 and m.d_ssm // m.ngroups % 128 == 0 and m.ngroups <= 64)
+                          and m.d_model % 32 == 0 and m.d_ssm // m.ngroups % 128 == 0 and m.ngroups <= 64
+                          # the state update must land on its one-CTA-per-head kernel (the early-launch chain needs it)
+                          and m.d_state == 128 and m.headdim % 64 == 0 and m.nheads <= 128 and not m.qchunk_scan.grouped)
             self.__dict__["_fusable"] = ok
         return ok and 1 <= batch <= 4 and not _UNFUSED_DECODE
 
@@ -151,23 +153,24 @@ class QuambaMixerModel(nn.Module):
         """One token per sequence through all layers and the head; returns logits fp16 (batch, vocab)."""
         h = self.embedding(input_ids[:, 0])
         residual = None
-        for layer in self.layers:
-            m, c, s = layer.mixer, layer.mixer.conv1d, layer.mixer.qchunk_scan
-            conv_state, ssm_state = m._get_states_from_cache(inference_params, h.shape[0])
-            gn = m.ngroups * m.d_state
-            conv = dict(state=conv_state, weight=c.weight, bias=c.bias, col0=m.d_ssm, x_dim=m.d_ssm, gn=gn,
-                        scale_in=(c.wx_scale * c.x_scale, c.wB_scale * c.B_scale, c.wC_scale * c.C_scale),
-                        scale_bias=(c.bx_scale or 0.0, c.bB_scale or 0.0, c.bC_scale or 0.0),
-                        out_scales=(c.x_out_scales, c.B_out_scales, c.C_out_scales))
-            zxbcdt, residual = ops.decode_norm_linear(h, residual, layer.norm.weight, layer.norm.eps, layer.norm.output_scale,
-                                                      m.in_proj.prepared(), m.in_proj.input_scale, True, self.residual_in_fp32, conv)
-            dt = zxbcdt[:, 2 * m.d_ssm + 2 * gn:2 * m.d_ssm + 2 * gn + m.nheads]
-            y = s.update(ssm_state, conv["x"], dt, conv["B"], conv["C"], z=None)
-            a = ops.decode_gate_had_quant(y.flatten(-2), zxbcdt[:, :m.d_ssm], m.norm.z_scale, m.norm.weight, m.norm.eps,
-                                          m.norm.group_size or m.d_ssm, m.had.had_scale / m.had.x_H_scale)
-            h = ops.decode_linear(a, m.out_proj.prepared(), m.out_proj.input_scale)[:, :m.d_model]
-        logits, _ = ops.decode_norm_linear(h, residual, self.norm_f.weight, self.norm_f.eps, self.norm_f.output_scale,
-                                           lm_head.prepared(), lm_head.input_scale, False, self.residual_in_fp32)
+        with ops.early_dependents():
+            for layer in self.layers:
+                m, c, s = layer.mixer, layer.mixer.conv1d, layer.mixer.qchunk_scan
+                conv_state, ssm_state = m._get_states_from_cache(inference_params, h.shape[0])
+                gn = m.ngroups * m.d_state
+                conv = dict(state=conv_state, weight=c.weight, bias=c.bias, col0=m.d_ssm, x_dim=m.d_ssm, gn=gn,
+                            scale_in=(c.wx_scale * c.x_scale, c.wB_scale * c.B_scale, c.wC_scale * c.C_scale),
+                            scale_bias=(c.bx_scale or 0.0, c.bB_scale or 0.0, c.bC_scale or 0.0),
+                            out_scales=(c.x_out_scales, c.B_out_scales, c.C_out_scales))
+                zxbcdt, residual = ops.decode_norm_linear(h, residual, layer.norm.weight, layer.norm.eps, layer.norm.output_scale,
+                                                          m.in_proj.prepared(), m.in_proj.input_scale, True, self.residual_in_fp32, conv)
+                dt = zxbcdt[:, 2 * m.d_ssm + 2 * gn:2 * m.d_ssm + 2 * gn + m.nheads]
+                y = s.update(ssm_state, conv["x"], dt, conv["B"], conv["C"], z=None)
+                a = ops.decode_gate_had_quant(y.flatten(-2), zxbcdt[:, :m.d_ssm], m.norm.z_scale, m.norm.weight, m.norm.eps,
+                                              m.norm.group_size or m.d_ssm, m.had.had_scale / m.had.x_H_scale)
+                h = ops.decode_linear(a, m.out_proj.prepared(), m.out_proj.input_scale)[:, :m.d_model]
+            logits, _ = ops.decode_norm_linear(h, residual, self.norm_f.weight, self.norm_f.eps, self.norm_f.output_scale,
+                                               lm_head.prepared(), lm_head.input_scale, False, self.residual_in_fp32)
         return logits[:, :lm_head.out_features]
 
     def forward(self, input_ids, inference_params=None, num_last_tokens=0, **mixer_kwargs):

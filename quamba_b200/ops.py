@@ -278,6 +278,22 @@ class quant_sscan_cuda:
 
 
 # ------------------------------------------------------------------------------------------------
+# Programmatic early launch between the kernels of a fused decode step: the kernels named in the header's early_launch note
+# read their producer's output past L1, so each may let its successor start while it runs.  The switch is on only inside
+# QuambaMixerModel.decode_step_fused, whose launch sequence consists of exactly those kernels.
+_EARLY = False
+
+
+class early_dependents:
+    def __enter__(self):
+        global _EARLY
+        self.prev, _EARLY = _EARLY, True
+
+    def __exit__(self, *exc):
+        global _EARLY
+        _EARLY = self.prev
+
+
 def _update(state, q_x, x_scales, hgr, dgr, q_dt, dt_scale, q_A_log, A_log_scale, ssm_state_scale, q_B, B_scale,
             q_C, C_scale, q_D, D_scale, q_z, z_scale, dt_bias, dt_bias_scale, dt_softplus, grouped):
     has_heads = state.dim() > 3
@@ -343,7 +359,8 @@ def _update(state, q_x, x_scales, hgr, dgr, q_dt, dt_scale, q_A_log, A_log_scale
         bias_sh=dt_bias.stride(0) if dt_bias is not None else 0, bias_sp=dt_bias.stride(1) if dt_bias is not None else 0,
         out_sb=out.stride(0), out_sh=out.stride(1), batch=batch, nheads=nheads, headdim=dim, dstate=dstate,
         ngroups=ngroups, grouped=int(grouped), nhead_groups=hgr.shape[1] if grouped else 0,
-        ndim_groups=dgr.shape[2] if grouped else 0, dt_bias_is_half=bias_is_half, dt_softplus=int(bool(dt_softplus)))
+        ndim_groups=dgr.shape[2] if grouped else 0, dt_bias_is_half=bias_is_half, dt_softplus=int(bool(dt_softplus)),
+        early_launch=int(_EARLY))
     _run("qb_sscan_update", args, q_x)
     return out if has_heads else out.squeeze(1)
 
@@ -808,7 +825,8 @@ def decode_norm_linear(x, residual, norm_weight, eps, norm_out_scale, prep, s_to
                      x_row_stride=x.stride(0), residual_row_stride=residual.stride(0) if residual is not None else 0,
                      residual_out_row_stride=residual_out.stride(0), out_row_stride=out.stride(0), rows=rows, n=prep.size_n,
                      k=k, w_is_s4=s4, out_int8=int(out_int8), residual_is_f32=int(residual is not None and residual.dtype == torch.float32),
-                     residual_out_is_f32=int(res_dtype == torch.float32), eps=float(eps), norm_out_scale=float(norm_out_scale), **kw)
+                     residual_out_is_f32=int(res_dtype == torch.float32), eps=float(eps), norm_out_scale=float(norm_out_scale),
+                     early_launch=int(_EARLY), **kw)
     _run("qb_decode_norm_linear", args, x)
     return out, residual_out
 
@@ -820,7 +838,7 @@ def decode_linear(a, prep, s_tok, out_int8=False):
     out = torch.empty((rows, prep.size_n), dtype=torch.int8 if out_int8 else torch.float16, device=a.device)
     args = _lib.make("qb_decode_norm_linear_args", a_int8=_p(a), w=_p(w), s_channel_nat=_p(prep.sc), s_tok=_p(s_tok), out=_p(out),
                      x_row_stride=a.stride(0), out_row_stride=out.stride(0), rows=rows, n=prep.size_n, k=k, w_is_s4=s4,
-                     out_int8=int(out_int8))
+                     out_int8=int(out_int8), early_launch=int(_EARLY))
     _run("qb_decode_norm_linear", args, a)
     return out
 
@@ -832,6 +850,7 @@ def decode_gate_had_quant(y, z, z_scale, norm_weight, eps, group_size, had_scale
     out = torch.empty((rows, d), dtype=torch.int8, device=y.device)
     args = _lib.make("qb_decode_gate_had_quant_args", y=_p(y), z=_p(z), norm_weight=_p(norm_weight), out=_p(out),
                      y_row_stride=y.stride(0), z_row_stride=z.stride(0), out_row_stride=out.stride(0), rows=rows, d=d,
-                     group_size=group_size, z_scale=float(z_scale), eps=float(eps), had_scale=float(had_scale))
+                     group_size=group_size, z_scale=float(z_scale), eps=float(eps), had_scale=float(had_scale),
+                     early_launch=int(_EARLY))
     _run("qb_decode_gate_had_quant", args, y)
     return out
