@@ -51,6 +51,16 @@ def peaks():
     return out
 
 
+def gemm_traffic():
+    """DRAM bytes (read + written) per launch of the GEMM kernel at the prefill shapes, from the committed summary of an ncu
+    launch list of this benchmark; (None, None) when the file is absent."""
+    f = ROOT / "profiles" / "model_2p7b_w4a8_traffic.json"
+    if not f.exists():
+        return None, None
+    t = json.loads(f.read_text())
+    return t["dram_bytes_read_per_launch"] + t["dram_bytes_write_per_launch"], f"{t['source']} (captured {t['captured']})"
+
+
 def model_flops_and_bytes(m, L, group_size):
     """Algorithmic int8 flops of one prefill and HBM bytes of one decode token (weights + states + head + embedding row)."""
     D, H, P, G, N = m["d_model"] * m["expand"], m["d_model"] * m["expand"] // m["headdim"], m["headdim"], m["ngroups"], m["d_state"]
@@ -303,8 +313,9 @@ def run_ours(args, rank, local_rank, world):
     top_ms = sp[top]["ms"]
     if top in ("qb_w4a8_gemm", "qb_w8a8_gemm"):
         achieved = m["n_layer"] * gemm_flops_layer / (top_ms * 1e-3) / 1e12
+        traffic, traffic_source = gemm_traffic()
         roof = {"kernel": "gemm_s8_tcgen05 (in_proj + out_proj of 64 layers)", "bound": "tensor", "achieved": achieved, "peak": pk["i8"],
-                "unit": "TOP/s", "frac": achieved / pk["i8"], "traffic": None, "peak_source": pk["i8_source"],
+                "unit": "TOP/s", "frac": achieved / pk["i8"], "traffic": traffic, "traffic_source": traffic_source, "peak_source": pk["i8_source"],
                 "algorithmic_flops": m["n_layer"] * gemm_flops_layer, "ms": top_ms}
     else:
         roof = {"kernel": top, "bound": "hbm", "achieved": None, "peak": pk["hbm"], "unit": "GB/s", "frac": None, "traffic": None,

@@ -33,10 +33,18 @@ WORKLOAD = ("configs[1]: Mamba2 int8 causal_conv1d + SSD chunk scan, batch 4, se
             "ngroups 1, d_state 128, chunk 256, d_conv 4")
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one ssd_tc_kernel launch, from an ncu pass over this very benchmark
-# (batch 4: 65.2 MB read + 47.3 MB written; it grows with the number of (batch, head) pairs, hence per batch row).  Reads
-# are the inputs plus the widened B / C; of the 86 MB the kernel writes, part is still dirty in the 126 MB L2 when it ends.
-SSD_TRAFFIC_PER_BATCH_ROW = (65.17e6 + 47.30e6) / 4
+def ssd_traffic(batch_rows):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one ssd_tc_kernel launch, from the committed summary of an ncu pass
+    over this very benchmark (it grows with the number of (batch, head) pairs, hence scaled by batch rows).  Returns
+    (bytes, source) or (None, None) when the summary file is absent."""
+    import json
+    from pathlib import Path
+    f = Path(__file__).resolve().parent / "profiles" / "mixer_core_cfg2_traffic.json"
+    if not f.exists():
+        return None, None
+    t = json.loads(f.read_text())
+    per_row = (t["dram_bytes_read_per_launch"] + t["dram_bytes_write_per_launch"]) / t["batch_rows"]
+    return per_row * batch_rows, f"{t['source']} (captured {t['captured']})"
 
 
 def algorithmic_bytes():
@@ -350,7 +358,7 @@ def run(args):
                 "d2h_bytes_per_step": int(host_y.numel() * 2 + host_f.numel())},
         "gpu_launches": 3 * steps,
         "roofline": {"kernel": "ssd_tc_kernel (+ ssd_prep_kernel)", "bound": "hbm", "achieved": ssd_gbs, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": ssd_gbs / hbm_peak, "traffic": SSD_TRAFFIC_PER_BATCH_ROW * B, "peak_source": "measured" if peaks else "fallback",
+                     "frac": ssd_gbs / hbm_peak, "traffic": ssd_traffic(B)[0], "traffic_source": ssd_traffic(B)[1], "peak_source": "measured" if peaks else "fallback",
                      "algorithmic_bytes": ssd_bytes, "ms": ssd_ms,
                      # the same kernel against the tensor roofline (the op is balanced between the two): dense fp16 MMA
                      # flops it issues per 128-token block (C.B^T 128x128x128 + three 128x64x128) over the measured bf16 peak

@@ -23,4 +23,19 @@ from .embedding import W4O16Embedding, W8O16Embedding  # noqa: F401
 from .mixer import W4A8QMamba2, W8A8QMamba2  # noqa: F401
 from .model import InferenceParams, QuambaConfig, QuambaLMHeadModel, QuambaMixerModel  # noqa: F401
 
+
+
+def check_device_status(stream=None):
+    """Waits for ``stream`` (default: torch's current stream) and raises if a kernel of this library gave up on one of
+    its bounded device waits, or rejected an input on the device (an embedding id out of range), since the last check.
+    Outputs are valid only if this passes; call it at the natural synchronisation points of a caller (the end of a
+    generation loop, after a benchmark step, before results leave the device).  ``generate_greedy`` does."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    elif hasattr(stream, "cuda_stream"):
+        stream = stream.cuda_stream
+    _lib.read_device_status(stream)
+
+
 __version__ = "0.1.0"

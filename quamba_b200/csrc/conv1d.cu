@@ -1,13 +1,14 @@
 // int8 causal depthwise conv1d (+bias, SiLU, int8 requantisation) for sm_100a.
 //
 // Both layouts are pure streaming passes (1 byte in, 1 byte out per element), so the kernels
-// are organised around 16-byte coalesced loads/stores and keep the arithmetic per element to
-// one byte-permute (window slide), one dp4a (the <=4 taps), one fma, one tanh.approx (SiLU)
-// and the rounding.
+// are organised around coalesced loads/stores and keep the arithmetic per element to one
+// byte-permute (window slide), one dp4a (the <=4 taps), one fma, one tanh.approx (SiLU) and the
+// rounding.
 //
-//   channel-last  (Quamba2 xBC, and Quamba1 when the channel stride is 1): a thread owns 16
-//                 adjacent channels and walks TL consecutive time steps, keeping each channel's
-//                 last four samples packed in one register.
+//   channel-last  (Quamba2 xBC, and Quamba1 when the channel stride is 1): a thread owns 4
+//                 adjacent channels (one 32-bit word; a warp moves one 128-byte line per time
+//                 step) and walks TL consecutive time steps, keeping each channel's last four
+//                 samples packed in one register.
 //   sequence-last (Quamba1 (B, D, L) with L contiguous): a thread owns 16 adjacent time steps
 //                 of one (batch, channel) row; windows are funnel shifts of adjacent words.
 #include "common.cuh"

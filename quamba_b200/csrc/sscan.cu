@@ -15,8 +15,8 @@
 namespace qb {
 namespace {
 
-// (b, d) rows per CTA == threads per CTA: 128 while the fp32 B / C tiles are small, 64 for the wide states
-constexpr int rows_per_cta(int dstate) { return dstate <= 16 ? 64 : 64; }
+// (b, d) rows per CTA == threads per CTA: 64 for every state width that is built
+constexpr int rows_per_cta(int /*dstate*/) { return 64; }
 constexpr int kTile = 64;    // time steps per shared-memory tile
 constexpr int kRowPad = 68;  // bytes per staged int8 row: 17 words, conflict-free column reads
 constexpr int kChunk = 2048; // the reference stores the state after every 2048 steps

@@ -274,6 +274,8 @@ class QuambaLMHeadModel(nn.Module):
                 token = ops.greedy_next_token(logits[:, -1])
             params.seqlen_offset += 1
             out.append(token[:, None])
+        from . import check_device_status
+        check_device_status()          # a kernel that gave up on a bounded wait leaves garbage behind: raise, do not return it
         return torch.cat(out, dim=1)
 
 

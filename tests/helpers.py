@@ -109,7 +109,7 @@ def make_ssd_case(Bsz, L, H, P, G, N, Q, grouped=False, seed=0, with_z=False, d_
 
 
 def make_sscan_case(Bsz, D, L, N, G=1, seed=0, with_z=True):
-    """BASELINE config 1 recipe: u, z, delta_raw, B, C ~ N(0,1) -> per-tensor int8; A = -[1..N]."""
+    """The recipe of the reference's scan test (quamba/tests/test_qsscan.py): u, z, delta_raw, B, C ~ N(0,1) -> per-tensor int8; A = -[1..N]."""
     g = torch.Generator().manual_seed(seed)
     c = {}
     c["q_u"], c["s_u"] = q8(torch.randn(Bsz, D, L, generator=g))

@@ -54,6 +54,33 @@ def test_ssd_full_size_is_independent_of_how_the_work_is_cut():
     assert torch.equal(y4, y4b) and torch.equal(f4, f4b)
 
 
+def test_ssd_full_size_every_pair_against_the_oracle():
+    """The benchmarked launch itself (320 (batch, head) pairs cut into 148 ranges, a state hand-off at every cut) against
+    the CPU oracle run pair by pair: every pair of the full problem, so every cut position is covered.  fp16 outputs within
+    1e-2 relative + 1e-3 x the pair's largest |reference|; final int8 states within 1 LSB.  The largest absolute error is
+    printed next to the largest |reference| (the bound is relative to the output range, not 1e-3 absolute)."""
+    from oracle import ssd as ossd
+    c = make_ssd_case(B, L, H, P, G, N, Q, seed=11)
+    y, fs = run_ssd(c)
+    y, fs = y.cpu().float(), fs.cpu().int()
+    worst_abs, worst_rel_to_max, ref_max = 0.0, 0.0, 0.0
+    for b in range(B):
+        for h in range(H):
+            want_y, want_f = ossd.chunk_scan_faithful(
+                c["q_x"][b:b + 1, :, h:h + 1], c["x_scales"], None, None, c["q_dt"][b:b + 1, :, h:h + 1], c["s_dt"], c["q_A_log"][h:h + 1],
+                c["s_A"], c["q_B"][b:b + 1], c["s_B"], c["q_C"][b:b + 1], c["s_C"], c["state_scale"], Q, c["q_D"][h:h + 1], c["s_D"], None,
+                None, c["dt_bias"][h:h + 1], True)
+            w = want_y[0, :, 0].float()
+            err = (y[b, :, h] - w).abs()
+            assert (err <= 1e-3 * w.abs().max() + 1e-2 * w.abs()).all(), f"pair ({b}, {h}): max err {err.max().item():.4g} of {w.abs().max().item():.4g}"
+            assert (fs[b, h] - want_f[0, 0].int()).abs().max() <= 1, f"pair ({b}, {h}): final state"
+            worst_abs = max(worst_abs, err.max().item())
+            worst_rel_to_max = max(worst_rel_to_max, (err.max() / w.abs().max()).item())
+            ref_max = max(ref_max, w.abs().max().item())
+    print(f"ssd full size, 320 pairs: max |y - oracle| = {worst_abs:.3e} (largest |oracle| {ref_max:.2f}); "
+          f"worst pair: {worst_rel_to_max:.2e} of its largest |oracle|")
+
+
 def test_ssd_full_size_is_causal():
     c = make_ssd_case(B, L, H, P, G, N, Q, seed=12)
     y, _ = run_ssd(c)

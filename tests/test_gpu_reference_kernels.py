@@ -142,3 +142,59 @@ def test_embedding_against_reference_kernel():
     p8, s8 = oemb.pack_w8(table)
     assert torch.equal(ops().quant_embedding_cuda.w8a16_embedding_lookup(ids, dev(p8), dev(s8)),
                        r.w8a16_embedding_lookup(ids, dev(p8), dev(s8)))
+
+
+def _time_us(fn, reps=20, warm=3):
+    for _ in range(warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def test_speed_beside_the_reference_kernels():
+    """The reference's kernels (compiled for sm_100a, unchanged) timed beside this package's at the per-layer shapes of
+    the models they serve: same device tensors, eager launches through each side's Python binding, CUDA events, 20
+    repetitions.  Both sides pay their own host-side launch path, so the small decode shapes compare bindings as much as
+    kernels.  The table is printed (pytest -s) and written to $QB_REF_TIMING_JSON when that is set."""
+    import json
+    import os
+    rows = {}
+    # Quamba2 conv1d forward, B4 L2048 (80 heads x 64, one group, d_state 128)
+    r = ref("quamba2_conv1d_cuda")
+    c = make_conv2_case(4, 2048, 80, 64, 1, 128, grouped=False, seed=1)
+    xBC = c["xBC"].transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+    args = (xBC, c["sx"], c["sB"], c["sC"], c["x_dim"], 64, 128, 1, None, None, dev(c["x_scales"]), dev(c["B_scales"]), dev(c["C_scales"]),
+            dev(c["weight"]), c["swx"], c["swB"], c["swC"], dev(c["bias"]), c["sbx"], c["sbB"], c["sbC"], None, None, None, True)
+    rows["quamba2_conv1d fwd B4 L2048 C5376"] = (_time_us(lambda: r.fwd(*args)), _time_us(lambda: ops().quamba2_conv1d_cuda.fwd(*args)))
+    # Hadamard 40 x 128 + quantise, 8192 rows
+    r = ref("quant_hadamard")
+    x = torch.randn(8192, 5120, generator=torch.Generator().manual_seed(0)).to(torch.float16).to(DEV)
+    rows["hadamard_40N 8192 x 5120"] = (_time_us(lambda: r.fast_hadamard_transform_40N(x, 0.3)),
+                                        _time_us(lambda: ops().quant_hadamard.fast_hadamard_transform_40N(x, 0.3)))
+    # Mamba1 selective scan, B16 D5120 L1024 N16
+    r = ref("quant_sscan_cuda")
+    s = {k: dev(v) for k, v in make_sscan_case(16, 5120, 1024, 16, seed=2, with_z=True).items()}
+    sargs = (s["q_u"], s["s_u"], s["q_delta"], s["s_delta"], s["q_A"], s["s_A"], s["q_B"], s["s_B"], s["q_C"], s["s_C"], s["s_state"],
+             s["q_D"], s["s_D"], s["q_z"], s["s_z"], s["q_bias"], s["s_bias"], True)
+    rows["sscan fwd B16 D5120 L1024 N16"] = (_time_us(lambda: r.fwd(*sargs), reps=5), _time_us(lambda: ops().quant_sscan_cuda.fwd(*sargs), reps=5))
+    # Quamba1 conv1d forward, B16 D5120 L1024
+    r = ref("quant_causal_conv1d_cuda")
+    g = torch.Generator().manual_seed(3)
+    xq, sx = q8(torch.randn(16, 5120, 1024, generator=g))
+    w, sw = q8(torch.randn(5120, 4, generator=g) * 0.2)
+    b, sb = q8(torch.randn(5120, generator=g) * 0.02)
+    cargs = (dev(xq), float(sx), dev(w), float(sw), 0.02, float(sb), dev(b), None, None, None, True)
+    rows["causal_conv1d fwd B16 D5120 L1024"] = (_time_us(lambda: r.fwd(*cargs)), _time_us(lambda: ops().quant_causal_conv1d_cuda.fwd(*cargs)))
+    out = {k: {"reference_us": round(a, 2), "this_us": round(b_, 2), "speedup": round(a / b_, 2)} for k, (a, b_) in rows.items()}
+    for k, v in out.items():
+        print(f"{k:40s} reference {v['reference_us']:9.1f} us   this package {v['this_us']:9.1f} us   x{v['speedup']}")
+        assert v["this_us"] > 0 and v["reference_us"] > 0
+    if os.environ.get("QB_REF_TIMING_JSON"):
+        with open(os.environ["QB_REF_TIMING_JSON"], "w") as f:
+            json.dump(out, f, indent=1)
