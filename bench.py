@@ -267,7 +267,7 @@ def run_head_parallel(args, rank, local_rank, world, pk):
                    "l2": "131072 tokens per step: every activation tensor is far larger than the 126 MB L2",
                    "note": "at N = 1 bench.py reports the Mamba2-2.7B line (the metric's own configuration) and carries this workload's "
                            "single-GPU time in its head_parallel_8b key: that is the base of this strong-scaling curve"},
-        "head_parallel_8b": r,
+        "head_parallel_8b": r, "clocks": r.get("clocks"),
         "e2e": {"value": r["value"], "unit": "tok/s", "h2d_bytes_per_step": bp.BATCH * bp.PROMPT * 8, "d2h_bytes_per_step": bp.BATCH * bp.CFG8B["vocab_size"] * 2,
                 "note": "token ids and last-token logits are 1 MB + 16 MB against a step of hundreds of ms: the end-to-end figure equals the device-timed one to three digits"},
         "gpu_launches": args.steps * r["layers"] * (bp.BATCH // r["chunk_sequences"]) * 8,
@@ -285,6 +285,8 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        if args.comm_sms > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_sms))
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
     if world > 1 or args.model == "8b":
@@ -375,6 +377,7 @@ def main():
     ap.add_argument("--layers", type=int, default=MODEL["n_layer"], help="fewer layers = a reduced profiling case, flagged in config")
     ap.add_argument("--model", default="2.7b", choices=["2.7b", "8b"], help="8b: the head-parallel Mamba2-8B prefill (always used for --gpus >= 2)")
     ap.add_argument("--no-8b-base", action="store_true", help="skip the single-GPU Mamba2-8B measurement added to the 2.7B line")
+    ap.add_argument("--comm-sms", type=int, default=16, help="--gpus >= 2: multiprocessors left to NCCL (compute grids use the rest); 0 = no split")
     ap.add_argument("--seqlen", type=int, default=PROMPT)
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
     args = ap.parse_args()

@@ -18,6 +18,7 @@ import torch.distributed as dist
 
 CFG8B = dict(d_model=4096, n_layer=56, vocab_size=256000, d_state=128, d_conv=4, expand=2, headdim=64, ngroups=8, chunk_size=256)
 BATCH, PROMPT, HAD_BLOCKS = 32, 4096, 8
+COMM_SMS = 16      # multiprocessors left to NCCL while the all-reduce of one chunk overlaps the compute of the next
 WORKLOAD8B = ("configs[4]: Quamba2 Mamba2-8B W4A8 (d_model 4096, 56 layers, 128 heads x 64, ngroups 8, d_state 128, vocab 256000), "
               "head-parallel, batch 32, prefill 4096 token ids")
 
@@ -127,12 +128,24 @@ def run(args, rank, local_rank, world, layers=None):
         barrier()
         return e0.elapsed_time(e1) / steps
 
+    # Room for the collective: the compute kernels are persistent (one CTA per SM), so with the whole GPU taken NCCL's CTAs
+    # get an SM only when a kernel ends, and once they are in, the next persistent grid runs in two waves.  The library
+    # sizes its grids for all but COMM_SMS multiprocessors and NCCL is capped at as many CTAs (NCCL_MAX_CTAS, set by
+    # bench.py before the process group exists).
+    comm_sms = getattr(args, "comm_sms", COMM_SMS) if world > 1 else 0
+    sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
+    _lib.set_sm_budget(sm_total - comm_sms if comm_sms > 0 else 0)
     steps = max(1, args.steps)
-    for _ in range(max(2, min(args.warmup, 3))):
+    for _ in range(max(3, min(args.warmup, 3))):
         logits = stack.prefill(ids[0], chunk_seqs)
     barrier()
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+    from bench_mixer_core import ClockSampler
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
     ms_step = timed(steps)
+    clocks = sampler.stop() if rank == 0 else None
     ms_compute = timed(max(1, steps // 2), collective=False)
     ms_comm = timed(max(1, steps // 2), compute=False) if world > 1 else 0.0
     ms_step, ms_compute, ms_comm = max_over_ranks([ms_step, ms_compute, ms_comm], device=dev)
@@ -149,4 +162,5 @@ def run(args, rank, local_rank, world, layers=None):
             "allreduce_bus_gbs": (2 * (world - 1) / world * reduce_bytes / (ms_comm * 1e-3) / 1e9) if world > 1 and ms_comm > 0 else None,
             "gemm_flops_per_step": flops, "gemm_tops_per_gpu": flops / world / (ms_compute * 1e-3) / 1e12,
             "chunk_sequences": chunk_seqs, "layers": cfg["n_layer"], "build_seconds": build_s, "workload": WORKLOAD8B,
+            "clocks": clocks, "compute_sms": sm_total - comm_sms, "nccl_max_ctas": comm_sms if world > 1 else None,
             "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}

@@ -45,6 +45,13 @@ int64_t qb_sizeof(const char* struct_name);
 #define QB_PATH_GEMM_SMALL_TILES 4
 #define QB_PATH_UPDATE_CTA_TILES 8
 int qb_set_path_override(int mask);
+/* Caps the number of multiprocessors the library's kernels size their grids for (persistent kernels launch one CTA per
+ * SM of the budget; one-wave grids are cut for it).  0 (default) = all SMs of the device.  A caller that overlaps these
+ * kernels with a collective on another stream leaves the collective's CTAs room this way: a persistent grid that fills
+ * every SM lets the collective start only when a kernel ends, and a collective that got in first makes the next
+ * persistent grid run in two waves.  Results do not depend on the budget.  Process-wide; returns the previous value.
+ * No reference counterpart. */
+int qb_set_sm_budget(int sms);
 /* Synchronises `stream`, then returns and clears the device status word: QB_OK, or QB_ERR_TIMEOUT
  * if a kernel gave up on a bounded wait (its outputs are then undefined).  The only entry point
  * that blocks the host. */

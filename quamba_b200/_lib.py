@@ -137,5 +137,11 @@ class path_override:
         lib().qb_set_path_override(self.prev)
 
 
+def set_sm_budget(sms: int) -> int:
+    """Cap the multiprocessors the library's kernels size their grids for (0 = all); returns the previous value.  See
+    qb_set_sm_budget in the header: leaves a concurrent collective's CTAs room."""
+    return lib().qb_set_sm_budget(int(sms))
+
+
 def read_device_status(stream: int):
     check(lib().qb_read_device_status(ctypes.c_void_p(stream)))

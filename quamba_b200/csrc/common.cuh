@@ -79,7 +79,8 @@ bool path_override(int bit);
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-int sm_count();  // multiprocessor count of the current device (cached per device)
+int sm_count();         // multiprocessors the kernels size their grids for: the device's count, capped by qb_set_sm_budget
+int device_sm_count();  // multiprocessor count of the current device (cached per device)
 
 // One-time-per-device guard for cudaFuncSetAttribute calls: kernel attributes belong to a device, so a process that
 // drives several GPUs must set them on each.  Returns true the first time it is asked about the current device.

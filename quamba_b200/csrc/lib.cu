@@ -15,7 +15,9 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-int sm_count() {
+static std::atomic<int> g_sm_budget{0};
+
+int device_sm_count() {
   static int cached[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 148;
@@ -24,6 +26,11 @@ int sm_count() {
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
   if (dev < 64) cached[dev] = n;
   return n;
+}
+
+int sm_count() {
+  const int n = device_sm_count(), cap = g_sm_budget.load(std::memory_order_relaxed);
+  return cap > 0 && cap < n ? cap : n;
 }
 
 static std::atomic<int> g_path_override{0};
@@ -65,6 +72,10 @@ extern "C" int qb_read_device_status(void* stream) {
 
 extern "C" int qb_set_path_override(int mask) {
   return qb::g_path_override.exchange(mask);
+}
+
+extern "C" int qb_set_sm_budget(int sms) {
+  return qb::g_sm_budget.exchange(sms < 0 ? 0 : sms);
 }
 
 extern "C" const char* qb_last_error(void) { return qb::t_error; }
