@@ -623,6 +623,11 @@ int qb_argmax_rows(const void* logits, int64_t row_stride, int32_t rows, int32_t
  * qb_decode_norm_linear: h = x (+ residual); residual_out = h; a = int8(rmsnorm(h) * norm_weight / norm_out_scale);
  *   out (rows, n) = a @ W^T scaled by s_channel_nat[n] * s_tok, int8 (rint, saturating) or fp16.  W is the int8 copy
  *   qb_w4a8_unpack makes (n, k), or with w_is_s4 != 0 the nibble copy qb_w4a8_pack_nibbles makes (per-channel weights).
+ *   With w_is_s4 != 0 and s_group_nat != null the weight is a GROUP-128 one streamed as 4 bits: w holds the raw codes in
+ *   the same nibble layout (byte b of 32-bit word i of a row: code of k = 8 i + b low, of k = 8 i + 4 + b high) and
+ *   s_group_nat the fp16 group scales in natural order, (n, k / 128) row-major; the kernel rebuilds the int8 weights
+ *   (q - 8) * s_group in registers with the reference's own fp16 fma (marlin_qqq_gemm_kernel.cuh:136-178), so the result
+ *   equals the product with the int8 copy bit for bit from half the bytes.
  *   With a_int8 != null (rows x k int8, row stride x_row_stride) the norm is skipped and a_int8 is multiplied as it is:
  *   the plain decode-sized product with this kernel's load scheduling.
  *   With conv_state != null the columns [conv_col0, conv_col0 + conv_dim) are not stored: each is fed to that channel's
@@ -642,6 +647,7 @@ typedef struct {
   const void* norm_weight;
   const void* w;
   const float* s_channel_nat;
+  const void* s_group_nat;
   const float* s_tok;
   void* out;
   int8_t* conv_state;

@@ -48,8 +48,15 @@ __device__ __forceinline__ float s8f(uint32_t w_biased, int k) {      // byte k 
   return __uint_as_float(__byte_perm(w_biased, 0x4B000000u, 0x7650 + k)) - 8388736.0f;
 }
 
+// Weight formats a launch can stream (the template parameter WM of the kernels):
+//   0  int8 (n, k): the expansion qb_w4a8_unpack makes
+//   1  nibbles (n, k / 2) of a per-channel weight: value + 8, the int8 weight is 16 x the value
+//   2  nibbles (n, k / 2) of a group-128 weight: the raw 4-bit codes, with s_grp (n, k / 128) fp16 group scales; the int8
+//      weight (q - 8) * s_group rounded half to even is rebuilt in registers, two at a time in fp16 arithmetic, exactly as
+//      the reference's kernel does it (marlin_qqq_gemm_kernel.cuh:136-178: one fp16 fma against 1152)
 struct Linear {
-  const uint8_t* w;        // int8 (n, k) rows, or the nibble copy (n, k / 2) when s4
+  const __half* s_grp;     // format 2 only
+  const uint8_t* w;        // int8 (n, k) rows, or a nibble copy (n, k / 2)
   const float* s_ch;       // channel scales in natural order
   const float* s_tok;      // input scale, one element
   void* out;
@@ -74,7 +81,26 @@ struct ConvEpi {
 // A lane loads kNB weight chunks per column BEFORE it uses any (clamped addresses, so the loads need no branches): at the
 // model's sizes that is the lane's whole share of a column in one round trip to L2 instead of one round trip per chunk.
 constexpr int kNB = 5;
-template <int MB, bool S4>
+
+// One 32-bit word of format 2 (byte b: code of k = b in the low, of k = 4 + b in the high nibble) -> the int8 weights of
+// k = 0..3 and of k = 4..7.  (1024 + q) - 1032 = q - 8 is exact in fp16; fma(q - 8, s, 1152) rounds the exact product once,
+// at integer granularity, and leaves 128 + result in the low mantissa byte.
+__device__ __forceinline__ void dequant8_group(uint32_t w, __half2 s2, uint32_t& lo4, uint32_t& hi4) {
+  const __half2 k1032 = __half2half2(__ushort_as_half((unsigned short)0x6408));
+  const __half2 k1152 = __half2half2(__ushort_as_half((unsigned short)0x6480));
+  uint32_t p[4] = {(w & 0x000f000fu) | 0x64006400u, ((w >> 8) & 0x000f000fu) | 0x64006400u,
+                   ((w >> 4) & 0x000f000fu) | 0x64006400u, ((w >> 12) & 0x000f000fu) | 0x64006400u};
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 v = __hfma2(__hsub2(*reinterpret_cast<const __half2*>(&p[i]), k1032), s2, k1152);
+    r[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  lo4 = __byte_perm(r[0], r[1], 0x6240) ^ 0x80808080u;
+  hi4 = __byte_perm(r[2], r[3], 0x6240) ^ 0x80808080u;
+}
+
+template <int MB, int S4>
 __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][kNW]) {
   int sa[MB];
 #pragma unroll
@@ -88,13 +114,18 @@ __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, i
   const uint4* wrow[kNW];
 #pragma unroll
   for (int j = 0; j < kNW; ++j) wrow[j] = reinterpret_cast<const uint4*>(L.w + (int64_t)min(n0 + j, L.n - 1) * ldw);
+  const int groups = L.k / 128;
   for (int c0 = lane; c0 < chunks; c0 += 32 * kNB) {
     uint4 w[kNW][kNB];
+    unsigned short sg[kNW][kNB];     // format 2: the group scale of each chunk (a chunk is 32 codes of one group)
 #pragma unroll
     for (int b = 0; b < kNB; ++b) {
       const int c = min(c0 + 32 * b, chunks - 1);
 #pragma unroll
-      for (int j = 0; j < kNW; ++j) w[j][b] = __ldg(wrow[j] + c);
+      for (int j = 0; j < kNW; ++j) {
+        w[j][b] = __ldg(wrow[j] + c);
+        if (S4 == 2) sg[j][b] = __ldg(reinterpret_cast<const unsigned short*>(L.s_grp) + (int64_t)min(n0 + j, L.n - 1) * groups + (c >> 2));
+      }
     }
 #pragma unroll
     for (int b = 0; b < kNB; ++b) {
@@ -111,6 +142,8 @@ __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, i
               t = __dp4a((int)a.z, (int)w[j][b].z, t); t = __dp4a((int)a.w, (int)w[j][b].w, t);
               acc[i][j] = t;
             }
+          } else if (S4 == 2) {
+            // handled below, once per chunk for all rows
           } else {
             const uint4 a0 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c);
             const uint4 a1 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c + 1);
@@ -132,16 +165,39 @@ __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, i
             }
           }
         }
+        if (S4 == 2) {
+#pragma unroll
+          for (int j = 0; j < kNW; ++j) {
+            const __half2 s2 = __half2half2(__ushort_as_half(sg[j][b]));
+            const uint32_t ww[4] = {w[j][b].x, w[j][b].y, w[j][b].z, w[j][b].w};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dequant8_group(ww[q], s2, lo[q], hi[q]);
+#pragma unroll
+            for (int i = 0; i < MB; ++i) {
+              const uint4 a0 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c);
+              const uint4 a1 = *(reinterpret_cast<const uint4*>(sA + (int64_t)i * L.k) + 2 * c + 1);
+              const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+              int t = acc[i][j];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                t = __dp4a(av[2 * q], (int)lo[q], t);
+                t = __dp4a(av[2 * q + 1], (int)hi[q], t);
+              }
+              acc[i][j] = t;
+            }
+          }
+        }
       }
     }
   }
 #pragma unroll
   for (int i = 0; i < MB; ++i) {
-    const int s = S4 ? warp_sum_i(sa[i]) : 0;
+    const int s = S4 == 1 ? warp_sum_i(sa[i]) : 0;
 #pragma unroll
     for (int j = 0; j < kNW; ++j) {
       const int t = warp_sum_i(acc[i][j]);
-      acc[i][j] = S4 ? 16 * (t - 8 * s) : t;      // nibbles hold value + 8; the int8 weight is 16 x the value
+      acc[i][j] = S4 == 1 ? 16 * (t - 8 * s) : t;      // format 1: nibbles hold value + 8, the int8 weight is 16 x the value
     }
   }
 }
@@ -202,7 +258,7 @@ __device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, const
 // Ask L2 for every weight row this warp will stream (all its passes).  Weights do not depend on the kernel before this
 // one, so the call sits ahead of the dependency wait and of the shared-memory prologue: HBM delivers while the prologue
 // computes, and each pass then costs a round trip to L2 instead of one to HBM.
-template <bool S4>
+template <int S4>
 __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row_bytes = S4 ? L.k / 2 : L.k;
@@ -217,7 +273,7 @@ __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
 }
 
 // `pre`: the finishing lane's constants of the first pass, loaded by the caller before the dependency wait.
-template <int MB, bool S4>
+template <int MB, int S4>
 __device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows, FinishPre pre) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = lane / kNW, j = lane % kNW;
@@ -262,7 +318,7 @@ struct NormIn {
   float eps, out_scale;
 };
 
-template <int MB, bool S4>
+template <int MB, int S4>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   extern __shared__ __align__(16) uint8_t dsm[];
@@ -527,15 +583,18 @@ int opt_in_smem(K kernel, size_t bytes) {
 
 using namespace qb;
 
-#define QB_DISPATCH_MB_S4(KERNEL, rows, s4, grid, smem, st, ...)                                                          \
+#define QB_LAUNCH_ONE(KERNEL, MBV, WMV, grid, smem, st, ...)                                                             \
+  { rc__ = opt_in_smem(KERNEL<MBV, WMV>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<MBV, WMV>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }
+#define QB_DISPATCH_WM(KERNEL, MBV, wm, grid, smem, st, ...)                                                             \
+  if (wm == 2) QB_LAUNCH_ONE(KERNEL, MBV, 2, grid, smem, st, __VA_ARGS__)                                                 \
+  else if (wm == 1) QB_LAUNCH_ONE(KERNEL, MBV, 1, grid, smem, st, __VA_ARGS__)                                            \
+  else QB_LAUNCH_ONE(KERNEL, MBV, 0, grid, smem, st, __VA_ARGS__)
+#define QB_DISPATCH_MB_S4(KERNEL, rows, wm, grid, smem, st, ...)                                                          \
   do {                                                                                                                    \
     int rc__ = QB_OK;                                                                                                     \
-    if (rows == 1 && s4) { rc__ = opt_in_smem(KERNEL<1, true>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<1, true>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }        \
-    else if (rows == 1) { rc__ = opt_in_smem(KERNEL<1, false>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<1, false>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }      \
-    else if (rows == 2 && s4) { rc__ = opt_in_smem(KERNEL<2, true>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<2, true>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }   \
-    else if (rows == 2) { rc__ = opt_in_smem(KERNEL<2, false>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<2, false>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }      \
-    else if (s4) { rc__ = opt_in_smem(KERNEL<4, true>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<4, true>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }               \
-    else { rc__ = opt_in_smem(KERNEL<4, false>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<4, false>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }                     \
+    if (rows == 1) { QB_DISPATCH_WM(KERNEL, 1, wm, grid, smem, st, __VA_ARGS__) }                                         \
+    else if (rows == 2) { QB_DISPATCH_WM(KERNEL, 2, wm, grid, smem, st, __VA_ARGS__) }                                    \
+    else { QB_DISPATCH_WM(KERNEL, 4, wm, grid, smem, st, __VA_ARGS__) }                                                   \
     if (rc__ != QB_OK) return rc__;                                                                                       \
   } while (0)
 
@@ -579,7 +638,12 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
   const dim3 grid(grid_for(a->n, 2));
   cudaStream_t st = (cudaStream_t)stream;
   const int rows = a->rows;
-  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, a->w_is_s4 != 0, grid, smem, st, nin, L, cv, rows);
+  const int wm = a->w_is_s4 == 0 ? 0 : (a->s_group_nat != nullptr ? 2 : 1);
+  if (wm == 2) {
+    QB_REQUIRE(a->k % 128 == 0 && aligned(a->s_group_nat, 2), QB_ERR_INVALID_ARG, "decode_norm_linear: group scales need k to be a multiple of 128");
+    L.s_grp = static_cast<const __half*>(a->s_group_nat);
+  }
+  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, wm, grid, smem, st, nin, L, cv, rows);
   QB_LAUNCH_OK("decode_norm_linear_kernel");
   return QB_OK;
 }

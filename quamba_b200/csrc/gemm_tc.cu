@@ -447,7 +447,9 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
   if (!no_persistent && ptiles >= sm_count()) {   // enough 128 x 256 tiles to give every SM at least one
     // tile width: the one whose rounds of the grid cost least (rounds x width); ties go to the wider tile.  Only multiples
     // of 64 columns: 144 .. 240 in steps of 16 were measured too, and every width that is not a multiple of 64 ran 25-90 %
-    // slower per column than its neighbours.
+    // slower per column than its neighbours.  128- and 64-column tiles were measured at the 2.7B layer shapes as well (2048
+    // and 8192 rows) and lost everywhere (10-20 % and 60-110 % slower): every column of W a tile does not cover is another
+    // pass of the A tile through shared memory.
     int bn = PBN;
     int64_t best = INT64_MAX;
     for (int cand = PBN; cand >= 192; cand -= 64) {

@@ -282,13 +282,15 @@ def olin_ref(ql, x):
                           ql.size_k, False)[:, :ql.out_features]
 
 
-@pytest.mark.parametrize("group,batch", [(-1, 1), (None, 1), (-1, 2), (None, 3), (-1, 4)])
-def test_fused_decode_step_equals_the_op_by_op_step(group, batch, monkeypatch):
+@pytest.mark.parametrize("group,batch,nibbles", [(-1, 1, False), (None, 1, False), (-1, 2, False), (None, 3, False), (-1, 4, False),
+                                                 (None, 2, True)])
+def test_fused_decode_step_equals_the_op_by_op_step(group, batch, nibbles, monkeypatch):
     """The three-launch decode step against the seven-launch one on the same model, token and caches, and against the
     CPU oracle's step: conv state bit for bit, int8 ssm state +-1 LSB, logits within the model-level tolerance."""
     import copy
     import quamba_b200.model as qmodel
     from quamba_b200.model import InferenceParams
+    monkeypatch.setattr(ops(), "GROUP_NIBBLES", nibbles)      # group-128 weights streamed as 4-bit codes in the fused step
     q, ids = _small(11 + batch, group, n_layer=2, L=40, batch=batch)
     gq = copy.deepcopy(q).to(DEV)
     params = InferenceParams(max_seqlen=64, max_batch_size=batch)
@@ -318,3 +320,36 @@ def test_fused_decode_step_equals_the_op_by_op_step(group, batch, monkeypatch):
         else:           # later layers inherit +-1 LSB differences of the layer before
             assert (conv_f.int() - conv_p.int()).abs().float().mean().item() < 0.05
             assert (ssm_f.int() - ssm_p.int()).abs().max().item() <= 2
+
+
+@pytest.mark.parametrize("K,N,rows,out_int8", [(2560, 10624, 1, True), (5120, 2560, 1, False), (256, 320, 3, False),
+                                               (1024, 4160, 4, True), (384, 128, 2, False)])
+def test_decode_product_from_group128_nibbles_is_bit_identical(K, N, rows, out_int8):
+    """Group-128 weights streamed as 4-bit codes + fp16 group scales, the int8 weights rebuilt in registers with the
+    reference's fp16 fma, against (a) the same kernel on the int8 expansion qb_w4a8_unpack makes and (b) the large-M product
+    entry point on that expansion: all three bit for bit."""
+    from quamba_b200.modules import W4A8B8O8Linear, W4A8B16O16Linear
+    o = ops()
+    g = torch.Generator().manual_seed(K + N)
+    lin = torch.nn.Linear(K, N, bias=False)
+    lin.weight.data = torch.randn(N, K, generator=g) * 0.02 * (1 + 3 * torch.rand(N, 1, generator=g))
+    cls = W4A8B8O8Linear if out_int8 else W4A8B16O16Linear
+    ql = (cls.from_fp16(lin, torch.tensor(0.02), torch.tensor(0.05)) if out_int8 else cls.from_fp16(lin, torch.tensor(0.02))).to(DEV)
+    prep = ql.prepared()
+    assert not prep.per_channel
+    a = torch.randint(-127, 128, (rows, K), generator=g, dtype=torch.int32).to(torch.int8).to(DEV)
+    s_tok = ql.input_scale
+    old = o.GROUP_NIBBLES
+    try:
+        o.GROUP_NIBBLES = True
+        got = o.decode_linear(a, prep, s_tok, out_int8=out_int8)
+        codes, scales = prep.need_w4g()
+        assert codes.shape == (prep.size_n, K // 2) and scales.shape == (prep.size_n, K // 128)
+        o.GROUP_NIBBLES = False
+        from_int8 = o.decode_linear(a, prep, s_tok, out_int8=out_int8)
+    finally:
+        o.GROUP_NIBBLES = old
+    big = o.w4a8_linear(a, prep, s_tok, out_int8=out_int8)
+    torch.cuda.synchronize()
+    assert torch.equal(got, from_int8)
+    assert torch.equal(got, big)
