@@ -70,8 +70,12 @@ class Stack:
         del head, table
         torch.cuda.empty_cache()
 
-    @torch.no_grad()
     def prefill(self, ids, chunk_seqs, collective=True, compute=True):
+        from quamba_b200 import _lib
+        with _lib.early_overlap(True), torch.no_grad():
+            return self._prefill(ids, chunk_seqs, collective, compute)
+
+    def _prefill(self, ids, chunk_seqs, collective=True, compute=True):
         """ids (batch, L) on the device -> last-token logits (batch, vocab).  ``collective`` / ``compute`` switch the two
         halves off for the separate timings."""
         chunks = list(ids.split(chunk_seqs))

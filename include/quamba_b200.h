@@ -52,6 +52,15 @@ int qb_set_path_override(int mask);
  * persistent grid run in two waves.  Results do not depend on the budget.  Process-wide; returns the previous value.
  * No reference counterpart. */
 int qb_set_sm_budget(int sms);
+/* While on (non-zero), the kernels of a prefill chain -- norms, the tensor-core GEMMs, conv1d forward, the SSD scan, the
+ * Hadamard kernel -- signal as they start that the NEXT programmatic launch on the stream may become resident and run its
+ * prologue (barrier and tensor-memory set-up, constant tables, weight prefetch) while they still work; its
+ * griddepcontrol.wait then holds it until this kernel's results are complete.  What follows such a kernel on the stream
+ * must be a kernel of this library (all of them read activations through L2, by TMA / bulk copies or ld.global.cg, which an
+ * early start requires) or an ordinary launch (which waits for full completion anyway).  Off by default; the model's
+ * forward switches it on around its own launch sequence.  Process-wide; returns the previous value.  No reference
+ * counterpart. */
+int qb_set_early_overlap(int on);
 /* Synchronises `stream`, then returns and clears the device status word: QB_OK, or QB_ERR_TIMEOUT
  * if a kernel gave up on a bounded wait (its outputs are then undefined).  The only entry point
  * that blocks the host. */

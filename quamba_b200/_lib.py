@@ -137,6 +137,21 @@ class path_override:
         lib().qb_set_path_override(self.prev)
 
 
+class early_overlap:
+    """``with early_overlap(): ...`` lets the prefill kernels launched inside start their successors early (see
+    qb_set_early_overlap in the header).  Only this library's own launch sequences belong inside."""
+
+    def __init__(self, on=True):
+        self.on = on
+
+    def __enter__(self):
+        self.prev = lib().qb_set_early_overlap(int(self.on))
+        return self
+
+    def __exit__(self, *exc):
+        lib().qb_set_early_overlap(self.prev)
+
+
 def set_sm_budget(sms: int) -> int:
     """Cap the multiprocessors the library's kernels size their grids for (0 = all); returns the previous value.  See
     qb_set_sm_budget in the header: leaves a concurrent collective's CTAs room."""

@@ -56,6 +56,11 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 //    that the SM cached before this kernel overwrote it: a captured decode step produced garbage that way, while the same
 //    launches issued one by one from the host, which never overlap, were correct.
 __device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Load of an ACTIVATION (anything a kernel earlier on the stream may have written): through L2, never from this SM's L1.
+// Constants of a model (weights, scales, tables) keep their cached loads.
+template <typename T>
+__device__ __forceinline__ T ld_act(const T* p) { return __ldcg(p); }
+__device__ __forceinline__ int8_t ld_act(const int8_t* p) { return (int8_t)__ldcg(reinterpret_cast<const signed char*>(p)); }
 template <typename... KArgs, typename... Args>
 inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -71,6 +76,12 @@ inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif
+
+// qb_set_early_overlap: while on, the kernels of a prefill chain (norms, GEMMs, conv1d, SSD, Hadamard) execute
+// grid_dependency_launch() as they start, so that the next programmatic launch on the stream gets its CTAs resident and its
+// prologue done while this kernel still works.  Every kernel of this library that is launched as a programmatic dependent
+// reads activations past L1 (ld_act() below, TMA or bulk copies), which is what makes that safe.
+bool early_overlap();
 
 // Cross-check switches (qb_set_path_override): each bit sends an op to its portable twin so that two implementations can be
 // compared on one device.  Off by default; set explicitly through the C ABI, never read from the environment.

@@ -59,7 +59,8 @@ template <bool kSilu>
 __global__ void __launch_bounds__(kClBlock)
 conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t in_sl,
                            const int8_t* __restrict__ weight, const int8_t* __restrict__ bias,
-                           ClSegments seg, int batch, int dim, int seqlen, int width, int tl, int nseg) {
+                           ClSegments seg, int batch, int dim, int seqlen, int width, int tl, int nseg, int early) {
+  if (early) grid_dependency_launch();
   const int cv = dim / kCh;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = (int64_t)batch * nseg * cv;
@@ -106,13 +107,16 @@ conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t
   int8_t* dst = seg.dst[s] + (int64_t)b * seg.dst_sb[s] + (c0 - cbase);
   const int64_t dsl = seg.dst_sl[s];
 
+  // launched as a programmatic dependent: taps, bias and scales above are constants and were fetched while the kernel
+  // before this one may still have been running; the input is read from here on, past L1 (ld_act)
+  grid_dependency_wait();
   uint32_t win[kCh];
 #pragma unroll
   for (int j = 0; j < kCh; ++j) win[j] = 0;
 #pragma unroll
   for (int h = 3; h >= 1; --h) {
     const int l = l0 - h;
-    const uint32_t r = l >= 0 ? __ldg(reinterpret_cast<const uint32_t*>(src + (int64_t)l * in_sl)) : 0u;
+    const uint32_t r = l >= 0 ? ld_act(reinterpret_cast<const uint32_t*>(src + (int64_t)l * in_sl)) : 0u;
 #pragma unroll
     for (int j = 0; j < kCh; ++j) win[j] = __byte_perm(win[j], r, 0x0321 | ((4 + j) << 12));
   }
@@ -125,7 +129,7 @@ conv1d_channel_last_kernel(const int8_t* __restrict__ in, int64_t in_sb, int64_t
     uint32_t rows[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u)
-      rows[u] = (l + u < l1) ? __ldg(reinterpret_cast<const uint32_t*>(p + (int64_t)u * in_sl)) : 0u;
+      rows[u] = (l + u < l1) ? ld_act(reinterpret_cast<const uint32_t*>(p + (int64_t)u * in_sl)) : 0u;
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       int q[kCh];
@@ -288,8 +292,8 @@ conv1d_update_w4_kernel(const int8_t* __restrict__ x, int64_t x_sb, int64_t x_sd
   const int c = (int)(idx % dim);
   const int b = (int)(idx / dim);
   uint32_t* st = state + (int64_t)b * st_sb_words + c;
-  const uint32_t xv = (uint32_t)(uint8_t)x[(int64_t)b * x_sb + (int64_t)c * x_sd];
-  const uint32_t win = (*st >> 8) | (xv << 24);   // drop the oldest sample, append the new one
+  const uint32_t xv = (uint32_t)(uint8_t)ld_act(x + (int64_t)b * x_sb + (int64_t)c * x_sd);
+  const uint32_t win = (ld_act(st) >> 8) | (xv << 24);   // drop the oldest sample, append the new one
   *st = win;
   const float acc = (float)__dp4a((int)win, (int)__ldg(weight + c), 0);
   update_finish(acc, b, c, bias, seg, silu);
@@ -318,12 +322,13 @@ int launch_channel_last(const int8_t* in, int64_t in_sb, int64_t in_sl, const in
   const int nseg = (int)ceil_div(seqlen, tl);
   const int64_t total = (int64_t)batch * nseg * cv;
   const unsigned grid = (unsigned)ceil_div(total, kClBlock);
+  const int early = early_overlap() ? 1 : 0;
   if (silu) {
-    conv1d_channel_last_kernel<true><<<grid, kClBlock, 0, stream>>>(in, in_sb, in_sl, weight, bias, seg, batch, dim, seqlen,
-                                                                    width, tl, nseg);
+    launch_dependent(conv1d_channel_last_kernel<true>, dim3(grid), dim3(kClBlock), 0, stream, in, in_sb, in_sl, weight, bias, seg, batch,
+                     dim, seqlen, width, tl, nseg, early);
   } else {
-    conv1d_channel_last_kernel<false><<<grid, kClBlock, 0, stream>>>(in, in_sb, in_sl, weight, bias, seg, batch, dim, seqlen,
-                                                                     width, tl, nseg);
+    launch_dependent(conv1d_channel_last_kernel<false>, dim3(grid), dim3(kClBlock), 0, stream, in, in_sb, in_sl, weight, bias, seg, batch,
+                     dim, seqlen, width, tl, nseg, early);
   }
   QB_LAUNCH_OK("conv1d_channel_last_kernel");
   return QB_OK;

@@ -18,7 +18,7 @@ embedding_kernel(const void* __restrict__ table, const __half* __restrict__ scal
   const int lane = threadIdx.x & 31;
   const int64_t tok = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (tok >= n_tokens) return;
-  int64_t id = tokens[tok];
+  int64_t id = ld_act(tokens + tok);       // written by the argmax of the step before when a decode graph feeds itself
   if (id < 0 || id >= vocab) {       // an out-of-range id reads row 0 and raises the status word instead of faulting
     if (lane == 0) atomicCAS(status, 0, kStatusTokenRange);
     id = 0;

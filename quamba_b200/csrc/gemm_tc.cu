@@ -80,7 +80,8 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int m, int 
 template <int kBN>
 __global__ void __launch_bounds__(kThreads)
 gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                       int M, int N, int K, int a_rows, Epilogue ep, int* status) {
+                       int M, int N, int K, int a_rows, Epilogue ep, int* status, int early) {
+  if (early) grid_dependency_launch();
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -112,6 +113,9 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // launched as a programmatic dependent: barriers, tensor memory and descriptors above were set up while the kernel
+  // before this one may still have been running; A (and per-row scales) are read from here on, by TMA or past L1
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -190,7 +194,8 @@ constexpr int kPThreads = 64 + 256;
 // slots and the TMEM accumulators keep their 256-column size.
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                                  int M, int N, int K, int bn, Epilogue ep, int* status) {
+                                  int M, int N, int K, int bn, Epilogue ep, int* status, int early) {
+  if (early) grid_dependency_launch();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStages * kPStageBytes);
@@ -221,6 +226,9 @@ gemm_s8_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, co
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // launched as a programmatic dependent: barriers, tensor memory and descriptors above were set up while the kernel
+  // before this one may still have been running; A (and per-row scales) are read from here on, by TMA or past L1
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -465,7 +473,8 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
       if (dev < 64) pattr_set[dev] = true;
     }
     const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(M, BM) * ceil_div(N, bn), sm_count());
-    gemm_s8_tcgen05_persistent_kernel<<<grid, kPThreads, kPSmemBytes, st>>>(ta, tw, M, N, K, bn, ep, status);
+    launch_dependent(gemm_s8_tcgen05_persistent_kernel, dim3(grid), dim3(kPThreads), (size_t)kPSmemBytes, st, ta, tw, M, N, K, bn, ep, status,
+                     early_overlap() ? 1 : 0);
     QB_LAUNCH_OK("gemm_s8_tcgen05_persistent_kernel");
     return QB_OK;
   }
@@ -485,8 +494,9 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
     if (dev < 64) attr_set[dev] = true;
   }
   dim3 grid((unsigned)ceil_div(M, BM), (unsigned)ceil_div(N, bn));
-  if (bn == 64) gemm_s8_tcgen05_kernel<64><<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, a_rows, ep, status);
-  else gemm_s8_tcgen05_kernel<128><<<grid, kThreads, kSmemBytes, st>>>(ta, tw, M, N, K, a_rows, ep, status);
+  const int early = early_overlap() ? 1 : 0;
+  if (bn == 64) launch_dependent(gemm_s8_tcgen05_kernel<64>, grid, dim3(kThreads), (size_t)kSmemBytes, st, ta, tw, M, N, K, a_rows, ep, status, early);
+  else launch_dependent(gemm_s8_tcgen05_kernel<128>, grid, dim3(kThreads), (size_t)kSmemBytes, st, ta, tw, M, N, K, a_rows, ep, status, early);
   QB_LAUNCH_OK("gemm_s8_tcgen05_kernel");
   return QB_OK;
 }

@@ -60,7 +60,8 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 template <int S, int SPAD, int R>
 __global__ void __launch_bounds__(kThreadsH, 1)
 hadamard_tc_kernel(const __grid_constant__ CUtensorMap tm_x, int8_t* __restrict__ out, int64_t out_rs, int64_t rows,
-                   float scale128, const unsigned long long* __restrict__ neg_masks, int* status) {
+                   float scale128, const unsigned long long* __restrict__ neg_masks, int* status, int early) {
+  if (early) grid_dependency_launch();
   constexpr int N1 = R * S;                      // GEMM1 N
   constexpr int W = R * SPAD;                    // TMEM columns of the D region of one buffer
   constexpr int kColHi = W, kColLo = W + W / 2;  // packed fp16 pairs: SPAD / 2 columns per row
@@ -320,7 +321,8 @@ int launch_one(const qb_hadamard_quant_args* a, const unsigned long long* masks,
   QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "hadamard: device status word unavailable");
   const int64_t units = ceil_div(a->rows, R);
   const unsigned grid = (unsigned)std::min<int64_t>(units, sm_count());
-  launch_dependent(kern, dim3(grid), dim3(kThreadsH), (size_t)kSmem, st, tm, a->out, a->out_row_stride, a->rows, a->scale * 128.0f, masks, status);
+  launch_dependent(kern, dim3(grid), dim3(kThreadsH), (size_t)kSmem, st, tm, a->out, a->out_row_stride, a->rows, a->scale * 128.0f, masks, status,
+                   early_overlap() ? 1 : 0);
   QB_LAUNCH_OK("hadamard_tc_kernel");
   return QB_OK;
 }

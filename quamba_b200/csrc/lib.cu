@@ -15,6 +15,9 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static std::atomic<int> g_early_overlap{0};
+bool early_overlap() { return g_early_overlap.load(std::memory_order_relaxed) != 0; }
+
 static std::atomic<int> g_sm_budget{0};
 
 int device_sm_count() {
@@ -72,6 +75,10 @@ extern "C" int qb_read_device_status(void* stream) {
 
 extern "C" int qb_set_path_override(int mask) {
   return qb::g_path_override.exchange(mask);
+}
+
+extern "C" int qb_set_early_overlap(int on) {
+  return qb::g_early_overlap.exchange(on != 0 ? 1 : 0);
 }
 
 extern "C" int qb_set_sm_budget(int sms) {

@@ -197,7 +197,7 @@ gemv_s8_kernel(const int8_t* __restrict__ A, int64_t lda, const int8_t* __restri
 #pragma unroll
       for (int i = 0; i < MB; ++i) {
         const int m = min(m0 + i, M - 1);
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + c);
+        const uint4 a = ld_act(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + c);
 #pragma unroll
         for (int j = 0; j < kNW; ++j) {
           int t = acc[i][j];
@@ -270,8 +270,8 @@ gemv_s4_kernel(const int8_t* __restrict__ A, int64_t lda, const uint8_t* __restr
 #pragma unroll
       for (int i = 0; i < MB; ++i) {
         const int m = min(m0 + i, M - 1);
-        const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + 2 * c);
-        const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + 2 * c + 1);
+        const uint4 a0 = ld_act(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + 2 * c);
+        const uint4 a1 = ld_act(reinterpret_cast<const uint4*>(A + (int64_t)m * lda) + 2 * c + 1);
         const int av[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
         int s = sa[i];
 #pragma unroll

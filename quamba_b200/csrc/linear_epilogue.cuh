@@ -22,6 +22,8 @@ struct Epilogue {
     const float f = (float)acc;
     if (use_alpha) return alpha * f;
     const float cs = col_scale[col_per ? n : 0];
+    // (per-row scales come from the kernel that quantised the rows, through a cached load: that kernel therefore never
+    // lets its successor start early, see run_norm)
     const float rs = row_scale[row_per ? m : 0];
     return (f * cs) * rs;
   }

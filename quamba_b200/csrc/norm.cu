@@ -24,6 +24,7 @@ struct NormParams {
   int64_t x_stride, res_stride, res_out_stride, z_stride, y_stride;
   int M, N, ngroups;      // N: elements per normalised segment
   int res_f32, res_out_f32, out_kind, gate_first, rms, pad_zero;
+  int early;              // let the next programmatic launch start while this kernel runs (early_overlap())
   float eps, out_scale, z_scale;
 };
 
@@ -86,6 +87,7 @@ norm_quant_kernel(const NormParams p) {
 #pragma unroll
   for (int i = 0; i < CH; ++i) { const int c = t + i * T; on[i] = c < chunks; cc[i] = on[i] ? c : chunks - 1; }
 
+  if (p.early) grid_dependency_launch();
   // weights do not depend on the kernel before this one: fetch them ahead of the dependency wait
   uint4 wr[CH];
 #pragma unroll
@@ -95,17 +97,17 @@ norm_quant_kernel(const NormParams p) {
   uint4 xr[CH];
   uint2 zr[CH];
 #pragma unroll
-  for (int i = 0; i < CH; ++i) xr[i] = __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + col0) + cc[i]);
+  for (int i = 0; i < CH; ++i) xr[i] = ld_act(reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.x_stride + col0) + cc[i]);
   if (GATE != 0) {
 #pragma unroll
-    for (int i = 0; i < CH; ++i) zr[i] = __ldg(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + cc[i]);
+    for (int i = 0; i < CH; ++i) zr[i] = ld_act(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + cc[i]);
   }
   float v[CH][8];
   if (GATE == 0 && p.residual != nullptr && p.res_f32) {
     float4 ra[CH], rb[CH];
     const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(p.residual) + (int64_t)row * p.res_stride + col0);
 #pragma unroll
-    for (int i = 0; i < CH; ++i) { ra[i] = __ldg(r + 2 * cc[i]); rb[i] = __ldg(r + 2 * cc[i] + 1); }
+    for (int i = 0; i < CH; ++i) { ra[i] = ld_act(r + 2 * cc[i]); rb[i] = ld_act(r + 2 * cc[i] + 1); }
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
       v[i][0] = ra[i].x; v[i][1] = ra[i].y; v[i][2] = ra[i].z; v[i][3] = ra[i].w;
@@ -115,7 +117,7 @@ norm_quant_kernel(const NormParams p) {
     uint4 rr[CH];
     const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.residual) + (int64_t)row * p.res_stride + col0);
 #pragma unroll
-    for (int i = 0; i < CH; ++i) rr[i] = __ldg(r + cc[i]);
+    for (int i = 0; i < CH; ++i) rr[i] = ld_act(r + cc[i]);
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
       const __half2* rh = reinterpret_cast<const __half2*>(&rr[i]);
@@ -230,18 +232,19 @@ norm_quant_kernel(const NormParams p) {
 // Any segment length and alignment: one CTA per segment, three strided passes over global memory.
 __global__ void __launch_bounds__(256) norm_quant_generic_kernel(const NormParams p) {
   __shared__ float red[8];
+  if (p.early) grid_dependency_launch();
   grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x / p.ngroups, grp = blockIdx.x % p.ngroups;
   const int64_t col0 = (int64_t)grp * p.N;
   auto load = [&](int j, float& zsig) {
-    float x = __half2float(p.x[(int64_t)row * p.x_stride + col0 + j]);
+    float x = __half2float(ld_act(p.x + (int64_t)row * p.x_stride + col0 + j));
     if (p.residual != nullptr)
-      x += p.res_f32 ? static_cast<const float*>(p.residual)[(int64_t)row * p.res_stride + col0 + j]
-                     : __half2float(static_cast<const __half*>(p.residual)[(int64_t)row * p.res_stride + col0 + j]);
+      x += p.res_f32 ? ld_act(static_cast<const float*>(p.residual) + (int64_t)row * p.res_stride + col0 + j)
+                     : __half2float(ld_act(static_cast<const __half*>(p.residual) + (int64_t)row * p.res_stride + col0 + j));
     zsig = 1.f;
     if (p.z != nullptr) {
-      const float zf = (float)p.z[(int64_t)row * p.z_stride + col0 + j] * p.z_scale;
+      const float zf = (float)ld_act(p.z + (int64_t)row * p.z_stride + col0 + j) * p.z_scale;
       zsig = zf * (1.0f / (1.0f + __expf(-zf)));
       if (p.gate_first) x *= zsig;
     }
@@ -379,6 +382,8 @@ int check_and_run(const qb_rmsnorm_args* a, bool gated, void* stream) {
   // The reference reduces max(y) over a power-of-two block whose padding lanes hold 0.
   p.pad_zero = (a->group_size & (a->group_size - 1)) != 0;
   p.eps = a->eps; p.out_scale = a->out_scale; p.z_scale = a->z_scale;
+  // a dynamic-scale norm writes the per-row scales the next product reads through L1: no early start after it
+  p.early = early_overlap() && a->dyn_scale == nullptr ? 1 : 0;
   return run_norm(p, (cudaStream_t)stream);
 }
 

@@ -502,14 +502,14 @@ sscan_update_warp_kernel(qb_sscan_update_args a, int tiles, int* status) {
     const int p = (t % tiles_per_head) * kWTileRows + (lane & 15);
     r.hd = hd; r.p = p;
     if (lane < 16) {
-      const float x = xs0 * (float)a.x[(int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p];
+      const float x = xs0 * (float)ld_act(a.x + (int64_t)b * a.x_sb + (int64_t)hd * a.x_sh + p);
       float bias = 0.0f;
       if (a.dt_bias != nullptr) {
         const int64_t bi = (int64_t)hd * a.bias_sh + (int64_t)p * a.bias_sp;
         bias = a.dt_bias_is_half ? __half2float(static_cast<const __half*>(a.dt_bias)[bi])
                                  : bias_scale * (float)static_cast<const int8_t*>(a.dt_bias)[bi];
       }
-      float dt = fmaf(dt_scale, (float)a.dt[(int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp], bias);
+      float dt = fmaf(dt_scale, (float)ld_act(a.dt + (int64_t)b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp), bias);
       if (a.dt_softplus) dt = softplus_f(dt);
       const float A2 = -__expf(A_scale * (float)a.A_log[(int64_t)hd * a.A_sh + (int64_t)p * a.A_sp]) * kLog2e;
       r.x = x;
@@ -531,8 +531,8 @@ sscan_update_warp_kernel(qb_sscan_update_args a, int tiles, int* status) {
     if (b * a.ngroups + g != cur_bg) {                        // warp-uniform: this lane's slices of B and C
       cur_bg = b * a.ngroups + g;
       const float Bs = a.B_scale[0] / ss0, Cs = a.C_scale[0] * ss0;
-      const uint4 bq = __ldg(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0));
-      const uint4 cq = __ldg(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0));
+      const uint4 bq = ld_act(reinterpret_cast<const uint4*>(a.Bm + (int64_t)b * a.B_sb + (int64_t)g * a.B_sg + n0));
+      const uint4 cq = ld_act(reinterpret_cast<const uint4*>(a.Cm + (int64_t)b * a.C_sb + (int64_t)g * a.C_sg + n0));
       const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w}, cw[4] = {cq.x, cq.y, cq.z, cq.w};
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
@@ -585,7 +585,7 @@ sscan_update_warp_kernel(qb_sscan_update_args a, int tiles, int* status) {
     if (lane < 16) {            // y of row `lane`: D skip term, z gate, fp16 store
       float y = ykeep + cur.dsk;
       if (a.z != nullptr) {
-        const float z = z_scale * (float)a.z[(int64_t)b * a.z_sb + (int64_t)cur.hd * a.z_sh + cur.p];
+        const float z = z_scale * (float)ld_act(a.z + (int64_t)b * a.z_sb + (int64_t)cur.hd * a.z_sh + cur.p);
         y *= silu_exact(z);
       }
       static_cast<__half*>(a.out)[(int64_t)b * a.out_sb + (int64_t)cur.hd * a.out_sh + cur.p] = __float2half_rn(y);
@@ -665,8 +665,8 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
         const int hd = c.hd0 + (int)(pr / (unsigned)a.headdim);
         const int p = (int)(pr % (unsigned)a.headdim);
         raw[i].hd = hd; raw[i].p = p;
-        raw[i].xq = a.x[(int64_t)c.b * a.x_sb + (int64_t)hd * a.x_sh + p];
-        raw[i].dtq = a.dt[(int64_t)c.b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp];
+        raw[i].xq = ld_act(a.x + (int64_t)c.b * a.x_sb + (int64_t)hd * a.x_sh + p);
+        raw[i].dtq = ld_act(a.dt + (int64_t)c.b * a.dt_sb + (int64_t)hd * a.dt_sh + (int64_t)p * a.dt_sp);
         raw[i].aq = kTied ? (int)a.A_log[(int64_t)hd * a.A_sh + (int64_t)p * a.A_sp] : 0;
         raw[i].bias = 0.0f;
         if (a.dt_bias != nullptr) {
@@ -712,7 +712,7 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
       float y = rY[buf][r];
       if (a.D != nullptr) y = fmaf(rX[buf][r], (*a.D_scale) * (float)a.D[(int64_t)hd * a.D_sh + (int64_t)p * a.D_sp], y);
       if (a.z != nullptr) {
-        const float z = (*a.z_scale) * (float)a.z[(int64_t)c.b * a.z_sb + (int64_t)hd * a.z_sh + p];
+        const float z = (*a.z_scale) * (float)ld_act(a.z + (int64_t)c.b * a.z_sb + (int64_t)hd * a.z_sh + p);
         y *= silu_exact(z);
       }
       static_cast<__half*>(a.out)[(int64_t)c.b * a.out_sb + (int64_t)hd * a.out_sh + p] = __float2half_rn(y);
@@ -737,8 +737,8 @@ sscan_update_bulk_kernel(qb_sscan_update_args a, int tiles, int tiles_per_cta, i
       if (tid < kDstate) {
         const float Bs = kGrouped ? a.B_scale[g] : a.B_scale[0];
         const float Cs = kGrouped ? a.C_scale[g] : a.C_scale[0];
-        sB[tid] = Bs * (float)a.Bm[(int64_t)cur.b * a.B_sb + (int64_t)g * a.B_sg + tid] / ss0;
-        sC[tid] = Cs * (float)a.Cm[(int64_t)cur.b * a.C_sb + (int64_t)g * a.C_sg + tid] * ss0;
+        sB[tid] = Bs * (float)ld_act(a.Bm + (int64_t)cur.b * a.B_sb + (int64_t)g * a.B_sg + tid) / ss0;
+        sC[tid] = Cs * (float)ld_act(a.Cm + (int64_t)cur.b * a.C_sb + (int64_t)g * a.C_sg + tid) * ss0;
       }
     }
     __syncthreads();  // row scalars of this tile (written last iteration) and sB / sC are visible

@@ -219,7 +219,9 @@ template <bool kDPerChannel>
 __global__ void __launch_bounds__(kThreads, 1)
 ssd_tc_kernel(const __grid_constant__ CUtensorMap tm_b16, const __grid_constant__ CUtensorMap tm_c16,
               const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_out, qb_ssd_args a,
-              const float* __restrict__ ab_ws, const float* __restrict__ hc_ws, float* __restrict__ handoff, int* __restrict__ flags, int split, int* status) {
+              const float* __restrict__ ab_ws, const float* __restrict__ hc_ws, float* __restrict__ handoff, int* __restrict__ flags, int split, int* status,
+              int early) {
+  if (early) grid_dependency_launch();   // the kernel after this one may get resident and run its prologue as CTAs here finish
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Misc& ms = *reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -727,7 +729,7 @@ __device__ __forceinline__ void ssd_widen_bc(int64_t block, const int8_t* __rest
   const int l = (int)((idx / ((int64_t)pieces * ngroups)) % seqlen);
   const int bb = (int)(idx / ((int64_t)pieces * ngroups * seqlen));
   auto widen = [&](const int8_t* src, __half* dst) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+    const uint4 v = ld_act(reinterpret_cast<const uint4*>(src));     // conv output: an activation, read past L1
     __half2 o[8];
     s8x4_to_h2x2(v.x, o[0], o[1]);
     s8x4_to_h2x2(v.y, o[2], o[3]);
@@ -799,7 +801,7 @@ __device__ __forceinline__ void ssd_dt(int64_t block, const qb_ssd_args& a, floa
     const int l = j * T + lane * 4 + i;
     float v = 0.0f;
     if (l < a.seqlen) {
-      v = fmaf(s_dt, (float)dtp[(int64_t)l * a.dt_sl], bias);
+      v = fmaf(s_dt, (float)ld_act(dtp + (int64_t)l * a.dt_sl), bias);
       if (a.dt_softplus) v = softplus_f(v);
       v = fminf(fmaxf(v, a.dt_min), a.dt_max);
     }
@@ -947,10 +949,11 @@ int ssd_tc_launch(const qb_ssd_args* a, cudaStream_t st) {
     cfg.numAttrs = 1;
     const float* ab_c = ab_ws;
     const float* hc_c = hc_ws;
+    const int early = early_overlap() ? 1 : 0;
     if (a->D != nullptr && a->D_has_hdim) {
-      QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel<true>, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status));
+      QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel<true>, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status, early));
     } else {
-      QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel<false>, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status));
+      QB_CUDA_OK(cudaLaunchKernelEx(&cfg, ssd_tc_kernel<false>, tb, tcm, tx, tout, *a, ab_c, hc_c, handoff, flags, split, status, early));
     }
   }
   return QB_OK;

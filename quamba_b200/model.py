@@ -19,6 +19,7 @@ import torch.nn as nn
 from . import embedding as _emb
 from . import mixer as _mixer
 from . import modules as _modules
+from . import _lib
 from . import ops
 from .norm import QRMSNorm
 
@@ -28,6 +29,8 @@ CausalLMOutput = namedtuple("CausalLMOutput", ["logits"])
 # Development switch: QB_UNFUSED_DECODE=1 keeps the decode step on the one-op-per-launch path (for A/B comparisons).
 import os as _os
 _UNFUSED_DECODE = bool(_os.environ.get("QB_UNFUSED_DECODE"))
+# Development switch: QB_NO_EARLY_OVERLAP=1 launches the prefill kernels without early dependent starts (for A/B comparisons).
+_EARLY_OVERLAP = not _os.environ.get("QB_NO_EARLY_OVERLAP")
 
 
 @dataclass
@@ -174,13 +177,16 @@ class QuambaMixerModel(nn.Module):
         return logits[:, :lm_head.out_features]
 
     def forward(self, input_ids, inference_params=None, num_last_tokens=0, **mixer_kwargs):
-        hidden_states = self.embedding(input_ids)
-        residual = None
-        for layer in self.layers:
-            hidden_states, residual = layer(hidden_states, residual, inference_params=inference_params, **mixer_kwargs)
-        if num_last_tokens > 0:       # the final norm works row by row: rows nobody reads are skipped
-            hidden_states, residual = hidden_states[:, -num_last_tokens:], residual[:, -num_last_tokens:]
-        return self.norm_f(hidden_states, residual=residual, prenorm=False, residual_in_fp32=self.residual_in_fp32)
+        # the layers' kernels let their successors start early (prologue and residency overlap the tail of the kernel
+        # before): the launch sequence in here consists of this library's kernels and ordinary torch launches only
+        with _lib.early_overlap(_EARLY_OVERLAP):
+            hidden_states = self.embedding(input_ids)
+            residual = None
+            for layer in self.layers:
+                hidden_states, residual = layer(hidden_states, residual, inference_params=inference_params, **mixer_kwargs)
+            if num_last_tokens > 0:       # the final norm works row by row: rows nobody reads are skipped
+                hidden_states, residual = hidden_states[:, -num_last_tokens:], residual[:, -num_last_tokens:]
+            return self.norm_f(hidden_states, residual=residual, prenorm=False, residual_in_fp32=self.residual_in_fp32)
 
 
 class QuambaLMHeadModel(nn.Module):

@@ -247,6 +247,34 @@ def test_model_prefill_and_graph_decode_match_oracle():
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
 
 
+@pytest.mark.parametrize("group", [None, -1])
+def test_graph_replayed_prefill_equals_the_eager_prefill_bit_for_bit(group):
+    """Eager launches are separated by host time and never overlap; a replayed graph runs the same launches back to back
+    with each kernel's successor started early.  Equal logits and caches, bit for bit and over several replays on
+    different prompts, is the check that no kernel reads what its predecessor has not finished writing (or a stale copy
+    of it)."""
+    import copy
+    from quamba_b200.model import InferenceParams
+    q, _ = _small(21, group, d_model=512, n_layer=3, vocab=640, L=64, batch=2)
+    gq = copy.deepcopy(q).to(DEV)
+    L = 700
+    runner = gq.capture_prefill(2, L)
+    g = torch.Generator().manual_seed(5)
+    for rep in range(4):
+        ids = torch.randint(0, 640, (2, L), generator=g).to(DEV)
+        runner.input_ids.copy_(ids)
+        got = runner.replay().clone()
+        got_states = {k: tuple(t.clone() for t in v) for k, v in runner.inference_params.key_value_memory_dict.items()}
+        params = InferenceParams(max_seqlen=L + 8, max_batch_size=2)
+        want = gq(ids, inference_params=params, num_last_tokens=1).logits[:, -1]
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"replay {rep}: logits differ between the graph and the eager prefill"
+        for k, v in params.key_value_memory_dict.items():
+            assert torch.equal(got_states[k][0], v[0]) and torch.equal(got_states[k][1], v[1]), f"replay {rep}: layer {k} caches differ"
+    import quamba_b200
+    quamba_b200.check_device_status()
+
+
 def test_generate_greedy_graph_equals_eager():
     import copy
     q, ids = _small(5, -1, n_layer=2, L=64, batch=1)
