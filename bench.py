@@ -378,6 +378,8 @@ def main():
     ap.add_argument("--model", default="2.7b", choices=["2.7b", "8b"], help="8b: the head-parallel Mamba2-8B prefill (always used for --gpus >= 2)")
     ap.add_argument("--no-8b-base", action="store_true", help="skip the single-GPU Mamba2-8B measurement added to the 2.7B line")
     ap.add_argument("--comm-sms", type=int, default=16, help="--gpus >= 2: multiprocessors left to NCCL (compute grids use the rest); 0 = no split")
+    ap.add_argument("--plain-allreduce", action="store_true", help="--gpus >= 2: one fp16 all-reduce per layer and a replicated block norm "
+                    "instead of reduce-scatter + token-sharded norm + int8 all-gather")
     ap.add_argument("--seqlen", type=int, default=PROMPT)
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
     args = ap.parse_args()

@@ -34,6 +34,7 @@ class Stack:
         from quamba_b200.norm import QRMSNorm
         from quamba_b200.parallel import shard_mixer
         self.cfg, self.rank, self.world, self.dev = cfg, rank, world, dev
+        self.token_sharded_norm = True
         gen = torch.Generator(device=dev).manual_seed(seed)
         d, V = cfg["d_model"], cfg["vocab_size"]
         table = (torch.randn(V, d, generator=gen, device=dev) * 0.02).half()
@@ -76,6 +77,80 @@ class Stack:
             return self._prefill(ids, chunk_seqs, collective, compute)
 
     def _prefill(self, ids, chunk_seqs, collective=True, compute=True):
+        if self.world > 1 and self.token_sharded_norm:
+            return self._prefill_token_sharded(ids, chunk_seqs, collective, compute)
+        return self._prefill_allreduce(ids, chunk_seqs, collective, compute)
+
+    def _prefill_token_sharded(self, ids, chunk_seqs, collective=True, compute=True):
+        """The layer's all-reduce split into its two halves with the block norm between them: reduce-scatter of the fp16
+        partial outputs over the token rows, residual add + RMSNorm + quantise on this rank's rows only (the residual
+        stream stays sharded by rows), all-gather of the INT8 rows for the next in_proj.  Same sums as the all-reduce,
+        3 instead of 4 bytes per element over NVLink, and the norm is no longer replicated on every rank."""
+        T, rank = self.world, self.rank
+        chunks = list(ids.split(chunk_seqs))
+        n = len(chunks)
+        d = self.cfg["d_model"]
+        rows = chunks[0].numel()
+        assert rows % T == 0
+        per = rows // T
+        mine = slice(rank * per, (rank + 1) * per)
+        # embedding: every rank looks up its own rows only
+        hs = [self.embedding(c.reshape(-1)[mine]) if compute else torch.empty((per, d), dtype=torch.float16, device=self.dev) for c in chunks]
+        res = [None] * n
+        partial = [None] * n
+        q_full = [torch.empty((rows, d), dtype=torch.int8, device=self.dev) for _ in range(n)]
+        pend_rs, pend_ag = [None] * n, [None] * n
+        L = len(self.norms)
+        for li, (norm, shard) in enumerate(zip(self.norms, self.shards)):
+            for c in range(n):
+                if pend_rs[c] is not None:
+                    pend_rs[c].wait(); pend_rs[c] = None
+                if compute:
+                    q, res[c] = norm(hs[c], residual=res[c], prenorm=True, residual_in_fp32=True)
+                else:
+                    q = q_full[c][mine]
+                if collective:
+                    pend_ag[c] = dist.all_gather_into_tensor(q_full[c], q.contiguous(), async_op=True)
+                else:
+                    q_full[c][mine].copy_(q)
+            for c in range(n):
+                if pend_ag[c] is not None:
+                    pend_ag[c].wait(); pend_ag[c] = None
+                if compute:
+                    partial[c] = shard(q_full[c].view(chunks[c].shape[0], -1, d)).reshape(rows, d)
+                    if not partial[c].is_contiguous():
+                        partial[c] = partial[c].contiguous()
+                elif partial[c] is None:
+                    partial[c] = torch.zeros((rows, d), dtype=torch.float16, device=self.dev)
+                if collective:
+                    hs[c] = torch.empty((per, d), dtype=torch.float16, device=self.dev)
+                    pend_rs[c] = dist.reduce_scatter_tensor(hs[c], partial[c], async_op=True)
+                else:
+                    hs[c] = partial[c][mine]
+        for c in range(n):
+            if pend_rs[c] is not None:
+                pend_rs[c].wait()
+        if not compute:
+            return None
+        # last token of every sequence: its row lives on one rank; every rank fills its own rows of a small buffer and one
+        # tiny all-reduce gives all of them to everybody
+        seqlen = chunks[0].shape[1]
+        lasts = []
+        for c in range(n):
+            nseq = chunks[c].shape[0]
+            buf_h = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
+            buf_r = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
+            for s_ in range(nseq):
+                row = (s_ + 1) * seqlen - 1
+                if rank * per <= row < (rank + 1) * per:
+                    buf_h[s_] = hs[c][row - rank * per].float()
+                    buf_r[s_] = res[c][row - rank * per]
+            if collective:
+                dist.all_reduce(buf_h); dist.all_reduce(buf_r)
+            lasts.append(self.norm_f(buf_h.half()[:, None], residual=buf_r[:, None], prenorm=False, residual_in_fp32=True))
+        return self.lm_head(torch.cat(lasts))[:, -1]
+
+    def _prefill_allreduce(self, ids, chunk_seqs, collective=True, compute=True):
         """ids (batch, L) on the device -> last-token logits (batch, vocab).  ``collective`` / ``compute`` switch the two
         halves off for the separate timings."""
         chunks = list(ids.split(chunk_seqs))
@@ -112,6 +187,7 @@ def run(args, rank, local_rank, world, layers=None):
     cfg = dict(CFG8B, n_layer=layers or CFG8B["n_layer"])
     t0 = time.time()
     stack = Stack(cfg, rank, world, dev)
+    stack.token_sharded_norm = not getattr(args, "plain_allreduce", False)
     build_s = time.time() - t0
     g = torch.Generator().manual_seed(99)
     ids = [torch.randint(0, cfg["vocab_size"], (BATCH, PROMPT), generator=g).to(dev) for _ in range(2)]
@@ -144,6 +220,16 @@ def run(args, rank, local_rank, world, layers=None):
         logits = stack.prefill(ids[0], chunk_seqs)
     barrier()
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
+    # the two forms of the layer's collective compute the same sums: compare their last-token logits once, outside the timing
+    form_diff = None
+    if world > 1 and stack.token_sharded_norm:
+        with _lib.early_overlap(True), torch.no_grad():
+            other = stack._prefill_allreduce(ids[0], chunk_seqs)
+        torch.cuda.synchronize()
+        form_diff = {"max_abs_diff": (logits.float() - other.float()).abs().max().item(), "max_abs_logit": other.float().abs().max().item(),
+                     "same_argmax": bool((logits.argmax(-1) == other.argmax(-1)).all().item())}
+        del other
+    barrier()
     from bench_mixer_core import ClockSampler
     sampler = ClockSampler(dev.index)
     if rank == 0:
@@ -159,12 +245,19 @@ def run(args, rank, local_rank, world, layers=None):
     D, G, N, H = cfg["d_model"] * cfg["expand"], cfg["ngroups"], cfg["d_state"], cfg["d_model"] * cfg["expand"] // cfg["headdim"]
     flops = cfg["n_layer"] * 2 * tokens * cfg["d_model"] * (2 * D + 2 * G * N + H + D)
     reduce_bytes = cfg["n_layer"] * tokens * cfg["d_model"] * 2
+    link_factor = ((world - 1) / world * 1.5 if stack.token_sharded_norm else 2 * (world - 1) / world) if world > 1 else 0.0
     return {"value": tokens / (ms_step * 1e-3), "unit": "tok/s", "ms_per_step": ms_step, "compute_only_ms": ms_compute,
             "allreduce_alone_ms": ms_comm, "allreduce_exposed_ms": max(0.0, ms_step - ms_compute) if world > 1 else 0.0,
             "allreduce_share_of_step": max(0.0, ms_step - ms_compute) / ms_step if world > 1 else 0.0,
             "allreduce_bytes_per_step": reduce_bytes if world > 1 else 0,
-            "allreduce_bus_gbs": (2 * (world - 1) / world * reduce_bytes / (ms_comm * 1e-3) / 1e9) if world > 1 and ms_comm > 0 else None,
+            # bytes every rank sends (= receives) per step over NVLink, and the rate when the collectives run alone:
+            # all-reduce 2 (T-1)/T x 2 B per element; reduce-scatter + int8 all-gather (T-1)/T x (2 + 1) B
+            "nvlink_bytes_per_rank_per_step": int(link_factor * reduce_bytes) if world > 1 else 0,
+            "allreduce_bus_gbs": (link_factor * reduce_bytes / (ms_comm * 1e-3) / 1e9) if world > 1 and ms_comm > 0 else None,
             "gemm_flops_per_step": flops, "gemm_tops_per_gpu": flops / world / (ms_compute * 1e-3) / 1e12,
             "chunk_sequences": chunk_seqs, "layers": cfg["n_layer"], "build_seconds": build_s, "workload": WORKLOAD8B,
             "clocks": clocks, "compute_sms": sm_total - comm_sms, "nccl_max_ctas": comm_sms if world > 1 else None,
+            "token_sharded_vs_allreduce_logits": form_diff,
+            "collective": ("reduce-scatter (fp16) + all-gather (int8) around a token-sharded block norm" if stack.token_sharded_norm
+                           else "all-reduce (fp16)") if world > 1 else None,
             "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}
