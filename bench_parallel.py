@@ -34,7 +34,6 @@ class Stack:
         from quamba_b200.norm import QRMSNorm
         from quamba_b200.parallel import shard_mixer
         self.cfg, self.rank, self.world, self.dev = cfg, rank, world, dev
-        self.token_sharded_norm = True
         gen = torch.Generator(device=dev).manual_seed(seed)
         d, V = cfg["d_model"], cfg["vocab_size"]
         table = (torch.randn(V, d, generator=gen, device=dev) * 0.02).half()
@@ -71,112 +70,10 @@ class Stack:
         del head, table
         torch.cuda.empty_cache()
 
-    def prefill(self, ids, chunk_seqs, collective=True, compute=True):
-        from quamba_b200 import _lib
-        with _lib.early_overlap(True), torch.no_grad():
-            return self._prefill(ids, chunk_seqs, collective, compute)
-
-    def _prefill(self, ids, chunk_seqs, collective=True, compute=True):
-        if self.world > 1 and self.token_sharded_norm:
-            return self._prefill_token_sharded(ids, chunk_seqs, collective, compute)
-        return self._prefill_allreduce(ids, chunk_seqs, collective, compute)
-
-    def _prefill_token_sharded(self, ids, chunk_seqs, collective=True, compute=True):
-        """The layer's all-reduce split into its two halves with the block norm between them: reduce-scatter of the fp16
-        partial outputs over the token rows, residual add + RMSNorm + quantise on this rank's rows only (the residual
-        stream stays sharded by rows), all-gather of the INT8 rows for the next in_proj.  Same sums as the all-reduce,
-        3 instead of 4 bytes per element over NVLink, and the norm is no longer replicated on every rank."""
-        T, rank = self.world, self.rank
-        chunks = list(ids.split(chunk_seqs))
-        n = len(chunks)
-        d = self.cfg["d_model"]
-        rows = chunks[0].numel()
-        assert rows % T == 0
-        per = rows // T
-        mine = slice(rank * per, (rank + 1) * per)
-        # embedding: every rank looks up its own rows only
-        hs = [self.embedding(c.reshape(-1)[mine]) if compute else torch.empty((per, d), dtype=torch.float16, device=self.dev) for c in chunks]
-        res = [None] * n
-        partial = [None] * n
-        q_full = [torch.empty((rows, d), dtype=torch.int8, device=self.dev) for _ in range(n)]
-        pend_rs, pend_ag = [None] * n, [None] * n
-        L = len(self.norms)
-        for li, (norm, shard) in enumerate(zip(self.norms, self.shards)):
-            for c in range(n):
-                if pend_rs[c] is not None:
-                    pend_rs[c].wait(); pend_rs[c] = None
-                if compute:
-                    q, res[c] = norm(hs[c], residual=res[c], prenorm=True, residual_in_fp32=True)
-                else:
-                    q = q_full[c][mine]
-                if collective:
-                    pend_ag[c] = dist.all_gather_into_tensor(q_full[c], q.contiguous(), async_op=True)
-                else:
-                    q_full[c][mine].copy_(q)
-            for c in range(n):
-                if pend_ag[c] is not None:
-                    pend_ag[c].wait(); pend_ag[c] = None
-                if compute:
-                    partial[c] = shard(q_full[c].view(chunks[c].shape[0], -1, d)).reshape(rows, d)
-                    if not partial[c].is_contiguous():
-                        partial[c] = partial[c].contiguous()
-                elif partial[c] is None:
-                    partial[c] = torch.zeros((rows, d), dtype=torch.float16, device=self.dev)
-                if collective:
-                    hs[c] = torch.empty((per, d), dtype=torch.float16, device=self.dev)
-                    pend_rs[c] = dist.reduce_scatter_tensor(hs[c], partial[c], async_op=True)
-                else:
-                    hs[c] = partial[c][mine]
-        for c in range(n):
-            if pend_rs[c] is not None:
-                pend_rs[c].wait()
-        if not compute:
-            return None
-        # last token of every sequence: its row lives on one rank; every rank fills its own rows of a small buffer and one
-        # tiny all-reduce gives all of them to everybody
-        seqlen = chunks[0].shape[1]
-        lasts = []
-        for c in range(n):
-            nseq = chunks[c].shape[0]
-            buf_h = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
-            buf_r = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
-            for s_ in range(nseq):
-                row = (s_ + 1) * seqlen - 1
-                if rank * per <= row < (rank + 1) * per:
-                    buf_h[s_] = hs[c][row - rank * per].float()
-                    buf_r[s_] = res[c][row - rank * per]
-            if collective:
-                dist.all_reduce(buf_h); dist.all_reduce(buf_r)
-            lasts.append(self.norm_f(buf_h.half()[:, None], residual=buf_r[:, None], prenorm=False, residual_in_fp32=True))
-        return self.lm_head(torch.cat(lasts))[:, -1]
-
-    def _prefill_allreduce(self, ids, chunk_seqs, collective=True, compute=True):
-        """ids (batch, L) on the device -> last-token logits (batch, vocab).  ``collective`` / ``compute`` switch the two
-        halves off for the separate timings."""
-        chunks = list(ids.split(chunk_seqs))
-        n = len(chunks)
-        h = [self.embedding(c) for c in chunks]
-        res = [None] * n
-        pending = [None] * n
-        for norm, shard in zip(self.norms, self.shards):
-            for c in range(n):
-                if pending[c] is not None:
-                    pending[c].wait()
-                    pending[c] = None
-                if compute:
-                    q, res[c] = norm(h[c], residual=res[c], prenorm=True, residual_in_fp32=True)
-                    h[c] = shard(q)
-                if collective and self.world > 1:
-                    if not h[c].is_contiguous():
-                        h[c] = h[c].contiguous()
-                    pending[c] = dist.all_reduce(h[c], async_op=True)
-        for c in range(n):
-            if pending[c] is not None:
-                pending[c].wait()
-        if not compute:
-            return None
-        last = torch.cat([self.norm_f(h[c][:, -1:], residual=res[c][:, -1:], prenorm=False, residual_in_fp32=True) for c in range(n)])
-        return self.lm_head(last)[:, -1]
+    def runner(self):
+        from quamba_b200.parallel import HeadParallelStack
+        return HeadParallelStack(self.embedding, self.norms, self.shards, self.norm_f, self.lm_head, self.rank, self.world,
+                                 self.cfg["d_model"])
 
 
 def run(args, rank, local_rank, world, layers=None):
@@ -186,7 +83,7 @@ def run(args, rank, local_rank, world, layers=None):
     dev = torch.device("cuda", local_rank)
     cfg = dict(CFG8B, n_layer=layers or CFG8B["n_layer"])
     t0 = time.time()
-    stack = Stack(cfg, rank, world, dev)
+    stack = Stack(cfg, rank, world, dev).runner()
     stack.token_sharded_norm = not getattr(args, "plain_allreduce", False)
     build_s = time.time() - t0
     g = torch.Generator().manual_seed(99)

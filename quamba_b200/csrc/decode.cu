@@ -20,7 +20,11 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kNW = 2;              // output columns per warp and pass
+// Output columns per warp and pass (NW) and 16-byte weight chunks a lane requests per column before it uses any (NB).
+// SH = 0: 2 x 5, any k up to 8192.  SH = 1: 5 x 3 for wide products of short columns (at most 96 chunks per column): the
+// 2.7B in_proj is 4.5 columns per resident warp, i.e. three dependent passes of two columns for a quarter of the warps and
+// two for the rest -- or ONE pass of five for all of them; what a pass costs is its chain of round trips, not its bytes.
+template <int SH> struct Shape { static constexpr int NW = SH ? 5 : 2; static constexpr int NB = SH ? 3 : 5; };
 constexpr int kMaxRows = 4;         // batch rows a launch takes
 
 
@@ -80,7 +84,6 @@ struct ConvEpi {
 // dot products of the int8 rows in shared memory (MB rows of k bytes) with weight columns n0 .. n0 + kNW - 1.
 // A lane loads kNB weight chunks per column BEFORE it uses any (clamped addresses, so the loads need no branches): at the
 // model's sizes that is the lane's whole share of a column in one round trip to L2 instead of one round trip per chunk.
-constexpr int kNB = 5;
 
 // One 32-bit word of format 2 (byte b: code of k = b in the low, of k = 4 + b in the high nibble) -> the int8 weights of
 // k = 0..3 and of k = 4..7.  (1024 + q) - 1032 = q - 8 is exact in fp16; fma(q - 8, s, 1152) rounds the exact product once,
@@ -100,8 +103,9 @@ __device__ __forceinline__ void dequant8_group(uint32_t w, __half2 s2, uint32_t&
   hi4 = __byte_perm(r[2], r[3], 0x6240) ^ 0x80808080u;
 }
 
-template <int MB, int S4>
-__device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][kNW]) {
+template <int MB, int S4, int SH>
+__device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][Shape<SH>::NW]) {
+  constexpr int kNW = Shape<SH>::NW, kNB = Shape<SH>::NB;
   int sa[MB];
 #pragma unroll
   for (int i = 0; i < MB; ++i) {
@@ -258,8 +262,9 @@ __device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, const
 // Ask L2 for every weight row this warp will stream (all its passes).  Weights do not depend on the kernel before this
 // one, so the call sits ahead of the dependency wait and of the shared-memory prologue: HBM delivers while the prologue
 // computes, and each pass then costs a round trip to L2 instead of one to HBM.
-template <int S4>
+template <int S4, int SH>
 __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
+  constexpr int kNW = Shape<SH>::NW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row_bytes = S4 ? L.k / 2 : L.k;
   for (int n0 = (blockIdx.x * kWarps + warp) * kNW; n0 < L.n; n0 += (int)gridDim.x * kWarps * kNW) {
@@ -273,8 +278,9 @@ __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
 }
 
 // `pre`: the finishing lane's constants of the first pass, loaded by the caller before the dependency wait.
-template <int MB, int S4>
+template <int MB, int S4, int SH>
 __device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows, FinishPre pre) {
+  constexpr int kNW = Shape<SH>::NW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = lane / kNW, j = lane % kNW;
   const int first = (blockIdx.x * kWarps + warp) * kNW;
@@ -282,7 +288,7 @@ __device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& c
     const bool mine = lane < MB * kNW && i < rows && n0 + j < L.n;
     if (n0 != first && mine) pre = finish_prefetch(L, cv, i, n0 + j);
     int acc[MB][kNW];
-    dot_columns<MB, S4>(L, sA, n0, lane, acc);
+    dot_columns<MB, S4, SH>(L, sA, n0, lane, acc);
     // lanes 0 .. MB * kNW - 1 finish one (row, column) each, so that the conv windows of a warp's columns move in parallel
     if (mine) {
       int v = 0;
@@ -296,8 +302,9 @@ __device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& c
   }
 }
 
-template <int MB>
+template <int MB, int SH>
 __device__ __forceinline__ FinishPre first_pass_prefetch(const Linear& L, const ConvEpi& cv, int rows) {
+  constexpr int kNW = Shape<SH>::NW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = lane / kNW, j = lane % kNW;
   const int n0 = (blockIdx.x * kWarps + warp) * kNW;
@@ -318,7 +325,7 @@ struct NormIn {
   float eps, out_scale;
 };
 
-template <int MB, int S4>
+template <int MB, int S4, int SH>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   extern __shared__ __align__(16) uint8_t dsm[];
@@ -326,8 +333,8 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
   int8_t* sA = reinterpret_cast<int8_t*>(dsm);                 // MB rows of k int8
   const int K = L.k;
   if (nin.early_launch) grid_dependency_launch();
-  prefetch_first_columns<S4>(L);
-  const FinishPre pre = first_pass_prefetch<MB>(L, cv, rows);
+  prefetch_first_columns<S4, SH>(L);
+  const FinishPre pre = first_pass_prefetch<MB, SH>(L, cv, rows);
   const int chunks = K / 8;
   uint4 nw[4];               // the norm weights of this thread's chunks: constants, fetched ahead of the wait
   if (nin.a_int8 == nullptr) {
@@ -342,7 +349,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
         *(reinterpret_cast<uint4*>(sA + (int64_t)m * K) + c) = __ldcg(reinterpret_cast<const uint4*>(nin.a_int8 + (int64_t)row * nin.x_stride) + c);
     }
     __syncthreads();
-    stream_columns<MB, S4>(L, cv, sA, rows, pre);
+    stream_columns<MB, S4, SH>(L, cv, sA, rows, pre);
     return;
   }
   const float inv_scale = 1.0f / nin.out_scale;
@@ -411,7 +418,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
     }
   }
   __syncthreads();
-  stream_columns<MB, S4>(L, cv, sA, rows, pre);
+  stream_columns<MB, S4, SH>(L, cv, sA, rows, pre);
 }
 
 // ---- launch 3: gate, grouped RMSNorm, Hadamard rotation, quantise -> product -------------------------------------------
@@ -567,8 +574,8 @@ int fill_linear(Linear& L, const void* w, const float* s_ch, const float* s_tok,
   return QB_OK;
 }
 
-unsigned grid_for(int n, int ctas_per_sm) {
-  return (unsigned)std::min<int64_t>(ceil_div(n, kWarps * kNW), (int64_t)sm_count() * ctas_per_sm);
+unsigned grid_for(int n, int ctas_per_sm, int nw) {
+  return (unsigned)std::min<int64_t>(ceil_div(n, kWarps * nw), (int64_t)sm_count() * ctas_per_sm);
 }
 
 template <typename K>
@@ -584,14 +591,16 @@ int opt_in_smem(K kernel, size_t bytes) {
 using namespace qb;
 
 #define QB_LAUNCH_ONE(KERNEL, MBV, WMV, grid, smem, st, ...)                                                             \
-  { rc__ = opt_in_smem(KERNEL<MBV, WMV>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<MBV, WMV>, grid, dim3(kThreads), smem, st, __VA_ARGS__); }
+  { if (sh__) { rc__ = opt_in_smem(KERNEL<MBV, WMV, 1>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<MBV, WMV, 1>, grid, dim3(kThreads), smem, st, __VA_ARGS__); } \
+    else { rc__ = opt_in_smem(KERNEL<MBV, WMV, 0>, smem); if (rc__ == QB_OK) launch_dependent(KERNEL<MBV, WMV, 0>, grid, dim3(kThreads), smem, st, __VA_ARGS__); } }
 #define QB_DISPATCH_WM(KERNEL, MBV, wm, grid, smem, st, ...)                                                             \
   if (wm == 2) QB_LAUNCH_ONE(KERNEL, MBV, 2, grid, smem, st, __VA_ARGS__)                                                 \
   else if (wm == 1) QB_LAUNCH_ONE(KERNEL, MBV, 1, grid, smem, st, __VA_ARGS__)                                            \
   else QB_LAUNCH_ONE(KERNEL, MBV, 0, grid, smem, st, __VA_ARGS__)
-#define QB_DISPATCH_MB_S4(KERNEL, rows, wm, grid, smem, st, ...)                                                          \
+#define QB_DISPATCH_MB_S4(KERNEL, rows, wm, sh, grid, smem, st, ...)                                                      \
   do {                                                                                                                    \
     int rc__ = QB_OK;                                                                                                     \
+    const int sh__ = (sh);                                                                                                \
     if (rows == 1) { QB_DISPATCH_WM(KERNEL, 1, wm, grid, smem, st, __VA_ARGS__) }                                         \
     else if (rows == 2) { QB_DISPATCH_WM(KERNEL, 2, wm, grid, smem, st, __VA_ARGS__) }                                    \
     else { QB_DISPATCH_WM(KERNEL, 4, wm, grid, smem, st, __VA_ARGS__) }                                                   \
@@ -635,7 +644,11 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
   }
   const int mb = a->rows <= 2 ? a->rows : 4;
   const size_t smem = (size_t)mb * a->k;
-  const dim3 grid(grid_for(a->n, 2));
+  // five columns per warp in one pass when the columns are short (at most 96 chunks) and two per warp would take more
+  // than one pass of the resident warps
+  const int chunks = a->w_is_s4 != 0 ? a->k / 32 : a->k / 16;
+  const int sh = chunks <= 96 && (int64_t)a->n > (int64_t)sm_count() * 2 * kWarps * 2 ? 1 : 0;
+  const dim3 grid(grid_for(a->n, 2, sh ? 5 : 2));
   cudaStream_t st = (cudaStream_t)stream;
   const int rows = a->rows;
   const int wm = a->w_is_s4 == 0 ? 0 : (a->s_group_nat != nullptr ? 2 : 1);
@@ -643,7 +656,7 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
     QB_REQUIRE(a->k % 128 == 0 && aligned(a->s_group_nat, 2), QB_ERR_INVALID_ARG, "decode_norm_linear: group scales need k to be a multiple of 128");
     L.s_grp = static_cast<const __half*>(a->s_group_nat);
   }
-  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, wm, grid, smem, st, nin, L, cv, rows);
+  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, wm, sh, grid, smem, st, nin, L, cv, rows);
   QB_LAUNCH_OK("decode_norm_linear_kernel");
   return QB_OK;
 }

@@ -16,12 +16,13 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from . import _lib
 from . import packing
 from .mixer import W4A8QMamba2, _QMamba2
 from .modules import QHadamard, Quamb2Conv1D, Quamba2ChunkScan, W4A8B8O8LinearParallel, W4A8B16O16Linear
 from .norm import QRMSNormGated
 
-__all__ = ["shard_w4a8_columns", "shard_w4a8_rows", "shard_mixer", "HeadParallelMixer", "rank_columns"]
+__all__ = ["shard_w4a8_columns", "shard_w4a8_rows", "shard_mixer", "HeadParallelMixer", "HeadParallelStack", "rank_columns"]
 
 
 def _codes(lin):
@@ -142,3 +143,127 @@ class HeadParallelMixer(nn.Module):
             out = out.contiguous()
         work = dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.process_group, async_op=async_op)
         return (out, work) if async_op else out
+
+
+class HeadParallelStack:
+    """A rank's share of a whole model for head-parallel prefill: replicated embedding, block norms, final norm and head,
+    sharded mixers (:func:`shard_mixer`).  ``prefill`` runs the layers on chunks of sequences so that the collective of one
+    chunk overlaps the compute of the next, in one of two forms of the layer's single exchange step:
+
+    * ``token_sharded_norm = True`` (default): reduce-scatter of the fp16 partial outputs over the token rows, residual add
+      + RMSNorm + quantise on this rank's rows only, all-gather of the int8 rows for the next in_proj;
+    * ``False``: one fp16 all-reduce per layer, block norm replicated on every rank.
+
+    ``collective`` / ``compute`` switch the two halves off for separate timings (the results are then meaningless)."""
+
+    def __init__(self, embedding, norms, shards, norm_f, lm_head, rank, world, d_model):
+        self.embedding, self.norms, self.shards, self.norm_f, self.lm_head = embedding, norms, shards, norm_f, lm_head
+        self.rank, self.world, self.d_model = rank, world, d_model
+        self.dev = lm_head.weight.device
+        self.token_sharded_norm = True
+
+    def prefill(self, ids, chunk_seqs, collective=True, compute=True):
+        with _lib.early_overlap(True), torch.no_grad():
+            return self._prefill(ids, chunk_seqs, collective, compute)
+
+    def _prefill(self, ids, chunk_seqs, collective=True, compute=True):
+        if self.world > 1 and self.token_sharded_norm:
+            return self._prefill_token_sharded(ids, chunk_seqs, collective, compute)
+        return self._prefill_allreduce(ids, chunk_seqs, collective, compute)
+
+    def _prefill_token_sharded(self, ids, chunk_seqs, collective=True, compute=True):
+        """The layer's all-reduce split into its two halves with the block norm between them: reduce-scatter of the fp16
+        partial outputs over the token rows, residual add + RMSNorm + quantise on this rank's rows only (the residual
+        stream stays sharded by rows), all-gather of the INT8 rows for the next in_proj.  Same sums as the all-reduce,
+        3 instead of 4 bytes per element over NVLink, and the norm is no longer replicated on every rank."""
+        T, rank = self.world, self.rank
+        chunks = list(ids.split(chunk_seqs))
+        n = len(chunks)
+        d = self.d_model
+        rows = chunks[0].numel()
+        assert rows % T == 0
+        per = rows // T
+        mine = slice(rank * per, (rank + 1) * per)
+        # embedding: every rank looks up its own rows only
+        hs = [self.embedding(c.reshape(-1)[mine]) if compute else torch.empty((per, d), dtype=torch.float16, device=self.dev) for c in chunks]
+        res = [None] * n
+        partial = [None] * n
+        q_full = [torch.empty((rows, d), dtype=torch.int8, device=self.dev) for _ in range(n)]
+        pend_rs, pend_ag = [None] * n, [None] * n
+        L = len(self.norms)
+        for li, (norm, shard) in enumerate(zip(self.norms, self.shards)):
+            for c in range(n):
+                if pend_rs[c] is not None:
+                    pend_rs[c].wait(); pend_rs[c] = None
+                if compute:
+                    q, res[c] = norm(hs[c], residual=res[c], prenorm=True, residual_in_fp32=True)
+                else:
+                    q = q_full[c][mine]
+                if collective:
+                    pend_ag[c] = dist.all_gather_into_tensor(q_full[c], q.contiguous(), async_op=True)
+                else:
+                    q_full[c][mine].copy_(q)
+            for c in range(n):
+                if pend_ag[c] is not None:
+                    pend_ag[c].wait(); pend_ag[c] = None
+                if compute:
+                    partial[c] = shard(q_full[c].view(chunks[c].shape[0], -1, d)).reshape(rows, d)
+                    if not partial[c].is_contiguous():
+                        partial[c] = partial[c].contiguous()
+                elif partial[c] is None:
+                    partial[c] = torch.zeros((rows, d), dtype=torch.float16, device=self.dev)
+                if collective:
+                    hs[c] = torch.empty((per, d), dtype=torch.float16, device=self.dev)
+                    pend_rs[c] = dist.reduce_scatter_tensor(hs[c], partial[c], async_op=True)
+                else:
+                    hs[c] = partial[c][mine]
+        for c in range(n):
+            if pend_rs[c] is not None:
+                pend_rs[c].wait()
+        if not compute:
+            return None
+        # last token of every sequence: its row lives on one rank; every rank fills its own rows of a small buffer and one
+        # tiny all-reduce gives all of them to everybody
+        seqlen = chunks[0].shape[1]
+        lasts = []
+        for c in range(n):
+            nseq = chunks[c].shape[0]
+            buf_h = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
+            buf_r = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
+            for s_ in range(nseq):
+                row = (s_ + 1) * seqlen - 1
+                if rank * per <= row < (rank + 1) * per:
+                    buf_h[s_] = hs[c][row - rank * per].float()
+                    buf_r[s_] = res[c][row - rank * per]
+            if collective:
+                dist.all_reduce(buf_h); dist.all_reduce(buf_r)
+            lasts.append(self.norm_f(buf_h.half()[:, None], residual=buf_r[:, None], prenorm=False, residual_in_fp32=True))
+        return self.lm_head(torch.cat(lasts))[:, -1]
+
+    def _prefill_allreduce(self, ids, chunk_seqs, collective=True, compute=True):
+        """ids (batch, L) on the device -> last-token logits (batch, vocab).  ``collective`` / ``compute`` switch the two
+        halves off for the separate timings."""
+        chunks = list(ids.split(chunk_seqs))
+        n = len(chunks)
+        h = [self.embedding(c) for c in chunks]
+        res = [None] * n
+        pending = [None] * n
+        for norm, shard in zip(self.norms, self.shards):
+            for c in range(n):
+                if pending[c] is not None:
+                    pending[c].wait()
+                    pending[c] = None
+                if compute:
+                    q, res[c] = norm(h[c], residual=res[c], prenorm=True, residual_in_fp32=True)
+                    h[c] = shard(q)
+                if collective and self.world > 1:
+                    if not h[c].is_contiguous():
+                        h[c] = h[c].contiguous()
+                    pending[c] = dist.all_reduce(h[c], async_op=True)
+        for c in range(n):
+            if pending[c] is not None:
+                pending[c].wait()
+        if not compute:
+            return None
+        last = torch.cat([self.norm_f(h[c][:, -1:], residual=res[c][:, -1:], prenorm=False, residual_in_fp32=True) for c in range(n)])
+        return self.lm_head(last)[:, -1]
