@@ -85,6 +85,8 @@ def run(args, rank, local_rank, world, layers=None):
     t0 = time.time()
     stack = Stack(cfg, rank, world, dev).runner()
     stack.token_sharded_norm = not getattr(args, "plain_allreduce", False)
+    import os
+    stack.early_overlap = not os.environ.get("QB_NO_EARLY_OVERLAP")
     build_s = time.time() - t0
     g = torch.Generator().manual_seed(99)
     ids = [torch.randint(0, cfg["vocab_size"], (BATCH, PROMPT), generator=g).to(dev) for _ in range(2)]
@@ -120,7 +122,7 @@ def run(args, rank, local_rank, world, layers=None):
     # the two forms of the layer's collective compute the same sums: compare their last-token logits once, outside the timing
     form_diff = None
     if world > 1 and stack.token_sharded_norm:
-        with _lib.early_overlap(True), torch.no_grad():
+        with _lib.early_overlap(stack.early_overlap), torch.no_grad():
             other = stack._prefill_allreduce(ids[0], chunk_seqs)
         torch.cuda.synchronize()
         form_diff = {"max_abs_diff": (logits.float() - other.float()).abs().max().item(), "max_abs_logit": other.float().abs().max().item(),
@@ -155,6 +157,9 @@ def run(args, rank, local_rank, world, layers=None):
             "chunk_sequences": chunk_seqs, "layers": cfg["n_layer"], "build_seconds": build_s, "workload": WORKLOAD8B,
             "clocks": clocks, "compute_sms": sm_total - comm_sms, "nccl_max_ctas": comm_sms if world > 1 else None,
             "token_sharded_vs_allreduce_logits": form_diff,
+            # the same seed builds the same model on any number of GPUs: these must agree between N = 1 and N > 1
+            "logits_digest": {"argmax": logits.argmax(-1).tolist(), "row0_first8": [round(v, 4) for v in logits[0, :8].float().tolist()],
+                              "abs_sum": round(logits.float().abs().sum().item(), 2)},
             "collective": ("reduce-scatter (fp16) + all-gather (int8) around a token-sharded block norm" if stack.token_sharded_norm
                            else "all-reduce (fp16)") if world > 1 else None,
             "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}

@@ -161,9 +161,10 @@ class HeadParallelStack:
         self.rank, self.world, self.d_model = rank, world, d_model
         self.dev = lm_head.weight.device
         self.token_sharded_norm = True
+        self.early_overlap = True
 
     def prefill(self, ids, chunk_seqs, collective=True, compute=True):
-        with _lib.early_overlap(True), torch.no_grad():
+        with _lib.early_overlap(self.early_overlap), torch.no_grad():
             return self._prefill(ids, chunk_seqs, collective, compute)
 
     def _prefill(self, ids, chunk_seqs, collective=True, compute=True):
