@@ -135,14 +135,24 @@ def build_model(dev, group_size, seed, n_layer):
 
 
 def trace_shares(run, stream):
-    """One eager pass of ``run`` with a CUDA-event pair around every C-ABI call: {entry point: (calls, total ms)}."""
+    """One eager pass of ``run`` with a CUDA-event pair around every C-ABI call: {entry point: (calls, total ms)}.
+    Eager launches are host-bound (the device would wait for the host between calls, and an event pair would then time the
+    host's launch path, not the kernel), so the stream is first parked on a device-side delay twice as long as the host
+    needs to enqueue the whole pass: the device then finds every launch already queued and the event pairs bracket
+    kernel time only."""
     import torch
     from quamba_b200 import _lib
     sink = []
     with torch.cuda.stream(stream):
         run()
         stream.synchronize()
+        _lib.set_call_trace([])                      # rehearsal with the tracing overhead, to size the delay
+        h0 = time.perf_counter()
+        run()
+        host_ms = (time.perf_counter() - h0) * 1e3
+        stream.synchronize()
         _lib.set_call_trace(sink)
+        torch.cuda._sleep(int(2.0 * host_ms * 2.0e6))   # ~2 x 10^6 cycles per millisecond at the boost clock
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record(stream)
         run()
