@@ -297,7 +297,12 @@ def run_ours(args, rank, local_rank, world):
     if world > 1:
         if args.comm_sms > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_sms))
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL's kernels on a high-priority stream: their CTAs are placed ahead of the pending CTAs of the compute kernels, so
+        # a collective starts as soon as SM slots free up instead of after the kernel that is draining
+        opts = None
+        if not os.environ.get("QB_NCCL_NORMAL_PRIORITY"):
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     pk = peaks()
     if world > 1 or args.model == "8b":
         run_head_parallel(args, rank, local_rank, world, pk)
