@@ -258,6 +258,89 @@ def op_w4a8_decode_b64(dev, gen, ops):
     return _w4a8(dev, gen, ops, 64, 2560, 10624, True, "Mamba2-2.7B in_proj, 64 sequences x one token")
 
 
+def _decode_linear_layer(dev, K, N, seed):
+    from quamba_b200.modules import W4A8B8O8Linear, W4A8B16O16Linear
+    lin = torch.nn.Linear(K, N, bias=False)
+    lin.weight.data = torch.randn(N, K, generator=torch.Generator().manual_seed(seed)) * 0.02
+    lin.w4_group_size = -1
+    return lin
+
+
+def op_decode_in_proj(dev, gen, ops):
+    """Launch 1 of the fused decode step at the 2.7B shape: residual add + RMSNorm + quantise + in_proj (nibble weights) +
+    conv1d update in the epilogue, one token."""
+    from quamba_b200.modules import W4A8B8O8Linear
+    K, N, D, GN = 2560, 10576, 5120, 128
+    import copy
+    n = _sets_for(K * N // 2)
+    first = W4A8B8O8Linear.from_fp16(_decode_linear_layer(dev, K, N, 0), torch.tensor(0.03), torch.tensor(0.05)).to(dev)
+    layers = [first] + [copy.deepcopy(first) for _ in range(n - 1)]       # every set streams its own copy of the weights
+    preps = [l.prepared() for l in layers]
+    x = torch.randn((1, K), device=dev, generator=gen).half()
+    res = torch.randn((1, K), device=dev, generator=gen)
+    nw = torch.ones(K, dtype=torch.float16, device=dev)
+    C = D + 2 * GN
+    convs = []
+    for i in range(n):
+        st = torch.zeros((1, 4, C), dtype=torch.int8, device=dev).transpose(1, 2)
+        convs.append(dict(state=st, weight=_i8((C, 4), dev, gen), bias=None, col0=D, x_dim=D, gn=GN, scale_in=(1e-4, 1e-4, 1e-4),
+                          scale_bias=(0.0, 0.0, 0.0), out_scales=tuple(torch.tensor([0.02], device=dev) for _ in range(3))))
+
+    def mk(i):
+        return lambda: ops.decode_norm_linear(x, res, nw, 1e-5, 0.03, preps[i], layers[i].input_scale, True, True, convs[i])
+    by = K * layers[0].size_n // 2 + K * 10 + layers[0].size_n
+    return dict(workload=f"fused decode launch 1, Mamba2-2.7B: residual + RMSNorm + in_proj {K} -> {layers[0].size_n} (4-bit weights from HBM) + conv1d update, one token",
+                bytes=by, flops=0, nsets=n, make=mk, kernel="decode_norm_linear_kernel<1, 1, 1>", launches=1)
+
+
+def op_decode_out_proj(dev, gen, ops):
+    from quamba_b200.modules import W4A8B16O16Linear
+    K, N = 5120, 2560
+    import copy
+    n = _sets_for(K * N // 2)
+    first = W4A8B16O16Linear.from_fp16(_decode_linear_layer(dev, K, N, 100), torch.tensor(0.03)).to(dev)
+    layers = [first] + [copy.deepcopy(first) for _ in range(n - 1)]
+    preps = [l.prepared() for l in layers]
+    a = _i8((1, K), dev, gen)
+
+    def mk(i):
+        return lambda: ops.decode_linear(a, preps[i], layers[i].input_scale)
+    return dict(workload=f"fused decode launch 4, Mamba2-2.7B: out_proj {K} -> {N} on int8 input (4-bit weights from HBM), one token",
+                bytes=K * N // 2 + K + 2 * N, flops=0, nsets=n, make=mk, kernel="decode_norm_linear_kernel<1, 1, 0>", launches=1)
+
+
+def op_decode_gate_had(dev, gen, ops):
+    D = 5120
+    n = 8
+    ys = [torch.randn((1, D), device=dev, generator=gen).half() for _ in range(n)]
+    zs = [_i8((1, D), dev, gen) for _ in range(n)]
+    w = torch.ones(D, dtype=torch.float16, device=dev)
+
+    def mk(i):
+        return lambda: ops.decode_gate_had_quant(ys[i], zs[i], 0.02, w, 1e-5, D, (1.0 / D ** 0.5) / 0.05)
+    return dict(workload=f"fused decode launch 3, Mamba2-2.7B: gate + RMSNorm + Hadamard (40 x 128) + int8 quantise of one row of {D}",
+                bytes=D * (2 + 1 + 2 + 1), flops=0, nsets=n, make=mk, kernel="decode_gate_had_quant_kernel", launches=1,
+                note="latency-bound: 36 KB of traffic; the figure of merit is the time, not the bandwidth")
+
+
+def op_decode_update(dev, gen, ops):
+    H, P, N = 80, 64, 128
+    n = 8
+    states = [_i8((1, H, P, N), dev, gen) for _ in range(n)]
+    x = _i8((1, H, P), dev, gen)
+    dt = _i8((1, H), dev, gen)
+    Bm, Cm = _i8((1, 1, N), dev, gen), _i8((1, 1, N), dev, gen)
+    A = _i8((H,), dev, gen)
+    one = torch.tensor([0.02], device=dev)
+    bias = torch.zeros((H,), dtype=torch.float16, device=dev)
+
+    def mk(i):
+        return lambda: ops.quant_sscan_update_triton(states[i], x, one, dt[:, :, None].expand(-1, -1, P), one, A[:, None, None].expand(-1, P, N), one,
+                                                     one, Bm, one, Cm, one, None, None, None, None, bias[:, None].expand(-1, P), None, True)
+    return dict(workload=f"fused decode launch 2, Mamba2-2.7B: int8 state update of one token, H{H} P{P} N{N} (one CTA per head)",
+                bytes=2 * H * P * N + H * P * 3 + H + 2 * N, flops=0, nsets=n, make=mk, kernel="sscan_update_small_kernel", launches=1)
+
+
 def op_w8a8(dev, gen, ops):
     M, K, N = 16384, 2560, 10240
     by = M * K + K * N + M * N
@@ -276,7 +359,8 @@ def op_w8a8(dev, gen, ops):
 OPS = {"conv": op_conv, "conv_update": op_conv_update, "hadamard": op_hadamard, "sscan": op_sscan, "ssd": op_ssd,
        "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out,
        "w4a8_in_proj_b1": op_w4a8_in_b1, "w4a8_out_proj_b1": op_w4a8_out_b1, "rmsnorm": op_rmsnorm, "rmsnorm_gated": op_rmsnorm_gated, "w4a8_decode": op_w4a8_decode, "w4a8_decode_pc": op_w4a8_decode_pc, "w4a8_decode_b64": op_w4a8_decode_b64,
-       "w8a8": op_w8a8}
+       "decode_in_proj": op_decode_in_proj, "decode_update": op_decode_update, "decode_gate_had": op_decode_gate_had,
+       "decode_out_proj": op_decode_out_proj, "w8a8": op_w8a8}
 
 
 def i8_peak():

@@ -13,6 +13,7 @@
 // linear.cu), so results agree with the unfused path to the same tolerances.
 #include <algorithm>
 #include "common.cuh"
+#include "tc_common.cuh"
 #include "hadamard_tables.inc"
 
 namespace qb {
@@ -104,7 +105,9 @@ __device__ __forceinline__ void dequant8_group(uint32_t w, __half2 s2, uint32_t&
 }
 
 template <int MB, int S4, int SH>
-__device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][Shape<SH>::NW]) {
+__device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, int n0, int lane, int (&acc)[MB][Shape<SH>::NW],
+                                            const uint8_t* sw = nullptr) {
+  // sw: this warp's kNW weight rows staged in shared memory by a bulk copy (first pass), or null: read them from global
   constexpr int kNW = Shape<SH>::NW, kNB = Shape<SH>::NB;
   int sa[MB];
 #pragma unroll
@@ -127,7 +130,7 @@ __device__ __forceinline__ void dot_columns(const Linear& L, const int8_t* sA, i
       const int c = min(c0 + 32 * b, chunks - 1);
 #pragma unroll
       for (int j = 0; j < kNW; ++j) {
-        w[j][b] = __ldg(wrow[j] + c);
+        w[j][b] = sw != nullptr ? *(reinterpret_cast<const uint4*>(sw + (int64_t)j * ldw) + c) : __ldg(wrow[j] + c);
         if (S4 == 2) sg[j][b] = __ldg(reinterpret_cast<const unsigned short*>(L.s_grp) + (int64_t)min(n0 + j, L.n - 1) * groups + (c >> 2));
       }
     }
@@ -263,11 +266,12 @@ __device__ __forceinline__ void finish(const Linear& L, const ConvEpi& cv, const
 // one, so the call sits ahead of the dependency wait and of the shared-memory prologue: HBM delivers while the prologue
 // computes, and each pass then costs a round trip to L2 instead of one to HBM.
 template <int S4, int SH>
-__device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
+__device__ __forceinline__ void prefetch_first_columns(const Linear& L, bool skip_first) {
   constexpr int kNW = Shape<SH>::NW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row_bytes = S4 ? L.k / 2 : L.k;
-  for (int n0 = (blockIdx.x * kWarps + warp) * kNW; n0 < L.n; n0 += (int)gridDim.x * kWarps * kNW) {
+  const int stride = (int)gridDim.x * kWarps * kNW;
+  for (int n0 = (blockIdx.x * kWarps + warp) * kNW + (skip_first ? stride : 0); n0 < L.n; n0 += stride) {
     for (int j = 0; j < kNW; ++j) {
       if (n0 + j >= L.n) break;
       const uint8_t* rowp = L.w + (int64_t)(n0 + j) * row_bytes;
@@ -279,7 +283,8 @@ __device__ __forceinline__ void prefetch_first_columns(const Linear& L) {
 
 // `pre`: the finishing lane's constants of the first pass, loaded by the caller before the dependency wait.
 template <int MB, int S4, int SH>
-__device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows, FinishPre pre) {
+__device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& cv, const int8_t* sA, int rows, FinishPre pre,
+                                               const uint8_t* sw, uint64_t* wbar, int* status) {
   constexpr int kNW = Shape<SH>::NW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = lane / kNW, j = lane % kNW;
@@ -288,7 +293,9 @@ __device__ __forceinline__ void stream_columns(const Linear& L, const ConvEpi& c
     const bool mine = lane < MB * kNW && i < rows && n0 + j < L.n;
     if (n0 != first && mine) pre = finish_prefetch(L, cv, i, n0 + j);
     int acc[MB][kNW];
-    dot_columns<MB, S4, SH>(L, sA, n0, lane, acc);
+    const bool staged = sw != nullptr && n0 == first;
+    if (staged) tc::mbar_wait(wbar, 0, status, QB_ERR_TIMEOUT);      // the bulk copies of this warp's first rows have landed
+    dot_columns<MB, S4, SH>(L, sA, n0, lane, acc, staged ? sw : nullptr);
     // lanes 0 .. MB * kNW - 1 finish one (row, column) each, so that the conv windows of a warp's columns move in parallel
     if (mine) {
       int v = 0;
@@ -322,18 +329,43 @@ struct NormIn {
   const __half* weight;     // (k)
   int64_t x_stride, res_stride, res_out_stride;
   int res_f32, res_out_f32, early_launch;
+  int stage_w;              // the first pass's weight rows go to shared memory by bulk copies issued before the dependency wait
   float eps, out_scale;
 };
 
 template <int MB, int S4, int SH>
 __global__ void __launch_bounds__(kThreads, 2)
-decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
+decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows, int* status) {
   extern __shared__ __align__(16) uint8_t dsm[];
   __shared__ float red[kWarps];
+  __shared__ __align__(8) uint64_t wbar[kWarps];
   int8_t* sA = reinterpret_cast<int8_t*>(dsm);                 // MB rows of k int8
   const int K = L.k;
   if (nin.early_launch) grid_dependency_launch();
-  prefetch_first_columns<S4, SH>(L);
+  // The weights of this warp's first pass travel HBM -> shared memory as bulk copies that are in flight during the
+  // dependency wait and the norm: the product then reads them at shared-memory latency instead of paying a round trip
+  // to L2 (or HBM) after the activations are ready.  Later passes (wide products) are prefetched into L2 as before.
+  constexpr int kNWs = Shape<SH>::NW;
+  const int64_t row_bytes = S4 ? K / 2 : K;
+  const uint8_t* sw = nullptr;
+  if (nin.stage_w) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* sW = dsm + (((int64_t)MB * K + 15) & ~(int64_t)15);
+    if (threadIdx.x == 0) {
+      for (int w = 0; w < kWarps; ++w) tc::mbar_init(&wbar[w], 1);
+      tc::fence_barrier_init();
+    }
+    __syncthreads();
+    sw = sW + (int64_t)warp * kNWs * row_bytes;
+    const int n0 = (blockIdx.x * kWarps + warp) * kNWs;
+    if (lane == 0 && n0 < L.n) {
+      const int cols = min(kNWs, L.n - n0);
+      tc::mbar_arrive_expect_tx(&wbar[warp], (uint32_t)(cols * row_bytes));
+      for (int j = 0; j < cols; ++j)
+        tc::bulk_load(const_cast<uint8_t*>(sw) + (int64_t)j * row_bytes, L.w + (int64_t)(n0 + j) * row_bytes, (uint32_t)row_bytes, &wbar[warp]);
+    }
+  }
+  prefetch_first_columns<S4, SH>(L, nin.stage_w != 0);
   const FinishPre pre = first_pass_prefetch<MB, SH>(L, cv, rows);
   const int chunks = K / 8;
   uint4 nw[4];               // the norm weights of this thread's chunks: constants, fetched ahead of the wait
@@ -349,7 +381,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
         *(reinterpret_cast<uint4*>(sA + (int64_t)m * K) + c) = __ldcg(reinterpret_cast<const uint4*>(nin.a_int8 + (int64_t)row * nin.x_stride) + c);
     }
     __syncthreads();
-    stream_columns<MB, S4, SH>(L, cv, sA, rows, pre);
+    stream_columns<MB, S4, SH>(L, cv, sA, rows, pre, sw, &wbar[threadIdx.x >> 5], status);
     return;
   }
   const float inv_scale = 1.0f / nin.out_scale;
@@ -418,7 +450,7 @@ decode_norm_linear_kernel(NormIn nin, Linear L, ConvEpi cv, int rows) {
     }
   }
   __syncthreads();
-  stream_columns<MB, S4, SH>(L, cv, sA, rows, pre);
+  stream_columns<MB, S4, SH>(L, cv, sA, rows, pre, sw, &wbar[threadIdx.x >> 5], status);
 }
 
 // ---- launch 3: gate, grouped RMSNorm, Hadamard rotation, quantise -> product -------------------------------------------
@@ -643,12 +675,20 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
     cv.c0 = a->conv_col0; cv.dim = a->conv_dim; cv.end0 = a->conv_x_dim; cv.end1 = a->conv_x_dim + a->conv_gn;
   }
   const int mb = a->rows <= 2 ? a->rows : 4;
-  const size_t smem = (size_t)mb * a->k;
+  size_t smem = (size_t)mb * a->k;
   // five columns per warp in one pass when the columns are short (at most 96 chunks) and two per warp would take more
   // than one pass of the resident warps
   const int chunks = a->w_is_s4 != 0 ? a->k / 32 : a->k / 16;
   const int sh = chunks <= 96 && (int64_t)a->n > (int64_t)sm_count() * 2 * kWarps * 2 ? 1 : 0;
   const dim3 grid(grid_for(a->n, 2, sh ? 5 : 2));
+  // first-pass weights staged in shared memory when two CTAs of the kernel still fit an SM with them
+  const size_t row_bytes = a->w_is_s4 != 0 ? (size_t)a->k / 2 : (size_t)a->k;
+  const size_t stage_bytes = (size_t)kWarps * (sh ? 5 : 2) * row_bytes;
+  const size_t smem_staged = ((smem + 15) & ~(size_t)15) + stage_bytes;
+  nin.stage_w = row_bytes % 16 == 0 && smem_staged <= 100 * 1024 ? 1 : 0;
+  if (nin.stage_w) smem = smem_staged;
+  int* status = device_status_ptr();
+  QB_REQUIRE(status != nullptr, QB_ERR_CUDA, "decode_norm_linear: device status word unavailable");
   cudaStream_t st = (cudaStream_t)stream;
   const int rows = a->rows;
   const int wm = a->w_is_s4 == 0 ? 0 : (a->s_group_nat != nullptr ? 2 : 1);
@@ -656,7 +696,7 @@ extern "C" int qb_decode_norm_linear(const qb_decode_norm_linear_args* a, void* 
     QB_REQUIRE(a->k % 128 == 0 && aligned(a->s_group_nat, 2), QB_ERR_INVALID_ARG, "decode_norm_linear: group scales need k to be a multiple of 128");
     L.s_grp = static_cast<const __half*>(a->s_group_nat);
   }
-  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, wm, sh, grid, smem, st, nin, L, cv, rows);
+  QB_DISPATCH_MB_S4(decode_norm_linear_kernel, mb, wm, sh, grid, smem, st, nin, L, cv, rows, status);
   QB_LAUNCH_OK("decode_norm_linear_kernel");
   return QB_OK;
 }
