@@ -75,15 +75,16 @@ def model_flops_and_bytes(m, L, group_size):
 
 
 # ---- the CPU arm -----------------------------------------------------------------------------------------------------------
-def cpu_sample(layers=1, L=512, vocab=4096):
+def cpu_sample(layers=1, L=512, vocab=4096, model=None, prompt_desc="the 2048 prompt tokens (batch 1)"):
     """oracle/'s dequantise-then-fp32 path on a bounded sample: ``layers`` layers at full width over ``L`` tokens, scaled
-    to 64 layers (every layer has the same shapes), plus the final norm and the head on the last token (vocabulary cut to
-    ``vocab`` rows to keep the set-up short; the head's share of a prefill is far below a percent)."""
+    to all the model's layers (every layer has the same shapes), plus the final norm and the head on the last token
+    (vocabulary cut to ``vocab`` rows to keep the set-up short; the head's share of a prefill is far below a percent)."""
     import torch
     from oracle import model as omodel
     from quamba_b200 import calibrate as cal
     torch.set_num_threads(os.cpu_count() or 1)
-    cfg = dict(MODEL, n_layer=layers, vocab_size=vocab)
+    model = model or MODEL
+    cfg = dict(model, n_layer=layers, vocab_size=vocab)
     fm = cal.Mamba2LMFloat(**cfg, w4_group_size=-1, seed=0, device="cpu")
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, vocab, (1, L), generator=g)
@@ -100,8 +101,8 @@ def cpu_sample(layers=1, L=512, vocab=4096):
     t_rest = time.perf_counter() - t0
     fp.layers = saved
     per_layer = (t_all - t_rest) / layers
-    t_full = per_layer * MODEL["n_layer"] + t_rest
-    sample = (f"{layers} of the 64 layers at full width over {L} of the 2048 prompt tokens (batch 1), time scaled to 64 layers, "
+    t_full = per_layer * model["n_layer"] + t_rest
+    sample = (f"{layers} of the {model['n_layer']} layers at full width over {L} of {prompt_desc}, time scaled to {model['n_layer']} layers, "
               f"vocabulary cut to {vocab}; torch fp32 on dequantised weights")
     return L / t_full, t_full, sample
 
@@ -109,11 +110,18 @@ def cpu_sample(layers=1, L=512, vocab=4096):
 def run_reference(args, rank):
     if rank != 0:
         return
-    tok_s, t_full, sample = cpu_sample()
+    workload = WORKLOAD
+    if args.gpus >= 2 or args.model == "8b":      # the GPU arm then runs the head-parallel Mamba2-8B prefill: same workload here
+        import bench_parallel as bp
+        tok_s, t_full, sample = cpu_sample(model=bp.CFG8B, prompt_desc="the 32 x 4096 prompt tokens")
+        workload = bp.WORKLOAD8B
+    else:
+        tok_s, t_full, sample = cpu_sample()
     cores = os.cpu_count() or 1
     line = {"impl": "reference", "metric": "prefill_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": 1,
-            "warmup": 1, "ms_per_step": t_full * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+            "warmup": 1, "ms_per_step": t_full * 1e3, "higher_is_better": True, "scaling": "weak" if workload == WORKLOAD else "strong",
+            "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": workload, "sample": sample},
             "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
