@@ -9,8 +9,22 @@ from . import conv1d as oconv, hadamard as ohad, linear as olin, norm as onorm, 
 
 
 def _w4a8(lin, a_int8, out_int8):
-    sg = lin.s_group if lin.s_group.numel() else None
-    out = olin.w4a8_gemm(a_int8, lin.weight, lin.input_scale.reshape(1), lin.s_channel, sg, lin.size_n, lin.size_k, out_int8)
+    """The product of a quantized linear layer, read off its buffers: W4A8 (Marlin-QQQ packed weight, qLinearLayer.py:227-273,
+    :370-414) or W8A8 (int8 weight with ``a`` / ``b`` scales; one row goes through the reference's GEMV forms,
+    qLinearLayer.py:607-647, :725-742, :805-820)."""
+    if hasattr(lin, "s_channel"):
+        sg = lin.s_group if lin.s_group.numel() else None
+        out = olin.w4a8_gemm(a_int8, lin.weight, lin.input_scale.reshape(1), lin.s_channel, sg, lin.size_n, lin.size_k, out_int8)
+        return out[:, :lin.out_features]
+    w_kn = lin.weight                                   # (K, N_pad) view of a row-major (N_pad, K) matrix
+    out_dtype = torch.int8 if out_int8 else torch.float16
+    if a_int8.shape[0] == 1:
+        if lin.b.numel() > 1:                           # W8A8B8O8LinearParallel._matvec
+            out = olin.w8a8o8_gemv(w_kn.t(), a_int8, lin.b, lin.a)
+        else:                                           # cutlass_scaled_mv_dq with the folded alpha
+            out = olin.w8a8_gemv_alpha(w_kn.t(), a_int8, lin.alpha, out_dtype)
+    else:
+        out = olin.w8a8_gemm(a_int8, w_kn, lin.a, lin.b, out_dtype)
     return out[:, :lin.out_features]
 
 

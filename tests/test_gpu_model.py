@@ -131,12 +131,12 @@ def test_greedy_next_token():
 
 
 # ---- layer and model --------------------------------------------------------------------------------------------------
-def _small(seed, group, d_model=256, n_layer=2, vocab=320, L=300, batch=2):
+def _small(seed, group, d_model=256, n_layer=2, vocab=320, L=300, batch=2, w_bits=4):
     from quamba_b200 import calibrate as cal
     m = cal.Mamba2LMFloat(d_model=d_model, n_layer=n_layer, vocab_size=vocab, seed=seed, w4_group_size=group)
     g = torch.Generator().manual_seed(seed)
     ids = torch.randint(0, vocab, (batch, L), generator=g)
-    q = cal.quantize_model(m, cal.calibrate(m, [ids]))
+    q = cal.quantize_model(m, cal.calibrate(m, [ids]), w_bits=w_bits)
     return q, ids
 
 
@@ -273,6 +273,35 @@ def test_graph_replayed_prefill_equals_the_eager_prefill_bit_for_bit(group):
             assert torch.equal(got_states[k][0], v[0]) and torch.equal(got_states[k][1], v[1]), f"replay {rep}: layer {k} caches differ"
     import quamba_b200
     quamba_b200.check_device_status()
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_w8a8_model_prefill_and_graph_decode_match_oracle(batch):
+    """The reference's default layer class, W8A8QMamba2 (W8 embedding, W8A8 head): prefill logits and three graph-replayed
+    decode steps against the CPU oracle.  Batch 1 takes the single-row GEMV forms of the W8A8 linears, batch 2 the GEMM."""
+    import copy
+    from quamba_b200 import _lib
+    from quamba_b200.mixer import W8A8QMamba2
+    q, ids = _small(31 + batch, None, n_layer=2, L=150, batch=batch, w_bits=8)
+    assert isinstance(q.backbone.layers[0].mixer, W8A8QMamba2)
+    want = omodel.model_forward(q, ids, num_last_tokens=1)[:, -1]
+    gq = copy.deepcopy(q).to(DEV)
+    runner = gq.capture_prefill(batch, 150)
+    runner.input_ids.copy_(ids)
+    got = runner.replay()
+    torch.cuda.synchronize()
+    _close(got, want, "W8A8 prefill logits", atol_rel=3e-2, max_frac=0.02)
+    params = runner.inference_params
+    params.seqlen_offset = 150
+    dec = gq.capture_decode(batch, 200, inference_params=params)
+    tok = ops().greedy_next_token(got.contiguous())
+    for _ in range(3):
+        cpu_states = {k: tuple(t.cpu().clone() for t in v) for k, v in params.key_value_memory_dict.items()}
+        dec.input_ids.copy_(tok[:, None])
+        logits = dec.replay().clone()
+        _close(logits, omodel.model_step(q, tok.cpu(), cpu_states), "W8A8 decode logits", atol_rel=3e-2, max_frac=0.02)
+        tok = dec.input_ids[:, 0].clone()
+    _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
 
 
 def test_generate_greedy_graph_equals_eager():
