@@ -174,7 +174,7 @@ def trace_shares(run, stream):
     return agg, t0.elapsed_time(t1)
 
 
-def measure(model, args, dev, rank, world, group_size):
+def measure(model, args, dev, rank, world, group_size, batch=1, vocab=None):
     import torch
     import torch.distributed as dist
     from quamba_b200 import _lib, ops
@@ -188,9 +188,9 @@ def measure(model, args, dev, rank, world, group_size):
         torch.cuda.synchronize()
 
     g = torch.Generator().manual_seed(1234 + rank)
-    host_ids = [torch.randint(0, MODEL["vocab_size"], (1, L), generator=g).pin_memory() for _ in range(3)]
+    host_ids = [torch.randint(0, vocab or MODEL["vocab_size"], (batch, L), generator=g).pin_memory() for _ in range(3)]
     dev_ids = [t.to(dev) for t in host_ids]
-    pre = model.capture_prefill(1, L)
+    pre = model.capture_prefill(batch, L)
     st = pre.stream
     with torch.cuda.stream(st):
         for i in range(warmup):
@@ -215,7 +215,7 @@ def measure(model, args, dev, rank, world, group_size):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end: pinned host token ids -> device -> prefill -> last-token logits in pinned host memory ----
-    host_logits = torch.empty((1, model.lm_head.out_features), dtype=torch.float16).pin_memory()
+    host_logits = torch.empty((batch, model.lm_head.out_features), dtype=torch.float16).pin_memory()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     with torch.cuda.stream(st):
@@ -231,7 +231,7 @@ def measure(model, args, dev, rank, world, group_size):
     # ---- decode: 256 greedy tokens from the prefill's caches, one CUDA graph per step ----
     params = pre.inference_params
     params.seqlen_offset = L
-    dec = model.capture_decode(1, L + ntok, inference_params=params)
+    dec = model.capture_decode(batch, L + ntok, inference_params=params)
     with torch.cuda.stream(st):
         dec.stream.wait_stream(st)
     with torch.cuda.stream(dec.stream):
@@ -251,7 +251,7 @@ def measure(model, args, dev, rank, world, group_size):
     _lib.read_device_status(dec.stream.cuda_stream)
 
     # ---- per entry point: CUDA events around every call of one eager prefill and one eager decode step ----
-    pparams = type(params)(max_seqlen=L + 1, max_batch_size=1, key_value_memory_dict=params.key_value_memory_dict)
+    pparams = type(params)(max_seqlen=L + 1, max_batch_size=batch, key_value_memory_dict=params.key_value_memory_dict)
     shares_p, eager_ms = trace_shares(lambda: model(dev_ids[0], inference_params=pparams, num_last_tokens=1), st)
     params.seqlen_offset = L
     tok = dec.input_ids.clone()
@@ -296,6 +296,49 @@ def run_head_parallel(args, rank, local_rank, world, pk):
     print(json.dumps(line), flush=True)
 
 
+MAMBA1 = dict(d_model=2560, n_layer=64, vocab_size=50280, d_state=16, d_conv=4, expand=2)
+WORKLOAD_MAMBA1 = ("configs[3]: Quamba Mamba1-2.8B W8A8 (d_model 2560, 64 layers, d_inner 5120, d_state 16, dt_rank 160, d_conv 4, "
+                   "vocab 50280), batch 16, prefill 1024 token ids, then 128 greedy decode tokens")
+
+
+def run_mamba1(args, dev, pk):
+    """``--model mamba1``: the Mamba1-2.8B W8A8 model (int8 selective scan, Quamba1 conv1d, W8A8 linears, Hadamard), batch 16."""
+    import torch
+    from quamba_b200 import calibrate as cal
+    layers = args.layers if args.layers != MODEL["n_layer"] else MAMBA1["n_layer"]
+    fm = cal.Mamba1LMFloat(**dict(MAMBA1, n_layer=layers), seed=0, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    calib = [torch.randint(0, MAMBA1["vocab_size"], (1, 128), generator=g, device=dev) for _ in range(CALIB_SEQS)]
+    model = cal.quantize_mamba1_model(fm, calib, w_bits=8)
+    del fm
+    torch.cuda.empty_cache()
+    args.seqlen = 1024 if args.seqlen == PROMPT else args.seqlen
+    args.decode_tokens = 128 if args.decode_tokens == DECODE_TOKENS else args.decode_tokens
+    batch = 16
+    r = measure(model, args, dev, 0, 1, -1, batch=batch, vocab=MAMBA1["vocab_size"])
+    tokens = batch * r["L"]
+    D, N, R_, d = MAMBA1["d_model"] * 2, MAMBA1["d_state"], 160, MAMBA1["d_model"]
+    gemm_flops = layers * 2 * tokens * (d * 2 * D + D * (R_ + 2 * N) + R_ * D + D * d)
+    scan_bytes = layers * (batch * D * r["L"] * 5 + 2 * batch * N * r["L"] + batch * D * N + D * (N + 2))
+    sp = shares_table(r["shares_p"])
+    line = {
+        "metric": "prefill_tok_per_s", "value": tokens / (r["ms_prefill"] * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": r["ms_prefill"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 (int8 weights and activations, int32 accumulate; fp32 scan math)", "data": "synthetic",
+        "config": {"workload": WORKLOAD_MAMBA1 if layers == MAMBA1["n_layer"] else f"REDUCED to {layers} layers: " + WORKLOAD_MAMBA1,
+                   "l2": "every step streams all layers' int8 weights and 16 x 1024 tokens of activations: far beyond the 126 MB L2",
+                   "graphs": "prefill and decode step replayed from CUDA graphs"},
+        "decode": {"tpot_ms": r["tpot_ms"], "tokens": r["ntok"], "batch": batch, "tok_per_s": batch * 1e3 / r["tpot_ms"]},
+        "e2e": {"value": tokens / (r["ms_e2e"] * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+        "gpu_launches": args.steps * sum(v["calls"] for v in sp.values()),
+        "roofline": {"shares_prefill": sp, "shares_decode_step": shares_table(r["shares_d"]),
+                     "gemm_flops_per_step": gemm_flops, "gemm_tensor_bound_ms": gemm_flops / (pk["i8"] * 1e12) * 1e3,
+                     "scan_algorithmic_bytes_per_step": scan_bytes, "scan_hbm_bound_ms": scan_bytes / (pk["hbm"] * 1e9) * 1e3},
+        "eager_prefill_ms": r["eager_ms"], "clocks": r["clocks"],
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
@@ -312,6 +355,9 @@ def run_ours(args, rank, local_rank, world):
             opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     pk = peaks()
+    if world == 1 and args.model == "mamba1":
+        run_mamba1(args, dev, pk)
+        return
     if world > 1 or args.model == "8b":
         run_head_parallel(args, rank, local_rank, world, pk)
         if world > 1:
@@ -398,7 +444,8 @@ def main():
     ap.add_argument("--group-size", type=int, default=-1, choices=[-1, 128], help="int4 weight format: per output channel or group 128")
     ap.add_argument("--also-group128", action="store_true", help="measure the group-128 weight format too (second model build)")
     ap.add_argument("--layers", type=int, default=MODEL["n_layer"], help="fewer layers = a reduced profiling case, flagged in config")
-    ap.add_argument("--model", default="2.7b", choices=["2.7b", "8b"], help="8b: the head-parallel Mamba2-8B prefill (always used for --gpus >= 2)")
+    ap.add_argument("--model", default="2.7b", choices=["2.7b", "8b", "mamba1"],
+                    help="8b: the head-parallel Mamba2-8B prefill (always used for --gpus >= 2); mamba1: the Mamba1-2.8B W8A8 model, batch 16")
     ap.add_argument("--no-8b-base", action="store_true", help="skip the single-GPU Mamba2-8B measurement added to the 2.7B line")
     ap.add_argument("--comm-sms", type=int, default=16, help="--gpus >= 2: multiprocessors left to NCCL (compute grids use the rest); 0 = no split")
     ap.add_argument("--plain-allreduce", action="store_true", help="--gpus >= 2: one fp16 all-reduce per layer and a replicated block norm "

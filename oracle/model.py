@@ -6,6 +6,7 @@ oracle's ops in the order of W4A8QMamba2.forward / .step (quamba/qMamba2.py:920-
 import torch
 
 from . import conv1d as oconv, hadamard as ohad, linear as olin, norm as onorm, ssd as ossd, update as oupd, embedding as oemb
+from . import sscan as osscan
 
 
 def _w4a8(lin, a_int8, out_int8):
@@ -86,6 +87,56 @@ def mixer_step(m, u_int8, conv_state, ssm_state):
     return _gate_rotate_project(m, y.reshape(b, -1), z.contiguous())
 
 
+# ---- Mamba1 mixers (W8A8QMamba / W4A8QMamba, quamba/qMambaLayer.py:512-1003) ----------------------------------------------
+def _mamba1_rotate_project(m, y16):
+    if hasattr(m.had, "x_H_scale"):
+        q, _ = ohad.quant_hadamard(y16.reshape(-1, y16.shape[-1]), m.had.had_scale / m.had.x_H_scale)
+    else:                                                # QAct: clamp(x / scale), cast truncates (qActLayer.py:24)
+        q = (y16.reshape(-1, y16.shape[-1]) / m.had.scale).clamp(min=-128, max=127).to(torch.int8)
+    return _w4a8(m.out_proj, q, False)
+
+
+def mamba1_forward(m, u_int8, want_states=False):
+    """u_int8 (b, l, d_model) -> fp16 (b, l, d_model) [, conv_state (b, d_inner, d_conv) int8, ssm_state (b, d_inner, N) int8]
+    in the order of W8A8QMamba.forward (qMambaLayer.py:903-940)."""
+    b, l, _ = u_int8.shape
+    R, N, D = m.dt_rank, m.d_state, m.d_inner
+    xz = _w4a8(m.in_proj, u_int8.reshape(b * l, -1), True).reshape(b, l, 2 * D).transpose(1, 2)       # (b, 2D, l)
+    x, z = xz[:, :D], xz[:, D:]
+    c = m.conv1d
+    conv_state = torch.nn.functional.pad(x, (m.d_conv - l, 0)).contiguous()
+    x = oconv.quant_causal_conv1d_fwd(x, c.input_scale, c.weight, c.weight_scale, c.output_scale, c.bias_scale, c.bias, True)
+    x_dbl = _w4a8(m.x_proj, x.transpose(1, 2).reshape(b * l, D), True)
+    dt, Bq, Cq = torch.split(x_dbl, [R, N, N], dim=-1)
+    dt = _w4a8(m.dt_proj, dt.contiguous(), True).reshape(b, l, D).transpose(1, 2)
+    Bq = Bq.reshape(b, l, N).transpose(1, 2)[:, None]                                                 # (b, 1, N, l)
+    Cq = Cq.reshape(b, l, N).transpose(1, 2)[:, None]
+    sc = m.selective_scan
+    y, xs, _ = osscan.quant_sscan_fwd(x, sc.u_scale, dt, sc.dt_scale, sc.A_log, sc.A_scale, Bq, sc.B_scale, Cq, sc.C_scale,
+                                      sc.ssm_state_scale, sc.D, sc.D_scale, z, sc.z_scale, sc.dt_bias, sc.dt_bias_scale,
+                                      sc.delta_softplus)
+    out = _mamba1_rotate_project(m, y.reshape(b * l, D)).reshape(b, l, -1)
+    return (out, conv_state, xs[:, :, -1, :].contiguous()) if want_states else out
+
+
+def mamba1_step(m, u_int8, conv_state, ssm_state):
+    """One decode token: u_int8 (b, d_model); conv_state (b, d_inner, d_conv) and ssm_state (b, d_inner, N) int8 are updated
+    in place (qMambaLayer.py:942-962).  Returns fp16 (b, d_model)."""
+    R, N, D = m.dt_rank, m.d_state, m.d_inner
+    xz = _w4a8(m.in_proj, u_int8, True)
+    x, z = xz[:, :D], xz[:, D:]
+    c = m.conv1d
+    x = oconv.quant_causal_conv1d_update(x, conv_state, c.input_scale, c.weight, c.weight_scale, c.output_scale, c.bias_scale, c.bias, True)
+    x_dbl = _w4a8(m.x_proj, x, True)
+    dt, Bq, Cq = torch.split(x_dbl, [R, N, N], dim=-1)
+    dt = _w4a8(m.dt_proj, dt.contiguous(), True)
+    sc = m.selective_scan
+    y, _ = oupd.quant_sscan_update(ssm_state, x, sc.u_scale, dt, sc.dt_scale, sc.A_log, sc.A_scale, sc.ssm_state_scale, Bq.contiguous(),
+                                   sc.B_scale, Cq.contiguous(), sc.C_scale, sc.D, sc.D_scale, z, sc.z_scale, sc.dt_bias,
+                                   sc.dt_bias_scale, sc.delta_softplus)
+    return _mamba1_rotate_project(m, y)
+
+
 def _embed(e, ids):
     if e.weight.dtype == torch.int32:
         return oemb.lookup_w4(ids, e.weight.data, e.scales)
@@ -105,10 +156,11 @@ def model_forward(model, input_ids, num_last_tokens=0, states=None):
         nq = layer.norm
         q, residual, _ = onorm.qlayer_norm_fwd(h.reshape(b * l, d), nq.weight, None, nq.eps, residual,
                                                static_out_scale=nq.output_scale, residual_dtype=torch.float32)
+        fwd = mamba1_forward if hasattr(layer.mixer, "selective_scan") else mixer_forward
         if states is None:
-            h = mixer_forward(layer.mixer, q.reshape(b, l, d))
+            h = fwd(layer.mixer, q.reshape(b, l, d))
         else:
-            h, cs, ss = mixer_forward(layer.mixer, q.reshape(b, l, d), True)
+            h, cs, ss = fwd(layer.mixer, q.reshape(b, l, d), True)
             states[i] = (cs, ss)
     h, residual = h.reshape(b, l, d), residual.reshape(b, l, d)
     if num_last_tokens > 0:
@@ -128,7 +180,7 @@ def model_step(model, token_ids, states):
         nq = layer.norm
         q, residual, _ = onorm.qlayer_norm_fwd(h, nq.weight, None, nq.eps, residual, static_out_scale=nq.output_scale,
                                                residual_dtype=torch.float32)
-        h = mixer_step(layer.mixer, q, *states[i])
+        h = (mamba1_step if hasattr(layer.mixer, "selective_scan") else mixer_step)(layer.mixer, q, *states[i])
     q, _, _ = onorm.qlayer_norm_fwd(h, bb.norm_f.weight, None, bb.norm_f.eps, residual, static_out_scale=bb.norm_f.output_scale,
                                     residual_dtype=torch.float32)
     return _w4a8(model.lm_head, q, False)

@@ -7,7 +7,7 @@ reference's own extension-level and module-level interfaces:
     from quamba_b200 import QSScan, Quamba2ChunkScan, QCausalConv1D, Quamb2Conv1D, QHadamard, \
         W4A8B16O16Linear, W4A8B8O8Linear, W4A8B8O8LinearParallel, W8A8B8O8Linear, \
         W8A8B8O8LinearParallel, W8A8B16O16Linear, QRMSNorm, QRMSNormGated, W4O16Embedding, W8O16Embedding, \
-        W4A8QMamba2, W8A8QMamba2, QuambaLMHeadModel
+        W4A8QMamba2, W8A8QMamba2, W4A8QMamba, W8A8QMamba, QuambaLMHeadModel
 
 Importing the package does not touch the GPU; the shared library is loaded on first use and
 its absence is an error (there is no CPU or PyTorch fallback).
@@ -21,6 +21,7 @@ from .packing import w4a8_quantize  # noqa: F401
 from .norm import QRMSNorm, QRMSNormGated  # noqa: F401
 from .embedding import W4O16Embedding, W8O16Embedding  # noqa: F401
 from .mixer import W4A8QMamba2, W8A8QMamba2  # noqa: F401
+from .mixer1 import QAct, W4A8QMamba, W8A8QMamba  # noqa: F401
 from .model import InferenceParams, QuambaConfig, QuambaLMHeadModel, QuambaMixerModel  # noqa: F401
 
 

@@ -441,7 +441,7 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
                             const Epilogue& ep, cudaStream_t st) {
   // TMA rules: 16-byte aligned bases and pitches; the inner extent must cover whole 16-byte units.
   if (K % 16 != 0 || lda % 16 != 0 || ldw % 16 != 0 || !aligned(A, 16) || !aligned(W, 16)) return QB_ERR_UNSUPPORTED;
-  if (M < 32) return QB_ERR_UNSUPPORTED;  // tiny M is weight-streaming work for the portable kernel
+  if (M < 9) return QB_ERR_UNSUPPORTED;   // a few rows are weight-streaming work for the dp4a kernel
   CUtensorMap ta, tw;
   int rc = encode_tmap_2d_u8(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
   if (rc != QB_OK) return rc;

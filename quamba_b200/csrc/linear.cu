@@ -334,7 +334,8 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
 
 int run_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int M, int N, int K, const Epilogue& ep,
              cudaStream_t st) {
-  if (M < 32) {  // decode-sized problems stream the weights once; the 128-row MMA tile would be mostly padding
+  if (M <= 8) {  // a few rows stream the weights once through dp4a; from nine rows on the tensor-core kernel with
+                 // 64-column tiles and a TMA box of only the rows that exist is faster (batch-16 decode: 30 us -> see bench)
     const int rc = launch_gemv(A, lda, W, ldw, M, N, K, ep, st);
     if (rc != QB_ERR_UNSUPPORTED) return rc;
   }

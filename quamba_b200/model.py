@@ -18,6 +18,7 @@ import torch.nn as nn
 
 from . import embedding as _emb
 from . import mixer as _mixer
+from . import mixer1 as _mixer1
 from . import modules as _modules
 from . import _lib
 from . import ops
@@ -70,7 +71,8 @@ class InferenceParams:
             self.lengths_per_sample.zero_()
 
 
-_MIXERS = {"W4A8QMamba2": _mixer.W4A8QMamba2, "W8A8QMamba2": _mixer.W8A8QMamba2}
+_MIXERS = {"W4A8QMamba2": _mixer.W4A8QMamba2, "W8A8QMamba2": _mixer.W8A8QMamba2,
+           "W4A8QMamba": _mixer1.W4A8QMamba, "W8A8QMamba": _mixer1.W8A8QMamba}
 _EMBEDDINGS = {"Embedding": _emb.F16Embedding, "W4O16Embedding": _emb.W4O16Embedding, "W8O16Embedding": _emb.W8O16Embedding}
 _LM_HEADS = {"W4A8B16O16Linear": _modules.W4A8B16O16Linear, "W8A8B16O16Linear": _modules.W8A8B16O16Linear}
 
