@@ -602,8 +602,9 @@ def _w4a8(a, prep, s_tok, size_m, size_n, size_k, output_transpose, out_int8):
     common = dict(s_tok=_p(s_tok), out=_p(out), a_row_stride=a.stride(0), out_row_stride=out.stride(0), m=size_m, n=size_n,
                   k=size_k, s_tok_per_row=int(s_tok.numel() != 1), out_int8=int(out_int8),
                   output_transpose=int(bool(output_transpose)))
-    if (0 < size_m < 32 and prep.per_channel and size_k % 32 == 0 and a.stride(0) % 16 == 0 and a.data_ptr() % 16 == 0):
-        # decode-sized call on per-channel weights: stream the nibble copy (half the bytes, identical results)
+    if (0 < size_m <= 8 and prep.per_channel and size_k % 32 == 0 and a.stride(0) % 16 == 0 and a.data_ptr() % 16 == 0):
+        # a few rows on per-channel weights: stream the nibble copy (half the bytes, identical results); from nine rows on
+        # the tensor-core kernel on the int8 copy is faster than re-streaming the weights for every eight rows
         w4 = prep.need_w4()
         args = _lib.make("qb_w4a8_gemv_s4_args", a=_p(a), w4=_p(w4), s_channel_nat=_p(prep.sc), **common)
         _run("qb_w4a8_gemv_s4", args, a)

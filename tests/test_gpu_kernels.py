@@ -310,7 +310,7 @@ def test_ssd_tensor_core_path_equals_portable_path_on_device():
 
 # ---- linears ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("tag", ["g128", "g128_pad", "perchannel"])
-@pytest.mark.parametrize("M", [1, 5, 89, 256])
+@pytest.mark.parametrize("M", [1, 5, 16, 89, 256])
 def test_w4a8_gemm_with_reference_packed_weights(tag, M):
     g = load_golden(f"linear_w4a8_{tag}.npz")
     K = g["w"].shape[0]
