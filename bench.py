@@ -450,6 +450,7 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=16, help="--gpus >= 2: multiprocessors left to NCCL (compute grids use the rest); 0 = no split")
     ap.add_argument("--plain-allreduce", action="store_true", help="--gpus >= 2: one fp16 all-reduce per layer and a replicated block norm "
                     "instead of reduce-scatter + token-sharded norm + int8 all-gather")
+    ap.add_argument("--chunk-seqs", type=int, default=0, help="head-parallel prefill: sequences per chunk (0: 8 on several GPUs, 4 on one)")
     ap.add_argument("--seqlen", type=int, default=PROMPT)
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
     args = ap.parse_args()

@@ -90,7 +90,7 @@ def run(args, rank, local_rank, world, layers=None):
     build_s = time.time() - t0
     g = torch.Generator().manual_seed(99)
     ids = [torch.randint(0, cfg["vocab_size"], (BATCH, PROMPT), generator=g).to(dev) for _ in range(2)]
-    chunk_seqs = 8 if world > 1 else 4
+    chunk_seqs = getattr(args, "chunk_seqs", 0) or (8 if world > 1 else 4)
 
     def barrier():
         if world > 1:
