@@ -77,7 +77,10 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], int m, int 
 // tiles put a CTA on every SM -- 83 CTAs of 128 columns cannot pull the weights of the 2.7B in_proj at HBM speed.
 // a_rows: rows of A that exist (the TMA box of A; the MMA still multiplies 128 rows, the rest of the tile is whatever
 // shared memory held, and those output rows are masked in the epilogue).
-template <int kBN>
+// kARows: rows of A a stage has room for (a multiple of 8; the MMA's 128-row read then runs on into the stages behind it, whose
+// contents only reach masked output rows), kSt: stages.  Few rows of A leave room for a deeper ring: a decode batch of 16
+// streams its weights through eight 12 KB stages instead of three 24 KB ones.
+template <int kBN, int kARows = BM, int kSt = kStages>
 __global__ void __launch_bounds__(kThreads)
 gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                        int M, int N, int K, int a_rows, Epilogue ep, int* status, int early) {
@@ -87,19 +90,21 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   constexpr int kWBytes = kBN * BK;
-  uint8_t* sW = smem + kStages * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (kTileBytes + kWBytes));
+  constexpr int kABytes = kARows * BK;
+  static_assert(kARows % 8 == 0 && (BM - kARows) * BK <= kSt * kWBytes, "the 128-row read of the last stage must stay inside the ring");
+  uint8_t* sW = smem + kSt * kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSt * (kABytes + kWBytes));
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + kStages;
-  uint64_t* accum_bar = bars + 2 * kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+  uint64_t* empty_bar = bars + kSt;
+  uint64_t* accum_bar = bars + 2 * kSt;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kSt + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * kBN;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < kSt; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(accum_bar, 1);
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
@@ -120,11 +125,11 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   if (warp == 0) {
     if (lane == 0) {
       for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t ph = (kb / kStages) & 1;
+        const int s = kb % kSt;
+        const uint32_t ph = (kb / kSt) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, status, QB_ERR_TIMEOUT)) break;
         mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(a_rows * BK + kWBytes));
-        tma_load_2d(sA + s * kTileBytes, &tmap_a, &full_bar[s], kb * BK, m0);
+        tma_load_2d(sA + s * kABytes, &tmap_a, &full_bar[s], kb * BK, m0);
         tma_load_2d(sW + s * kWBytes, &tmap_w, &full_bar[s], kb * BK, n0);
       }
     }
@@ -137,12 +142,12 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       const SmemDesc dw0 = make_smem_desc2(smem_u32(sW), 16, 1024, kSwizzle128B);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t ph = (kb / kStages) & 1;
+        const int s = kb % kSt;
+        const uint32_t ph = (kb / kSt) & 1;
         ok = mbar_wait(&full_bar[s], ph, status, QB_ERR_TIMEOUT);
         if (!ok) break;
         tc_fence_after_sync();
-        const SmemDesc da = desc_advance(da0, (uint32_t)s * kTileBytes);
+        const SmemDesc da = desc_advance(da0, (uint32_t)s * kABytes);
         const SmemDesc dw = desc_advance(dw0, (uint32_t)s * kWBytes);
 #pragma unroll
         for (int k = 0; k < BK / 32; ++k)
@@ -488,14 +493,22 @@ int launch_tensor_core_gemm(const int8_t* A, int64_t lda, const int8_t* W, int64
   }
   rc = encode_tmap_2d_u8(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, bn, BK);
   if (rc != QB_OK) return rc;
+  constexpr int kSmem32 = 8 * (32 * BK + 64 * BK) + 1024 + 256;     // <64, 32 rows, 8 stages>
+  constexpr int kSmem64 = 6 * (64 * BK + 64 * BK) + 1024 + 256;     // <64, 64 rows, 6 stages>
   if (dev >= 64 || !attr_set[dev]) {
     QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel<64, 32, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem32));
+    QB_CUDA_OK(cudaFuncSetAttribute(gemm_s8_tcgen05_kernel<64, 64, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem64));
     if (dev < 64) attr_set[dev] = true;
   }
   dim3 grid((unsigned)ceil_div(M, BM), (unsigned)ceil_div(N, bn));
   const int early = early_overlap() ? 1 : 0;
-  if (bn == 64) launch_dependent(gemm_s8_tcgen05_kernel<64>, grid, dim3(kThreads), (size_t)kSmemBytes, st, ta, tw, M, N, K, a_rows, ep, status, early);
+  if (bn == 64 && a_rows <= 32)
+    launch_dependent(gemm_s8_tcgen05_kernel<64, 32, 8>, grid, dim3(kThreads), (size_t)kSmem32, st, ta, tw, M, N, K, a_rows, ep, status, early);
+  else if (bn == 64 && a_rows <= 64)
+    launch_dependent(gemm_s8_tcgen05_kernel<64, 64, 6>, grid, dim3(kThreads), (size_t)kSmem64, st, ta, tw, M, N, K, a_rows, ep, status, early);
+  else if (bn == 64) launch_dependent(gemm_s8_tcgen05_kernel<64>, grid, dim3(kThreads), (size_t)kSmemBytes, st, ta, tw, M, N, K, a_rows, ep, status, early);
   else launch_dependent(gemm_s8_tcgen05_kernel<128>, grid, dim3(kThreads), (size_t)kSmemBytes, st, ta, tw, M, N, K, a_rows, ep, status, early);
   QB_LAUNCH_OK("gemm_s8_tcgen05_kernel");
   return QB_OK;
