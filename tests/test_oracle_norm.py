@@ -7,6 +7,7 @@ import torch
 
 from helpers import load_golden
 from oracle import embedding as oemb, model as omodel, norm as onorm
+from quamba_b200 import calibrate as cal
 
 STATIC = ["static_res32", "static_res16", "static_nores"]
 
@@ -114,3 +115,50 @@ def test_oracle_decode_step_continues_the_prefill():
     full = omodel.model_forward(q, ids)[:, -1]
     # the step starts from int8-rounded states, the prefill carries them in floating point
     assert (step.float() - full.float()).abs().max().item() < 0.05 * full.float().abs().max().item()
+
+
+# ---- Mamba1 mixers and the W8A8 Mamba2 model on CPU ------------------------------------------------------------------------
+@pytest.mark.parametrize("cls_name,tol", [("W8A8QMamba", 0.08), ("W4A8QMamba", 0.35)])
+def test_mamba1_mixer_quantises_on_cpu_and_the_oracle_tracks_the_float_layer(cls_name, tol):
+    """Float Mamba1 layer -> calibration -> W8A8QMamba / W4A8QMamba (buffers built on CPU) -> the oracle's composition of
+    the Quamba1 ops stays within a quantisation-sized error of the float layer (4-bit weights of a 256-wide random layer
+    are coarse: the bound reflects that), and a decode step from the prefill's caches equals the next token of a longer
+    prefill up to +-1 LSB effects."""
+    from quamba_b200 import mixer1
+    g = torch.Generator().manual_seed(0)
+    fl = cal.Mamba1Float(256, layer_idx=0, generator=g, w4_group_size=128)
+    u = torch.randn(2, 33, 256, generator=g)
+    s = cal.calibrate_mamba1(fl, [u])
+    assert set(s) == {"in_proj:input", "in_proj:output", "x_proj:input", "x_proj:output", "dt_proj:output", "ssm_state_act:input",
+                      "out_proj:input"}
+    q = getattr(mixer1, cls_name).from_fp16(fl, s)
+    u8 = (u / s["in_proj:input"]).round().clamp(-128, 127).to(torch.int8)
+    with torch.no_grad():
+        ref = fl(u)
+    out, conv, ssm = omodel.mamba1_forward(q, u8, want_states=True)
+    assert out.dtype == torch.float16 and conv.shape == (2, 512, 4) and ssm.shape == (2, 512, 16) and ssm.dtype == torch.int8
+    err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+    assert err < tol, f"oracle vs float layer: {err:.3f} of the largest output"
+    head, conv_h, ssm_h = omodel.mamba1_forward(q, u8[:, :-1], want_states=True)
+    step = omodel.mamba1_step(q, u8[:, -1], conv_h, ssm_h)      # moves both caches on in place
+    assert torch.equal(conv_h, conv)
+    assert (ssm_h.int() - ssm.int()).abs().max().item() <= 1
+    d = (step.float() - out[:, -1].float()).abs().max().item() / out.float().abs().max().item()
+    assert d < 0.05, f"decode step vs last prefill token: {d:.3f}"
+
+
+def test_w8a8_mamba2_model_oracle_on_cpu():
+    """quantize_model(w_bits=8) builds the reference's default layer class on CPU; the model oracle reads its W8A8 layers
+    (GEMM form for several rows, the two GEMV forms for one) and tracks the float model."""
+    from quamba_b200.mixer import W8A8QMamba2
+    m = cal.Mamba2LMFloat(d_model=256, n_layer=2, vocab_size=320, seed=3)
+    ids = torch.randint(0, 320, (1, 40), generator=torch.Generator().manual_seed(0))
+    q = cal.quantize_model(m, cal.calibrate(m, [ids]), w_bits=8)
+    assert isinstance(q.backbone.layers[0].mixer, W8A8QMamba2)
+    st = {}
+    lg = omodel.model_forward(q, ids, num_last_tokens=1, states=st)[:, -1]
+    with torch.no_grad():
+        ref = m(ids)[:, -1]
+    assert (lg.float() - ref).abs().max().item() < 0.15 * ref.abs().max().item()
+    nxt = omodel.model_step(q, lg.argmax(-1), st)
+    assert nxt.shape == (1, 320) and torch.isfinite(nxt.float()).all()
