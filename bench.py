@@ -281,7 +281,7 @@ def run_head_parallel(args, rank, local_rank, world, pk):
         "dtype": "int8 (int4 weights, int8 activations, int32 accumulate; fp16 / fp32 scan and norm math)", "data": "synthetic",
         "config": {"workload": r["workload"] + ("" if r["layers"] == bp.CFG8B["n_layer"] else f" -- REDUCED to {r['layers']} layers (profiling case)"),
                    "weights": "int4 per output channel", "parallelism": f"head-parallel tp{world}: in_proj column-parallel by SSD group, "
-                   "out_proj row-parallel, one NCCL all-reduce per layer in chunks of sequences overlapped with compute",
+                   "out_proj row-parallel, one exchange step per layer in chunks of sequences overlapped with compute: " + str(r["collective"]),
                    "l2": "131072 tokens per step: every activation tensor is far larger than the 126 MB L2",
                    "note": "at N = 1 bench.py reports the Mamba2-2.7B line (the metric's own configuration) and carries this workload's "
                            "single-GPU time in its head_parallel_8b key: that is the base of this strong-scaling curve"},
@@ -342,6 +342,10 @@ def run_mamba1(args, dev, pk):
 def run_ours(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
+    if world > 1:
+        # before the CUDA context exists: streams of one process on hardware queues of their own (a put queued behind another
+        # stream's waiting kernel would keep a peer waiting in turn)
+        os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -450,6 +454,9 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=16, help="--gpus >= 2: multiprocessors left to NCCL (compute grids use the rest); 0 = no split")
     ap.add_argument("--plain-allreduce", action="store_true", help="--gpus >= 2: one fp16 all-reduce per layer and a replicated block norm "
                     "instead of reduce-scatter + token-sharded norm + int8 all-gather")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="--gpus >= 2: who moves the bytes of the token-sharded layer exchange: NCCL reduce-scatter / all-gather kernels, or "
+                    "copy-engine puts into peer memory with flags and bounded waits (quamba_b200/peer.py)")
     ap.add_argument("--chunk-seqs", type=int, default=0, help="head-parallel prefill: sequences per chunk (0: 8 on several GPUs, 4 on one)")
     ap.add_argument("--seqlen", type=int, default=PROMPT)
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)

@@ -85,6 +85,8 @@ def run(args, rank, local_rank, world, layers=None):
     t0 = time.time()
     stack = Stack(cfg, rank, world, dev).runner()
     stack.token_sharded_norm = not getattr(args, "plain_allreduce", False)
+    stack.exchange = getattr(args, "exchange", "nccl") if world > 1 and stack.token_sharded_norm else "nccl"
+    peer = stack.exchange == "peer"
     import os
     stack.early_overlap = not os.environ.get("QB_NO_EARLY_OVERLAP")
     build_s = time.time() - t0
@@ -111,7 +113,7 @@ def run(args, rank, local_rank, world, layers=None):
     # get an SM only when a kernel ends, and once they are in, the next persistent grid runs in two waves.  The library
     # sizes its grids for all but COMM_SMS multiprocessors and NCCL is capped at as many CTAs (NCCL_MAX_CTAS, set by
     # bench.py before the process group exists).
-    comm_sms = getattr(args, "comm_sms", COMM_SMS) if world > 1 else 0
+    comm_sms = getattr(args, "comm_sms", COMM_SMS) if world > 1 and not peer else 0   # copy engines need no multiprocessor
     sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
     _lib.set_sm_budget(sm_total - comm_sms if comm_sms > 0 else 0)
     steps = max(1, args.steps)
@@ -120,11 +122,16 @@ def run(args, rank, local_rank, world, layers=None):
     barrier()
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
     # the two forms of the layer's collective compute the same sums: compare their last-token logits once, outside the timing
-    form_diff = None
+    form_diff = peer_diff = None
     if world > 1 and stack.token_sharded_norm:
         with _lib.early_overlap(stack.early_overlap), torch.no_grad():
             other = stack._prefill_allreduce(ids[0], chunk_seqs)
+            via_nccl = stack._prefill_token_sharded(ids[0], chunk_seqs) if peer else None
         torch.cuda.synchronize()
+        if via_nccl is not None:      # the same exchange through NCCL's reduce-scatter / all-gather
+            peer_diff = {"max_abs_diff": (logits.float() - via_nccl.float()).abs().max().item(),
+                         "same_argmax": bool((logits.argmax(-1) == via_nccl.argmax(-1)).all().item())}
+            del via_nccl
         form_diff = {"max_abs_diff": (logits.float() - other.float()).abs().max().item(), "max_abs_logit": other.float().abs().max().item(),
                      "same_argmax": bool((logits.argmax(-1) == other.argmax(-1)).all().item())}
         del other
@@ -138,6 +145,9 @@ def run(args, rank, local_rank, world, layers=None):
     ms_compute = timed(max(1, steps // 2), collective=False)
     ms_comm = timed(max(1, steps // 2), compute=False) if world > 1 else 0.0
     ms_step, ms_compute, ms_comm = max_over_ranks([ms_step, ms_compute, ms_comm], device=dev)
+    _lib.read_device_status(torch.cuda.current_stream().cuda_stream)     # a wait that gave up would have left its code here
+    barrier()
+    stack.close()
     if rank != 0:
         return None
     tokens = BATCH * PROMPT
@@ -156,10 +166,12 @@ def run(args, rank, local_rank, world, layers=None):
             "gemm_flops_per_step": flops, "gemm_tops_per_gpu": flops / world / (ms_compute * 1e-3) / 1e12,
             "chunk_sequences": chunk_seqs, "layers": cfg["n_layer"], "build_seconds": build_s, "workload": WORKLOAD8B,
             "clocks": clocks, "compute_sms": sm_total - comm_sms, "nccl_max_ctas": comm_sms if world > 1 else None,
-            "token_sharded_vs_allreduce_logits": form_diff,
+            "token_sharded_vs_allreduce_logits": form_diff, "peer_exchange_vs_nccl_logits": peer_diff, "exchange": stack.exchange,
             # the same seed builds the same model on any number of GPUs: these must agree between N = 1 and N > 1
             "logits_digest": {"argmax": logits.argmax(-1).tolist(), "row0_first8": [round(v, 4) for v in logits[0, :8].float().tolist()],
                               "abs_sum": round(logits.float().abs().sum().item(), 2)},
-            "collective": ("reduce-scatter (fp16) + all-gather (int8) around a token-sharded block norm" if stack.token_sharded_norm
+            "collective": (("copy-engine puts into peer memory (fp16 partial sums by owner, int8 rows to all), flags, bounded waits and "
+                            "a local sum, around a token-sharded block norm") if peer else
+                           "reduce-scatter (fp16) + all-gather (int8) around a token-sharded block norm" if stack.token_sharded_norm
                            else "all-reduce (fp16)") if world > 1 else None,
             "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}

@@ -716,6 +716,46 @@ typedef struct {
 } qb_decode_gate_had_quant_args;
 int qb_decode_gate_had_quant(const qb_decode_gate_had_quant_args* a, void* stream);
 
+/* ---- the exchange step of a head-parallel layer over peer memory ------------------------------------------------------
+ * The reference has no tensor parallelism (quamba/qMamba2.py:84-88 asserts process_group is None); these entry points
+ * serve this library's head-parallel layers (one process per GPU).  Every rank owns one region of device memory that its
+ * peers map through a CUDA IPC handle.  A rank PUTS its pieces into its peers' regions with copy-engine transfers (no
+ * multiprocessor is used, the transfers run beside the compute stream's kernels) and then raises one 32-bit flag per
+ * peer; a consumer WAITS for its own flags with a one-warp kernel whose polling is bounded in time: when the limit
+ * passes, the kernel records QB_ERR_TIMEOUT in the device status word (qb_read_device_status) and returns, so the
+ * context stays usable.  Flags are counters that only grow: a waiter passes when `flag - value >= 0` (wrap-safe).
+ *
+ * qb_peer_alloc:  cudaMalloc + zero fill of `bytes`, and the 64-byte IPC handle other processes open.
+ * qb_peer_open:   maps a peer's region into this process (peer access is enabled lazily by the driver).
+ * qb_peer_close / qb_peer_free: the inverses.  Close every mapping before the owner frees its region.
+ * qb_peer_put:    for every rank q < n with dst[q] != NULL: one cudaMemcpyAsync of `bytes` from
+ *                 src + q * src_stride_bytes to dst[q] on `stream` (src_stride_bytes 0 sends the same piece to all),
+ *                 issued in the order self+1, self+2, ... so that the ranks do not all start on the same peer; then one
+ *                 kernel on `stream` that stores `value` to every flag[q] != NULL with system scope.  Stream order puts the
+ *                 flag after the data.
+ * qb_peer_wait:   one warp on `stream`; lane i < n polls flags[i] (this rank's own memory) until it reaches `value` or
+ *                 `timeout_ms` passes.
+ * qb_sum_partials: out[i] = fp16(sum over p < n_partials of partials[p * partial_stride + i]) for i < n, the sum taken
+ *                 in fp32 in the order p = 0, 1, ...: the reduce half of the exchange on the receiving rank. */
+#define QB_MAX_PEERS 16
+typedef struct {
+  const void* src;
+  int64_t src_stride_bytes;
+  int64_t bytes;
+  void* dst[QB_MAX_PEERS];
+  uint32_t* flag[QB_MAX_PEERS];
+  int32_t n;
+  int32_t self;
+  uint32_t value;
+} qb_peer_put_args;
+int qb_peer_alloc(int64_t bytes, void** ptr, unsigned char handle[64]);
+int qb_peer_open(const unsigned char handle[64], void** ptr);
+int qb_peer_close(void* ptr);
+int qb_peer_free(void* ptr);
+int qb_peer_put(const qb_peer_put_args* a, void* stream);
+int qb_peer_wait(const uint32_t* flags, int32_t n, uint32_t value, int32_t timeout_ms, void* stream);
+int qb_sum_partials(const void* partials, int32_t n_partials, int64_t partial_stride, void* out, int64_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

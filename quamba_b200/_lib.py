@@ -17,6 +17,7 @@ _CTYPES = {
     "int64_t": ctypes.c_int64,
     "int32_t": ctypes.c_int32,
     "int": ctypes.c_int32,
+    "uint32_t": ctypes.c_uint32,
     "float": ctypes.c_float,
 }
 
@@ -31,6 +32,7 @@ QB_ERR_TOO_LARGE = -5
 def parse_header(text: str):
     """Return ({struct_name: [(field, ctype), ...]}, [function names])."""
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    defines = {k: int(v) for k, v in re.findall(r"^#define\s+(QB_\w+)\s+(\d+)\s*$", text, flags=re.M)}
     structs = {}
     for body, name in re.findall(r"typedef\s+struct\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
         fields = []
@@ -38,12 +40,14 @@ def parse_header(text: str):
             line = line.strip()
             if not line:
                 continue
-            m = re.match(r"^(.*?)(\w+)\s*;$", line)
-            ctype_txt, fname = m.group(1).strip(), m.group(2)
+            m = re.match(r"^(.*?)(\w+)\s*(?:\[(\w+)\])?\s*;$", line)
+            ctype_txt, fname, count = m.group(1).strip(), m.group(2), m.group(3)
             if "*" in ctype_txt:
                 ct = ctypes.c_void_p
             else:
                 ct = _CTYPES[ctype_txt.replace("const", "").strip()]
+            if count is not None:                     # a fixed-size array field: `type name[N];`, N a number or a #define
+                ct = ct * (int(count) if count.isdigit() else defines[count])
             fields.append((fname, ct))
         structs[name] = fields
     funcs = re.findall(r"^\s*(?:const\s+char\s*\*|int64_t|int)\s+(qb_\w+)\s*\(", text, flags=re.M)

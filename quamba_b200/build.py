@@ -11,7 +11,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libquamba_b200.so"
 SOURCES = ["lib.cu", "conv1d.cu", "hadamard.cu", "hadamard_tc.cu", "sscan.cu", "ssd.cu", "ssd_tc.cu", "linear.cu", "gemm_tc.cu", "norm.cu",
-           "embedding.cu", "decode.cu"]
+           "embedding.cu", "decode.cu", "peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

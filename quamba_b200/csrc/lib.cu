@@ -108,6 +108,7 @@ extern "C" int64_t qb_sizeof(const char* name) {
   QB_SZ(qb_embedding_args);
   QB_SZ(qb_decode_norm_linear_args);
   QB_SZ(qb_decode_gate_had_quant_args);
+  QB_SZ(qb_peer_put_args);
 #undef QB_SZ
   return -1;
 }

@@ -154,6 +154,10 @@ class HeadParallelStack:
       + RMSNorm + quantise on this rank's rows only, all-gather of the int8 rows for the next in_proj;
     * ``False``: one fp16 all-reduce per layer, block norm replicated on every rank.
 
+    ``exchange`` picks who moves the bytes of the token-sharded form: ``"nccl"`` (reduce-scatter / all-gather kernels on
+    NCCL's stream) or ``"peer"`` (:class:`quamba_b200.peer.LayerExchange`: copy-engine puts into the peers' memory, flags,
+    time-bounded waits and a local sum, no multiprocessor spent on the transfer).
+
     ``collective`` / ``compute`` switch the two halves off for separate timings (the results are then meaningless)."""
 
     def __init__(self, embedding, norms, shards, norm_f, lm_head, rank, world, d_model):
@@ -162,12 +166,17 @@ class HeadParallelStack:
         self.dev = lm_head.weight.device
         self.token_sharded_norm = True
         self.early_overlap = True
+        self.exchange = "nccl"
+        self.peer_timeout_ms = 20000
+        self._peer, self._peer_key, self._peer_epoch, self._comm_stream = None, None, 0, None
 
     def prefill(self, ids, chunk_seqs, collective=True, compute=True):
         with _lib.early_overlap(self.early_overlap), torch.no_grad():
             return self._prefill(ids, chunk_seqs, collective, compute)
 
     def _prefill(self, ids, chunk_seqs, collective=True, compute=True):
+        if self.world > 1 and self.token_sharded_norm and self.exchange == "peer":
+            return self._prefill_peer(ids, chunk_seqs, collective, compute)
         if self.world > 1 and self.token_sharded_norm:
             return self._prefill_token_sharded(ids, chunk_seqs, collective, compute)
         return self._prefill_allreduce(ids, chunk_seqs, collective, compute)
@@ -223,11 +232,15 @@ class HeadParallelStack:
                 pend_rs[c].wait()
         if not compute:
             return None
-        # last token of every sequence: its row lives on one rank; every rank fills its own rows of a small buffer and one
-        # tiny all-reduce gives all of them to everybody
+        return self._last_token_logits(chunks, hs, res, per, collective)
+
+    def _last_token_logits(self, chunks, hs, res, per, collective):
+        """Last token of every sequence: its row lives on one rank; every rank fills its own rows of a small buffer and one
+        tiny all-reduce gives all of them to everybody."""
+        rank, d = self.rank, self.d_model
         seqlen = chunks[0].shape[1]
         lasts = []
-        for c in range(n):
+        for c in range(len(chunks)):
             nseq = chunks[c].shape[0]
             buf_h = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
             buf_r = torch.zeros((nseq, d), dtype=torch.float32, device=self.dev)
@@ -240,6 +253,93 @@ class HeadParallelStack:
                 dist.all_reduce(buf_h); dist.all_reduce(buf_r)
             lasts.append(self.norm_f(buf_h.half()[:, None], residual=buf_r[:, None], prenorm=False, residual_in_fp32=True))
         return self.lm_head(torch.cat(lasts))[:, -1]
+
+    def _peer_exchange(self, rows, n):
+        from .peer import LayerExchange
+        key = (rows, n)
+        if self._peer_key != key:
+            if self._peer is not None:
+                self._peer.close()
+            self._peer = LayerExchange(self.rank, self.world, rows, self.d_model, n, self.dev, timeout_ms=self.peer_timeout_ms)
+            self._peer_key, self._peer_epoch = key, 0
+            self._comm_stream = torch.cuda.Stream(device=self.dev, priority=-1)
+            dist.barrier()                       # nobody puts before every rank has mapped every region
+        return self._peer
+
+    def close(self):
+        if self._peer is not None:
+            self._peer.close()
+            self._peer = self._peer_key = None
+
+    def _prefill_peer(self, ids, chunk_seqs, collective=True, compute=True):
+        """The token-sharded exchange of :meth:`_prefill_token_sharded` with the bytes moved by copy engines.  Per layer and
+        chunk, on the compute stream: [wait for the T partial pieces of the layer before -> sum them ->] residual add + norm
+        + quantise of this rank's rows; wait for everybody's int8 rows -> the layer shard -> fp16 partial output.  On the
+        side stream, each behind an event of its producer: put of the int8 rows into every rank's buffer, put of the
+        partial output's T row pieces into their owners' slots.  A buffer is reused one layer later, and every reuse is
+        ordered behind its last reader by the flags themselves: a peer can only put layer l + 1's rows after it has summed
+        layer l's pieces, and only put layer l + 1's pieces after it has consumed layer l + 1's rows."""
+        T, rank, d = self.world, self.rank, self.d_model
+        chunks = list(ids.split(chunk_seqs))
+        n = len(chunks)
+        rows = chunks[0].numel()
+        assert rows % T == 0 and all(c.numel() == rows for c in chunks)
+        per = rows // T
+        mine = slice(rank * per, (rank + 1) * per)
+        ex = self._peer_exchange(rows, n)
+        main, comm = torch.cuda.current_stream(self.dev), self._comm_stream
+        hs = [self.embedding(c.reshape(-1)[mine]) if compute else torch.empty((per, d), dtype=torch.float16, device=self.dev) for c in chunks]
+        res = [None] * n
+        L = len(self.norms)
+        e0 = self._peer_epoch
+        if collective:
+            self._peer_epoch += L
+        dummy_q = dummy_p = None
+        if not compute:
+            dummy_q = torch.zeros((per, d), dtype=torch.int8, device=self.dev)
+            dummy_p = torch.zeros((rows, d), dtype=torch.float16, device=self.dev)
+
+        def after_main(put, *a):
+            ev = torch.cuda.Event()
+            ev.record(main)
+            comm.wait_event(ev)
+            put(*a, comm)
+
+        for li, (norm, shard) in enumerate(zip(self.norms, self.shards)):
+            v = e0 + li + 1
+            for c in range(n):
+                if li > 0 and collective:
+                    ex.wait_partials(c, v - 1)
+                    if compute:
+                        hs[c] = ex.reduce(c)
+                q = norm(hs[c], residual=res[c], prenorm=True, residual_in_fp32=True) if compute else None
+                if compute:
+                    q, res[c] = q
+                    q = q.contiguous()
+                if collective:
+                    after_main(ex.put_rows, c, q if compute else dummy_q, v)
+                elif compute:
+                    ex.rows_int8[c][mine].copy_(q)
+            for c in range(n):
+                if collective:
+                    ex.wait_rows(c, v)
+                partial = None
+                if compute:
+                    partial = shard(ex.rows_int8[c].view(chunks[c].shape[0], -1, d)).reshape(rows, d)
+                    if not partial.is_contiguous():
+                        partial = partial.contiguous()
+                if collective:
+                    after_main(ex.put_partials, c, partial if compute else dummy_p, v)
+                elif compute:
+                    hs[c] = partial[mine]
+        if collective:
+            for c in range(n):
+                ex.wait_partials(c, e0 + L)
+                if compute:
+                    hs[c] = ex.reduce(c)
+        if not compute:
+            return None
+        return self._last_token_logits(chunks, hs, res, per, collective)
 
     def _prefill_allreduce(self, ids, chunk_seqs, collective=True, compute=True):
         """ids (batch, L) on the device -> last-token logits (batch, vocab).  ``collective`` / ``compute`` switch the two
