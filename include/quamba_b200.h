@@ -732,7 +732,9 @@ int qb_decode_gate_had_quant(const qb_decode_gate_had_quant_args* a, void* strea
  *                 src + q * src_stride_bytes to dst[q] on `stream` (src_stride_bytes 0 sends the same piece to all),
  *                 issued in the order self+1, self+2, ... so that the ranks do not all start on the same peer; then one
  *                 kernel on `stream` that stores `value` to every flag[q] != NULL with system scope.  Stream order puts the
- *                 flag after the data.
+ *                 flag after the data.  With stream_of[q] != NULL the piece for rank q and its flag go on that stream
+ *                 instead (one stream per destination lets several copy engines work at once); after_event != NULL
+ *                 (a cudaEvent_t) makes every stream used wait for that event first: the producer of `src`.
  * qb_peer_wait:   one warp on `stream`; lane i < n polls flags[i] (this rank's own memory) until it reaches `value` or
  *                 `timeout_ms` passes.
  * qb_sum_partials: out[i] = fp16(sum over p < n_partials of partials[p * partial_stride + i]) for i < n, the sum taken
@@ -744,6 +746,8 @@ typedef struct {
   int64_t bytes;
   void* dst[QB_MAX_PEERS];
   uint32_t* flag[QB_MAX_PEERS];
+  void* stream_of[QB_MAX_PEERS];
+  void* after_event;
   int32_t n;
   int32_t self;
   uint32_t value;

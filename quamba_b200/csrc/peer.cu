@@ -140,23 +140,46 @@ extern "C" int qb_peer_put(const qb_peer_put_args* a, void* stream) {
              a->self);
   QB_REQUIRE(a->bytes >= 0 && a->src_stride_bytes >= 0 && (a->bytes == 0 || a->src != nullptr), QB_ERR_INVALID_ARG, "peer_put: bad source");
   cudaStream_t st = (cudaStream_t)stream;
-  FlagList f;
-  bool any_flag = false;
-  for (int q = 0; q < QB_MAX_PEERS; ++q) {
-    f.p[q] = q < a->n ? a->flag[q] : nullptr;
-    any_flag = any_flag || f.p[q] != nullptr;
-  }
-  if (a->bytes > 0) {
-    for (int k = 1; k <= a->n; ++k) {
-      const int q = (a->self + k) % a->n;      // own piece last
-      if (a->dst[q] == nullptr) continue;
-      const char* s = static_cast<const char*>(a->src) + (int64_t)q * a->src_stride_bytes;
-      QB_CUDA_OK(cudaMemcpyAsync(a->dst[q], s, (size_t)a->bytes, cudaMemcpyDeviceToDevice, st));
+  cudaEvent_t ev = (cudaEvent_t)a->after_event;
+  bool per_peer = false;
+  for (int q = 0; q < a->n; ++q) per_peer = per_peer || a->stream_of[q] != nullptr;
+  if (!per_peer) {
+    FlagList f;
+    bool any_flag = false;
+    for (int q = 0; q < QB_MAX_PEERS; ++q) {
+      f.p[q] = q < a->n ? a->flag[q] : nullptr;
+      any_flag = any_flag || f.p[q] != nullptr;
     }
+    if (ev != nullptr) QB_CUDA_OK(cudaStreamWaitEvent(st, ev, 0));
+    if (a->bytes > 0) {
+      for (int k = 1; k <= a->n; ++k) {
+        const int q = (a->self + k) % a->n;      // own piece last
+        if (a->dst[q] == nullptr) continue;
+        const char* s = static_cast<const char*>(a->src) + (int64_t)q * a->src_stride_bytes;
+        QB_CUDA_OK(cudaMemcpyAsync(a->dst[q], s, (size_t)a->bytes, cudaMemcpyDeviceToDevice, st));
+      }
+    }
+    if (any_flag) {
+      peer_signal_kernel<<<1, QB_MAX_PEERS, 0, st>>>(f, a->n, a->value);
+      QB_LAUNCH_OK("peer_signal_kernel");
+    }
+    return QB_OK;
   }
-  if (any_flag) {
-    peer_signal_kernel<<<1, QB_MAX_PEERS, 0, st>>>(f, a->n, a->value);
-    QB_LAUNCH_OK("peer_signal_kernel");
+  for (int k = 1; k <= a->n; ++k) {
+    const int q = (a->self + k) % a->n;
+    if (a->dst[q] == nullptr && a->flag[q] == nullptr) continue;
+    cudaStream_t sq = a->stream_of[q] != nullptr ? (cudaStream_t)a->stream_of[q] : st;
+    if (ev != nullptr) QB_CUDA_OK(cudaStreamWaitEvent(sq, ev, 0));
+    if (a->bytes > 0 && a->dst[q] != nullptr) {
+      const char* s = static_cast<const char*>(a->src) + (int64_t)q * a->src_stride_bytes;
+      QB_CUDA_OK(cudaMemcpyAsync(a->dst[q], s, (size_t)a->bytes, cudaMemcpyDeviceToDevice, sq));
+    }
+    if (a->flag[q] != nullptr) {
+      FlagList f = {};
+      f.p[0] = a->flag[q];
+      peer_signal_kernel<<<1, 32, 0, sq>>>(f, 1, a->value);
+      QB_LAUNCH_OK("peer_signal_kernel");
+    }
   }
   return QB_OK;
 }

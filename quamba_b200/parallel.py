@@ -168,7 +168,8 @@ class HeadParallelStack:
         self.early_overlap = True
         self.exchange = "nccl"
         self.peer_timeout_ms = 20000
-        self._peer, self._peer_key, self._peer_epoch, self._comm_stream = None, None, 0, None
+        self.peer_lag = None           # B tasks between a partial output and the norm that consumes it (None: half the chunks)
+        self._peer, self._peer_key, self._peer_epoch = None, None, 0
 
     def prefill(self, ids, chunk_seqs, collective=True, compute=True):
         with _lib.early_overlap(self.early_overlap), torch.no_grad():
@@ -262,7 +263,6 @@ class HeadParallelStack:
                 self._peer.close()
             self._peer = LayerExchange(self.rank, self.world, rows, self.d_model, n, self.dev, timeout_ms=self.peer_timeout_ms)
             self._peer_key, self._peer_epoch = key, 0
-            self._comm_stream = torch.cuda.Stream(device=self.dev, priority=-1)
             dist.barrier()                       # nobody puts before every rank has mapped every region
         return self._peer
 
@@ -272,13 +272,20 @@ class HeadParallelStack:
             self._peer = self._peer_key = None
 
     def _prefill_peer(self, ids, chunk_seqs, collective=True, compute=True):
-        """The token-sharded exchange of :meth:`_prefill_token_sharded` with the bytes moved by copy engines.  Per layer and
-        chunk, on the compute stream: [wait for the T partial pieces of the layer before -> sum them ->] residual add + norm
-        + quantise of this rank's rows; wait for everybody's int8 rows -> the layer shard -> fp16 partial output.  On the
-        side stream, each behind an event of its producer: put of the int8 rows into every rank's buffer, put of the
-        partial output's T row pieces into their owners' slots.  A buffer is reused one layer later, and every reuse is
-        ordered behind its last reader by the flags themselves: a peer can only put layer l + 1's rows after it has summed
-        layer l's pieces, and only put layer l + 1's pieces after it has consumed layer l + 1's rows."""
+        """The token-sharded exchange of :meth:`_prefill_token_sharded` with the bytes moved by copy engines.  Two kinds of
+        task per (layer, chunk) on the compute stream:
+
+        * A: [wait for the T partial pieces of the layer before -> sum them ->] residual add + norm + quantise of this
+          rank's rows, then the put of the int8 rows into every rank's buffer;
+        * B: wait for everybody's int8 rows -> the layer shard -> the put of the fp16 partial output's T row pieces into
+          their owners' slots.
+
+        The puts run on side streams behind an event of their producer.  Tasks are issued skewed, so that a transfer has the
+        compute of other chunks to hide behind: with n chunks and k counting (layer, chunk) pairs in order, A(k) follows
+        B(k - n + lag) and so comes ``lag`` B tasks after B(k - n), whose partial output it needs; B(k) comes n - lag - 1 B
+        tasks after A(k), whose rows it needs.  A buffer is reused one layer later, and every reuse is ordered behind its last
+        reader by the flags themselves: a peer can only put layer l + 1's rows after it has summed layer l's pieces, and only
+        put layer l + 1's pieces after it has consumed layer l + 1's rows."""
         T, rank, d = self.world, self.rank, self.d_model
         chunks = list(ids.split(chunk_seqs))
         n = len(chunks)
@@ -287,7 +294,6 @@ class HeadParallelStack:
         per = rows // T
         mine = slice(rank * per, (rank + 1) * per)
         ex = self._peer_exchange(rows, n)
-        main, comm = torch.cuda.current_stream(self.dev), self._comm_stream
         hs = [self.embedding(c.reshape(-1)[mine]) if compute else torch.empty((per, d), dtype=torch.float16, device=self.dev) for c in chunks]
         res = [None] * n
         L = len(self.norms)
@@ -299,44 +305,53 @@ class HeadParallelStack:
             dummy_q = torch.zeros((per, d), dtype=torch.int8, device=self.dev)
             dummy_p = torch.zeros((rows, d), dtype=torch.float16, device=self.dev)
 
-        def after_main(put, *a):
-            ev = torch.cuda.Event()
-            ev.record(main)
-            comm.wait_event(ev)
-            put(*a, comm)
-
-        for li, (norm, shard) in enumerate(zip(self.norms, self.shards)):
-            v = e0 + li + 1
-            for c in range(n):
-                if li > 0 and collective:
-                    ex.wait_partials(c, v - 1)
+        def task_a(k):
+            li, c = divmod(k, n)
+            if li > 0:
+                if collective:
+                    ex.wait_partials(c, e0 + li)
                     if compute:
                         hs[c] = ex.reduce(c)
-                q = norm(hs[c], residual=res[c], prenorm=True, residual_in_fp32=True) if compute else None
-                if compute:
-                    q, res[c] = q
-                    q = q.contiguous()
-                if collective:
-                    after_main(ex.put_rows, c, q if compute else dummy_q, v)
-                elif compute:
-                    ex.rows_int8[c][mine].copy_(q)
-            for c in range(n):
-                if collective:
-                    ex.wait_rows(c, v)
-                partial = None
-                if compute:
-                    partial = shard(ex.rows_int8[c].view(chunks[c].shape[0], -1, d)).reshape(rows, d)
-                    if not partial.is_contiguous():
-                        partial = partial.contiguous()
-                if collective:
-                    after_main(ex.put_partials, c, partial if compute else dummy_p, v)
-                elif compute:
-                    hs[c] = partial[mine]
-        if collective:
-            for c in range(n):
-                ex.wait_partials(c, e0 + L)
-                if compute:
-                    hs[c] = ex.reduce(c)
+            if li == L:                    # past the last layer: only the sum of its output
+                return
+            q = None
+            if compute:
+                q, res[c] = self.norms[li](hs[c], residual=res[c], prenorm=True, residual_in_fp32=True)
+                q = q.contiguous()
+            if collective:
+                ex.put_rows(c, q if compute else dummy_q, e0 + li + 1)
+            elif compute:
+                ex.rows_int8[c][mine].copy_(q)
+
+        def task_b(k):
+            li, c = divmod(k, n)
+            if collective:
+                ex.wait_rows(c, e0 + li + 1)
+            partial = None
+            if compute:
+                partial = self.shards[li](ex.rows_int8[c].view(chunks[c].shape[0], -1, d)).reshape(rows, d)
+                if not partial.is_contiguous():
+                    partial = partial.contiguous()
+            if collective:
+                ex.put_partials(c, partial if compute else dummy_p, e0 + li + 1)
+            elif compute:
+                hs[c] = partial[mine]
+
+        lag = self.peer_lag if self.peer_lag is not None else max(1, n // 2)
+        lead = max(1, n - min(lag, n - 1)) if n > 1 else 1
+        total_a, total_b = (L + 1) * n, L * n
+        next_a = 0
+        for k in range(min(lead, total_a)):
+            task_a(k)
+            next_a = k + 1
+        for j in range(total_b):
+            task_b(j)
+            if j + lead < total_a:
+                assert next_a == j + lead
+                task_a(j + lead)
+                next_a = j + lead + 1
+        for k in range(next_a, total_a):
+            task_a(k)
         if not compute:
             return None
         return self._last_token_logits(chunks, hs, res, per, collective)

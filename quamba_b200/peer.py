@@ -121,7 +121,9 @@ class LayerExchange:
       all-gather half.
 
     Each put raises one flag per destination (a counter the caller advances once per layer); ``wait_partials`` /
-    ``wait_rows`` hold the CURRENT stream until all T flags of the chunk have reached the value."""
+    ``wait_rows`` hold the CURRENT stream until all T flags of the chunk have reached the value.  A put is issued behind
+    an event of the stream that produced its source, on one high-priority stream per destination, so that the pieces of
+    one put travel on several copy engines at once."""
 
     def __init__(self, rank, world, rows, d, n_chunks, device, group=None, timeout_ms=20000):
         assert rows % world == 0 and (rows // world * d) % 16 == 0
@@ -148,22 +150,30 @@ class LayerExchange:
                 b.flag[q] = base + off + self._recv_b + self._rows_b + 4 * (32 + rank)
             self._args_partials.append(a)
             self._args_rows.append(b)
+        with torch.cuda.device(self.region.device):
+            self.streams = [torch.cuda.Stream(priority=-1) for _ in range(T)]
+        for args in self._args_partials + self._args_rows:
+            for q in range(T):
+                args.stream_of[q] = self.streams[q].cuda_stream
 
-    def put_partials(self, c, partial, value, stream):
-        """partial: (rows, d) fp16 contiguous.  ``stream``: a torch stream that already waits for the producer of it."""
+    def _issue(self, args, src, value):
+        """Behind everything queued so far on the current stream (the producer of ``src``)."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.region.device))
+        args.src, args.value, args.after_event = src.data_ptr(), value & 0xFFFFFFFF, ev.cuda_event
+        _put(args, self.streams[self.rank].cuda_stream)
+        for st in self.streams:
+            src.record_stream(st)
+
+    def put_partials(self, c, partial, value):
+        """partial: (rows, d) fp16 contiguous, produced on the current stream."""
         assert partial.dtype == torch.float16 and partial.is_contiguous() and partial.numel() == self.rows * self.d
-        a = self._args_partials[c]
-        a.src, a.value = partial.data_ptr(), value & 0xFFFFFFFF
-        _put(a, stream.cuda_stream)
-        partial.record_stream(stream)
+        self._issue(self._args_partials[c], partial, value)
 
-    def put_rows(self, c, q_rows, value, stream):
-        """q_rows: (rows / T, d) int8 contiguous, this rank's rows."""
+    def put_rows(self, c, q_rows, value):
+        """q_rows: (rows / T, d) int8 contiguous, this rank's rows, produced on the current stream."""
         assert q_rows.dtype == torch.int8 and q_rows.is_contiguous() and q_rows.numel() == self.per * self.d
-        b = self._args_rows[c]
-        b.src, b.value = q_rows.data_ptr(), value & 0xFFFFFFFF
-        _put(b, stream.cuda_stream)
-        q_rows.record_stream(stream)
+        self._issue(self._args_rows[c], q_rows, value)
 
     def _wait(self, c, first_word, value):
         f = self._flags[c]

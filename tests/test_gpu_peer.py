@@ -39,15 +39,13 @@ def test_puts_flags_and_waits_inside_one_process():
     from quamba_b200.peer import LayerExchange
     ex = LayerExchange(0, 1, rows=64, d=256, n_chunks=2, device="cuda:0", timeout_ms=2000)
     try:
-        side = torch.cuda.Stream()
         g = torch.Generator().manual_seed(0)
         for value in (1, 2, 3):
             for c in range(2):
                 q = torch.randint(-128, 128, (64, 256), generator=g, dtype=torch.int32).to(torch.int8).cuda()
                 part = torch.randn(64, 256, generator=g).half().cuda()
-                side.wait_stream(torch.cuda.current_stream())
-                ex.put_rows(c, q, value, side)
-                ex.put_partials(c, part, value, side)
+                ex.put_rows(c, q, value)
+                ex.put_partials(c, part, value)
                 ex.wait_rows(c, value)
                 ex.wait_partials(c, value)
                 assert torch.equal(ex.rows_int8[c], q)
@@ -99,9 +97,11 @@ def _two_rank_worker(rank, world, port, out_dir):
     g = torch.Generator().manual_seed(5)
     ids = torch.randint(0, 1000, (4, 256), generator=g).to(dev)
     results = {}
-    for name in ("nccl", "peer", "peer"):            # the second peer pass runs on advanced flag counters
+    # the second peer pass runs on advanced flag counters, the third on four chunks (the skewed task order; the
+    # exchange buffers are rebuilt for the new chunk size; chunking does not change any token's result)
+    for name, chunk_seqs in (("nccl", 2), ("peer", 2), ("peer", 2), ("peer", 1)):
         stack.exchange = name
-        logits = stack.prefill(ids, 2)
+        logits = stack.prefill(ids, chunk_seqs)
         torch.cuda.synchronize()
         _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
         results.setdefault(name, []).append(logits.cpu())
