@@ -454,7 +454,7 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=16, help="--gpus >= 2: multiprocessors left to NCCL (compute grids use the rest); 0 = no split")
     ap.add_argument("--plain-allreduce", action="store_true", help="--gpus >= 2: one fp16 all-reduce per layer and a replicated block norm "
                     "instead of reduce-scatter + token-sharded norm + int8 all-gather")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="--gpus >= 2: who moves the bytes of the token-sharded layer exchange: NCCL reduce-scatter / all-gather kernels, or "
                     "copy-engine puts into peer memory with flags and bounded waits (quamba_b200/peer.py)")
     ap.add_argument("--chunk-seqs", type=int, default=0, help="head-parallel prefill: sequences per chunk (0: 8 on several GPUs, 4 on one)")

@@ -85,14 +85,29 @@ def run(args, rank, local_rank, world, layers=None):
     t0 = time.time()
     stack = Stack(cfg, rank, world, dev).runner()
     stack.token_sharded_norm = not getattr(args, "plain_allreduce", False)
-    stack.exchange = getattr(args, "exchange", "nccl") if world > 1 and stack.token_sharded_norm else "nccl"
+    stack.exchange = getattr(args, "exchange", "peer") if world > 1 and stack.token_sharded_norm else "nccl"
+    chunk_seqs = getattr(args, "chunk_seqs", 0) or (8 if world > 1 else 4)
+    fallback = None
+    if stack.exchange == "peer":
+        # map the peers' memory now; if any rank cannot (no IPC between the processes, say), every rank takes the NCCL exchange
+        try:
+            stack._peer_exchange(chunk_seqs * PROMPT, BATCH // chunk_seqs)
+            mine_ok, why = 1, ""
+        except Exception as e:  # noqa: BLE001 - whatever the set-up raised is the reason reported
+            mine_ok, why = 0, f"{type(e).__name__}: {e}"
+        ok = torch.tensor([mine_ok], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            reasons = [None] * world
+            dist.all_gather_object(reasons, why)
+            fallback = next((r for r in reasons if r), "a peer failed")[:300]
+            stack.exchange = "nccl"
     peer = stack.exchange == "peer"
     import os
     stack.early_overlap = not os.environ.get("QB_NO_EARLY_OVERLAP")
     build_s = time.time() - t0
     g = torch.Generator().manual_seed(99)
     ids = [torch.randint(0, cfg["vocab_size"], (BATCH, PROMPT), generator=g).to(dev) for _ in range(2)]
-    chunk_seqs = getattr(args, "chunk_seqs", 0) or (8 if world > 1 else 4)
 
     def barrier():
         if world > 1:
@@ -166,7 +181,7 @@ def run(args, rank, local_rank, world, layers=None):
             "gemm_flops_per_step": flops, "gemm_tops_per_gpu": flops / world / (ms_compute * 1e-3) / 1e12,
             "chunk_sequences": chunk_seqs, "layers": cfg["n_layer"], "build_seconds": build_s, "workload": WORKLOAD8B,
             "clocks": clocks, "compute_sms": sm_total - comm_sms, "nccl_max_ctas": comm_sms if world > 1 else None,
-            "token_sharded_vs_allreduce_logits": form_diff, "peer_exchange_vs_nccl_logits": peer_diff, "exchange": stack.exchange,
+            "token_sharded_vs_allreduce_logits": form_diff, "peer_exchange_vs_nccl_logits": peer_diff, "exchange": stack.exchange, "exchange_fallback": fallback,
             # the same seed builds the same model on any number of GPUs: these must agree between N = 1 and N > 1
             "logits_digest": {"argmax": logits.argmax(-1).tolist(), "row0_first8": [round(v, 4) for v in logits[0, :8].float().tolist()],
                               "abs_sum": round(logits.float().abs().sum().item(), 2)},

@@ -66,24 +66,52 @@ class PeerRegion:
         self.nbytes, self.rank, self.world, self.device, self.group = int(nbytes), rank, world, torch.device(device), group
         L = _bind()
         ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-        with torch.cuda.device(self.device):
-            _lib.check(L.qb_peer_alloc(self.nbytes, ctypes.byref(ptr), handle))
         self.base = [None] * world
-        self.base[rank] = ptr.value
-        self._opened = []
+        self._opened, self._bytes = [], None
+        # Every rank goes through the same sequence of collectives whatever happens locally, and all ranks raise together:
+        # a caller may then choose another exchange on every rank at once.
+        err = None
+        try:
+            with torch.cuda.device(self.device):
+                _lib.check(L.qb_peer_alloc(self.nbytes, ctypes.byref(ptr), handle))
+            self.base[rank] = ptr.value
+            self._bytes = torch.as_tensor(_DeviceBytes(ptr.value, self.nbytes))
+            assert self._bytes.data_ptr() == ptr.value and self._bytes.device == self.device, (self._bytes.device, self.device)
+        except Exception as e:  # noqa: BLE001
+            err = f"rank {rank}: {type(e).__name__}: {e}"
         if world > 1:
-            handles = [None] * world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            for q in range(world):
-                if q == rank:
-                    continue
-                p = ctypes.c_void_p()
-                with torch.cuda.device(self.device):
-                    _lib.check(L.qb_peer_open(handles[q], ctypes.byref(p)))
-                self.base[q] = p.value
-                self._opened.append(p.value)
-        self._bytes = torch.as_tensor(_DeviceBytes(ptr.value, self.nbytes))
-        assert self._bytes.data_ptr() == ptr.value and self._bytes.device == self.device, (self._bytes.device, self.device)
+            infos = [None] * world
+            dist.all_gather_object(infos, (handle.raw, err), group=group)
+            err = next((i[1] for i in infos if i[1]), None)
+            if err is None:
+                try:
+                    for q in range(world):
+                        if q == rank:
+                            continue
+                        p = ctypes.c_void_p()
+                        with torch.cuda.device(self.device):
+                            _lib.check(L.qb_peer_open(infos[q][0], ctypes.byref(p)))
+                        self.base[q] = p.value
+                        self._opened.append(p.value)
+                except Exception as e:  # noqa: BLE001
+                    err = f"rank {rank}: {type(e).__name__}: {e}"
+                errs = [None] * world
+                dist.all_gather_object(errs, err, group=group)
+                err = next((e for e in errs if e), None)
+        if err is not None:
+            self._release()
+            raise RuntimeError(f"peer memory set-up failed ({err})")
+
+    def _release(self):
+        L = _bind()
+        self._bytes = None
+        if self._opened or self.base[self.rank] is not None:
+            with torch.cuda.device(self.device):
+                for p in self._opened:
+                    L.qb_peer_close(p)
+                if self.base[self.rank] is not None:
+                    L.qb_peer_free(self.base[self.rank])
+        self.base, self._opened = None, []
 
     def local(self, offset, shape, dtype):
         """A view of this rank's own region."""

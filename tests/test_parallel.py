@@ -64,3 +64,28 @@ def test_shard_repacks_the_same_integers():
     q_out = packing.unpack_int4(m.out_proj.weight, m.out_proj.size_k, m.out_proj.size_n, False)
     assert torch.equal(torch.cat([packing.unpack_int4(r.weight, r.size_k, r.size_n, False) for r in (r0, r1)]), q_out)
     assert torch.equal(r0.s_channel, m.out_proj.s_channel)
+
+
+def _peer_setup_worker(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from quamba_b200.peer import PeerRegion
+    try:
+        PeerRegion(4096, rank, world, "cuda:0")
+        outcome = "mapped"
+    except RuntimeError as e:
+        outcome = str(e)
+    dist.barrier()              # both ranks are still in step: the set-up ran the same collectives on each
+    (Path(out_dir) / f"peer{rank}.txt").write_text(outcome)
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="the failing set-up needs a machine without a GPU")
+def test_peer_memory_setup_fails_on_every_rank_together(tmp_path):
+    """Without a GPU the region cannot be allocated: every rank must raise the same error after the same collectives
+    (a caller then moves all ranks to the NCCL exchange), never one rank ahead of the other."""
+    port = 29870 + os.getpid() % 100
+    mp.spawn(_peer_setup_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    a, b = ((tmp_path / f"peer{r}.txt").read_text() for r in (0, 1))
+    assert a.startswith("peer memory set-up failed") and a == b
