@@ -4,9 +4,11 @@ Workload (strong scaling: the same job on 1, 2, 4 or 8 GPUs): Quamba2 Mamba2-8B 
 expand 2 (128 heads x 64), ngroups 8, d_state 128, d_conv 4, vocab 256000, random-init weights N(0, 0.02) quantized to
 int4 per output channel, int8 activations with static scales calibrated on 4 random sequences -- batch 32, prefill of
 4096 uniform-random token ids.  Every rank holds all token rows and 1/T of every layer's heads (in_proj column-parallel by
-SSD group, conv / SSD / gated norm local, block-diagonal Hadamard, out_proj row-parallel); the only collective is one NCCL
-all-reduce of the (tokens, 4096) fp16 layer output per layer, issued per chunk of sequences so that the reduction of one
-chunk overlaps the compute of the next.  Embedding, block norms and the head are replicated.
+SSD group, conv / SSD / gated norm local, block-diagonal Hadamard, out_proj row-parallel); the only exchange is the sum of
+the (tokens, 4096) fp16 layer output per layer, issued per chunk of sequences so that the transfer of one chunk overlaps
+the compute of the next: by default as partial sums sent to the owners of their token rows, a block norm on those rows and
+int8 rows sent to everybody, moved by copy engines into peer memory (``--exchange peer``) or by NCCL's reduce-scatter and
+all-gather (``--exchange nccl``); ``--plain-allreduce`` is one NCCL all-reduce per layer with a replicated block norm.
 
 The model is built layer by layer (float layer -> calibration taps on the running calibration batch -> quantise -> cut
 this rank's shard -> drop the rest), identically on every rank from one seed.
