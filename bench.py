@@ -457,6 +457,8 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="--gpus >= 2: who moves the bytes of the token-sharded layer exchange: NCCL reduce-scatter / all-gather kernels, or "
                     "copy-engine puts into peer memory with flags and bounded waits (quamba_b200/peer.py)")
+    ap.add_argument("--peer-lag", type=int, default=0, help="--exchange peer: shard tasks of other chunks between a partial output and the "
+                    "norm that consumes it (0: half the number of chunks)")
     ap.add_argument("--chunk-seqs", type=int, default=0, help="head-parallel prefill: sequences per chunk (0: 8 on several GPUs, 4 on one)")
     ap.add_argument("--seqlen", type=int, default=PROMPT)
     ap.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)

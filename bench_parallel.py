@@ -89,6 +89,7 @@ def run(args, rank, local_rank, world, layers=None):
     stack.token_sharded_norm = not getattr(args, "plain_allreduce", False)
     stack.exchange = getattr(args, "exchange", "peer") if world > 1 and stack.token_sharded_norm else "nccl"
     chunk_seqs = getattr(args, "chunk_seqs", 0) or (8 if world > 1 else 4)
+    stack.peer_lag = getattr(args, "peer_lag", 0) or None
     fallback = None
     if stack.exchange == "peer":
         # map the peers' memory now; if any rank cannot (no IPC between the processes, say), every rank takes the NCCL exchange
