@@ -561,6 +561,10 @@ int qb_i8_mma_peak(int groups, int repeats, void* stream, double* tops, double* 
  * scale = max(y) / 127 written to dyn_scale[group * rows + row] (the reference takes the maximum of y,
  * not of |y|, over a power-of-two block padded with zeros; reproduced);  2: fp16.
  * Row strides in elements.  group_size * 2 must stay below 64 KB as in the reference.
+ * qb_rmsnorm_quant only, n_partials > 1 (no reference counterpart; the reduce half of a head-parallel layer's exchange
+ * fused into the block norm): the input row is fp16(sum over p < n_partials of partial p), the sum taken in fp32 in the
+ * order p = 0, 1, ...; partial p is x + p * partial_stride (elements), except p == own_index when own_partial != NULL,
+ * which is read from own_partial (same row stride as x).  0 or 1: x alone.
  * ------------------------------------------------------------------------------------------ */
 typedef struct {
   const void* x;
@@ -587,6 +591,10 @@ typedef struct {
   float eps;
   float out_scale;
   float z_scale;
+  int32_t n_partials;
+  int32_t own_index;
+  int64_t partial_stride;
+  const void* own_partial;
 } qb_rmsnorm_args;
 int qb_rmsnorm_quant(const qb_rmsnorm_args* a, void* stream);
 int qb_rmsnorm_gated(const qb_rmsnorm_args* a, void* stream);

@@ -25,6 +25,9 @@ struct NormParams {
   int M, N, ngroups;      // N: elements per normalised segment
   int res_f32, res_out_f32, out_kind, gate_first, rms, pad_zero;
   int early;              // let the next programmatic launch start while this kernel runs (early_overlap())
+  int n_partials, own_index;       // > 1: x is the fp16-rounded fp32 sum of n_partials inputs
+  int64_t partial_stride;          // partial p at x + p * partial_stride, p == own_index at own (when given)
+  const __half* own;
   float eps, out_scale, z_scale;
 };
 
@@ -101,6 +104,32 @@ norm_quant_kernel(const NormParams p) {
   if (GATE != 0) {
 #pragma unroll
     for (int i = 0; i < CH; ++i) zr[i] = ld_act(reinterpret_cast<const uint2*>(p.z + (int64_t)row * p.z_stride + col0) + cc[i]);
+  }
+  if (GATE == 0 && p.n_partials > 1) {
+    float xs[CH][8];
+#pragma unroll 1
+    for (int s = 0; s < p.n_partials; ++s) {
+      const __half* base = (s == p.own_index && p.own != nullptr) ? p.own : p.x + (int64_t)s * p.partial_stride;
+      uint4 t[CH];
+#pragma unroll
+      for (int i = 0; i < CH; ++i) t[i] = ld_act(reinterpret_cast<const uint4*>(base + (int64_t)row * p.x_stride + col0) + cc[i]);
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const __half2* h = reinterpret_cast<const __half2*>(&t[i]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h[e]);
+          xs[i][2 * e] = s == 0 ? f.x : xs[i][2 * e] + f.x;
+          xs[i][2 * e + 1] = s == 0 ? f.y : xs[i][2 * e + 1] + f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      __half2* h = reinterpret_cast<__half2*>(&xr[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(xs[i][2 * e], xs[i][2 * e + 1]);
+    }
   }
   float v[CH][8];
   if (GATE == 0 && p.residual != nullptr && p.res_f32) {
@@ -239,6 +268,14 @@ __global__ void __launch_bounds__(256) norm_quant_generic_kernel(const NormParam
   const int64_t col0 = (int64_t)grp * p.N;
   auto load = [&](int j, float& zsig) {
     float x = __half2float(ld_act(p.x + (int64_t)row * p.x_stride + col0 + j));
+    if (p.n_partials > 1) {
+      float acc = 0.f;
+      for (int s = 0; s < p.n_partials; ++s) {
+        const __half* base = (s == p.own_index && p.own != nullptr) ? p.own : p.x + (int64_t)s * p.partial_stride;
+        acc += __half2float(ld_act(base + (int64_t)row * p.x_stride + col0 + j));
+      }
+      x = __half2float(__float2half_rn(acc));
+    }
     if (p.residual != nullptr)
       x += p.res_f32 ? ld_act(static_cast<const float*>(p.residual) + (int64_t)row * p.res_stride + col0 + j)
                      : __half2float(ld_act(static_cast<const __half*>(p.residual) + (int64_t)row * p.res_stride + col0 + j));
@@ -328,6 +365,7 @@ int run_norm(const NormParams& p, cudaStream_t st) {
   if (p.residual) vec = vec && aligned(p.residual, 16) && p.res_stride % 8 == 0;
   if (p.residual_out) vec = vec && aligned(p.residual_out, 16) && p.res_out_stride % 8 == 0;
   if (p.z) vec = vec && aligned(p.z, 8) && p.z_stride % 8 == 0;
+  if (p.n_partials > 1) vec = vec && p.partial_stride % 8 == 0 && (p.own == nullptr || aligned(p.own, 16));
   if (!vec) {
     QB_REQUIRE(units < (1ll << 31), QB_ERR_TOO_LARGE, "norm: too many rows");
     launch_dependent(norm_quant_generic_kernel, dim3((unsigned)units), dim3(256), 0, st, p);
@@ -385,6 +423,12 @@ int check_and_run(const qb_rmsnorm_args* a, bool gated, void* stream) {
   p.eps = a->eps; p.out_scale = a->out_scale; p.z_scale = a->z_scale;
   // a dynamic-scale norm writes the per-row scales the next product reads through L1: no early start after it
   p.early = early_overlap() && a->dyn_scale == nullptr ? 1 : 0;
+  QB_REQUIRE(a->n_partials >= 0 && a->n_partials <= 64 && (a->n_partials <= 1 || !gated), QB_ERR_INVALID_ARG,
+             "%s: n_partials = %d (the gated norm takes one input)", who, a->n_partials);
+  QB_REQUIRE(a->n_partials <= 1 || (a->partial_stride >= 0 && a->own_index >= -1 && a->own_index < a->n_partials), QB_ERR_INVALID_ARG,
+             "%s: bad partial layout", who);
+  p.n_partials = a->n_partials; p.own_index = a->own_index; p.partial_stride = a->partial_stride;
+  p.own = a->n_partials > 1 ? static_cast<const __half*>(a->own_partial) : nullptr;
   return run_norm(p, (cudaStream_t)stream);
 }
 

@@ -36,7 +36,10 @@ class QRMSNorm(_FloatStateMixin, nn.Module):
         return q
 
     @torch.no_grad()
-    def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False, **kwargs):
+    def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False, partials=None, out=None, **kwargs):
+        """``partials`` (head-parallel exchange): (slots (n, rows, d) fp16, own_index, own or None); x is then slots[0] and
+        the normalised input is the fp16-rounded sum of the slots (see ops._qlayer_norm_fwd).  ``out``: an int8 tensor of x's
+        shape that receives the result instead of a new one."""
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         if x2.stride(-1) != 1:
@@ -49,7 +52,8 @@ class QRMSNorm(_FloatStateMixin, nn.Module):
         residual_dtype = residual.dtype if residual is not None else (torch.float32 if residual_in_fp32 else None)
         y, residual_out, per_token = ops._qlayer_norm_fwd(x2, self.weight, self.bias, self.eps, residual,
                                                           static_out_scale=self.output_scale,
-                                                          residual_dtype=residual_dtype, is_rms_norm=True)
+                                                          residual_dtype=residual_dtype, is_rms_norm=True, partials=partials,
+                                                          out=None if out is None else out.reshape(-1, shape[-1]))
         y, residual_out = y.reshape(shape), residual_out.reshape(shape)
         if self.output_scale is not None:
             return y if not prenorm else (y, residual_out)

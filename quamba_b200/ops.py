@@ -690,7 +690,11 @@ class quant_linear_cuda:
 
 # ------------------------------------------------------------------------------------------------
 def _norm_call(fn, x, weight, bias, eps, residual, residual_out, q_z, z_scale, out, dyn, group_size, ngroups, out_kind,
-               out_scale, norm_before_gate, is_rms_norm):
+               out_scale, norm_before_gate, is_rms_norm, partials=None):
+    extra = {}
+    if partials is not None:          # (n, stride in elements, index of the partial read from ``own``, own or None)
+        n_p, stride_p, own_i, own = partials
+        extra = dict(n_partials=n_p, partial_stride=stride_p, own_index=own_i if own is not None else -1, own_partial=_p(own))
     args = _lib.make(
         "qb_rmsnorm_args", x=_p(x), residual=_p(residual), residual_out=_p(residual_out), z=_p(q_z), weight=_p(weight),
         bias=_p(bias), out=_p(out), dyn_scale=_p(dyn), x_row_stride=x.stride(0),
@@ -701,12 +705,22 @@ def _norm_call(fn, x, weight, bias, eps, residual, residual_out, q_z, z_scale, o
         residual_is_f32=int(residual is not None and residual.dtype == torch.float32),
         residual_out_is_f32=int(residual_out is not None and residual_out.dtype == torch.float32), out_kind=out_kind,
         norm_before_gate=int(bool(norm_before_gate)), is_rms_norm=int(bool(is_rms_norm)), eps=float(eps),
-        out_scale=float(out_scale), z_scale=float(z_scale))
+        out_scale=float(out_scale), z_scale=float(z_scale), **extra)
     _run(fn, args, x)
 
 
-def _qlayer_norm_fwd(x, weight, bias, eps, residual=None, static_out_scale=None, residual_dtype=None, is_rms_norm=False):
-    """quamba/triton/quant_norm.py:134-206: returns (y int8, residual_out, per_token_scale or None)."""
+def _qlayer_norm_fwd(x, weight, bias, eps, residual=None, static_out_scale=None, residual_dtype=None, is_rms_norm=False,
+                     partials=None, out=None):
+    """quamba/triton/quant_norm.py:134-206: returns (y int8, residual_out, per_token_scale or None).  ``partials`` (not in
+    the reference): (slots, own_index, own) with slots fp16 (n, M, N) -- the input is then the fp16-rounded fp32 sum of
+    the n slots, slot ``own_index`` read from the (M, N) tensor ``own`` when that is given; ``x`` must be ``slots[0]``."""
+    if partials is not None:
+        slots, own_i, own = partials
+        _req(slots.dim() == 3 and slots.dtype == torch.float16 and slots[0].is_contiguous() and x.data_ptr() == slots.data_ptr(),
+             "partials: fp16 (n, M, N) slots with contiguous rows, x = slots[0]")
+        _req(own is None or (own.shape == x.shape and own.dtype == torch.float16 and own.stride() == x.stride()),
+             "partials: own piece must have the shape and strides of a slot")
+        partials = (slots.shape[0], slots.stride(0), own_i, own)
     _req(x.is_cuda and x.dtype == torch.float16 and x.dim() == 2, "x must be a 2-D float16 CUDA tensor")
     _req(x.stride(-1) == 1, "x must be contiguous in its last dim")
     M, N = x.shape
@@ -718,7 +732,10 @@ def _qlayer_norm_fwd(x, weight, bias, eps, residual=None, static_out_scale=None,
         _req(residual.dtype in (torch.float16, torch.float32), "residual must be float16 or float32")
         residual_dtype = residual.dtype
     _req(N * x.element_size() < 65536, "This layer norm doesn't support feature dim >= 64KB.")
-    y = torch.empty((M, N), dtype=torch.int8, device=x.device)
+    if out is not None:               # not in the reference: the int8 rows land in a caller's buffer (rows contiguous)
+        _req(out.dtype == torch.int8 and tuple(out.shape) == (M, N) and out.stride(-1) == 1 and out.device == x.device,
+             "out must be an int8 (M, N) tensor on x's device, contiguous in its last dim")
+    y = out if out is not None else torch.empty((M, N), dtype=torch.int8, device=x.device)
     residual_out = None
     if residual is not None or (residual_dtype is not None and residual_dtype != x.dtype):
         _req(residual_dtype in (torch.float16, torch.float32), "residual_dtype must be float16 or float32")
@@ -727,7 +744,7 @@ def _qlayer_norm_fwd(x, weight, bias, eps, residual=None, static_out_scale=None,
     dyn = None if static else torch.empty((M,), dtype=torch.float32, device=x.device)
     if M > 0:
         _norm_call("qb_rmsnorm_quant", x, weight, bias, eps, residual, residual_out, None, 0.0, y, dyn, N, 1,
-                   0 if static else 1, static_out_scale if static else 0.0, True, is_rms_norm)
+                   0 if static else 1, static_out_scale if static else 0.0, True, is_rms_norm, partials=partials)
     return y, (residual_out if residual_out is not None else x), dyn
 
 

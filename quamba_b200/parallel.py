@@ -300,28 +300,28 @@ class HeadParallelStack:
         e0 = self._peer_epoch
         if collective:
             self._peer_epoch += L
-        dummy_q = dummy_p = None
+        dummy_p = None
         if not compute:
-            dummy_q = torch.zeros((per, d), dtype=torch.int8, device=self.dev)
             dummy_p = torch.zeros((rows, d), dtype=torch.float16, device=self.dev)
+
+        held = [None] * n                  # a chunk's partial output stays alive until the next layer's norm has read this rank's piece
 
         def task_a(k):
             li, c = divmod(k, n)
-            if li > 0:
-                if collective:
-                    ex.wait_partials(c, e0 + li)
-                    if compute:
-                        hs[c] = ex.reduce(c)
-            if li == L:                    # past the last layer: only the sum of its output
+            fused = None
+            if li > 0 and collective:
+                ex.wait_partials(c, e0 + li)
+                if compute and li == L:    # past the last layer: only the sum of its output (its own piece was copied too)
+                    hs[c] = ex.reduce(c)
+                elif compute:              # the norm sums the T slots itself and reads this rank's piece where shard left it
+                    hs[c], fused = ex.recv[c][0], (ex.recv[c], rank, held[c][mine])
+            if li == L:
                 return
-            q = None
+            q = ex.rows_int8[c][mine]      # the int8 rows are written straight into this rank's block of the gathered buffer
             if compute:
-                q, res[c] = self.norms[li](hs[c], residual=res[c], prenorm=True, residual_in_fp32=True)
-                q = q.contiguous()
+                _, res[c] = self.norms[li](hs[c], residual=res[c], prenorm=True, residual_in_fp32=True, partials=fused, out=q)
             if collective:
-                ex.put_rows(c, q if compute else dummy_q, e0 + li + 1)
-            elif compute:
-                ex.rows_int8[c][mine].copy_(q)
+                ex.put_rows(c, q, e0 + li + 1, own=False)
 
         def task_b(k):
             li, c = divmod(k, n)
@@ -333,7 +333,8 @@ class HeadParallelStack:
                 if not partial.is_contiguous():
                     partial = partial.contiguous()
             if collective:
-                ex.put_partials(c, partial if compute else dummy_p, e0 + li + 1)
+                held[c] = partial
+                ex.put_partials(c, partial if compute else dummy_p, e0 + li + 1, own=li == L - 1)
             elif compute:
                 hs[c] = partial[mine]
 

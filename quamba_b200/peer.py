@@ -184,24 +184,32 @@ class LayerExchange:
             for q in range(T):
                 args.stream_of[q] = self.streams[q].cuda_stream
 
-    def _issue(self, args, src, value):
-        """Behind everything queued so far on the current stream (the producer of ``src``)."""
+    def _issue(self, args, src, value, own):
+        """Behind everything queued so far on the current stream (the producer of ``src``).  ``own`` False: this rank's own
+        piece is not copied (its consumer reads it where it is); the own flag is raised all the same."""
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.region.device))
         args.src, args.value, args.after_event = src.data_ptr(), value & 0xFFFFFFFF, ev.cuda_event
-        _put(args, self.streams[self.rank].cuda_stream)
+        keep = args.dst[self.rank]
+        if not own:
+            args.dst[self.rank] = None
+        try:
+            _put(args, self.streams[self.rank].cuda_stream)
+        finally:
+            args.dst[self.rank] = keep
         for st in self.streams:
             src.record_stream(st)
 
-    def put_partials(self, c, partial, value):
+    def put_partials(self, c, partial, value, own=True):
         """partial: (rows, d) fp16 contiguous, produced on the current stream."""
         assert partial.dtype == torch.float16 and partial.is_contiguous() and partial.numel() == self.rows * self.d
-        self._issue(self._args_partials[c], partial, value)
+        self._issue(self._args_partials[c], partial, value, own)
 
-    def put_rows(self, c, q_rows, value):
-        """q_rows: (rows / T, d) int8 contiguous, this rank's rows, produced on the current stream."""
+    def put_rows(self, c, q_rows, value, own=True):
+        """q_rows: (rows / T, d) int8 contiguous, this rank's rows, produced on the current stream (``own=False`` when it
+        already is this rank's row block of ``rows_int8[c]``)."""
         assert q_rows.dtype == torch.int8 and q_rows.is_contiguous() and q_rows.numel() == self.per * self.d
-        self._issue(self._args_rows[c], q_rows, value)
+        self._issue(self._args_rows[c], q_rows, value, own)
 
     def _wait(self, c, first_word, value):
         f = self._flags[c]

@@ -33,6 +33,33 @@ def test_sum_partials_is_the_fp32_sum_rounded_once(n, shape):
     assert torch.equal(got, acc.half())
 
 
+@pytest.mark.parametrize("n,rows,d,own_i", [(2, 33, 4096, 0), (4, 17, 2560, 3), (8, 9, 4096, 5), (3, 5, 200, None), (2, 4, 100, 1)])
+def test_block_norm_sums_the_partial_slots_itself(n, rows, d, own_i):
+    """QRMSNorm with ``partials``: the input is the fp16-rounded fp32 sum of the slots (one of them read from a tensor of
+    its own) -- bit-identical to sum_partials followed by the plain norm, residual stream and int8 rows written in place."""
+    _cuda()
+    from quamba_b200.norm import QRMSNorm
+    from quamba_b200.peer import sum_partials
+    g = torch.Generator().manual_seed(n * 100 + rows)
+    slots = (torch.randn(n, rows, d, generator=g) * 2).half().cuda()
+    res = torch.randn(rows, d, generator=g).cuda()
+    norm = QRMSNorm(d, eps=1e-5, device="cuda")
+    norm.weight.data = (1 + 0.1 * torch.randn(d, generator=g)).half().cuda()
+    norm.output_scale = 0.05
+    own = None
+    full = slots.clone()
+    if own_i is not None:
+        own = full[own_i].clone()
+        slots[own_i].fill_(777.0)          # the slot of the own piece must not be read
+    want_q, want_res = norm(sum_partials(full), residual=res, prenorm=True, residual_in_fp32=True)
+    out = torch.zeros(rows + 2, d, dtype=torch.int8, device="cuda")
+    got_q, got_res = norm(slots[0], residual=res, prenorm=True, residual_in_fp32=True,
+                          partials=(slots, own_i if own_i is not None else 0, own), out=out[1:-1])
+    assert got_q.data_ptr() == out[1:-1].data_ptr()
+    assert torch.equal(got_q, want_q) and torch.equal(got_res, want_res)
+    assert out[0].abs().max().item() == 0 and out[-1].abs().max().item() == 0
+
+
 def test_puts_flags_and_waits_inside_one_process():
     _cuda()
     from quamba_b200 import _lib
@@ -52,6 +79,11 @@ def test_puts_flags_and_waits_inside_one_process():
                 assert torch.equal(ex.reduce(c), part)
         # a flag that is already past the value lets the waiter through at once (counters only grow)
         ex.wait_rows(0, 1)
+        # own=False: this rank's piece is not copied, its flag is raised all the same
+        before = ex.recv[0].clone()
+        ex.put_partials(0, before[0] + 1, 4, own=False)
+        ex.wait_partials(0, 4)
+        assert torch.equal(ex.recv[0], before)
         torch.cuda.synchronize()
         _lib.read_device_status(torch.cuda.current_stream().cuda_stream)
     finally:
