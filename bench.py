@@ -286,8 +286,9 @@ def run_head_parallel(args, rank, local_rank, world, pk):
                    "note": "at N = 1 bench.py reports the Mamba2-2.7B line (the metric's own configuration) and carries this workload's "
                            "single-GPU time in its head_parallel_8b key: that is the base of this strong-scaling curve"},
         "head_parallel_8b": r, "clocks": r.get("clocks"),
-        "e2e": {"value": r["value"], "unit": "tok/s", "h2d_bytes_per_step": bp.BATCH * bp.PROMPT * 8, "d2h_bytes_per_step": bp.BATCH * bp.CFG8B["vocab_size"] * 2,
-                "note": "token ids and last-token logits are 1 MB + 16 MB against a step of hundreds of ms: the end-to-end figure equals the device-timed one to three digits"},
+        "e2e": {"value": r["e2e_value"], "unit": "tok/s", "ms_per_step": r["e2e_ms_per_step"], "h2d_bytes_per_step": bp.BATCH * bp.PROMPT * 8,
+                "d2h_bytes_per_step": bp.BATCH * bp.CFG8B["vocab_size"] * 2,
+                "note": "every rank copies the token ids from pinned host memory and its last-token logits back to pinned host memory inside the timed region"},
         "gpu_launches": args.steps * r["layers"] * (bp.BATCH // r["chunk_sequences"]) * 8,
         "roofline": {"kernel": "gemm_s8_tcgen05 (in_proj + out_proj shards)", "bound": "tensor", "achieved": r["gemm_tops_per_gpu"], "peak": pk["i8"],
                      "unit": "TOP/s", "frac": r["gemm_tops_per_gpu"] / pk["i8"], "traffic": None, "peak_source": pk["i8_source"],

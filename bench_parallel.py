@@ -127,6 +127,23 @@ def run(args, rank, local_rank, world, layers=None):
         barrier()
         return e0.elapsed_time(e1) / steps
 
+    def timed_e2e(steps):
+        """The same step from pinned host token ids to last-token logits in pinned host memory, both copies inside the
+        timed region."""
+        host_ids = [i.cpu().pin_memory() for i in ids]
+        dev_ids = torch.empty_like(ids[0])
+        host_logits = torch.empty((BATCH, cfg["vocab_size"]), dtype=torch.float16).pin_memory()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(steps):
+            dev_ids.copy_(host_ids[i % 2], non_blocking=True)
+            out = stack.prefill(dev_ids, chunk_seqs)
+            host_logits.copy_(out, non_blocking=True)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
     # Room for the collective: the compute kernels are persistent (one CTA per SM), so with the whole GPU taken NCCL's CTAs
     # get an SM only when a kernel ends, and once they are in, the next persistent grid runs in two waves.  The library
     # sizes its grids for all but COMM_SMS multiprocessors and NCCL is capped at as many CTAs (NCCL_MAX_CTAS, set by
@@ -162,7 +179,8 @@ def run(args, rank, local_rank, world, layers=None):
     clocks = sampler.stop() if rank == 0 else None
     ms_compute = timed(max(1, steps // 2), collective=False)
     ms_comm = timed(max(1, steps // 2), compute=False) if world > 1 else 0.0
-    ms_step, ms_compute, ms_comm = max_over_ranks([ms_step, ms_compute, ms_comm], device=dev)
+    ms_e2e = timed_e2e(max(1, steps // 2))
+    ms_step, ms_compute, ms_comm, ms_e2e = max_over_ranks([ms_step, ms_compute, ms_comm, ms_e2e], device=dev)
     _lib.read_device_status(torch.cuda.current_stream().cuda_stream)     # a wait that gave up would have left its code here
     barrier()
     stack.close()
@@ -174,6 +192,7 @@ def run(args, rank, local_rank, world, layers=None):
     reduce_bytes = cfg["n_layer"] * tokens * cfg["d_model"] * 2
     link_factor = ((world - 1) / world * 1.5 if stack.token_sharded_norm else 2 * (world - 1) / world) if world > 1 else 0.0
     return {"value": tokens / (ms_step * 1e-3), "unit": "tok/s", "ms_per_step": ms_step, "compute_only_ms": ms_compute,
+            "e2e_ms_per_step": ms_e2e, "e2e_value": tokens / (ms_e2e * 1e-3),
             "allreduce_alone_ms": ms_comm, "allreduce_exposed_ms": max(0.0, ms_step - ms_compute) if world > 1 else 0.0,
             "allreduce_share_of_step": max(0.0, ms_step - ms_compute) / ms_step if world > 1 else 0.0,
             "allreduce_bytes_per_step": reduce_bytes if world > 1 else 0,
