@@ -231,6 +231,23 @@ def op_rmsnorm(dev, gen, ops):
                 bytes=by, flops=0, nsets=n, make=mk, kernel="norm_quant_kernel<2, 0, 5>", launches=1)
 
 
+def op_rmsnorm_partials(dev, gen, ops):
+    """The block norm of a head-parallel layer at eight ranks: sums the eight received fp16 slots of this rank's rows itself."""
+    T, M, N = 8, 4096, 4096
+    by = M * N * (2 * T + 4 + 4 + 1)
+    n = _sets_for(by)
+    w = torch.ones(N, dtype=torch.float16, device=dev)
+    xs = [torch.randn((T, M, N), device=dev, generator=gen).half() for _ in range(n)]
+    rs = [torch.randn((M, N), device=dev, generator=gen) for _ in range(n)]
+
+    def mk(i):
+        return lambda: ops._qlayer_norm_fwd(xs[i][0], w, None, 1e-5, rs[i], static_out_scale=0.03, is_rms_norm=True,
+                                            partials=(xs[i], 0, None))
+    return dict(workload=f"QRMSNorm + residual add over the sum of {T} partial inputs (head-parallel Mamba2-8B at eight ranks, one chunk's rows "
+                         f"of one rank): M{M} N{N}, {T} fp16 slots, fp32 residual in and out, int8 out",
+                bytes=by, flops=0, nsets=n, make=mk, kernel="norm_quant_kernel<4, 0, 4> (n_partials = 8)", launches=1)
+
+
 def op_rmsnorm_gated(dev, gen, ops):
     M, N = 2048, 5120
     by = M * N * (2 + 1 + 2)
@@ -358,7 +375,8 @@ def op_w8a8(dev, gen, ops):
 
 OPS = {"conv": op_conv, "conv_update": op_conv_update, "hadamard": op_hadamard, "sscan": op_sscan, "ssd": op_ssd,
        "ssd_update": op_ssd_update, "w4a8_in_proj": op_w4a8_in, "w4a8_out_proj": op_w4a8_out,
-       "w4a8_in_proj_b1": op_w4a8_in_b1, "w4a8_out_proj_b1": op_w4a8_out_b1, "rmsnorm": op_rmsnorm, "rmsnorm_gated": op_rmsnorm_gated, "w4a8_decode": op_w4a8_decode, "w4a8_decode_pc": op_w4a8_decode_pc, "w4a8_decode_b64": op_w4a8_decode_b64,
+       "w4a8_in_proj_b1": op_w4a8_in_b1, "w4a8_out_proj_b1": op_w4a8_out_b1, "rmsnorm": op_rmsnorm, "rmsnorm_partials": op_rmsnorm_partials,
+       "rmsnorm_gated": op_rmsnorm_gated, "w4a8_decode": op_w4a8_decode, "w4a8_decode_pc": op_w4a8_decode_pc, "w4a8_decode_b64": op_w4a8_decode_b64,
        "decode_in_proj": op_decode_in_proj, "decode_update": op_decode_update, "decode_gate_had": op_decode_gate_had,
        "decode_out_proj": op_decode_out_proj, "w8a8": op_w8a8}
 
