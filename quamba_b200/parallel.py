@@ -22,7 +22,8 @@ from .mixer import W4A8QMamba2, _QMamba2
 from .modules import QHadamard, Quamb2Conv1D, Quamba2ChunkScan, W4A8B8O8LinearParallel, W4A8B16O16Linear
 from .norm import QRMSNormGated
 
-__all__ = ["shard_w4a8_columns", "shard_w4a8_rows", "shard_mixer", "HeadParallelMixer", "HeadParallelStack", "rank_columns"]
+__all__ = ["shard_w4a8_columns", "shard_w4a8_rows", "shard_mixer", "HeadParallelMixer", "HeadParallelStack", "rank_columns",
+           "peer_task_order"]
 
 
 def _codes(lin):
@@ -125,6 +126,31 @@ def shard_mixer(m: W4A8QMamba2, rank: int, world: int):
     s.norm = sn
     s.had = QHadamard(D, x_H_scale=m.had.x_H_scale, blocks=blocks // T)
     return s
+
+
+def peer_task_order(n_layers, n_chunks, lag=None):
+    """The issue order of the peer-memory prefill's tasks as a list of ("A" | "B", k), k = layer * n_chunks + chunk.
+
+    A(k) = [sum of the partial outputs of B(k - n_chunks) ->] block norm of layer k // n_chunks on chunk k % n_chunks, then the
+    put of its int8 rows (k up to n_layers * n_chunks + n_chunks - 1: the last n_chunks only sum the last layer's output);
+    B(k) = the layer shard on the gathered rows of A(k), then the put of its partial output.  The order keeps A(k) before
+    B(k) and B(k - n_chunks) before A(k), and skews the two so that a transfer has other chunks' compute to hide behind:
+    A(k) comes ``lag`` B tasks after B(k - n_chunks) and B(k) comes n_chunks - lag - 1 B tasks after A(k)
+    (``lag`` None: half the chunks; clipped to [1, n_chunks - 1])."""
+    n = n_chunks
+    if lag is None:
+        lag = max(1, n // 2)
+    lead = max(1, n - min(max(1, lag), n - 1)) if n > 1 else 1
+    total_a, total_b = (n_layers + 1) * n, n_layers * n
+    order = [("A", k) for k in range(min(lead, total_a))]
+    next_a = len(order)
+    for j in range(total_b):
+        order.append(("B", j))
+        if j + lead < total_a:
+            order.append(("A", j + lead))
+            next_a = j + lead + 1
+    order.extend(("A", k) for k in range(next_a, total_a))
+    return order
 
 
 class HeadParallelMixer(nn.Module):
@@ -338,21 +364,8 @@ class HeadParallelStack:
             elif compute:
                 hs[c] = partial[mine]
 
-        lag = self.peer_lag if self.peer_lag is not None else max(1, n // 2)
-        lead = max(1, n - min(lag, n - 1)) if n > 1 else 1
-        total_a, total_b = (L + 1) * n, L * n
-        next_a = 0
-        for k in range(min(lead, total_a)):
-            task_a(k)
-            next_a = k + 1
-        for j in range(total_b):
-            task_b(j)
-            if j + lead < total_a:
-                assert next_a == j + lead
-                task_a(j + lead)
-                next_a = j + lead + 1
-        for k in range(next_a, total_a):
-            task_a(k)
+        for kind, k in peer_task_order(L, n, self.peer_lag):
+            (task_a if kind == "A" else task_b)(k)
         if not compute:
             return None
         return self._last_token_logits(chunks, hs, res, per, collective)

@@ -89,3 +89,25 @@ def test_peer_memory_setup_fails_on_every_rank_together(tmp_path):
     mp.spawn(_peer_setup_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     a, b = ((tmp_path / f"peer{r}.txt").read_text() for r in (0, 1))
     assert a.startswith("peer memory set-up failed") and a == b
+
+
+@pytest.mark.parametrize("n_layers,n_chunks,lag", [(1, 1, None), (3, 1, 2), (4, 2, None), (5, 3, 1), (5, 4, None), (5, 4, 1), (5, 4, 3),
+                                                    (3, 8, None), (3, 8, 7), (2, 4, 9)])
+def test_peer_task_order_respects_the_data_flow(n_layers, n_chunks, lag):
+    """Every task exactly once; the norm of a (layer, chunk) before its shard; a shard before the norm that consumes its
+    partial output one layer later; and the skew: ``lag`` shard tasks between a partial output and its norm."""
+    from quamba_b200.parallel import peer_task_order
+    order = peer_task_order(n_layers, n_chunks, lag)
+    pos = {t: i for i, t in enumerate(order)}
+    n = n_chunks
+    assert len(order) == len(pos) == (2 * n_layers + 1) * n
+    assert set(pos) == {("A", k) for k in range((n_layers + 1) * n)} | {("B", k) for k in range(n_layers * n)}
+    for k in range(n_layers * n):
+        assert pos[("A", k)] < pos[("B", k)]
+        assert pos[("B", k)] < pos[("A", k + n)]
+    if n > 1 and n_layers >= 3:
+        eff = min(max(1, n // 2 if lag is None else lag), n - 1)
+        k = 2 * n + 1
+        between = lambda a, b: sum(1 for t in order[pos[a] + 1:pos[b]] if t[0] == "B")
+        assert between(("B", k - n), ("A", k)) == eff
+        assert between(("A", k), ("B", k)) == n - eff - 1
