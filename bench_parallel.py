@@ -207,8 +207,8 @@ def run(args, rank, local_rank, world, layers=None):
             # the same seed builds the same model on any number of GPUs: these must agree between N = 1 and N > 1
             "logits_digest": {"argmax": logits.argmax(-1).tolist(), "row0_first8": [round(v, 4) for v in logits[0, :8].float().tolist()],
                               "abs_sum": round(logits.float().abs().sum().item(), 2)},
-            "collective": (("copy-engine puts into peer memory (fp16 partial sums by owner, int8 rows to all), flags, bounded waits and "
-                            "a local sum, around a token-sharded block norm") if peer else
+            "collective": (("copy-engine puts into peer memory (fp16 partial sums by owner, int8 rows to all), flags, bounded waits; the "
+                            "token-sharded block norm sums the received pieces itself") if peer else
                            "reduce-scatter (fp16) + all-gather (int8) around a token-sharded block norm" if stack.token_sharded_norm
                            else "all-reduce (fp16)") if world > 1 else None,
             "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}
