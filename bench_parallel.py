@@ -211,4 +211,5 @@ def run(args, rank, local_rank, world, layers=None):
                             "token-sharded block norm sums the received pieces itself") if peer else
                            "reduce-scatter (fp16) + all-gather (int8) around a token-sharded block norm" if stack.token_sharded_norm
                            else "all-reduce (fp16)") if world > 1 else None,
-            "limiting": "the per-layer all-reduce of the (tokens, 4096) fp16 output over NVLink" if world > 1 else "compute"}
+            "limiting": ("the per-layer exchange of the (tokens, 4096) layer output over NVLink: fp16 partial sums to the owners of their token rows, "
+                         "int8 rows to every rank (at eight ranks the exchange alone takes longer than the compute alone)") if world > 1 else "compute"}
